@@ -1,0 +1,186 @@
+/* libmycaffe_attn -- C ABI of the B200 (sm_100a) attention library.
+ *
+ * Two layers, both plain C:
+ *
+ *  1. The reference's own dispatch ABI.  MyCaffe's C# CudaDnn<T> reaches native code through
+ *     DLL_Invoke* with a kernel index, a function id and packed float / long arrays
+ *     (CudaDnnDLL/CudaDnnDLL.cpp:134,314,495).  This library exports the same entry points with
+ *     the same argument packing, error codes and handle semantics for the function ids on the
+ *     attention path (and the few memory ids needed to own the handles), so a host binding for
+ *     CudaDnnDLL binds this library unchanged.
+ *
+ *  2. Raw entry points (mca_*) that take device pointers, sizes and a CUDA stream.  The
+ *     dispatch layer calls these; a host that owns its device memory may call them directly.
+ *
+ * Every function returns 0 on success, a CUDA runtime error code, or one of the ERROR_*
+ * codes of the reference (CudaDnnDLL/Cuda Files/util.h:128-211; 90000-based).  There is no CPU
+ * fallback anywhere: without a compute-capability-10.x device the calls fail.
+ *
+ * Paths in comments are relative to the reference project root.
+ */
+#ifndef MYCAFFE_ATTN_H_
+#define MYCAFFE_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define MCA_API __declspec(dllexport)
+#else
+#define MCA_API __attribute__((visibility("default")))
+#endif
+
+/* Windows types of the reference ABI.  LONG is 32-bit on Windows; LPTSTR is a char string
+ * here (the ANSI build of the reference). */
+typedef int32_t MCA_LONG;
+typedef int64_t MCA_LONGLONG;
+typedef char* MCA_LPTSTR;
+
+/* ---- function ids honoured by DLL_Invoke* --------------------------------------------- */
+/* Cuda Files/main.h:23-32 */
+#define CUDA_DLL_FREEMEM (-1)      /* free a pinned result buffer returned through ppOutput */
+#define CUDA_DLL_INITIALIZE (-2)   /* floats {deviceId, flags} -> out[0] = kernel index */
+#define CUDA_DLL_CLEANUP (-3)
+/* inc/FunctionIDs.h:71-95,126-127,222-226,532-535 */
+#define CUDA_FN_SETDEVICE 1
+#define CUDA_FN_SYNCHRONIZEDEVICE 5
+#define CUDA_FN_ALLOCMEM 20        /* longs {count[,hStream]}, floats {count, data...}? -> out[0] = handle (device.cu:854-899) */
+#define CUDA_FN_FREEMEM 21         /* longs {h} */
+#define CUDA_FN_GETMEM 22          /* longs {h[,count]} -> floats (device.cu:973-1026) */
+#define CUDA_FN_SETMEM 23          /* longs {h,count}, floats {h,count,data...} (device.cu:1029) */
+#define CUDNN_FN_CREATE_CUDNN 47   /* -> out[0] = hCuDnn (passed through by ATTN_*) */
+#define CUDNN_FN_FREE_CUDNN 48
+#define CUDNN_FN_ATTN_CREATE 160   /* -> out[0] = hAttn                      (device.h:2435-2448) */
+#define CUDNN_FN_ATTN_FREE 161     /* floats {hAttn}                          (device.h:2450-2461) */
+#define CUDNN_FN_ATTN_SET 162      /* floats {dropout}; longs {hCuDnn,hAttn,gpuId,bTraining,B,blockSize,H,D,seed}
+                                      (device.h:2463-2486) + optional 10th long: MCA_DTYPE_*, 11th: MCA_FLAG_* */
+#define CUDNN_FN_ATTN_FWD 163      /* longs {hCuDnn,hAttn,T,hQ,hK,hV,hMask,hY,bBatchMask}   (device.h:2488-2506) */
+#define CUDNN_FN_ATTN_BWD 164      /* longs {hCuDnn,hAttn,hQ,hdQ,hK,hdK,hV,hdV,hMask,hY,hdY} (device.h:2508-2529) */
+#define CUDA_FN_CREATE_ROPE 980    /* floats {theta}; longs {sharedIdx,gpuId,count,B,T,H,D} -> hRope (device.h:4200-4228) */
+#define CUDA_FN_FREE_ROPE 981      /* floats {hRope} */
+#define CUDA_FN_ROPE_FWD 982       /* longs {hRope,n,hX,hY[,freqOffset]}      (device.h:4243-4265) */
+#define CUDA_FN_ROPE_BWD 983       /* longs {hRope,n,hX,hYdiff,hXdiff}        (device.h:4267-4283) */
+/* Ids added by this library (no counterpart in the reference; above its highest id). */
+#define MCA_FN_ALLOCMEM_BF16 2001  /* longs {count} -> handle to bf16 storage; SETMEM/GETMEM convert from/to float */
+#define MCA_FN_CONVERT 2002        /* longs {hSrc,hDst,count}: copy with float<->bf16 conversion as the handles require */
+#define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode */
+#define MCA_FN_DECODE_FREE 2011    /* floats {hDecode} */
+#define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
+#define MCA_FN_TFT_ATTN_FWD 2020   /* longs {hQ,hK,hV,hMask,B,H,Nq,Nk,d,hOut,hAttn} */
+#define MCA_FN_SET_ASYNC 2030      /* longs {0|1}: 1 = do not synchronise the stream after each call (default 0, as the reference) */
+
+/* 10th long of ATTN_SET */
+#define MCA_DTYPE_F32 0   /* exact fp32 arithmetic on CUDA cores (default; what the reference computes) */
+#define MCA_DTYPE_TF32 1  /* fp32 tensors, tcgen05 kind::tf32 products with fp32 accumulation */
+#define MCA_DTYPE_BF16 2  /* bf16 tensors (handles from MCA_FN_ALLOCMEM_BF16), tcgen05 kind::f16 */
+/* 11th long of ATTN_SET */
+#define MCA_FLAG_CAUSAL_IMPLICIT 1  /* hMask is ignored and the mask is the analytic lower triangle */
+
+/* mask_mode of the raw entry points */
+#define MCA_MASK_MODE_NONE 0
+#define MCA_MASK_MODE_TT 1      /* (T,T) floats, masked where 0 */
+#define MCA_MASK_MODE_BATCH 2   /* (B,T) floats key mask, masked where 0 */
+#define MCA_MASK_MODE_CAUSAL 3  /* analytic lower triangle, mask pointer unused */
+
+/* handle types of Internal_GetPointer* (Cuda Files/memory.h HANDLE_TYPE) */
+#define MCA_HT_MEMORY 1
+
+/* ---- 1. reference dispatch ABI ---------------------------------------------------------- */
+
+/* Replaces DLL_InvokeFloat, CudaDnnDLL/CudaDnnDLL.cpp:134-312. */
+MCA_API MCA_LONG DLL_InvokeFloat(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput,
+                                 float** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+/* Replaces DLL_InvokeFloatEx2, CudaDnnDLL.cpp:314-493 (float + 64-bit integer inputs). */
+MCA_API MCA_LONG DLL_InvokeFloatEx2(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput,
+                                    MCA_LONGLONG* plInput, MCA_LONG llInput, float** ppOutput, MCA_LONG* plOutput,
+                                    MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+/* Replaces DLL_InvokeFloatEx, CudaDnnDLL.cpp:495-672 (string input; no id on this path takes one). */
+MCA_API MCA_LONG DLL_InvokeFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput,
+                                   MCA_LPTSTR pszInput, float** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr,
+                                   MCA_LONG lszErrMax);
+/* The double twins (CudaDnnDLL.cpp:674-853 and following).  The attention path of this
+ * library computes in fp32/tf32/bf16 only: every id returns ERROR_NOT_IMPLEMENTED (90009). */
+MCA_API MCA_LONG DLL_InvokeDouble(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, double* pInput, MCA_LONG lInput,
+                                  double** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+MCA_API MCA_LONG DLL_InvokeDoubleEx2(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, double* pInput, MCA_LONG lInput,
+                                     MCA_LONGLONG* plInput, MCA_LONG llInput, double** ppOutput,
+                                     MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+/* Replaces Internal_GetPointerFloat, CudaDnnDLL.cpp:57-73: raw device pointer behind a memory handle. */
+MCA_API MCA_LONG Internal_GetPointerFloat(MCA_LONG ht, MCA_LONG lKernelIdx, MCA_LONG hHandle, void** ppPtr);
+/* Replaces Internal_AllocHostFloat, CudaDnnDLL.cpp:93-109: pinned host buffer, optionally filled from pSrc. */
+MCA_API MCA_LONG Internal_AllocHostFloat(MCA_LONG lKernelIdx, MCA_LONG lCount, float** ppDst, float* pSrc,
+                                         bool bSrcOnDevice);
+
+/* ---- 2. raw entry points ------------------------------------------------------------------ */
+/* All tensors are contiguous row-major device memory; `stream` is a cudaStream_t (0 = default). */
+
+/* fp32 SDPA forward, exact fp32 arithmetic.  Replaces attnHandle<T>::Forward,
+ * CudaDnnDLL/Cuda Files/attn.cu:518-602.  q,k,v,y: (B,H,T,D), D <= 128.  causal_flag: optional device
+ * int written by mca_classify_causal_mask; when it holds 1 a MASK_MODE_TT mask is treated as causal.
+ * row_max,row_sum: optional (B,H,T) softmax statistics kept for the backward; y_copy: optional
+ * second copy of y kept for the backward. */
+MCA_API int mca_sdpa_forward_f32(const float* q, const float* k, const float* v, const float* mask, int mask_mode,
+                                 const int* causal_flag, int B, int H, int T, int D, float* y, float* row_max,
+                                 float* row_sum, float* y_copy, void* stream);
+/* fp32 SDPA backward.  Replaces attnHandle<T>::Backward, attn.cu:608-661.  Recomputes the
+ * probabilities from row_max/row_sum instead of reading a saved (B,H,T,T) tensor.
+ * delta_scratch: (B,H,T) floats of scratch. */
+MCA_API int mca_sdpa_backward_f32(const float* q, const float* k, const float* v, const float* dy,
+                                  const float* y_saved, const float* mask, int mask_mode, const int* causal_flag,
+                                  const float* row_max, const float* row_sum, float* delta_scratch, int B, int H,
+                                  int T, int D, float* dq, float* dk, float* dv, void* stream);
+/* Writes 1 to *flag iff mask (T,T) equals the lower-triangular ones built by fillMask,
+ * MyCaffe.layers.gpt/layers.gpt/CausalSelfAttentionLayer.cs:276-291; else 0. */
+MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* stream);
+
+/* Tensor-core SDPA forward (tcgen05 + TMEM + TMA).  Same math as attn.cu:518-602 with a causal
+ * or absent mask.  dtype: MCA_DTYPE_BF16 (q,k,v,y bf16) or MCA_DTYPE_TF32 (q,k,v,y fp32).
+ * D in {64,128}; lse: optional (B,H,T) floats, log2-domain log-sum-exp kept for the backward.
+ * status: device int[4] the kernel writes when a bounded wait gives up (0 = ok). */
+MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
+                                int T, int D, void* y, float* lse, int* status, void* stream);
+
+/* RoPE on a (B,T,H,D) tensor.  Replaces RopeDataGpu<T>::Forward/Backward, Cuda Files/rope.cu:784-864.
+ * Tables are (T,D/2) as built by mca_rope_tables_host. */
+MCA_API int mca_rope_f32(const float* x, float* y, int64_t n, int T, int H, int D, const float* cos_table,
+                         const float* sin_table, int freq_offset, int backward, void* stream);
+/* Host-side table construction, rope.cu:501-553 (powf/cosf/sinf in fp32). */
+MCA_API int mca_rope_tables_host(int T, int D, float theta, float* cos_table, float* sin_table);
+
+/* Split-KV decode attention for one new token of B independent sequences.  Replaces
+ * Primitives::rope + the cache append + Primitives::attention of TransformerGpu::forward,
+ * CudaExtension.llm32.llama2/Files/llama2_gpu.cpp:64-75 (kernels primitives.cu:99-202).
+ * q: (B, n_heads*hs) and k_new,v_new: (B, n_kv_heads*hs) are the projections of the new token
+ * before RoPE; caches are (B, seq_len, n_kv_heads*hs) fp32 or bf16 with cache_batch_stride
+ * elements between sequences; row pos[b] is written, rows 0..pos[b] are attended.  max_len
+ * must be >= max_b pos[b]+1.  freq_real/imag: (seq_len, hs/2) or both null (no RoPE, q/k already
+ * rotated).  k_new = v_new = null skips the append.  scratch: floats from mca_decode_plan. */
+MCA_API int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_len, int* split_len,
+                            int* nsplit, int64_t* scratch_floats);
+MCA_API int mca_decode_attention(const float* q, const float* k_new, const float* v_new, void* k_cache,
+                                 void* v_cache, int cache_is_bf16, int64_t cache_batch_stride, const int* pos,
+                                 int B, int n_heads, int n_kv_heads, int head_size, int seq_len, int max_len,
+                                 const float* freq_real, const float* freq_imag, float* scratch,
+                                 int64_t scratch_floats, float* out, void* stream);
+
+/* TFT interpretable attention forward.  Replaces the attention block of
+ * MultiHeadAttentionInterpLayer<T>.forward, MyCaffe.layers.tft/layers.tft/
+ * MultiHeadAttentionInterpLayer.cs:728-759.  q (B,H,Nq,d), k (B,H,Nk,d), v (B,Nk,d) shared by the
+ * heads, mask (Nq,Nk) masked where 1 (or null) -> out (B,Nq,d) = mean_h P_h V, attn (B,Nq,Nk) = mean_h P_h. */
+MCA_API int mca_tft_attention_forward_f32(const float* q, const float* k, const float* v, const float* mask, int B,
+                                          int H, int Nq, int Nk, int d, float* out, float* attn, void* stream);
+
+/* float <-> bf16 copies used at the handle boundary. */
+MCA_API int mca_convert_f32_to_bf16(const float* x, void* y, int64_t n, void* stream);
+MCA_API int mca_convert_bf16_to_f32(const void* x, float* y, int64_t n, void* stream);
+
+/* Library identification: "mycaffe_attn_b200 <version> sm_100a". */
+MCA_API const char* mca_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MYCAFFE_ATTN_H_ */

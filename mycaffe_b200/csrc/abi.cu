@@ -1,0 +1,798 @@
+// The reference's dispatch ABI for the attention path: kernel table, memory-handle table,
+// function-id switch.  Mirrors CudaDnnDLL/CudaDnnDLL.cpp (exports), Cuda Files/main.cu
+// (Kernel<T>::Run switch) and Cuda Files/device.h / device.cu (argument unpacking) for the
+// ids listed in mycaffe_attn.h, and nothing else of that DLL.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <algorithm>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+constexpr int kMaxKernels = 2048;  // Cuda Files/main.h:21
+
+struct MemItem {
+  void* ptr = nullptr;
+  int64_t count = 0;
+  bool bf16 = false;
+  size_t bytes() const { return (size_t)count * (bf16 ? 2 : 4); }
+};
+
+struct AttnHandle {
+  bool configured = false;
+  int B = 0, block = 0, H = 0, D = 0, dtype = MCA_DTYPE_F32, flags = 0;
+  bool training = false;
+  float dropout = 0.f;
+  // owned device buffers, sized at Set for the configured block size
+  float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr, *delta = nullptr, *lse = nullptr;
+  int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
+  // state of the last forward, consumed by backward
+  bool have_fwd = false;
+  int fwd_T = 0, fwd_mask_mode = 0;
+  const float* fwd_mask = nullptr;
+  // mask classification cache
+  const float* cls_mask = nullptr;
+  int cls_T = 0;
+  int cls_host = -1;  // host copy of the flag (-1 unknown)
+  void release() {
+    cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
+    row_max = row_sum = y_copy = delta = lse = nullptr;
+    causal_flag = nullptr;
+    configured = have_fwd = false;
+    cls_mask = nullptr; cls_T = 0; cls_host = -1;
+  }
+};
+
+struct RopeHandle {
+  int B = 0, T = 0, H = 0, D = 0, shared_index = 0, refs = 1;
+  float *cos_t = nullptr, *sin_t = nullptr;
+};
+
+struct DecodeHandle {
+  int B = 0, n_heads = 0, n_kv_heads = 0, hs = 0, seq_len = 0;
+  bool bf16 = false;
+  float *fr = nullptr, *fi = nullptr, *scratch = nullptr;
+  int64_t scratch_floats = 0;
+};
+
+struct Kernel {
+  int device = 0;
+  bool async = false;
+  long next_handle = 1;
+  std::unordered_map<long, MemItem> mem;
+  std::unordered_map<long, AttnHandle> attn;
+  std::unordered_map<long, RopeHandle> rope;
+  std::unordered_map<long, DecodeHandle> decode;
+  std::unordered_map<long, int> cudnn;
+  std::vector<void*> host_bufs;
+  std::string last_detail;
+  float* stage = nullptr;  // grow-only fp32 staging buffer for float <-> bf16 transfers
+  size_t stage_count = 0;
+
+  float* staging(size_t count) {
+    if (count > stage_count) {
+      cudaFree(stage);
+      stage = nullptr;
+      stage_count = 0;
+      if (cudaMalloc(&stage, count * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+      stage_count = count;
+    }
+    return stage;
+  }
+
+  MemItem* get(long h) {
+    auto it = mem.find(h);
+    return it == mem.end() ? nullptr : &it->second;
+  }
+};
+
+Kernel* g_kernels[kMaxKernels];
+std::mutex g_table_lock;
+
+const char* error_name(long e) {
+  switch (e) {
+    case ERROR_DLL_NOT_INIT: return "DLL not initialized";
+    case ERROR_PARAM_OUT_OF_RANGE: return "parameter out of range";
+    case ERROR_PARAM_NULL: return "parameter null";
+    case ERROR_MEMORY_OUT: return "out of memory";
+    case ERROR_NOT_IMPLEMENTED: return "not implemented";
+    case ERROR_MEMORY_RANGE_EXCEEDED: return "memory range exceeded";
+    case ERROR_MEMORY_MIXED_HALF_TYPES: return "memory handle has the wrong element type";
+    case ERROR_MEMORY_NOT_FOUND: return "memory handle not found";
+    case ERROR_MEMORY_TOO_SMALL: return "memory too small";
+    case ERROR_ROPE_NOT_INITIALIZED: return "rope not initialized";
+    case ERROR_ATTN_NOT_INITIALIZED: return "attn not initialized";
+    case ERROR_ATTN + 3: return "attn missing descriptor";
+    case ERROR_ATTN_INCOMPATIBLE_BLOB_SIZE: return "attn incompatible blob size";
+    case ERROR_ATTN_INVALID_BLOCK_SIZE: return "attn invalid block size";
+    case ERROR_ATTN_UNSUPPORTED_SHAPE: return "attn: no sm_100a kernel for this head size / dtype / mask";
+    case ERROR_ATTN_KERNEL_TIMEOUT: return "attn: a bounded device-side wait gave up";
+    case ERROR_ATTN_BACKWARD_WITHOUT_FORWARD: return "attn: backward needs a training-mode forward at the configured block size on the same handle";
+    case ERROR_ATTN_NOT_B200: return "attn: device is not compute capability 10.x";
+    case ERROR_ATTN_SCRATCH_TOO_SMALL: return "attn: scratch too small";
+  }
+  return nullptr;
+}
+
+// getError, CudaDnnDLL.cpp:1727-1745: copy a message for the code into the caller's buffer.
+void get_error(long err, MCA_LPTSTR szErr, MCA_LONG max, const Kernel* k = nullptr) {
+  if (!szErr || max <= 0) return;
+  const char* name = error_name(err);
+  char buf[512];
+  if (name) snprintf(buf, sizeof(buf), "MyCaffe attn (%ld): %s", err, name);
+  else if (err > 0 && err < 2000) snprintf(buf, sizeof(buf), "CUDA (%ld): %s", err, cudaGetErrorString((cudaError_t)err));
+  else snprintf(buf, sizeof(buf), "error %ld", err);
+  if (k && !k->last_detail.empty()) {
+    size_t n = strlen(buf);
+    snprintf(buf + n, sizeof(buf) - n, " [%s]", k->last_detail.c_str());
+  }
+  strncpy(szErr, buf, (size_t)max - 1);
+  szErr[max - 1] = 0;
+}
+
+long verify_in(long n, const void* p, long lo, long hi) {  // Device<T>::verifyInput, device.h:710-740
+  if (n < lo || n > hi) return ERROR_PARAM_OUT_OF_RANGE;
+  if (lo == 0 && hi == 0) return 0;
+  if (p == nullptr) return ERROR_PARAM_NULL;
+  return 0;
+}
+long verify_out(MCA_LONG* plOutput, float** ppOutput) {  // device.h:742-752
+  if (!plOutput || !ppOutput) return ERROR_PARAM_NULL;
+  return 0;
+}
+long set_out(float v, MCA_LONG* plOutput, float** ppOutput) {
+  *plOutput = 1;
+  (*ppOutput)[0] = v;
+  return 0;
+}
+
+long finish(Kernel* k, long err) {
+  if (err) return err;
+  if (!k->async) return (long)cudaStreamSynchronize(0);  // the reference blocks after every op (attn.cu:601)
+  return 0;
+}
+
+long check_f32(Kernel* k, long h, int64_t need, float** out) {
+  MemItem* m = k->get(h);
+  if (!m) return ERROR_MEMORY_NOT_FOUND;
+  if (m->bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
+  if (m->count < need) return ERROR_MEMORY_TOO_SMALL;
+  *out = (float*)m->ptr;
+  return 0;
+}
+long check_any(Kernel* k, long h, int64_t need, bool want_bf16, void** out) {
+  MemItem* m = k->get(h);
+  if (!m) return ERROR_MEMORY_NOT_FOUND;
+  if (m->bf16 != want_bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
+  if (m->count < need) return ERROR_MEMORY_TOO_SMALL;
+  *out = m->ptr;
+  return 0;
+}
+
+// ---- memory ids -------------------------------------------------------------------------
+
+long alloc_mem(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput,
+               float** ppOutput, bool bf16) {
+  long e;
+  if ((e = verify_in(llInput, pl, 1, 2))) return e;
+  if ((e = verify_out(plOutput, ppOutput))) return e;
+  const int64_t count = pl[0];
+  if (count <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  const float* src = nullptr;
+  if (lInput > 1) {  // Device<T>::AllocMemory, device.cu:854-899
+    if (!pf) return ERROR_PARAM_NULL;
+    if (lInput == count + 1) src = pf + 1;
+    else if (lInput == count + 2) src = pf + 2;
+    else return ERROR_PARAM_OUT_OF_RANGE;
+  }
+  MemItem m;
+  m.count = count;
+  m.bf16 = bf16;
+  cudaError_t ce = cudaMalloc(&m.ptr, m.bytes());
+  if (ce != cudaSuccess) { cudaGetLastError(); return ce == cudaErrorMemoryAllocation ? ERROR_MEMORY_OUT : (long)ce; }
+  if (src) {
+    if (!bf16) {
+      if ((ce = cudaMemcpy(m.ptr, src, m.bytes(), cudaMemcpyHostToDevice)) != cudaSuccess) { cudaFree(m.ptr); return ce; }
+    } else {
+      float* tmp = nullptr;
+      if ((ce = cudaMalloc(&tmp, count * 4)) != cudaSuccess) { cudaFree(m.ptr); return ce; }
+      cudaMemcpy(tmp, src, count * 4, cudaMemcpyHostToDevice);
+      mca_convert_f32_to_bf16(tmp, m.ptr, count, 0);
+      cudaStreamSynchronize(0);
+      cudaFree(tmp);
+    }
+  } else {
+    cudaMemsetAsync(m.ptr, 0, m.bytes(), 0);
+  }
+  const long h = k->next_handle++;
+  k->mem[h] = m;
+  return set_out((float)h, plOutput, ppOutput);
+}
+
+long free_mem(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 1, 1))) return e;
+  auto it = k->mem.find((long)pl[0]);
+  if (it == k->mem.end()) return ERROR_MEMORY_NOT_FOUND;
+  cudaFree(it->second.ptr);
+  k->mem.erase(it);
+  return 0;
+}
+
+long alloc_host(Kernel* k, int64_t count, float** dst) {
+  cudaError_t ce = cudaMallocHost((void**)dst, (size_t)count * sizeof(float));
+  if (ce != cudaSuccess) { cudaGetLastError(); return ERROR_MEMORY_OUT; }
+  k->host_bufs.push_back(*dst);
+  return 0;
+}
+
+long copy_to_host(Kernel* k, const MemItem* m, int64_t count, float* dst) {
+  if (!m->bf16) return (long)cudaMemcpy(dst, m->ptr, (size_t)count * 4, cudaMemcpyDeviceToHost);
+  float* tmp = k->staging((size_t)count);
+  if (!tmp) return ERROR_MEMORY_OUT;
+  long e = mca_convert_bf16_to_f32(m->ptr, tmp, count, 0);
+  if (!e) e = (long)cudaMemcpy(dst, tmp, (size_t)count * 4, cudaMemcpyDeviceToHost);
+  return e;
+}
+
+long get_mem(Kernel* k, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput, float** ppOutput) {
+  long e;  // Device<T>::GetMemory, device.cu:973-1026
+  if ((e = verify_in(llInput, pl, 1, 2))) return e;
+  if ((e = verify_out(plOutput, ppOutput))) return e;
+  MemItem* m = k->get((long)pl[0]);
+  if (!m) return ERROR_MEMORY_NOT_FOUND;
+  int64_t count = llInput > 1 ? pl[1] : 0;
+  if (llInput <= 1 || count < 0) count = m->count;
+  else if (count > m->count) return ERROR_PARAM_OUT_OF_RANGE;
+  if (count > 0x7fffffffLL) return ERROR_PARAM_OUT_OF_RANGE;
+  if (count <= *plOutput) {
+    if ((e = copy_to_host(k, m, count, *ppOutput))) return e;
+  } else {
+    float* buf = nullptr;
+    if ((e = alloc_host(k, count, &buf))) return e;
+    if ((e = copy_to_host(k, m, count, buf))) return e;
+    *ppOutput = buf;
+  }
+  *plOutput = (MCA_LONG)count;
+  return 0;
+}
+
+long set_mem(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
+  long e;  // Device<T>::SetMemory, device.cu:1029-1100
+  if ((e = verify_in(lInput, pf, 2, 0x7fffffff))) return e;
+  if ((e = verify_in(llInput, pl, 2, 2))) return e;
+  MemItem* m = k->get((long)pl[0]);
+  if (!m) return ERROR_MEMORY_NOT_FOUND;
+  const int64_t count = pl[1];
+  const float* data;
+  if (count == lInput - 2) data = pf + 2;
+  else if (count == lInput - 3) data = pf + 3;
+  else return ERROR_PARAM_OUT_OF_RANGE;
+  if (count > m->count) return ERROR_MEMORY_RANGE_EXCEEDED;
+  if (!m->bf16) return (long)cudaMemcpy(m->ptr, data, (size_t)count * 4, cudaMemcpyHostToDevice);
+  float* tmp = k->staging((size_t)count);
+  if (!tmp) return ERROR_MEMORY_OUT;
+  cudaError_t ce = cudaMemcpy(tmp, data, (size_t)count * 4, cudaMemcpyHostToDevice);
+  if (ce != cudaSuccess) return ce;
+  e = mca_convert_f32_to_bf16(tmp, m->ptr, count, 0);
+  if (!e) e = (long)cudaStreamSynchronize(0);
+  return e;
+}
+
+long convert_mem(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 3, 3))) return e;
+  MemItem *s = k->get((long)pl[0]), *d = k->get((long)pl[1]);
+  if (!s || !d) return ERROR_MEMORY_NOT_FOUND;
+  const int64_t n = pl[2];
+  if (n <= 0 || n > s->count || n > d->count) return ERROR_PARAM_OUT_OF_RANGE;
+  if (s->bf16 == d->bf16) return (long)cudaMemcpyAsync(d->ptr, s->ptr, (size_t)n * (s->bf16 ? 2 : 4), cudaMemcpyDeviceToDevice, 0);
+  if (d->bf16) return mca_convert_f32_to_bf16((const float*)s->ptr, d->ptr, n, 0);
+  return mca_convert_bf16_to_f32(s->ptr, (float*)d->ptr, n, 0);
+}
+
+// ---- attention ids ------------------------------------------------------------------------
+
+long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
+  long e;  // Device<T>::SetAttn, device.h:2463-2486 (exactly 9 longs there; 10th/11th are extensions)
+  if ((e = verify_in(llInput, pl, 9, 11))) return e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  auto it = k->attn.find((long)pl[1]);
+  if (it == k->attn.end()) return ERROR_ATTN_NOT_INITIALIZED;
+  AttnHandle& a = it->second;
+  a.release();  // attnHandle<T>::Set starts with CleanUp(), attn.cu:412
+  a.training = pl[3] != 0;
+  a.B = (int)pl[4]; a.block = (int)pl[5]; a.H = (int)pl[6]; a.D = (int)pl[7];
+  a.dropout = pf[0];
+  a.dtype = llInput > 9 ? (int)pl[9] : MCA_DTYPE_F32;
+  a.flags = llInput > 10 ? (int)pl[10] : 0;
+  if (a.B <= 0 || a.block <= 0 || a.H <= 0 || a.D <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  if (a.dtype < MCA_DTYPE_F32 || a.dtype > MCA_DTYPE_BF16) return ERROR_PARAM_OUT_OF_RANGE;
+  if (a.D > 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (a.dtype != MCA_DTYPE_F32 && a.D != 64 && a.D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  const size_t rows = (size_t)a.B * a.H * a.block;
+  cudaError_t ce;
+  if ((ce = cudaMalloc(&a.causal_flag, 8 * sizeof(int))) != cudaSuccess) { a.release(); return ERROR_MEMORY_OUT; }
+  cudaMemsetAsync(a.causal_flag, 0, 8 * sizeof(int), 0);
+  if ((ce = cudaMalloc(&a.lse, rows * 4)) != cudaSuccess) { a.release(); return ERROR_MEMORY_OUT; }
+  if (a.training) {
+    // What Backward needs from Forward: the softmax row statistics and the output.  The
+    // reference keeps (B,H,T,T) probabilities instead (attn.cu:436-452).
+    if (cudaMalloc(&a.row_max, rows * 4) != cudaSuccess || cudaMalloc(&a.row_sum, rows * 4) != cudaSuccess ||
+        cudaMalloc(&a.delta, rows * 4) != cudaSuccess || cudaMalloc(&a.y_copy, rows * a.D * 4) != cudaSuccess) {
+      cudaGetLastError();
+      a.release();
+      return ERROR_MEMORY_OUT;
+    }
+  }
+  a.configured = true;
+  return 0;
+}
+
+// Decide how the mask of this call is applied; classifies a (T,T) mask once per (pointer, T).
+long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, const float** mask, int* mode,
+                  bool need_host_answer) {
+  *mask = nullptr;
+  if (a.flags & MCA_FLAG_CAUSAL_IMPLICIT) { *mode = MCA_MASK_CAUSAL; return 0; }
+  if (hMask == 0) { *mode = MCA_MASK_NONE; return 0; }
+  float* m = nullptr;
+  long e = check_f32(k, hMask, batch_mask ? (int64_t)a.B * T : (int64_t)T * T, &m);
+  if (e) return e;
+  *mask = m;
+  if (batch_mask) { *mode = MCA_MASK_BATCH; return 0; }
+  *mode = MCA_MASK_TT;
+  if (a.cls_mask != m || a.cls_T != T) {
+    if ((e = mca_classify_causal_mask(m, T, a.causal_flag, 0))) return e;
+    a.cls_mask = m; a.cls_T = T; a.cls_host = -1;
+  }
+  if (need_host_answer) {
+    if (a.cls_host < 0) {
+      int v = 0;
+      cudaError_t ce = cudaMemcpy(&v, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost);
+      if (ce != cudaSuccess) return ce;
+      a.cls_host = v;
+    }
+    if (a.cls_host == 1) *mode = MCA_MASK_CAUSAL;
+  }
+  return 0;
+}
+
+long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;  // Device<T>::AttnForward, device.h:2488-2506; attnHandle<T>::Forward, attn.cu:518-602
+  if ((e = verify_in(llInput, pl, 9, 9))) return e;
+  auto it = k->attn.find((long)pl[1]);
+  if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
+  AttnHandle& a = it->second;
+  const int T = (int)pl[2];
+  if (T > a.block) return ERROR_ATTN_INVALID_BLOCK_SIZE;  // attn.cu:530-531
+  if (T <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  if (a.training && a.dropout > 0.f) return ERROR_ATTN + 3;  // the reference's guard always fails here (attn.cu:265)
+  const int64_t n = (int64_t)a.B * a.H * T * a.D;
+  const bool batch_mask = pl[8] != 0;
+  const float* mask = nullptr;
+  int mode = 0;
+  a.have_fwd = false;
+  if (a.dtype == MCA_DTYPE_F32) {
+    float *q, *kk, *v, *y;
+    if ((e = check_f32(k, (long)pl[3], n, &q)) || (e = check_f32(k, (long)pl[4], n, &kk)) ||
+        (e = check_f32(k, (long)pl[5], n, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
+      return e;
+    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, false))) return e;
+    const bool save = a.training && T == a.block;
+    e = mca_sdpa_forward_f32(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
+                             save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, 0);
+    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; }
+    return e;
+  }
+  // tensor-core variants: causal or absent mask only
+  if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true))) return e;
+  const bool bf16 = a.dtype == MCA_DTYPE_BF16;
+  void *q, *kk, *v, *y;
+  if ((e = check_any(k, (long)pl[3], n, bf16, &q)) || (e = check_any(k, (long)pl[4], n, bf16, &kk)) ||
+      (e = check_any(k, (long)pl[5], n, bf16, &v)) || (e = check_any(k, (long)pl[7], n, bf16, &y)))
+    return e;
+  if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH) {
+    if (bf16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+    // a general mask with tf32 requested: the exact fp32 kernel handles it
+    return mca_sdpa_forward_f32((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
+                                (float*)y, nullptr, nullptr, nullptr, 0);
+  }
+  e = mca_sdpa_forward_tc(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, 0);
+  if (e) return e;
+  if (!k->async) {
+    int st[4] = {0, 0, 0, 0};
+    cudaError_t ce = cudaMemcpy(st, a.causal_flag + 1, sizeof(st), cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return ce;
+    if (st[0] != 0) {
+      char buf[96];
+      snprintf(buf, sizeof(buf), "status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
+      k->last_detail = buf;
+      cudaMemsetAsync(a.causal_flag + 1, 0, 4 * sizeof(int), 0);
+      return ERROR_ATTN_KERNEL_TIMEOUT;
+    }
+  }
+  return 0;
+}
+
+long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;  // Device<T>::AttnBackward, device.h:2508-2529; attnHandle<T>::Backward, attn.cu:608-661
+  if ((e = verify_in(llInput, pl, 11, 11))) return e;
+  auto it = k->attn.find((long)pl[1]);
+  if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
+  AttnHandle& a = it->second;
+  if (a.dtype != MCA_DTYPE_F32) return ERROR_NOT_IMPLEMENTED;
+  // The reference's Backward always works at the configured block size on the tensors its
+  // Forward left in the handle (attn.cu:622-634); it reads neither hMask nor the data of hY.
+  if (!a.have_fwd || a.fwd_T != a.block) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;
+  const int T = a.block;
+  const int64_t n = (int64_t)a.B * a.H * T * a.D;
+  float *q, *dq, *kk, *dk, *v, *dv, *dy;
+  if ((e = check_f32(k, (long)pl[2], n, &q)) || (e = check_f32(k, (long)pl[3], n, &dq)) ||
+      (e = check_f32(k, (long)pl[4], n, &kk)) || (e = check_f32(k, (long)pl[5], n, &dk)) ||
+      (e = check_f32(k, (long)pl[6], n, &v)) || (e = check_f32(k, (long)pl[7], n, &dv)) ||
+      (e = check_f32(k, (long)pl[10], n, &dy)))
+    return e;
+  return mca_sdpa_backward_f32(q, kk, v, dy, a.y_copy, a.fwd_mask, a.fwd_mask_mode, a.causal_flag, a.row_max, a.row_sum,
+                               a.delta, a.B, a.H, T, a.D, dq, dk, dv, 0);
+}
+
+// ---- rope ids ------------------------------------------------------------------------------
+
+long rope_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput,
+                 float** ppOutput) {
+  long e;  // Device<T>::CreateRope, device.h:4200-4228
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  if ((e = verify_in(llInput, pl, 7, 7))) return e;
+  if ((e = verify_out(plOutput, ppOutput))) return e;
+  const int shared = (int)pl[0];
+  if (shared > 0) {  // Memory<T>::CreateRope with a shared index returns the existing handle, memory.h:2182-2226
+    for (auto& kv : k->rope)
+      if (kv.second.shared_index == shared) { kv.second.refs++; return set_out((float)kv.first, plOutput, ppOutput); }
+  }
+  RopeHandle r;
+  r.shared_index = shared;
+  r.B = (int)pl[3]; r.T = (int)pl[4]; r.H = (int)pl[5]; r.D = (int)pl[6];
+  if (r.T <= 0 || r.H <= 0 || r.D <= 0 || (r.D & 1)) return ERROR_PARAM_OUT_OF_RANGE;
+  const size_t n = (size_t)r.T * (r.D / 2);
+  std::vector<float> c(n), s(n);
+  mca_rope_tables_host(r.T, r.D, pf[0], c.data(), s.data());
+  if (cudaMalloc(&r.cos_t, n * 4) != cudaSuccess || cudaMalloc(&r.sin_t, n * 4) != cudaSuccess) {
+    cudaGetLastError(); cudaFree(r.cos_t); return ERROR_MEMORY_OUT;
+  }
+  cudaMemcpy(r.cos_t, c.data(), n * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(r.sin_t, s.data(), n * 4, cudaMemcpyHostToDevice);
+  const long h = k->next_handle++;
+  k->rope[h] = r;
+  return set_out((float)h, plOutput, ppOutput);
+}
+
+long rope_free(Kernel* k, long lInput, float* pf) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  auto it = k->rope.find((long)pf[0]);
+  if (it == k->rope.end()) return ERROR_ROPE_NOT_INITIALIZED;
+  if (--it->second.refs > 0) return 0;
+  cudaFree(it->second.cos_t); cudaFree(it->second.sin_t);
+  k->rope.erase(it);
+  return 0;
+}
+
+long rope_run(Kernel* k, long llInput, MCA_LONGLONG* pl, bool backward) {
+  long e;  // Device<T>::RopeForward / RopeBackward, device.h:4243-4283
+  if (!backward) { if ((e = verify_in(llInput, pl, 4, 5))) return e; }
+  else { if ((e = verify_in(llInput, pl, 5, 5))) return e; }
+  auto it = k->rope.find((long)pl[0]);
+  if (it == k->rope.end()) return ERROR_ROPE_NOT_INITIALIZED;
+  RopeHandle& r = it->second;
+  const int64_t n = pl[1];
+  float *x, *y;
+  int off = -1;
+  if (!backward) {
+    if ((e = check_f32(k, (long)pl[2], n, &x)) || (e = check_f32(k, (long)pl[3], n, &y))) return e;
+    if (llInput > 4) off = (int)pl[4];
+  } else {  // longs {hRope,n,hX,hYdiff,hXdiff}: rotate hYdiff by -angle into hXdiff (rope.cu:828-864)
+    if ((e = check_f32(k, (long)pl[3], n, &x)) || (e = check_f32(k, (long)pl[4], n, &y))) return e;
+  }
+  // positions beyond the table would read out of bounds in the reference; refuse instead
+  const int64_t half = r.D / 2, full = half * r.H;
+  const int64_t last_pos = std::min<int64_t>(n / 2 - 1, (int64_t)r.T * full - 1) / full;
+  if ((off > 0 ? off : 0) + (last_pos + 1) * half > (int64_t)r.T * half) return ERROR_PARAM_OUT_OF_RANGE;
+  return mca_rope_f32(x, y, n, r.T, r.H, r.D, r.cos_t, r.sin_t, off, backward ? 1 : 0, 0);
+}
+
+// ---- decode ids ----------------------------------------------------------------------------
+
+long decode_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput,
+                   float** ppOutput) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  if ((e = verify_in(llInput, pl, 6, 6))) return e;
+  if ((e = verify_out(plOutput, ppOutput))) return e;
+  DecodeHandle d;
+  d.B = (int)pl[0]; d.n_heads = (int)pl[1]; d.n_kv_heads = (int)pl[2]; d.hs = (int)pl[3]; d.seq_len = (int)pl[4];
+  d.bf16 = pl[5] != 0;
+  if (d.B <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.seq_len <= 0 || d.n_heads % d.n_kv_heads) return ERROR_PARAM_OUT_OF_RANGE;
+  if (d.hs != 64 && d.hs != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  int sl, ns;
+  if ((e = mca_decode_plan(d.B, d.n_heads, d.n_kv_heads, d.hs, d.seq_len, &sl, &ns, &d.scratch_floats))) return e;
+  // the plan's split length grows with the work, so the longest plan bounds every shorter one
+  int64_t worst = d.scratch_floats;
+  for (int len = 128; len < d.seq_len; len *= 2) {
+    int64_t need;
+    mca_decode_plan(d.B, d.n_heads, d.n_kv_heads, d.hs, len, &sl, &ns, &need);
+    worst = std::max(worst, need);
+  }
+  worst = std::max<int64_t>(worst, (int64_t)d.B * d.n_heads * ((d.seq_len + 127) / 128) * (d.hs + 2));
+  d.scratch_floats = worst;
+  const size_t n = (size_t)d.seq_len * (d.hs / 2);
+  std::vector<float> c(n), s(n);
+  mca_rope_tables_host(d.seq_len, d.hs, pf[0], c.data(), s.data());  // same table as precompute_freqs_cis
+  if (cudaMalloc(&d.fr, n * 4) != cudaSuccess || cudaMalloc(&d.fi, n * 4) != cudaSuccess ||
+      cudaMalloc(&d.scratch, (size_t)d.scratch_floats * 4) != cudaSuccess) {
+    cudaGetLastError(); cudaFree(d.fr); cudaFree(d.fi); return ERROR_MEMORY_OUT;
+  }
+  cudaMemcpy(d.fr, c.data(), n * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(d.fi, s.data(), n * 4, cudaMemcpyHostToDevice);
+  const long h = k->next_handle++;
+  k->decode[h] = d;
+  return set_out((float)h, plOutput, ppOutput);
+}
+
+long decode_free(Kernel* k, long lInput, float* pf) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  auto it = k->decode.find((long)pf[0]);
+  if (it == k->decode.end()) return ERROR_PARAM_OUT_OF_RANGE;
+  cudaFree(it->second.fr); cudaFree(it->second.fi); cudaFree(it->second.scratch);
+  k->decode.erase(it);
+  return 0;
+}
+
+long decode_step(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 9, 9))) return e;
+  auto it = k->decode.find((long)pl[0]);
+  if (it == k->decode.end()) return ERROR_PARAM_OUT_OF_RANGE;
+  DecodeHandle& d = it->second;
+  const int dim = d.n_heads * d.hs, kv_dim = d.n_kv_heads * d.hs;
+  float *q, *kn = nullptr, *vn = nullptr, *out, *posf;
+  void *kc, *vc;
+  if ((e = check_f32(k, (long)pl[1], (int64_t)d.B * dim, &q))) return e;
+  if (pl[2] != 0 || pl[3] != 0) {
+    if ((e = check_f32(k, (long)pl[2], (int64_t)d.B * kv_dim, &kn)) || (e = check_f32(k, (long)pl[3], (int64_t)d.B * kv_dim, &vn))) return e;
+  }
+  const int64_t cache_n = (int64_t)d.B * d.seq_len * kv_dim;
+  if ((e = check_any(k, (long)pl[4], cache_n, d.bf16, &kc)) || (e = check_any(k, (long)pl[5], cache_n, d.bf16, &vc))) return e;
+  // positions travel in a memory handle holding int32 values (allocated as `count` 4-byte elements)
+  if ((e = check_f32(k, (long)pl[6], d.B, &posf))) return e;
+  if ((e = check_f32(k, (long)pl[8], (int64_t)d.B * dim, &out))) return e;
+  const int max_len = (int)pl[7];
+  if (max_len <= 0 || max_len > d.seq_len) return ERROR_PARAM_OUT_OF_RANGE;
+  return mca_decode_attention(q, kn, vn, kc, vc, d.bf16 ? 1 : 0, (int64_t)d.seq_len * kv_dim, (const int*)posf, d.B,
+                              d.n_heads, d.n_kv_heads, d.hs, d.seq_len, max_len, d.fr, d.fi, d.scratch,
+                              d.scratch_floats, out, 0);
+}
+
+long tft_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 11, 11))) return e;
+  const int B = (int)pl[4], H = (int)pl[5], Nq = (int)pl[6], Nk = (int)pl[7], d = (int)pl[8];
+  if (B <= 0 || H <= 0 || Nq <= 0 || Nk <= 0 || d <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  float *q, *kk, *v, *mask = nullptr, *out, *attn;
+  if ((e = check_f32(k, (long)pl[0], (int64_t)B * H * Nq * d, &q)) || (e = check_f32(k, (long)pl[1], (int64_t)B * H * Nk * d, &kk)) ||
+      (e = check_f32(k, (long)pl[2], (int64_t)B * Nk * d, &v)) || (e = check_f32(k, (long)pl[9], (int64_t)B * Nq * d, &out)) ||
+      (e = check_f32(k, (long)pl[10], (int64_t)B * Nq * Nk, &attn)))
+    return e;
+  if (pl[3] != 0 && (e = check_f32(k, (long)pl[3], (int64_t)Nq * Nk, &mask))) return e;
+  return mca_tft_attention_forward_f32(q, kk, v, mask, B, H, Nq, Nk, d, out, attn, 0);
+}
+
+// ---- kernel lifecycle ----------------------------------------------------------------------
+
+long kernel_init(float* pInput, long lInput, long* idx_out) {
+  long e;  // CUDA_DLL_INITIALIZE: floats {deviceId, flags}, CudaDnnDLL.cpp:154-176
+  if ((e = verify_in(lInput, pInput, 1, 3))) return e;
+  const int dev = (int)pInput[0];
+  int count = 0;
+  cudaError_t ce = cudaGetDeviceCount(&count);
+  if (ce != cudaSuccess) { cudaGetLastError(); return ce; }
+  if (dev < 0 || dev >= count) return ERROR_PARAM_OUT_OF_RANGE;
+  cudaDeviceProp prop;
+  if ((ce = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return ce;
+  if (prop.major != 10) return ERROR_ATTN_NOT_B200;  // sm_100a code only: fail loudly elsewhere
+  if ((ce = cudaSetDevice(dev)) != cudaSuccess) return ce;
+  std::lock_guard<std::mutex> lock(g_table_lock);
+  for (int i = 1; i < kMaxKernels; ++i) {
+    if (!g_kernels[i]) {
+      g_kernels[i] = new Kernel();
+      g_kernels[i]->device = dev;
+      *idx_out = i;
+      return 0;
+    }
+  }
+  return ERROR_MEMORY_OUT;
+}
+
+void kernel_cleanup(long idx) {
+  std::lock_guard<std::mutex> lock(g_table_lock);
+  Kernel* k = g_kernels[idx];
+  if (!k) return;
+  cudaSetDevice(k->device);
+  cudaDeviceSynchronize();
+  for (auto& kv : k->mem) cudaFree(kv.second.ptr);
+  for (auto& kv : k->attn) kv.second.release();
+  for (auto& kv : k->rope) { cudaFree(kv.second.cos_t); cudaFree(kv.second.sin_t); }
+  for (auto& kv : k->decode) { cudaFree(kv.second.fr); cudaFree(kv.second.fi); cudaFree(kv.second.scratch); }
+  for (void* p : k->host_bufs) cudaFreeHost(p);
+  cudaFree(k->stage);
+  delete k;
+  g_kernels[idx] = nullptr;
+}
+
+long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llInput, float** ppOutput,
+         MCA_LONG* plOutput) {
+  cudaError_t ce = cudaSetDevice(k->device);
+  if (ce != cudaSuccess) return ce;
+  k->last_detail.clear();
+  long e;
+  switch (fn) {
+    case CUDA_FN_SETDEVICE: return 0;
+    case CUDA_FN_SYNCHRONIZEDEVICE: return (long)cudaStreamSynchronize(0);
+    case CUDA_FN_ALLOCMEM: return alloc_mem(k, lInput, pf, llInput, pl, plOutput, ppOutput, false);
+    case MCA_FN_ALLOCMEM_BF16: return alloc_mem(k, lInput, pf, llInput, pl, plOutput, ppOutput, true);
+    case CUDA_FN_FREEMEM: return free_mem(k, llInput, pl);
+    case CUDA_FN_GETMEM: return get_mem(k, llInput, pl, plOutput, ppOutput);
+    case CUDA_FN_SETMEM: return set_mem(k, lInput, pf, llInput, pl);
+    case MCA_FN_CONVERT: return finish(k, convert_mem(k, llInput, pl));
+    case CUDNN_FN_CREATE_CUDNN: {
+      if ((e = verify_out(plOutput, ppOutput))) return e;
+      const long h = k->next_handle++;
+      k->cudnn[h] = 1;
+      return set_out((float)h, plOutput, ppOutput);
+    }
+    case CUDNN_FN_FREE_CUDNN:
+      if ((e = verify_in(lInput, pf, 1, 1))) return e;
+      k->cudnn.erase((long)pf[0]);
+      return 0;
+    case CUDNN_FN_ATTN_CREATE: {
+      if ((e = verify_out(plOutput, ppOutput))) return e;
+      const long h = k->next_handle++;
+      k->attn[h] = AttnHandle();
+      return set_out((float)h, plOutput, ppOutput);
+    }
+    case CUDNN_FN_ATTN_FREE: {
+      if ((e = verify_in(lInput, pf, 1, 1))) return e;
+      auto it = k->attn.find((long)pf[0]);
+      if (it == k->attn.end()) return ERROR_PARAM_OUT_OF_RANGE;
+      cudaStreamSynchronize(0);
+      it->second.release();
+      k->attn.erase(it);
+      return 0;
+    }
+    case CUDNN_FN_ATTN_SET: return finish(k, attn_set(k, lInput, pf, llInput, pl));
+    case CUDNN_FN_ATTN_FWD: return finish(k, attn_fwd(k, llInput, pl));
+    case CUDNN_FN_ATTN_BWD: return finish(k, attn_bwd(k, llInput, pl));
+    case CUDA_FN_CREATE_ROPE: return rope_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
+    case CUDA_FN_FREE_ROPE: return rope_free(k, lInput, pf);
+    case CUDA_FN_ROPE_FWD: return finish(k, rope_run(k, llInput, pl, false));
+    case CUDA_FN_ROPE_BWD: return finish(k, rope_run(k, llInput, pl, true));
+    case MCA_FN_DECODE_CREATE: return decode_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
+    case MCA_FN_DECODE_FREE: return decode_free(k, lInput, pf);
+    case MCA_FN_DECODE_STEP: return finish(k, decode_step(k, llInput, pl));
+    case MCA_FN_TFT_ATTN_FWD: return finish(k, tft_fwd(k, llInput, pl));
+    case MCA_FN_SET_ASYNC:
+      if ((e = verify_in(llInput, pl, 1, 1))) return e;
+      k->async = pl[0] != 0;
+      return 0;
+  }
+  return ERROR_NOT_IMPLEMENTED;
+}
+
+long invoke(MCA_LONG lKernelIdx, MCA_LONG fn, float* pInput, MCA_LONG lInput, MCA_LONGLONG* plInput,
+            MCA_LONG llInput, float** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;  // CudaDnnDLL.cpp:144-145
+  long e = 0;
+  if (fn == CUDA_DLL_INITIALIZE) {
+    if ((e = verify_out(plOutput, ppOutput))) { get_error(e, szErr, lszErrMax); return e; }
+    long idx = 0;
+    if ((e = kernel_init(pInput, lInput, &idx))) { get_error(e, szErr, lszErrMax); return e; }
+    return set_out((float)idx, plOutput, ppOutput);
+  }
+  if (fn == CUDA_DLL_CLEANUP) { kernel_cleanup(lKernelIdx); return 0; }
+  Kernel* k = g_kernels[lKernelIdx];
+  if (!k) { e = ERROR_PARAM_NULL; get_error(e, szErr, lszErrMax); return e; }
+  if (fn == CUDA_DLL_FREEMEM) {  // Kernel<T>::FreeHost, CudaDnnDLL.cpp:188-201
+    for (size_t i = 0; i < k->host_bufs.size(); ++i)
+      if (k->host_bufs[i] == (void*)pInput) {
+        cudaFreeHost(pInput);
+        k->host_bufs.erase(k->host_bufs.begin() + i);
+        return 0;
+      }
+    e = ERROR_MEMORY_NOT_FOUND;
+    get_error(e, szErr, lszErrMax);
+    return e;
+  }
+  e = run(k, fn, pInput, lInput, plInput, llInput, ppOutput, plOutput);
+  if (e) get_error(e, szErr, lszErrMax, k);
+  return e;
+}
+
+}  // namespace
+
+extern "C" {
+
+MCA_LONG DLL_InvokeFloat(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput, float** ppOutput,
+                         MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  return (MCA_LONG)invoke(lKernelIdx, lFunctionIdx, pInput, lInput, nullptr, 0, ppOutput, plOutput, szErr, lszErrMax);
+}
+
+MCA_LONG DLL_InvokeFloatEx2(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput,
+                            MCA_LONGLONG* plInput, MCA_LONG llInput, float** ppOutput, MCA_LONG* plOutput,
+                            MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  return (MCA_LONG)invoke(lKernelIdx, lFunctionIdx, pInput, lInput, plInput, llInput, ppOutput, plOutput, szErr, lszErrMax);
+}
+
+MCA_LONG DLL_InvokeFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput, MCA_LPTSTR,
+                           float** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  return (MCA_LONG)invoke(lKernelIdx, lFunctionIdx, pInput, lInput, nullptr, 0, ppOutput, plOutput, szErr, lszErrMax);
+}
+
+MCA_LONG DLL_InvokeDouble(MCA_LONG, MCA_LONG, double*, MCA_LONG, double**, MCA_LONG*, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  get_error(ERROR_NOT_IMPLEMENTED, szErr, lszErrMax);
+  return ERROR_NOT_IMPLEMENTED;
+}
+
+MCA_LONG DLL_InvokeDoubleEx2(MCA_LONG, MCA_LONG, double*, MCA_LONG, MCA_LONGLONG*, MCA_LONG, double**, MCA_LONG*,
+                             MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  get_error(ERROR_NOT_IMPLEMENTED, szErr, lszErrMax);
+  return ERROR_NOT_IMPLEMENTED;
+}
+
+MCA_LONG Internal_GetPointerFloat(MCA_LONG ht, MCA_LONG lKernelIdx, MCA_LONG hHandle, void** ppPtr) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  Kernel* k = g_kernels[lKernelIdx];
+  if (!k || !ppPtr) return ERROR_PARAM_NULL;
+  if (ht != MCA_HT_MEMORY) return ERROR_NOT_IMPLEMENTED;
+  MemItem* m = k->get(hHandle);
+  if (!m) return ERROR_MEMORY_NOT_FOUND;
+  *ppPtr = m->ptr;
+  return 0;
+}
+
+MCA_LONG Internal_AllocHostFloat(MCA_LONG lKernelIdx, MCA_LONG lCount, float** ppDst, float* pSrc, bool bSrcOnDevice) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  Kernel* k = g_kernels[lKernelIdx];
+  if (!k || !ppDst) return ERROR_PARAM_NULL;
+  if (lCount <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  long e = alloc_host(k, lCount, ppDst);
+  if (e) return (MCA_LONG)e;
+  if (pSrc)
+    return (MCA_LONG)cudaMemcpy(*ppDst, pSrc, (size_t)lCount * 4, bSrcOnDevice ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost);
+  return 0;
+}
+
+int mca_rope_tables_host(int T, int D, float theta, float* cos_table, float* sin_table) {
+  if (!cos_table || !sin_table) return ERROR_PARAM_NULL;
+  if (T <= 0 || D <= 0 || (D & 1)) return ERROR_PARAM_OUT_OF_RANGE;
+  const int half = D / 2;
+  std::vector<float> freq(half);
+  for (int i = 0, idx = 0; i < D; i += 2, ++idx) freq[idx] = 1.0f / powf(theta, (float)(i / (float)D));
+  for (int pos = 0; pos < T; ++pos)
+    for (int i = 0; i < half; ++i) {
+      const float f = freq[i] * pos;
+      cos_table[(size_t)pos * half + i] = cosf(f);
+      sin_table[(size_t)pos * half + i] = sinf(f);
+    }
+  return 0;
+}
+
+const char* mca_version(void) { return "mycaffe_attn_b200 0.1 sm_100a"; }
+
+}  // extern "C"

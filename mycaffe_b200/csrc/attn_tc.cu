@@ -1,0 +1,597 @@
+// Fused flash-style attention forward on the 5th-generation tensor cores (sm_100a):
+// S = Q K^T by tcgen05.mma into TMEM, online softmax by two warpgroups that read S from TMEM
+// and write the probabilities back to TMEM as the A operand of the second product, O += P V
+// accumulated in TMEM; Q/K/V tiles arrive by TMA (cp.async.bulk.tensor, no multicast) into
+// 128-byte-swizzled shared memory behind mbarrier pipelines.
+//
+// Same mathematics as the reference's attnHandle<T>::Forward (CudaDnnDLL/Cuda Files/
+// attn.cu:518-602: scale, mask, max-subtracted softmax, times V) for a causal or absent mask.
+// The reference materialises the (B,H,T,T) logits and probabilities in HBM and makes three
+// passes over them; here they never leave the SM.
+//
+// One CTA owns two 128-row query tiles of one (batch, head) and walks the keys 128 at a time:
+//   warp 0        TMA producer (one lane)
+//   warp 1        MMA issuer (one lane); owns the TMEM allocation
+//   warps 2-5     softmax for query tile 0, one thread per row
+//   warps 6-9     softmax for query tile 1
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (bf16, packed two per
+// column) overwrites the first columns of its S.  The MMA lane alternates between the two
+// query tiles so one tile's softmax overlaps the other tile's products.  The running maximum
+// used for the exponent is only raised when the true maximum has grown by more than 2^8, so
+// the O accumulator in TMEM is rescaled rarely; the final division by the row sum makes the
+// result exact regardless.
+//
+// Every wait on an mbarrier is bounded: after about a second without progress the waiting
+// thread records where it gave up in a status word and the CTA drains and exits.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+constexpr int BLK = 128;               // query rows per tile and keys per step
+constexpr int NQT = 2;                 // query tiles per CTA
+constexpr int TC_THREADS = 64 + NQT * 128;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false after WAIT_LIMIT_NS (or as soon as another CTA reported a
+// failure) and records {code, stage, block, iteration} in status[0..3].
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 63u) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (atomicCAS(status, 0, 1) == 0) {
+          status[1] = stage;
+          status[2] = (int)(blockIdx.x + gridDim.x * blockIdx.y);
+          status[3] = iter;
+          __threadfence();
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, stage, iter);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t result_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base_lane + t).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Descriptors
+// ---------------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile whose rows are 128 bytes:
+// bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset
+// >> 4, [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+//  * K-major operand (rows = M or N index, 64 bf16 of K per row): 8-row groups are 1024 bytes
+//    apart (SBO); LBO is not used by the swizzled K-major form.
+//  * MN-major operand (rows = K index, 64 bf16 of N per row): 8-row groups along K are 1024
+//    bytes apart (SBO); the next 64 columns of N start LBO bytes later.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16, bf16 x bf16 -> fp32: c_format [4,6) = 1 (F32), a_format
+// [7,10) = 1 (BF16), b_format [10,13) = 1, a_major bit 15, b_major bit 16 (0 = K-major,
+// 1 = MN-major), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory plan (all tiles 1024-byte aligned)
+// ---------------------------------------------------------------------------------------------
+template <int HD> struct Plan {
+  static constexpr int SUB = HD / 64;                      // 64-column (128-byte) sub-tiles per row
+  static constexpr uint32_t SUB_BYTES = BLK * 128;         // one sub-tile: 128 rows x 128 bytes
+  static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 x HD bf16
+  static constexpr int STAGES = 2;
+  static constexpr uint32_t OFF_Q = 0;
+  static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
+  static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
+  static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
+  static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;  // barriers + alignment slack
+};
+
+enum Bar : int {  // mbarrier indices
+  BAR_Q_FULL = 0,    // [NQT]
+  BAR_K_FULL = 2,    // [STAGES]
+  BAR_K_EMPTY = 4,
+  BAR_V_FULL = 6,
+  BAR_V_EMPTY = 8,
+  BAR_S_FULL = 10,   // [NQT]  S tile written by the MMA
+  BAR_P_READY = 12,  // [NQT]  P written (and O rescaled) by the softmax warpgroup
+  BAR_O_DONE = 14,   // [NQT]  P V product of the step finished
+  BAR_DRAIN = 16,
+  BAR_COUNT = 17
+};
+
+struct TcParams {
+  void* y;        // (B*H, T, HD) bf16
+  float* lse;     // (B*H, T) or null: log2-domain log-sum-exp of the scaled logits
+  int* status;
+  int T, causal;
+  float scale_log2;  // (1/sqrt(HD)) * log2(e)
+};
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  using PL = Plan<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar0 = smem_base + PL::OFF_BAR;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR + BAR_COUNT * 8);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int T = p.T;
+  // longest causal work first
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int q0 = pair * (NQT * BLK);
+  int n_tiles[NQT];
+#pragma unroll
+  for (int x = 0; x < NQT; ++x) {
+    const int qx = q0 + x * BLK;
+    if (qx >= T) n_tiles[x] = 0;
+    else n_tiles[x] = p.causal ? (min(qx + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
+  __shared__ int s_abort;
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_abort != 0) return;
+
+  if (tid == 0) {
+    for (int i = 0; i < BAR_COUNT; ++i) {
+      const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT);
+      mbar_init(bar(i), softmax_bar ? 128u : 1u);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+#pragma unroll
+      for (int x = 0; x < NQT; ++x) {
+        if (n_tiles[x] == 0) continue;
+        mbar_expect_tx(bar(BAR_Q_FULL + x), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s)
+          tma_load_3d(smem_base + PL::OFF_Q + x * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_q, bar(BAR_Q_FULL + x), s * 64,
+                      q0 + x * BLK, bh);
+      }
+      int issued_k = 0, issued_v = 0;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        ok = mbar_wait(bar(BAR_K_EMPTY + st), ph ^ 1u, p.status, 10, j);
+        if (!ok) break;
+        mbar_expect_tx(bar(BAR_K_FULL + st), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s)
+          tma_load_3d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * 64,
+                      j * BLK, bh);
+        issued_k = j + 1;
+        ok = mbar_wait(bar(BAR_V_EMPTY + st), ph ^ 1u, p.status, 11, j);
+        if (!ok) break;
+        mbar_expect_tx(bar(BAR_V_FULL + st), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s)
+          tma_load_3d(smem_base + PL::OFF_V + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_v, bar(BAR_V_FULL + st), s * 64,
+                      j * BLK, bh);
+        issued_v = j + 1;
+      }
+      if (!ok) {
+        // give copies already in flight a bounded time to land before the CTA's memory is released
+        for (int x = 0; x < NQT; ++x)
+          if (n_tiles[x]) mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 12, x);
+        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(bar(BAR_K_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 13, j);
+        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(BAR_V_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 14, j);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = make_idesc_bf16(BLK, BLK, 0, 0);
+      constexpr uint32_t IDESC_PV = make_idesc_bf16(BLK, HD, 0, 1);
+      auto issue_qk = [&](int x, int st) {
+        const uint32_t q_addr = smem_base + PL::OFF_Q + x * PL::TILE_BYTES;
+        const uint32_t k_addr = smem_base + PL::OFF_K + st * PL::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+          umma_ss(tmem_base + x * BLK, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_QK,
+                  kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int x, int st, bool first) {
+        const uint32_t v_addr = smem_base + PL::OFF_V + st * PL::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {
+          // A: P rows in TMEM, 16 bf16 = 8 columns per step.  B: V, 16 key rows = 2048 bytes per step.
+          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + kk * 8,
+                  make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+        }
+      };
+#pragma unroll
+      for (int x = 0; x < NQT; ++x)
+        if (n_tiles[x] && ok) ok = mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 20, x);
+      if (ok && n_max > 0) {
+        ok = mbar_wait(bar(BAR_K_FULL + 0), 0, p.status, 21, 0);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int x = 0; x < NQT; ++x) {
+            if (n_tiles[x] > 0) { issue_qk(x, 0); umma_commit(bar(BAR_S_FULL + x)); }
+          }
+          umma_commit(bar(BAR_K_EMPTY + 0));
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1, st_n = (j + 1) & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1), ph_n = (uint32_t)(((j + 1) >> 1) & 1);
+        ok = mbar_wait(bar(BAR_V_FULL + st), ph, p.status, 22, j);
+        if (!ok) break;
+        bool k_next_ready = false;
+#pragma unroll
+        for (int x = 0; x < NQT; ++x) {
+          if (j < n_tiles[x]) {
+            ok = mbar_wait(bar(BAR_P_READY + x), (uint32_t)(j & 1), p.status, 23 + x, j);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(x, st, j == 0);
+            umma_commit(bar(BAR_O_DONE + x));
+          }
+          if (x == NQT - 1) umma_commit(bar(BAR_V_EMPTY + st));
+          if (j + 1 < n_tiles[x]) {
+            if (!k_next_ready) {
+              ok = mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 25, j);
+              if (!ok) break;
+              tc_fence_after();
+              k_next_ready = true;
+            }
+            issue_qk(x, st_n);
+            umma_commit(bar(BAR_S_FULL + x));
+          }
+          if (x == NQT - 1 && j + 1 < n_max) {
+            if (!k_next_ready) {  // no query tile needs this K tile any more (cannot happen for n_max), keep the ring moving
+              ok = mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 26, j);
+              if (!ok) break;
+            }
+            umma_commit(bar(BAR_K_EMPTY + st_n));
+          }
+        }
+      }
+      // all products issued: wait (bounded) until the tensor pipe is idle before TMEM is freed
+      umma_commit(bar(BAR_DRAIN));
+      mbar_wait(bar(BAR_DRAIN), 0, p.status, 27, 0);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int x = (warp - 2) >> 2;                 // query tile of this warpgroup
+    const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
+    const int row = lane_base + lane;              // row within the tile
+    const int qi = q0 + x * BLK + row;             // absolute query index
+    const uint32_t t_s = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(x * BLK);
+    const uint32_t t_o = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(2 * BLK + x * BLK);
+    const int n = n_tiles[x];
+    float m_used = -INFINITY, l = 0.f;
+    for (int j = 0; j < n && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
+      tmem_wait_ld();
+      const int k0 = j * BLK;
+      const bool need_mask = (p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(s[c][i]) * p.scale_log2;
+          if (need_mask) {
+            const int kj = k0 + c * 32 + i;
+            if (kj >= T || (p.causal && kj > qi)) v = -INFINITY;
+          }
+          s[c][i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      // Raise the running maximum only on the first step or when it would grow by more than 2^8.
+      float m_new = m_used;
+      bool raise = false;
+      if (mx > m_used + RESCALE_THRESHOLD || j == 0) { m_new = fmaxf(mx, m_used); raise = (j > 0); }
+      if (m_new == -INFINITY) m_new = 0.f;  // a row with no visible key yet (rows beyond T)
+      if (__any_sync(0xffffffffu, raise)) {
+        // rescale O in TMEM: the previous P V product must have finished
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
+        if (!ok) break;
+        tc_fence_after();
+        const float f = raise ? fast_exp2(m_used - m_new) : 1.0f;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st32(t_o + c * 32, o);
+        }
+        l *= f;
+      }
+      m_used = m_new;
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(__uint_as_float(s[c][2 * i]) - m_used);
+          const float p1 = fast_exp2(__uint_as_float(s[c][2 * i + 1]) - m_used);
+          pk[i] = pack_bf16(p0, p1);
+          // sum what the tensor core will actually multiply (the bf16-rounded values)
+          rs += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
+        }
+        tmem_st16(t_s + c * 16, pk);
+      }
+      l += rs;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_P_READY + x));
+    }
+    if (ok && n > 0) {
+      // epilogue: O / l -> bf16 -> global
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c * 32, o);
+          tmem_wait_ld();
+          if (qi < T) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(yrow + c * 32 + i) = w;
+            }
+          }
+        }
+        if (p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used + log2f(l);
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)ptr;
+  return fn;
+}
+
+// (BH, T, HD) bf16 tensor, box = 64 columns x 128 rows of one (b,h), 128-byte swizzle.
+int make_map_bf16(CUtensorMap* map, const void* base, int BH, int T, int HD) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return ERROR_NOT_IMPLEMENTED;
+  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)T * HD * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)BLK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : ERROR_PARAM_OUT_OF_RANGE;
+}
+
+template <int HD>
+int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
+              int* status, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  int e;
+  if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
+      (e = make_map_bf16(&mv, v, B * H, T, HD)))
+    return e;
+  TcParams p;
+  p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal;
+  p.scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
+  const size_t smem = Plan<HD>::BYTES;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(mca_ceil_div(T, NQT * BLK), B * H);
+  sdpa_fwd_tc_kernel<HD><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
+  return mca_launch_status();
+}
+
+}  // namespace
+
+int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
+                        void* y, float* lse, int* status, void* stream) {
+  if (!q || !k || !v || !y || !status) return ERROR_PARAM_NULL;
+  if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  if (dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;  // tf32 variant: not built yet
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(y)) & 15)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128) return launch_tc<128>(q, k, v, causal, B, H, T, y, lse, status, st);
+  if (D == 64) return launch_tc<64>(q, k, v, causal, B, H, T, y, lse, status, st);
+  return ERROR_ATTN_UNSUPPORTED_SHAPE;
+}

@@ -1,0 +1,60 @@
+// Shared declarations for the attention library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+// Error codes of the reference's native layer that this path can return
+// (CudaDnnDLL/Cuda Files/util.h:128-146,198-211).  CUDA runtime codes pass through unchanged.
+constexpr int ERROR_BASE = 90000;
+constexpr int ERROR_DLL_NOT_INIT = ERROR_BASE - 1;
+constexpr int ERROR_PARAM = ERROR_BASE;
+constexpr int ERROR_PARAM_OUT_OF_RANGE = ERROR_PARAM + 1;
+constexpr int ERROR_PARAM_NULL = ERROR_PARAM + 2;
+constexpr int ERROR_MEMORY_OUT = ERROR_PARAM + 7;
+constexpr int ERROR_MEMORY_NULL = ERROR_PARAM + 8;
+constexpr int ERROR_NOT_IMPLEMENTED = ERROR_PARAM + 9;
+constexpr int ERROR_MEMORY_RANGE_EXCEEDED = ERROR_PARAM + 10;
+constexpr int ERROR_MEMORY_MIXED_HALF_TYPES = ERROR_PARAM + 11;
+constexpr int ERROR_MEMORY_NOT_FOUND = ERROR_PARAM + 14;
+constexpr int ERROR_MEMORY_TOO_SMALL = ERROR_PARAM + 16;
+// ERROR_MATRIX = +20, VECTOR = +40, NN = +60, CUDA = +80, TSNE = NN+40 = +100, SSD = +120,
+// LAYERNORM = +160, ROPE = +200, RNN8 = +240, ATTN = +280 (util.h:150-211).
+constexpr int ERROR_ROPE = ERROR_PARAM + 200;
+constexpr int ERROR_ROPE_NOT_INITIALIZED = ERROR_ROPE + 1;
+constexpr int ERROR_ATTN = ERROR_PARAM + 280;
+constexpr int ERROR_ATTN_NOT_INITIALIZED = ERROR_ATTN + 1;
+constexpr int ERROR_ATTN_INCOMPATIBLE_BLOB_SIZE = ERROR_ATTN + 4;
+constexpr int ERROR_ATTN_INVALID_BLOCK_SIZE = ERROR_ATTN + 5;
+// Codes added by this library (outside every range the reference defines).
+constexpr int ERROR_ATTN_B200 = ERROR_PARAM + 900;
+constexpr int ERROR_ATTN_UNSUPPORTED_SHAPE = ERROR_ATTN_B200 + 1;   // head size / dtype combination has no kernel
+constexpr int ERROR_ATTN_KERNEL_TIMEOUT = ERROR_ATTN_B200 + 2;      // a bounded device-side wait gave up
+constexpr int ERROR_ATTN_BACKWARD_WITHOUT_FORWARD = ERROR_ATTN_B200 + 3;
+constexpr int ERROR_ATTN_NOT_B200 = ERROR_ATTN_B200 + 4;            // device is not compute capability 10.x
+constexpr int ERROR_ATTN_SCRATCH_TOO_SMALL = ERROR_ATTN_B200 + 5;
+
+// Value the reference writes over masked logits (finite): attn.cu:302-329.
+#define MCA_MASKED_LOGIT (-1e29f)
+
+// Mask modes shared by host and device code.
+enum McaMaskMode : int {
+  MCA_MASK_NONE = 0,    // hMask == 0 (attn.cu:544,571)
+  MCA_MASK_TT = 1,      // (1,1,T,T), masked where mask == 0 (apply_mask)
+  MCA_MASK_BATCH = 2,   // (B,T,1,1) key mask, masked where mask == 0 (apply_mask_batch)
+  MCA_MASK_CAUSAL = 3,  // analytic lower triangle: same result as a tril(ones) MCA_MASK_TT mask
+};
+
+#define MCA_CUDA_TRY(expr)                      \
+  do {                                          \
+    cudaError_t _e = (expr);                    \
+    if (_e != cudaSuccess) return (int)_e;      \
+  } while (0)
+
+static inline int mca_launch_status() {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+  return 0;
+}
+
+__host__ __device__ static inline int mca_ceil_div(int a, int b) { return (a + b - 1) / b; }

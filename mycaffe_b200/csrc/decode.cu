@@ -1,0 +1,327 @@
+// Split-KV flash decoding for the llama2 KV-cache path.
+//
+// Replaces the reference's decode attention for one new token
+// (Primitives::attention / multi_head_attention_kernel, CudaExtension.llm32.llama2/Files/
+// primitives.cu:158-202,391-403, CPU twin llama2_cpu.cpp:304-342) together with the steps
+// the reference runs as separate launches before it: RoPE on the new q/k (rope_kernel,
+// primitives.cu:99-116) and the append of k,v to the cache (llama2_gpu.cpp:67-72).
+//
+// The reference launches one CTA per head and lets each thread walk a whole K row, so its
+// cache reads are uncoalesced and 32 CTAs cannot fill the machine.  Here the keys of every
+// (sequence, kv-head) are cut into splits; a CTA streams its split once with 128-bit loads
+// in which the lanes of a group cover one contiguous cache row, reduces dot products with
+// warp shuffles, keeps an online-softmax state per lane group, and writes one partial
+// (max, sum, weighted V) per head.  A second small kernel combines the partials.  The work
+// is bound by HBM traffic: every cache byte is read exactly once.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr int EPL = 16;  // cache elements per lane per row
+
+struct DecodeParams {
+  const float* q;        // (B, n_heads*HS): projection of the new token (before RoPE when fr != null)
+  const float* k_new;    // (B, kv_dim) or null: new key (before RoPE); appended to the cache at pos[b]
+  const float* v_new;    // (B, kv_dim) or null
+  void* k_cache;         // (B, seq_len, kv_dim) cache element type
+  void* v_cache;
+  const int* pos;        // (B): index of the new token; keys 0..pos[b] are attended
+  const float* fr;       // (seq_len, HS/2) cos table or null (no RoPE)
+  const float* fi;       // (seq_len, HS/2) sin table
+  float* part_acc;       // (B, n_heads, nsplit, HS)
+  float* part_ml;        // (B, n_heads, nsplit, 2)
+  float* out;            // (B, n_heads*HS)
+  int64_t cache_batch_stride;  // elements between sequences in the caches
+  int n_heads, n_kv_heads, kv_mul, seq_len, split_len, nsplit;
+};
+
+template <typename CT> struct Row16;
+template <> struct Row16<float> {
+  // chunk c of lane gl covers elements (c*G + gl)*4 .. +3
+  template <int G> static __device__ __forceinline__ void load(const float* row, int gl, float (&x)[EPL]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float4 t = __ldcs(reinterpret_cast<const float4*>(row) + c * G + gl);
+      x[c * 4 + 0] = t.x; x[c * 4 + 1] = t.y; x[c * 4 + 2] = t.z; x[c * 4 + 3] = t.w;
+    }
+  }
+  template <int G> static __device__ __forceinline__ void store(float* row, int gl, const float (&x)[EPL]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      reinterpret_cast<float4*>(row)[c * G + gl] = make_float4(x[c * 4], x[c * 4 + 1], x[c * 4 + 2], x[c * 4 + 3]);
+  }
+  template <int G> static __device__ __forceinline__ int elem(int gl, int i) { return ((i >> 2) * G + gl) * 4 + (i & 3); }
+};
+template <> struct Row16<__nv_bfloat16> {
+  // chunk c of lane gl covers elements (c*G + gl)*8 .. +7
+  template <int G> static __device__ __forceinline__ void load(const __nv_bfloat16* row, int gl, float (&x)[EPL]) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint4 t = __ldcs(reinterpret_cast<const uint4*>(row) + c * G + gl);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[c * 8 + 2 * i] = __uint_as_float(w[i] << 16);
+        x[c * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    }
+  }
+  template <int G> static __device__ __forceinline__ void store(__nv_bfloat16* row, int gl, const float (&x)[EPL]) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(x[c * 8 + 2 * i], x[c * 8 + 2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(row)[c * G + gl] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  template <int G> static __device__ __forceinline__ int elem(int gl, int i) { return ((i >> 3) * G + gl) * 8 + (i & 7); }
+};
+
+// Load 16 elements of a float vector in the lane's element order, optionally rotating
+// adjacent pairs by the RoPE angle of this position (rope, llama2_cpu.cpp:239-262).
+template <typename CT, int G>
+__device__ __forceinline__ void load_vec_rope(const float* __restrict__ src, int gl, const float* __restrict__ cr,
+                                              const float* __restrict__ ci, float (&x)[EPL]) {
+#pragma unroll
+  for (int i = 0; i < EPL; i += 2) {
+    const int e = Row16<CT>::template elem<G>(gl, i);  // even
+    const float x0 = src[e], x1 = src[e + 1];
+    if (cr != nullptr) {
+      const float c = cr[e >> 1], s = ci[e >> 1];
+      x[i] = x0 * c - x1 * s;
+      x[i + 1] = x0 * s + x1 * c;
+    } else {
+      x[i] = x0; x[i + 1] = x1;
+    }
+  }
+}
+
+template <typename CT, int HS, int KVM>
+__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeParams p) {
+  constexpr int G = HS / EPL;     // lanes per cache row
+  constexpr int RPW = 32 / G;     // rows per warp per step
+  constexpr int U = 2;            // steps in flight
+  __shared__ float s_acc[DEC_WARPS][KVM][HS];
+  __shared__ float s_ml[DEC_WARPS][KVM][2];
+
+  const int b = blockIdx.z;
+  const int h0 = blockIdx.y * KVM;          // first query head of this CTA
+  const int kvh = h0 / p.kv_mul;
+  const int split = blockIdx.x;
+  const int pos = p.pos[b];
+  const int L = pos + 1;
+  const int r_begin = split * p.split_len;
+  if (r_begin >= L) return;
+  const int r_end = min(L, r_begin + p.split_len);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gl = lane % G, g = lane / G;
+  const int kv_dim = p.n_kv_heads * HS;
+  const int dim = p.n_heads * HS;
+  CT* kc = reinterpret_cast<CT*>(p.k_cache) + (int64_t)b * p.cache_batch_stride + (int64_t)kvh * HS;
+  CT* vc = reinterpret_cast<CT*>(p.v_cache) + (int64_t)b * p.cache_batch_stride + (int64_t)kvh * HS;
+  const float* cr = p.fr ? p.fr + (int64_t)pos * (HS / 2) : nullptr;
+  const float* ci = p.fi ? p.fi + (int64_t)pos * (HS / 2) : nullptr;
+  const float inv_div = sqrtf((float)HS);
+
+  float q[KVM][EPL];
+#pragma unroll
+  for (int x = 0; x < KVM; ++x) load_vec_rope<CT, G>(p.q + (int64_t)b * dim + (int64_t)(h0 + x) * HS, gl, cr, ci, q[x]);
+
+  float m[KVM], l[KVM], acc[KVM][EPL];
+#pragma unroll
+  for (int x = 0; x < KVM; ++x) {
+    m[x] = -INFINITY; l[x] = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) acc[x][i] = 0.f;
+  }
+
+  const bool has_new = (p.k_new != nullptr);
+  for (int base = r_begin + warp * RPW; base < r_end; base += DEC_WARPS * RPW * U) {
+    float kx[U][EPL], vx[U][EPL];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int row = base + u * DEC_WARPS * RPW + g;
+      valid[u] = row < r_end;
+      if (valid[u]) {
+        if (has_new && row == pos) {
+          // the new token: take k,v from the projections, rotate k, and append both to the cache
+          load_vec_rope<CT, G>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx[u]);
+          load_vec_rope<CT, G>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx[u]);
+          if (h0 % p.kv_mul == 0) {
+            Row16<CT>::template store<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
+            Row16<CT>::template store<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
+          }
+          if (sizeof(CT) == 2) {  // attend to what a later step will read back from the cache
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+              kx[u][i] = __bfloat162float(__float2bfloat16_rn(kx[u][i]));
+              vx[u][i] = __bfloat162float(__float2bfloat16_rn(vx[u][i]));
+            }
+          }
+        } else {
+          Row16<CT>::template load<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
+          Row16<CT>::template load<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int x = 0; x < KVM; ++x) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) s = fmaf(q[x][i], kx[u][i], s);
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid[u]) {
+          s = s / inv_div;  // score /= sqrtf(head_size), llama2_cpu.cpp:322
+          const float m_new = fmaxf(m[x], s);
+          const float corr = __expf(m[x] - m_new);
+          const float pw = __expf(s - m_new);
+          l[x] = l[x] * corr + pw;
+          m[x] = m_new;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[u][i], acc[x][i] * corr);
+        }
+      }
+    }
+  }
+
+  // merge the lane groups of a warp, then the warps of the CTA
+#pragma unroll
+  for (int x = 0; x < KVM; ++x) {
+    float m_all = m[x];
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+    const float f = (m[x] == -INFINITY) ? 0.f : __expf(m[x] - m_all);
+    float lsum = l[x] * f;
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      float a = acc[x][i] * f;
+#pragma unroll
+      for (int o = G; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (g == 0) s_acc[warp][x][Row16<CT>::template elem<G>(gl, i)] = a;
+    }
+    if (lane == 0) { s_ml[warp][x][0] = m_all; s_ml[warp][x][1] = lsum; }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < KVM * HS; idx += DEC_THREADS) {
+    const int x = idx / HS, e = idx % HS;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, s_ml[w][x][0]);
+    float lsum = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float mw = s_ml[w][x][0];
+      const float f = (mw == -INFINITY) ? 0.f : __expf(mw - M);
+      lsum += s_ml[w][x][1] * f;
+      a += s_acc[w][x][e] * f;
+    }
+    const int h = h0 + x;
+    if (p.nsplit == 1) {
+      p.out[(int64_t)b * dim + (int64_t)h * HS + e] = a / lsum;
+    } else {
+      const int64_t slot = ((int64_t)b * p.n_heads + h) * p.nsplit + split;
+      p.part_acc[slot * HS + e] = a;
+      if (e == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = lsum; }
+    }
+  }
+}
+
+// Combine pass: out[b,h,:] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.
+template <int HS>
+__global__ void __launch_bounds__(HS) decode_combine_kernel(const float* __restrict__ part_acc,
+                                                            const float* __restrict__ part_ml,
+                                                            const int* __restrict__ pos, int n_heads, int nsplit,
+                                                            int split_len, float* __restrict__ out) {
+  const int h = blockIdx.x, b = blockIdx.y, e = threadIdx.x;
+  const int n_valid = min(nsplit, (pos[b] + split_len) / split_len);  // ceil((pos+1)/split_len)
+  const int64_t slot0 = ((int64_t)b * n_heads + h) * nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < n_valid; ++s) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
+  float lsum = 0.f, a = 0.f;
+  for (int s = 0; s < n_valid; ++s) {
+    const float f = __expf(part_ml[(slot0 + s) * 2] - M);
+    lsum += part_ml[(slot0 + s) * 2 + 1] * f;
+    a += part_acc[(slot0 + s) * HS + e] * f;
+  }
+  out[((int64_t)b * n_heads + h) * HS + e] = a / lsum;
+}
+
+template <typename CT, int HS>
+int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
+  const int kvmt = p.kv_mul >= 4 ? 4 : p.kv_mul;
+  dim3 grid(p.nsplit, p.n_heads / kvmt, B);
+  switch (kvmt) {
+    case 1: decode_split_kernel<CT, HS, 1><<<grid, DEC_THREADS, 0, st>>>(p); break;
+    case 2: decode_split_kernel<CT, HS, 2><<<grid, DEC_THREADS, 0, st>>>(p); break;
+    case 4: decode_split_kernel<CT, HS, 4><<<grid, DEC_THREADS, 0, st>>>(p); break;
+    default: return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  }
+  int e = mca_launch_status();
+  if (e) return e;
+  if (p.nsplit > 1) {
+    decode_combine_kernel<HS><<<dim3(p.n_heads, B), HS, 0, st>>>(p.part_acc, p.part_ml, p.pos, p.n_heads, p.nsplit,
+                                                                 p.split_len, p.out);
+    e = mca_launch_status();
+  }
+  return e;
+}
+
+}  // namespace
+
+int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_len, int* split_len, int* nsplit,
+                    int64_t* scratch_floats) {
+  if (B <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_len <= 0 || n_heads % n_kv_heads != 0)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  // Aim for a few waves of CTAs over 148 SMs x 2 resident CTAs, with at least 128 keys each.
+  const int64_t rows = (int64_t)B * n_kv_heads * max_len;
+  int64_t sl = rows / (148 * 2 * 4);
+  sl = (sl + 127) / 128 * 128;
+  if (sl < 128) sl = 128;
+  if (sl > 1024) sl = 1024;
+  *split_len = (int)sl;
+  *nsplit = (max_len + (int)sl - 1) / (int)sl;
+  *scratch_floats = (int64_t)B * n_heads * (*nsplit) * (head_size + 2);
+  return 0;
+}
+
+int mca_decode_attention(const float* q, const float* k_new, const float* v_new, void* k_cache, void* v_cache,
+                         int cache_is_bf16, int64_t cache_batch_stride, const int* pos, int B, int n_heads,
+                         int n_kv_heads, int head_size, int seq_len, int max_len, const float* freq_real,
+                         const float* freq_imag, float* scratch, int64_t scratch_floats, float* out, void* stream) {
+  if (!q || !k_cache || !v_cache || !pos || !out) return ERROR_PARAM_NULL;
+  if ((k_new == nullptr) != (v_new == nullptr)) return ERROR_PARAM_NULL;
+  if ((freq_real == nullptr) != (freq_imag == nullptr)) return ERROR_PARAM_NULL;
+  if (head_size != 64 && head_size != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (max_len <= 0 || max_len > seq_len || B > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  DecodeParams p;
+  int64_t need = 0;
+  int e = mca_decode_plan(B, n_heads, n_kv_heads, head_size, max_len, &p.split_len, &p.nsplit, &need);
+  if (e) return e;
+  if (p.nsplit > 1 && (scratch == nullptr || scratch_floats < need)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
+  p.q = q; p.k_new = k_new; p.v_new = v_new; p.k_cache = k_cache; p.v_cache = v_cache; p.pos = pos;
+  p.fr = freq_real; p.fi = freq_imag; p.out = out;
+  p.part_acc = scratch;
+  p.part_ml = scratch ? scratch + (int64_t)B * n_heads * p.nsplit * head_size : nullptr;
+  p.cache_batch_stride = cache_batch_stride;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.kv_mul = n_heads / n_kv_heads; p.seq_len = seq_len;
+  if (p.kv_mul > 4 && p.kv_mul % 4 != 0) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (p.kv_mul == 3) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cache_is_bf16) {
+    return head_size == 128 ? launch_decode<__nv_bfloat16, 128>(p, B, st) : launch_decode<__nv_bfloat16, 64>(p, B, st);
+  }
+  return head_size == 128 ? launch_decode<float, 128>(p, B, st) : launch_decode<float, 64>(p, B, st);
+}

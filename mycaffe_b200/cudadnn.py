@@ -1,0 +1,200 @@
+"""Host-side mirror of the attention part of MyCaffe's ``CudaDnn<T>`` class
+(MyCaffe/common/CudaDnn.cs), over the C ABI of libmycaffe_attn.so.
+
+The reference's host side is C#; no .NET toolchain exists where this package is built, so the
+same surface is written in Python with ctypes.  Method names, argument order and meaning and
+the error behaviour (a non-zero native code becomes an exception carrying the native message,
+as the COM layer does for C#) follow ``CudaDnn.cs``: memory ``:2584-2723``, attention
+``:5611-5701``, RoPE ``:6375-6431``.  Every call goes through ``DLL_InvokeFloatEx2`` with the
+packed float / long arrays the C# code builds.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from . import function_ids as ids
+
+
+class CudaDnnError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"[{code}] {message}")
+        self.code = int(code)
+        self.native_message = message
+
+
+class CudaDnn:
+    """One instance == one native kernel index (CudaDnn.cs:1693-1735)."""
+
+    def __init__(self, device_id: int = 0):
+        self._lib = _lib.load()
+        self._kernel = 0
+        out = self._invoke(ids.CUDA_DLL_INITIALIZE, [float(device_id), 0.0], None)
+        self._kernel = int(out[0])
+        self.device_id = device_id
+
+    # ------------------------------------------------------------------ plumbing
+    def _invoke(self, fn, floats=None, longs=None, out_capacity=1, out_buf=None):
+        lib = self._lib
+        fa = np.ascontiguousarray(floats, dtype=np.float32) if floats is not None else None
+        la = np.ascontiguousarray(longs, dtype=np.int64) if longs is not None else None
+        if out_buf is None:
+            out_buf = np.zeros(max(1, out_capacity), np.float32)
+        pp = C.cast(out_buf.ctypes.data, C.POINTER(C.c_float))
+        n_out = _lib.LONG(out_buf.size)
+        err = C.create_string_buffer(1024)
+        rc = lib.DLL_InvokeFloatEx2(
+            self._kernel, fn,
+            fa.ctypes.data_as(C.POINTER(C.c_float)) if fa is not None else None, fa.size if fa is not None else 0,
+            la.ctypes.data_as(C.POINTER(C.c_int64)) if la is not None else None, la.size if la is not None else 0,
+            C.byref(pp), C.byref(n_out), err, 1024)
+        if rc != 0:
+            raise CudaDnnError(rc, err.value.decode(errors="replace"))
+        n = n_out.value
+        if C.cast(pp, C.c_void_p).value != out_buf.ctypes.data:
+            # the library returned a pinned buffer of its own; copy out and release it (FREEMEM -1)
+            res = np.ctypeslib.as_array(pp, shape=(n,)).copy()
+            lib.DLL_InvokeFloat(self._kernel, ids.CUDA_DLL_FREEMEM, pp, 0, None, None, err, 1024)
+            return res
+        return out_buf[:n]
+
+    def Dispose(self):
+        if self._kernel:
+            self._lib.DLL_InvokeFloat(self._kernel, ids.CUDA_DLL_CLEANUP, None, 0, None, None, None, 0)
+            self._kernel = 0
+
+    def __del__(self):
+        try:
+            self.Dispose()
+        except Exception:
+            pass
+
+    @property
+    def KernelHandle(self):
+        return self._kernel
+
+    # ------------------------------------------------------------------ memory (CudaDnn.cs:2584-2723)
+    def AllocMemory(self, data_or_count) -> int:
+        if np.isscalar(data_or_count):
+            return int(self._invoke(ids.CUDA_FN_ALLOCMEM, None, [int(data_or_count)])[0])
+        data = np.ascontiguousarray(data_or_count, np.float32).ravel()
+        packed = np.empty(data.size + 1, np.float32)
+        packed[0] = data.size
+        packed[1:] = data
+        return int(self._invoke(ids.CUDA_FN_ALLOCMEM, packed, [data.size])[0])
+
+    def AllocMemoryBf16(self, data_or_count) -> int:
+        """Extension: bf16 storage behind a handle; host data stays float and is converted on the device."""
+        if np.isscalar(data_or_count):
+            return int(self._invoke(ids.MCA_FN_ALLOCMEM_BF16, None, [int(data_or_count)])[0])
+        data = np.ascontiguousarray(data_or_count, np.float32).ravel()
+        packed = np.empty(data.size + 1, np.float32)
+        packed[0] = data.size
+        packed[1:] = data
+        return int(self._invoke(ids.MCA_FN_ALLOCMEM_BF16, packed, [data.size])[0])
+
+    def FreeMemory(self, h):
+        self._invoke(ids.CUDA_FN_FREEMEM, None, [int(h)])
+
+    def GetMemory(self, h, count=-1) -> np.ndarray:
+        cap = int(count) if count and count > 0 else 1
+        return np.array(self._invoke(ids.CUDA_FN_GETMEM, None, [int(h), int(count)], out_capacity=cap))
+
+    def GetMemoryInto(self, h, out: np.ndarray):
+        """GETMEM into a caller-owned float32 buffer (no intermediate copy)."""
+        assert out.dtype == np.float32 and out.flags.c_contiguous
+        self._invoke(ids.CUDA_FN_GETMEM, None, [int(h), out.size], out_buf=out.reshape(-1))
+
+    def _invoke_raw(self, fn, packed_floats: np.ndarray, longs):
+        """Invoke with an already packed float32 array (used to send large host buffers without a copy)."""
+        assert packed_floats.dtype == np.float32 and packed_floats.flags.c_contiguous
+        return self._invoke(fn, packed_floats, longs)
+
+    def SetMemory(self, h, data):
+        data = np.ascontiguousarray(data, np.float32).ravel()
+        packed = np.empty(data.size + 2, np.float32)
+        packed[0] = h
+        packed[1] = data.size
+        packed[2:] = data
+        self._invoke(ids.CUDA_FN_SETMEM, packed, [int(h), data.size])
+
+    def SetMemoryInt32(self, h, data):
+        """int32 values through a 4-byte-element handle (bit pattern preserved)."""
+        self.SetMemory(h, np.ascontiguousarray(data, np.int32).view(np.float32))
+
+    def ConvertMemory(self, hSrc, hDst, count):
+        self._invoke(ids.MCA_FN_CONVERT, None, [int(hSrc), int(hDst), int(count)])
+
+    def GetPointer(self, h) -> int:
+        p = C.c_void_p()
+        rc = self._lib.Internal_GetPointerFloat(1, self._kernel, int(h), C.byref(p))
+        if rc:
+            raise CudaDnnError(rc, "Internal_GetPointerFloat")
+        return int(p.value)
+
+    def SynchronizeDevice(self):
+        self._invoke(ids.CUDA_FN_SYNCHRONIZEDEVICE)
+
+    def SetAsync(self, enabled: bool):
+        """Extension: skip the per-call stream synchronise that the reference performs."""
+        self._invoke(ids.MCA_FN_SET_ASYNC, None, [1 if enabled else 0])
+
+    # ------------------------------------------------------------------ cuDNN handle (passed through only)
+    def CreateCuDNN(self) -> int:
+        return int(self._invoke(ids.CUDNN_FN_CREATE_CUDNN)[0])
+
+    def FreeCuDNN(self, h):
+        self._invoke(ids.CUDNN_FN_FREE_CUDNN, [float(h)])
+
+    # ------------------------------------------------------------------ attention (CudaDnn.cs:5611-5701)
+    def CreateAttn(self) -> int:
+        return int(self._invoke(ids.CUDNN_FN_ATTN_CREATE)[0])
+
+    def FreeAttn(self, h):
+        self._invoke(ids.CUDNN_FN_ATTN_FREE, [float(h)])
+
+    def SetAttn(self, hCuDnn, hAttn, nGpuID, bTraining, nBatch, nBlockSize, nHeads, nSize, fDropout, lSeed=0,
+                dtype=None, flags=None):
+        longs = [hCuDnn, hAttn, nGpuID, 1 if bTraining else 0, nBatch, nBlockSize, nHeads, nSize, lSeed]
+        if dtype is not None or flags is not None:
+            longs.append(dtype or 0)
+        if flags is not None:
+            longs.append(flags)
+        self._invoke(ids.CUDNN_FN_ATTN_SET, [float(fDropout)], longs)
+
+    def AttnScaledDotProductForward(self, hCuDnn, hAttn, nBlockSize, hQ, hK, hV, hMask, hY, bBatchMask=False):
+        self._invoke(ids.CUDNN_FN_ATTN_FWD, None,
+                     [hCuDnn, hAttn, nBlockSize, hQ, hK, hV, hMask, hY, 1 if bBatchMask else 0])
+
+    def AttnScaledDotProductBackward(self, hCuDnn, hAttn, hQ, hdQ, hK, hdK, hV, hdV, hMask, hY, hdY):
+        self._invoke(ids.CUDNN_FN_ATTN_BWD, None, [hCuDnn, hAttn, hQ, hdQ, hK, hdK, hV, hdV, hMask, hY, hdY])
+
+    # ------------------------------------------------------------------ RoPE (CudaDnn.cs:6375-6431)
+    def CreateRope(self, nSharedIndex, nGpuID, nCount, nBatch, nSeqLen, nHeads, nDim, fTheta=10000.0) -> int:
+        return int(self._invoke(ids.CUDA_FN_CREATE_ROPE, [float(fTheta)],
+                                [nSharedIndex, nGpuID, nCount, nBatch, nSeqLen, nHeads, nDim])[0])
+
+    def FreeRope(self, h):
+        self._invoke(ids.CUDA_FN_FREE_ROPE, [float(h)])
+
+    def RopeForward(self, hRope, n, hX, hY, nFreqOffset=-1):
+        self._invoke(ids.CUDA_FN_ROPE_FWD, None, [hRope, n, hX, hY, nFreqOffset])
+
+    def RopeBackward(self, hRope, n, hX, hYdiff, hXdiff):
+        self._invoke(ids.CUDA_FN_ROPE_BWD, None, [hRope, n, hX, hYdiff, hXdiff])
+
+    # ------------------------------------------------------------------ extensions: decode, TFT
+    def CreateDecode(self, nBatch, nHeads, nKvHeads, nHeadSize, nSeqLen, bCacheBf16=False, fTheta=10000.0) -> int:
+        return int(self._invoke(ids.MCA_FN_DECODE_CREATE, [float(fTheta)],
+                                [nBatch, nHeads, nKvHeads, nHeadSize, nSeqLen, 1 if bCacheBf16 else 0])[0])
+
+    def FreeDecode(self, h):
+        self._invoke(ids.MCA_FN_DECODE_FREE, [float(h)])
+
+    def DecodeStep(self, hDecode, hQ, hKnew, hVnew, hKcache, hVcache, hPos, nMaxLen, hOut):
+        self._invoke(ids.MCA_FN_DECODE_STEP, None, [hDecode, hQ, hKnew, hVnew, hKcache, hVcache, hPos, nMaxLen, hOut])
+
+    def TftAttnForward(self, hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn):
+        self._invoke(ids.MCA_FN_TFT_ATTN_FWD, None, [hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn])

@@ -76,6 +76,8 @@ def _c(a, dt=np.float32):
 
 
 def _mask_args(mask, mask_mode):
+    if mask_mode == 3:
+        return np.zeros(1, np.float32), 3
     if mask is None or mask_mode == 0:
         return np.zeros(1, np.float32), 0
     return _c(mask), int(mask_mode)

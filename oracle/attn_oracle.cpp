@@ -47,7 +47,9 @@ inline void softmax_row(const ACC* s, int n, ACC* p) {
 //   P = softmax_row(S)        (attn.cu:587)
 //   Y = P V                   (attn.cu:598)
 // mask_mode 0: none; 1: (T,T) mask, masked where mask==0 (apply_mask);
-// 2: (B,T) key mask, masked where mask==0 (apply_mask_batch).
+// 2: (B,T) key mask, masked where mask==0 (apply_mask_batch); 3: the lower-triangular mask of
+// fillMask (CausalSelfAttentionLayer.cs:276-291) generated on the fly (same result as mode 1 with
+// tril(ones), without holding a T x T array).
 // q_begin/q_step select a strided subset of query rows (used to bound the
 // work at very long T); rows not selected are left untouched.
 template <typename ACC, typename OUT>
@@ -70,6 +72,7 @@ void sdpa_forward(const float* Q, const float* K, const float* V, const float* m
           acc *= scale;
           if (mask_mode == 1 && mask[(int64_t)i * T + j] == 0.0f) acc = ACC(kMaskedLogit);
           if (mask_mode == 2 && mask[(int64_t)b * T + j] == 0.0f) acc = ACC(kMaskedLogit);
+          if (mask_mode == 3 && j > i) acc = ACC(kMaskedLogit);
           s[j] = acc;
         }
         softmax_row<ACC>(s.data(), T, p.data());
@@ -119,6 +122,7 @@ void sdpa_backward(const float* Q, const float* K, const float* V, const float* 
         acc *= scale;
         if (mask_mode == 1 && mask[(int64_t)i * T + j] == 0.0f) acc = ACC(kMaskedLogit);
         if (mask_mode == 2 && mask[(int64_t)b * T + j] == 0.0f) acc = ACC(kMaskedLogit);
+        if (mask_mode == 3 && j > i) acc = ACC(kMaskedLogit);
         s[j] = acc;
       }
       softmax_row<ACC>(s.data(), T, p.data());

@@ -1,0 +1,273 @@
+"""Parity of the CUDA attention path against the CPU oracle, through the C ABI
+(function ids ATTN_CREATE/SET/FWD/BWD as CudaDnn.cs:5611-5701 packs them).
+
+Tolerances: max-abs error relative to the output scale <= 1e-4 for fp32, <= 2e-2 for bf16
+(the targets stated for this path); most fp32 cases are held to 2e-5."""
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import Sdpa, bf16_round
+from helpers import PICO_CASES, csa_forward, csa_qkv, rel_err
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-4
+FP32_TIGHT = 2e-5
+BF16_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    from mycaffe_b200 import CudaDnn
+    c = CudaDnn(0)
+    yield c
+    c.Dispose()
+
+
+def rand_qkv(rng, B, H, T, D, scale=1.0):
+    return tuple((scale * rng.standard_normal((B, H, T, D))).astype(np.float32) for _ in range(3))
+
+
+@pytest.mark.parametrize("case", list(PICO_CASES))
+def test_pico_golden_forward_backward(cuda, pico, case):
+    """The reference's own golden vectors (gpt-pico-csa*) through ATTN_FWD / ATTN_BWD."""
+    H = PICO_CASES[case]
+    g = lambda n: pico[f"{case}/{n}"]
+    x = g("x")
+    B, T, C = x.shape
+    q, k, v = csa_qkv(x, g("attn_weight"), g("attn_bias"), H)
+    a = Sdpa(cuda, B, T, H, C // H, training=True)
+    y = a.forward(q, k, v, oracle.causal_mask(T))
+    if f"{case}/var_y" in pico.files:
+        np.testing.assert_allclose(y, g("var_y"), atol=3e-7)
+    full = csa_forward(x, g("attn_weight"), g("attn_bias"), g("attn_proj_weight"), g("attn_proj_bias"), H,
+                       lambda *_: y)
+    np.testing.assert_allclose(full, g("y"), atol=3e-7)
+    dq, dk, dv = a.backward(g("grad_y_pre_transpose"))
+    np.testing.assert_allclose(dq, g("grad_qt"), atol=3e-8)
+    np.testing.assert_allclose(dk, g("grad_kt"), atol=3e-8)
+    np.testing.assert_allclose(dv, g("grad_vt"), atol=3e-8)
+    a.close()
+
+
+def test_config1_causal_block(cuda):
+    """BASELINE config 1: one CausalSelfAttention block forward, fp32, B=1, T=128, 4 heads x 16."""
+    import torch
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 128, 64, generator=gen).numpy()
+    w_attn = (0.02 * torch.randn(192, 64, generator=gen)).numpy()
+    w_proj = (0.02 * torch.randn(64, 64, generator=gen)).numpy()
+    zeros = np.zeros
+    mask = oracle.causal_mask(128)
+    a = Sdpa(cuda, 1, 128, 4, 16)
+    got = csa_forward(x, w_attn, zeros(192, np.float32), w_proj, zeros(64, np.float32), 4,
+                      lambda q, k, v: a.forward(q, k, v, mask))
+    ref = csa_forward(x, w_attn, zeros(192, np.float32), w_proj, zeros(64, np.float32), 4,
+                      lambda q, k, v: oracle.sdpa_forward(q, k, v, mask, 1, f64=True))
+    assert rel_err(got, ref) < FP32_TIGHT
+    a.close()
+
+
+def test_reference_self_consistency_recipe(cuda):
+    """TestCudaAttentionForward/Backward (TestGPT_MultiheadAttentionLayer.cs:945-1036): random
+    (3,8,200,64), all-ones batch mask, composed route vs the direct route."""
+    rng = np.random.default_rng(0)
+    B, H, T, D = 3, 8, 200, 64
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    mask = np.ones((B, T), np.float32)
+    a = Sdpa(cuda, B, T, H, D, training=True)
+    y = a.forward(q, k, v, mask, batch_mask=True)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, 2, f64=True)) < FP32_TIGHT
+    dy = rng.standard_normal(q.shape).astype(np.float32)
+    got = a.backward(dy)
+    ref = oracle.sdpa_backward(q, k, v, dy, mask, 2, f64=True)
+    for g_, r_ in zip(got, ref):
+        assert rel_err(g_, r_) < FP32_TIGHT
+    a.close()
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 5, 17, 64, 127, 129, 200])
+@pytest.mark.parametrize("D", [1, 3, 16, 32, 64, 128])
+def test_forward_backward_ragged_shapes_causal(cuda, T, D):
+    rng = np.random.default_rng(T * 131 + D)
+    B, H = 2, 3
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    mask = oracle.causal_mask(T)
+    a = Sdpa(cuda, B, T, H, D, training=True)
+    y = a.forward(q, k, v, mask)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, 1, f64=True)) < FP32_TIGHT
+    dy = rng.standard_normal(q.shape).astype(np.float32)
+    got = a.backward(dy)
+    ref = oracle.sdpa_backward(q, k, v, dy, mask, 1, f64=True)
+    for g_, r_ in zip(got, ref):
+        assert rel_err(g_, r_) < FP32_TIGHT
+    a.close()
+
+
+@pytest.mark.parametrize("mode", ["none", "random_tt", "batch_with_dead_row"])
+def test_mask_forms(cuda, mode):
+    """No mask (hMask = 0), an arbitrary (T,T) mask, and a (B,T) key mask with one batch row fully
+    masked: masked logits are -1e29, so that row becomes a uniform distribution (math.cu:2994-3002)."""
+    rng = np.random.default_rng(11)
+    B, H, T, D = 3, 2, 150, 32
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    dy = rng.standard_normal(q.shape).astype(np.float32)
+    if mode == "none":
+        mask, omode, batch = None, 0, False
+    elif mode == "random_tt":
+        mask = (rng.random((T, T)) > 0.3).astype(np.float32)
+        mask[7, :] = 0  # one fully masked query row
+        omode, batch = 1, False
+    else:
+        mask = (rng.random((B, T)) > 0.2).astype(np.float32)
+        mask[1, :] = 0
+        omode, batch = 2, True
+    a = Sdpa(cuda, B, T, H, D, training=True)
+    y = a.forward(q, k, v, mask, batch_mask=batch)
+    ref = oracle.sdpa_forward(q, k, v, mask, omode, f64=True)
+    assert rel_err(y, ref) < FP32_TIGHT
+    if mode == "batch_with_dead_row":
+        np.testing.assert_allclose(y[1], np.broadcast_to(v[1].mean(axis=1, keepdims=True), v[1].shape), atol=2e-6)
+    got = a.backward(dy)
+    for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, omode, f64=True)):
+        assert rel_err(g_, r_) < FP32_TIGHT
+    a.close()
+
+
+def test_forward_shorter_than_block(cuda):
+    """Forward accepts nBlockSize <= the configured block size (attn.cu:530-531)."""
+    rng = np.random.default_rng(5)
+    B, H, T, D = 2, 4, 40, 16
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    a = Sdpa(cuda, B, 64, H, D)
+    y = a.forward(q, k, v, oracle.causal_mask(T), T=T)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, oracle.causal_mask(T), 1, f64=True)) < FP32_TIGHT
+    a.close()
+
+
+def test_gpt2_small_shape_layer(cuda):
+    """BASELINE config 2 shape (12 heads x 64, T=1024), one layer's attention core, B reduced to 2
+    so that the CPU oracle finishes in seconds."""
+    rng = np.random.default_rng(2)
+    B, H, T, D = 2, 12, 1024, 64
+    q, k, v = rand_qkv(rng, B, H, T, D, 0.5)
+    mask = oracle.causal_mask(T)
+    a = Sdpa(cuda, B, T, H, D, training=True)
+    y = a.forward(q, k, v, mask)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, 1)) < FP32_TOL
+    dy = rng.standard_normal(q.shape).astype(np.float32)
+    got = a.backward(dy)
+    for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, 1)):
+        assert rel_err(g_, r_) < FP32_TOL
+    a.close()
+
+
+def test_error_paths(cuda):
+    from mycaffe_b200 import CudaDnnError, function_ids as ids
+    rng = np.random.default_rng(3)
+    q, k, v = rand_qkv(rng, 1, 2, 8, 16)
+    a = Sdpa(cuda, 1, 8, 2, 16, training=True)
+    with pytest.raises(CudaDnnError) as e:  # T above the configured block size
+        a.forward(q, k, v, None, T=9)
+    assert e.value.code == ids.ERROR_ATTN_INVALID_BLOCK_SIZE
+    with pytest.raises(CudaDnnError) as e:  # backward before any forward on this handle
+        a.hQ = a.hK = a.hV = a.hY = a._alloc(q)
+        a.backward(q)
+    assert e.value.code == ids.ERROR_ATTN_BACKWARD_WITHOUT_FORWARD
+    with pytest.raises(CudaDnnError) as e:  # unknown memory handle
+        cuda.AttnScaledDotProductForward(a.hCudnn, a.hAttn, 8, 99999, a.hK, a.hV, 0, a.hY, False)
+    assert e.value.code == ids.ERROR_MEMORY_NOT_FOUND
+    with pytest.raises(CudaDnnError) as e:  # tensor smaller than B*H*T*D
+        small = a._alloc(4)
+        cuda.AttnScaledDotProductForward(a.hCudnn, a.hAttn, 8, small, a.hK, a.hV, 0, a.hY, False)
+    assert e.value.code == ids.ERROR_MEMORY_TOO_SMALL
+    with pytest.raises(CudaDnnError) as e:  # wrong number of longs (device.h:2492 wants exactly 9)
+        cuda._invoke(ids.CUDNN_FN_ATTN_FWD, None, [1, 2, 3])
+    assert e.value.code == ids.ERROR_PARAM_OUT_OF_RANGE
+    with pytest.raises(CudaDnnError) as e:  # forward on a handle that was never Set
+        h = cuda.CreateAttn()
+        cuda.AttnScaledDotProductForward(a.hCudnn, h, 8, a.hQ, a.hK, a.hV, 0, a.hY, False)
+    assert e.value.code == ids.ERROR_ATTN_NOT_INITIALIZED
+    a.close()
+    # attention dropout in training: the reference's guard always errors on this route (attn.cu:265)
+    d = Sdpa(cuda, 1, 8, 2, 16, training=True, dropout=0.1)
+    with pytest.raises(CudaDnnError) as e:
+        d.forward(q, k, v, None)
+    assert e.value.code == ids.ERROR_ATTN_MISSING_DESCRIPTOR
+    d.close()
+    with pytest.raises(CudaDnnError) as e:  # head size beyond the kernels
+        Sdpa(cuda, 1, 8, 2, 256)
+    assert e.value.code == ids.ERROR_ATTN_UNSUPPORTED_SHAPE
+
+
+def test_memory_roundtrip_and_pinned_result(cuda):
+    rng = np.random.default_rng(4)
+    data = rng.standard_normal(1000).astype(np.float32)
+    h = cuda.AllocMemory(data)
+    np.testing.assert_array_equal(cuda.GetMemory(h, 1000), data)
+    np.testing.assert_array_equal(cuda.GetMemory(h), data)      # count -1: library-owned pinned buffer
+    cuda.SetMemory(h, data[::-1].copy())
+    np.testing.assert_array_equal(cuda.GetMemory(h, 10), data[::-1][:10])
+    hb = cuda.AllocMemoryBf16(data)
+    np.testing.assert_array_equal(cuda.GetMemory(hb, 1000), bf16_round(data))
+    assert cuda.GetPointer(h) % 256 == 0
+    cuda.FreeMemory(h)
+    cuda.FreeMemory(hb)
+
+
+# --------------------------------------------------------------------------- tensor-core path
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [128, 256, 200, 384, 1000, 2048])
+@pytest.mark.parametrize("causal", [True, False])
+def test_bf16_tensor_core_forward(cuda, T, D, causal):
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(T + D)
+    B, H = 1, 3
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, H, T, D))
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16,
+             flags=ids.MCA_FLAG_CAUSAL_IMPLICIT if causal else 0)
+    y = a.forward(q, k, v, None)
+    mask = oracle.causal_mask(T) if causal else None
+    ref = oracle.sdpa_forward(q, k, v, mask, 1 if causal else 0, f64=True)
+    assert rel_err(y, ref) < BF16_TOL
+    a.close()
+
+
+def test_bf16_tensor_core_accepts_causal_mask_handle(cuda):
+    """A (T,T) tril mask passed the reference's way is recognised as causal; another mask is refused."""
+    from mycaffe_b200 import CudaDnnError, function_ids as ids
+    rng = np.random.default_rng(9)
+    B, H, T, D = 2, 2, 256, 64
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, H, T, D))
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16)
+    y = a.forward(q, k, v, oracle.causal_mask(T))
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, oracle.causal_mask(T), 1, f64=True)) < BF16_TOL
+    a.close()
+    b = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16)
+    with pytest.raises(CudaDnnError) as e:
+        b.forward(q, k, v, np.ones((T, T), np.float32) - np.eye(T, dtype=np.float32))
+    assert e.value.code == ids.ERROR_ATTN_UNSUPPORTED_SHAPE
+    b.close()
+
+
+def test_long_context_shape_properties(cuda):
+    """BASELINE config 5 shape (16 heads x 128, bf16, causal) at T = 8192: the CPU oracle checks a
+    strided subset of query rows, and a size-independent property checks the rest: with V = 1 every
+    output element is 1, and with Q = 0 row i is the mean of V[0..i]."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(8)
+    B, H, T, D = 1, 16, 8192, 128
+    q, k, v = (bf16_round(a / np.sqrt(np.float32(D))) for a in rand_qkv(rng, B, H, T, D))
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16, flags=ids.MCA_FLAG_CAUSAL_IMPLICIT)
+    y = a.forward(q, k, v, None)
+    ref = oracle.sdpa_forward_rows(q, k, v, None, 3, 5, 257)
+    assert rel_err(y[:, :, 5::257], ref) < BF16_TOL
+    ones = np.ones_like(v)
+    y1 = a.forward(q, k, ones, None)
+    assert np.abs(y1 - 1).max() < 1e-2
+    y0 = a.forward(np.zeros_like(q), k, v, None)
+    cm = np.cumsum(v.astype(np.float64), axis=2) / np.arange(1, T + 1)[None, None, :, None]
+    assert rel_err(y0, cm) < BF16_TOL
+    a.close()
