@@ -436,20 +436,28 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
       tmem_wait_ld();
       const int k0 = j * BLK;
-      const bool need_mask = (p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T);
-      float mx = -INFINITY;
+      // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
+      if ((p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kj = k0 + c * 32 + i;
+            if (kj >= T || (p.causal && kj > qi)) s[c][i] = 0xff800000u;  // -inf
+          }
+      }
+      // row maximum of the raw logits (four independent chains), then in scaled log2 units
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(s[c][i]) * p.scale_log2;
-          if (need_mask) {
-            const int kj = k0 + c * 32 + i;
-            if (kj >= T || (p.causal && kj > qi)) v = -INFINITY;
-          }
-          s[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+        for (int i = 0; i < 32; i += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[c][i + 0]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[c][i + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[c][i + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[c][i + 3]));
         }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       // Raise the running maximum only on the first step or when it would grow by more than 2^8.
       float m_new = m_used;
       bool raise = false;
@@ -473,20 +481,25 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         l *= f;
       }
       m_used = m_new;
-      float rs = 0.f;
+      // p = 2^(s * scale_log2 - m): one FFMA and one ex2 per element; the row sum is taken in fp32
+      const float neg_m = -m_used;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(__uint_as_float(s[c][2 * i]) - m_used);
-          const float p1 = fast_exp2(__uint_as_float(s[c][2 * i + 1]) - m_used);
+        for (int i = 0; i < 16; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 0]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 1]), p.scale_log2, neg_m));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 2]), p.scale_log2, neg_m));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 3]), p.scale_log2, neg_m));
           pk[i] = pack_bf16(p0, p1);
-          // sum what the tensor core will actually multiply (the bf16-rounded values)
-          rs += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
+          pk[i + 1] = pack_bf16(p2, p3);
+          rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
         }
         tmem_st16(t_s + c * 16, pk);
       }
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l += rs;
       tmem_wait_st();
       tc_fence_before();

@@ -143,7 +143,10 @@ def test_rope_forward_backward(cuda, B, T, H, D):
     one = x[:, 3:4].copy()
     hO, hO2 = cuda.AllocMemory(one), cuda.AllocMemory(one.size)
     cuda.RopeForward(h, one.size, hO, hO2, 3 * D // 2)
-    np.testing.assert_allclose(cuda.GetMemory(hO2, one.size).reshape(one.shape), y[:, 3:4], atol=1e-6)
+    got = cuda.GetMemory(hO2, one.size).reshape(one.shape)
+    np.testing.assert_allclose(got, oracle.rope_apply(one, T, H, D, cos_t, sin_t, freq_offset=3 * D // 2), atol=1e-6)
+    # the first H*D/2 pairs sit at table position 0 + offset, i.e. position 3 (the reference's B = 1 use)
+    np.testing.assert_allclose(got[0], y[0, 3:4], atol=1e-6)
     for m in (hX, hY, hO, hO2):
         cuda.FreeMemory(m)
     # a shared index returns the same handle (memory.h:2182-2226)
