@@ -54,7 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc(), *NVCC_FLAGS, *os.environ.get("MCA_NVCC_EXTRA", "").split(), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, cmd))

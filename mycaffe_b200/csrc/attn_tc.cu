@@ -10,10 +10,11 @@
 // passes over them; here they never leave the SM.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks the keys 128 at a time:
-//   warp 0        TMA producer (one lane)
-//   warp 1        MMA issuer (one lane); owns the TMEM allocation
-//   warps 2-5     softmax for query tile 0, one thread per row
-//   warps 6-9     softmax for query tile 1
+//   warps 0-3     softmax for query tile 0, one thread per row
+//   warps 4-7     softmax for query tile 1
+//   warp 8        TMA producer (one lane)
+//   warp 9        MMA issuer (one lane); owns the TMEM allocation
+//   warps 10-11   idle (they complete the third warpgroup)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (bf16, packed two per
 // column) overwrites the first columns of its S.  The MMA lane alternates between the two
 // query tiles so one tile's softmax overlaps the other tile's products.  The running maximum
@@ -32,7 +33,9 @@ namespace {
 
 constexpr int BLK = 128;               // query rows per tile and keys per step
 constexpr int NQT = 2;                 // query tiles per CTA
-constexpr int TC_THREADS = 64 + NQT * 128;
+constexpr int TC_THREADS = NQT * 128 + 128;  // two softmax warpgroups + one warpgroup for TMA / MMA
+constexpr int WARP_TMA = NQT * 4;       // first warp of the third warpgroup
+constexpr int WARP_MMA = NQT * 4 + 1;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
@@ -177,6 +180,33 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed fp32 pair arithmetic (two lanes per instruction on sm_100).
+#ifndef MCA_USE_F32X2
+#define MCA_USE_F32X2 0
+#endif
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+#if !MCA_USE_F32X2
+  return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+#endif
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)), "l"(*reinterpret_cast<uint64_t*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+#if !MCA_USE_F32X2
+  return make_float2(a.x + b.x, a.y + b.y);
+#endif
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -222,7 +252,7 @@ template <int HD> struct Plan {
   static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-  static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;  // barriers + alignment slack
+  static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;  // barriers (19 x 8 bytes) + TMEM slot + alignment slack
 };
 
 enum Bar : int {  // mbarrier indices
@@ -235,8 +265,21 @@ enum Bar : int {  // mbarrier indices
   BAR_P_READY = 12,  // [NQT]  P written (and O rescaled) by the softmax warpgroup
   BAR_O_DONE = 14,   // [NQT]  P V product of the step finished
   BAR_DRAIN = 16,
-  BAR_COUNT = 17
+  BAR_P_HALF = 17,   // [NQT]  first 64 key columns of P written
+  BAR_COUNT = 19
 };
+
+// Optional timeline capture for tuning (compiled out unless MCA_TC_TRACE is defined): one CTA
+// writes clock64 stamps of its softmax and MMA threads into a small global buffer.
+#ifdef MCA_TC_TRACE
+__device__ long long g_tc_trace[3 * 64 * 8];
+#define TC_TRACE(role, it, slot)                                                                         \
+  do {                                                                                                   \
+    if (trace_on && (it) < 64) g_tc_trace[((role) * 64 + (it)) * 8 + (slot)] = clock64();                \
+  } while (0)
+#else
+#define TC_TRACE(role, it, slot) do { } while (0)
+#endif
 
 struct TcParams {
   void* y;        // (B*H, T, HD) bf16
@@ -272,6 +315,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     else n_tiles[x] = p.causal ? (min(qx + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
+#ifdef MCA_TC_TRACE
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && ((warp & 3) == 0 || warp == WARP_MMA);
+#endif
 
   // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
   __shared__ int s_abort;
@@ -281,7 +327,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
-      const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT);
+      const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT) || (i >= BAR_P_HALF && i < BAR_P_HALF + NQT);
       mbar_init(bar(i), softmax_bar ? 128u : 1u);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -289,7 +335,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
   }
-  if (warp == 1) {
+  if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
     tmem_relinquish();
   }
@@ -299,7 +345,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp == 0) {
+  if (warp == WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
 #pragma unroll
@@ -340,7 +386,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(BAR_V_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 14, j);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == WARP_MMA) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = make_idesc_bf16(BLK, BLK, 0, 0);
@@ -355,10 +401,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                   kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int x, int st, bool first) {
+      auto issue_pv = [&](int x, int st, bool first, int half) {
         const uint32_t v_addr = smem_base + PL::OFF_V + st * PL::TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk) {
+        for (int kk = half * (BLK / 32); kk < (half + 1) * (BLK / 32); ++kk) {
           // A: P rows in TMEM, 16 bf16 = 8 columns per step.  B: V, 16 key rows = 2048 bytes per step.
           umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + kk * 8,
                   make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_PV, (first && kk == 0) ? 0u : 1u);
@@ -387,10 +433,17 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int x = 0; x < NQT; ++x) {
           if (j < n_tiles[x]) {
+            TC_TRACE(2, j, x * 4 + 0);
+            ok = mbar_wait(bar(BAR_P_HALF + x), (uint32_t)(j & 1), p.status, 28 + x, j);
+            if (!ok) break;
+            TC_TRACE(2, j, x * 4 + 1);
+            tc_fence_after();
+            issue_pv(x, st, j == 0, 0);
             ok = mbar_wait(bar(BAR_P_READY + x), (uint32_t)(j & 1), p.status, 23 + x, j);
             if (!ok) break;
+            TC_TRACE(2, j, x * 4 + 3);
             tc_fence_after();
-            issue_pv(x, st, j == 0);
+            issue_pv(x, st, j == 0, 1);
             umma_commit(bar(BAR_O_DONE + x));
           }
           if (x == NQT - 1) umma_commit(bar(BAR_V_EMPTY + st));
@@ -403,6 +456,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             issue_qk(x, st_n);
             umma_commit(bar(BAR_S_FULL + x));
+            TC_TRACE(2, j, x * 4 + 2);
           }
           if (x == NQT - 1 && j + 1 < n_max) {
             if (!k_next_ready) {  // no query tile needs this K tile any more (cannot happen for n_max), keep the ring moving
@@ -417,9 +471,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       umma_commit(bar(BAR_DRAIN));
       mbar_wait(bar(BAR_DRAIN), 0, p.status, 27, 0);
     }
-  } else {
+  } else if (warp < WARP_TMA) {
     // ------------------------------------------------------------------ softmax warpgroups
-    const int x = (warp - 2) >> 2;                 // query tile of this warpgroup
+    const int x = warp >> 2;                       // query tile of this warpgroup
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int row = lane_base + lane;              // row within the tile
     const int qi = q0 + x * BLK + row;             // absolute query index
@@ -428,35 +482,45 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int n = n_tiles[x];
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < n && ok; ++j) {
+      TC_TRACE(x, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
       if (!ok) break;
+      TC_TRACE(x, j, 1);
       tc_fence_after();
       uint32_t s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
+      tmem_ld32(t_s + 0, s[0]);
+      tmem_ld32(t_s + 32, s[1]);
       tmem_wait_ld();
+      tmem_ld32(t_s + 64, s[2]);   // in flight while the first half is reduced
+      tmem_ld32(t_s + 96, s[3]);
+      TC_TRACE(x, j, 2);
       const int k0 = j * BLK;
       // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
-      if ((p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T)) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kj = k0 + c * 32 + i;
-            if (kj >= T || (p.causal && kj > qi)) s[c][i] = 0xff800000u;  // -inf
-          }
-      }
-      // row maximum of the raw logits (four independent chains), then in scaled log2 units
+      const bool need_mask = (p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1) tmem_wait_ld();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[c][i + 0]));
-          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[c][i + 1]));
-          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[c][i + 2]));
-          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[c][i + 3]));
+          for (int c = 2 * h; c < 2 * h + 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kj = k0 + c * 32 + i;
+              if (kj >= T || (p.causal && kj > qi)) s[c][i] = 0xff800000u;  // -inf
+            }
         }
+        // row maximum of the raw logits: four independent chains of three-input maxima
+#pragma unroll
+        for (int c = 2 * h; c < 2 * h + 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            mx4[0] = max3(mx4[0], __uint_as_float(s[c][i + 0]), __uint_as_float(s[c][i + 1]));
+            mx4[1] = max3(mx4[1], __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+            mx4[2] = max3(mx4[2], __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
+            mx4[3] = max3(mx4[3], __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
+          }
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       // Raise the running maximum only on the first step or when it would grow by more than 2^8.
       float m_new = m_used;
@@ -481,29 +545,44 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         l *= f;
       }
       m_used = m_new;
+      TC_TRACE(x, j, 3);
       // p = 2^(s * scale_log2 - m): one FFMA and one ex2 per element; the row sum is taken in fp32
+      // p = 2^(s * scale_log2 - m): one FFMA and one ex2 per element, staged 16 at a time so that
+      // independent operations are in flight; the row sum is taken in fp32.  After the first 64
+      // key columns the MMA warp is told that it may start on that half of P V.
       const float neg_m = -m_used;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 0]), p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 1]), p.scale_log2, neg_m));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 2]), p.scale_log2, neg_m));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 3]), p.scale_log2, neg_m));
-          pk[i] = pack_bf16(p0, p1);
-          pk[i + 1] = pack_bf16(p2, p3);
-          rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
+        for (int g = 0; g < 2; ++g) {
+          float e[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) e[i] = fmaf(__uint_as_float(s[c][g * 16 + i]), p.scale_log2, neg_m);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) e[i] = fast_exp2(e[i]);
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            pk[g * 8 + i / 2] = pack_bf16(e[i], e[i + 1]);
+            pk[g * 8 + i / 2 + 1] = pack_bf16(e[i + 2], e[i + 3]);
+            rs4[0] += e[i]; rs4[1] += e[i + 1]; rs4[2] += e[i + 2]; rs4[3] += e[i + 3];
+          }
         }
         tmem_st16(t_s + c * 16, pk);
+        if (c == 1) {
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(BAR_P_HALF + x));
+        }
       }
       const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l += rs;
+      TC_TRACE(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_READY + x));
+      TC_TRACE(x, j, 5);
     }
     if (ok && n > 0) {
       // epilogue: O / l -> bf16 -> global
@@ -536,7 +615,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -594,6 +673,12 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
 }
 
 }  // namespace
+
+#ifdef MCA_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * count);
+}
+#endif
 
 int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
                         void* y, float* lse, int* status, void* stream) {
