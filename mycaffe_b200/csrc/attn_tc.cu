@@ -10,11 +10,14 @@
 // passes over them; here they never leave the SM.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks the keys 128 at a time:
-//   warps 0-3     softmax for query tile 0, one thread per row
-//   warps 4-7     softmax for query tile 1
-//   warp 8        TMA producer (one lane)
-//   warp 9        MMA issuer (one lane); owns the TMEM allocation
-//   warps 10-11   idle (they complete the third warpgroup)
+//   warps 0-7     softmax for query tile 0: two threads per row, warps 0-3 take the first 64 keys
+//                 of every tile (and the first half of the O columns), warps 4-7 the other half
+//   warps 8-15    softmax for query tile 1, same split
+//   warp 16       TMA producer (one lane)
+//   warp 17       MMA issuer (one lane); owns the TMEM allocation
+// Two warps of a query tile share each scheduler, so while one waits for the ex2 unit the other
+// issues its FMA / pack / add instructions; the pair exchanges its row maxima through shared
+// memory and a 256-thread named barrier once per tile.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (bf16, packed two per
 // column) overwrites the first columns of its S.  The MMA lane alternates between the two
 // query tiles so one tile's softmax overlaps the other tile's products.  The running maximum
@@ -33,9 +36,9 @@ namespace {
 
 constexpr int BLK = 128;               // query rows per tile and keys per step
 constexpr int NQT = 2;                 // query tiles per CTA
-constexpr int TC_THREADS = NQT * 128 + 128;  // two softmax warpgroups + one warpgroup for TMA / MMA
-constexpr int WARP_TMA = NQT * 4;       // first warp of the third warpgroup
-constexpr int WARP_MMA = NQT * 4 + 1;
+constexpr int WARP_TMA = NQT * 8;       // after the softmax warps (two warpgroups per query tile)
+constexpr int WARP_MMA = NQT * 8 + 1;
+constexpr int TC_THREADS = (NQT * 8 + 2) * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
@@ -175,6 +178,21 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -252,7 +270,8 @@ template <int HD> struct Plan {
   static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-  static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;  // barriers (19 x 8 bytes) + TMEM slot + alignment slack
+  static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row-max / row-sum exchange: [2][NQT][2][128] floats
+  static constexpr uint32_t BYTES = OFF_RED + 2 * NQT * 2 * 128 * 4 + 1024;  // + alignment slack
 };
 
 enum Bar : int {  // mbarrier indices
@@ -316,7 +335,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
 #ifdef MCA_TC_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && ((warp & 3) == 0 || warp == WARP_MMA);
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && ((warp & 7) == 0 || warp == WARP_MMA);
 #endif
 
   // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
@@ -406,7 +425,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int kk = half * (BLK / 32); kk < (half + 1) * (BLK / 32); ++kk) {
           // A: P rows in TMEM, 16 bf16 = 8 columns per step.  B: V, 16 key rows = 2048 bytes per step.
-          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + kk * 8,
+          // P of keys 0..63 sits in the first 32 columns of the S tile, P of keys 64..127 from column 64
+          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + (kk / 4) * 64 + (kk % 4) * 8,
                   make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_PV, (first && kk == 0) ? 0u : 1u);
         }
       };
@@ -473,12 +493,17 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp < WARP_TMA) {
     // ------------------------------------------------------------------ softmax warpgroups
-    const int x = warp >> 2;                       // query tile of this warpgroup
+    const int x = warp >> 3;                       // query tile
+    const int half = (warp >> 2) & 1;              // which 64 keys of each tile / which half of the O columns
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int row = lane_base + lane;              // row within the tile
     const int qi = q0 + x * BLK + row;             // absolute query index
-    const uint32_t t_s = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(x * BLK);
-    const uint32_t t_o = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(2 * BLK + x * BLK);
+    constexpr int OC = HD / 2;                     // O columns per thread
+    const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
+    const uint32_t t_s = t_row + (uint32_t)(x * BLK + half * 64);
+    const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + half * OC);
+    float* red = reinterpret_cast<float*>(smem_gen + PL::OFF_RED);
+    auto red_at = [&](int parity, int hf) { return red + ((parity * NQT + x) * 2 + hf) * 128 + row; };
     const int n = n_tiles[x];
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < n && ok; ++j) {
@@ -487,32 +512,29 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (!ok) break;
       TC_TRACE(x, j, 1);
       tc_fence_after();
-      uint32_t s[4][32];
-      tmem_ld32(t_s + 0, s[0]);
-      tmem_ld32(t_s + 32, s[1]);
-      tmem_wait_ld();
-      tmem_ld32(t_s + 64, s[2]);   // in flight while the first half is reduced
-      tmem_ld32(t_s + 96, s[3]);
-      TC_TRACE(x, j, 2);
-      const int k0 = j * BLK;
+      const int k0 = j * BLK + half * 64;
       // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
-      const bool need_mask = (p.causal && k0 + BLK - 1 > q0 + x * BLK) || (k0 + BLK > T);
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (h == 1) tmem_wait_ld();
+      const bool need_mask = (p.causal && j * BLK + BLK - 1 > q0 + x * BLK) || (j * BLK + BLK > T);
+      float mx_half;
+      {
+        // pass 1: maximum of this thread's 64 raw logits (four chains of three-input maxima)
+        uint32_t s[2][32];
+        tmem_ld32(t_s + 0, s[0]);
+        tmem_ld32(t_s + 32, s[1]);
+        tmem_wait_ld();
+        TC_TRACE(x, j, 2);
         if (need_mask) {
 #pragma unroll
-          for (int c = 2 * h; c < 2 * h + 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int kj = k0 + c * 32 + i;
               if (kj >= T || (p.causal && kj > qi)) s[c][i] = 0xff800000u;  // -inf
             }
         }
-        // row maximum of the raw logits: four independent chains of three-input maxima
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 2 * h; c < 2 * h + 2; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             mx4[0] = max3(mx4[0], __uint_as_float(s[c][i + 0]), __uint_as_float(s[c][i + 1]));
@@ -520,79 +542,90 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mx4[2] = max3(mx4[2], __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
             mx4[3] = max3(mx4[3], __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
           }
+        mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      // ... combined with the partner thread that holds the other 64 keys of the row
+      *red_at(j & 1, half) = mx_half;
+      if (x == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      const float mx = fmaxf(mx_half, *red_at(j & 1, half ^ 1)) * p.scale_log2;
       // Raise the running maximum only on the first step or when it would grow by more than 2^8.
       float m_new = m_used;
       bool raise = false;
       if (mx > m_used + RESCALE_THRESHOLD || j == 0) { m_new = fmaxf(mx, m_used); raise = (j > 0); }
       if (m_new == -INFINITY) m_new = 0.f;  // a row with no visible key yet (rows beyond T)
       if (__any_sync(0xffffffffu, raise)) {
-        // rescale O in TMEM: the previous P V product must have finished
+        // rescale this thread's half of O in TMEM: the previous P V product must have finished
         ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
         if (!ok) break;
         tc_fence_after();
         const float f = raise ? fast_exp2(m_used - m_new) : 1.0f;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_o + c * 32, o);
+        for (int c = 0; c < OC / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(t_o + c * 16, o);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st32(t_o + c * 32, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st16(t_o + c * 16, o);
         }
         l *= f;
       }
       m_used = m_new;
       TC_TRACE(x, j, 3);
-      // p = 2^(s * scale_log2 - m): one FFMA and one ex2 per element; the row sum is taken in fp32
-      // p = 2^(s * scale_log2 - m): one FFMA and one ex2 per element, staged 16 at a time so that
-      // independent operations are in flight; the row sum is taken in fp32.  After the first 64
-      // key columns the MMA warp is told that it may start on that half of P V.
+      // pass 2: re-read the logits 16 at a time (the next 16 are in flight meanwhile),
+      // p = 2^(s * scale_log2 - m) with one FFMA and one ex2 per element, packed to bf16 over the
+      // columns just consumed; the row sum is taken in fp32.
       const float neg_m = -m_used;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t sa[16], sb[16];
+      tmem_ld16(t_s, sa);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        uint32_t (&cur)[16] = (c & 1) ? sb : sa;
+        uint32_t (&nxt)[16] = (c & 1) ? sa : sb;
+        tmem_wait_ld();
+        if (c < 3) tmem_ld16(t_s + (c + 1) * 16, nxt);
+        if (need_mask) {
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          float e[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) e[i] = fmaf(__uint_as_float(s[c][g * 16 + i]), p.scale_log2, neg_m);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) e[i] = fast_exp2(e[i]);
-#pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            pk[g * 8 + i / 2] = pack_bf16(e[i], e[i + 1]);
-            pk[g * 8 + i / 2 + 1] = pack_bf16(e[i + 2], e[i + 3]);
-            rs4[0] += e[i]; rs4[1] += e[i + 1]; rs4[2] += e[i + 2]; rs4[3] += e[i + 3];
+          for (int i = 0; i < 16; ++i) {
+            const int kj = k0 + c * 16 + i;
+            if (kj >= T || (p.causal && kj > qi)) cur[i] = 0xff800000u;
           }
         }
-        tmem_st16(t_s + c * 16, pk);
-        if (c == 1) {
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar(BAR_P_HALF + x));
+        uint32_t pk[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(cur[i + 0]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2, neg_m));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(cur[i + 2]), p.scale_log2, neg_m));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(cur[i + 3]), p.scale_log2, neg_m));
+          pk[i / 2] = pack_bf16(p0, p1);
+          pk[i / 2 + 1] = pack_bf16(p2, p3);
+          rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
         }
+        tmem_st8(t_s + c * 8, pk);
       }
-      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      l += rs;
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       TC_TRACE(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(BAR_P_READY + x));
+      mbar_arrive(bar((half == 0 ? BAR_P_HALF : BAR_P_READY) + x));
       TC_TRACE(x, j, 5);
     }
     if (ok && n > 0) {
-      // epilogue: O / l -> bf16 -> global
+      // epilogue: row sum of both halves, then O / l -> bf16 -> global
+      *red_at(n & 1, half) = l;
+      if (x == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      l += *red_at(n & 1, half ^ 1);
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l;
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD;
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(t_o + c * 32, o);
           tmem_wait_ld();
@@ -608,7 +641,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
           }
         }
-        if (p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used + log2f(l);
+        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used + log2f(l);
       }
     }
   }
