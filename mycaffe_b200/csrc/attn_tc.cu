@@ -10,14 +10,13 @@
 // passes over them; here they never leave the SM.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks the keys 128 at a time:
-//   warps 0-7     softmax for query tile 0: two threads per row, warps 0-3 take the first 64 keys
-//                 of every tile (and the first half of the O columns), warps 4-7 the other half
-//   warps 8-15    softmax for query tile 1, same split
+//   warps 0-15    softmax: all sixteen warps work on one query tile at a time, alternating between
+//                 the two tiles.  Four threads share a row (warp w owns rows 32*(w%4).. and the
+//                 32 key columns / quarter of the O columns number w/4), so a tile's softmax is
+//                 short and four warps per scheduler keep the ex2 unit busy; the four threads
+//                 exchange their maxima through shared memory once per tile.
 //   warp 16       TMA producer (one lane)
 //   warp 17       MMA issuer (one lane); owns the TMEM allocation
-// Two warps of a query tile share each scheduler, so while one waits for the ex2 unit the other
-// issues its FMA / pack / add instructions; the pair exchanges its row maxima through shared
-// memory and a 256-thread named barrier once per tile.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (bf16, packed two per
 // column) overwrites the first columns of its S.  The MMA lane alternates between the two
 // query tiles so one tile's softmax overlaps the other tile's products.  The running maximum
@@ -94,6 +93,29 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* 
     }
   }
   return true;
+}
+#ifndef MCA_SPIN_POLLS
+#define MCA_SPIN_POLLS 0
+#endif
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Latency-critical wait of the softmax warps: poll without suspending for a bounded number of
+// rounds (a suspended try_wait wakes up to a few hundred cycles late), then fall back.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
+#pragma unroll 1
+  for (int i = 0; i < MCA_SPIN_POLLS; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, stage, iter);
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -220,6 +242,27 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
   return *reinterpret_cast<float2*>(&d);
 }
+// 2^x on the FMA / ALU pipes instead of the ex2 unit (which is the scarcest resource of the
+// softmax): floor by the round-down magic-number add, a degree-3 minimax polynomial for 2^f on
+// [0,1) (relative error 7.5e-5, far below the bf16 rounding of P), and the integer part added
+// straight into the exponent field.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.0f);
+  float xr;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(xr) : "f"(x), "f"(12582912.0f));  // 1.5 * 2^23: low mantissa bits = floor(x)
+  const float f = x - (xr - 12582912.0f);
+  const float pl = fmaf(fmaf(fmaf(0.07802452147006989f, f, 0.22606715559959412f), f, 0.6958335638046265f), f, 0.9999251961708069f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
+}
+// Which of every eight consecutive elements take the polynomial path (bit i set = element i).
+// Measured on B200 with four softmax warps per scheduler the kernel is bound by instruction
+// issue rather than by the ex2 unit, so the polynomial path costs more than it saves: default off.
+#ifndef MCA_POLY_MASK
+#define MCA_POLY_MASK 0x00
+#endif
+__device__ __forceinline__ float exp2_sel(float x, int i) {
+  return ((MCA_POLY_MASK >> (i & 7)) & 1) ? poly_exp2(x) : fast_exp2(x);
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -270,8 +313,8 @@ template <int HD> struct Plan {
   static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-  static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row-max / row-sum exchange: [2][NQT][2][128] floats
-  static constexpr uint32_t BYTES = OFF_RED + 2 * NQT * 2 * 128 * 4 + 1024;  // + alignment slack
+  static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row-max / row-sum exchange: [2][4][128] floats
+  static constexpr uint32_t BYTES = OFF_RED + 2 * 4 * 128 * 4 + 1024;  // + alignment slack
 };
 
 enum Bar : int {  // mbarrier indices
@@ -285,19 +328,26 @@ enum Bar : int {  // mbarrier indices
   BAR_O_DONE = 14,   // [NQT]  P V product of the step finished
   BAR_DRAIN = 16,
   BAR_P_HALF = 17,   // [NQT]  first 64 key columns of P written
-  BAR_COUNT = 19
+  BAR_RED = 19,      // all softmax threads have published their partial row maximum / sum
+  BAR_COUNT = 20
 };
 
 // Optional timeline capture for tuning (compiled out unless MCA_TC_TRACE is defined): one CTA
 // writes clock64 stamps of its softmax and MMA threads into a small global buffer.
 #ifdef MCA_TC_TRACE
 __device__ long long g_tc_trace[3 * 64 * 8];
+__device__ long long g_tc_trace_w[16 * 64 * 4];  // per softmax warp, query tile 0: got S, local max done, exchange done, arrived
+#define TC_TRACE_W(it, slot)                                                                              \
+  do {                                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && x == 0 && (it) < 64) g_tc_trace_w[(warp * 64 + (it)) * 4 + (slot)] = clock64(); \
+  } while (0)
 #define TC_TRACE(role, it, slot)                                                                         \
   do {                                                                                                   \
     if (trace_on && (it) < 64) g_tc_trace[((role) * 64 + (it)) * 8 + (slot)] = clock64();                \
   } while (0)
 #else
 #define TC_TRACE(role, it, slot) do { } while (0)
+#define TC_TRACE_W(it, slot) do { } while (0)
 #endif
 
 struct TcParams {
@@ -335,7 +385,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
 #ifdef MCA_TC_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && ((warp & 7) == 0 || warp == WARP_MMA);
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && (warp == 0 || warp == WARP_MMA);
 #endif
 
   // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
@@ -347,7 +397,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
       const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT) || (i >= BAR_P_HALF && i < BAR_P_HALF + NQT);
-      mbar_init(bar(i), softmax_bar ? 128u : 1u);
+      mbar_init(bar(i), i == BAR_RED ? 16u : softmax_bar ? 8u : 1u);  // softmax warps arrive once per warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&map_q);
@@ -425,8 +475,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int kk = half * (BLK / 32); kk < (half + 1) * (BLK / 32); ++kk) {
           // A: P rows in TMEM, 16 bf16 = 8 columns per step.  B: V, 16 key rows = 2048 bytes per step.
-          // P of keys 0..63 sits in the first 32 columns of the S tile, P of keys 64..127 from column 64
-          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + (kk / 4) * 64 + (kk % 4) * 8,
+          // P of keys 32q..32q+31 sits in the first 16 columns of quarter q of the S tile
+          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_PV, (first && kk == 0) ? 0u : 1u);
         }
       };
@@ -492,157 +542,154 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_wait(bar(BAR_DRAIN), 0, p.status, 27, 0);
     }
   } else if (warp < WARP_TMA) {
-    // ------------------------------------------------------------------ softmax warpgroups
-    const int x = warp >> 3;                       // query tile
-    const int half = (warp >> 2) & 1;              // which 64 keys of each tile / which half of the O columns
+    // ------------------------------------------------------------------ softmax warps
+    const int qtr = warp >> 2;                     // which 32 keys of each tile / which quarter of the O columns
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int row = lane_base + lane;              // row within the tile
-    const int qi = q0 + x * BLK + row;             // absolute query index
-    constexpr int OC = HD / 2;                     // O columns per thread
+    constexpr int OC = HD / 4;                     // O columns per thread
     const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
-    const uint32_t t_s = t_row + (uint32_t)(x * BLK + half * 64);
-    const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + half * OC);
     float* red = reinterpret_cast<float*>(smem_gen + PL::OFF_RED);
-    auto red_at = [&](int parity, int hf) { return red + ((parity * NQT + x) * 2 + hf) * 128 + row; };
-    const int n = n_tiles[x];
-    float m_used = -INFINITY, l = 0.f;
-    for (int j = 0; j < n && ok; ++j) {
-      TC_TRACE(x, j, 0);
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
-      if (!ok) break;
-      TC_TRACE(x, j, 1);
-      tc_fence_after();
-      const int k0 = j * BLK + half * 64;
-      // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
-      const bool need_mask = (p.causal && j * BLK + BLK - 1 > q0 + x * BLK) || (j * BLK + BLK > T);
-      float mx_half;
-      {
-        // pass 1: maximum of this thread's 64 raw logits (four chains of three-input maxima)
-        uint32_t s[2][32];
-        tmem_ld32(t_s + 0, s[0]);
-        tmem_ld32(t_s + 32, s[1]);
+    auto red_at = [&](int parity, int q) { return red + (parity * 4 + q) * 128 + row; };
+    uint32_t red_cnt = 0;                          // exchanges done so far (parity of the BAR_RED phase)
+    float m_used[NQT], l[NQT];
+#pragma unroll
+    for (int x = 0; x < NQT; ++x) { m_used[x] = -INFINITY; l[x] = 0.f; }
+    for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+      for (int x = 0; x < NQT; ++x) {
+        if (j >= n_tiles[x] || !ok) continue;
+        const int qi = q0 + x * BLK + row;
+        const uint32_t t_s = t_row + (uint32_t)(x * BLK + qtr * 32);
+        const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + qtr * OC);
+        TC_TRACE(x, j, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
+        if (!ok) break;
+        TC_TRACE(x, j, 1);
+        TC_TRACE_W(j, 0);
+        tc_fence_after();
+        uint32_t s[32];
+        tmem_ld32(t_s, s);
         tmem_wait_ld();
         TC_TRACE(x, j, 2);
-        if (need_mask) {
+        const int k0 = j * BLK + qtr * 32;
+        // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
+        if ((p.causal && j * BLK + BLK - 1 > q0 + x * BLK) || (j * BLK + BLK > T)) {
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kj = k0 + c * 32 + i;
-              if (kj >= T || (p.causal && kj > qi)) s[c][i] = 0xff800000u;  // -inf
-            }
+          for (int i = 0; i < 32; ++i) {
+            const int kj = k0 + i;
+            if (kj >= T || (p.causal && kj > qi)) s[i] = 0xff800000u;  // -inf
+          }
         }
+        // maximum of this thread's 32 raw logits, then of the four threads of the row
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int i = 0; i < 32; i += 8) {
+          mx4[0] = max3(mx4[0], __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
+          mx4[1] = max3(mx4[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+          mx4[2] = max3(mx4[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+          mx4[3] = max3(mx4[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+        }
+        const int par = (int)(red_cnt & 1u);
+        *red_at(par, qtr) = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        __syncwarp();
+        TC_TRACE_W(j, 1);
+        if (lane == 0) mbar_arrive(bar(BAR_RED));
+        // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
+        // the row sum is taken in fp32.
+        uint32_t pk[16];
+        float rs;
+        auto exp_tile = [&](float neg_m) {
+          float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            mx4[0] = max3(mx4[0], __uint_as_float(s[c][i + 0]), __uint_as_float(s[c][i + 1]));
-            mx4[1] = max3(mx4[1], __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
-            mx4[2] = max3(mx4[2], __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
-            mx4[3] = max3(mx4[3], __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = exp2_sel(fmaf(__uint_as_float(s[i + 0]), p.scale_log2, neg_m), i + 0);
+            const float p1 = exp2_sel(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_m), i + 1);
+            const float p2 = exp2_sel(fmaf(__uint_as_float(s[i + 2]), p.scale_log2, neg_m), i + 2);
+            const float p3 = exp2_sel(fmaf(__uint_as_float(s[i + 3]), p.scale_log2, neg_m), i + 3);
+            pk[i / 2] = pack_bf16(p0, p1);
+            pk[i / 2 + 1] = pack_bf16(p2, p3);
+            rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
           }
-        mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      }
-      // ... combined with the partner thread that holds the other 64 keys of the row
-      *red_at(j & 1, half) = mx_half;
-      if (x == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-      else asm volatile("bar.sync 2, 256;" ::: "memory");
-      const float mx = fmaxf(mx_half, *red_at(j & 1, half ^ 1)) * p.scale_log2;
-      // Raise the running maximum only on the first step or when it would grow by more than 2^8.
-      float m_new = m_used;
-      bool raise = false;
-      if (mx > m_used + RESCALE_THRESHOLD || j == 0) { m_new = fmaxf(mx, m_used); raise = (j > 0); }
-      if (m_new == -INFINITY) m_new = 0.f;  // a row with no visible key yet (rows beyond T)
-      if (__any_sync(0xffffffffu, raise)) {
-        // rescale this thread's half of O in TMEM: the previous P V product must have finished
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
+          rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        };
+        ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_RED), red_cnt & 1u, p.status, 36, j));
         if (!ok) break;
-        tc_fence_after();
-        const float f = raise ? fast_exp2(m_used - m_new) : 1.0f;
+        TC_TRACE_W(j, 2);
+        ++red_cnt;
+        const float mx = fmaxf(fmaxf(*red_at(par, 0), *red_at(par, 1)), fmaxf(*red_at(par, 2), *red_at(par, 3))) * p.scale_log2;
+        float m_new = m_used[x];
+        bool raise = false;
+        if (mx > m_used[x] + RESCALE_THRESHOLD || j == 0) { m_new = fmaxf(mx, m_used[x]); raise = (j > 0); }
+        if (m_new == -INFINITY) m_new = 0.f;  // a row with no visible key yet (rows beyond T)
+        if (__any_sync(0xffffffffu, raise)) {
+          // rescale this thread's quarter of O in TMEM: the previous P V product must have finished
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
+          if (!ok) break;
+          tc_fence_after();
+          const float f = raise ? fast_exp2(m_used[x] - m_new) : 1.0f;
 #pragma unroll
-        for (int c = 0; c < OC / 16; ++c) {
-          uint32_t o[16];
-          tmem_ld16(t_o + c * 16, o);
-          tmem_wait_ld();
+          for (int c = 0; c < OC / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(t_o + c * 16, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st16(t_o + c * 16, o);
-        }
-        l *= f;
-      }
-      m_used = m_new;
-      TC_TRACE(x, j, 3);
-      // pass 2: re-read the logits 16 at a time (the next 16 are in flight meanwhile),
-      // p = 2^(s * scale_log2 - m) with one FFMA and one ex2 per element, packed to bf16 over the
-      // columns just consumed; the row sum is taken in fp32.
-      const float neg_m = -m_used;
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t sa[16], sb[16];
-      tmem_ld16(t_s, sa);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t (&cur)[16] = (c & 1) ? sb : sa;
-        uint32_t (&nxt)[16] = (c & 1) ? sa : sb;
-        tmem_wait_ld();
-        if (c < 3) tmem_ld16(t_s + (c + 1) * 16, nxt);
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int kj = k0 + c * 16 + i;
-            if (kj >= T || (p.causal && kj > qi)) cur[i] = 0xff800000u;
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st16(t_o + c * 16, o);
           }
+          l[x] *= f;
         }
-        uint32_t pk[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(cur[i + 0]), p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2, neg_m));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(cur[i + 2]), p.scale_log2, neg_m));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(cur[i + 3]), p.scale_log2, neg_m));
-          pk[i / 2] = pack_bf16(p0, p1);
-          pk[i / 2 + 1] = pack_bf16(p2, p3);
-          rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
-        }
-        tmem_st8(t_s + c * 8, pk);
+        exp_tile(-m_new);
+        m_used[x] = m_new;
+        TC_TRACE(x, j, 3);
+        tmem_st16(t_s, pk);
+        l[x] += rs;
+        TC_TRACE(x, j, 4);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar((qtr < 2 ? BAR_P_HALF : BAR_P_READY) + x));
+        TC_TRACE(x, j, 5);
+        TC_TRACE_W(j, 3);
       }
-      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      TC_TRACE(x, j, 4);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar((half == 0 ? BAR_P_HALF : BAR_P_READY) + x));
-      TC_TRACE(x, j, 5);
     }
-    if (ok && n > 0) {
-      // epilogue: row sum of both halves, then O / l -> bf16 -> global
-      *red_at(n & 1, half) = l;
-      if (x == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-      else asm volatile("bar.sync 2, 256;" ::: "memory");
-      l += *red_at(n & 1, half ^ 1);
+    // epilogue: row sums of the four threads, then O / l -> bf16 -> global
+#pragma unroll
+    for (int x = 0; x < NQT; ++x) {
+      const int n = n_tiles[x];
+      if (!ok || n == 0) continue;
+      const int qi = q0 + x * BLK + row;
+      const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + qtr * OC);
+      const int par = (int)(red_cnt & 1u);
+      *red_at(par, qtr) = l[x];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_RED));
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_RED), red_cnt & 1u, p.status, 37, x));
+      if (!ok) break;
+      ++red_cnt;
+      const float lsum = (*red_at(par, 0) + *red_at(par, 1)) + (*red_at(par, 2) + *red_at(par, 3));
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
-      if (ok) {
-        tc_fence_after();
-        const float inv = 1.0f / l;
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = 1.0f / lsum;
+      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + qtr * OC;
 #pragma unroll
-        for (int c = 0; c < OC / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_o + c * 32, o);
-          tmem_wait_ld();
-          if (qi < T) {
+      for (int c = 0; c < OC / 16; ++c) {
+        uint32_t o[16];
+        tmem_ld16(t_o + c * 16, o);
+        tmem_wait_ld();
+        if (qi < T) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
-              w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-              w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(yrow + c * 32 + i) = w;
-            }
+          for (int i = 0; i < 16; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
           }
         }
-        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used + log2f(l);
       }
+      if (qtr == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used[x] + log2f(lsum);
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -710,6 +757,9 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
 #ifdef MCA_TC_TRACE
 extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch(long long* host, int count) {
   return (int)cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * count);
+}
+extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch_w(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_tc_trace_w, sizeof(long long) * count);
 }
 #endif
 
