@@ -67,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                          "-lms", "20", "-i", str(self.gpu_index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -331,7 +331,7 @@ def run_e2e(args, torch, dev, local, rank, world, barrier, B, H, Hl, T, D, q, k,
 
 # --------------------------------------------------------------------------------------------- CPU legs
 
-def cpu_baseline_prefill(T, D, H, q_step=32, heads=4):
+def cpu_baseline_prefill(T, D, H, q_step=4, heads=16):
     """Restated reference math (oracle port), OpenMP over all host cores, on a bounded sample:
     query rows q_step//2::q_step of `heads` heads; throughput is causal FLOPs of those rows / time."""
     import oracle
@@ -405,10 +405,10 @@ def run_reference(args):
     oracle.build()
     vals = []
     for _ in range(args.warmup):
-        cpu_baseline_prefill(args.seq_len, PF_D, PF_H, q_step=256, heads=2)
+        cpu_baseline_prefill(args.seq_len, PF_D, PF_H, q_step=32, heads=16)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        vals.append(cpu_baseline_prefill(args.seq_len, PF_D, PF_H, q_step=256, heads=2))
+        vals.append(cpu_baseline_prefill(args.seq_len, PF_D, PF_H, q_step=32, heads=16))
     dt = time.perf_counter() - t0
     v = float(np.mean([x["value"] for x in vals]))
     base = dict(vals[-1])
