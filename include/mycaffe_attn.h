@@ -166,6 +166,25 @@ MCA_API int mca_decode_attention(const float* q, const float* k_new, const float
                                  const float* freq_real, const float* freq_imag, float* scratch,
                                  int64_t scratch_floats, float* out, void* stream);
 
+/* Decode attention for callers that must not allocate device memory.  No counterpart in the
+ * reference.  Some hosts cannot call cudaMalloc at the point where they decode -- a plug-in that is
+ * only handed its inputs and outputs, or code running where the allocator must stay untouched -- so
+ * this variant keeps the split-KV partials in an 8 MiB array that is part of the library image
+ * (mca_decode_static_scratch_floats() floats; every GPU that loads the library holds it until
+ * exit).  Same arguments and result as mca_decode_attention without the scratch pair.  It calls no
+ * cudaMalloc, cudaFree or any other allocating routine.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress, with that device current); make that first
+ * call before any stream capture.  A problem whose partials do not fit (B * n_heads * nsplit *
+ * (head_size + 2) floats, see mca_decode_plan) is refused with 90906.  All calls share the one
+ * array and it keeps the previous call's contents: nothing in it needs clearing, but two calls
+ * whose kernels overlap on the GPU (different streams or threads) race on it. */
+MCA_API int64_t mca_decode_static_scratch_floats(void);
+MCA_API int mca_decode_attention_static(const float* q, const float* k_new, const float* v_new, void* k_cache,
+                                        void* v_cache, int cache_is_bf16, int64_t cache_batch_stride,
+                                        const int* pos, int B, int n_heads, int n_kv_heads, int head_size,
+                                        int seq_len, int max_len, const float* freq_real, const float* freq_imag,
+                                        float* out, void* stream);
+
 /* TFT interpretable attention forward.  Replaces the attention block of
  * MultiHeadAttentionInterpLayer<T>.forward, MyCaffe.layers.tft/layers.tft/
  * MultiHeadAttentionInterpLayer.cs:728-759.  q (B,H,Nq,d), k (B,H,Nk,d), v (B,Nk,d) shared by the

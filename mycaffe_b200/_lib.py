@@ -37,6 +37,8 @@ SIGNATURES = {
     "mca_decode_plan": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "mca_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i64,
                                   _vp, _vp]),
+    "mca_decode_static_scratch_floats": (_i64, []),
+    "mca_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_tft_attention_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "mca_convert_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "mca_convert_bf16_to_f32": (_i, [_vp, _vp, _i64, _vp]),

@@ -117,6 +117,7 @@ const char* error_name(long e) {
     case ERROR_ATTN_BACKWARD_WITHOUT_FORWARD: return "attn: backward needs a training-mode forward at the configured block size on the same handle";
     case ERROR_ATTN_NOT_B200: return "attn: device is not compute capability 10.x";
     case ERROR_ATTN_SCRATCH_TOO_SMALL: return "attn: scratch too small";
+    case ERROR_ATTN_STATIC_SCRATCH_EXCEEDED: return "attn: problem too large for the library's built-in decode scratch";
   }
   return nullptr;
 }

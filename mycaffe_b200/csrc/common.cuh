@@ -33,6 +33,7 @@ constexpr int ERROR_ATTN_KERNEL_TIMEOUT = ERROR_ATTN_B200 + 2;      // a bounded
 constexpr int ERROR_ATTN_BACKWARD_WITHOUT_FORWARD = ERROR_ATTN_B200 + 3;
 constexpr int ERROR_ATTN_NOT_B200 = ERROR_ATTN_B200 + 4;            // device is not compute capability 10.x
 constexpr int ERROR_ATTN_SCRATCH_TOO_SMALL = ERROR_ATTN_B200 + 5;
+constexpr int ERROR_ATTN_STATIC_SCRATCH_EXCEEDED = ERROR_ATTN_B200 + 6;  // problem too large for the built-in scratch
 
 // Value the reference writes over masked logits (finite): attn.cu:302-329.
 #define MCA_MASKED_LOGIT (-1e29f)

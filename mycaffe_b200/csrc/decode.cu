@@ -13,8 +13,17 @@
 // warp shuffles, keeps an online-softmax state per lane group, and writes one partial
 // (max, sum, weighted V) per head.  A second small kernel combines the partials.  The work
 // is bound by HBM traffic: every cache byte is read exactly once.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
+
+// Scratch of the no-allocation entry point (mca_decode_attention_static): the split partials
+// live in this fixed array instead of caller-provided memory.  Every GPU that loads the library
+// holds these 8 MiB until the process exits.  In host code the symbol is only a stand-in; the
+// device address is obtained once per device with cudaGetSymbolAddress.
+constexpr int64_t MCA_STATIC_SCRATCH_FLOATS = 2 * 1024 * 1024;
+static __device__ __align__(256) float g_static_decode_scratch[MCA_STATIC_SCRATCH_FLOATS];
 
 namespace {
 
@@ -295,6 +304,38 @@ int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_l
   *nsplit = (max_len + (int)sl - 1) / (int)sl;
   *scratch_floats = (int64_t)B * n_heads * (*nsplit) * (head_size + 2);
   return 0;
+}
+
+int64_t mca_decode_static_scratch_floats(void) { return MCA_STATIC_SCRATCH_FLOATS; }
+
+int mca_decode_attention_static(const float* q, const float* k_new, const float* v_new, void* k_cache, void* v_cache,
+                                int cache_is_bf16, int64_t cache_batch_stride, const int* pos, int B, int n_heads,
+                                int n_kv_heads, int head_size, int seq_len, int max_len, const float* freq_real,
+                                const float* freq_imag, float* out, void* stream) {
+  // Device address of the static scratch, looked up once per device with that device current.
+  static std::mutex lock;
+  static float* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  MCA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ERROR_PARAM_OUT_OF_RANGE;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(lock);
+    if (dev_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      MCA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_decode_scratch));
+      dev_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = dev_ptr[dev];
+  }
+  int split_len = 0, nsplit = 0;
+  int64_t need = 0;
+  int e = mca_decode_plan(B, n_heads, n_kv_heads, head_size, max_len, &split_len, &nsplit, &need);
+  if (e) return e;
+  if (nsplit > 1 && need > MCA_STATIC_SCRATCH_FLOATS) return ERROR_ATTN_STATIC_SCRATCH_EXCEEDED;
+  return mca_decode_attention(q, k_new, v_new, k_cache, v_cache, cache_is_bf16, cache_batch_stride, pos, B, n_heads,
+                              n_kv_heads, head_size, seq_len, max_len, freq_real, freq_imag, scratch,
+                              MCA_STATIC_SCRATCH_FLOATS, out, stream);
 }
 
 int mca_decode_attention(const float* q, const float* k_new, const float* v_new, void* k_cache, void* v_cache,
