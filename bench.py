@@ -426,6 +426,44 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_profile_case(case):
+    """Small stand-alone cases for `ncu --set full` captures (a few launches, inputs above L2 where
+    DRAM matters): `prefill-small` = config-5 shape at T = 8192, B = 1; `decode-small` = config-3 shape,
+    16 sequences of 4096 keys."""
+    import torch
+    from mycaffe_b200 import _lib, function_ids as ids
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    if case == "prefill-small":
+        B, H, T, D = 1, PF_H, 8192, PF_D
+        q, k, v = (torch.randn(B, H, T, D, device=dev).div_(D ** 0.5).bfloat16() for _ in range(3))
+        y = torch.empty_like(q)
+        st = torch.zeros(8, dtype=torch.int32, device=dev)
+        for _ in range(3):
+            rc = lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
+                                         y.data_ptr(), None, st.data_ptr(), None)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": case, "rc": rc, "status": st[:4].tolist(), "causal_flops": causal_flops(B, H, T, D)}))
+    else:
+        Bd, nh, hs, S = 16, DEC_HEADS, DEC_HS, DEC_SEQ
+        kv = nh * hs
+        kc, vc = torch.randn(Bd, S, kv, device=dev), torch.randn(Bd, S, kv, device=dev)
+        qn, kn, vn = (torch.randn(Bd, kv, device=dev) for _ in range(3))
+        pos = torch.full((Bd,), S - 1, dtype=torch.int32, device=dev)
+        out = torch.empty(Bd, kv, device=dev)
+        sl, ns, need = C.c_int(), C.c_int(), C.c_int64()
+        lib.mca_decode_plan(Bd, nh, nh, hs, S, C.byref(sl), C.byref(ns), C.byref(need))
+        scratch = torch.empty(need.value, device=dev)
+        fr, fi = torch.ones(S, hs // 2, device=dev), torch.zeros(S, hs // 2, device=dev)
+        for _ in range(3):
+            rc = lib.mca_decode_attention(qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), kc.data_ptr(), vc.data_ptr(), 0,
+                                          S * kv, pos.data_ptr(), Bd, nh, nh, hs, S, S, fr.data_ptr(), fi.data_ptr(),
+                                          scratch.data_ptr(), scratch.numel(), out.data_ptr(), None)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": case, "rc": rc, "split_len": sl.value, "nsplit": ns.value,
+                          "bytes_per_launch": decode_bytes([S] * Bd, kv, kv, 4)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -435,7 +473,11 @@ def main():
     ap.add_argument("--batch", type=int, default=PF_B)
     ap.add_argument("--seq-len", type=int, default=PF_T)
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--case", default=None, choices=["prefill-small", "decode-small"],
+                    help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
+    if args.case:
+        return run_profile_case(args.case)
     args.warmup = max(args.warmup, 3)
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
