@@ -232,6 +232,7 @@ def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
     kn = torch.randn(DEC_B, kv_dim, device=dev)
     vn = torch.randn(DEC_B, kv_dim, device=dev)
     out = torch.empty(DEC_B, dim, device=dev)
+    out_all = torch.empty(world, DEC_B, dim, device=dev) if world > 1 else None
     sl, ns, need = C.c_int(), C.c_int(), C.c_int64()
     lib.mca_decode_plan(DEC_B, heads, heads, DEC_HS, max_len, C.byref(sl), C.byref(ns), C.byref(need))
     scratch = torch.empty(max(1, need.value), device=dev)
@@ -249,6 +250,8 @@ def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
                                       out.data_ptr(), sp)
         if rc:
             raise RuntimeError(f"mca_decode_attention failed with {rc}")
+        if world > 1:  # the head outputs of every rank, as the Wo projection of the next step needs them
+            torch.distributed.all_gather_into_tensor(out_all, out)
 
     steps = max(3, min(args.steps, 10))
     for i in range(3 * DEC_BUFFERS):

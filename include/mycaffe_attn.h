@@ -143,6 +143,14 @@ MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* 
 MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                 int T, int D, void* y, float* lse, int* status, void* stream);
 
+/* Tensor-core SDPA backward (bf16).  Same math as attnHandle<T>::Backward, attn.cu:608-661, with a
+ * causal or absent mask; P is recomputed from `lse` (written by mca_sdpa_forward_tc on the same
+ * inputs) instead of read from a saved (B,H,T,T) tensor.  q,k,v,y,dy,dq,dk,dv: (B,H,T,D) bf16,
+ * D in {64,128}; delta_scratch: (B,H,T) floats of scratch; status as in the forward. */
+MCA_API int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void* y, const void* dy,
+                                 const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
+                                 int T, int D, void* dq, void* dk, void* dv, int* status, void* stream);
+
 /* RoPE on a (B,T,H,D) tensor.  Replaces RopeDataGpu<T>::Forward/Backward, Cuda Files/rope.cu:784-864.
  * Tables are (T,D/2) as built by mca_rope_tables_host. */
 MCA_API int mca_rope_f32(const float* x, float* y, int64_t n, int T, int H, int D, const float* cos_table,

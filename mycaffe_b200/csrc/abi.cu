@@ -365,6 +365,23 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   return 0;
 }
 
+// After a tensor-core launch (unless the caller asked for asynchronous calls): read the status
+// words the kernel writes when one of its bounded waits gives up.
+long tc_status(Kernel* k, AttnHandle& a) {
+  if (k->async) return 0;
+  int st[4] = {0, 0, 0, 0};
+  cudaError_t ce = cudaMemcpy(st, a.causal_flag + 1, sizeof(st), cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) return ce;
+  if (st[0] != 0) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
+    k->last_detail = buf;
+    cudaMemsetAsync(a.causal_flag + 1, 0, 4 * sizeof(int), 0);
+    return ERROR_ATTN_KERNEL_TIMEOUT;
+  }
+  return 0;
+}
+
 long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   long e;  // Device<T>::AttnForward, device.h:2488-2506; attnHandle<T>::Forward, attn.cu:518-602
   if ((e = verify_in(llInput, pl, 9, 9))) return e;
@@ -407,19 +424,13 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   }
   e = mca_sdpa_forward_tc(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, 0);
   if (e) return e;
-  if (!k->async) {
-    int st[4] = {0, 0, 0, 0};
-    cudaError_t ce = cudaMemcpy(st, a.causal_flag + 1, sizeof(st), cudaMemcpyDeviceToHost);
+  if (a.training && T == a.block && bf16) {
+    // Backward needs O and the log-sum-exp of this Forward; it cannot trust the data of hY
+    cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
     if (ce != cudaSuccess) return ce;
-    if (st[0] != 0) {
-      char buf[96];
-      snprintf(buf, sizeof(buf), "status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
-      k->last_detail = buf;
-      cudaMemsetAsync(a.causal_flag + 1, 0, 4 * sizeof(int), 0);
-      return ERROR_ATTN_KERNEL_TIMEOUT;
-    }
+    a.have_fwd = true; a.fwd_T = T; a.fwd_mask = nullptr; a.fwd_mask_mode = mode;
   }
-  return 0;
+  return tc_status(k, a);
 }
 
 long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
@@ -428,12 +439,24 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   auto it = k->attn.find((long)pl[1]);
   if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
   AttnHandle& a = it->second;
-  if (a.dtype != MCA_DTYPE_F32) return ERROR_NOT_IMPLEMENTED;
+  if (a.dtype == MCA_DTYPE_TF32) return ERROR_NOT_IMPLEMENTED;
   // The reference's Backward always works at the configured block size on the tensors its
   // Forward left in the handle (attn.cu:622-634); it reads neither hMask nor the data of hY.
   if (!a.have_fwd || a.fwd_T != a.block) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;
   const int T = a.block;
   const int64_t n = (int64_t)a.B * a.H * T * a.D;
+  if (a.dtype == MCA_DTYPE_BF16) {
+    void *q, *dq, *kk, *dk, *v, *dv, *dy;
+    if ((e = check_any(k, (long)pl[2], n, true, &q)) || (e = check_any(k, (long)pl[3], n, true, &dq)) ||
+        (e = check_any(k, (long)pl[4], n, true, &kk)) || (e = check_any(k, (long)pl[5], n, true, &dk)) ||
+        (e = check_any(k, (long)pl[6], n, true, &v)) || (e = check_any(k, (long)pl[7], n, true, &dv)) ||
+        (e = check_any(k, (long)pl[10], n, true, &dy)))
+      return e;
+    e = mca_sdpa_backward_tc(q, kk, v, a.y_copy, dy, a.lse, a.delta, MCA_DTYPE_BF16, a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B,
+                             a.H, T, a.D, dq, dk, dv, a.causal_flag + 1, 0);
+    if (e) return e;
+    return tc_status(k, a);
+  }
   float *q, *dq, *kk, *dk, *v, *dv, *dy;
   if ((e = check_f32(k, (long)pl[2], n, &q)) || (e = check_f32(k, (long)pl[3], n, &dq)) ||
       (e = check_f32(k, (long)pl[4], n, &kk)) || (e = check_f32(k, (long)pl[5], n, &dk)) ||

@@ -1,0 +1,530 @@
+// Fused attention backward on the tensor cores (sm_100a, bf16): the counterpart of the forward
+// kernel in attn_tc.cu for training.
+//
+// Same mathematics as the reference's attnHandle<T>::Backward (CudaDnnDLL/Cuda Files/
+// attn.cu:608-661 with blob<T>::matmulgrad attn.cu:380-397):
+//   dP = dY V^T,  dV = P^T dY,  dS = P o (dP - rowsum(dP o P)),  dS *= 1/sqrt(D),
+//   dQ = dS K,    dK = dS^T Q
+// The reference reads the (B,H,T,T) probabilities its Forward saved; here P is recomputed tile
+// by tile from the log-sum-exp kept by the forward kernel, and rowsum(dP o P) is taken as
+// delta = rowsum(dY o Y), so no T x T tensor exists.
+//
+// Two kernels (no atomics, deterministic):
+//   * dq kernel: one CTA per 128-row query tile walks the key tiles:  S = Q K^T and dP = dY V^T
+//     (tcgen05.mma, both operands in shared memory), dS computed by sixteen warps straight from
+//     TMEM and written back as a bf16 A operand, dQ += dS K accumulated in TMEM.
+//   * dkdv kernel: one CTA per 128-row key tile walks the query tiles with the transposed
+//     products S^T = K Q^T and dP^T = V dY^T, so that P^T and dS^T come out in the layout the
+//     A operand of dV += P^T dY and dK += dS^T Q needs.
+// Q/K/V/dY tiles arrive by TMA (no multicast) through two-stage rings; every mbarrier wait is
+// bounded as in the forward kernel.
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int EW_WARPS = 16;                 // element-wise warps: four threads per row, 32 columns each
+constexpr int WARP_TMA = EW_WARPS;
+constexpr int WARP_MMA = EW_WARPS + 1;
+constexpr int BW_THREADS = (EW_WARPS + 2) * 32;
+
+template <int HD> struct BwdPlan {
+  static constexpr int SUB = HD / 64;
+  static constexpr uint32_t SUB_BYTES = BLK * 128;
+  static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 x HD bf16
+  // [0] and [1]: the two resident tiles (Q,dY or K,V); then two ring stages of two tiles each
+  static constexpr uint32_t OFF_RES0 = 0;
+  static constexpr uint32_t OFF_RES1 = TILE_BYTES;
+  static constexpr uint32_t OFF_RING = 2 * TILE_BYTES;     // stage s: tile a at +s*2*TILE, tile b at +TILE after it
+  static constexpr uint32_t OFF_BAR = 6 * TILE_BYTES;
+  static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;
+};
+
+struct BwdParams {
+  const float* lse;    // (BH, T) log2-domain log-sum-exp of the scaled logits, from the forward kernel
+  const float* delta;  // (BH, T) rowsum(dY o Y)
+  void* out0;          // dq kernel: dQ;  dkdv kernel: dK
+  void* out1;          // dkdv kernel: dV
+  int* status;
+  int T, causal;
+  float scale_log2;    // (1/sqrt(HD)) * log2(e)
+  float scale;         // 1/sqrt(HD)
+};
+
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 8) {
+    uint4 w;
+    w.x = pack_bf16(__uint_as_float(o[i + 0]) * mul, __uint_as_float(o[i + 1]) * mul);
+    w.y = pack_bf16(__uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
+    w.z = pack_bf16(__uint_as_float(o[i + 4]) * mul, __uint_as_float(o[i + 5]) * mul);
+    w.w = pack_bf16(__uint_as_float(o[i + 6]) * mul, __uint_as_float(o[i + 7]) * mul);
+    *reinterpret_cast<uint4*>(dst + i) = w;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ kernel.  TMEM columns: S [0,128)  dP [128,256)  dS (bf16, packed) [256,320)  dQ [320,320+HD)
+// ---------------------------------------------------------------------------------------------
+enum DqBar : int {
+  DQ_QDO_FULL = 0,
+  DQ_K_FULL = 1,    // [2]
+  DQ_K_EMPTY = 3,   // [2]
+  DQ_V_FULL = 5,    // [2]
+  DQ_V_EMPTY = 7,   // [2]
+  DQ_SDP_FULL = 9,  // S and dP of the step written by the MMA
+  DQ_SDP_FREE = 10, // element-wise warps have S and dP in registers
+  DQ_DS_READY = 11, // dS written to TMEM
+  DQ_DQ_DONE = 12,  // dQ += dS K of the step finished (dS may be overwritten)
+  DQ_DRAIN = 13,
+  DQ_BAR_COUNT = 14
+};
+
+template <int HD>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                      const BwdParams p) {
+  using PL = BwdPlan<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar0 = smem_base + PL::OFF_BAR;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR + DQ_BAR_COUNT * 8);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, T = p.T;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest causal work first
+  const int q0 = qt * BLK;
+  const int n = p.causal ? (min(q0 + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
+
+  __shared__ int s_abort;
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_abort != 0) return;
+  if (tid == 0) {
+    for (int i = 0; i < DQ_BAR_COUNT; ++i)
+      mbar_init(bar(i), (i == DQ_SDP_FREE || i == DQ_DS_READY) ? (uint32_t)EW_WARPS : 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
+  if (warp == WARP_MMA) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DS = 256, C_DQ = 320;
+  bool ok = true;
+
+  if (warp == WARP_TMA) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(DQ_QDO_FULL), 2 * PL::TILE_BYTES);
+#pragma unroll
+      for (int s = 0; s < PL::SUB; ++s) {
+        tma_load_3d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_q, bar(DQ_QDO_FULL), s * 64, q0, bh);
+        tma_load_3d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_do, bar(DQ_QDO_FULL), s * 64, q0, bh);
+      }
+      int issued_k = 0, issued_v = 0;
+      for (int j = 0; j < n && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        const uint32_t k_dst = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, v_dst = k_dst + PL::TILE_BYTES;
+        ok = mbar_wait(bar(DQ_K_EMPTY + st), ph ^ 1u, p.status, 110, j);
+        if (!ok) break;
+        mbar_expect_tx(bar(DQ_K_FULL + st), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s) tma_load_3d(k_dst + s * PL::SUB_BYTES, &map_k, bar(DQ_K_FULL + st), s * 64, j * BLK, bh);
+        issued_k = j + 1;
+        ok = mbar_wait(bar(DQ_V_EMPTY + st), ph ^ 1u, p.status, 111, j);
+        if (!ok) break;
+        mbar_expect_tx(bar(DQ_V_FULL + st), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s) tma_load_3d(v_dst + s * PL::SUB_BYTES, &map_v, bar(DQ_V_FULL + st), s * 64, j * BLK, bh);
+        issued_v = j + 1;
+      }
+      if (!ok) {  // let copies in flight land (bounded) before the CTA's memory is released
+        mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 112, 0);
+        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(bar(DQ_K_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 113, j);
+        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(DQ_V_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 114, j);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);  // both operands K-major
+      constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 0, 1);   // A from TMEM, B = K tile MN-major
+      const uint32_t q_addr = smem_base + PL::OFF_RES0, do_addr = smem_base + PL::OFF_RES1;
+      auto issue_sdp = [&](int st) {
+        const uint32_t k_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, v_addr = k_addr + PL::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+          umma_ss(tmem_base + C_S, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_NT, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+          umma_ss(tmem_base + C_DP, make_desc(do_addr + off, 16, 1024), make_desc(v_addr + off, 16, 1024), IDESC_NT, kk > 0);
+        }
+      };
+      ok = mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 120, 0);
+      if (ok) ok = mbar_wait(bar(DQ_K_FULL + 0), 0, p.status, 121, 0);
+      if (ok) ok = mbar_wait(bar(DQ_V_FULL + 0), 0, p.status, 122, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+        umma_commit(bar(DQ_SDP_FULL));
+        umma_commit(bar(DQ_V_EMPTY + 0));
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        const int st = j & 1, st_n = (j + 1) & 1;
+        const uint32_t ph_n = (uint32_t)(((j + 1) >> 1) & 1);
+        if (j + 1 < n) {
+          // next S / dP as soon as the element-wise warps hold the current ones in registers
+          ok = mbar_wait(bar(DQ_SDP_FREE), (uint32_t)(j & 1), p.status, 123, j);
+          if (ok) ok = mbar_wait(bar(DQ_K_FULL + st_n), ph_n, p.status, 124, j);
+          if (ok) ok = mbar_wait(bar(DQ_V_FULL + st_n), ph_n, p.status, 125, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(st_n);
+          umma_commit(bar(DQ_SDP_FULL));
+          umma_commit(bar(DQ_V_EMPTY + st_n));
+        }
+        ok = mbar_wait(bar(DQ_DS_READY), (uint32_t)(j & 1), p.status, 126, j);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma_ts(tmem_base + C_DQ, tmem_base + C_DS + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(DQ_DQ_DONE));
+        umma_commit(bar(DQ_K_EMPTY + st));
+      }
+      umma_commit(bar(DQ_DRAIN));
+      mbar_wait(bar(DQ_DRAIN), 0, p.status, 127, 0);
+    }
+  } else {
+    // ------------------------------------------------------------------ element-wise warps
+    const int qtr = warp >> 2, lane_base = (warp & 3) * 32, row = lane_base + lane;
+    const int qi = q0 + row;
+    constexpr int OC = HD / 4;
+    const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
+    const bool row_ok = qi < T;
+    const float lse = row_ok ? p.lse[(int64_t)bh * T + qi] : 0.f;
+    const float delta = row_ok ? p.delta[(int64_t)bh * T + qi] : 0.f;
+    for (int j = 0; j < n && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_SDP_FULL), (uint32_t)(j & 1), p.status, 130, j));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[32], dp[32];
+      tmem_ld32(t_row + C_S + qtr * 32, s);
+      tmem_ld32(t_row + C_DP + qtr * 32, dp);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_SDP_FREE));
+      const int k0 = j * BLK + qtr * 32;
+      const bool edge = (p.causal && j * BLK + BLK - 1 > q0) || (j * BLK + BLK > T);
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float d0, d1;
+        {
+          const float pr = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse));
+          d0 = pr * (__uint_as_float(dp[i]) - delta) * p.scale;
+          const float pr1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse));
+          d1 = pr1 * (__uint_as_float(dp[i + 1]) - delta) * p.scale;
+        }
+        if (edge) {
+          const int kj = k0 + i;
+          if (!row_ok || kj >= T || (p.causal && kj > qi)) d0 = 0.f;
+          if (!row_ok || kj + 1 >= T || (p.causal && kj + 1 > qi)) d1 = 0.f;
+        } else if (!row_ok) { d0 = 0.f; d1 = 0.f; }
+        pk[i / 2] = pack_bf16(d0, d1);
+      }
+      if (j > 0) {  // the previous dQ product must have consumed the previous dS
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((j - 1) & 1), p.status, 131, j));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st16(t_row + C_DS + qtr * 16, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_DS_READY));
+    }
+    if (ok && n > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((n - 1) & 1), p.status, 132, n));
+      if (ok) {
+        tc_fence_after();
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + ((int64_t)bh * T + qi) * HD + qtr * OC;
+#pragma unroll
+        for (int c = 0; c < OC / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(t_row + C_DQ + qtr * OC + c * 16, o);
+          tmem_wait_ld();
+          if (row_ok) store_row_bf16(dst + c * 16, o, 1.0f);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK/dV kernel.  TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+HD)  dK [384,384+HD);
+// P^T and dS^T (bf16, packed) overwrite the first 16 columns of each 32-column quarter of S^T / dP^T.
+// ---------------------------------------------------------------------------------------------
+enum KvBar : int {
+  KV_KV_FULL = 0,
+  KV_Q_FULL = 1,     // [2]  Q and dY of a step (one barrier for both tiles)
+  KV_Q_EMPTY = 3,    // [2]
+  KV_ST_FULL = 5,    // S^T and dP^T written by the MMA
+  KV_PT_READY = 6,   // P^T and dS^T written to TMEM
+  KV_ACC_DONE = 7,   // dV / dK products of the step finished
+  KV_DRAIN = 8,
+  KV_BAR_COUNT = 9
+};
+
+template <int HD>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                        const BwdParams p) {
+  using PL = BwdPlan<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar0 = smem_base + PL::OFF_BAR;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR + KV_BAR_COUNT * 8);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, T = p.T;
+  const int kt = blockIdx.x;            // key tile; tile 0 has the most causal work and comes first
+  const int k0 = kt * BLK;
+  const int n_q_tiles = (T + BLK - 1) / BLK;
+  const int i_begin = p.causal ? kt : 0;
+  const int n = n_q_tiles - i_begin;    // query tiles to walk
+
+  __shared__ int s_abort;
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_abort != 0) return;
+  if (tid == 0) {
+    for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), i == KV_PT_READY ? (uint32_t)EW_WARPS : 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
+  if (warp == WARP_MMA) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
+  bool ok = true;
+
+  if (warp == WARP_TMA) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(KV_KV_FULL), 2 * PL::TILE_BYTES);
+#pragma unroll
+      for (int s = 0; s < PL::SUB; ++s) {
+        tma_load_3d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_k, bar(KV_KV_FULL), s * 64, k0, bh);
+        tma_load_3d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_v, bar(KV_KV_FULL), s * 64, k0, bh);
+      }
+      int issued = 0;
+      for (int it = 0; it < n && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)((it >> 1) & 1);
+        const uint32_t q_dst = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, do_dst = q_dst + PL::TILE_BYTES;
+        ok = mbar_wait(bar(KV_Q_EMPTY + st), ph ^ 1u, p.status, 210, it);
+        if (!ok) break;
+        mbar_expect_tx(bar(KV_Q_FULL + st), 2 * PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s) {
+          tma_load_3d(q_dst + s * PL::SUB_BYTES, &map_q, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, bh);
+          tma_load_3d(do_dst + s * PL::SUB_BYTES, &map_do, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, bh);
+        }
+        issued = it + 1;
+      }
+      if (!ok) {
+        mbar_wait(bar(KV_KV_FULL), 0, p.status, 212, 0);
+        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(bar(KV_Q_FULL + (it & 1)), (uint32_t)((it >> 1) & 1), p.status, 213, it);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);
+      constexpr uint32_t IDESC_ACC = make_idesc_bf16(BLK, HD, 0, 1);
+      const uint32_t k_addr = smem_base + PL::OFF_RES0, v_addr = smem_base + PL::OFF_RES1;
+      ok = mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0);
+      for (int it = 0; it < n && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)((it >> 1) & 1);
+        const uint32_t q_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, do_addr = q_addr + PL::TILE_BYTES;
+        ok = mbar_wait(bar(KV_Q_FULL + st), ph, p.status, 221, it);
+        if (!ok) break;
+        tc_fence_after();
+        // S^T = K Q^T and dP^T = V dY^T (rows = keys, columns = queries); they follow the previous
+        // step's dV / dK products in the same in-order pipe, so the aliased columns are free
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+          umma_ss(tmem_base + C_ST, make_desc(k_addr + off, 16, 1024), make_desc(q_addr + off, 16, 1024), IDESC_NT, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+          umma_ss(tmem_base + C_DPT, make_desc(v_addr + off, 16, 1024), make_desc(do_addr + off, 16, 1024), IDESC_NT, kk > 0);
+        }
+        umma_commit(bar(KV_ST_FULL));
+        ok = mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it);
+        if (!ok) break;
+        tc_fence_after();
+        // dV += P^T dY, dK += dS^T Q: A from TMEM (16 queries = 8 packed columns per step), B MN-major
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
+                  make_desc(do_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
+                  make_desc(q_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(KV_Q_EMPTY + st));
+        umma_commit(bar(KV_ACC_DONE));
+      }
+      umma_commit(bar(KV_DRAIN));
+      mbar_wait(bar(KV_DRAIN), 0, p.status, 227, 0);
+    }
+  } else {
+    // ------------------------------------------------------------------ element-wise warps
+    const int qtr = warp >> 2, lane_base = (warp & 3) * 32, row = lane_base + lane;
+    const int kj = k0 + row;               // this thread's key
+    constexpr int OC = HD / 4;
+    const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
+    const bool key_ok = kj < T;
+    for (int it = 0; it < n && ok; ++it) {
+      const int q_base = (i_begin + it) * BLK + qtr * 32;   // first of this thread's 32 queries
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ST_FULL), (uint32_t)(it & 1), p.status, 230, it));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[32], dp[32];
+      tmem_ld32(t_row + C_ST + qtr * 32, s);
+      tmem_ld32(t_row + C_DPT + qtr * 32, dp);
+      tmem_wait_ld();
+      const float* lse_p = p.lse + (int64_t)bh * T + q_base;
+      const float* del_p = p.delta + (int64_t)bh * T + q_base;
+      uint32_t pkp[16], pkd[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float pr[2], ds[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int qi = q_base + i + e;
+          const bool valid = key_ok && qi < T && !(p.causal && kj > qi);
+          const float lse = valid ? __ldg(lse_p + i + e) : 0.f;
+          const float del = valid ? __ldg(del_p + i + e) : 0.f;
+          const float v = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, -lse));
+          pr[e] = valid ? v : 0.f;
+          ds[e] = valid ? v * (__uint_as_float(dp[i + e]) - del) * p.scale : 0.f;
+        }
+        pkp[i / 2] = pack_bf16(pr[0], pr[1]);
+        pkd[i / 2] = pack_bf16(ds[0], ds[1]);
+      }
+      tmem_st16(t_row + C_ST + qtr * 32, pkp);
+      tmem_st16(t_row + C_DPT + qtr * 32, pkd);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_PT_READY));
+    }
+    if (ok && n > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
+      if (ok) {
+        tc_fence_after();
+        __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + ((int64_t)bh * T + kj) * HD + qtr * OC;
+        __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + ((int64_t)bh * T + kj) * HD + qtr * OC;
+#pragma unroll
+        for (int c = 0; c < OC / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(t_row + C_DK + qtr * OC + c * 16, o);
+          tmem_wait_ld();
+          if (key_ok) store_row_bf16(dk_dst + c * 16, o, 1.0f);
+          tmem_ld16(t_row + C_DV + qtr * OC + c * 16, o);
+          tmem_wait_ld();
+          if (key_ok) store_row_bf16(dv_dst + c * 16, o, 1.0f);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// delta[row] = sum_c dY[row][c] * Y[row][c]  (bf16 inputs, fp32 result); one warp per row.
+__global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
+                                      int64_t rows, int D, float* __restrict__ delta) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float acc = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + row * D + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + row * D + c));
+    acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) delta[row] = acc;
+}
+
+template <int HD>
+int launch_bwd(const void* q, const void* k, const void* v, const void* dy, const float* lse, const float* delta,
+               int causal, int B, int H, int T, void* dq, void* dk, void* dv, int* status, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mdo;
+  int e;
+  if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
+      (e = make_map_bf16(&mv, v, B * H, T, HD)) || (e = make_map_bf16(&mdo, dy, B * H, T, HD)))
+    return e;
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal;
+  p.scale = 1.0f / sqrtf((float)HD);
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  const size_t smem = BwdPlan<HD>::BYTES;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(mca_ceil_div(T, BLK), B * H);
+  p.out0 = dk; p.out1 = dv;
+  sdpa_bwd_dkdv_tc_kernel<HD><<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+  if ((e = mca_launch_status())) return e;
+  p.out0 = dq; p.out1 = nullptr;
+  sdpa_bwd_dq_tc_kernel<HD><<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+  return mca_launch_status();
+}
+
+}  // namespace
+
+int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void* y, const void* dy, const float* lse,
+                         float* delta_scratch, int dtype, int causal, int B, int H, int T, int D, void* dq, void* dk,
+                         void* dv, int* status, void* stream) {
+  if (!q || !k || !v || !y || !dy || !lse || !delta_scratch || !dq || !dk || !dv || !status) return ERROR_PARAM_NULL;
+  if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  if (dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+       reinterpret_cast<uintptr_t>(dv)) & 15)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  if (D != 64 && D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows = (int64_t)B * H * T;
+  bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, D,
+                                                                   delta_scratch);
+  int e = mca_launch_status();
+  if (e) return e;
+  if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, st);
+  return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, st);
+}

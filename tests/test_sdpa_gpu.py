@@ -271,3 +271,41 @@ def test_long_context_shape_properties(cuda):
     cm = np.cumsum(v.astype(np.float64), axis=2) / np.arange(1, T + 1)[None, None, :, None]
     assert rel_err(y0, cm) < BF16_TOL
     a.close()
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [128, 256, 200, 640, 1024])
+@pytest.mark.parametrize("causal", [True, False])
+def test_bf16_tensor_core_backward(cuda, T, D, causal):
+    """ATTN_BWD with bf16 handles: tcgen05 dQ and dK/dV kernels against the fp64 oracle."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(7 * T + D)
+    B, H = 2, 2
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, H, T, D))
+    dy = bf16_round(rng.standard_normal(q.shape).astype(np.float32))
+    a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16,
+             flags=ids.MCA_FLAG_CAUSAL_IMPLICIT if causal else 0)
+    y = a.forward(q, k, v, None)
+    mode = 3 if causal else 0
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, None, mode, f64=True)) < BF16_TOL
+    got = a.backward(dy)
+    ref = oracle.sdpa_backward(q, k, v, dy, None, mode, f64=True)
+    for name, g_, r_ in zip("qkv", got, ref):
+        assert rel_err(g_, r_) < BF16_TOL, name
+    a.close()
+
+
+def test_gpt2_small_shape_layer_bf16(cuda):
+    """BASELINE config 2 shape in bf16 (12 heads x 64, T = 1024), forward + backward, B reduced to 2."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(12)
+    B, H, T, D = 2, 12, 1024, 64
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, H, T, D, 0.5))
+    dy = bf16_round(rng.standard_normal(q.shape).astype(np.float32))
+    a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16)
+    y = a.forward(q, k, v, oracle.causal_mask(T))   # the mask handle the C# layer passes
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, None, 3)) < BF16_TOL
+    got = a.backward(dy)
+    for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, None, 3)):
+        assert rel_err(g_, r_) < BF16_TOL
+    a.close()
