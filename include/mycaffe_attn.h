@@ -69,6 +69,8 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode */
 #define MCA_FN_DECODE_FREE 2011    /* floats {hDecode} */
 #define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
+#define MCA_FN_DECODE_QKV 2013     /* floats {eps}; longs {hX,hRmsW,hWq,hWk,hWv,B,dim,kvDim,hQ,hK,hV}: RMSNorm + q,k,v projections */
+#define MCA_FN_DECODE_OUT 2014     /* longs {hAttn,hWo,B,dim,hX}: x += Wo . attn */
 #define MCA_FN_TFT_ATTN_FWD 2020   /* longs {hQ,hK,hV,hMask,B,H,Nq,Nk,d,hOut,hAttn} */
 #define MCA_FN_SET_ASYNC 2030      /* longs {0|1}: 1 = do not synchronise the stream after each call (default 0, as the reference) */
 
@@ -173,6 +175,19 @@ MCA_API int mca_decode_attention(const float* q, const float* k_new, const float
                                  int B, int n_heads, int n_kv_heads, int head_size, int seq_len, int max_len,
                                  const float* freq_real, const float* freq_imag, float* scratch,
                                  int64_t scratch_floats, float* out, void* stream);
+
+/* The projections around the decode attention, each fused with its neighbour and bound by the
+ * one pass over the weights.  Replace Primitives::rmsnorm + three Primitives::matmul (cublasSgemv)
+ * calls, and the Wo matmul + residual add, of TransformerGpu::forward,
+ * CudaExtension.llm32.llama2/Files/llama2_gpu.cpp:56-61,78-81 (kernels primitives.cu:281-340).
+ * Weights are (out, in) row-major as in the llama2 checkpoint (primitives.cu:322-332), fp32 or bf16;
+ * x: (B, dim); dim must be a multiple of 256.
+ *   q,k,v = [Wq;Wk;Wv] . (rms_weight o x / sqrt(mean(x^2) + eps));   x_inout += Wo . attn        */
+MCA_API int mca_decode_qkv_rmsnorm(const float* x, const float* rms_weight, float eps, const void* wq,
+                                   const void* wk, const void* wv, int weights_bf16, int B, int dim, int kv_dim,
+                                   float* q_out, float* k_out, float* v_out, void* stream);
+MCA_API int mca_decode_out_proj(const float* attn, const void* wo, int weights_bf16, int B, int dim, float* x_inout,
+                                void* stream);
 
 /* Decode attention for callers that must not allocate device memory.  No counterpart in the
  * reference.  Some hosts cannot call cudaMalloc at the point where they decode -- a plug-in that is

@@ -38,6 +38,8 @@ SIGNATURES = {
     "mca_decode_plan": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "mca_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i64,
                                   _vp, _vp]),
+    "mca_decode_qkv_rmsnorm": (_i, [_vp, _vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "mca_decode_out_proj": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "mca_decode_static_scratch_floats": (_i64, []),
     "mca_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_tft_attention_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),

@@ -604,6 +604,37 @@ long decode_step(Kernel* k, long llInput, MCA_LONGLONG* pl) {
                               d.scratch_floats, out, 0);
 }
 
+long decode_qkv(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  if ((e = verify_in(llInput, pl, 11, 11))) return e;
+  const int B = (int)pl[5], dim = (int)pl[6], kv_dim = (int)pl[7];
+  if (B <= 0 || dim <= 0 || kv_dim <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  float *x, *rw, *q, *kk, *v;
+  if ((e = check_f32(k, (long)pl[0], (int64_t)B * dim, &x)) || (e = check_f32(k, (long)pl[1], dim, &rw)) ||
+      (e = check_f32(k, (long)pl[8], (int64_t)B * dim, &q)) || (e = check_f32(k, (long)pl[9], (int64_t)B * kv_dim, &kk)) ||
+      (e = check_f32(k, (long)pl[10], (int64_t)B * kv_dim, &v)))
+    return e;
+  MemItem *wq = k->get((long)pl[2]), *wk = k->get((long)pl[3]), *wv = k->get((long)pl[4]);
+  if (!wq || !wk || !wv) return ERROR_MEMORY_NOT_FOUND;
+  if (wq->bf16 != wk->bf16 || wq->bf16 != wv->bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
+  if (wq->count < (int64_t)dim * dim || wk->count < (int64_t)kv_dim * dim || wv->count < (int64_t)kv_dim * dim) return ERROR_MEMORY_TOO_SMALL;
+  return mca_decode_qkv_rmsnorm(x, rw, pf[0], wq->ptr, wk->ptr, wv->ptr, wq->bf16 ? 1 : 0, B, dim, kv_dim, q, kk, v, 0);
+}
+
+long decode_out(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 5, 5))) return e;
+  const int B = (int)pl[2], dim = (int)pl[3];
+  if (B <= 0 || dim <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  float *attn, *x;
+  if ((e = check_f32(k, (long)pl[0], (int64_t)B * dim, &attn)) || (e = check_f32(k, (long)pl[4], (int64_t)B * dim, &x))) return e;
+  MemItem* wo = k->get((long)pl[1]);
+  if (!wo) return ERROR_MEMORY_NOT_FOUND;
+  if (wo->count < (int64_t)dim * dim) return ERROR_MEMORY_TOO_SMALL;
+  return mca_decode_out_proj(attn, wo->ptr, wo->bf16 ? 1 : 0, B, dim, x, 0);
+}
+
 long tft_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   long e;
   if ((e = verify_in(llInput, pl, 11, 11))) return e;
@@ -710,6 +741,8 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
     case MCA_FN_DECODE_CREATE: return decode_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
     case MCA_FN_DECODE_FREE: return decode_free(k, lInput, pf);
     case MCA_FN_DECODE_STEP: return finish(k, decode_step(k, llInput, pl));
+    case MCA_FN_DECODE_QKV: return finish(k, decode_qkv(k, lInput, pf, llInput, pl));
+    case MCA_FN_DECODE_OUT: return finish(k, decode_out(k, llInput, pl));
     case MCA_FN_TFT_ATTN_FWD: return finish(k, tft_fwd(k, llInput, pl));
     case MCA_FN_SET_ASYNC:
       if ((e = verify_in(llInput, pl, 1, 1))) return e;

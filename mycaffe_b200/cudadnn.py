@@ -196,5 +196,13 @@ class CudaDnn:
     def DecodeStep(self, hDecode, hQ, hKnew, hVnew, hKcache, hVcache, hPos, nMaxLen, hOut):
         self._invoke(ids.MCA_FN_DECODE_STEP, None, [hDecode, hQ, hKnew, hVnew, hKcache, hVcache, hPos, nMaxLen, hOut])
 
+    def DecodeQkv(self, hX, hRmsW, hWq, hWk, hWv, nBatch, nDim, nKvDim, hQ, hK, hV, fEps=1e-5):
+        """RMSNorm + q,k,v projections of the new token (llama2_gpu.cpp:56-61)."""
+        self._invoke(ids.MCA_FN_DECODE_QKV, [float(fEps)], [hX, hRmsW, hWq, hWk, hWv, nBatch, nDim, nKvDim, hQ, hK, hV])
+
+    def DecodeOut(self, hAttn, hWo, nBatch, nDim, hX):
+        """x += Wo . attn (llama2_gpu.cpp:78-81)."""
+        self._invoke(ids.MCA_FN_DECODE_OUT, None, [hAttn, hWo, nBatch, nDim, hX])
+
     def TftAttnForward(self, hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn):
         self._invoke(ids.MCA_FN_TFT_ATTN_FWD, None, [hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn])

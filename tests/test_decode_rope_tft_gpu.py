@@ -179,3 +179,70 @@ def test_tft_interpretable_attention(cuda, B, H, Nh, Nf, d, self_attn):
     np.testing.assert_allclose(attn.sum(-1), 1.0, atol=1e-5)
     for h in hs + [hOut, hAttn]:
         cuda.FreeMemory(h)
+
+
+@pytest.mark.parametrize("bf16_weights", [False, True])
+def test_decode_block_projections_match_reference_twin(cuda, tmp_path, bf16_weights):
+    """The whole attention block of one decode step (llama2_gpu.cpp:56-81): fused RMSNorm + q,k,v
+    projections, RoPE + cache append + attention, Wo projection + residual, against the reference's own
+    TransformerCpu on a synthetic one-layer checkpoint."""
+    if oracle.ref_lib() is None:
+        pytest.skip("compiled reference twin not available")
+    dim, n_heads, hs, seq_len = 512, 8, 64, 24
+    rng = np.random.default_rng(3)
+    hidden, vocab = 8, 16
+    mk = lambda *s: (0.05 * rng.standard_normal(s)).astype(np.float32)
+    w = {"rms_att_weight": (1 + 0.1 * rng.standard_normal((1, dim))).astype(np.float32),
+         "rms_ffn_weight": np.ones((1, dim), np.float32), "rms_final_weight": np.ones(dim, np.float32),
+         "token_embedding_table": rng.standard_normal((vocab, dim)).astype(np.float32),
+         "wq": mk(1, dim, dim), "wk": mk(1, dim, dim), "wv": mk(1, dim, dim), "wo": mk(1, dim, dim),
+         "w1": np.zeros((1, hidden, dim), np.float32), "w2": np.zeros((1, dim, hidden), np.float32),
+         "w3": np.zeros((1, hidden, dim), np.float32)}
+    if bf16_weights:  # the reference then runs on the same (bf16-representable) weights in fp32
+        for n_ in ("wq", "wk", "wv", "wo"):
+            w[n_] = bf16_round(w[n_])
+    path = tmp_path / "blk.bin"
+    oracle.write_llama_checkpoint(path, dim, hidden, 1, n_heads, n_heads, vocab, seq_len, w)
+    ref = oracle.RefLlama(path)
+    alloc_w = cuda.AllocMemoryBf16 if bf16_weights else cuda.AllocMemory
+    hW = {n_: alloc_w(w[n_][0]) for n_ in ("wq", "wk", "wv", "wo")}
+    hRms = cuda.AllocMemory(w["rms_att_weight"][0])
+    d = Decoder(cuda, 1, n_heads, n_heads, hs, seq_len, False)
+    hX, hAttn = cuda.AllocMemory(dim), cuda.AllocMemory(dim)
+    tokens = rng.integers(0, vocab, seq_len)
+    for pos in range(seq_len):
+        x0 = w["token_embedding_table"][tokens[pos]]
+        ref.forward(int(tokens[pos]), pos)
+        cuda.SetMemory(hX, x0)
+        cuda.DecodeQkv(hX, hRms, hW["wq"], hW["wk"], hW["wv"], 1, dim, dim, d.hQ, d.hK, d.hV, 1e-5)
+        v_got = cuda.GetMemory(d.hV, dim)
+        assert rel_err(v_got, ref.state("v")) < 2e-5
+        cuda.SetMemoryInt32(d.hPos, np.array([pos], np.int32))
+        cuda.DecodeStep(d.h, d.hQ, d.hK, d.hV, d.hKc, d.hVc, d.hPos, pos + 1, hAttn)
+        cuda.DecodeOut(hAttn, hW["wo"], 1, dim, hX)
+        x1 = cuda.GetMemory(hX, dim)
+        assert rel_err(x1 - x0, ref.state("xb2")) < 5e-5   # the residual update equals Wo . attention output
+    kc, _ = d.caches()
+    assert rel_err(kc[0].ravel(), ref.state("key_cache")) < 2e-5
+    d.close()
+    ref.close()
+
+
+@pytest.mark.parametrize("B", [1, 3, 8, 13])
+def test_fused_rmsnorm_qkv_batched(cuda, B):
+    """Several sequences share one pass over the weights; GQA-shaped (kv_dim < dim) projections."""
+    rng = np.random.default_rng(B)
+    dim, kv_dim = 1024, 256
+    x = rng.standard_normal((B, dim)).astype(np.float32)
+    rw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    wq, wk, wv = ((0.05 * rng.standard_normal(s)).astype(np.float32) for s in ((dim, dim), (kv_dim, dim), (kv_dim, dim)))
+    hs = [cuda.AllocMemory(a) for a in (x, rw, wq, wk, wv)]
+    hQ, hK, hV = cuda.AllocMemory(B * dim), cuda.AllocMemory(B * kv_dim), cuda.AllocMemory(B * kv_dim)
+    cuda.DecodeQkv(hs[0], hs[1], hs[2], hs[3], hs[4], B, dim, kv_dim, hQ, hK, hV, 1e-5)
+    for b in range(B):
+        xn = oracle.rmsnorm(x[b], rw)
+        for h, wmat, n in ((hQ, wq, dim), (hK, wk, kv_dim), (hV, wv, kv_dim)):
+            got = cuda.GetMemory(h, B * n).reshape(B, n)[b]
+            assert rel_err(got, oracle.gemv(wmat, xn)) < 2e-5
+    for h in hs + [hQ, hK, hV]:
+        cuda.FreeMemory(h)
