@@ -411,16 +411,22 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   }
   // tensor-core variants: causal or absent mask only
   if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true))) return e;
+  // tf32 products are an inference-time option for 64-wide heads; training (Backward needs the exact
+  // row statistics) and other head sizes run the exact fp32 kernel on the same fp32 handles
+  const bool tf32_exact = a.dtype == MCA_DTYPE_TF32 && (a.training || a.D != 64);
   const bool bf16 = a.dtype == MCA_DTYPE_BF16;
   void *q, *kk, *v, *y;
   if ((e = check_any(k, (long)pl[3], n, bf16, &q)) || (e = check_any(k, (long)pl[4], n, bf16, &kk)) ||
       (e = check_any(k, (long)pl[5], n, bf16, &v)) || (e = check_any(k, (long)pl[7], n, bf16, &y)))
     return e;
-  if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH) {
+  if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH || tf32_exact) {
     if (bf16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
-    // a general mask with tf32 requested: the exact fp32 kernel handles it
-    return mca_sdpa_forward_f32((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
-                                (float*)y, nullptr, nullptr, nullptr, 0);
+    // a general mask (or training) with tf32 requested: the exact fp32 kernel handles it
+    const bool save = a.training && T == a.block;
+    e = mca_sdpa_forward_f32((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, (float*)y,
+                             save ? a.row_max : nullptr, save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, 0);
+    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; }
+    return e;
   }
   e = mca_sdpa_forward_tc(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, 0);
   if (e) return e;
@@ -439,7 +445,6 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   auto it = k->attn.find((long)pl[1]);
   if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
   AttnHandle& a = it->second;
-  if (a.dtype == MCA_DTYPE_TF32) return ERROR_NOT_IMPLEMENTED;
   // The reference's Backward always works at the configured block size on the tensors its
   // Forward left in the handle (attn.cu:622-634); it reads neither hMask nor the data of hY.
   if (!a.have_fwd || a.fwd_T != a.block) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;

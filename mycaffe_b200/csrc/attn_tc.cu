@@ -46,10 +46,10 @@ constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan (all tiles 1024-byte aligned)
 // ---------------------------------------------------------------------------------------------
-template <int HD> struct Plan {
-  static constexpr int SUB = HD / 64;                      // 64-column (128-byte) sub-tiles per row
+template <int ROW_BYTES> struct Plan {                     // ROW_BYTES = head size x element size
+  static constexpr int SUB = ROW_BYTES / 128;              // 128-byte sub-tiles per row
   static constexpr uint32_t SUB_BYTES = BLK * 128;         // one sub-tile: 128 rows x 128 bytes
-  static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 x HD bf16
+  static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 rows of one tensor
   static constexpr int STAGES = 2;
   static constexpr uint32_t OFF_Q = 0;
   static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
@@ -100,11 +100,15 @@ struct TcParams {
   float scale_log2;  // (1/sqrt(HD)) * log2(e)
 };
 
-template <int HD>
+// TF32 = false: bf16 tensors, kind::f16.  TF32 = true: fp32 tensors read as tf32 (kind::tf32),
+// P handed to the second product as fp32 in place of S, fp32 output.
+template <int HD, bool TF32>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
-  using PL = Plan<HD>;
+  constexpr int ELT = TF32 ? 4 : 2;            // bytes per element
+  constexpr int BOX = 128 / ELT;               // elements per 128-byte sub-tile row
+  using PL = Plan<HD * ELT>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -165,7 +169,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_expect_tx(bar(BAR_Q_FULL + x), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_Q + x * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_q, bar(BAR_Q_FULL + x), s * 64,
+          tma_load_3d(smem_base + PL::OFF_Q + x * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_q, bar(BAR_Q_FULL + x), s * BOX,
                       q0 + x * BLK, bh);
       }
       int issued_k = 0, issued_v = 0;
@@ -177,7 +181,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_expect_tx(bar(BAR_K_FULL + st), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * 64,
+          tma_load_3d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * BOX,
                       j * BLK, bh);
         issued_k = j + 1;
         ok = mbar_wait(bar(BAR_V_EMPTY + st), ph ^ 1u, p.status, 11, j);
@@ -185,7 +189,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_expect_tx(bar(BAR_V_FULL + st), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_V + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_v, bar(BAR_V_FULL + st), s * 64,
+          tma_load_3d(smem_base + PL::OFF_V + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_v, bar(BAR_V_FULL + st), s * BOX,
                       j * BLK, bh);
         issued_v = j + 1;
       }
@@ -200,26 +204,32 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else if (warp == WARP_MMA) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t IDESC_QK = make_idesc_bf16(BLK, BLK, 0, 0);
-      constexpr uint32_t IDESC_PV = make_idesc_bf16(BLK, HD, 0, 1);
+      constexpr uint32_t IDESC_QK = make_idesc_fmt(BLK, BLK, 0, 0, TF32 ? 2 : 1);
+      constexpr uint32_t IDESC_PV = make_idesc_fmt(BLK, HD, 0, 1, TF32 ? 2 : 1);
+      constexpr int KSTEPS_QK = HD * ELT / 32;   // 32 bytes of the head dimension per MMA
+      constexpr int KSTEPS_PV = BLK * ELT / 32;  // 16 (bf16) or 8 (tf32) keys per MMA
       auto issue_qk = [&](int x, int st) {
         const uint32_t q_addr = smem_base + PL::OFF_Q + x * PL::TILE_BYTES;
         const uint32_t k_addr = smem_base + PL::OFF_K + st * PL::TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+        for (int kk = 0; kk < KSTEPS_QK; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss(tmem_base + x * BLK, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_QK,
-                  kk > 0 ? 1u : 0u);
+          umma_ss_t<TF32>(tmem_base + x * BLK, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024),
+                          IDESC_QK, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int x, int st, bool first, int half) {
         const uint32_t v_addr = smem_base + PL::OFF_V + st * PL::TILE_BYTES;
 #pragma unroll
-        for (int kk = half * (BLK / 32); kk < (half + 1) * (BLK / 32); ++kk) {
-          // A: P rows in TMEM, 16 bf16 = 8 columns per step.  B: V, 16 key rows = 2048 bytes per step.
-          // P of keys 32q..32q+31 sits in the first 16 columns of quarter q of the S tile
-          umma_ts(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + (kk / 2) * 32 + (kk % 2) * 8,
-                  make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+        for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk) {
+          // A: P rows in TMEM, 8 columns per step (16 bf16 or 8 tf32).  bf16 P of keys 32q..32q+31 sits in
+          // the first 16 columns of quarter q of the S tile; tf32 P overwrites S column for column.
+          // B: V, one step = 16 or 8 key rows of 128 bytes per sub-tile.
+          const uint32_t a_col = TF32 ? (uint32_t)(kk * 8) : (uint32_t)((kk / 2) * 32 + (kk % 2) * 8);
+          const uint64_t v_desc = TF32 ? make_desc_mn32(v_addr + kk * 1024, PL::SUB_BYTES, 512)
+                                       : make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024);
+          umma_ts_t<TF32>(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + a_col, v_desc, IDESC_PV,
+                          (first && kk == 0) ? 0u : 1u);
         }
       };
 #pragma unroll
@@ -348,8 +358,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float p1 = exp2_sel(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_m), i + 1);
             const float p2 = exp2_sel(fmaf(__uint_as_float(s[i + 2]), p.scale_log2, neg_m), i + 2);
             const float p3 = exp2_sel(fmaf(__uint_as_float(s[i + 3]), p.scale_log2, neg_m), i + 3);
-            pk[i / 2] = pack_bf16(p0, p1);
-            pk[i / 2 + 1] = pack_bf16(p2, p3);
+            if constexpr (TF32) {
+              s[i + 0] = __float_as_uint(p0); s[i + 1] = __float_as_uint(p1);
+              s[i + 2] = __float_as_uint(p2); s[i + 3] = __float_as_uint(p3);
+            } else {
+              pk[i / 2] = pack_bf16(p0, p1);
+              pk[i / 2 + 1] = pack_bf16(p2, p3);
+            }
             rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
           }
           rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
@@ -383,7 +398,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         exp_tile(-m_new);
         m_used[x] = m_new;
         TC_TRACE(x, j, 3);
-        tmem_st16(t_s, pk);
+        if constexpr (TF32) tmem_st32(t_s, s);
+        else tmem_st16(t_s, pk);
         l[x] += rs;
         TC_TRACE(x, j, 4);
         tmem_wait_st();
@@ -414,12 +430,21 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_after();
       const float inv = 1.0f / lsum;
       __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + qtr * OC;
+      float* yrow_f = reinterpret_cast<float*>(p.y) + ((int64_t)bh * T + qi) * HD + qtr * OC;
 #pragma unroll
       for (int c = 0; c < OC / 16; ++c) {
         uint32_t o[16];
         tmem_ld16(t_o + c * 16, o);
         tmem_wait_ld();
-        if (qi < T) {
+        if constexpr (TF32) {
+          if (qi < T) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(yrow_f + c * 16 + i) =
+                  make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, __uint_as_float(o[i + 2]) * inv,
+                              __uint_as_float(o[i + 3]) * inv);
+          }
+        } else if (qi < T) {
 #pragma unroll
           for (int i = 0; i < 16; i += 8) {
             uint4 w;
@@ -444,21 +469,27 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 
-template <int HD>
+template <int HD, bool TF32>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
               int* status, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   int e;
-  if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
-      (e = make_map_bf16(&mv, v, B * H, T, HD)))
-    return e;
+  if constexpr (TF32) {
+    if ((e = make_map_f32(&mq, q, B * H, T, HD)) || (e = make_map_f32(&mk, k, B * H, T, HD)) ||
+        (e = make_map_f32(&mv, v, B * H, T, HD, true)))
+      return e;
+  } else {
+    if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
+        (e = make_map_bf16(&mv, v, B * H, T, HD)))
+      return e;
+  }
   TcParams p;
   p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
-  const size_t smem = Plan<HD>::BYTES;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const size_t smem = Plan<HD * (TF32 ? 4 : 2)>::BYTES;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(mca_ceil_div(T, NQT * BLK), B * H);
-  sdpa_fwd_tc_kernel<HD><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
+  sdpa_fwd_tc_kernel<HD, TF32><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
   return mca_launch_status();
 }
 
@@ -477,12 +508,18 @@ int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, 
                         void* y, float* lse, int* status, void* stream) {
   if (!q || !k || !v || !y || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
-  if (dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;  // tf32 variant: not built yet
+  if (dtype != MCA_DTYPE_BF16 && dtype != MCA_DTYPE_TF32) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(y)) & 15)
     return ERROR_PARAM_OUT_OF_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128) return launch_tc<128>(q, k, v, causal, B, H, T, y, lse, status, st);
-  if (D == 64) return launch_tc<64>(q, k, v, causal, B, H, T, y, lse, status, st);
+  if (dtype == MCA_DTYPE_TF32) {
+    // fp32 rows are twice as wide: only the 64-wide head fits the shared-memory plan (two query tiles,
+    // two K/V stages); wider heads use the exact fp32 kernel
+    if (D == 64) return launch_tc<64, true>(q, k, v, causal, B, H, T, y, lse, status, st);
+    return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  }
+  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y, lse, status, st);
+  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y, lse, status, st);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

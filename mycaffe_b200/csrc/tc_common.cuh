@@ -132,6 +132,32 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same two forms with the operand kind as a template parameter: kind::f16 (bf16 inputs) or
+// kind::tf32 (fp32 inputs read as tf32); fp32 accumulation in TMEM either way.
+template <bool TF32>
+__device__ __forceinline__ void umma_ss_t(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+  }
+}
+template <bool TF32>
+__device__ __forceinline__ void umma_ts_t(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+  }
+}
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -254,6 +280,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 //    apart (SBO); LBO is not used by the swizzled K-major form.
 //  * MN-major operand (rows = K index, 64 bf16 of N per row): 8-row groups along K are 1024
 //    bytes apart (SBO); the next 64 columns of N start LBO bytes later.
+// Layout type 1 (128-byte swizzle with a 32-byte atom) for an MN-major tf32 operand: rows (K index) are
+// 128 bytes, groups of four rows are SBO bytes apart, the next 32 columns of N start LBO bytes later.
+__device__ __forceinline__ uint64_t make_desc_mn32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
+}
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
@@ -279,6 +316,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Same descriptor with the input format as a parameter: 1 = bf16 (kind::f16), 2 = tf32 (kind::tf32).
+__host__ __device__ constexpr uint32_t make_idesc_fmt(int M, int N, int a_mn_major, int b_mn_major, int fmt) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn_major << 15) |
+         ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
 inline EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
   if (fn) return fn;
@@ -301,6 +344,24 @@ inline int make_map_bf16(CUtensorMap* map, const void* base, int BH, int T, int 
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : ERROR_PARAM_OUT_OF_RANGE;
+}
+
+// (BH, T, HD) fp32 tensor, box = 32 columns (128 bytes) x 128 rows of one (b,h).  K-major operands
+// use the ordinary 128-byte swizzle; an MN-major tf32 operand (V) must use the 32-byte-atom variant
+// (the only layout the tensor core accepts for 32-bit MN-major data).
+inline int make_map_f32(CUtensorMap* map, const void* base, int BH, int T, int HD, bool mn_major_operand = false) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return ERROR_NOT_IMPLEMENTED;
+  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)HD * 4, (cuuint64_t)T * HD * 4};
+  cuuint32_t box[3] = {32, (cuuint32_t)BLK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major_operand ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : ERROR_PARAM_OUT_OF_RANGE;
 }

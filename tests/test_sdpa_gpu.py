@@ -295,6 +295,43 @@ def test_bf16_tensor_core_backward(cuda, T, D, causal):
     a.close()
 
 
+TF32_TOL = 5e-3  # tf32 products keep 10 mantissa bits; this variant sits behind a flag for that reason
+
+
+@pytest.mark.parametrize("T", [128, 200, 1024])
+@pytest.mark.parametrize("causal", [True, False])
+def test_tf32_tensor_core_forward(cuda, T, causal):
+    """dtype = MCA_DTYPE_TF32 on fp32 handles: tcgen05 kind::tf32 for 64-wide heads (inference)."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(T)
+    B, H, D = 2, 3, 64
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_TF32, flags=ids.MCA_FLAG_CAUSAL_IMPLICIT if causal else 0)
+    y = a.forward(q, k, v, None)
+    err = rel_err(y, oracle.sdpa_forward(q, k, v, None, 3 if causal else 0, f64=True))
+    assert 1e-6 < err < TF32_TOL   # not the exact-fp32 kernel, and within the tf32 budget
+    a.close()
+
+
+def test_tf32_falls_back_to_exact_fp32_when_training_or_wide(cuda):
+    """Training (Backward needs exact row statistics) and head sizes other than 64 run the exact kernel."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(1)
+    B, H, T, D = 1, 2, 256, 64
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    dy = rng.standard_normal(q.shape).astype(np.float32)
+    a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_TF32, flags=ids.MCA_FLAG_CAUSAL_IMPLICIT)
+    y = a.forward(q, k, v, None)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < FP32_TIGHT
+    for g_, r_ in zip(a.backward(dy), oracle.sdpa_backward(q, k, v, dy, None, 3, f64=True)):
+        assert rel_err(g_, r_) < FP32_TIGHT
+    a.close()
+    q, k, v = rand_qkv(rng, 1, 2, 256, 128)
+    b = Sdpa(cuda, 1, 256, 2, 128, dtype=ids.MCA_DTYPE_TF32)
+    assert rel_err(b.forward(q, k, v, oracle.causal_mask(256)), oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < FP32_TIGHT
+    b.close()
+
+
 def test_gpt2_small_shape_layer_bf16(cuda):
     """BASELINE config 2 shape in bf16 (12 heads x 64, T = 1024), forward + backward, B reduced to 2."""
     from mycaffe_b200 import function_ids as ids
