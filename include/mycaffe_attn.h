@@ -72,6 +72,7 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_DECODE_QKV 2013     /* floats {eps}; longs {hX,hRmsW,hWq,hWk,hWv,B,dim,kvDim,hQ,hK,hV}: RMSNorm + q,k,v projections */
 #define MCA_FN_DECODE_OUT 2014     /* longs {hAttn,hWo,B,dim,hX}: x += Wo . attn */
 #define MCA_FN_TFT_ATTN_FWD 2020   /* longs {hQ,hK,hV,hMask,B,H,Nq,Nk,d,hOut,hAttn} */
+#define MCA_FN_TFT_ATTN_BWD 2021   /* longs {hQ,hK,hV,hMask,hdOut,hdAttn,B,H,Nq,Nk,d,hdQ,hdK,hdV} (hMask, hdAttn may be 0) */
 #define MCA_FN_SET_ASYNC 2030      /* longs {0|1}: 1 = do not synchronise the stream after each call (default 0, as the reference) */
 
 /* 10th long of ATTN_SET */
@@ -214,6 +215,14 @@ MCA_API int mca_decode_attention_static(const float* q, const float* k_new, cons
  * heads, mask (Nq,Nk) masked where 1 (or null) -> out (B,Nq,d) = mean_h P_h V, attn (B,Nq,Nk) = mean_h P_h. */
 MCA_API int mca_tft_attention_forward_f32(const float* q, const float* k, const float* v, const float* mask, int B,
                                           int H, int Nq, int Nk, int d, float* out, float* attn, void* stream);
+
+/* TFT interpretable attention backward.  Replaces the attention part of
+ * MultiHeadAttentionInterpLayer<T>.backward, MultiHeadAttentionInterpLayer.cs:780-859.
+ * d_out (B,Nq,d) and d_attn (B,Nq,Nk, may be null) are the gradients of the two outputs of the
+ * forward; returns dq (B,H,Nq,d), dk (B,H,Nk,d), dv (B,Nk,d). */
+MCA_API int mca_tft_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
+                                           const float* d_out, const float* d_attn, int B, int H, int Nq, int Nk,
+                                           int d, float* dq, float* dk, float* dv, void* stream);
 
 /* float <-> bf16 copies used at the handle boundary. */
 MCA_API int mca_convert_f32_to_bf16(const float* x, void* y, int64_t n, void* stream);

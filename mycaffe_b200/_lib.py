@@ -43,6 +43,7 @@ SIGNATURES = {
     "mca_decode_static_scratch_floats": (_i64, []),
     "mca_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_tft_attention_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "mca_tft_attention_backward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_convert_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "mca_convert_bf16_to_f32": (_i, [_vp, _vp, _i64, _vp]),
     "mca_version": (C.c_char_p, []),

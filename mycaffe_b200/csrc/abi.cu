@@ -654,6 +654,22 @@ long tft_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   return mca_tft_attention_forward_f32(q, kk, v, mask, B, H, Nq, Nk, d, out, attn, 0);
 }
 
+long tft_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(llInput, pl, 14, 14))) return e;
+  const int B = (int)pl[6], H = (int)pl[7], Nq = (int)pl[8], Nk = (int)pl[9], d = (int)pl[10];
+  if (B <= 0 || H <= 0 || Nq <= 0 || Nk <= 0 || d <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  float *q, *kk, *v, *mask = nullptr, *go, *ga = nullptr, *dq, *dk, *dv;
+  if ((e = check_f32(k, (long)pl[0], (int64_t)B * H * Nq * d, &q)) || (e = check_f32(k, (long)pl[1], (int64_t)B * H * Nk * d, &kk)) ||
+      (e = check_f32(k, (long)pl[2], (int64_t)B * Nk * d, &v)) || (e = check_f32(k, (long)pl[4], (int64_t)B * Nq * d, &go)) ||
+      (e = check_f32(k, (long)pl[11], (int64_t)B * H * Nq * d, &dq)) || (e = check_f32(k, (long)pl[12], (int64_t)B * H * Nk * d, &dk)) ||
+      (e = check_f32(k, (long)pl[13], (int64_t)B * Nk * d, &dv)))
+    return e;
+  if (pl[3] != 0 && (e = check_f32(k, (long)pl[3], (int64_t)Nq * Nk, &mask))) return e;
+  if (pl[5] != 0 && (e = check_f32(k, (long)pl[5], (int64_t)B * Nq * Nk, &ga))) return e;
+  return mca_tft_attention_backward_f32(q, kk, v, mask, go, ga, B, H, Nq, Nk, d, dq, dk, dv, 0);
+}
+
 // ---- kernel lifecycle ----------------------------------------------------------------------
 
 long kernel_init(float* pInput, long lInput, long* idx_out) {
@@ -749,6 +765,7 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
     case MCA_FN_DECODE_QKV: return finish(k, decode_qkv(k, lInput, pf, llInput, pl));
     case MCA_FN_DECODE_OUT: return finish(k, decode_out(k, llInput, pl));
     case MCA_FN_TFT_ATTN_FWD: return finish(k, tft_fwd(k, llInput, pl));
+    case MCA_FN_TFT_ATTN_BWD: return finish(k, tft_bwd(k, llInput, pl));
     case MCA_FN_SET_ASYNC:
       if ((e = verify_in(llInput, pl, 1, 1))) return e;
       k->async = pl[0] != 0;

@@ -105,7 +105,141 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_fwd_kernel(const float* __res
   }
 }
 
+// Backward of the block above (MultiHeadAttentionInterpLayer<T>.backward,
+// MultiHeadAttentionInterpLayer.cs:780-859: the two head-mean backward loops, matmul grads,
+// softmax backward, scale, and the sum of the per-head V gradients into the shared V).
+// One CTA per batch element walks the heads; K_h, V and the dK_h / dV accumulators live in shared
+// memory (every thread owns fixed accumulator elements, so there are no atomics); eight query
+// rows are processed per step, one per warp, with the probabilities recomputed.
+// smem: Ks[Nk][d+4] | Vs[Nk][d+4] | dKs[Nk][d] | dVs[Nk][d] | ps[8][Nk] | dss[8][Nk] | qs[8][d] | gos[8][d]
+__global__ void __launch_bounds__(TFT_THREADS) tft_bwd_kernel(const float* __restrict__ Q, const float* __restrict__ K,
+                                                              const float* __restrict__ V,
+                                                              const float* __restrict__ mask,
+                                                              const float* __restrict__ d_out,
+                                                              const float* __restrict__ d_attn, int H, int Nq, int Nk,
+                                                              int d, float scale, float* __restrict__ dQ,
+                                                              float* __restrict__ dK, float* __restrict__ dV) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = d + 4;
+  float* Ks = smem;
+  float* Vs = Ks + (size_t)Nk * ld;
+  float* dKs = Vs + (size_t)Nk * ld;
+  float* dVs = dKs + (size_t)Nk * d;
+  float* ps = dVs + (size_t)Nk * d;
+  float* dss = ps + (size_t)TFT_ROWS * Nk;
+  float* qs = dss + (size_t)TFT_ROWS * Nk;
+  float* gos = qs + (size_t)TFT_ROWS * d;
+  const int b = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int d4 = d / 4;
+  const float inv_h = 1.f / (float)H;
+
+  const float4* Vg = reinterpret_cast<const float4*>(V + (int64_t)b * Nk * d);
+  for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS)
+    *reinterpret_cast<float4*>(Vs + (size_t)(idx / d4) * ld + (idx % d4) * 4) = __ldg(Vg + idx);
+  for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dVs[idx] = 0.f;
+
+  for (int h = 0; h < H; ++h) {
+    __syncthreads();  // previous head's dKs written out, Ks readers done
+    const float4* Kg = reinterpret_cast<const float4*>(K + ((int64_t)b * H + h) * Nk * d);
+    for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS)
+      *reinterpret_cast<float4*>(Ks + (size_t)(idx / d4) * ld + (idx % d4) * 4) = __ldg(Kg + idx);
+    for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dKs[idx] = 0.f;
+    for (int q0 = 0; q0 < Nq; q0 += TFT_ROWS) {
+      __syncthreads();  // K tile loaded / previous step's accumulation done
+      const int i = q0 + w;
+      const bool row_ok = i < Nq;
+      // this warp's query row and its output gradient (already divided by the number of heads)
+      for (int c = lane; c < d; c += 32) {
+        qs[w * d + c] = row_ok ? Q[(((int64_t)b * H + h) * Nq + i) * d + c] : 0.f;
+        gos[w * d + c] = row_ok ? d_out[((int64_t)b * Nq + i) * d + c] * inv_h : 0.f;
+      }
+      __syncwarp();
+      float mx = -INFINITY;
+      for (int j = lane; j < Nk; j += 32) {
+        const float* krow = Ks + (size_t)j * ld;
+        const float* vrow = Vs + (size_t)j * ld;
+        float acc = 0.f, dp = 0.f;
+        for (int c = 0; c < d; c += 4) {
+          const float4 kq = *reinterpret_cast<const float4*>(krow + c);
+          const float4 vq = *reinterpret_cast<const float4*>(vrow + c);
+          const float4 qq = *reinterpret_cast<const float4*>(qs + w * d + c);
+          const float4 gq = *reinterpret_cast<const float4*>(gos + w * d + c);
+          acc = fmaf(qq.x, kq.x, acc); acc = fmaf(qq.y, kq.y, acc); acc = fmaf(qq.z, kq.z, acc); acc = fmaf(qq.w, kq.w, acc);
+          dp = fmaf(gq.x, vq.x, dp); dp = fmaf(gq.y, vq.y, dp); dp = fmaf(gq.z, vq.z, dp); dp = fmaf(gq.w, vq.w, dp);
+        }
+        acc *= scale;
+        if (mask != nullptr && row_ok && __ldg(mask + (int64_t)i * Nk + j) == 1.0f) acc = MCA_MASKED_LOGIT;
+        if (d_attn != nullptr && row_ok) dp += __ldg(d_attn + ((int64_t)b * Nq + i) * Nk + j) * inv_h;
+        ps[w * Nk + j] = acc;
+        dss[w * Nk + j] = dp;
+        mx = fmaxf(mx, acc);
+      }
+      mx = warp_max(mx);
+      float sum = 0.f;
+      for (int j = lane; j < Nk; j += 32) {
+        const float e = expf(ps[w * Nk + j] - mx);
+        ps[w * Nk + j] = e;
+        sum += e;
+      }
+      sum = warp_sum(sum);
+      const float inv = row_ok ? 1.f / sum : 0.f;
+      float dot = 0.f;
+      for (int j = lane; j < Nk; j += 32) {
+        const float pj = ps[w * Nk + j] * inv;
+        ps[w * Nk + j] = pj;
+        dot = fmaf(pj, dss[w * Nk + j], dot);
+      }
+      dot = warp_sum(dot);
+      for (int j = lane; j < Nk; j += 32) dss[w * Nk + j] = ps[w * Nk + j] * (dss[w * Nk + j] - dot) * scale;
+      __syncwarp();
+      if (row_ok) {
+        for (int c = lane; c < d; c += 32) {
+          float acc = 0.f;
+          for (int j = 0; j < Nk; ++j) acc = fmaf(dss[w * Nk + j], Ks[(size_t)j * ld + c], acc);
+          dQ[(((int64_t)b * H + h) * Nq + i) * d + c] = acc;
+        }
+      }
+      __syncthreads();
+      // accumulate dK_h += dS^T Q_h and dV += P^T dO over the eight rows of this step
+      for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) {
+        const int j = idx / d, c = idx % d;
+        float ak = dKs[idx], av = dVs[idx];
+#pragma unroll
+        for (int r = 0; r < TFT_ROWS; ++r) {
+          ak = fmaf(dss[r * Nk + j], qs[r * d + c], ak);
+          av = fmaf(ps[r * Nk + j], gos[r * d + c], av);
+        }
+        dKs[idx] = ak;
+        dVs[idx] = av;
+      }
+    }
+    __syncthreads();
+    float* dKg = dK + ((int64_t)b * H + h) * Nk * d;
+    for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dKg[idx] = dKs[idx];
+  }
+  __syncthreads();
+  float* dVg = dV + (int64_t)b * Nk * d;
+  for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dVg[idx] = dVs[idx];
+}
+
 }  // namespace
+
+int mca_tft_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
+                                   const float* d_out, const float* d_attn, int B, int H, int Nq, int Nk, int d,
+                                   float* dq, float* dk, float* dv, void* stream) {
+  if (!q || !k || !v || !d_out || !dq || !dk || !dv) return ERROR_PARAM_NULL;
+  if (B <= 0 || H <= 0 || Nq <= 0 || Nk <= 0 || d <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  if (d % 4 != 0 || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
+    return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  const size_t smem = sizeof(float) * (2 * (size_t)Nk * (d + 4) + 2 * (size_t)Nk * d + 2 * (size_t)TFT_ROWS * Nk +
+                                       2 * (size_t)TFT_ROWS * d);
+  if (smem > 227 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  tft_bwd_kernel<<<B, TFT_THREADS, smem, (cudaStream_t)stream>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, d,
+                                                                  1.0f / sqrtf((float)d), dq, dk, dv);
+  return mca_launch_status();
+}
 
 int mca_tft_attention_forward_f32(const float* q, const float* k, const float* v, const float* mask, int B, int H,
                                   int Nq, int Nk, int d, float* out, float* attn, void* stream) {

@@ -204,5 +204,9 @@ class CudaDnn:
         """x += Wo . attn (llama2_gpu.cpp:78-81)."""
         self._invoke(ids.MCA_FN_DECODE_OUT, None, [hAttn, hWo, nBatch, nDim, hX])
 
+    def TftAttnBackward(self, hQ, hK, hV, hMask, hdOut, hdAttn, nBatch, nHeads, nQ, nK, nDim, hdQ, hdK, hdV):
+        self._invoke(ids.MCA_FN_TFT_ATTN_BWD, None,
+                     [hQ, hK, hV, hMask, hdOut, hdAttn, nBatch, nHeads, nQ, nK, nDim, hdQ, hdK, hdV])
+
     def TftAttnForward(self, hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn):
         self._invoke(ids.MCA_FN_TFT_ATTN_FWD, None, [hQ, hK, hV, hMask, nBatch, nHeads, nQ, nK, nDim, hOut, hAttn])

@@ -181,6 +181,32 @@ def test_tft_interpretable_attention(cuda, B, H, Nh, Nf, d, self_attn):
         cuda.FreeMemory(h)
 
 
+@pytest.mark.parametrize("B,H,Nh,Nf,d,self_attn,with_attn_grad", [
+    (3, 4, 8, 4, 16, True, True), (64, 4, 168, 24, 64, True, True), (8, 4, 168, 24, 64, False, False),
+    (5, 3, 21, 7, 32, True, False)])
+def test_tft_interpretable_attention_backward(cuda, B, H, Nh, Nf, d, self_attn, with_attn_grad):
+    """Gradients of the TFT attention block w.r.t. Q, K and the shared V, from the gradients of both
+    outputs (MultiHeadAttentionInterpLayer.cs:780-859), against the fp64 oracle."""
+    rng = np.random.default_rng(B * 7 + Nh)
+    Nk = Nh + Nf
+    Nq = Nf if self_attn else Nk
+    q = rng.standard_normal((B, H, Nq, d)).astype(np.float32)
+    k = rng.standard_normal((B, H, Nk, d)).astype(np.float32)
+    v = rng.standard_normal((B, Nk, d)).astype(np.float32)
+    mask = oracle.tft_mask(Nh, Nf) if self_attn else np.triu(np.ones((Nk, Nk), np.float32), 1)
+    d_out = rng.standard_normal((B, Nq, d)).astype(np.float32)
+    d_attn = rng.standard_normal((B, Nq, Nk)).astype(np.float32) if with_attn_grad else None
+    hs = [cuda.AllocMemory(a) for a in (q, k, v, mask, d_out)]
+    hdA = cuda.AllocMemory(d_attn) if with_attn_grad else 0
+    hdQ, hdK, hdV = cuda.AllocMemory(q.size), cuda.AllocMemory(k.size), cuda.AllocMemory(v.size)
+    cuda.TftAttnBackward(hs[0], hs[1], hs[2], hs[3], hs[4], hdA, B, H, Nq, Nk, d, hdQ, hdK, hdV)
+    ref = oracle.tft_backward(q, k, v, mask, d_out, d_attn, f64=True)
+    for h, r_, a in zip((hdQ, hdK, hdV), ref, (q, k, v)):
+        assert rel_err(cuda.GetMemory(h, a.size).reshape(a.shape), r_) < 2e-5
+    for h in hs + [hdQ, hdK, hdV] + ([hdA] if hdA else []):
+        cuda.FreeMemory(h)
+
+
 @pytest.mark.parametrize("bf16_weights", [False, True])
 def test_decode_block_projections_match_reference_twin(cuda, tmp_path, bf16_weights):
     """The whole attention block of one decode step (llama2_gpu.cpp:56-81): fused RMSNorm + q,k,v
