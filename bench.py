@@ -108,7 +108,7 @@ class ClockSampler:
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from mycaffe_b200 import CudaDnn, _lib, function_ids as ids
+    from mycaffe_b200 import CudaDnn, _lib, function_ids as ids, head_shard
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -131,13 +131,13 @@ def run_ours(args):
 
     # ----------------------------------------------------------------- prefill (headline)
     B, H, D, T = args.batch, PF_H, PF_D, args.seq_len
-    assert H % world == 0
-    Hl = H // world
+    h_lo, h_hi = head_shard.head_range(rank, world, H)
+    Hl = h_hi - h_lo
     gen = torch.Generator(device=dev)
     q = torch.empty(B, Hl, T, D, device=dev, dtype=torch.bfloat16)
     k, v = torch.empty_like(q), torch.empty_like(q)
     for hl in range(Hl):  # per-head seeds: the same global problem for every N
-        gen.manual_seed(1000 + rank * Hl + hl)
+        gen.manual_seed(1000 + h_lo + hl)
         for t_ in (q, k, v):
             t_[:, hl] = (torch.randn(B, T, D, device=dev, generator=gen) / D ** 0.5).to(torch.bfloat16)
     y = torch.empty_like(q)
@@ -150,7 +150,7 @@ def run_ours(args):
         if rc:
             raise RuntimeError(f"mca_sdpa_forward_tc failed with {rc}")
         if world > 1:
-            dist.all_gather_into_tensor(y_all, y)
+            head_shard.gather_heads(y, out=y_all, strided=True)
 
     for _ in range(args.warmup):
         prefill_step()
@@ -170,7 +170,7 @@ def run_ours(args):
                                      y.data_ptr(), None, status.data_ptr(), sp)
         kern_ev[i][1].record(stream)
         if world > 1:
-            dist.all_gather_into_tensor(y_all, y)
+            head_shard.gather_heads(y, out=y_all, strided=True)
         ev[i + 1].record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -218,7 +218,9 @@ def run_ours(args):
 
 def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
     """llama2-7B-shape decode attention: one new token for 64 sequences, one launch pair per layer."""
-    heads = DEC_HEADS // world
+    from mycaffe_b200 import head_shard
+    lo, hi = head_shard.head_range(rank, world, DEC_HEADS)
+    heads = hi - lo
     kv_dim = heads * DEC_HS
     dim = heads * DEC_HS
     rng = np.random.default_rng(0)
@@ -251,7 +253,7 @@ def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
         if rc:
             raise RuntimeError(f"mca_decode_attention failed with {rc}")
         if world > 1:  # the head outputs of every rank, as the Wo projection of the next step needs them
-            torch.distributed.all_gather_into_tensor(out_all, out)
+            head_shard.gather_decode_outputs(out, out=out_all)
 
     steps = max(3, min(args.steps, 10))
     for i in range(3 * DEC_BUFFERS):
