@@ -47,7 +47,7 @@ typedef char* MCA_LPTSTR;
 /* inc/FunctionIDs.h:71-95,126-127,222-226,532-535 */
 #define CUDA_FN_SETDEVICE 1
 #define CUDA_FN_SYNCHRONIZEDEVICE 5
-#define CUDA_FN_ALLOCMEM 20        /* longs {count[,hStream]}, floats {count, data...}? -> out[0] = handle (device.cu:854-899) */
+#define CUDA_FN_ALLOCMEM 20        /* longs {count[,hStream]}; optional floats {count[,pad], data...} to initialise -> out[0] = handle (device.cu:854-899) */
 #define CUDA_FN_FREEMEM 21         /* longs {h} */
 #define CUDA_FN_GETMEM 22          /* longs {h[,count]} -> floats (device.cu:973-1026) */
 #define CUDA_FN_SETMEM 23          /* longs {h,count}, floats {h,count,data...} (device.cu:1029) */
