@@ -289,49 +289,84 @@ def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
 
 
 def run_e2e(args, torch, dev, local, rank, world, barrier, B, H, Hl, T, D, q, k, v):
-    """The same prefill step through the reference-facing ABI (SETMEM -> ATTN_FWD -> GETMEM on
-    handles), host buffers in pinned memory, copies inside the timed region."""
+    """The same prefill step from HOST tensors (pinned), copies inside the timed region, three ways:
+    the chunked copy/compute pipeline on bf16 host tensors (id 2003; the headline), the same on fp32
+    host tensors, and the reference's own call sequence SETMEM x3 -> ATTN_FWD -> GETMEM on handles."""
     from mycaffe_b200 import CudaDnn, function_ids as ids
     n = q.numel()
     steps = max(2, min(args.steps, 5))
     cuda = CudaDnn(local)
+
+    def timed(step):
+        step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        barrier()
+        dt = (time.perf_counter() - t0) / steps
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        return dt
+
+    def entry(dt, h2d, d2h, path):
+        return {"value": round(causal_flops(B, H, T, D) / dt / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(dt * 1e3, 3),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps, "path": path}
+
+    # ---- pipelined, bf16 host tensors
+    hb = [t_.cpu().pin_memory() for t_ in (q, k, v)]
+    yb = torch.empty_like(hb[0]).pin_memory()
+    longs = [hb[0].data_ptr(), hb[1].data_ptr(), hb[2].data_ptr(), yb.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D, 0]
+
+    def step_bf16():
+        cuda._invoke(ids.MCA_FN_ATTN_FWD_HOST, None, longs)
+        return float(yb.view(-1)[0])
+
+    res = entry(timed(step_bf16), 3 * n * 2, n * 2,
+                "MCA_FN_ATTN_FWD_HOST: pinned bf16 host tensors, chunks of (batch, head) pairs, H2D / kernel / D2H "
+                "overlapped on three streams, per-rank heads")
+    # ---- pipelined, fp32 host tensors
+    hf = [t_.float().cpu().pin_memory() for t_ in (q, k, v)]
+    yf = torch.empty_like(hf[0]).pin_memory()
+    longs_f = [hf[0].data_ptr(), hf[1].data_ptr(), hf[2].data_ptr(), yf.data_ptr(), ids.MCA_DTYPE_F32, 1, B, Hl, T, D, 0]
+
+    def step_f32():
+        cuda._invoke(ids.MCA_FN_ATTN_FWD_HOST, None, longs_f)
+        return float(yf.view(-1)[0])
+
+    res["host_f32_pipelined"] = entry(timed(step_f32), 3 * n * 4, n * 4,
+                                      "MCA_FN_ATTN_FWD_HOST: pinned fp32 host tensors, converted to bf16 on the device")
+    if not torch.equal(yf.view(-1)[:4096], yb.float().view(-1)[:4096]):
+        raise RuntimeError("fp32-host and bf16-host pipelines disagree")
+    # ---- the reference's call sequence on handles
     hA, hC = cuda.CreateAttn(), cuda.CreateCuDNN()
     cuda.SetAttn(hC, hA, local, False, B, T, Hl, D, 0.0, 0, ids.MCA_DTYPE_BF16, ids.MCA_FLAG_CAUSAL_IMPLICIT)
     hs = [cuda.AllocMemoryBf16(n) for _ in range(4)]
-    # host-side packed SETMEM arrays {handle, count, data...} (CudaDnn.cs SetMemory), pinned
-    packed = []
-    for h, src in zip(hs[:3], (q, k, v)):
+    packed = []  # host-side packed SETMEM arrays {handle, count, data...} (CudaDnn.cs SetMemory), pinned
+    for h, src in zip(hs[:3], hf):
         buf = torch.empty(n + 2, dtype=torch.float32, pin_memory=True)
         buf[0], buf[1] = float(h), float(n)
-        buf[2:] = src.float().flatten().cpu()
+        buf[2:] = src.flatten()
         packed.append(buf.numpy())
-    out_host = torch.empty(n, dtype=torch.float32, pin_memory=True).numpy()
+    out_host = yf.view(-1).numpy()
 
-    def step():
+    def step_handles():
         for h, pk in zip(hs[:3], packed):
             cuda._invoke_raw(ids.CUDA_FN_SETMEM, pk, [h, n])
         cuda.AttnScaledDotProductForward(hC, hA, T, hs[0], hs[1], hs[2], 0, hs[3], False)
         cuda.GetMemoryInto(hs[3], out_host)
         return float(out_host[0])
 
-    step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    barrier()
-    dt = (time.perf_counter() - t0) / steps
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([dt], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
+    res["reference_call_sequence"] = entry(timed(step_handles), 3 * n * 4, n * 4,
+                                           "SETMEM x3 (float host arrays, converted to bf16 on the device) -> ATTN_FWD "
+                                           "-> GETMEM on handles, blocking copies as the reference issues them")
     for h in hs:
         cuda.FreeMemory(h)
     cuda.Dispose()
-    return {"value": round(causal_flops(B, H, T, D) / dt / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(dt * 1e3, 3),
-            "h2d_bytes_per_step": 3 * n * 4, "d2h_bytes_per_step": n * 4, "steps": steps,
-            "path": "SETMEM x3 (float host arrays, converted to bf16 on the device) -> ATTN_FWD -> GETMEM, per-rank heads"}
+    return res
 
 
 # --------------------------------------------------------------------------------------------- CPU legs

@@ -66,6 +66,7 @@ typedef char* MCA_LPTSTR;
 /* Ids added by this library (no counterpart in the reference; above its highest id). */
 #define MCA_FN_ALLOCMEM_BF16 2001  /* longs {count} -> handle to bf16 storage; SETMEM/GETMEM convert from/to float */
 #define MCA_FN_CONVERT 2002        /* longs {hSrc,hDst,count}: copy with float<->bf16 conversion as the handles require */
+#define MCA_FN_ATTN_FWD_HOST 2003  /* longs {pQ,pK,pV,pY (host addresses),hostDtype,causal,B,H,T,D[,headsPerChunk]}: mca_sdpa_forward_host */
 #define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode */
 #define MCA_FN_DECODE_FREE 2011    /* floats {hDecode} */
 #define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
@@ -153,6 +154,22 @@ MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int
 MCA_API int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void* y, const void* dy,
                                  const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
                                  int T, int D, void* dq, void* dk, void* dv, int* status, void* stream);
+
+/* Tensor-core SDPA forward for tensors in HOST memory.  Replaces the reference's host round trip
+ * SetMemory x3 -> AttnScaledDotProductForward -> GetMemory (CudaDnn.cs:2946,3027,5673-5679; the
+ * copies are blocking cudaMemcpy calls, Cuda Files/memory.cu:451,539, and attn.cu:601 synchronises), whose time is the sum of
+ * its parts: here chunks of consecutive (batch, head) pairs flow through three streams so that
+ * the PCIe copies in both directions overlap the kernel.  q,k,v,y: host (B,H,T,D), fp32
+ * (host_dtype MCA_DTYPE_F32; converted to bf16 on the device) or bf16 (MCA_DTYPE_BF16); pinned
+ * memory is needed for overlap.  D in {64,128}; causal or no mask; arithmetic as
+ * mca_sdpa_forward_tc in bf16.  heads_per_chunk 0 = chosen by mca_host_pipeline_chunk.
+ * Returns when y is complete.  Device staging is owned by the library and grows on demand. */
+MCA_API int mca_sdpa_forward_host(const void* q, const void* k, const void* v, void* y, int host_dtype, int causal,
+                                  int B, int H, int T, int D, int heads_per_chunk);
+/* (batch, head) pairs per chunk the pipeline uses (host arithmetic, no device call). */
+MCA_API int mca_host_pipeline_chunk(int B, int H, int T, int heads_per_chunk);
+/* Free the pipeline's device staging buffers on the current device. */
+MCA_API int mca_host_pipeline_release(void);
 
 /* RoPE on a (B,T,H,D) tensor.  Replaces RopeDataGpu<T>::Forward/Backward, Cuda Files/rope.cu:784-864.
  * Tables are (T,D/2) as built by mca_rope_tables_host. */

@@ -33,6 +33,9 @@ SIGNATURES = {
     "mca_classify_causal_mask": (_i, [_vp, _i, _vp, _vp]),
     "mca_sdpa_forward_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_sdpa_backward_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mca_sdpa_forward_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "mca_host_pipeline_chunk": (_i, [_i, _i, _i, _i]),
+    "mca_host_pipeline_release": (_i, []),
     "mca_rope_f32": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "mca_rope_tables_host": (_i, [_i, _i, C.c_float, _fp, _fp]),
     "mca_decode_plan": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),

@@ -766,6 +766,12 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
     case MCA_FN_DECODE_OUT: return finish(k, decode_out(k, llInput, pl));
     case MCA_FN_TFT_ATTN_FWD: return finish(k, tft_fwd(k, llInput, pl));
     case MCA_FN_TFT_ATTN_BWD: return finish(k, tft_bwd(k, llInput, pl));
+    case MCA_FN_ATTN_FWD_HOST:
+      if ((e = verify_in(llInput, pl, 10, 11))) return e;
+      return mca_sdpa_forward_host(reinterpret_cast<const void*>(pl[0]), reinterpret_cast<const void*>(pl[1]),
+                                   reinterpret_cast<const void*>(pl[2]), reinterpret_cast<void*>(pl[3]), (int)pl[4],
+                                   (int)pl[5], (int)pl[6], (int)pl[7], (int)pl[8], (int)pl[9],
+                                   llInput > 10 ? (int)pl[10] : 0);
     case MCA_FN_SET_ASYNC:
       if ((e = verify_in(llInput, pl, 1, 1))) return e;
       k->async = pl[0] != 0;

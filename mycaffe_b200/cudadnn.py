@@ -204,6 +204,18 @@ class CudaDnn:
         """x += Wo . attn (llama2_gpu.cpp:78-81)."""
         self._invoke(ids.MCA_FN_DECODE_OUT, None, [hAttn, hWo, nBatch, nDim, hX])
 
+    def AttnForwardHost(self, q, k, v, y, bCausal, nHeadsPerChunk=0):
+        """Forward for (B,H,T,D) numpy tensors in host memory (float32, or bf16 bit patterns as uint16),
+        copies overlapped with the kernel; `y` is filled in place."""
+        B, H, T, D = q.shape
+        dt = ids.MCA_DTYPE_F32 if q.dtype == np.float32 else ids.MCA_DTYPE_BF16
+        for a in (q, k, v, y):
+            assert a.flags.c_contiguous and a.dtype == q.dtype and a.shape == q.shape
+        assert q.dtype in (np.float32, np.uint16)
+        self._invoke(ids.MCA_FN_ATTN_FWD_HOST, None,
+                     [q.ctypes.data, k.ctypes.data, v.ctypes.data, y.ctypes.data, dt, 1 if bCausal else 0, B, H, T, D,
+                      int(nHeadsPerChunk)])
+
     def TftAttnBackward(self, hQ, hK, hV, hMask, hdOut, hdAttn, nBatch, nHeads, nQ, nK, nDim, hdQ, hdK, hdV):
         self._invoke(ids.MCA_FN_TFT_ATTN_BWD, None,
                      [hQ, hK, hV, hMask, hdOut, hdAttn, nBatch, nHeads, nQ, nK, nDim, hdQ, hdK, hdV])

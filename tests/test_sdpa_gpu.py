@@ -346,3 +346,44 @@ def test_gpt2_small_shape_layer_bf16(cuda):
     for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, None, 3)):
         assert rel_err(g_, r_) < BF16_TOL
     a.close()
+
+
+def _to_bf16_bits(a):
+    return (bf16_round(a).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def _from_bf16_bits(u):
+    return (u.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("host", ["f32", "bf16"])
+@pytest.mark.parametrize("B,H,T,D,chunk", [(1, 1, 128, 64, 0), (2, 3, 200, 128, 0), (2, 5, 384, 64, 3),
+                                           (1, 7, 1000, 128, 2), (3, 4, 256, 128, 1)])
+def test_forward_from_host_tensors_pipelined(cuda, host, B, H, T, D, chunk):
+    """Chunked three-stream pipeline over host tensors (id 2003): same result as the oracle whatever the
+    chunking (including a ragged last chunk), for fp32 and bf16 host tensors, and identical to the
+    handle-based bf16 path."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(B * 1000 + T + D)
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, H, T, D))
+    ref = oracle.sdpa_forward(q, k, v, oracle.causal_mask(T), 1, f64=True)
+    if host == "f32":
+        y = np.zeros_like(q)
+        cuda.AttnForwardHost(q, k, v, y, True, chunk)
+    else:
+        yb = np.zeros(q.shape, np.uint16)
+        cuda.AttnForwardHost(_to_bf16_bits(q), _to_bf16_bits(k), _to_bf16_bits(v), yb, True, chunk)
+        y = _from_bf16_bits(yb)
+    assert rel_err(y, ref) < BF16_TOL
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16, flags=ids.MCA_FLAG_CAUSAL_IMPLICIT)
+    y2 = a.forward(q, k, v, None)
+    a.close()
+    np.testing.assert_array_equal(y, y2)
+
+
+def test_forward_from_host_rejects_bad_arguments(cuda):
+    from mycaffe_b200 import CudaDnnError
+    q = np.zeros((1, 1, 128, 32), np.float32)
+    with pytest.raises(CudaDnnError) as ei:
+        cuda.AttnForwardHost(q, q, q, q.copy(), True)
+    assert ei.value.code == 90901      # no tensor-core kernel for this head size
