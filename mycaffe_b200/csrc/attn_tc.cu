@@ -1,5 +1,5 @@
 // Fused flash-style attention forward on the 5th-generation tensor cores (sm_100a):
-// S = Q K^T by tcgen05.mma into TMEM, online softmax by two warpgroups that read S from TMEM
+// S = Q K^T by tcgen05.mma into TMEM, online softmax by two groups of eight warps that read S from TMEM
 // and write the probabilities back to TMEM as the A operand of the second product, O += P V
 // accumulated in TMEM; Q/K/V tiles arrive by TMA (cp.async.bulk.tensor, no multicast) into
 // 128-byte-swizzled shared memory behind mbarrier pipelines.
@@ -10,13 +10,15 @@
 // passes over them; here they never leave the SM.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks the keys 128 at a time:
-//   warps 0-15    softmax: all sixteen warps work on one query tile at a time, alternating between
-//                 the two tiles.  Four threads share a row (warp w owns rows 32*(w%4).. and the
-//                 32 key columns / quarter of the O columns number w/4), so a tile's softmax is
-//                 short and four warps per scheduler keep the ex2 unit busy; the four threads
-//                 exchange their maxima through shared memory once per tile.
+//   warps 0-7     softmax of query tile 0, warps 8-15 of query tile 1.  A warp reads 16 rows x
+//                 128 keys of S in the 16-lane quad layout (four threads per row), so the row
+//                 maximum and sum are two shuffles, no shared memory and no barrier; the two
+//                 groups run independently, one tile's exponentials over the other's loads.
 //   warp 16       TMA producer (one lane)
-//   warp 17       MMA issuer (one lane); owns the TMEM allocation
+//   warp 17       MMA issuer: the warp runs in lock step and one elected lane issues, so that
+//                 descriptors are warp-uniform values (the issuing thread's instruction count per
+//                 tcgen05.mma bounds the tensor rate when it shares a scheduler with four busy
+//                 softmax warps); owns the TMEM allocation
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (bf16, packed two per
 // column) overwrites the first columns of its S.  The MMA lane alternates between the two
 // query tiles so one tile's softmax overlaps the other tile's products.  The running maximum
@@ -38,7 +40,7 @@ namespace {
 using namespace tc;
 
 constexpr int NQT = 2;                 // query tiles per CTA
-constexpr int WARP_TMA = NQT * 8;       // after the softmax warps (two warpgroups per query tile)
+constexpr int WARP_TMA = NQT * 8;       // after the softmax warps (eight per query tile)
 constexpr int WARP_MMA = NQT * 8 + 1;
 constexpr int TC_THREADS = (NQT * 8 + 2) * 32;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -55,7 +57,7 @@ template <int ROW_BYTES> struct Plan {                     // ROW_BYTES = head s
   static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-  static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row-max / row-sum exchange: [2][4][128] floats
+  static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row sums and maxima for the epilogue: [NQT][2][128] floats
   static constexpr uint32_t BYTES = OFF_RED + 2 * 4 * 128 * 4 + 1024;  // + alignment slack
 };
 
@@ -70,14 +72,14 @@ enum Bar : int {  // mbarrier indices
   BAR_O_DONE = 14,   // [NQT]  P V product of the step finished
   BAR_DRAIN = 16,
   BAR_P_HALF = 17,   // [NQT]  first 64 key columns of P written
-  BAR_RED = 19,      // all softmax threads have published their partial row maximum / sum
-  BAR_COUNT = 20
+  BAR_RED = 19,      // [NQT]  the group's row sums are in shared memory (epilogue)
+  BAR_COUNT = 21
 };
 
 // Optional timeline capture for tuning (compiled out unless MCA_TC_TRACE is defined): one CTA
 // writes clock64 stamps of its softmax and MMA threads into a small global buffer.
 #ifdef MCA_TC_TRACE
-__device__ long long g_tc_trace[3 * 64 * 8];
+__device__ long long g_tc_trace[4 * 64 * 8];
 __device__ long long g_tc_trace_w[16 * 64 * 4];  // per softmax warp, query tile 0: got S, local max done, exchange done, arrived
 #define TC_TRACE_W(it, slot)                                                                              \
   do {                                                                                                   \
@@ -131,7 +133,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
 #ifdef MCA_TC_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && (warp == 0 || warp == WARP_MMA);
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && (warp == 0 || warp == 8 || warp == WARP_MMA);
 #endif
 
   // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
@@ -143,7 +145,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
       const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT) || (i >= BAR_P_HALF && i < BAR_P_HALF + NQT);
-      mbar_init(bar(i), i == BAR_RED ? 16u : softmax_bar ? 8u : 1u);  // softmax warps arrive once per warp
+      mbar_init(bar(i), (softmax_bar || i >= BAR_RED) ? 8u : 1u);  // the eight warps of a group arrive once per warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&map_q);
@@ -203,260 +205,305 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp == WARP_MMA) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this role in lock step and one elected lane issues the tcgen05
+    // instructions: addresses and descriptors are then warp-uniform values, which keeps the
+    // per-instruction overhead of the issuing thread small.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t IDESC_QK = make_idesc_fmt(BLK, BLK, 0, 0, TF32 ? 2 : 1);
       constexpr uint32_t IDESC_PV = make_idesc_fmt(BLK, HD, 0, 1, TF32 ? 2 : 1);
       constexpr int KSTEPS_QK = HD * ELT / 32;   // 32 bytes of the head dimension per MMA
       constexpr int KSTEPS_PV = BLK * ELT / 32;  // 16 (bf16) or 8 (tf32) keys per MMA
+      // A descriptor's start-address field (bits 0-13, in 16-byte units) never carries for offsets
+      // inside the CTA's shared memory, so stepping a tile is an add on the low word.
+      const uint64_t desc_q0 = make_desc(smem_base + PL::OFF_Q, 16, 1024);
+      const uint64_t desc_k0 = make_desc(smem_base + PL::OFF_K, 16, 1024);
+      const uint64_t desc_v0 = TF32 ? make_desc_mn32(smem_base + PL::OFF_V, PL::SUB_BYTES, 512)
+                                    : make_desc(smem_base + PL::OFF_V, PL::SUB_BYTES, 1024);
+      constexpr uint32_t V_STEP = (TF32 ? 1024u : 2048u) >> 4;  // one MMA's key rows of V
+      auto commit_by_leader = [&](uint32_t b) { umma_commit_if(leader, b); };
       auto issue_qk = [&](int x, int st) {
-        const uint32_t q_addr = smem_base + PL::OFF_Q + x * PL::TILE_BYTES;
-        const uint32_t k_addr = smem_base + PL::OFF_K + st * PL::TILE_BYTES;
+        const uint64_t dq = desc_q0 + (uint64_t)((x * PL::TILE_BYTES) >> 4);
+        const uint64_t dk = desc_k0 + (uint64_t)((st * PL::TILE_BYTES) >> 4);
+        const uint32_t d_tmem = tmem_base_u + x * BLK;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS_QK; ++kk) {
-          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss_t<TF32>(tmem_base + x * BLK, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024),
-                          IDESC_QK, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((uint32_t)(kk >> 2) * PL::SUB_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
+          umma_ss_if<TF32>(leader, d_tmem, dq + off, dk + off, IDESC_QK, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int x, int st, bool first, int half) {
-        const uint32_t v_addr = smem_base + PL::OFF_V + st * PL::TILE_BYTES;
+        // A: P rows in TMEM, 8 columns per step (16 bf16 or 8 tf32).  bf16 P is packed two keys per column
+        // into the first 64 columns of the S tile; tf32 P overwrites S column for column.
+        // B: V, one step = 16 or 8 key rows of 128 bytes per sub-tile.
+        const uint64_t dv = desc_v0 + (uint64_t)((st * PL::TILE_BYTES) >> 4);
+        const uint32_t d_tmem = tmem_base_u + 2 * BLK + x * BLK;
+        const uint32_t a_tmem = tmem_base_u + x * BLK;
 #pragma unroll
-        for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk) {
-          // A: P rows in TMEM, 8 columns per step (16 bf16 or 8 tf32).  bf16 P of keys 32q..32q+31 sits in
-          // the first 16 columns of quarter q of the S tile; tf32 P overwrites S column for column.
-          // B: V, one step = 16 or 8 key rows of 128 bytes per sub-tile.
-          const uint32_t a_col = TF32 ? (uint32_t)(kk * 8) : (uint32_t)((kk / 2) * 32 + (kk % 2) * 8);
-          const uint64_t v_desc = TF32 ? make_desc_mn32(v_addr + kk * 1024, PL::SUB_BYTES, 512)
-                                       : make_desc(v_addr + kk * 2048, PL::SUB_BYTES, 1024);
-          umma_ts_t<TF32>(tmem_base + 2 * BLK + x * BLK, tmem_base + x * BLK + a_col, v_desc, IDESC_PV,
-                          (first && kk == 0) ? 0u : 1u);
-        }
+        for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk)
+          umma_ts_if<TF32>(leader, d_tmem, a_tmem + (uint32_t)(kk * 8), dv + (uint64_t)((uint32_t)kk * V_STEP), IDESC_PV,
+                           (first && kk == 0) ? 0u : 1u);
       };
 #pragma unroll
       for (int x = 0; x < NQT; ++x)
-        if (n_tiles[x] && ok) ok = mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 20, x);
+        if (n_tiles[x] && ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 20, x));
       if (ok && n_max > 0) {
-        ok = mbar_wait(bar(BAR_K_FULL + 0), 0, p.status, 21, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_K_FULL + 0), 0, p.status, 21, 0));
         if (ok) {
           tc_fence_after();
 #pragma unroll
           for (int x = 0; x < NQT; ++x) {
-            if (n_tiles[x] > 0) { issue_qk(x, 0); umma_commit(bar(BAR_S_FULL + x)); }
+            if (n_tiles[x] > 0) { issue_qk(x, 0); commit_by_leader(bar(BAR_S_FULL + x)); }
           }
-          umma_commit(bar(BAR_K_EMPTY + 0));
+          commit_by_leader(bar(BAR_K_EMPTY + 0));
         }
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int st = j & 1, st_n = (j + 1) & 1;
         const uint32_t ph = (uint32_t)((j >> 1) & 1), ph_n = (uint32_t)(((j + 1) >> 1) & 1);
-        ok = mbar_wait(bar(BAR_V_FULL + st), ph, p.status, 22, j);
+        TC_TRACE(3, j, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_V_FULL + st), ph, p.status, 22, j));
         if (!ok) break;
+        TC_TRACE(3, j, 1);
         bool k_next_ready = false;
 #pragma unroll
         for (int x = 0; x < NQT; ++x) {
           if (j < n_tiles[x]) {
             TC_TRACE(2, j, x * 4 + 0);
-            ok = mbar_wait(bar(BAR_P_HALF + x), (uint32_t)(j & 1), p.status, 28 + x, j);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_P_HALF + x), (uint32_t)(j & 1), p.status, 28 + x, j));
             if (!ok) break;
             TC_TRACE(2, j, x * 4 + 1);
             tc_fence_after();
             issue_pv(x, st, j == 0, 0);
-            ok = mbar_wait(bar(BAR_P_READY + x), (uint32_t)(j & 1), p.status, 23 + x, j);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_P_READY + x), (uint32_t)(j & 1), p.status, 23 + x, j));
             if (!ok) break;
             TC_TRACE(2, j, x * 4 + 3);
             tc_fence_after();
             issue_pv(x, st, j == 0, 1);
-            umma_commit(bar(BAR_O_DONE + x));
+            TC_TRACE(3, j, 4 + x);
+            commit_by_leader(bar(BAR_O_DONE + x));
           }
-          if (x == NQT - 1) umma_commit(bar(BAR_V_EMPTY + st));
+          if (x == NQT - 1) commit_by_leader(bar(BAR_V_EMPTY + st));
           if (j + 1 < n_tiles[x]) {
             if (!k_next_ready) {
-              ok = mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 25, j);
+              TC_TRACE(3, j, 2);
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 25, j));
               if (!ok) break;
+              TC_TRACE(3, j, 3);
               tc_fence_after();
               k_next_ready = true;
             }
             issue_qk(x, st_n);
-            umma_commit(bar(BAR_S_FULL + x));
+            commit_by_leader(bar(BAR_S_FULL + x));
             TC_TRACE(2, j, x * 4 + 2);
           }
           if (x == NQT - 1 && j + 1 < n_max) {
             if (!k_next_ready) {  // no query tile needs this K tile any more (cannot happen for n_max), keep the ring moving
-              ok = mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 26, j);
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_K_FULL + st_n), ph_n, p.status, 26, j));
               if (!ok) break;
             }
-            umma_commit(bar(BAR_K_EMPTY + st_n));
+            commit_by_leader(bar(BAR_K_EMPTY + st_n));
           }
         }
       }
       // all products issued: wait (bounded) until the tensor pipe is idle before TMEM is freed
-      umma_commit(bar(BAR_DRAIN));
+      commit_by_leader(bar(BAR_DRAIN));
       mbar_wait(bar(BAR_DRAIN), 0, p.status, 27, 0);
+      __syncwarp();
     }
   } else if (warp < WARP_TMA) {
     // ------------------------------------------------------------------ softmax warps
-    const int qtr = warp >> 2;                     // which 32 keys of each tile / which quarter of the O columns
-    const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
-    const int row = lane_base + lane;              // row within the tile
-    constexpr int OC = HD / 4;                     // O columns per thread
+    // Group x = warp / 8 owns query tile x.  A warp covers 16 rows x all 128 keys in the quad
+    // layout (four threads per row, rows r0 and r0 + 8 per thread), so row maxima and sums are
+    // two shuffles and the two groups run independently of each other.
+    const int x = warp >> 3;
+    const int half = (warp >> 2) & 1;
+    const int lane_base = (warp & 3) * 32 + half * 16;  // first of this warp's 16 TMEM lanes
+    const int quad = lane & 3;
+    const int r0 = lane_base + (lane >> 2);             // tile rows r0 and r0 + 8
     const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
-    float* red = reinterpret_cast<float*>(smem_gen + PL::OFF_RED);
-    auto red_at = [&](int parity, int q) { return red + (parity * 4 + q) * 128 + row; };
-    uint32_t red_cnt = 0;                          // exchanges done so far (parity of the BAR_RED phase)
-    float m_used[NQT], l[NQT];
-#pragma unroll
-    for (int x = 0; x < NQT; ++x) { m_used[x] = -INFINITY; l[x] = 0.f; }
-    for (int j = 0; j < n_max && ok; ++j) {
-#pragma unroll
-      for (int x = 0; x < NQT; ++x) {
-        if (j >= n_tiles[x] || !ok) continue;
-        const int qi = q0 + x * BLK + row;
-        const uint32_t t_s = t_row + (uint32_t)(x * BLK + qtr * 32);
-        const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + qtr * OC);
-        TC_TRACE(x, j, 0);
-        ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
-        if (!ok) break;
-        TC_TRACE(x, j, 1);
-        TC_TRACE_W(j, 0);
-        tc_fence_after();
-        uint32_t s[32];
-        tmem_ld32(t_s, s);
-        tmem_wait_ld();
-        TC_TRACE(x, j, 2);
-        const int k0 = j * BLK + qtr * 32;
-        // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
-        if ((p.causal && j * BLK + BLK - 1 > q0 + x * BLK) || (j * BLK + BLK > T)) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kj = k0 + i;
-            if (kj >= T || (p.causal && kj > qi)) s[i] = 0xff800000u;  // -inf
-          }
-        }
-        // maximum of this thread's 32 raw logits, then of the four threads of the row
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          mx4[0] = max3(mx4[0], __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
-          mx4[1] = max3(mx4[1], __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-          mx4[2] = max3(mx4[2], __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-          mx4[3] = max3(mx4[3], __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-        }
-        const int par = (int)(red_cnt & 1u);
-        *red_at(par, qtr) = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        __syncwarp();
-        TC_TRACE_W(j, 1);
-        if (lane == 0) mbar_arrive(bar(BAR_RED));
-        // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
-        // the row sum is taken in fp32.
-        uint32_t pk[16];
-        float rs;
-        auto exp_tile = [&](float neg_m) {
-          float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float p0 = exp2_sel(fmaf(__uint_as_float(s[i + 0]), p.scale_log2, neg_m), i + 0);
-            const float p1 = exp2_sel(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_m), i + 1);
-            const float p2 = exp2_sel(fmaf(__uint_as_float(s[i + 2]), p.scale_log2, neg_m), i + 2);
-            const float p3 = exp2_sel(fmaf(__uint_as_float(s[i + 3]), p.scale_log2, neg_m), i + 3);
-            if constexpr (TF32) {
-              s[i + 0] = __float_as_uint(p0); s[i + 1] = __float_as_uint(p1);
-              s[i + 2] = __float_as_uint(p2); s[i + 3] = __float_as_uint(p3);
-            } else {
-              pk[i / 2] = pack_bf16(p0, p1);
-              pk[i / 2 + 1] = pack_bf16(p2, p3);
-            }
-            rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
-          }
-          rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-        };
-        ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_RED), red_cnt & 1u, p.status, 36, j));
-        if (!ok) break;
-        TC_TRACE_W(j, 2);
-        ++red_cnt;
-        const float mx = fmaxf(fmaxf(*red_at(par, 0), *red_at(par, 1)), fmaxf(*red_at(par, 2), *red_at(par, 3))) * p.scale_log2;
-        float m_new = m_used[x];
-        bool raise = false;
-        if (mx > m_used[x] + RESCALE_THRESHOLD || j == 0) { m_new = fmaxf(mx, m_used[x]); raise = (j > 0); }
-        if (m_new == -INFINITY) m_new = 0.f;  // a row with no visible key yet (rows beyond T)
-        if (__any_sync(0xffffffffu, raise)) {
-          // rescale this thread's quarter of O in TMEM: the previous P V product must have finished
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
-          if (!ok) break;
-          tc_fence_after();
-          const float f = raise ? fast_exp2(m_used[x] - m_new) : 1.0f;
-#pragma unroll
-          for (int c = 0; c < OC / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld16(t_o + c * 16, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st16(t_o + c * 16, o);
-          }
-          l[x] *= f;
-        }
-        exp_tile(-m_new);
-        m_used[x] = m_new;
-        TC_TRACE(x, j, 3);
-        if constexpr (TF32) tmem_st32(t_s, s);
-        else tmem_st16(t_s, pk);
-        l[x] += rs;
-        TC_TRACE(x, j, 4);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar((qtr < 2 ? BAR_P_HALF : BAR_P_READY) + x));
-        TC_TRACE(x, j, 5);
-        TC_TRACE_W(j, 3);
-      }
-    }
-    // epilogue: row sums of the four threads, then O / l -> bf16 -> global
-#pragma unroll
-    for (int x = 0; x < NQT; ++x) {
-      const int n = n_tiles[x];
-      if (!ok || n == 0) continue;
-      const int qi = q0 + x * BLK + row;
-      const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK + qtr * OC);
-      const int par = (int)(red_cnt & 1u);
-      *red_at(par, qtr) = l[x];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_RED));
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_RED), red_cnt & 1u, p.status, 37, x));
+    const uint32_t t_s = t_row + (uint32_t)(x * BLK);
+    const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK);
+    const int n = n_tiles[x];
+    const int qrow0 = q0 + x * BLK;
+    float m_used[2] = {-INFINITY, -INFINITY};
+    float l[2] = {0.f, 0.f};                            // this thread's part of the row sums
+    for (int j = 0; j < n && ok; ++j) {
+      TC_TRACE(x, j, 0);
+      ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
       if (!ok) break;
-      ++red_cnt;
-      const float lsum = (*red_at(par, 0) + *red_at(par, 1)) + (*red_at(par, 2) + *red_at(par, 3));
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
-      if (!ok) break;
+      TC_TRACE(x, j, 1);
+      TC_TRACE_W(j, 0);
       tc_fence_after();
-      const float inv = 1.0f / lsum;
-      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + qtr * OC;
-      float* yrow_f = reinterpret_cast<float*>(p.y) + ((int64_t)bh * T + qi) * HD + qtr * OC;
+      // s[4g + 2h + e] = logit of row r0 + 8h, key 8g + 2*quad + e
+      uint32_t s[64];
+      tmem_ldq256_x8(t_s, s);
+      tmem_ldq256_x8(t_s + 64, s + 32);
+      tmem_wait_ld();
+      TC_TRACE(x, j, 2);
+      // Only the diagonal tile (causal) and the last tile (keys beyond T) need masking.
+      if ((p.causal && j * BLK + BLK - 1 > qrow0) || (j * BLK + BLK > T)) {
 #pragma unroll
-      for (int c = 0; c < OC / 16; ++c) {
-        uint32_t o[16];
-        tmem_ld16(t_o + c * 16, o);
-        tmem_wait_ld();
-        if constexpr (TF32) {
-          if (qi < T) {
-#pragma unroll
-            for (int i = 0; i < 16; i += 4)
-              *reinterpret_cast<float4*>(yrow_f + c * 16 + i) =
-                  make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, __uint_as_float(o[i + 2]) * inv,
-                              __uint_as_float(o[i + 3]) * inv);
-          }
-        } else if (qi < T) {
-#pragma unroll
-          for (int i = 0; i < 16; i += 8) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
-            w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-            w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
-          }
+        for (int i = 0; i < 64; ++i) {
+          const int kj = j * BLK + 8 * (i >> 2) + 2 * quad + (i & 1);
+          const int qi = qrow0 + r0 + 8 * ((i >> 1) & 1);
+          if (kj >= T || (p.causal && kj > qi)) s[i] = 0xff800000u;  // -inf
         }
       }
-      if (qtr == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = m_used[x] + log2f(lsum);
+      float mx[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float ma = -INFINITY, mb = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < 16; g += 2) {
+          ma = max3(ma, __uint_as_float(s[4 * g + 2 * h]), __uint_as_float(s[4 * g + 2 * h + 1]));
+          mb = max3(mb, __uint_as_float(s[4 * g + 4 + 2 * h]), __uint_as_float(s[4 * g + 4 + 2 * h + 1]));
+        }
+        float m = fmaxf(ma, mb);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        mx[h] = m * p.scale_log2;
+      }
+      TC_TRACE_W(j, 1);
+      float m_new[2];
+      bool raise = false;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_new[h] = m_used[h];
+        if (mx[h] > m_used[h] + RESCALE_THRESHOLD || j == 0) { m_new[h] = fmaxf(mx[h], m_used[h]); raise = raise || (j > 0); }
+        if (m_new[h] == -INFINITY) m_new[h] = 0.f;  // a row with no visible key yet (rows beyond T)
+      }
+      if (__any_sync(0xffffffffu, raise)) {
+        // rescale this warp's 16 rows of O in TMEM: the previous P V product must have finished
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((j - 1) & 1), p.status, 32 + x, j));
+        if (!ok) break;
+        tc_fence_after();
+        float f[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          f[h] = (m_new[h] != m_used[h]) ? fast_exp2(m_used[h] - m_new[h]) : 1.0f;
+          l[h] *= f[h];
+        }
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[16];
+          tmem_ldq256_x4(t_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f[(i >> 1) & 1]);
+          tmem_stq256_x4(t_o + c * 32, o);
+        }
+      }
+      TC_TRACE_W(j, 2);
+      // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
+      // the row sum is taken in fp32.  The first 64 keys are handed to the MMA warp before the rest.
+      const float nm[2] = {-m_new[0], -m_new[1]};
+      float rs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+      uint32_t pk[16];
+      // exponentials of key groups [g_lo, g_hi) (8 keys each); bf16 results packed into pk[0..], tf32 in place
+      auto exp_groups = [&](const int g_lo, const int g_hi) {
+#pragma unroll
+        for (int g = g_lo; g < g_hi; ++g) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const float p0 = exp2_sel(fmaf(__uint_as_float(s[4 * g + 2 * h]), p.scale_log2, nm[h]), 2 * g);
+            const float p1 = exp2_sel(fmaf(__uint_as_float(s[4 * g + 2 * h + 1]), p.scale_log2, nm[h]), 2 * g + 1);
+            if constexpr (TF32) {
+              s[4 * g + 2 * h] = __float_as_uint(p0);
+              s[4 * g + 2 * h + 1] = __float_as_uint(p1);
+            } else {
+              pk[2 * (g - g_lo) + h] = pack_bf16(p0, p1);
+            }
+            rs[h][0] += p0;
+            rs[h][1] += p1;
+          }
+        }
+      };
+      // bf16 P: keys 2c, 2c+1 in column c of the S region (64 columns); tf32 P: in place of S.
+      // The store of the first 64 keys completes behind the next exponentials, so its wait is short;
+      // only the last quarter's store latency is exposed before the second product can finish.
+      exp_groups(0, 8);
+      if constexpr (TF32) tmem_stq256_x8(t_s, s);
+      else tmem_stq128_x8(t_s, pk);
+      TC_TRACE(x, j, 3);
+      exp_groups(8, 12);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_HALF + x));
+      if constexpr (TF32) tmem_stq256_x4(t_s + 64, s + 32);
+      else tmem_stq128_x4(t_s + 32, pk);
+      exp_groups(12, 16);
+      if constexpr (TF32) tmem_stq256_x4(t_s + 96, s + 48);
+      else tmem_stq128_x4(t_s + 48, pk);
+      TC_TRACE(x, j, 4);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_READY + x));
+      l[0] += rs[0][0] + rs[0][1];
+      l[1] += rs[1][0] + rs[1][1];
+      m_used[0] = m_new[0];
+      m_used[1] = m_new[1];
+      TC_TRACE(x, j, 5);
+      TC_TRACE_W(j, 3);
+    }
+    // epilogue: finish the row sums, hand them to the thread that owns the row in the one-lane-per-
+    // thread layout, then O / l -> global
+    if (ok && n > 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+      }
+      float* red_l = reinterpret_cast<float*>(smem_gen + PL::OFF_RED) + x * 256;
+      float* red_m = red_l + 128;
+      if (quad == 0) {
+        red_l[r0] = l[0]; red_l[r0 + 8] = l[1];
+        red_m[r0] = m_used[0]; red_m[r0 + 8] = m_used[1];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_RED + x));
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_RED + x), 0, p.status, 36 + x, n));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
+      if (ok) {
+        tc_fence_after();
+        constexpr int OC = HD / 2;                       // O columns per thread: row = lane, half of the head
+        const int row = (warp & 3) * 32 + lane;
+        const int qi = qrow0 + row;
+        const float lsum = red_l[row];
+        const float inv = 1.0f / lsum;
+        const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BLK + x * BLK + half * OC);
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
+        float* yrow_f = reinterpret_cast<float*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
+#pragma unroll
+        for (int c = 0; c < OC / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(t_o32 + c * 16, o);
+          tmem_wait_ld();
+          if constexpr (TF32) {
+            if (qi < T) {
+#pragma unroll
+              for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(yrow_f + c * 16 + i) =
+                    make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, __uint_as_float(o[i + 2]) * inv,
+                                __uint_as_float(o[i + 3]) * inv);
+            }
+          } else if (qi < T) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
+            }
+          }
+        }
+        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum);
+      }
     }
   }
   // ------------------------------------------------------------------ teardown
