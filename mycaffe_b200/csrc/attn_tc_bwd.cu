@@ -151,7 +151,11 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
   } else if (warp == WARP_MMA) {
-    if (lane == 0) {
+    // The warp runs this role in lock step and one elected lane issues, so that addresses and
+    // descriptors are warp-uniform values (fewer instructions per tcgen05.mma for the issuing thread).
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);  // both operands K-major
       constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 0, 1);   // A from TMEM, B = K tile MN-major
       const uint32_t q_addr = smem_base + PL::OFF_RES0, do_addr = smem_base + PL::OFF_RES1;
@@ -160,49 +164,49 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss(tmem_base + C_S, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          umma_ss_if<false>(leader, tmem_u + C_S, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss(tmem_base + C_DP, make_desc(do_addr + off, 16, 1024), make_desc(v_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          umma_ss_if<false>(leader, tmem_u + C_DP, make_desc(do_addr + off, 16, 1024), make_desc(v_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
       };
-      ok = mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 120, 0);
-      if (ok) ok = mbar_wait(bar(DQ_K_FULL + 0), 0, p.status, 121, 0);
-      if (ok) ok = mbar_wait(bar(DQ_V_FULL + 0), 0, p.status, 122, 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 120, 0));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_K_FULL + 0), 0, p.status, 121, 0));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_V_FULL + 0), 0, p.status, 122, 0));
       if (ok) {
         tc_fence_after();
         issue_sdp(0);
-        umma_commit(bar(DQ_SDP_FULL));
-        umma_commit(bar(DQ_V_EMPTY + 0));
+        umma_commit_if(leader, bar(DQ_SDP_FULL));
+        umma_commit_if(leader, bar(DQ_V_EMPTY + 0));
       }
       for (int j = 0; j < n && ok; ++j) {
         const int st = j & 1, st_n = (j + 1) & 1;
         const uint32_t ph_n = (uint32_t)(((j + 1) >> 1) & 1);
         if (j + 1 < n) {
           // next S / dP as soon as the element-wise warps hold the current ones in registers
-          ok = mbar_wait(bar(DQ_SDP_FREE), (uint32_t)(j & 1), p.status, 123, j);
-          if (ok) ok = mbar_wait(bar(DQ_K_FULL + st_n), ph_n, p.status, 124, j);
-          if (ok) ok = mbar_wait(bar(DQ_V_FULL + st_n), ph_n, p.status, 125, j);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_SDP_FREE), (uint32_t)(j & 1), p.status, 123, j));
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_K_FULL + st_n), ph_n, p.status, 124, j));
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_V_FULL + st_n), ph_n, p.status, 125, j));
           if (!ok) break;
           tc_fence_after();
           issue_sdp(st_n);
-          umma_commit(bar(DQ_SDP_FULL));
-          umma_commit(bar(DQ_V_EMPTY + st_n));
+          umma_commit_if(leader, bar(DQ_SDP_FULL));
+          umma_commit_if(leader, bar(DQ_V_EMPTY + st_n));
         }
-        ok = mbar_wait(bar(DQ_DS_READY), (uint32_t)(j & 1), p.status, 126, j);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DS_READY), (uint32_t)(j & 1), p.status, 126, j));
         if (!ok) break;
         tc_fence_after();
         const uint32_t k_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts(tmem_base + C_DQ, tmem_base + C_DS + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ,
+          umma_ts_if<false>(leader, tmem_u + C_DQ, tmem_u + C_DS + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ,
                   (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(DQ_DQ_DONE));
-        umma_commit(bar(DQ_K_EMPTY + st));
+        umma_commit_if(leader, bar(DQ_DQ_DONE));
+        umma_commit_if(leader, bar(DQ_K_EMPTY + st));
       }
-      umma_commit(bar(DQ_DRAIN));
+      umma_commit_if(leader, bar(DQ_DRAIN));
       mbar_wait(bar(DQ_DRAIN), 0, p.status, 127, 0);
     }
   } else {
@@ -356,16 +360,20 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
   } else if (warp == WARP_MMA) {
-    if (lane == 0) {
+    // The warp runs this role in lock step and one elected lane issues, so that addresses and
+    // descriptors are warp-uniform values (fewer instructions per tcgen05.mma for the issuing thread).
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BLK, HD, 0, 1);
       const uint32_t k_addr = smem_base + PL::OFF_RES0, v_addr = smem_base + PL::OFF_RES1;
-      ok = mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0));
       for (int it = 0; it < n && ok; ++it) {
         const int st = it & 1;
         const uint32_t ph = (uint32_t)((it >> 1) & 1);
         const uint32_t q_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, do_addr = q_addr + PL::TILE_BYTES;
-        ok = mbar_wait(bar(KV_Q_FULL + st), ph, p.status, 221, it);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + st), ph, p.status, 221, it));
         if (!ok) break;
         tc_fence_after();
         // S^T = K Q^T and dP^T = V dY^T (rows = keys, columns = queries); they follow the previous
@@ -373,30 +381,30 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss(tmem_base + C_ST, make_desc(k_addr + off, 16, 1024), make_desc(q_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          umma_ss_if<false>(leader, tmem_u + C_ST, make_desc(k_addr + off, 16, 1024), make_desc(q_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss(tmem_base + C_DPT, make_desc(v_addr + off, 16, 1024), make_desc(do_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          umma_ss_if<false>(leader, tmem_u + C_DPT, make_desc(v_addr + off, 16, 1024), make_desc(do_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
-        umma_commit(bar(KV_ST_FULL));
-        ok = mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it);
+        umma_commit_if(leader, bar(KV_ST_FULL));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it));
         if (!ok) break;
         tc_fence_after();
         // dV += P^T dY, dK += dS^T Q: A from TMEM (16 queries = 8 packed columns per step), B MN-major
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
+          umma_ts_if<false>(leader, tmem_u + C_DV, tmem_u + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(do_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
+          umma_ts_if<false>(leader, tmem_u + C_DK, tmem_u + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(q_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(KV_Q_EMPTY + st));
-        umma_commit(bar(KV_ACC_DONE));
+        umma_commit_if(leader, bar(KV_Q_EMPTY + st));
+        umma_commit_if(leader, bar(KV_ACC_DONE));
       }
-      umma_commit(bar(KV_DRAIN));
+      umma_commit_if(leader, bar(KV_DRAIN));
       mbar_wait(bar(KV_DRAIN), 0, p.status, 227, 0);
     }
   } else {
