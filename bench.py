@@ -32,6 +32,8 @@ sys.path.insert(0, str(ROOT))
 
 # workload (BASELINE config 5 / config 3)
 PF_B, PF_H, PF_D, PF_T = 4, 16, 128, 32768
+PREFILL_TRAFFIC_PER_ALGORITHMIC_BYTE = 2180408320 / 2147483648   # measured DRAM bytes / (Q+K+V+O bytes)
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 2152038680 / 2148532224    # measured DRAM bytes / decode_bytes()
 DEC_B, DEC_HEADS, DEC_HS, DEC_SEQ, DEC_LAYERS, DEC_BUFFERS = 64, 32, 128, 4096, 32, 4
 DEC_LMIN, DEC_LMAX = 512, 4096
 
@@ -188,7 +190,11 @@ def run_ours(args):
     roofline = {"bound": "tensor", "kernel": "sdpa_fwd_tc_kernel<128>", "achieved": round(achieved, 2),
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
                 "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4) if peaks.get("bf16_tflops_sustained") else None,
-                "peak_source": peaks["source"], "kernel_ms": round(kern_ms, 4), "traffic": None,
+                "peak_source": peaks["source"], "kernel_ms": round(kern_ms, 4),
+                # dram__bytes_read + dram__bytes_write of one launch of this workload (ncu, `--case prefill-full`):
+                # 2.18 GB at B=4, T=32768 against 2.15 GB of Q, K, V, O; scaled by the bytes of other shapes
+                "traffic": int(PREFILL_TRAFFIC_PER_ALGORITHMIC_BYTE * 4 * q.numel() * 2),
+                "traffic_source": "ncu capture of the full-size launch (profiles/sdpa_fwd_tc_kernel_prefill.md)",
                 "flops_per_launch": flops_launch, "flop_count": "causal 4*B*H*D*T*(T+1)/2"}
 
     # ----------------------------------------------------------------- decode (secondary metric, rank-local heads)
@@ -285,7 +291,10 @@ def run_decode(args, lib, torch, dev, sp, stream, rank, world, barrier, peaks):
             "gpu_launches": steps * DEC_LAYERS * (2 if ns.value > 1 else 1),
             "roofline": {"bound": "hbm", "kernel": "decode_split_kernel<float,128,1>", "achieved": round(gbs, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
-                         "peak_source": peaks["source"], "bytes_per_launch": bytes_layer, "traffic": None}}
+                         "peak_source": peaks["source"], "bytes_per_launch": bytes_layer,
+                         # ncu on the 16-sequence case reads 1.0016 x the algorithmic bytes; traffic grows with the keys read
+                         "traffic": int(DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_layer),
+                         "traffic_source": "ncu capture of `--case decode-small`, scaled by bytes (profiles/decode_split_kernel.md)"}}
 
 
 def run_e2e(args, torch, dev, local, rank, world, barrier, B, H, Hl, T, D, q, k, v):
@@ -467,23 +476,68 @@ def run_reference(args):
 
 
 def run_profile_case(case):
-    """Small stand-alone cases for `ncu --set full` captures (a few launches, inputs above L2 where
-    DRAM matters): `prefill-small` = config-5 shape at T = 8192, B = 1; `decode-small` = config-3 shape,
-    16 sequences of 4096 keys."""
+    """Small stand-alone cases for `ncu` captures (a few launches, inputs above L2 where DRAM matters):
+    `prefill-small` = config-5 shape at T = 8192, B = 1; `prefill-full` = the bench workload itself, two
+    launches (single-pass metrics only); `bwd-small` = bf16 backward at the prefill-small shape;
+    `decode-small` = config-3 shape, 16 sequences of 4096 keys; `gemv-small` = the decode projections at
+    dim 4096 for 1 and 8 sequences (also prints their CUDA-event bandwidth)."""
     import torch
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
     dev = torch.device("cuda", 0)
-    if case == "prefill-small":
-        B, H, T, D = 1, PF_H, 8192, PF_D
+    if case == "gemv-small":
+        dim = DEC_HEADS * DEC_HS
+        ws = [torch.randn(dim, dim, device=dev) * 0.02 for _ in range(4)]   # wq, wk, wv, wo: 67 MB each
+        rms = torch.ones(dim, device=dev)
+        res = {"case": case}
+        for Bn in (1, 8):
+            x = torch.randn(Bn, dim, device=dev)
+            qo, ko, vo = (torch.empty(Bn, dim, device=dev) for _ in range(3))
+            def qkv():
+                return lib.mca_decode_qkv_rmsnorm(x.data_ptr(), rms.data_ptr(), 1e-5, ws[0].data_ptr(), ws[1].data_ptr(),
+                                                  ws[2].data_ptr(), 0, Bn, dim, dim, qo.data_ptr(), ko.data_ptr(), vo.data_ptr(), None)
+            def outp():
+                return lib.mca_decode_out_proj(qo.data_ptr(), ws[3].data_ptr(), 0, Bn, dim, x.data_ptr(), None)
+            for name, fn, nbytes in (("qkv", qkv, 3 * dim * dim * 4), ("out", outp, dim * dim * 4)):
+                for _ in range(3):
+                    rc = fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(20):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / 20
+                res[f"{name}_B{Bn}"] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+        print(json.dumps(res))
+        return
+    if case in ("prefill-small", "prefill-full", "bwd-small"):
+        B, H, T, D = (PF_B, PF_H, PF_T, PF_D) if case == "prefill-full" else (1, PF_H, 8192, PF_D)
+        if case == "bwd-small":
+            q, k, v, dy = (torch.randn(B, H, T, D, device=dev).div_(D ** 0.25).bfloat16() for _ in range(4))
+            y, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+            lse, delta = torch.empty(B, H, T, device=dev), torch.empty(B, H, T, device=dev)
+            st = torch.zeros(8, dtype=torch.int32, device=dev)
+            lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D, y.data_ptr(),
+                                    lse.data_ptr(), st.data_ptr(), None)
+            for _ in range(2):
+                rc = lib.mca_sdpa_backward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                              lse.data_ptr(), delta.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
+                                              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), st.data_ptr(), None)
+            torch.cuda.synchronize()
+            print(json.dumps({"case": case, "rc": rc, "status": st[:4].tolist(),
+                              "useful_flops": 2.5 * causal_flops(B, H, T, D)}))
+            return
         q, k, v = (torch.randn(B, H, T, D, device=dev).div_(D ** 0.5).bfloat16() for _ in range(3))
         y = torch.empty_like(q)
         st = torch.zeros(8, dtype=torch.int32, device=dev)
-        for _ in range(3):
+        for _ in range(2 if case == "prefill-full" else 3):
             rc = lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
                                          y.data_ptr(), None, st.data_ptr(), None)
         torch.cuda.synchronize()
-        print(json.dumps({"case": case, "rc": rc, "status": st[:4].tolist(), "causal_flops": causal_flops(B, H, T, D)}))
+        print(json.dumps({"case": case, "rc": rc, "status": st[:4].tolist(), "causal_flops": causal_flops(B, H, T, D),
+                          "algorithmic_bytes": 4 * q.numel() * 2}))
     else:
         Bd, nh, hs, S = 16, DEC_HEADS, DEC_HS, DEC_SEQ
         kv = nh * hs
@@ -513,7 +567,7 @@ def main():
     ap.add_argument("--batch", type=int, default=PF_B)
     ap.add_argument("--seq-len", type=int, default=PF_T)
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "decode-small"],
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
     if args.case:
