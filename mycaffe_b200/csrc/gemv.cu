@@ -12,29 +12,31 @@
 // nothing else matters, so the kernel is bound by HBM bandwidth.  Every CTA first builds the
 // normalised activation in shared memory (it is 16 KB per sequence and comes from L2), then
 // its warps walk their rows of the stacked [Wq; Wk; Wv] matrix with 128-bit loads, 512
-// contiguous bytes per warp instruction, and reduce with shuffles.  Up to 8 sequences share one
-// pass over the weights; larger batches take several passes.
+// contiguous bytes per warp instruction, and reduce with shuffles.  Every warp owns the same number
+// of consecutive rows and requests its first weight vectors before the activations are staged, so
+// HBM is busy from the first cycle.  Up to 8 sequences share one pass over the weights (then two
+// rows at a time per warp share the activation reads); larger batches take several passes.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace {
 
-constexpr int GV_THREADS = 256;
-constexpr int GV_WARPS = GV_THREADS / 32;
 constexpr int GV_BMAX = 8;   // sequences per pass over the weights
 
 template <typename WT> struct WLoad;
 template <> struct WLoad<float> {
   static constexpr int VEC = 4;
-  static __device__ __forceinline__ void load(const float* p, float (&w)[4]) {
-    const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
-    w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
-  }
+  using Raw = float4;
+  static __device__ __forceinline__ Raw raw(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ void unpack(const Raw& t, float (&w)[4]) { w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w; }
 };
 template <> struct WLoad<__nv_bfloat16> {
   static constexpr int VEC = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&w)[8]) {
-    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw raw(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ void unpack(const Raw& t, float (&w)[8]) {
     const uint32_t u[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) { w[2 * i] = __uint_as_float(u[i] << 16); w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
@@ -48,20 +50,50 @@ struct GemvParams {
   float* out[3];         // (B, rows[i]) each
   int rows[3];
   int n_mats, B, n, accumulate;  // accumulate: out += result (residual connection)
+  int rows_per_warp;             // consecutive rows owned by one warp (a multiple of R)
   float eps;
 };
 
-template <typename WT, int NB>
-__global__ void __launch_bounds__(GV_THREADS) gemv_fused_kernel(const GemvParams p, int b0) {
+// NB sequences per pass, R rows at a time per warp (they share the activation reads from shared
+// memory), THREADS per CTA.  A warp owns rows_per_warp consecutive rows of the stacked matrix, so
+// that all warps of the grid have the same amount of weight bytes to stream.
+template <typename WT, int NB, int R, int THREADS>
+__global__ void __launch_bounds__(THREADS) gemv_fused_kernel(const GemvParams p, int b0) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int VEC = WLoad<WT>::VEC;
+  constexpr int PRE = NB <= 2 ? 8 : 2;         // weight vectors per row requested before the activations are staged
   extern __shared__ __align__(16) float xs[];  // [NB][n] normalised activations
-  __shared__ float red[GV_WARPS][NB];
+  __shared__ float red[WARPS][NB];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = p.n;
+  const int total_rows = p.rows[0] + (p.n_mats > 1 ? p.rows[1] : 0) + (p.n_mats > 2 ? p.rows[2] : 0);
+  const int row_lo = (blockIdx.x * WARPS + warp) * p.rows_per_warp;
+  const int row_hi = min(row_lo + p.rows_per_warp, total_rows);
+  auto row_ptr = [&](int r, int& m, int& rr) -> const WT* {
+    m = 0; rr = r;
+    if (rr >= p.rows[0]) { rr -= p.rows[0]; m = 1; if (rr >= p.rows[1]) { rr -= p.rows[1]; m = 2; } }
+    const void* base = m == 0 ? p.w[0] : (m == 1 ? p.w[1] : p.w[2]);  // no dynamic indexing of the parameter block
+    return reinterpret_cast<const WT*>(base) + (int64_t)rr * n;
+  };
+  // ---- the first weight vectors of this warp's first rows leave for HBM before anything else
+  typename WLoad<WT>::Raw pre[R][PRE];
+  {
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      int m, rr;
+      const WT* wrow = row_ptr(min(row_lo + q, total_rows - 1), m, rr);
+#pragma unroll
+      for (int u = 0; u < PRE; ++u) {
+        const int k = (lane + 32 * u) * VEC;
+        pre[q][u] = WLoad<WT>::raw(wrow + (k < n ? k : 0));
+      }
+    }
+  }
   // ---- phase 1: activations of this pass's sequences -> shared memory, RMS-normalised
   float ss[NB];
 #pragma unroll
   for (int b = 0; b < NB; ++b) ss[b] = 0.f;
-  for (int k = tid * 4; k < n; k += GV_THREADS * 4) {
+  for (int k = tid * 4; k < n; k += THREADS * 4) {
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
       const float4 v = *reinterpret_cast<const float4*>(p.x + (int64_t)(b0 + b) * n + k);
@@ -82,11 +114,11 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_fused_kernel(const GemvParams
     for (int b = 0; b < NB; ++b) {
       float t = 0.f;
 #pragma unroll
-      for (int w = 0; w < GV_WARPS; ++w) t += red[w][b];
+      for (int w = 0; w < WARPS; ++w) t += red[w][b];
       t = t / (float)n + p.eps;
       scale[b] = 1.0f / sqrtf(t);
     }
-    for (int k = tid * 4; k < n; k += GV_THREADS * 4) {
+    for (int k = tid * 4; k < n; k += THREADS * 4) {
       const float4 g = *reinterpret_cast<const float4*>(p.norm_w + k);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
@@ -97,67 +129,107 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_fused_kernel(const GemvParams
     }
   }
   __syncthreads();
-  // ---- phase 2: rows of the stacked matrices, one row per warp at a time
-  const int total_rows = p.rows[0] + (p.n_mats > 1 ? p.rows[1] : 0) + (p.n_mats > 2 ? p.rows[2] : 0);
-  constexpr int VEC = WLoad<WT>::VEC;
-  for (int r = blockIdx.x * GV_WARPS + warp; r < total_rows; r += gridDim.x * GV_WARPS) {
-    int m = 0, rr = r;
-    if (rr >= p.rows[0]) { rr -= p.rows[0]; m = 1; if (rr >= p.rows[1]) { rr -= p.rows[1]; m = 2; } }
-    const WT* wrow = reinterpret_cast<const WT*>(p.w[m]) + (int64_t)rr * n;
-    float acc[NB];
+  // ---- phase 2: this warp's rows, R at a time
+  for (int r = row_lo; r < row_hi; r += R) {
+    const WT* wrow[R];
+    int mat[R], rin[R];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) acc[b] = 0.f;
-#pragma unroll(NB <= 2 ? 8 : 4)
-    for (int k = lane * VEC; k < n; k += 32 * VEC) {
+    for (int q = 0; q < R; ++q) wrow[q] = row_ptr(min(r + q, total_rows - 1), mat[q], rin[q]);
+    float acc[R][NB];
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) acc[q][b] = 0.f;
+    auto fma_vec = [&](const typename WLoad<WT>::Raw& raw, int q, int k) {
       float w[VEC];
-      WLoad<WT>::load(wrow + k, w);
+      WLoad<WT>::unpack(raw, w);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         const float* xv = xs + b * n + k;
 #pragma unroll
         for (int i = 0; i < VEC; i += 4) {
           const float4 t = *reinterpret_cast<const float4*>(xv + i);
-          acc[b] = fmaf(w[i], t.x, acc[b]); acc[b] = fmaf(w[i + 1], t.y, acc[b]);
-          acc[b] = fmaf(w[i + 2], t.z, acc[b]); acc[b] = fmaf(w[i + 3], t.w, acc[b]);
+          acc[q][b] = fmaf(w[i], t.x, acc[q][b]); acc[q][b] = fmaf(w[i + 1], t.y, acc[q][b]);
+          acc[q][b] = fmaf(w[i + 2], t.z, acc[q][b]); acc[q][b] = fmaf(w[i + 3], t.w, acc[q][b]);
         }
       }
+    };
+    int k_start = lane * VEC;
+    if (r == row_lo) {  // the vectors requested before phase 1
+#pragma unroll
+      for (int u = 0; u < PRE; ++u) {
+        const int k = (lane + 32 * u) * VEC;
+        if (k < n) {
+#pragma unroll
+          for (int q = 0; q < R; ++q) fma_vec(pre[q][u], q, k);
+        }
+      }
+      k_start = (lane + 32 * PRE) * VEC;
+    }
+#pragma unroll(NB <= 2 ? 8 : 2)
+    for (int k = k_start; k < n; k += 32 * VEC) {
+      typename WLoad<WT>::Raw raw[R];
+#pragma unroll
+      for (int q = 0; q < R; ++q) raw[q] = WLoad<WT>::raw(wrow[q] + k);
+#pragma unroll
+      for (int q = 0; q < R; ++q) fma_vec(raw[q], q, k);
     }
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], o);
-    }
-    if (lane == 0) {
+    for (int q = 0; q < R; ++q)
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        float* dst = p.out[m] + (int64_t)(b0 + b) * p.rows[m] + rr;
-        *dst = p.accumulate ? (*dst + acc[b]) : acc[b];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[q][b] += __shfl_xor_sync(0xffffffffu, acc[q][b], o);
+      }
+    if (lane == 0) {
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        if (r + q >= row_hi) continue;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          float* ob = mat[q] == 0 ? p.out[0] : (mat[q] == 1 ? p.out[1] : p.out[2]);
+          const int orows = mat[q] == 0 ? p.rows[0] : (mat[q] == 1 ? p.rows[1] : p.rows[2]);
+          float* dst = ob + (int64_t)(b0 + b) * orows + rin[q];
+          *dst = p.accumulate ? (*dst + acc[q][b]) : acc[q][b];
+        }
       }
     }
   }
 }
 
-template <typename WT, int NB>
-int launch_pass(const GemvParams& p, int b0, cudaStream_t st) {
+template <typename WT, int NB, int R, int THREADS>
+int launch_pass(GemvParams p, int b0, cudaStream_t st) {
+  constexpr int WARPS = THREADS / 32;
   const size_t smem = sizeof(float) * (size_t)NB * p.n;
   if (smem > 200 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(gemv_fused_kernel<WT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(gemv_fused_kernel<WT, NB, R, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int total_rows = p.rows[0] + (p.n_mats > 1 ? p.rows[1] : 0) + (p.n_mats > 2 ? p.rows[2] : 0);
-  int grid = 148 * (smem > 100 * 1024 ? 1 : smem > 40 * 1024 ? 2 : 4);
-  if (grid * GV_WARPS > total_rows) grid = mca_ceil_div(total_rows, GV_WARPS);
-  gemv_fused_kernel<WT, NB><<<grid, GV_THREADS, smem, st>>>(p, b0);
+  // as many warps as fit on the 148 SMs at once, every one of them with the same number of rows
+  int ctas_per_sm = 1, dev = 0, sms = 148;
+  MCA_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_fused_kernel<WT, NB, R, THREADS>, THREADS, smem));
+  MCA_CUDA_TRY(cudaGetDevice(&dev));
+  MCA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int max_warps = sms * std::max(1, ctas_per_sm) * WARPS;
+  int rpw = mca_ceil_div(total_rows, max_warps);
+  rpw = mca_ceil_div(rpw, R) * R;
+  p.rows_per_warp = rpw;
+  const int grid = mca_ceil_div(total_rows, rpw * WARPS);
+  gemv_fused_kernel<WT, NB, R, THREADS><<<grid, THREADS, smem, st>>>(p, b0);
   return mca_launch_status();
 }
 
 template <typename WT>
 int run_gemv(const GemvParams& p, cudaStream_t st) {
   int e = 0;
+  // two rows at a time need the stacked matrices to start on even rows
+  const bool even = (p.rows[0] % 2 == 0) && (p.rows[1] % 2 == 0);
   for (int b0 = 0; b0 < p.B && !e;) {
     const int left = p.B - b0;
-    if (left >= 8 && (size_t)8 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 8>(p, b0, st); b0 += 8; }
-    else if (left >= 4) { e = launch_pass<WT, 4>(p, b0, st); b0 += 4; }
-    else if (left >= 2) { e = launch_pass<WT, 2>(p, b0, st); b0 += 2; }
-    else { e = launch_pass<WT, 1>(p, b0, st); b0 += 1; }
+    if (left >= 8 && even && (size_t)8 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 8, 2, 512>(p, b0, st); b0 += 8; }
+    else if (left >= 4 && even && (size_t)4 * p.n * 4 <= 100 * 1024) { e = launch_pass<WT, 4, 2, 512>(p, b0, st); b0 += 4; }
+    else if (left >= 4) { e = launch_pass<WT, 4, 1, 256>(p, b0, st); b0 += 4; }
+    else if (left >= 2) { e = launch_pass<WT, 2, 1, 256>(p, b0, st); b0 += 2; }
+    else { e = launch_pass<WT, 1, 1, 256>(p, b0, st); b0 += 1; }
   }
   return e;
 }
