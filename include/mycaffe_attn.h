@@ -67,6 +67,8 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_ALLOCMEM_BF16 2001  /* longs {count} -> handle to bf16 storage; SETMEM/GETMEM convert from/to float */
 #define MCA_FN_CONVERT 2002        /* longs {hSrc,hDst,count}: copy with float<->bf16 conversion as the handles require */
 #define MCA_FN_ATTN_FWD_HOST 2003  /* longs {pQ,pK,pV,pY (host addresses),hostDtype,causal,B,H,T,D[,headsPerChunk]}: mca_sdpa_forward_host */
+#define MCA_FN_ATTN_FWD_PACKED 2004  /* longs {hCuDnn,hAttn,T,hQKV,hMask,hY,bBatchMask}: ATTN_FWD reading q,k,v from the (B,T,3C) c_attn output, y as (B,T,C) */
+#define MCA_FN_ATTN_BWD_PACKED 2005  /* longs {hCuDnn,hAttn,hQKV,hdQKV,hMask,hY,hdY}: its backward; dQKV (B,T,3C) from dY (B,T,C) */
 #define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode */
 #define MCA_FN_DECODE_FREE 2011    /* floats {hDecode} */
 #define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
@@ -88,6 +90,13 @@ typedef char* MCA_LPTSTR;
 #define MCA_MASK_MODE_TT 1      /* (T,T) floats, masked where 0 */
 #define MCA_MASK_MODE_BATCH 2   /* (B,T) floats key mask, masked where 0 */
 #define MCA_MASK_MODE_CAUSAL 3  /* analytic lower triangle, mask pointer unused */
+
+/* tensor layout of the *_layout entry points */
+#define MCA_LAYOUT_BHTD 0    /* q, k, v, y: separate contiguous (B,H,T,D) tensors (what attn.cu:535-556 expects) */
+#define MCA_LAYOUT_PACKED 1  /* q, k, v: the three feature thirds of one (B,T,3*H*D) tensor (pass base, base + H*D,
+                                base + 2*H*D); y, dy: (B,T,H*D).  The form the c_attn output has before
+                                CausalSelfAttentionLayer splits and transposes it (CausalSelfAttentionLayer.cs:537-557)
+                                and the form c_proj consumes (:604): no channel_copy, no head transposes */
 
 /* handle types of Internal_GetPointer* (Cuda Files/memory.h HANDLE_TYPE) */
 #define MCA_HT_MEMORY 1
@@ -136,6 +145,20 @@ MCA_API int mca_sdpa_backward_f32(const float* q, const float* k, const float* v
                                   const float* y_saved, const float* mask, int mask_mode, const int* causal_flag,
                                   const float* row_max, const float* row_sum, float* delta_scratch, int B, int H,
                                   int T, int D, float* dq, float* dk, float* dv, void* stream);
+/* The same two with a tensor layout (MCA_LAYOUT_*): with MCA_LAYOUT_PACKED the kernels read q, k, v
+ * straight out of the (B,T,3C) projection output and write y as (B,T,C); in the backward dy is
+ * (B,T,C) and dq, dk, dv are the thirds of a (B,T,3C) gradient.  Replaces, besides attn.cu:518-661,
+ * the three channel_copy calls and four head transposes either side of it
+ * (CausalSelfAttentionLayer.cs:537-557,604,666,719-737).  y_copy, y_saved and the row statistics
+ * stay (B,H,T,*) contiguous (they belong to the handle). */
+MCA_API int mca_sdpa_forward_f32_layout(const float* q, const float* k, const float* v, const float* mask,
+                                        int mask_mode, const int* causal_flag, int B, int H, int T, int D, float* y,
+                                        float* row_max, float* row_sum, float* y_copy, int layout, void* stream);
+MCA_API int mca_sdpa_backward_f32_layout(const float* q, const float* k, const float* v, const float* dy,
+                                         const float* y_saved, const float* mask, int mask_mode,
+                                         const int* causal_flag, const float* row_max, const float* row_sum,
+                                         float* delta_scratch, int B, int H, int T, int D, float* dq, float* dk,
+                                         float* dv, int layout, void* stream);
 /* Writes 1 to *flag iff mask (T,T) equals the lower-triangular ones built by fillMask,
  * MyCaffe.layers.gpt/layers.gpt/CausalSelfAttentionLayer.cs:276-291; else 0. */
 MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* stream);
@@ -170,6 +193,16 @@ MCA_API int mca_sdpa_forward_host(const void* q, const void* k, const void* v, v
 MCA_API int mca_host_pipeline_chunk(int B, int H, int T, int heads_per_chunk);
 /* Free the pipeline's device staging buffers on the current device. */
 MCA_API int mca_host_pipeline_release(void);
+
+/* The tensor-core pair with a tensor layout (MCA_LAYOUT_*), as mca_sdpa_forward_f32_layout: the 4-D
+ * tensor maps read q, k, v out of the (B,T,3C) projection output; y, dy are (B,T,C); dq, dk, dv are
+ * the thirds of a (B,T,3C) gradient.  `y` of the backward has the layout the forward wrote it in. */
+MCA_API int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
+                                       int T, int D, void* y, float* lse, int* status, int layout, void* stream);
+MCA_API int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, const void* y, const void* dy,
+                                        const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
+                                        int T, int D, void* dq, void* dk, void* dv, int* status, int layout,
+                                        void* stream);
 
 /* RoPE on a (B,T,H,D) tensor.  Replaces RopeDataGpu<T>::Forward/Backward, Cuda Files/rope.cu:784-864.
  * Tables are (T,D/2) as built by mca_rope_tables_host. */

@@ -30,6 +30,12 @@ SIGNATURES = {
     "Internal_AllocHostFloat": (LONG, [LONG, LONG, C.POINTER(_fp), _fp, C.c_bool]),
     "mca_sdpa_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mca_sdpa_backward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "mca_sdpa_forward_f32_layout": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
+    "mca_sdpa_backward_f32_layout": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp,
+                                          _i, _vp]),
+    "mca_sdpa_forward_tc_layout": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "mca_sdpa_backward_tc_layout": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i,
+                                         _vp]),
     "mca_classify_causal_mask": (_i, [_vp, _i, _vp, _vp]),
     "mca_sdpa_forward_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_sdpa_backward_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

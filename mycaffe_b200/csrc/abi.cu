@@ -35,7 +35,7 @@ struct AttnHandle {
   int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
   // state of the last forward, consumed by backward
   bool have_fwd = false;
-  int fwd_T = 0, fwd_mask_mode = 0;
+  int fwd_T = 0, fwd_mask_mode = 0, fwd_layout = 0;
   const float* fwd_mask = nullptr;
   // mask classification cache
   const float* cls_mask = nullptr;
@@ -382,7 +382,8 @@ long tc_status(Kernel* k, AttnHandle& a) {
   return 0;
 }
 
-long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+// layout MCA_LAYOUT_PACKED: pl[3..5] all name the (B,T,3C) projection output and pl[7] a (B,T,C) tensor
+long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   long e;  // Device<T>::AttnForward, device.h:2488-2506; attnHandle<T>::Forward, attn.cu:518-602
   if ((e = verify_in(llInput, pl, 9, 9))) return e;
   auto it = k->attn.find((long)pl[1]);
@@ -393,20 +394,24 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   if (T <= 0) return ERROR_PARAM_OUT_OF_RANGE;
   if (a.training && a.dropout > 0.f) return ERROR_ATTN + 3;  // the reference's guard always fails here (attn.cu:265)
   const int64_t n = (int64_t)a.B * a.H * T * a.D;
+  const bool packed = layout == MCA_LAYOUT_PACKED;
+  const int64_t n_in = packed ? 3 * n : n;               // elements the q / k / v handles must hold
+  const int64_t C = (int64_t)a.H * a.D;                  // k and v start C and 2C elements into a packed row
   const bool batch_mask = pl[8] != 0;
   const float* mask = nullptr;
   int mode = 0;
   a.have_fwd = false;
   if (a.dtype == MCA_DTYPE_F32) {
     float *q, *kk, *v, *y;
-    if ((e = check_f32(k, (long)pl[3], n, &q)) || (e = check_f32(k, (long)pl[4], n, &kk)) ||
-        (e = check_f32(k, (long)pl[5], n, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
+    if ((e = check_f32(k, (long)pl[3], n_in, &q)) || (e = check_f32(k, (long)pl[4], n_in, &kk)) ||
+        (e = check_f32(k, (long)pl[5], n_in, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
       return e;
+    if (packed) { kk += C; v += 2 * C; }
     if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, false))) return e;
     const bool save = a.training && T == a.block;
-    e = mca_sdpa_forward_f32(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
-                             save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, 0);
-    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; }
+    e = mca_sdpa_forward_f32_layout(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
+                                    save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, layout, 0);
+    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; a.fwd_layout = layout; }
     return e;
   }
   // tensor-core variants: causal or absent mask only
@@ -416,30 +421,39 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   const bool tf32_exact = a.dtype == MCA_DTYPE_TF32 && (a.training || a.D != 64);
   const bool bf16 = a.dtype == MCA_DTYPE_BF16;
   void *q, *kk, *v, *y;
-  if ((e = check_any(k, (long)pl[3], n, bf16, &q)) || (e = check_any(k, (long)pl[4], n, bf16, &kk)) ||
-      (e = check_any(k, (long)pl[5], n, bf16, &v)) || (e = check_any(k, (long)pl[7], n, bf16, &y)))
+  if ((e = check_any(k, (long)pl[3], n_in, bf16, &q)) || (e = check_any(k, (long)pl[4], n_in, bf16, &kk)) ||
+      (e = check_any(k, (long)pl[5], n_in, bf16, &v)) || (e = check_any(k, (long)pl[7], n, bf16, &y)))
     return e;
+  if (packed) {
+    const size_t esz = bf16 ? 2 : 4;
+    kk = static_cast<char*>(kk) + C * esz;
+    v = static_cast<char*>(v) + 2 * C * esz;
+  }
   if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH || tf32_exact) {
     if (bf16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
     // a general mask (or training) with tf32 requested: the exact fp32 kernel handles it
     const bool save = a.training && T == a.block;
-    e = mca_sdpa_forward_f32((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, (float*)y,
-                             save ? a.row_max : nullptr, save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, 0);
-    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; }
+    e = mca_sdpa_forward_f32_layout((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
+                                    (float*)y, save ? a.row_max : nullptr, save ? a.row_sum : nullptr,
+                                    save ? a.y_copy : nullptr, layout, 0);
+    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; a.fwd_layout = layout; }
     return e;
   }
-  e = mca_sdpa_forward_tc(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, 0);
+  e = mca_sdpa_forward_tc_layout(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1,
+                                 layout, 0);
   if (e) return e;
   if (a.training && T == a.block && bf16) {
-    // Backward needs O and the log-sum-exp of this Forward; it cannot trust the data of hY
+    // Backward needs O and the log-sum-exp of this Forward; it cannot trust the data of hY.  The copy keeps
+    // the layout y was written in.
     cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
     if (ce != cudaSuccess) return ce;
-    a.have_fwd = true; a.fwd_T = T; a.fwd_mask = nullptr; a.fwd_mask_mode = mode;
+    a.have_fwd = true; a.fwd_T = T; a.fwd_mask = nullptr; a.fwd_mask_mode = mode; a.fwd_layout = layout;
   }
   return tc_status(k, a);
 }
 
-long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
+// layout MCA_LAYOUT_PACKED: pl[2,4,6] name the (B,T,3C) projection output, pl[3,5,7] its gradient, pl[10] a (B,T,C) gradient
+long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   long e;  // Device<T>::AttnBackward, device.h:2508-2529; attnHandle<T>::Backward, attn.cu:608-661
   if ((e = verify_in(llInput, pl, 11, 11))) return e;
   auto it = k->attn.find((long)pl[1]);
@@ -447,29 +461,38 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   AttnHandle& a = it->second;
   // The reference's Backward always works at the configured block size on the tensors its
   // Forward left in the handle (attn.cu:622-634); it reads neither hMask nor the data of hY.
-  if (!a.have_fwd || a.fwd_T != a.block) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;
+  if (!a.have_fwd || a.fwd_T != a.block || a.fwd_layout != layout) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;
   const int T = a.block;
   const int64_t n = (int64_t)a.B * a.H * T * a.D;
+  const bool packed = layout == MCA_LAYOUT_PACKED;
+  const int64_t n_in = packed ? 3 * n : n;
+  const int64_t C = (int64_t)a.H * a.D;
   if (a.dtype == MCA_DTYPE_BF16) {
     void *q, *dq, *kk, *dk, *v, *dv, *dy;
-    if ((e = check_any(k, (long)pl[2], n, true, &q)) || (e = check_any(k, (long)pl[3], n, true, &dq)) ||
-        (e = check_any(k, (long)pl[4], n, true, &kk)) || (e = check_any(k, (long)pl[5], n, true, &dk)) ||
-        (e = check_any(k, (long)pl[6], n, true, &v)) || (e = check_any(k, (long)pl[7], n, true, &dv)) ||
+    if ((e = check_any(k, (long)pl[2], n_in, true, &q)) || (e = check_any(k, (long)pl[3], n_in, true, &dq)) ||
+        (e = check_any(k, (long)pl[4], n_in, true, &kk)) || (e = check_any(k, (long)pl[5], n_in, true, &dk)) ||
+        (e = check_any(k, (long)pl[6], n_in, true, &v)) || (e = check_any(k, (long)pl[7], n_in, true, &dv)) ||
         (e = check_any(k, (long)pl[10], n, true, &dy)))
       return e;
-    e = mca_sdpa_backward_tc(q, kk, v, a.y_copy, dy, a.lse, a.delta, MCA_DTYPE_BF16, a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B,
-                             a.H, T, a.D, dq, dk, dv, a.causal_flag + 1, 0);
+    if (packed) {
+      kk = static_cast<char*>(kk) + C * 2; dk = static_cast<char*>(dk) + C * 2;
+      v = static_cast<char*>(v) + 2 * C * 2; dv = static_cast<char*>(dv) + 2 * C * 2;
+    }
+    e = mca_sdpa_backward_tc_layout(q, kk, v, a.y_copy, dy, a.lse, a.delta, MCA_DTYPE_BF16,
+                                    a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, dq, dk, dv, a.causal_flag + 1,
+                                    layout, 0);
     if (e) return e;
     return tc_status(k, a);
   }
   float *q, *dq, *kk, *dk, *v, *dv, *dy;
-  if ((e = check_f32(k, (long)pl[2], n, &q)) || (e = check_f32(k, (long)pl[3], n, &dq)) ||
-      (e = check_f32(k, (long)pl[4], n, &kk)) || (e = check_f32(k, (long)pl[5], n, &dk)) ||
-      (e = check_f32(k, (long)pl[6], n, &v)) || (e = check_f32(k, (long)pl[7], n, &dv)) ||
+  if ((e = check_f32(k, (long)pl[2], n_in, &q)) || (e = check_f32(k, (long)pl[3], n_in, &dq)) ||
+      (e = check_f32(k, (long)pl[4], n_in, &kk)) || (e = check_f32(k, (long)pl[5], n_in, &dk)) ||
+      (e = check_f32(k, (long)pl[6], n_in, &v)) || (e = check_f32(k, (long)pl[7], n_in, &dv)) ||
       (e = check_f32(k, (long)pl[10], n, &dy)))
     return e;
-  return mca_sdpa_backward_f32(q, kk, v, dy, a.y_copy, a.fwd_mask, a.fwd_mask_mode, a.causal_flag, a.row_max, a.row_sum,
-                               a.delta, a.B, a.H, T, a.D, dq, dk, dv, 0);
+  if (packed) { kk += C; dk += C; v += 2 * C; dv += 2 * C; }
+  return mca_sdpa_backward_f32_layout(q, kk, v, dy, a.y_copy, a.fwd_mask, a.fwd_mask_mode, a.causal_flag, a.row_max,
+                                      a.row_sum, a.delta, a.B, a.H, T, a.D, dq, dk, dv, layout, 0);
 }
 
 // ---- rope ids ------------------------------------------------------------------------------
@@ -753,8 +776,18 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
       return 0;
     }
     case CUDNN_FN_ATTN_SET: return finish(k, attn_set(k, lInput, pf, llInput, pl));
-    case CUDNN_FN_ATTN_FWD: return finish(k, attn_fwd(k, llInput, pl));
-    case CUDNN_FN_ATTN_BWD: return finish(k, attn_bwd(k, llInput, pl));
+    case CUDNN_FN_ATTN_FWD: return finish(k, attn_fwd(k, llInput, pl, MCA_LAYOUT_BHTD));
+    case CUDNN_FN_ATTN_BWD: return finish(k, attn_bwd(k, llInput, pl, MCA_LAYOUT_BHTD));
+    case MCA_FN_ATTN_FWD_PACKED: {
+      if ((e = verify_in(llInput, pl, 7, 7))) return e;
+      MCA_LONGLONG a9[9] = {pl[0], pl[1], pl[2], pl[3], pl[3], pl[3], pl[4], pl[5], pl[6]};
+      return finish(k, attn_fwd(k, 9, a9, MCA_LAYOUT_PACKED));
+    }
+    case MCA_FN_ATTN_BWD_PACKED: {
+      if ((e = verify_in(llInput, pl, 7, 7))) return e;
+      MCA_LONGLONG a11[11] = {pl[0], pl[1], pl[2], pl[3], pl[2], pl[3], pl[2], pl[3], pl[4], pl[5], pl[6]};
+      return finish(k, attn_bwd(k, 11, a11, MCA_LAYOUT_PACKED));
+    }
     case CUDA_FN_CREATE_ROPE: return rope_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
     case CUDA_FN_FREE_ROPE: return rope_free(k, lInput, pf);
     case CUDA_FN_ROPE_FWD: return finish(k, rope_run(k, llInput, pl, false));

@@ -28,25 +28,25 @@ template <int DP> struct Tile {
   static constexpr int CPT = DP / 16;  // output columns per thread
 };
 
-// Copy rows [row0, row0+64) of a (T,D) row-major matrix into smem[64][DP+4], zero-filling
+// Copy rows [row0, row0+64) of a (T,D) matrix with row stride ld into smem[64][DP+4], zero-filling
 // rows >= T and columns >= D.
 template <int DP>
-__device__ __forceinline__ void load_tile(float* __restrict__ s, const float* __restrict__ g, int row0, int T,
-                                          int D, bool vec_ok, int tid) {
+__device__ __forceinline__ void load_tile(float* __restrict__ s, const float* __restrict__ g, int64_t ld, int row0,
+                                          int T, int D, bool vec_ok, int tid) {
   constexpr int LD = Tile<DP>::LD;
   if (vec_ok) {
     constexpr int C4 = DP / 4;
     for (int idx = tid; idx < 64 * C4; idx += NT) {
       const int r = idx / C4, c4 = idx % C4;
       float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row0 + r < T && c4 * 4 < D) val = __ldg(reinterpret_cast<const float4*>(g + (int64_t)(row0 + r) * D) + c4);
+      if (row0 + r < T && c4 * 4 < D) val = __ldg(reinterpret_cast<const float4*>(g + (int64_t)(row0 + r) * ld) + c4);
       *reinterpret_cast<float4*>(s + r * LD + c4 * 4) = val;
     }
   } else {
     for (int idx = tid; idx < 64 * DP; idx += NT) {
       const int r = idx / DP, c = idx % DP;
       float val = 0.f;
-      if (row0 + r < T && c < D) val = __ldg(g + (int64_t)(row0 + r) * D + c);
+      if (row0 + r < T && c < D) val = __ldg(g + (int64_t)(row0 + r) * ld + c);
       s[r * LD + c] = val;
     }
   }
@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(NT) sdpa_fwd_f32_kernel(const float* __restric
                                                          const int* __restrict__ causal_flag, int H, int T, int D,
                                                          float scale, float* __restrict__ Y,
                                                          float* __restrict__ row_max, float* __restrict__ row_sum,
-                                                         float* __restrict__ y_copy, int vec_ok) {
+                                                         float* __restrict__ y_copy, int vec_ok,
+                                                         const McaStrides sin, const McaStrides sout) {
   extern __shared__ __align__(16) float smem[];
   constexpr int LD = Tile<DP>::LD, CPT = Tile<DP>::CPT;
   float* Qs = smem;
@@ -178,11 +179,12 @@ __global__ void __launch_bounds__(NT) sdpa_fwd_f32_kernel(const float* __restric
   const int qt = gridDim.x - 1 - blockIdx.x;
   const int q0 = qt * BM;
   const int mode = effective_mode(mask_mode, causal_flag);
-  const float* Qg = Q + (int64_t)bh * T * D;
-  const float* Kg = K + (int64_t)bh * T * D;
-  const float* Vg = V + (int64_t)bh * T * D;
+  const int64_t in_base = (int64_t)b * sin.b + (int64_t)(bh - b * H) * sin.h;
+  const float* Qg = Q + in_base;
+  const float* Kg = K + in_base;
+  const float* Vg = V + in_base;
 
-  load_tile<DP>(Qs, Qg, q0, T, D, vec_ok, tid);
+  load_tile<DP>(Qs, Qg, sin.t, q0, T, D, vec_ok, tid);
 
   float m[4], l[4], acc[4][CPT];
 #pragma unroll
@@ -194,8 +196,8 @@ __global__ void __launch_bounds__(NT) sdpa_fwd_f32_kernel(const float* __restric
   const int kv_end = (mode == MCA_MASK_CAUSAL) ? min(T, q0 + BM) : T;
   for (int k0 = 0; k0 < kv_end; k0 += BN) {
     __syncthreads();  // previous step's readers of Ks/Vs/Ps are done (also orders the Q load)
-    load_tile<DP>(Ks, Kg, k0, T, D, vec_ok, tid);
-    load_tile<DP>(Vs, Vg, k0, T, D, vec_ok, tid);
+    load_tile<DP>(Ks, Kg, sin.t, k0, T, D, vec_ok, tid);
+    load_tile<DP>(Vs, Vg, sin.t, k0, T, D, vec_ok, tid);
     __syncthreads();
     float s[4][4];
     tile_nt<DP>(Qs, Ks, s, ty, tx);
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(NT) sdpa_fwd_f32_kernel(const float* __restric
     const int i = q0 + ty + 16 * a;
     if (i >= T) continue;
     const float inv = 1.f / l[a];
-    float* yo = Y + ((int64_t)bh * T + i) * D;
+    float* yo = Y + (int64_t)b * sout.b + (int64_t)(bh - b * H) * sout.h + (int64_t)i * sout.t;
     float* yc = y_copy ? y_copy + ((int64_t)bh * T + i) * D : nullptr;
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
@@ -250,12 +252,15 @@ __global__ void __launch_bounds__(NT) sdpa_fwd_f32_kernel(const float* __restric
 
 // delta[i] = sum_c dY[i][c] * Y[i][c]  (the rowsum(dP o P) term of the softmax backward).
 __global__ void sdpa_bwd_delta_kernel(const float* __restrict__ dY, const float* __restrict__ Ysaved, int64_t rows,
-                                      int D, float* __restrict__ delta) {
+                                      int H, int T, int D, const McaStrides sdy, float* __restrict__ delta) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
+  const int64_t bh = row / T;
+  const int64_t b = bh / H;
+  const float* dyr = dY + b * sdy.b + (bh - b * H) * sdy.h + (row - bh * T) * sdy.t;   // Ysaved is the handle's own contiguous copy
   float acc = 0.f;
-  for (int c = lane; c < D; c += 32) acc = fmaf(dY[row * D + c], Ysaved[row * D + c], acc);
+  for (int c = lane; c < D; c += 32) acc = fmaf(dyr[c], Ysaved[row * D + c], acc);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) delta[row] = acc;
@@ -271,7 +276,8 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dkdv_f32_kernel(
     const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
     const float* __restrict__ dY, const float* __restrict__ mask, int mask_mode, const int* __restrict__ causal_flag,
     const float* __restrict__ row_max, const float* __restrict__ row_sum, const float* __restrict__ delta, int H,
-    int T, int D, float scale, float* __restrict__ dK, float* __restrict__ dV, int vec_ok) {
+    int T, int D, float scale, float* __restrict__ dK, float* __restrict__ dV, int vec_ok, const McaStrides sin,
+    const McaStrides sout) {
   extern __shared__ __align__(16) float smem[];
   constexpr int LD = Tile<DP>::LD, CPT = Tile<DP>::CPT;
   float* Ks = smem;
@@ -284,9 +290,10 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dkdv_f32_kernel(
   const int bh = blockIdx.y, b = bh / H;
   const int k0 = blockIdx.x * BN;
   const int mode = effective_mode(mask_mode, causal_flag);
-  const int64_t base = (int64_t)bh * T * D;
-  load_tile<DP>(Ks, K + base, k0, T, D, vec_ok, tid);
-  load_tile<DP>(Vs, V + base, k0, T, D, vec_ok, tid);
+  const int64_t base = (int64_t)b * sin.b + (int64_t)(bh - b * H) * sin.h;
+  const int64_t base_dy = (int64_t)b * sout.b + (int64_t)(bh - b * H) * sout.h;
+  load_tile<DP>(Ks, K + base, sin.t, k0, T, D, vec_ok, tid);
+  load_tile<DP>(Vs, V + base, sin.t, k0, T, D, vec_ok, tid);
   float dk[4][CPT], dv[4][CPT];
 #pragma unroll
   for (int a = 0; a < 4; ++a)
@@ -295,8 +302,8 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dkdv_f32_kernel(
   const int q_begin = (mode == MCA_MASK_CAUSAL) ? k0 : 0;  // k0 is a multiple of 64
   for (int q0 = q_begin; q0 < T; q0 += BM) {
     __syncthreads();
-    load_tile<DP>(Qs, Q + base, q0, T, D, vec_ok, tid);
-    load_tile<DP>(dOs, dY + base, q0, T, D, vec_ok, tid);
+    load_tile<DP>(Qs, Q + base, sin.t, q0, T, D, vec_ok, tid);
+    load_tile<DP>(dOs, dY + base_dy, sout.t, q0, T, D, vec_ok, tid);
     __syncthreads();
     float s[4][4], dp[4][4];
     tile_nt<DP>(Qs, Ks, s, ty, tx);     // s[a][b]: query ty+16a, key tx+16b
@@ -328,7 +335,7 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dkdv_f32_kernel(
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
       const int col = out_col<DP>(tx, c);
-      if (col < D) { dK[base + (int64_t)j * D + col] = dk[a][c]; dV[base + (int64_t)j * D + col] = dv[a][c]; }
+      if (col < D) { dK[base + (int64_t)j * sin.t + col] = dk[a][c]; dV[base + (int64_t)j * sin.t + col] = dv[a][c]; }
     }
   }
 }
@@ -339,7 +346,7 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dq_f32_kernel(
     const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
     const float* __restrict__ dY, const float* __restrict__ mask, int mask_mode, const int* __restrict__ causal_flag,
     const float* __restrict__ row_max, const float* __restrict__ row_sum, const float* __restrict__ delta, int H,
-    int T, int D, float scale, float* __restrict__ dQ, int vec_ok) {
+    int T, int D, float scale, float* __restrict__ dQ, int vec_ok, const McaStrides sin, const McaStrides sout) {
   extern __shared__ __align__(16) float smem[];
   constexpr int LD = Tile<DP>::LD, CPT = Tile<DP>::CPT;
   float* Qs = smem;
@@ -352,9 +359,9 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dq_f32_kernel(
   const int qt = gridDim.x - 1 - blockIdx.x;
   const int q0 = qt * BM;
   const int mode = effective_mode(mask_mode, causal_flag);
-  const int64_t base = (int64_t)bh * T * D;
-  load_tile<DP>(Qs, Q + base, q0, T, D, vec_ok, tid);
-  load_tile<DP>(dOs, dY + base, q0, T, D, vec_ok, tid);
+  const int64_t base = (int64_t)b * sin.b + (int64_t)(bh - b * H) * sin.h;
+  load_tile<DP>(Qs, Q + base, sin.t, q0, T, D, vec_ok, tid);
+  load_tile<DP>(dOs, dY + (int64_t)b * sout.b + (int64_t)(bh - b * H) * sout.h, sout.t, q0, T, D, vec_ok, tid);
   float mi[4], inv_l[4], di[4], dq[4][CPT];
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
@@ -367,8 +374,8 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dq_f32_kernel(
   const int kv_end = (mode == MCA_MASK_CAUSAL) ? min(T, q0 + BM) : T;
   for (int k0 = 0; k0 < kv_end; k0 += BN) {
     __syncthreads();
-    load_tile<DP>(Ks, K + base, k0, T, D, vec_ok, tid);
-    load_tile<DP>(Vs, V + base, k0, T, D, vec_ok, tid);
+    load_tile<DP>(Ks, K + base, sin.t, k0, T, D, vec_ok, tid);
+    load_tile<DP>(Vs, V + base, sin.t, k0, T, D, vec_ok, tid);
     __syncthreads();
     float s[4][4], dp[4][4];
     tile_nt<DP>(Qs, Ks, s, ty, tx);
@@ -394,7 +401,7 @@ __global__ void __launch_bounds__(NT) sdpa_bwd_dq_f32_kernel(
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
       const int col = out_col<DP>(tx, c);
-      if (col < D) dQ[base + (int64_t)i * D + col] = dq[a][c];
+      if (col < D) dQ[base + (int64_t)i * sin.t + col] = dq[a][c];
     }
   }
 }
@@ -435,30 +442,40 @@ int mca_classify_causal_mask(const float* mask, int T, int* flag, void* stream) 
 
 template <int DP>
 static int launch_fwd(const float* q, const float* k, const float* v, const float* mask, int mode, const int* flag,
-                      int B, int H, int T, int D, float* y, float* rmax, float* rsum, float* ycopy, cudaStream_t st) {
+                      int B, int H, int T, int D, float* y, float* rmax, float* rsum, float* ycopy, int layout,
+                      cudaStream_t st) {
   const size_t smem = fwd_smem_bytes<DP>();
   int e = set_smem(sdpa_fwd_f32_kernel<DP>, smem);
   if (e) return e;
-  const int vec_ok = (D % 4 == 0) && aligned16(q) && aligned16(k) && aligned16(v);
+  const McaStrides sin = mca_in_strides(layout, H, T, D), sout = mca_out_strides(layout, H, T, D);
+  const int vec_ok = (D % 4 == 0) && aligned16(q) && aligned16(k) && aligned16(v);  // every stride is a multiple of D
   dim3 grid(mca_ceil_div(T, BM), B * H);
   sdpa_fwd_f32_kernel<DP><<<grid, NT, smem, st>>>(q, k, v, mask, mode, flag, H, T, D, 1.0f / sqrtf((float)D), y, rmax,
-                                                  rsum, ycopy, vec_ok);
+                                                  rsum, ycopy, vec_ok, sin, sout);
   return mca_launch_status();
 }
 
 int mca_sdpa_forward_f32(const float* q, const float* k, const float* v, const float* mask, int mask_mode,
                          const int* causal_flag, int B, int H, int T, int D, float* y, float* row_max,
                          float* row_sum, float* y_copy, void* stream) {
+  return mca_sdpa_forward_f32_layout(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy,
+                                     MCA_LAYOUT_BHTD, stream);
+}
+
+int mca_sdpa_forward_f32_layout(const float* q, const float* k, const float* v, const float* mask, int mask_mode,
+                                const int* causal_flag, int B, int H, int T, int D, float* y, float* row_max,
+                                float* row_sum, float* y_copy, int layout, void* stream) {
   if (!q || !k || !v || !y) return ERROR_PARAM_NULL;
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (B <= 0 || H <= 0 || T <= 0 || D <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if ((mask_mode == MCA_MASK_TT || mask_mode == MCA_MASK_BATCH) && !mask) return ERROR_PARAM_NULL;
   if ((row_max == nullptr) != (row_sum == nullptr)) return ERROR_PARAM_NULL;
   cudaStream_t st = (cudaStream_t)stream;
   switch (pick_dp(D)) {
-    case 16: return launch_fwd<16>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, st);
-    case 32: return launch_fwd<32>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, st);
-    case 64: return launch_fwd<64>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, st);
-    case 128: return launch_fwd<128>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, st);
+    case 16: return launch_fwd<16>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, layout, st);
+    case 32: return launch_fwd<32>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, layout, st);
+    case 64: return launch_fwd<64>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, layout, st);
+    case 128: return launch_fwd<128>(q, k, v, mask, mask_mode, causal_flag, B, H, T, D, y, row_max, row_sum, y_copy, layout, st);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }
@@ -466,7 +483,8 @@ int mca_sdpa_forward_f32(const float* q, const float* k, const float* v, const f
 template <int DP>
 static int launch_bwd(const float* q, const float* k, const float* v, const float* dy, const float* mask, int mode,
                       const int* flag, const float* rmax, const float* rsum, const float* delta, int B, int H, int T,
-                      int D, float* dq, float* dk, float* dv, cudaStream_t st) {
+                      int D, float* dq, float* dk, float* dv, int layout, cudaStream_t st) {
+  const McaStrides sin = mca_in_strides(layout, H, T, D), sout = mca_out_strides(layout, H, T, D);
   const size_t smem_a = bwd_smem_bytes<DP>();
   const size_t smem_b = sizeof(float) * (4 * 64 * (DP + 4) + 64 * PLD);
   int e = set_smem(sdpa_bwd_dkdv_f32_kernel<DP>, smem_a);
@@ -477,11 +495,11 @@ static int launch_bwd(const float* q, const float* k, const float* v, const floa
   const float scale = 1.0f / sqrtf((float)D);
   dim3 grid(mca_ceil_div(T, BM), B * H);
   sdpa_bwd_dkdv_f32_kernel<DP><<<grid, NT, smem_a, st>>>(q, k, v, dy, mask, mode, flag, rmax, rsum, delta, H, T, D,
-                                                         scale, dk, dv, vec_ok);
+                                                         scale, dk, dv, vec_ok, sin, sout);
   e = mca_launch_status();
   if (e) return e;
   sdpa_bwd_dq_f32_kernel<DP><<<grid, NT, smem_b, st>>>(q, k, v, dy, mask, mode, flag, rmax, rsum, delta, H, T, D, scale,
-                                                       dq, vec_ok);
+                                                       dq, vec_ok, sin, sout);
   return mca_launch_status();
 }
 
@@ -489,20 +507,30 @@ int mca_sdpa_backward_f32(const float* q, const float* k, const float* v, const 
                           const float* mask, int mask_mode, const int* causal_flag, const float* row_max,
                           const float* row_sum, float* delta_scratch, int B, int H, int T, int D, float* dq,
                           float* dk, float* dv, void* stream) {
+  return mca_sdpa_backward_f32_layout(q, k, v, dy, y_saved, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch,
+                                      B, H, T, D, dq, dk, dv, MCA_LAYOUT_BHTD, stream);
+}
+
+int mca_sdpa_backward_f32_layout(const float* q, const float* k, const float* v, const float* dy, const float* y_saved,
+                                 const float* mask, int mask_mode, const int* causal_flag, const float* row_max,
+                                 const float* row_sum, float* delta_scratch, int B, int H, int T, int D, float* dq,
+                                 float* dk, float* dv, int layout, void* stream) {
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !dy || !y_saved || !row_max || !row_sum || !delta_scratch || !dq || !dk || !dv)
     return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || D <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if ((mask_mode == MCA_MASK_TT || mask_mode == MCA_MASK_BATCH) && !mask) return ERROR_PARAM_NULL;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)B * H * T;
-  sdpa_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dy, y_saved, rows, D, delta_scratch);
+  sdpa_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dy, y_saved, rows, H, T, D,
+                                                                    mca_out_strides(layout, H, T, D), delta_scratch);
   int e = mca_launch_status();
   if (e) return e;
   switch (pick_dp(D)) {
-    case 16: return launch_bwd<16>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, st);
-    case 32: return launch_bwd<32>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, st);
-    case 64: return launch_bwd<64>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, st);
-    case 128: return launch_bwd<128>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, st);
+    case 16: return launch_bwd<16>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, layout, st);
+    case 32: return launch_bwd<32>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, layout, st);
+    case 64: return launch_bwd<64>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, layout, st);
+    case 128: return launch_bwd<128>(q, k, v, dy, mask, mask_mode, causal_flag, row_max, row_sum, delta_scratch, B, H, T, D, dq, dk, dv, layout, st);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

@@ -98,8 +98,9 @@ struct TcParams {
   void* y;        // (B*H, T, HD) bf16
   float* lse;     // (B*H, T) or null: log2-domain log-sum-exp of the scaled logits
   int* status;
-  int T, causal;
+  int T, causal, H;
   float scale_log2;  // (1/sqrt(HD)) * log2(e)
+  McaStrides ys;     // element strides of the output view
 };
 
 // TF32 = false: bf16 tensors, kind::f16.  TF32 = true: fp32 tensors read as tf32 (kind::tf32),
@@ -120,6 +121,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;
+  const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
   const int T = p.T;
   // longest causal work first
   const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;
@@ -171,8 +173,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_expect_tx(bar(BAR_Q_FULL + x), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_Q + x * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_q, bar(BAR_Q_FULL + x), s * BOX,
-                      q0 + x * BLK, bh);
+          tma_load_4d(smem_base + PL::OFF_Q + x * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_q, bar(BAR_Q_FULL + x), s * BOX,
+                      q0 + x * BLK, hi, bi);
       }
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_max && ok; ++j) {
@@ -183,16 +185,16 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_expect_tx(bar(BAR_K_FULL + st), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * BOX,
-                      j * BLK, bh);
+          tma_load_4d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * BOX,
+                      j * BLK, hi, bi);
         issued_k = j + 1;
         ok = mbar_wait(bar(BAR_V_EMPTY + st), ph ^ 1u, p.status, 11, j);
         if (!ok) break;
         mbar_expect_tx(bar(BAR_V_FULL + st), PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s)
-          tma_load_3d(smem_base + PL::OFF_V + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_v, bar(BAR_V_FULL + st), s * BOX,
-                      j * BLK, bh);
+          tma_load_4d(smem_base + PL::OFF_V + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_v, bar(BAR_V_FULL + st), s * BOX,
+                      j * BLK, hi, bi);
         issued_v = j + 1;
       }
       if (!ok) {
@@ -475,8 +477,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float lsum = red_l[row];
         const float inv = 1.0f / lsum;
         const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BLK + x * BLK + half * OC);
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
-        float* yrow_f = reinterpret_cast<float*>(p.y) + ((int64_t)bh * T + qi) * HD + half * OC;
+        const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
+        float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t o[16];
@@ -518,20 +521,22 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int HD, bool TF32>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
-              int* status, cudaStream_t st) {
+              int* status, int layout, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   int e;
+  const McaStrides sin = mca_in_strides(layout, H, T, HD);
   if constexpr (TF32) {
-    if ((e = make_map_f32(&mq, q, B * H, T, HD)) || (e = make_map_f32(&mk, k, B * H, T, HD)) ||
-        (e = make_map_f32(&mv, v, B * H, T, HD, true)))
+    if ((e = make_map_f32(&mq, q, B, H, T, HD, sin)) || (e = make_map_f32(&mk, k, B, H, T, HD, sin)) ||
+        (e = make_map_f32(&mv, v, B, H, T, HD, sin, true)))
       return e;
   } else {
-    if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
-        (e = make_map_bf16(&mv, v, B * H, T, HD)))
+    if ((e = make_map_bf16(&mq, q, B, H, T, HD, sin)) || (e = make_map_bf16(&mk, k, B, H, T, HD, sin)) ||
+        (e = make_map_bf16(&mv, v, B, H, T, HD, sin)))
       return e;
   }
   TcParams p;
-  p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal;
+  p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal; p.H = H;
+  p.ys = mca_out_strides(layout, H, T, HD);
   p.scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
   const size_t smem = Plan<HD * (TF32 ? 4 : 2)>::BYTES;
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -553,6 +558,12 @@ extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch_w(long 
 
 int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
                         void* y, float* lse, int* status, void* stream) {
+  return mca_sdpa_forward_tc_layout(q, k, v, dtype, causal, B, H, T, D, y, lse, status, MCA_LAYOUT_BHTD, stream);
+}
+
+int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T,
+                               int D, void* y, float* lse, int* status, int layout, void* stream) {
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if (dtype != MCA_DTYPE_BF16 && dtype != MCA_DTYPE_TF32) return ERROR_ATTN_UNSUPPORTED_SHAPE;
@@ -563,10 +574,10 @@ int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, 
   if (dtype == MCA_DTYPE_TF32) {
     // fp32 rows are twice as wide: only the 64-wide head fits the shared-memory plan (two query tiles,
     // two K/V stages); wider heads use the exact fp32 kernel
-    if (D == 64) return launch_tc<64, true>(q, k, v, causal, B, H, T, y, lse, status, st);
+    if (D == 64) return launch_tc<64, true>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
   }
-  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y, lse, status, st);
-  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y, lse, status, st);
+  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

@@ -48,9 +48,10 @@ struct BwdParams {
   void* out0;          // dq kernel: dQ;  dkdv kernel: dK
   void* out1;          // dkdv kernel: dV
   int* status;
-  int T, causal;
+  int T, causal, H;
   float scale_log2;    // (1/sqrt(HD)) * log2(e)
   float scale;         // 1/sqrt(HD)
+  McaStrides os;       // element strides of the gradient views dQ, dK, dV
 };
 
 __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
@@ -96,6 +97,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, T = p.T;
+  const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest causal work first
   const int q0 = qt * BLK;
   const int n = p.causal ? (min(q0 + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
@@ -123,8 +125,8 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_expect_tx(bar(DQ_QDO_FULL), 2 * PL::TILE_BYTES);
 #pragma unroll
       for (int s = 0; s < PL::SUB; ++s) {
-        tma_load_3d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_q, bar(DQ_QDO_FULL), s * 64, q0, bh);
-        tma_load_3d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_do, bar(DQ_QDO_FULL), s * 64, q0, bh);
+        tma_load_4d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_q, bar(DQ_QDO_FULL), s * 64, q0, hi, bi);
+        tma_load_4d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_do, bar(DQ_QDO_FULL), s * 64, q0, hi, bi);
       }
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n && ok; ++j) {
@@ -135,13 +137,13 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!ok) break;
         mbar_expect_tx(bar(DQ_K_FULL + st), PL::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < PL::SUB; ++s) tma_load_3d(k_dst + s * PL::SUB_BYTES, &map_k, bar(DQ_K_FULL + st), s * 64, j * BLK, bh);
+        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(k_dst + s * PL::SUB_BYTES, &map_k, bar(DQ_K_FULL + st), s * 64, j * BLK, hi, bi);
         issued_k = j + 1;
         ok = mbar_wait(bar(DQ_V_EMPTY + st), ph ^ 1u, p.status, 111, j);
         if (!ok) break;
         mbar_expect_tx(bar(DQ_V_FULL + st), PL::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < PL::SUB; ++s) tma_load_3d(v_dst + s * PL::SUB_BYTES, &map_v, bar(DQ_V_FULL + st), s * 64, j * BLK, bh);
+        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(v_dst + s * PL::SUB_BYTES, &map_v, bar(DQ_V_FULL + st), s * 64, j * BLK, hi, bi);
         issued_v = j + 1;
       }
       if (!ok) {  // let copies in flight land (bounded) before the CTA's memory is released
@@ -263,7 +265,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((n - 1) & 1), p.status, 132, n));
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + ((int64_t)bh * T + qi) * HD + qtr * OC;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)qi * p.os.t + qtr * OC;
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t o[16];
@@ -308,6 +310,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, T = p.T;
+  const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
   const int kt = blockIdx.x;            // key tile; tile 0 has the most causal work and comes first
   const int k0 = kt * BLK;
   const int n_q_tiles = (T + BLK - 1) / BLK;
@@ -336,8 +339,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_expect_tx(bar(KV_KV_FULL), 2 * PL::TILE_BYTES);
 #pragma unroll
       for (int s = 0; s < PL::SUB; ++s) {
-        tma_load_3d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_k, bar(KV_KV_FULL), s * 64, k0, bh);
-        tma_load_3d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_v, bar(KV_KV_FULL), s * 64, k0, bh);
+        tma_load_4d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_k, bar(KV_KV_FULL), s * 64, k0, hi, bi);
+        tma_load_4d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_v, bar(KV_KV_FULL), s * 64, k0, hi, bi);
       }
       int issued = 0;
       for (int it = 0; it < n && ok; ++it) {
@@ -349,8 +352,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         mbar_expect_tx(bar(KV_Q_FULL + st), 2 * PL::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < PL::SUB; ++s) {
-          tma_load_3d(q_dst + s * PL::SUB_BYTES, &map_q, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, bh);
-          tma_load_3d(do_dst + s * PL::SUB_BYTES, &map_do, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, bh);
+          tma_load_4d(q_dst + s * PL::SUB_BYTES, &map_q, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, hi, bi);
+          tma_load_4d(do_dst + s * PL::SUB_BYTES, &map_do, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, hi, bi);
         }
         issued = it + 1;
       }
@@ -453,8 +456,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + ((int64_t)bh * T + kj) * HD + qtr * OC;
-        __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + ((int64_t)bh * T + kj) * HD + qtr * OC;
+        __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
+        __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t o[16];
@@ -475,14 +478,16 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
 // delta[row] = sum_c dY[row][c] * Y[row][c]  (bf16 inputs, fp32 result); one warp per row.
 __global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
-                                      int64_t rows, int D, float* __restrict__ delta) {
+                                      int64_t rows, int H, int T, int D, const McaStrides ys, float* __restrict__ delta) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
+  const int64_t bh = row / T, bi = bh / H;
+  const int64_t off = bi * ys.b + (bh - bi * H) * ys.h + (row - bh * T) * ys.t;   // y and dy share the output layout
   float acc = 0.f;
   for (int c = lane * 2; c < D; c += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + row * D + c));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + row * D + c));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + off + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + off + c));
     acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
   }
 #pragma unroll
@@ -492,14 +497,16 @@ __global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, cons
 
 template <int HD>
 int launch_bwd(const void* q, const void* k, const void* v, const void* dy, const float* lse, const float* delta,
-               int causal, int B, int H, int T, void* dq, void* dk, void* dv, int* status, cudaStream_t st) {
+               int causal, int B, int H, int T, void* dq, void* dk, void* dv, int* status, int layout, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdo;
   int e;
-  if ((e = make_map_bf16(&mq, q, B * H, T, HD)) || (e = make_map_bf16(&mk, k, B * H, T, HD)) ||
-      (e = make_map_bf16(&mv, v, B * H, T, HD)) || (e = make_map_bf16(&mdo, dy, B * H, T, HD)))
+  const McaStrides sin = mca_in_strides(layout, H, T, HD), sout = mca_out_strides(layout, H, T, HD);
+  if ((e = make_map_bf16(&mq, q, B, H, T, HD, sin)) || (e = make_map_bf16(&mk, k, B, H, T, HD, sin)) ||
+      (e = make_map_bf16(&mv, v, B, H, T, HD, sin)) || (e = make_map_bf16(&mdo, dy, B, H, T, HD, sout)))
     return e;
   BwdParams p;
-  p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal;
+  p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal; p.H = H;
+  p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const size_t smem = BwdPlan<HD>::BYTES;
@@ -519,6 +526,14 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
 int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void* y, const void* dy, const float* lse,
                          float* delta_scratch, int dtype, int causal, int B, int H, int T, int D, void* dq, void* dk,
                          void* dv, int* status, void* stream) {
+  return mca_sdpa_backward_tc_layout(q, k, v, y, dy, lse, delta_scratch, dtype, causal, B, H, T, D, dq, dk, dv, status,
+                                     MCA_LAYOUT_BHTD, stream);
+}
+
+int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, const void* y, const void* dy,
+                                const float* lse, float* delta_scratch, int dtype, int causal, int B, int H, int T, int D,
+                                void* dq, void* dk, void* dv, int* status, int layout, void* stream) {
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !dy || !lse || !delta_scratch || !dq || !dk || !dv || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if (dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
@@ -529,10 +544,10 @@ int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void
   if (D != 64 && D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)B * H * T;
-  bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, D,
-                                                                   delta_scratch);
+  bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, H, T, D,
+                                                                   mca_out_strides(layout, H, T, D), delta_scratch);
   int e = mca_launch_status();
   if (e) return e;
-  if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, st);
-  return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, st);
+  if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
+  return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
 }

@@ -46,6 +46,22 @@ enum McaMaskMode : int {
   MCA_MASK_CAUSAL = 3,  // analytic lower triangle: same result as a tril(ones) MCA_MASK_TT mask
 };
 
+// Element strides of a (B, H, T, D) view whose head dimension is contiguous.
+struct McaStrides {
+  int64_t b, h, t;
+};
+// layout 0: separate contiguous (B,H,T,D) tensors.  layout 1: q | k | v are the three feature thirds of a
+// (B, T, 3*H*D) projection output (the c_attn blob of CausalSelfAttentionLayer.cs:537-557 before its split and
+// head transposes) and the attention output is (B, T, H*D) (what c_proj consumes, :604).
+static inline McaStrides mca_in_strides(int layout, int H, int T, int D) {
+  if (layout == 1) return McaStrides{(int64_t)T * 3 * H * D, (int64_t)D, (int64_t)3 * H * D};
+  return McaStrides{(int64_t)H * T * D, (int64_t)T * D, (int64_t)D};
+}
+static inline McaStrides mca_out_strides(int layout, int H, int T, int D) {
+  if (layout == 1) return McaStrides{(int64_t)T * H * D, (int64_t)D, (int64_t)H * D};
+  return McaStrides{(int64_t)H * T * D, (int64_t)T * D, (int64_t)D};
+}
+
 #define MCA_CUDA_TRY(expr)                      \
   do {                                          \
     cudaError_t _e = (expr);                    \

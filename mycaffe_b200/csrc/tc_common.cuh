@@ -98,6 +98,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -421,35 +427,30 @@ inline EncodeTiledFn get_encode_fn() {
 }
 
 // (BH, T, HD) bf16 tensor, box = 64 columns x 128 rows of one (b,h), 128-byte swizzle.
-inline int make_map_bf16(CUtensorMap* map, const void* base, int BH, int T, int HD) {
+inline int make_map_4d(CUtensorMap* map, const void* base, CUtensorMapDataType type, int elt, int B, int H, int T, int HD,
+                       const McaStrides& st, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return ERROR_NOT_IMPLEMENTED;
-  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)T * HD * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)BLK, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st.t * elt, (cuuint64_t)st.h * elt, (cuuint64_t)st.b * elt};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / elt), (cuuint32_t)BLK, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, type, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : ERROR_PARAM_OUT_OF_RANGE;
 }
-
-// (BH, T, HD) fp32 tensor, box = 32 columns (128 bytes) x 128 rows of one (b,h).  K-major operands
+// bf16 view (B, H, T, HD) with the given element strides, box = 64 columns (128 bytes) x 128 rows of one
+// (b,h), 128-byte swizzle.  Rows beyond T are zero-filled per head.
+inline int make_map_bf16(CUtensorMap* map, const void* base, int B, int H, int T, int HD, const McaStrides& st) {
+  return make_map_4d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, H, T, HD, st, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+// fp32 view, box = 32 columns (128 bytes) x 128 rows of one (b,h).  K-major operands
 // use the ordinary 128-byte swizzle; an MN-major tf32 operand (V) must use the 32-byte-atom variant
 // (the only layout the tensor core accepts for 32-bit MN-major data).
-inline int make_map_f32(CUtensorMap* map, const void* base, int BH, int T, int HD, bool mn_major_operand = false) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return ERROR_NOT_IMPLEMENTED;
-  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)T, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)HD * 4, (cuuint64_t)T * HD * 4};
-  cuuint32_t box[3] = {32, (cuuint32_t)BLK, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  mn_major_operand ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : ERROR_PARAM_OUT_OF_RANGE;
+inline int make_map_f32(CUtensorMap* map, const void* base, int B, int H, int T, int HD, const McaStrides& st,
+                        bool mn_major_operand = false) {
+  return make_map_4d(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, B, H, T, HD, st,
+                     mn_major_operand ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 }  // namespace tc

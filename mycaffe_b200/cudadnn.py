@@ -204,6 +204,14 @@ class CudaDnn:
         """x += Wo . attn (llama2_gpu.cpp:78-81)."""
         self._invoke(ids.MCA_FN_DECODE_OUT, None, [hAttn, hWo, nBatch, nDim, hX])
 
+    def AttnScaledDotProductForwardPacked(self, hCuDnn, hAttn, nBlockSize, hQKV, hMask, hY, bBatchMask=False):
+        """ATTN_FWD on the (B,T,3C) c_attn output: q, k, v are read in place, y is written as (B,T,C)."""
+        self._invoke(ids.MCA_FN_ATTN_FWD_PACKED, None,
+                     [hCuDnn, hAttn, nBlockSize, hQKV, hMask, hY, 1 if bBatchMask else 0])
+
+    def AttnScaledDotProductBackwardPacked(self, hCuDnn, hAttn, hQKV, hdQKV, hMask, hY, hdY):
+        self._invoke(ids.MCA_FN_ATTN_BWD_PACKED, None, [hCuDnn, hAttn, hQKV, hdQKV, hMask, hY, hdY])
+
     def AttnForwardHost(self, q, k, v, y, bCausal, nHeadsPerChunk=0):
         """Forward for (B,H,T,D) numpy tensors in host memory (float32, or bf16 bit patterns as uint16),
         copies overlapped with the kernel; `y` is filled in place."""

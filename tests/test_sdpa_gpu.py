@@ -387,3 +387,73 @@ def test_forward_from_host_rejects_bad_arguments(cuda):
     with pytest.raises(CudaDnnError) as ei:
         cuda.AttnForwardHost(q, q, q, q.copy(), True)
     assert ei.value.code == 90901      # no tensor-core kernel for this head size
+
+
+def _split_packed(qkv, H):
+    """(B,T,3C) c_attn output -> q, k, v as (B,H,T,D): the split + head transpose of
+    CausalSelfAttentionLayer.cs:537-557 restated in numpy."""
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    return tuple(np.ascontiguousarray(qkv[:, :, i * C:(i + 1) * C].reshape(B, T, H, C // H).transpose(0, 2, 1, 3))
+                 for i in range(3))
+
+
+def _merge_heads(y):
+    B, H, T, D = y.shape
+    return np.ascontiguousarray(y.transpose(0, 2, 1, 3).reshape(B, T, H * D))
+
+
+@pytest.mark.parametrize("dtype,B,H,T,D,mask_kind", [
+    ("f32", 2, 3, 70, 16, "causal_handle"), ("f32", 1, 4, 128, 16, "none"), ("f32", 2, 2, 200, 64, "batch"),
+    ("bf16", 2, 3, 200, 64, "causal"), ("bf16", 1, 2, 384, 128, "causal"), ("bf16", 2, 2, 256, 128, "none")])
+def test_packed_qkv_layout_forward_backward(cuda, dtype, B, H, T, D, mask_kind):
+    """Ids 2004/2005: q, k, v read in place from the (B,T,3C) projection output, y written as (B,T,C), and the
+    backward producing the (B,T,3C) gradient from a (B,T,C) one -- against the oracle on the split tensors."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(B * 100 + T + D)
+    C = H * D
+    bf16 = dtype == "bf16"
+    tol = BF16_TOL if bf16 else FP32_TIGHT
+    rnd = bf16_round if bf16 else (lambda a: a)
+    qkv = rnd(rng.standard_normal((B, T, 3 * C)).astype(np.float32))
+    dy = rnd(rng.standard_normal((B, T, C)).astype(np.float32))
+    q, k, v = _split_packed(qkv, H)
+    mask, mode, hmask_data, batch = None, 0, None, False
+    if mask_kind in ("causal", "causal_handle"):
+        mask, mode = oracle.causal_mask(T), 1
+        if mask_kind == "causal_handle":
+            hmask_data = mask
+    elif mask_kind == "batch":
+        mask = (rng.random((B, T)) > 0.3).astype(np.float32)
+        mask[:, 0] = 1
+        mode, hmask_data, batch = 2, mask, True
+    alloc = cuda.AllocMemoryBf16 if bf16 else cuda.AllocMemory
+    hC, hA = cuda.CreateCuDNN(), cuda.CreateAttn()
+    cuda.SetAttn(hC, hA, 0, True, B, T, H, D, 0.0, 0, ids.MCA_DTYPE_BF16 if bf16 else ids.MCA_DTYPE_F32,
+                 ids.MCA_FLAG_CAUSAL_IMPLICIT if mask_kind == "causal" else 0)
+    hQKV, hdQKV, hY, hdY = alloc(qkv), alloc(qkv.size), alloc(B * T * C), alloc(dy)
+    hMask = cuda.AllocMemory(hmask_data) if hmask_data is not None else 0
+    cuda.AttnScaledDotProductForwardPacked(hC, hA, T, hQKV, hMask, hY, batch)
+    y = cuda.GetMemory(hY, B * T * C).reshape(B, T, C)
+    y_ref = oracle.sdpa_forward(q, k, v, mask, mode, f64=True)
+    assert rel_err(y, _merge_heads(y_ref)) < tol
+    cuda.AttnScaledDotProductBackwardPacked(hC, hA, hQKV, hdQKV, 0, hY, hdY)
+    dqkv = cuda.GetMemory(hdQKV, qkv.size).reshape(B, T, 3 * C)
+    dy_h = np.ascontiguousarray(dy.reshape(B, T, H, D).transpose(0, 2, 1, 3))
+    ref = oracle.sdpa_backward(q, k, v, dy_h, mask, mode, f64=True)
+    for i, name in enumerate("qkv"):
+        assert rel_err(dqkv[:, :, i * C:(i + 1) * C], _merge_heads(ref[i])) < (tol if bf16 else FP32_TOL), name
+    # a backward in the other layout does not match this forward
+    from mycaffe_b200 import CudaDnnError
+    if not bf16:
+        n = B * H * T * D
+        hs = [cuda.AllocMemory(n) for _ in range(7)]
+        with pytest.raises(CudaDnnError) as ei:
+            cuda.AttnScaledDotProductBackward(hC, hA, hs[0], hs[1], hs[2], hs[3], hs[4], hs[5], 0, hY, hs[6])
+        assert ei.value.code == 90903
+        for h in hs:
+            cuda.FreeMemory(h)
+    for h in (hQKV, hdQKV, hY, hdY) + ((hMask,) if hMask else ()):
+        cuda.FreeMemory(h)
+    cuda.FreeAttn(hA)
+    cuda.FreeCuDNN(hC)
