@@ -69,7 +69,8 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_ATTN_FWD_HOST 2003  /* longs {pQ,pK,pV,pY (host addresses),hostDtype,causal,B,H,T,D[,headsPerChunk]}: mca_sdpa_forward_host */
 #define MCA_FN_ATTN_FWD_PACKED 2004  /* longs {hCuDnn,hAttn,T,hQKV,hMask,hY,bBatchMask}: ATTN_FWD reading q,k,v from the (B,T,3C) c_attn output, y as (B,T,C) */
 #define MCA_FN_ATTN_BWD_PACKED 2005  /* longs {hCuDnn,hAttn,hQKV,hdQKV,hMask,hY,hdY}: its backward; dQKV (B,T,3C) from dY (B,T,C) */
-#define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode */
+#define MCA_FN_DECODE_CREATE 2010  /* floats {theta}; longs {B,nHeads,nKvHeads,headSize,seqLen,cacheBf16} -> hDecode.
+                                      theta <= 0: no RoPE -- the KV-cache step of MultiheadAttentionLayer.cs:713-777 for B sequences */
 #define MCA_FN_DECODE_FREE 2011    /* floats {hDecode} */
 #define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
 #define MCA_FN_DECODE_QKV 2013     /* floats {eps}; longs {hX,hRmsW,hWq,hWk,hWv,B,dim,kvDim,hQ,hK,hV}: RMSNorm + q,k,v projections */

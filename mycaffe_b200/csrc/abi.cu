@@ -585,7 +585,15 @@ long decode_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG
   d.scratch_floats = worst;
   const size_t n = (size_t)d.seq_len * (d.hs / 2);
   std::vector<float> c(n), s(n);
-  mca_rope_tables_host(d.seq_len, d.hs, pf[0], c.data(), s.data());  // same table as precompute_freqs_cis
+  if (pf[0] > 0.f) {
+    mca_rope_tables_host(d.seq_len, d.hs, pf[0], c.data(), s.data());  // same table as precompute_freqs_cis
+  } else {
+    // theta <= 0: no rotation (cos 1, sin 0 reproduces q and k bit for bit).  This is the KV-cache step of
+    // MultiheadAttentionLayer (MultiheadAttentionLayer.cs:713-777: append k, v at nPos, scores over 0..nPos,
+    // softmax, times V) whose caches (nPos+1, heads, size) have the layout of one sequence here.
+    std::fill(c.begin(), c.end(), 1.0f);
+    std::fill(s.begin(), s.end(), 0.0f);
+  }
   if (cudaMalloc(&d.fr, n * 4) != cudaSuccess || cudaMalloc(&d.fi, n * 4) != cudaSuccess ||
       cudaMalloc(&d.scratch, (size_t)d.scratch_floats * 4) != cudaSuccess) {
     cudaGetLastError(); cudaFree(d.fr); cudaFree(d.fi); return ERROR_MEMORY_OUT;

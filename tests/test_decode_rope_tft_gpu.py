@@ -18,9 +18,9 @@ def cuda():
 
 
 class Decoder:
-    def __init__(self, cuda, B, n_heads, n_kv, hs, seq_len, bf16):
+    def __init__(self, cuda, B, n_heads, n_kv, hs, seq_len, bf16, theta=10000.0):
         self.cuda, self.B, self.nh, self.nkv, self.hs, self.seq_len, self.bf16 = cuda, B, n_heads, n_kv, hs, seq_len, bf16
-        self.h = cuda.CreateDecode(B, n_heads, n_kv, hs, seq_len, bf16)
+        self.h = cuda.CreateDecode(B, n_heads, n_kv, hs, seq_len, bf16, theta)
         alloc = cuda.AllocMemoryBf16 if bf16 else cuda.AllocMemory
         kv_dim = n_kv * hs
         self.hKc, self.hVc = alloc(B * seq_len * kv_dim), alloc(B * seq_len * kv_dim)
@@ -272,3 +272,22 @@ def test_fused_rmsnorm_qkv_batched(cuda, B):
             assert rel_err(got, oracle.gemv(wmat, xn)) < 2e-5
     for h in hs + [hQ, hK, hV]:
         cuda.FreeMemory(h)
+
+
+def test_kv_cache_decode_without_rope_matches_causal_sdpa(cuda):
+    """theta <= 0: the KV-cache generation step of MultiheadAttentionLayer (MultiheadAttentionLayer.cs:713-777:
+    append k, v at nPos, scores over 0..nPos, softmax, times V), here for two sequences at once.  Token t of the
+    loop must equal row t of the causal SDPA over the whole sequence, and the caches must hold k, v verbatim."""
+    rng = np.random.default_rng(11)
+    B, H, D, T = 2, 4, 64, 40
+    q, k, v = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(3))
+    ref = oracle.sdpa_forward(q, k, v, oracle.causal_mask(T), 1, f64=True)          # (B,H,T,D)
+    d = Decoder(cuda, B, H, H, D, T, False, theta=0.0)
+    for t in range(T):
+        tok = lambda a: np.ascontiguousarray(a[:, :, t, :]).reshape(B, H * D)
+        out = d.step(tok(q), tok(k), tok(v), np.full(B, t, np.int32))
+        assert rel_err(out, tok(ref)) < 2e-5, t
+    kc, vc = d.caches()
+    np.testing.assert_array_equal(kc.reshape(B, T, H, D), k.transpose(0, 2, 1, 3))
+    np.testing.assert_array_equal(vc.reshape(B, T, H, D), v.transpose(0, 2, 1, 3))
+    d.close()
