@@ -400,25 +400,27 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       TC_TRACE_W(j, 2);
       // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
       // the row sum is taken in fp32.  The first 64 keys are handed to the MMA warp before the rest.
-      const float nm[2] = {-m_new[0], -m_new[1]};
-      float rs[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+      const float2 nm2[2] = {make_float2(-m_new[0], -m_new[0]), make_float2(-m_new[1], -m_new[1])};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[16];
-      // exponentials of key groups [g_lo, g_hi) (8 keys each); bf16 results packed into pk[0..], tf32 in place
+      // exponentials of key groups [g_lo, g_hi) (8 keys each); bf16 results packed into pk[0..], tf32 in place.
+      // A thread's two adjacent keys of a row go through the scale-and-subtract and the row sum as one fp32 pair.
       auto exp_groups = [&](const int g_lo, const int g_hi) {
 #pragma unroll
         for (int g = g_lo; g < g_hi; ++g) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const float p0 = exp2_sel(fmaf(__uint_as_float(s[4 * g + 2 * h]), p.scale_log2, nm[h]), 2 * g);
-            const float p1 = exp2_sel(fmaf(__uint_as_float(s[4 * g + 2 * h + 1]), p.scale_log2, nm[h]), 2 * g + 1);
+            const float2 xx = ffma2(make_float2(__uint_as_float(s[4 * g + 2 * h]), __uint_as_float(s[4 * g + 2 * h + 1])), scale2, nm2[h]);
+            const float p0 = exp2_sel(xx.x, 2 * g);
+            const float p1 = exp2_sel(xx.y, 2 * g + 1);
             if constexpr (TF32) {
               s[4 * g + 2 * h] = __float_as_uint(p0);
               s[4 * g + 2 * h + 1] = __float_as_uint(p1);
             } else {
               pk[2 * (g - g_lo) + h] = pack_bf16(p0, p1);
             }
-            rs[h][0] += p0;
-            rs[h][1] += p1;
+            rs2[h] = fadd2(rs2[h], make_float2(p0, p1));
           }
         }
       };
@@ -444,8 +446,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_P_READY + x));
-      l[0] += rs[0][0] + rs[0][1];
-      l[1] += rs[1][0] + rs[1][1];
+      l[0] += rs2[0].x + rs2[0].y;
+      l[1] += rs2[1].x + rs2[1].y;
       m_used[0] = m_new[0];
       m_used[1] = m_new[1];
       TC_TRACE(x, j, 5);

@@ -26,14 +26,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Upper bound the hardware may keep a waiting thread suspended before try_wait returns false (it
+// wakes as soon as the phase completes): a long hint means a waiting warp issues almost nothing.
+#ifndef MCA_TRY_WAIT_HINT_NS
+#define MCA_TRY_WAIT_HINT_NS 1000000u
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(MCA_TRY_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
@@ -310,7 +315,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 // Packed fp32 pair arithmetic (two lanes per instruction on sm_100).
 #ifndef MCA_USE_F32X2
-#define MCA_USE_F32X2 0
+#define MCA_USE_F32X2 1
 #endif
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
 #if !MCA_USE_F32X2
