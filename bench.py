@@ -145,20 +145,54 @@ def run_ours(args):
     y = torch.empty_like(q)
     y_all = torch.empty(world, B, Hl, T, D, device=dev, dtype=torch.bfloat16) if world > 1 else None
     status = torch.zeros(8, device=dev, dtype=torch.int32)
+    # Exchange of the head outputs when world > 1: by default the kernel's epilogue stores its tiles straight
+    # into every rank's (B,H,T,D) buffer over NVLink and a one-element all-reduce follows; if symmetric memory
+    # cannot be set up on this box, a NCCL all-gather after the kernel.
+    peer_out, exchange = None, "none"
+    if world > 1:
+        exchange = "nccl all-gather after the kernel"
+        if not args.nccl_exchange:
+            try:
+                peer_out = head_shard.PeerOutput(B, H, T, D, dev)
+                peer_dst, (ysb, ysh, yst) = peer_out.destinations(h_lo), peer_out.strides
+                exchange = "kernel epilogue stores to every rank's buffer (peer memory over NVLink) + 1-element all-reduce"
+            except Exception as exc:  # noqa: BLE001 - any failure to map peer memory selects the NCCL exchange
+                peer_out = None
+                exchange += f" (symmetric memory unavailable: {type(exc).__name__})"
+
+    def launch_prefill():
+        if peer_out is not None:
+            return lib.mca_sdpa_forward_tc_scatter(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
+                                                   peer_dst, world, ysb, ysh, yst, None, status.data_ptr(), sp)
+        return lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
+                                       y.data_ptr(), None, status.data_ptr(), sp)
+
+    def exchange_outputs():
+        if peer_out is not None:
+            peer_out.wait()
+        elif world > 1:
+            head_shard.gather_heads(y, out=y_all, strided=True)
 
     def prefill_step():
-        rc = lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
-                                     y.data_ptr(), None, status.data_ptr(), sp)
+        rc = launch_prefill()
         if rc:
-            raise RuntimeError(f"mca_sdpa_forward_tc failed with {rc}")
-        if world > 1:
-            head_shard.gather_heads(y, out=y_all, strided=True)
+            raise RuntimeError(f"prefill launch failed with {rc}")
+        exchange_outputs()
 
     for _ in range(args.warmup):
         prefill_step()
     barrier()
     if int(status[0].item()) != 0:
         raise RuntimeError(f"prefill kernel reported status {status[:4].tolist()}")
+    if peer_out is not None:
+        # the buffers every rank filled must equal what a NCCL all-gather of the same head outputs gives
+        rc = lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
+                                     y.data_ptr(), None, status.data_ptr(), sp)
+        ref = head_shard.gather_heads(y, out=y_all)
+        torch.cuda.synchronize()
+        if rc or not torch.equal(ref, peer_out.tensor):
+            raise RuntimeError("peer-store exchange disagrees with the NCCL all-gather")
+        del ref
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -168,11 +202,9 @@ def run_ours(args):
     ev[0].record(stream)
     for i in range(args.steps):
         kern_ev[i][0].record(stream)
-        rc = lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
-                                     y.data_ptr(), None, status.data_ptr(), sp)
+        rc = launch_prefill()
         kern_ev[i][1].record(stream)
-        if world > 1:
-            head_shard.gather_heads(y, out=y_all, strided=True)
+        exchange_outputs()
         ev[i + 1].record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -209,7 +241,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"config5 causal prefill B={B} H={H} D={D} T={T} bf16, heads partitioned over {world} GPU(s)"
-                                   + (" + NCCL all-gather of head outputs" if world > 1 else ""),
+                                   + (f"; exchange of head outputs: {exchange}" if world > 1 else ""),
                        "l2": "inputs (Q,K,V,O %.0f MB per rank) exceed the 126 MB L2" % (4 * q.numel() * 2 / 1e6),
                        "parallelism": f"heads/{world}"},
             "gpu_launches": args.steps, "clocks": clocks, "roofline": roofline, "e2e": e2e, "decode": decode,
@@ -567,6 +599,8 @@ def main():
     ap.add_argument("--batch", type=int, default=PF_B)
     ap.add_argument("--seq-len", type=int, default=PF_T)
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
     ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()

@@ -205,6 +205,16 @@ MCA_API int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void
                                         int T, int D, void* dq, void* dk, void* dv, int* status, int layout,
                                         void* stream);
 
+/* Head-parallel forward whose epilogue is also the exchange: every finished 16-byte piece of the output
+ * tile is stored to each of the n_dst (<= 8) destinations -- this GPU's buffer and the peers' buffers
+ * mapped into this process (plain stores over NVLink; no collective follows, only a barrier before
+ * the buffers are read).  q,k,v: this rank's heads, (B,H,T,D) bf16 contiguous; y_dst[i]: where this
+ * rank's head 0 lies in destination i, with the element strides of the full (B,H_total,T,D) output.
+ * No reference counterpart (the reference has no tensor-parallel mode, MyCaffe/common/Parallel.cs:351-508). */
+MCA_API int mca_sdpa_forward_tc_scatter(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
+                                        int T, int D, void* const* y_dst, int n_dst, int64_t y_stride_b,
+                                        int64_t y_stride_h, int64_t y_stride_t, float* lse, int* status, void* stream);
+
 /* RoPE on a (B,T,H,D) tensor.  Replaces RopeDataGpu<T>::Forward/Backward, Cuda Files/rope.cu:784-864.
  * Tables are (T,D/2) as built by mca_rope_tables_host. */
 MCA_API int mca_rope_f32(const float* x, float* y, int64_t n, int T, int H, int D, const float* cos_table,

@@ -34,6 +34,7 @@ SIGNATURES = {
     "mca_sdpa_backward_f32_layout": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp,
                                           _i, _vp]),
     "mca_sdpa_forward_tc_layout": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "mca_sdpa_forward_tc_scatter": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), _i, _i64, _i64, _i64, _vp, _vp, _vp]),
     "mca_sdpa_backward_tc_layout": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i,
                                          _vp]),
     "mca_classify_causal_mask": (_i, [_vp, _i, _vp, _vp]),

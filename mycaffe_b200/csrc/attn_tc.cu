@@ -101,6 +101,8 @@ struct TcParams {
   int T, causal, H;
   float scale_log2;  // (1/sqrt(HD)) * log2(e)
   McaStrides ys;     // element strides of the output view
+  void* y_more[7];   // further destinations of the same bf16 output tile (peer GPUs' buffers), same strides
+  int n_more;
 };
 
 // TF32 = false: bf16 tensors, kind::f16.  TF32 = true: fp32 tensors read as tf32 (kind::tf32),
@@ -504,6 +506,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
               w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
               *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
+              // the same 16 bytes to every further destination: plain stores, over NVLink when it is a peer's buffer
+              for (int d = 0; d < p.n_more; ++d)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + y_off + c * 16 + i) = w;
             }
           }
         }
@@ -523,7 +528,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int HD, bool TF32>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
-              int* status, int layout, cudaStream_t st) {
+              int* status, int layout, cudaStream_t st, void* const* y_more = nullptr, int n_more = 0,
+              const McaStrides* y_strides = nullptr) {
   CUtensorMap mq, mk, mv;
   int e;
   const McaStrides sin = mca_in_strides(layout, H, T, HD);
@@ -538,7 +544,9 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   }
   TcParams p;
   p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal; p.H = H;
-  p.ys = mca_out_strides(layout, H, T, HD);
+  p.ys = y_strides ? *y_strides : mca_out_strides(layout, H, T, HD);
+  p.n_more = n_more;
+  for (int i = 0; i < 7; ++i) p.y_more[i] = i < n_more ? y_more[i] : nullptr;
   p.scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
   const size_t smem = Plan<HD * (TF32 ? 4 : 2)>::BYTES;
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -561,6 +569,27 @@ extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch_w(long 
 int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
                         void* y, float* lse, int* status, void* stream) {
   return mca_sdpa_forward_tc_layout(q, k, v, dtype, causal, B, H, T, D, y, lse, status, MCA_LAYOUT_BHTD, stream);
+}
+
+int mca_sdpa_forward_tc_scatter(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T,
+                                int D, void* const* y_dst, int n_dst, int64_t y_stride_b, int64_t y_stride_h,
+                                int64_t y_stride_t, float* lse, int* status, void* stream) {
+  if (!q || !k || !v || !y_dst || !status) return ERROR_PARAM_NULL;
+  if (n_dst < 1 || n_dst > 8) return ERROR_PARAM_OUT_OF_RANGE;
+  if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  if (dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (y_stride_t < D || y_stride_h <= 0 || y_stride_b <= 0 || (y_stride_t | y_stride_h | y_stride_b) % 8) return ERROR_PARAM_OUT_OF_RANGE;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v);
+  for (int i = 0; i < n_dst; ++i) {
+    if (!y_dst[i]) return ERROR_PARAM_NULL;
+    bits |= reinterpret_cast<uintptr_t>(y_dst[i]);
+  }
+  if (bits & 15) return ERROR_PARAM_OUT_OF_RANGE;
+  const McaStrides ys{y_stride_b, y_stride_h, y_stride_t};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
+  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
+  return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }
 
 int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T,

@@ -62,3 +62,51 @@ def gather_decode_outputs(o_local: torch.Tensor, group=None, out: torch.Tensor |
         out = torch.empty((world,) + tuple(o_local.shape), dtype=o_local.dtype, device=o_local.device)
     dist.all_gather_into_tensor(out.view(-1), o_local.view(-1), group=group)
     return out.transpose(0, 1).reshape(o_local.shape[0], world * o_local.shape[1])
+
+
+class PeerOutput:
+    """The full (B, H, T, D) bf16 attention output, held by every rank and filled by every rank's kernel.
+
+    The buffers are symmetric memory (`torch.distributed._symmetric_memory`): each rank maps its peers'
+    buffers, and the forward kernel stores every finished piece of its heads' output tiles into all of them
+    (`mca_sdpa_forward_tc_scatter`), so the all-gather disappears into the kernel's epilogue.  `wait()` is the
+    only synchronisation left: a one-element all-reduce on the current stream, after which every rank's
+    stores have landed everywhere."""
+
+    def __init__(self, B: int, H: int, T: int, D: int, device, group=None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+        self.shape = (B, H, T, D)
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if not 1 <= self.world <= 8:
+            raise ValueError("the scatter epilogue takes up to 8 destinations")
+        self.tensor = symm_mem.empty((B, H, T, D), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != self.tensor.data_ptr() or any(p == 0 or p % 16 for p in ptrs):
+            raise RuntimeError(f"unexpected symmetric-memory mapping {ptrs}")
+        self._ptrs = ptrs
+        self._flag = torch.zeros(1, device=device)
+        self._ctypes = ctypes
+
+    @property
+    def strides(self) -> tuple[int, int, int]:
+        B, H, T, D = self.shape
+        return H * T * D, T * D, D
+
+    def destinations(self, h_lo: int):
+        """ctypes array of where head `h_lo` lies in every rank's buffer, this rank's own buffer first."""
+        B, H, T, D = self.shape
+        if not 0 <= h_lo < H:
+            raise ValueError(f"head {h_lo} outside {H}")
+        off = h_lo * T * D * 2
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        arr = (self._ctypes.c_void_p * self.world)(*[self._ptrs[r] + off for r in order])
+        return arr
+
+    def wait(self) -> None:
+        """Every rank's kernel has finished (stream-ordered; the host does not block)."""
+        dist.all_reduce(self._flag, group=self.group)

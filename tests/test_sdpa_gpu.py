@@ -457,3 +457,33 @@ def test_packed_qkv_layout_forward_backward(cuda, dtype, B, H, T, D, mask_kind):
         cuda.FreeMemory(h)
     cuda.FreeAttn(hA)
     cuda.FreeCuDNN(hC)
+
+
+def test_scatter_epilogue_writes_every_destination(cuda):
+    """mca_sdpa_forward_tc_scatter: the heads of one rank land, at their offset, in every destination buffer
+    of the full (B, H_total, T, D) output (two local buffers stand in for this GPU's and a peer's)."""
+    import ctypes as C
+    from mycaffe_b200 import _lib, function_ids as ids
+    lib = _lib.load()
+    rng = np.random.default_rng(5)
+    B, Hl, Htot, h_lo, T, D = 2, 2, 6, 3, 200, 128
+    q, k, v = (bf16_round(a) for a in rand_qkv(rng, B, Hl, T, D))
+    hq, hk, hv = (cuda.AllocMemoryBf16(a) for a in (q, k, v))
+    n_full = B * Htot * T * D
+    dst = [cuda.AllocMemoryBf16(np.full(n_full, 7.0, np.float32)) for _ in range(2)]
+    hst = cuda.AllocMemory(np.zeros(8, np.float32))
+    ptrs = (C.c_void_p * 2)(*[cuda.GetPointer(h) + h_lo * T * D * 2 for h in dst])
+    rc = lib.mca_sdpa_forward_tc_scatter(cuda.GetPointer(hq), cuda.GetPointer(hk), cuda.GetPointer(hv), ids.MCA_DTYPE_BF16, 1,
+                                         B, Hl, T, D, ptrs, 2, Htot * T * D, T * D, D, None, cuda.GetPointer(hst), None)
+    assert rc == 0
+    cuda.SynchronizeDevice()
+    ref = oracle.sdpa_forward(q, k, v, None, 3, f64=True)
+    outs = [cuda.GetMemory(h, n_full).reshape(B, Htot, T, D) for h in dst]
+    np.testing.assert_array_equal(outs[0], outs[1])
+    assert rel_err(outs[0][:, h_lo:h_lo + Hl], ref) < BF16_TOL
+    untouched = np.ones(Htot, bool)
+    untouched[h_lo:h_lo + Hl] = False
+    assert np.all(outs[0][:, untouched] == 7.0)          # other ranks' heads are not written
+    assert np.all(cuda.GetMemory(hst, 8).view(np.int32)[:4] == 0)
+    for h in [hq, hk, hv, hst] + dst:
+        cuda.FreeMemory(h)
