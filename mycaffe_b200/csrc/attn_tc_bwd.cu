@@ -293,7 +293,8 @@ enum KvBar : int {
   KV_PT_READY = 6,   // P^T and dS^T written to TMEM
   KV_ACC_DONE = 7,   // dV / dK products of the step finished
   KV_DRAIN = 8,
-  KV_BAR_COUNT = 9
+  KV_LD_READY = 9,   // the step's per-query log-sum-exp and delta are staged in shared memory
+  KV_BAR_COUNT = 10
 };
 
 template <int HD>
@@ -322,7 +323,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __syncthreads();
   if (s_abort != 0) return;
   if (tid == 0) {
-    for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), i == KV_PT_READY ? (uint32_t)EW_WARPS : 1u);
+    for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), (i == KV_PT_READY || i == KV_LD_READY) ? (uint32_t)EW_WARPS : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
   }
@@ -417,8 +418,30 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     constexpr int OC = HD / 4;
     const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
     const bool key_ok = kj < T;
+    // The query-dependent terms (minus log-sum-exp, delta) are the same for every key row: the first 256
+    // element-wise threads fetch one value each a step ahead and stage them in shared memory, so that the
+    // inner loop reads them as broadcasts instead of 64 global loads per thread.  Rows beyond T get
+    // lse = +inf, which makes their probabilities exactly zero.
+    __shared__ __align__(16) float s_nlse[2][BLK];
+    __shared__ __align__(16) float s_del[2][BLK];
+    auto fetch = [&](int it) -> float {
+      const int qi = (i_begin + it) * BLK + (tid & (BLK - 1));
+      if (tid >= 2 * BLK || it >= n || qi >= T) return tid < BLK ? -INFINITY : 0.f;
+      return tid < BLK ? -__ldg(p.lse + (int64_t)bh * T + qi) : __ldg(p.delta + (int64_t)bh * T + qi);
+    };
+    auto stage = [&](int it, float v) {
+      if (tid < BLK) s_nlse[it & 1][tid] = v;
+      else if (tid < 2 * BLK) s_del[it & 1][tid - BLK] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_LD_READY));
+    };
+    if (n > 0) stage(0, fetch(0));
     for (int it = 0; it < n && ok; ++it) {
-      const int q_base = (i_begin + it) * BLK + qtr * 32;   // first of this thread's 32 queries
+      const int q_local = qtr * 32;                         // first of this thread's 32 queries within the tile
+      const int q_base = (i_begin + it) * BLK + q_local;
+      const float next = fetch(it + 1);                     // in flight while this step is processed
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_LD_READY), (uint32_t)(it & 1), p.status, 231, it));
+      if (!ok) break;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ST_FULL), (uint32_t)(it & 1), p.status, 230, it));
       if (!ok) break;
       tc_fence_after();
@@ -426,25 +449,29 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld32(t_row + C_ST + qtr * 32, s);
       tmem_ld32(t_row + C_DPT + qtr * 32, dp);
       tmem_wait_ld();
-      const float* lse_p = p.lse + (int64_t)bh * T + q_base;
-      const float* del_p = p.delta + (int64_t)bh * T + q_base;
+      const float* nlse_s = s_nlse[it & 1] + q_local;
+      const float* del_s = s_del[it & 1] + q_local;
+      const bool diag = p.causal && (i_begin + it) * BLK < k0 + BLK;   // only the diagonal tile needs the causal test
       uint32_t pkp[16], pkd[16];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float pr[2], ds[2];
+      for (int i = 0; i < 32; i += 4) {
+        const float4 nl = *reinterpret_cast<const float4*>(nlse_s + i);
+        const float4 de = *reinterpret_cast<const float4*>(del_s + i);
+        const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, des[4] = {de.x, de.y, de.z, de.w};
+        float pr[4], ds[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int qi = q_base + i + e;
-          const bool valid = key_ok && qi < T && !(p.causal && kj > qi);
-          const float lse = valid ? __ldg(lse_p + i + e) : 0.f;
-          const float del = valid ? __ldg(del_p + i + e) : 0.f;
-          const float v = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, -lse));
-          pr[e] = valid ? v : 0.f;
-          ds[e] = valid ? v * (__uint_as_float(dp[i + e]) - del) * p.scale : 0.f;
+        for (int e = 0; e < 4; ++e) {
+          float v = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, nls[e]));
+          if (!key_ok || (diag && kj > q_base + i + e)) v = 0.f;
+          pr[e] = v;
+          ds[e] = v * (__uint_as_float(dp[i + e]) - des[e]) * p.scale;
         }
         pkp[i / 2] = pack_bf16(pr[0], pr[1]);
+        pkp[i / 2 + 1] = pack_bf16(pr[2], pr[3]);
         pkd[i / 2] = pack_bf16(ds[0], ds[1]);
+        pkd[i / 2 + 1] = pack_bf16(ds[2], ds[3]);
       }
+      if (it + 1 < n) stage(it + 1, next);
       tmem_st16(t_row + C_ST + qtr * 32, pkp);
       tmem_st16(t_row + C_DPT + qtr * 32, pkd);
       tmem_wait_st();
