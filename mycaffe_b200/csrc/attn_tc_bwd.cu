@@ -289,12 +289,14 @@ enum KvBar : int {
   KV_KV_FULL = 0,
   KV_Q_FULL = 1,     // [2]  Q and dY of a step (one barrier for both tiles)
   KV_Q_EMPTY = 3,    // [2]
-  KV_ST_FULL = 5,    // S^T and dP^T written by the MMA
-  KV_PT_READY = 6,   // P^T and dS^T written to TMEM
+  KV_ST_FULL = 5,    // S^T written by the MMA
+  KV_PT_READY = 6,   // P^T written to TMEM (over S^T)
   KV_ACC_DONE = 7,   // dV / dK products of the step finished
   KV_DRAIN = 8,
   KV_LD_READY = 9,   // the step's per-query log-sum-exp and delta are staged in shared memory
-  KV_BAR_COUNT = 10
+  KV_DPT_FULL = 10,  // dP^T written by the MMA
+  KV_DST_READY = 11, // dS^T written to TMEM (over dP^T)
+  KV_BAR_COUNT = 12
 };
 
 template <int HD>
@@ -323,7 +325,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __syncthreads();
   if (s_abort != 0) return;
   if (tid == 0) {
-    for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), (i == KV_PT_READY || i == KV_LD_READY) ? (uint32_t)EW_WARPS : 1u);
+    for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), (i == KV_PT_READY || i == KV_LD_READY || i == KV_DST_READY) ? (uint32_t)EW_WARPS : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
   }
@@ -372,41 +374,67 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BLK, HD, 0, 1);
       const uint32_t k_addr = smem_base + PL::OFF_RES0, v_addr = smem_base + PL::OFF_RES1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0));
-      for (int it = 0; it < n && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (uint32_t)((it >> 1) & 1);
-        const uint32_t q_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, do_addr = q_addr + PL::TILE_BYTES;
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + st), ph, p.status, 221, it));
-        if (!ok) break;
-        tc_fence_after();
-        // S^T = K Q^T and dP^T = V dY^T (rows = keys, columns = queries); they follow the previous
-        // step's dV / dK products in the same in-order pipe, so the aliased columns are free
+      // S^T = K Q^T and dP^T = V dY^T (rows = keys, columns = queries); P^T overwrites S^T and dS^T overwrites
+      // dP^T.  The two halves of a step are interleaved with the next step's first products,
+      //   dV(it), S^T(it+1), dK(it), dP^T(it+1),
+      // (the in-order pipe keeps every product behind the one that still reads the columns it overwrites),
+      // so the element-wise warps work on P^T(it+1) while dK(it) and dP^T(it+1) run.
+      auto q_stage = [&](int it) { return smem_base + PL::OFF_RING + (it & 1) * 2 * PL::TILE_BYTES; };
+      auto issue_st = [&](int it) {
+        const uint32_t q_addr = q_stage(it);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
           umma_ss_if<false>(leader, tmem_u + C_ST, make_desc(k_addr + off, 16, 1024), make_desc(q_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
+        umma_commit_if(leader, bar(KV_ST_FULL));
+      };
+      auto issue_dpt = [&](int it) {
+        const uint32_t do_addr = q_stage(it) + PL::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
           umma_ss_if<false>(leader, tmem_u + C_DPT, make_desc(v_addr + off, 16, 1024), make_desc(do_addr + off, 16, 1024), IDESC_NT, kk > 0);
         }
-        umma_commit_if(leader, bar(KV_ST_FULL));
+        umma_commit_if(leader, bar(KV_DPT_FULL));
+      };
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0));
+      if (ok && n > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + 0), 0, p.status, 221, 0));
+        if (ok) {
+          tc_fence_after();
+          issue_st(0);
+          issue_dpt(0);
+        }
+      }
+      for (int it = 0; it < n && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t q_addr = q_stage(it), do_addr = q_addr + PL::TILE_BYTES;
+        // dV += P^T dY: A from TMEM (16 queries = 8 packed columns per step), B MN-major
         ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it));
         if (!ok) break;
         tc_fence_after();
-        // dV += P^T dY, dK += dS^T Q: A from TMEM (16 queries = 8 packed columns per step), B MN-major
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_ts_if<false>(leader, tmem_u + C_DV, tmem_u + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(do_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+        if (it + 1 < n) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + ((it + 1) & 1)), (uint32_t)(((it + 1) >> 1) & 1), p.status, 221, it + 1));
+          if (!ok) break;
+          tc_fence_after();
+          issue_st(it + 1);
+        }
+        // dK += dS^T Q
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_DST_READY), (uint32_t)(it & 1), p.status, 223, it));
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_ts_if<false>(leader, tmem_u + C_DK, tmem_u + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(q_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit_if(leader, bar(KV_Q_EMPTY + st));
         umma_commit_if(leader, bar(KV_ACC_DONE));
+        if (it + 1 < n) issue_dpt(it + 1);
       }
       umma_commit_if(leader, bar(KV_DRAIN));
       mbar_wait(bar(KV_DRAIN), 0, p.status, 227, 0);
@@ -445,39 +473,54 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ST_FULL), (uint32_t)(it & 1), p.status, 230, it));
       if (!ok) break;
       tc_fence_after();
-      uint32_t s[32], dp[32];
-      tmem_ld32(t_row + C_ST + qtr * 32, s);
-      tmem_ld32(t_row + C_DPT + qtr * 32, dp);
-      tmem_wait_ld();
       const float* nlse_s = s_nlse[it & 1] + q_local;
       const float* del_s = s_del[it & 1] + q_local;
       const bool diag = p.causal && (i_begin + it) * BLK < k0 + BLK;   // only the diagonal tile needs the causal test
-      uint32_t pkp[16], pkd[16];
+      // pass 1: P^T = 2^(S^T scale - lse), kept in fp32 for pass 2, packed to bf16 over S^T
+      uint32_t s[32], pk[16];
+      tmem_ld32(t_row + C_ST + qtr * 32, s);
+      tmem_wait_ld();
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         const float4 nl = *reinterpret_cast<const float4*>(nlse_s + i);
-        const float4 de = *reinterpret_cast<const float4*>(del_s + i);
-        const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, des[4] = {de.x, de.y, de.z, de.w};
-        float pr[4], ds[4];
+        const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, nls[e]));
           if (!key_ok || (diag && kj > q_base + i + e)) v = 0.f;
-          pr[e] = v;
-          ds[e] = v * (__uint_as_float(dp[i + e]) - des[e]) * p.scale;
+          s[i + e] = __float_as_uint(v);
         }
-        pkp[i / 2] = pack_bf16(pr[0], pr[1]);
-        pkp[i / 2 + 1] = pack_bf16(pr[2], pr[3]);
-        pkd[i / 2] = pack_bf16(ds[0], ds[1]);
-        pkd[i / 2 + 1] = pack_bf16(ds[2], ds[3]);
+        pk[i / 2] = pack_bf16(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        pk[i / 2 + 1] = pack_bf16(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
       }
-      if (it + 1 < n) stage(it + 1, next);
-      tmem_st16(t_row + C_ST + qtr * 32, pkp);
-      tmem_st16(t_row + C_DPT + qtr * 32, pkd);
+      tmem_st16(t_row + C_ST + qtr * 32, pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(KV_PT_READY));
+      // pass 2: dS^T = P^T o (dP^T - delta) scale, packed to bf16 over dP^T
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_DPT_FULL), (uint32_t)(it & 1), p.status, 233, it));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dp[32];
+      tmem_ld32(t_row + C_DPT + qtr * 32, dp);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 de = *reinterpret_cast<const float4*>(del_s + i);
+        const float des[4] = {de.x, de.y, de.z, de.w};
+        float ds[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ds[e] = __uint_as_float(s[i + e]) * (__uint_as_float(dp[i + e]) - des[e]) * p.scale;
+        pk[i / 2] = pack_bf16(ds[0], ds[1]);
+        pk[i / 2 + 1] = pack_bf16(ds[2], ds[3]);
+      }
+      if (it + 1 < n) stage(it + 1, next);
+      tmem_st16(t_row + C_DPT + qtr * 32, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KV_DST_READY));
     }
     if (ok && n > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
