@@ -233,16 +233,17 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (lane == 0) mbar_arrive(bar(DQ_SDP_FREE));
       const int k0 = j * BLK + qtr * 32;
       const bool edge = (p.causal && j * BLK + BLK - 1 > q0) || (j * BLK + BLK > T);
+      // dS = P o (dP - delta) scale with P = 2^(S scale_log2 - lse); adjacent keys go through as fp32 pairs
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse, -lse);
+      const float2 ps2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
+      const float2 zero2 = make_float2(0.f, 0.f);
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        float d0, d1;
-        {
-          const float pr = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse));
-          d0 = pr * (__uint_as_float(dp[i]) - delta) * p.scale;
-          const float pr1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse));
-          d1 = pr1 * (__uint_as_float(dp[i + 1]) - delta) * p.scale;
-        }
+        const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
+        const float2 g = ffma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ps2, nd2);
+        const float2 d = ffma2(make_float2(fast_exp2(x.x), fast_exp2(x.y)), g, zero2);
+        float d0 = d.x, d1 = d.y;
         if (edge) {
           const int kj = k0 + i;
           if (!row_ok || kj >= T || (p.causal && kj > qi)) d0 = 0.f;
@@ -446,7 +447,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     constexpr int OC = HD / 4;
     const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
     const bool key_ok = kj < T;
-    // The query-dependent terms (minus log-sum-exp, delta) are the same for every key row: the first 256
+    // The query-dependent terms (minus log-sum-exp, minus delta x scale) are the same for every key row: the first 256
     // element-wise threads fetch one value each a step ahead and stage them in shared memory, so that the
     // inner loop reads them as broadcasts instead of 64 global loads per thread.  Rows beyond T get
     // lse = +inf, which makes their probabilities exactly zero.
@@ -455,7 +456,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     auto fetch = [&](int it) -> float {
       const int qi = (i_begin + it) * BLK + (tid & (BLK - 1));
       if (tid >= 2 * BLK || it >= n || qi >= T) return tid < BLK ? -INFINITY : 0.f;
-      return tid < BLK ? -__ldg(p.lse + (int64_t)bh * T + qi) : __ldg(p.delta + (int64_t)bh * T + qi);
+      return tid < BLK ? -__ldg(p.lse + (int64_t)bh * T + qi) : -__ldg(p.delta + (int64_t)bh * T + qi) * p.scale;
     };
     auto stage = [&](int it, float v) {
       if (tid < BLK) s_nlse[it & 1][tid] = v;
@@ -476,7 +477,9 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const float* nlse_s = s_nlse[it & 1] + q_local;
       const float* del_s = s_del[it & 1] + q_local;
       const bool diag = p.causal && (i_begin + it) * BLK < k0 + BLK;   // only the diagonal tile needs the causal test
-      // pass 1: P^T = 2^(S^T scale - lse), kept in fp32 for pass 2, packed to bf16 over S^T
+      // pass 1: P^T = 2^(S^T scale - lse), kept in fp32 for pass 2, packed to bf16 over S^T (fp32 pairs)
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ps2 = make_float2(p.scale, p.scale);
+      const float2 zero2 = make_float2(0.f, 0.f);
       uint32_t s[32], pk[16];
       tmem_ld32(t_row + C_ST + qtr * 32, s);
       tmem_wait_ld();
@@ -485,10 +488,14 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const float4 nl = *reinterpret_cast<const float4*>(nlse_s + i);
         const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float v = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, nls[e]));
-          if (!key_ok || (diag && kj > q_base + i + e)) v = 0.f;
-          s[i + e] = __float_as_uint(v);
+        for (int e = 0; e < 4; e += 2) {
+          const float2 x = ffma2(make_float2(__uint_as_float(s[i + e]), __uint_as_float(s[i + e + 1])), sc2,
+                                 make_float2(nls[e], nls[e + 1]));
+          float v0 = fast_exp2(x.x), v1 = fast_exp2(x.y);
+          if (!key_ok || (diag && kj > q_base + i + e)) v0 = 0.f;
+          if (!key_ok || (diag && kj > q_base + i + e + 1)) v1 = 0.f;
+          s[i + e] = __float_as_uint(v0);
+          s[i + e + 1] = __float_as_uint(v1);
         }
         pk[i / 2] = pack_bf16(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
         pk[i / 2 + 1] = pack_bf16(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
@@ -509,11 +516,14 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int i = 0; i < 32; i += 4) {
         const float4 de = *reinterpret_cast<const float4*>(del_s + i);
         const float des[4] = {de.x, de.y, de.z, de.w};
-        float ds[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) ds[e] = __uint_as_float(s[i + e]) * (__uint_as_float(dp[i + e]) - des[e]) * p.scale;
-        pk[i / 2] = pack_bf16(ds[0], ds[1]);
-        pk[i / 2 + 1] = pack_bf16(ds[2], ds[3]);
+        for (int e = 0; e < 4; e += 2) {
+          // (dP - delta) scale as one fused pair operation, then times P
+          const float2 g = ffma2(make_float2(__uint_as_float(dp[i + e]), __uint_as_float(dp[i + e + 1])), ps2,
+                                 make_float2(des[e], des[e + 1]));
+          const float2 d = ffma2(make_float2(__uint_as_float(s[i + e]), __uint_as_float(s[i + e + 1])), g, zero2);
+          pk[(i + e) / 2] = pack_bf16(d.x, d.y);
+        }
       }
       if (it + 1 < n) stage(it + 1, next);
       tmem_st16(t_row + C_DPT + qtr * 32, pk);
