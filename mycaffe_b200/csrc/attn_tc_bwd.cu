@@ -40,6 +40,14 @@ template <int HD> struct BwdPlan {
   static constexpr uint32_t OFF_RING = 2 * TILE_BYTES;     // stage s: tile a at +s*2*TILE, tile b at +TILE after it
   static constexpr uint32_t OFF_BAR = 6 * TILE_BYTES;
   static constexpr uint32_t BYTES = OFF_BAR + 256 + 1024;
+  // dQ kernel: K lives until the step's dQ product, so its ring is one stage deeper than V's (K(j+2) could
+  // otherwise only be requested when dQ(j) has finished, one step before it is needed, and every step
+  // would wait out the load latency): K stages at OFF_RING + {0,1,2} tiles, V stages behind them.
+  static constexpr int K_STAGES = 3, V_STAGES = 2;
+  static constexpr uint32_t OFF_KRING = OFF_RING;
+  static constexpr uint32_t OFF_VRING = OFF_RING + K_STAGES * TILE_BYTES;
+  static constexpr uint32_t OFF_BAR_DQ = OFF_VRING + V_STAGES * TILE_BYTES;
+  static constexpr uint32_t BYTES_DQ = OFF_BAR_DQ + 256 + 1024;
 };
 
 struct BwdParams {
@@ -71,16 +79,16 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_
 // ---------------------------------------------------------------------------------------------
 enum DqBar : int {
   DQ_QDO_FULL = 0,
-  DQ_K_FULL = 1,    // [2]
-  DQ_K_EMPTY = 3,   // [2]
-  DQ_V_FULL = 5,    // [2]
-  DQ_V_EMPTY = 7,   // [2]
-  DQ_SDP_FULL = 9,  // S and dP of the step written by the MMA
-  DQ_SDP_FREE = 10, // element-wise warps have S and dP in registers
-  DQ_DS_READY = 11, // dS written to TMEM
-  DQ_DQ_DONE = 12,  // dQ += dS K of the step finished (dS may be overwritten)
-  DQ_DRAIN = 13,
-  DQ_BAR_COUNT = 14
+  DQ_K_FULL = 1,    // [3]
+  DQ_K_EMPTY = 4,   // [3]
+  DQ_V_FULL = 7,    // [2]
+  DQ_V_EMPTY = 9,   // [2]
+  DQ_SDP_FULL = 11, // S and dP of the step written by the MMA
+  DQ_SDP_FREE = 12, // element-wise warps have S and dP in registers
+  DQ_DS_READY = 13, // dS written to TMEM
+  DQ_DQ_DONE = 14,  // dQ += dS K of the step finished (dS may be overwritten)
+  DQ_DRAIN = 15,
+  DQ_BAR_COUNT = 16
 };
 
 template <int HD>
@@ -92,8 +100,8 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar0 = smem_base + PL::OFF_BAR;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR + DQ_BAR_COUNT * 8);
+  const uint32_t bar0 = smem_base + PL::OFF_BAR_DQ;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR_DQ + DQ_BAR_COUNT * 8);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, T = p.T;
@@ -130,26 +138,28 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        const uint32_t k_dst = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, v_dst = k_dst + PL::TILE_BYTES;
-        ok = mbar_wait(bar(DQ_K_EMPTY + st), ph ^ 1u, p.status, 110, j);
+        const int ks = j % PL::K_STAGES, vs = j % PL::V_STAGES;
+        const uint32_t kph = (uint32_t)((j / PL::K_STAGES) & 1), vph = (uint32_t)((j / PL::V_STAGES) & 1);
+        const uint32_t k_dst = smem_base + PL::OFF_KRING + ks * PL::TILE_BYTES, v_dst = smem_base + PL::OFF_VRING + vs * PL::TILE_BYTES;
+        ok = mbar_wait(bar(DQ_K_EMPTY + ks), kph ^ 1u, p.status, 110, j);
         if (!ok) break;
-        mbar_expect_tx(bar(DQ_K_FULL + st), PL::TILE_BYTES);
+        mbar_expect_tx(bar(DQ_K_FULL + ks), PL::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(k_dst + s * PL::SUB_BYTES, &map_k, bar(DQ_K_FULL + st), s * 64, j * BLK, hi, bi);
+        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(k_dst + s * PL::SUB_BYTES, &map_k, bar(DQ_K_FULL + ks), s * 64, j * BLK, hi, bi);
         issued_k = j + 1;
-        ok = mbar_wait(bar(DQ_V_EMPTY + st), ph ^ 1u, p.status, 111, j);
+        ok = mbar_wait(bar(DQ_V_EMPTY + vs), vph ^ 1u, p.status, 111, j);
         if (!ok) break;
-        mbar_expect_tx(bar(DQ_V_FULL + st), PL::TILE_BYTES);
+        mbar_expect_tx(bar(DQ_V_FULL + vs), PL::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(v_dst + s * PL::SUB_BYTES, &map_v, bar(DQ_V_FULL + st), s * 64, j * BLK, hi, bi);
+        for (int s = 0; s < PL::SUB; ++s) tma_load_4d(v_dst + s * PL::SUB_BYTES, &map_v, bar(DQ_V_FULL + vs), s * 64, j * BLK, hi, bi);
         issued_v = j + 1;
       }
       if (!ok) {  // let copies in flight land (bounded) before the CTA's memory is released
         mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 112, 0);
-        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(bar(DQ_K_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 113, j);
-        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(DQ_V_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 114, j);
+        for (int j = max(0, issued_k - PL::K_STAGES); j < issued_k; ++j)
+          mbar_wait(bar(DQ_K_FULL + j % PL::K_STAGES), (uint32_t)((j / PL::K_STAGES) & 1), p.status, 113, j);
+        for (int j = max(0, issued_v - PL::V_STAGES); j < issued_v; ++j)
+          mbar_wait(bar(DQ_V_FULL + j % PL::V_STAGES), (uint32_t)((j / PL::V_STAGES) & 1), p.status, 114, j);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -161,8 +171,9 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);  // both operands K-major
       constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 0, 1);   // A from TMEM, B = K tile MN-major
       const uint32_t q_addr = smem_base + PL::OFF_RES0, do_addr = smem_base + PL::OFF_RES1;
-      auto issue_sdp = [&](int st) {
-        const uint32_t k_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, v_addr = k_addr + PL::TILE_BYTES;
+      auto issue_sdp = [&](int j) {
+        const uint32_t k_addr = smem_base + PL::OFF_KRING + (j % PL::K_STAGES) * PL::TILE_BYTES;
+        const uint32_t v_addr = smem_base + PL::OFF_VRING + (j % PL::V_STAGES) * PL::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
@@ -184,29 +195,28 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         umma_commit_if(leader, bar(DQ_V_EMPTY + 0));
       }
       for (int j = 0; j < n && ok; ++j) {
-        const int st = j & 1, st_n = (j + 1) & 1;
-        const uint32_t ph_n = (uint32_t)(((j + 1) >> 1) & 1);
+        const int jn = j + 1;
         if (j + 1 < n) {
           // next S / dP as soon as the element-wise warps hold the current ones in registers
           ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_SDP_FREE), (uint32_t)(j & 1), p.status, 123, j));
-          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_K_FULL + st_n), ph_n, p.status, 124, j));
-          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_V_FULL + st_n), ph_n, p.status, 125, j));
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_K_FULL + jn % PL::K_STAGES), (uint32_t)((jn / PL::K_STAGES) & 1), p.status, 124, j));
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_V_FULL + jn % PL::V_STAGES), (uint32_t)((jn / PL::V_STAGES) & 1), p.status, 125, j));
           if (!ok) break;
           tc_fence_after();
-          issue_sdp(st_n);
+          issue_sdp(jn);
           umma_commit_if(leader, bar(DQ_SDP_FULL));
-          umma_commit_if(leader, bar(DQ_V_EMPTY + st_n));
+          umma_commit_if(leader, bar(DQ_V_EMPTY + jn % PL::V_STAGES));
         }
         ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DS_READY), (uint32_t)(j & 1), p.status, 126, j));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES;
+        const uint32_t k_addr = smem_base + PL::OFF_KRING + (j % PL::K_STAGES) * PL::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_ts_if<false>(leader, tmem_u + C_DQ, tmem_u + C_DS + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ,
                   (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit_if(leader, bar(DQ_DQ_DONE));
-        umma_commit_if(leader, bar(DQ_K_EMPTY + st));
+        umma_commit_if(leader, bar(DQ_K_EMPTY + j % PL::K_STAGES));
       }
       umma_commit_if(leader, bar(DQ_DRAIN));
       mbar_wait(bar(DQ_DRAIN), 0, p.status, 127, 0);
@@ -589,15 +599,15 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
   p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
-  const size_t smem = BwdPlan<HD>::BYTES;
+  const size_t smem = BwdPlan<HD>::BYTES, smem_dq = BwdPlan<HD>::BYTES_DQ;
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
   dim3 grid(mca_ceil_div(T, BLK), B * H);
   p.out0 = dk; p.out1 = dv;
   sdpa_bwd_dkdv_tc_kernel<HD><<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
   if ((e = mca_launch_status())) return e;
   p.out0 = dq; p.out1 = nullptr;
-  sdpa_bwd_dq_tc_kernel<HD><<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+  sdpa_bwd_dq_tc_kernel<HD><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
   return mca_launch_status();
 }
 
