@@ -48,6 +48,13 @@ template <int HD> struct BwdPlan {
   static constexpr uint32_t OFF_VRING = OFF_RING + K_STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR_DQ = OFF_VRING + V_STAGES * TILE_BYTES;
   static constexpr uint32_t BYTES_DQ = OFF_BAR_DQ + 256 + 1024;
+  // dK/dV kernel: the same seven tiles, then barriers, the staged per-query terms ([2][128] floats twice) and the
+  // abort flag, all in dynamic shared memory (no static allocation, so the dynamic base keeps its alignment).
+  // At HD = 128 this leaves 752 bytes for aligning the base to 1024; the kernel checks that it fits.
+  static constexpr uint32_t OFF_STAGE_KV = OFF_BAR_DQ + 256;
+  static constexpr uint32_t OFF_FLAG_KV = OFF_STAGE_KV + 2 * 2 * BLK * 4;
+  static constexpr uint32_t NEED_KV = OFF_FLAG_KV + 16;
+  static constexpr uint32_t BYTES_KV = (NEED_KV + 1024 <= 227u * 1024u) ? NEED_KV + 1024 : 227u * 1024u;
 };
 
 struct BwdParams {
@@ -298,16 +305,18 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ---------------------------------------------------------------------------------------------
 enum KvBar : int {
   KV_KV_FULL = 0,
-  KV_Q_FULL = 1,     // [2]  Q and dY of a step (one barrier for both tiles)
-  KV_Q_EMPTY = 3,    // [2]
-  KV_ST_FULL = 5,    // S^T written by the MMA
-  KV_PT_READY = 6,   // P^T written to TMEM (over S^T)
-  KV_ACC_DONE = 7,   // dV / dK products of the step finished
-  KV_DRAIN = 8,
-  KV_LD_READY = 9,   // the step's per-query log-sum-exp and delta are staged in shared memory
-  KV_DPT_FULL = 10,  // dP^T written by the MMA
-  KV_DST_READY = 11, // dS^T written to TMEM (over dP^T)
-  KV_BAR_COUNT = 12
+  KV_Q_FULL = 1,     // [3]  Q of a step (lives until the step's dK product: one stage deeper than dY)
+  KV_Q_EMPTY = 4,    // [3]
+  KV_DO_FULL = 7,    // [2]  dY of a step (last used by the step's dV product)
+  KV_DO_EMPTY = 9,   // [2]
+  KV_ST_FULL = 11,   // S^T written by the MMA
+  KV_PT_READY = 12,  // P^T written to TMEM (over S^T)
+  KV_ACC_DONE = 13,  // dV / dK products of the step finished
+  KV_DRAIN = 14,
+  KV_LD_READY = 15,  // the step's per-query log-sum-exp and delta are staged in shared memory
+  KV_DPT_FULL = 16,  // dP^T written by the MMA
+  KV_DST_READY = 17, // dS^T written to TMEM (over dP^T)
+  KV_BAR_COUNT = 18
 };
 
 template <int HD>
@@ -319,8 +328,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar0 = smem_base + PL::OFF_BAR;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR + KV_BAR_COUNT * 8);
+  const uint32_t bar0 = smem_base + PL::OFF_BAR_DQ;   // same seven-tile plan as the dQ kernel: Q ring where it has K, dY ring where it has V
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR_DQ + KV_BAR_COUNT * 8);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, T = p.T;
@@ -331,10 +340,17 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int i_begin = p.causal ? kt : 0;
   const int n = n_q_tiles - i_begin;    // query tiles to walk
 
-  __shared__ int s_abort;
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  // the aligned plan must fit in what was requested (it does unless the dynamic base is unusually placed)
+  uint32_t dyn_bytes;
+  asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+  if (smem_base + PL::NEED_KV > smem_u32(smem_raw) + dyn_bytes) {
+    if (tid == 0 && atomicCAS(p.status, 0, 2) == 0) { p.status[1] = 299; p.status[2] = (int)(smem_base - smem_u32(smem_raw)); }
+    return;
+  }
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + PL::OFF_FLAG_KV);
+  if (tid == 0) *s_abort = *reinterpret_cast<volatile int*>(p.status);
   __syncthreads();
-  if (s_abort != 0) return;
+  if (*s_abort != 0) return;
   if (tid == 0) {
     for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), (i == KV_PT_READY || i == KV_LD_READY || i == KV_DST_READY) ? (uint32_t)EW_WARPS : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -356,24 +372,32 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tma_load_4d(smem_base + PL::OFF_RES0 + s * PL::SUB_BYTES, &map_k, bar(KV_KV_FULL), s * 64, k0, hi, bi);
         tma_load_4d(smem_base + PL::OFF_RES1 + s * PL::SUB_BYTES, &map_v, bar(KV_KV_FULL), s * 64, k0, hi, bi);
       }
-      int issued = 0;
+      int issued = 0, issued_do = 0;
       for (int it = 0; it < n && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (uint32_t)((it >> 1) & 1);
-        const uint32_t q_dst = smem_base + PL::OFF_RING + st * 2 * PL::TILE_BYTES, do_dst = q_dst + PL::TILE_BYTES;
-        ok = mbar_wait(bar(KV_Q_EMPTY + st), ph ^ 1u, p.status, 210, it);
+        const int qs = it % PL::K_STAGES, ds = it % PL::V_STAGES;
+        const uint32_t qph = (uint32_t)((it / PL::K_STAGES) & 1), dph = (uint32_t)((it / PL::V_STAGES) & 1);
+        const uint32_t q_dst = smem_base + PL::OFF_KRING + qs * PL::TILE_BYTES, do_dst = smem_base + PL::OFF_VRING + ds * PL::TILE_BYTES;
+        ok = mbar_wait(bar(KV_Q_EMPTY + qs), qph ^ 1u, p.status, 210, it);
         if (!ok) break;
-        mbar_expect_tx(bar(KV_Q_FULL + st), 2 * PL::TILE_BYTES);
+        mbar_expect_tx(bar(KV_Q_FULL + qs), PL::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < PL::SUB; ++s) {
-          tma_load_4d(q_dst + s * PL::SUB_BYTES, &map_q, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, hi, bi);
-          tma_load_4d(do_dst + s * PL::SUB_BYTES, &map_do, bar(KV_Q_FULL + st), s * 64, (i_begin + it) * BLK, hi, bi);
-        }
+        for (int s = 0; s < PL::SUB; ++s)
+          tma_load_4d(q_dst + s * PL::SUB_BYTES, &map_q, bar(KV_Q_FULL + qs), s * 64, (i_begin + it) * BLK, hi, bi);
         issued = it + 1;
+        ok = mbar_wait(bar(KV_DO_EMPTY + ds), dph ^ 1u, p.status, 211, it);
+        if (!ok) break;
+        mbar_expect_tx(bar(KV_DO_FULL + ds), PL::TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < PL::SUB; ++s)
+          tma_load_4d(do_dst + s * PL::SUB_BYTES, &map_do, bar(KV_DO_FULL + ds), s * 64, (i_begin + it) * BLK, hi, bi);
+        issued_do = it + 1;
       }
       if (!ok) {
         mbar_wait(bar(KV_KV_FULL), 0, p.status, 212, 0);
-        for (int it = max(0, issued - 2); it < issued; ++it) mbar_wait(bar(KV_Q_FULL + (it & 1)), (uint32_t)((it >> 1) & 1), p.status, 213, it);
+        for (int it = max(0, issued - PL::K_STAGES); it < issued; ++it)
+          mbar_wait(bar(KV_Q_FULL + it % PL::K_STAGES), (uint32_t)((it / PL::K_STAGES) & 1), p.status, 213, it);
+        for (int it = max(0, issued_do - PL::V_STAGES); it < issued_do; ++it)
+          mbar_wait(bar(KV_DO_FULL + it % PL::V_STAGES), (uint32_t)((it / PL::V_STAGES) & 1), p.status, 214, it);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -390,7 +414,14 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       //   dV(it), S^T(it+1), dK(it), dP^T(it+1),
       // (the in-order pipe keeps every product behind the one that still reads the columns it overwrites),
       // so the element-wise warps work on P^T(it+1) while dK(it) and dP^T(it+1) run.
-      auto q_stage = [&](int it) { return smem_base + PL::OFF_RING + (it & 1) * 2 * PL::TILE_BYTES; };
+      auto q_stage = [&](int it) { return smem_base + PL::OFF_KRING + (it % PL::K_STAGES) * PL::TILE_BYTES; };
+      auto do_stage = [&](int it) { return smem_base + PL::OFF_VRING + (it % PL::V_STAGES) * PL::TILE_BYTES; };
+      auto wait_q = [&](int it) {
+        return __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + it % PL::K_STAGES), (uint32_t)((it / PL::K_STAGES) & 1), p.status, 221, it));
+      };
+      auto wait_do = [&](int it) {
+        return __all_sync(0xffffffffu, mbar_wait(bar(KV_DO_FULL + it % PL::V_STAGES), (uint32_t)((it / PL::V_STAGES) & 1), p.status, 224, it));
+      };
       auto issue_st = [&](int it) {
         const uint32_t q_addr = q_stage(it);
 #pragma unroll
@@ -401,7 +432,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         umma_commit_if(leader, bar(KV_ST_FULL));
       };
       auto issue_dpt = [&](int it) {
-        const uint32_t do_addr = q_stage(it) + PL::TILE_BYTES;
+        const uint32_t do_addr = do_stage(it);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
@@ -411,7 +442,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       };
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0));
       if (ok && n > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + 0), 0, p.status, 221, 0));
+        ok = wait_q(0);
+        if (ok) ok = wait_do(0);
         if (ok) {
           tc_fence_after();
           issue_st(0);
@@ -419,8 +451,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       }
       for (int it = 0; it < n && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t q_addr = q_stage(it), do_addr = q_addr + PL::TILE_BYTES;
+        const uint32_t q_addr = q_stage(it), do_addr = do_stage(it);
         // dV += P^T dY: A from TMEM (16 queries = 8 packed columns per step), B MN-major
         ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it));
         if (!ok) break;
@@ -429,8 +460,9 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_ts_if<false>(leader, tmem_u + C_DV, tmem_u + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(do_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit_if(leader, bar(KV_DO_EMPTY + it % PL::V_STAGES));   // dY(it) was last read by this product
         if (it + 1 < n) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_Q_FULL + ((it + 1) & 1)), (uint32_t)(((it + 1) >> 1) & 1), p.status, 221, it + 1));
+          ok = wait_q(it + 1);
           if (!ok) break;
           tc_fence_after();
           issue_st(it + 1);
@@ -443,9 +475,14 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_ts_if<false>(leader, tmem_u + C_DK, tmem_u + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
                   make_desc(q_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit_if(leader, bar(KV_Q_EMPTY + st));
+        umma_commit_if(leader, bar(KV_Q_EMPTY + it % PL::K_STAGES));
         umma_commit_if(leader, bar(KV_ACC_DONE));
-        if (it + 1 < n) issue_dpt(it + 1);
+        if (it + 1 < n) {
+          ok = wait_do(it + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dpt(it + 1);
+        }
       }
       umma_commit_if(leader, bar(KV_DRAIN));
       mbar_wait(bar(KV_DRAIN), 0, p.status, 227, 0);
@@ -461,8 +498,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // element-wise threads fetch one value each a step ahead and stage them in shared memory, so that the
     // inner loop reads them as broadcasts instead of 64 global loads per thread.  Rows beyond T get
     // lse = +inf, which makes their probabilities exactly zero.
-    __shared__ __align__(16) float s_nlse[2][BLK];
-    __shared__ __align__(16) float s_del[2][BLK];
+    float (*s_nlse)[BLK] = reinterpret_cast<float (*)[BLK]>(smem_gen + PL::OFF_STAGE_KV);
+    float (*s_del)[BLK] = s_nlse + 2;
     auto fetch = [&](int it) -> float {
       const int qi = (i_begin + it) * BLK + (tid & (BLK - 1));
       if (tid >= 2 * BLK || it >= n || qi >= T) return tid < BLK ? -INFINITY : 0.f;
@@ -599,12 +636,12 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
   p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
-  const size_t smem = BwdPlan<HD>::BYTES, smem_dq = BwdPlan<HD>::BYTES_DQ;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const size_t smem_kv = BwdPlan<HD>::BYTES_KV, smem_dq = BwdPlan<HD>::BYTES_DQ;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
   dim3 grid(mca_ceil_div(T, BLK), B * H);
   p.out0 = dk; p.out1 = dv;
-  sdpa_bwd_dkdv_tc_kernel<HD><<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+  sdpa_bwd_dkdv_tc_kernel<HD><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
   if ((e = mca_launch_status())) return e;
   p.out0 = dq; p.out1 = nullptr;
   sdpa_bwd_dq_tc_kernel<HD><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
