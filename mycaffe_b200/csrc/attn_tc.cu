@@ -507,8 +507,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
               *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
               // the same 16 bytes to every further destination: plain stores, over NVLink when it is a peer's buffer
-              for (int d = 0; d < p.n_more; ++d)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + y_off + c * 16 + i) = w;
+#pragma unroll
+              for (int d = 0; d < 7; ++d)   // constant indices: the parameter block is not copied to local memory
+                if (d < p.n_more) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + y_off + c * 16 + i) = w;
             }
           }
         }
