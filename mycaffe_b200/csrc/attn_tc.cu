@@ -30,6 +30,8 @@
 // thread records where it gave up in a status word and the CTA drains and exits.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -99,6 +101,7 @@ struct TcParams {
   float* lse;     // (B*H, T) or null: log2-domain log-sum-exp of the scaled logits
   int* status;
   int T, causal, H;
+  int group;         // (batch, head) pairs whose CTAs are interleaved longest-first (their K, V fit in L2 together)
   float scale_log2;  // (1/sqrt(HD)) * log2(e)
   McaStrides ys;     // element strides of the output view
   void* y_more[7];   // further destinations of the same bf16 output tile (peer GPUs' buffers), same strides
@@ -122,11 +125,18 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;
+  // Launch order -> work item.  Causal work per CTA grows with the query position, so CTAs are handed out
+  // longest first; to keep that order across heads without losing the L2 reuse of K and V, the heads are taken in
+  // groups of p.group whose K and V fit in L2 together, and inside a group the order is (work rank, head).
+  const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int grp = lin / (p.group * (int)gridDim.x);
+  const int in_grp = lin - grp * p.group * (int)gridDim.x;
+  const int grp_heads = min(p.group, (int)gridDim.y - grp * p.group);
+  const int rank = in_grp / grp_heads;
+  const int bh = grp * p.group + (in_grp - rank * grp_heads);
   const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
   const int T = p.T;
-  // longest causal work first
-  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int pair = (int)gridDim.x - 1 - rank;
   const int q0 = pair * (NQT * BLK);
   int n_tiles[NQT];
 #pragma unroll
@@ -545,6 +555,13 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   }
   TcParams p;
   p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal; p.H = H;
+  // K and V of one (batch, head) are 2 * T * HD elements; keep a group's set under about 64 MB of the 126 MB L2
+  {
+    const int64_t kv_bytes = (int64_t)2 * T * HD * (TF32 ? 4 : 2);
+    int64_t g = (64ll << 20) / kv_bytes;
+    p.group = (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)B * H));
+    if (!causal) p.group = 1;   // equal work per CTA: nothing to balance
+  }
   p.ys = y_strides ? *y_strides : mca_out_strides(layout, H, T, HD);
   p.n_more = n_more;
   for (int i = 0; i < 7; ++i) p.y_more[i] = i < n_more ? y_more[i] : nullptr;

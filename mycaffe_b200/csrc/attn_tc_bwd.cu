@@ -64,6 +64,7 @@ struct BwdParams {
   void* out1;          // dkdv kernel: dV
   int* status;
   int T, causal, H;
+  int group;           // (batch, head) pairs whose CTAs are interleaved longest-first (their tensors fit in L2 together)
   float scale_log2;    // (1/sqrt(HD)) * log2(e)
   float scale;         // 1/sqrt(HD)
   McaStrides os;       // element strides of the gradient views dQ, dK, dV
@@ -111,9 +112,15 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR_DQ + DQ_BAR_COUNT * 8);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y, T = p.T;
+  // launch order -> work item: longest causal work first inside groups of p.group heads (see the forward kernel)
+  const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int grp = lin / (p.group * (int)gridDim.x);
+  const int in_grp = lin - grp * p.group * (int)gridDim.x;
+  const int grp_heads = min(p.group, (int)gridDim.y - grp * p.group);
+  const int rank = in_grp / grp_heads;
+  const int bh = grp * p.group + (in_grp - rank * grp_heads), T = p.T;
   const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest causal work first
+  const int qt = (int)gridDim.x - 1 - rank;
   const int q0 = qt * BLK;
   const int n = p.causal ? (min(q0 + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
 
@@ -332,9 +339,15 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + PL::OFF_BAR_DQ + KV_BAR_COUNT * 8);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y, T = p.T;
+  // launch order -> work item: longest causal work first inside groups of p.group heads (see the forward kernel)
+  const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int grp = lin / (p.group * (int)gridDim.x);
+  const int in_grp = lin - grp * p.group * (int)gridDim.x;
+  const int grp_heads = min(p.group, (int)gridDim.y - grp * p.group);
+  const int rank = in_grp / grp_heads;
+  const int bh = grp * p.group + (in_grp - rank * grp_heads), T = p.T;
   const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
-  const int kt = blockIdx.x;            // key tile; tile 0 has the most causal work and comes first
+  const int kt = rank;                  // key tile; tile 0 has the most causal work and comes first
   const int k0 = kt * BLK;
   const int n_q_tiles = (T + BLK - 1) / BLK;
   const int i_begin = p.causal ? kt : 0;
@@ -633,6 +646,11 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
     return e;
   BwdParams p;
   p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal; p.H = H;
+  {
+    // Q, K, V, dY of one (batch, head): keep a group's set under about 64 MB of the 126 MB L2
+    const int64_t g = (64ll << 20) / ((int64_t)4 * T * HD * 2);
+    p.group = causal ? (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)B * H)) : 1;
+  }
   p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
