@@ -117,8 +117,8 @@ int mca_sdpa_forward_host(const void* q, const void* k, const void* v, void* y, 
   const char* hk = static_cast<const char*>(k);
   const char* hv = static_cast<const char*>(v);
   char* hy = static_cast<char*>(y);
-  int n = 0;
-  for (int64_t h0 = 0; h0 < BH && !e; h0 += chunk, ++n) {
+  // one chunk through the three streams; returns the first error (the caller still waits for what was issued)
+  auto run_chunk = [&](int n, int64_t h0) -> int {
     const int s = n % SLOTS;
     const int c = (int)(BH - h0 < chunk ? BH - h0 : chunk);
     const int64_t elems = (int64_t)c * head_elems;
@@ -126,34 +126,37 @@ int mca_sdpa_forward_host(const void* q, const void* k, const void* v, void* y, 
     // ---- inputs: the slot's Q/K/V are free once the kernel of chunk n-SLOTS has run
     if (n >= SLOTS) MCA_CUDA_TRY(cudaStreamWaitEvent(p.s_in, p.comp_done[s], 0));
     const char* src[3] = {hq + off, hk + off, hv + off};
-    for (int i = 0; i < 3 && !e; ++i) {
+    for (int i = 0; i < 3; ++i) {
       if (f32) {
         MCA_CUDA_TRY(cudaMemcpyAsync(p.f32[s][i], src[i], elems * 4, cudaMemcpyHostToDevice, p.s_in));
-        e = mca_convert_f32_to_bf16(p.f32[s][i], p.bf[s][i], elems, p.s_in);
+        const int ce = mca_convert_f32_to_bf16(p.f32[s][i], p.bf[s][i], elems, p.s_in);
+        if (ce) return ce;
       } else {
         MCA_CUDA_TRY(cudaMemcpyAsync(p.bf[s][i], src[i], elems * 2, cudaMemcpyHostToDevice, p.s_in));
       }
     }
-    if (e) break;
     MCA_CUDA_TRY(cudaEventRecord(p.in_done[s], p.s_in));
     // ---- kernel: needs the inputs, and the slot's Y must have left for the host (chunk n-SLOTS)
     MCA_CUDA_TRY(cudaStreamWaitEvent(p.s_comp, p.in_done[s], 0));
     if (n >= SLOTS) MCA_CUDA_TRY(cudaStreamWaitEvent(p.s_comp, p.out_done[s], 0));
-    e = mca_sdpa_forward_tc(p.bf[s][0], p.bf[s][1], p.bf[s][2], MCA_DTYPE_BF16, causal, 1, c, T, D, p.bf[s][3], nullptr,
-                            p.status, p.s_comp);
-    if (e) break;
+    const int ke = mca_sdpa_forward_tc(p.bf[s][0], p.bf[s][1], p.bf[s][2], MCA_DTYPE_BF16, causal, 1, c, T, D, p.bf[s][3],
+                                       nullptr, p.status, p.s_comp);
+    if (ke) return ke;
     MCA_CUDA_TRY(cudaEventRecord(p.comp_done[s], p.s_comp));
     // ---- output
     MCA_CUDA_TRY(cudaStreamWaitEvent(p.s_out, p.comp_done[s], 0));
     if (f32) {
-      e = mca_convert_bf16_to_f32(p.bf[s][3], p.f32[s][3], elems, p.s_out);
-      if (e) break;
+      const int ce = mca_convert_bf16_to_f32(p.bf[s][3], p.f32[s][3], elems, p.s_out);
+      if (ce) return ce;
       MCA_CUDA_TRY(cudaMemcpyAsync(hy + off, p.f32[s][3], elems * 4, cudaMemcpyDeviceToHost, p.s_out));
     } else {
       MCA_CUDA_TRY(cudaMemcpyAsync(hy + off, p.bf[s][3], elems * 2, cudaMemcpyDeviceToHost, p.s_out));
     }
     MCA_CUDA_TRY(cudaEventRecord(p.out_done[s], p.s_out));
-  }
+    return 0;
+  };
+  int n = 0;
+  for (int64_t h0 = 0; h0 < BH && !e; h0 += chunk, ++n) e = run_chunk(n, h0);
   // the call is synchronous: everything issued has finished (also after an error part-way)
   cudaError_t ce = cudaStreamSynchronize(p.s_in);
   cudaError_t c2 = cudaStreamSynchronize(p.s_comp);
