@@ -93,6 +93,26 @@ template <> struct Row16<__nv_bfloat16> {
   template <int G> static __device__ __forceinline__ int elem(int gl, int i) { return ((i >> 3) * G + gl) * 8 + (i & 7); }
 };
 
+// bf16 caches stream through a per-warp ring in shared memory filled by cp.async: a bf16 row is half the bytes of
+// an fp32 one, so twice the rows have to be outstanding to cover the HBM latency, and asynchronous copies keep them
+// in flight without holding them in registers.  Every lane copies exactly the 4 x 16 bytes it consumes itself
+// (two vectors of the K row, two of the V row), so no synchronisation other than its own wait_group is needed.
+constexpr int DEC_RING = 6;   // row steps in flight per warp (96 KB per CTA: two CTAs per SM overlap their ramps)
+constexpr size_t DEC_RING_BYTES = (size_t)DEC_WARPS * DEC_RING * 4 * 32 * sizeof(uint4);   // per CTA
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void unpack_bf16x8(const uint4& t, float* x) {
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
 // Load 16 elements of a float vector in the lane's element order, optionally rotating
 // adjacent pairs by the RoPE angle of this position (rope, llama2_cpu.cpp:239-262).
 template <typename CT, int G>
@@ -152,6 +172,84 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
   }
 
   const bool has_new = (p.k_new != nullptr);
+  if constexpr (sizeof(CT) == 2) {
+    // ---- bf16 cache: cp.async ring
+    extern __shared__ __align__(16) uint4 dec_ring[];
+    uint4* my_ring = dec_ring + (size_t)warp * DEC_RING * 4 * 32;          // [stage][vector][lane]
+    const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+    const __nv_bfloat16* kcb = reinterpret_cast<const __nv_bfloat16*>(kc);
+    const __nv_bfloat16* vcb = reinterpret_cast<const __nv_bfloat16*>(vc);
+    const int first = r_begin + warp * RPW;
+    const int stride = DEC_WARPS * RPW;
+    const int n_steps = first < r_end ? (r_end - first + stride - 1) / stride : 0;
+    auto issue = [&](int t) {
+      if (t < n_steps) {
+        const int row = first + t * stride + g;
+        if (row < r_end && !(has_new && row == pos)) {
+          const uint32_t dst = my_ring_s + (uint32_t)(((t % DEC_RING) * 4 * 32 + lane) * sizeof(uint4));
+          const uint4* ks = reinterpret_cast<const uint4*>(kcb + (int64_t)row * kv_dim);
+          const uint4* vs = reinterpret_cast<const uint4*>(vcb + (int64_t)row * kv_dim);
+          cp_async16(dst, ks + gl);
+          cp_async16(dst + 32 * sizeof(uint4), ks + G + gl);
+          cp_async16(dst + 64 * sizeof(uint4), vs + gl);
+          cp_async16(dst + 96 * sizeof(uint4), vs + G + gl);
+        }
+      }
+      cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
+    };
+#pragma unroll
+    for (int t = 0; t < DEC_RING - 1; ++t) issue(t);
+    for (int t = 0; t < n_steps; ++t) {
+      issue(t + DEC_RING - 1);     // its slot was read in the previous iteration
+      cp_async_wait<DEC_RING - 1>();
+      const int row = first + t * stride + g;
+      const bool valid = row < r_end;
+      float kx[EPL], vx[EPL];
+      if (valid && has_new && row == pos) {
+        // the new token: take k,v from the projections, rotate k, append both to the cache, and attend to what a
+        // later step will read back from the cache
+        load_vec_rope<CT, G>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx);
+        load_vec_rope<CT, G>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx);
+        if (h0 % p.kv_mul == 0) {
+          Row16<CT>::template store<G>(kc + (int64_t)row * kv_dim, gl, kx);
+          Row16<CT>::template store<G>(vc + (int64_t)row * kv_dim, gl, vx);
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          kx[i] = __bfloat162float(__float2bfloat16_rn(kx[i]));
+          vx[i] = __bfloat162float(__float2bfloat16_rn(vx[i]));
+        }
+      } else if (valid) {
+        const uint4* src = my_ring + (size_t)(t % DEC_RING) * 4 * 32 + lane;
+        unpack_bf16x8(src[0], kx);
+        unpack_bf16x8(src[32], kx + 8);
+        unpack_bf16x8(src[64], vx);
+        unpack_bf16x8(src[96], vx + 8);
+      } else {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) { kx[i] = 0.f; vx[i] = 0.f; }
+      }
+#pragma unroll
+      for (int x = 0; x < KVM; ++x) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) s = fmaf(q[x][i], kx[i], s);
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid) {
+          s = s / inv_div;  // score /= sqrtf(head_size), llama2_cpu.cpp:322
+          const float m_new = fmaxf(m[x], s);
+          const float corr = __expf(m[x] - m_new);
+          const float pw = __expf(s - m_new);
+          l[x] = l[x] * corr + pw;
+          m[x] = m_new;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[i], acc[x][i] * corr);
+        }
+      }
+    }
+    cp_async_wait<0>();
+  } else {
   for (int base = r_begin + warp * RPW; base < r_end; base += DEC_WARPS * RPW * U) {
     float kx[U][EPL], vx[U][EPL];
     bool valid[U];
@@ -202,6 +300,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
         }
       }
     }
+  }
+
   }
 
   // merge the lane groups of a warp, then the warps of the CTA
@@ -272,10 +372,16 @@ template <typename CT, int HS>
 int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
   const int kvmt = p.kv_mul >= 4 ? 4 : p.kv_mul;
   dim3 grid(p.nsplit, p.n_heads / kvmt, B);
+  const size_t smem = sizeof(CT) == 2 ? DEC_RING_BYTES : 0;   // the bf16 path's cp.async ring
+  if (smem) {
+    MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
   switch (kvmt) {
-    case 1: decode_split_kernel<CT, HS, 1><<<grid, DEC_THREADS, 0, st>>>(p); break;
-    case 2: decode_split_kernel<CT, HS, 2><<<grid, DEC_THREADS, 0, st>>>(p); break;
-    case 4: decode_split_kernel<CT, HS, 4><<<grid, DEC_THREADS, 0, st>>>(p); break;
+    case 1: decode_split_kernel<CT, HS, 1><<<grid, DEC_THREADS, smem, st>>>(p); break;
+    case 2: decode_split_kernel<CT, HS, 2><<<grid, DEC_THREADS, smem, st>>>(p); break;
+    case 4: decode_split_kernel<CT, HS, 4><<<grid, DEC_THREADS, smem, st>>>(p); break;
     default: return ERROR_ATTN_UNSUPPORTED_SHAPE;
   }
   int e = mca_launch_status();
