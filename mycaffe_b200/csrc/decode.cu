@@ -238,13 +238,17 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
         for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (valid) {
           s = s / inv_div;  // score /= sqrtf(head_size), llama2_cpu.cpp:322
-          const float m_new = fmaxf(m[x], s);
-          const float corr = __expf(m[x] - m_new);
-          const float pw = __expf(s - m_new);
-          l[x] = l[x] * corr + pw;
-          m[x] = m_new;
+          if (s > m[x]) {   // the running maximum moves (rare once it has settled): rescale what was accumulated
+            const float corr = __expf(m[x] - s);
+            l[x] *= corr;
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[i], acc[x][i] * corr);
+            for (int i = 0; i < EPL; ++i) acc[x][i] *= corr;
+            m[x] = s;
+          }
+          const float pw = __expf(s - m[x]);
+          l[x] += pw;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[i], acc[x][i]);
         }
       }
     }
@@ -290,13 +294,17 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
         for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (valid[u]) {
           s = s / inv_div;  // score /= sqrtf(head_size), llama2_cpu.cpp:322
-          const float m_new = fmaxf(m[x], s);
-          const float corr = __expf(m[x] - m_new);
-          const float pw = __expf(s - m_new);
-          l[x] = l[x] * corr + pw;
-          m[x] = m_new;
+          if (s > m[x]) {   // the running maximum moves (rare once it has settled): rescale what was accumulated
+            const float corr = __expf(m[x] - s);
+            l[x] *= corr;
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[u][i], acc[x][i] * corr);
+            for (int i = 0; i < EPL; ++i) acc[x][i] *= corr;
+            m[x] = s;
+          }
+          const float pw = __expf(s - m[x]);
+          l[x] += pw;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) acc[x][i] = fmaf(pw, vx[u][i], acc[x][i]);
         }
       }
     }
