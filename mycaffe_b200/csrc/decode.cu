@@ -408,9 +408,10 @@ int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_l
                     int64_t* scratch_floats) {
   if (B <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_len <= 0 || n_heads % n_kv_heads != 0)
     return ERROR_PARAM_OUT_OF_RANGE;
-  // Aim for a few waves of CTAs over 148 SMs x 2 resident CTAs, with at least 128 keys each.
+  // Aim for about two waves of CTAs over 148 SMs x 2 resident CTAs (short splits pay their set-up and the combine
+  // pass again; fewer waves leave ragged lengths unbalanced), with at least 128 keys each.
   const int64_t rows = (int64_t)B * n_kv_heads * max_len;
-  int64_t sl = rows / (148 * 2 * 4);
+  int64_t sl = rows / (148 * 2 * 2);
   sl = (sl + 127) / 128 * 128;
   if (sl < 128) sl = 128;
   if (sl > 1024) sl = 1024;
