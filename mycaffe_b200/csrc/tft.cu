@@ -16,6 +16,19 @@ namespace {
 constexpr int TFT_ROWS = 8;        // query rows per CTA, one per warp
 constexpr int TFT_THREADS = 256;
 
+// (Nk, d) tile -> shared memory rows of d + 4 floats with asynchronous 16-byte copies: all of a thread's copies are
+// in flight at once (a load-then-store loop serialises on the round trip of each one).
+__device__ __forceinline__ void tile_to_smem_async(float* dst, const float* __restrict__ src, int Nk, int d, int tid) {
+  const int d4 = d / 4, ld = d + 4;
+  for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS) {
+    const int j = idx / d4, c4 = idx - j * d4;
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + (size_t)j * ld + c4 * 4);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + (size_t)idx * 4) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tile_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -53,11 +66,8 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_fwd_kernel(const float* __res
 
   for (int h = 0; h < H; ++h) {
     __syncthreads();  // previous head's readers of KV are done; Qs/pm initialised
-    const float4* Kg = reinterpret_cast<const float4*>(K + ((int64_t)b * H + h) * Nk * d);
-    for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS) {
-      const int j = idx / d4, c4 = idx % d4;
-      *reinterpret_cast<float4*>(KV + (size_t)j * ld + c4 * 4) = __ldg(Kg + idx);
-    }
+    tile_to_smem_async(KV, K + ((int64_t)b * H + h) * Nk * d, Nk, d, tid);
+    tile_wait();
     __syncthreads();
     const float* qrow = Qs + ((size_t)h * TFT_ROWS + w) * d;
     float mx = -INFINITY;
@@ -88,13 +98,10 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_fwd_kernel(const float* __res
     for (int j = lane; j < Nk; j += 32) pm[w * Nk + j] += ps[w * Nk + j] * inv;  // running head sum (:255-260)
   }
   __syncthreads();
-  const float4* Vg = reinterpret_cast<const float4*>(V + (int64_t)b * Nk * d);
-  for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS) {
-    const int j = idx / d4, c4 = idx % d4;
-    *reinterpret_cast<float4*>(KV + (size_t)j * ld + c4 * 4) = __ldg(Vg + idx);
-  }
+  tile_to_smem_async(KV, V + (int64_t)b * Nk * d, Nk, d, tid);
   const float inv_h = 1.f / (float)H;
   for (int j = lane; j < Nk; j += 32) pm[w * Nk + j] *= inv_h;  // one scale by 1/H (:263)
+  tile_wait();
   __syncthreads();
   if (!row_ok) return;
   for (int j = lane; j < Nk; j += 32) attn[((int64_t)b * Nq + i) * Nk + j] = pm[w * Nk + j];
@@ -134,17 +141,14 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_bwd_kernel(const float* __res
   const int d4 = d / 4;
   const float inv_h = 1.f / (float)H;
 
-  const float4* Vg = reinterpret_cast<const float4*>(V + (int64_t)b * Nk * d);
-  for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS)
-    *reinterpret_cast<float4*>(Vs + (size_t)(idx / d4) * ld + (idx % d4) * 4) = __ldg(Vg + idx);
+  tile_to_smem_async(Vs, V + (int64_t)b * Nk * d, Nk, d, tid);
   for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dVs[idx] = 0.f;
 
   for (int h = 0; h < H; ++h) {
     __syncthreads();  // previous head's dKs written out, Ks readers done
-    const float4* Kg = reinterpret_cast<const float4*>(K + ((int64_t)b * H + h) * Nk * d);
-    for (int idx = tid; idx < Nk * d4; idx += TFT_THREADS)
-      *reinterpret_cast<float4*>(Ks + (size_t)(idx / d4) * ld + (idx % d4) * 4) = __ldg(Kg + idx);
+    tile_to_smem_async(Ks, K + ((int64_t)b * H + h) * Nk * d, Nk, d, tid);
     for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dKs[idx] = 0.f;
+    tile_wait();   // also covers the V tile requested before the loop
     for (int q0 = 0; q0 < Nq; q0 += TFT_ROWS) {
       __syncthreads();  // K tile loaded / previous step's accumulation done
       const int i = q0 + w;
