@@ -243,13 +243,65 @@ MCA_API int mca_decode_attention(const float* q, const float* k_new, const float
  * calls, and the Wo matmul + residual add, of TransformerGpu::forward,
  * CudaExtension.llm32.llama2/Files/llama2_gpu.cpp:56-61,78-81 (kernels primitives.cu:281-340).
  * Weights are (out, in) row-major as in the llama2 checkpoint (primitives.cu:322-332), fp32 or bf16;
- * x: (B, dim); dim must be a multiple of 256.
+ * x: (B, dim); dim must be a multiple of 8.
  *   q,k,v = [Wq;Wk;Wv] . (rms_weight o x / sqrt(mean(x^2) + eps));   x_inout += Wo . attn        */
 MCA_API int mca_decode_qkv_rmsnorm(const float* x, const float* rms_weight, float eps, const void* wq,
                                    const void* wk, const void* wv, int weights_bf16, int B, int dim, int kv_dim,
                                    float* q_out, float* k_out, float* v_out, void* stream);
 MCA_API int mca_decode_out_proj(const float* attn, const void* wo, int weights_bf16, int B, int dim, float* x_inout,
                                 void* stream);
+
+/* The feed-forward half of a llama2 layer for one new token of B sequences, in two launches.
+ * Replaces rmsnorm, two matmul (cublasSgemv), siglu, matmul and add of TransformerGpu::forward,
+ * llama2_gpu.cpp:84-97 (kernels primitives.cu:87-96,281-364); arithmetic as llama2_cpu.cpp:352-376:
+ *   xn = rms_weight o x / sqrt(mean(x^2) + eps);  h = silu(W1 xn) o (W3 xn);  x_inout += W2 h.
+ * w1, w3: (hidden_dim, dim); w2: (dim, hidden_dim); hidden_scratch: (B, hidden_dim) floats.
+ * dim and hidden_dim must be multiples of 8 and at most 51200. */
+MCA_API int mca_decode_ffn(const float* rms_weight, float eps, const void* w1, const void* w2, const void* w3,
+                           int weights_bf16, int B, int dim, int hidden_dim, float* hidden_scratch, float* x_inout,
+                           void* stream);
+/* Final RMSNorm + classifier: logits (B, vocab_size) = Wcls . (rms_weight o x / sqrt(mean(x^2) + eps)).
+ * Replaces llama2_gpu.cpp:101-105.  x is not modified (the reference normalises it in place). */
+MCA_API int mca_decode_logits(const float* x, const float* rms_weight, float eps, const void* wcls, int weights_bf16,
+                              int B, int dim, int vocab_size, float* logits, void* stream);
+
+/* One decode step of the whole transformer, token -> logits, for B independent sequences.
+ * Replaces TransformerGpu::forward(token, pos), llama2_gpu.cpp:32-111 (one sequence, about 16
+ * launches per layer with host synchronisations) by 5-6 launches per layer on `stream` with no host
+ * round trip; the call only enqueues work and may be captured into a CUDA graph.
+ * McaLlamaConfig is the reference's Config (llama2_cpu.h:17-25).  Weights are laid out as the
+ * checkpoint is (memory_map_weights, llama2_cpu.cpp:79-103): per-layer matrices stacked as
+ * (n_layers, out, in); the matrices and wcls are fp32 or bf16 (weights_bf16), the embedding table
+ * and the three norm weights fp32.  Caches are (n_layers, B, seq_len, kv_dim), fp32 or bf16;
+ * freq_real/imag (seq_len, head_size/2) as mca_rope_tables_host builds them.  tokens, pos: device
+ * int32 (B); row pos[b] of every layer's cache is written; max_len >= max_b pos[b] + 1.
+ * workspace: mca_llama_workspace_floats(cfg, B, max_len) floats, 16-byte aligned (returns -1 for a
+ * bad configuration).  head_size must be 64 or 128. */
+typedef struct McaLlamaConfig {
+  int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+} McaLlamaConfig;
+typedef struct McaLlamaWeights {
+  const float* token_embedding_table; /* (vocab_size, dim) */
+  const float* rms_att_weight;        /* (n_layers, dim) */
+  const float* rms_ffn_weight;        /* (n_layers, dim) */
+  const float* rms_final_weight;      /* (dim) */
+  const void *wq, *wk, *wv, *wo;      /* (n_layers, dim|kv_dim, dim), wo (n_layers, dim, dim) */
+  const void *w1, *w2, *w3;           /* (n_layers, hidden_dim, dim), (n_layers, dim, hidden_dim), as w1 */
+  const void* wcls;                   /* (vocab_size, dim) */
+  int weights_bf16;
+} McaLlamaWeights;
+typedef struct McaLlamaState {
+  void* key_cache;
+  void* value_cache;
+  int cache_is_bf16;
+  const float* freq_real;
+  const float* freq_imag;
+  float* workspace;
+  int64_t workspace_floats;
+} McaLlamaState;
+MCA_API int64_t mca_llama_workspace_floats(const McaLlamaConfig* cfg, int B, int max_len);
+MCA_API int mca_llama_forward(const McaLlamaConfig* cfg, const McaLlamaWeights* weights, const McaLlamaState* state,
+                              const int* tokens, const int* pos, int B, int max_len, float* logits, void* stream);
 
 /* Decode attention for callers that must not allocate device memory.  No counterpart in the
  * reference.  Some hosts cannot call cudaMalloc at the point where they decode -- a plug-in that is

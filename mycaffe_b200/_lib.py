@@ -50,6 +50,10 @@ SIGNATURES = {
                                   _vp, _vp]),
     "mca_decode_qkv_rmsnorm": (_i, [_vp, _vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_decode_out_proj": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "mca_decode_ffn": (_i, [_vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "mca_decode_logits": (_i, [_vp, _vp, C.c_float, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "mca_llama_workspace_floats": (_i64, [_vp, _i, _i]),
+    "mca_llama_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "mca_decode_static_scratch_floats": (_i64, []),
     "mca_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_tft_attention_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),

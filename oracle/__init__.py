@@ -228,6 +228,35 @@ def llama_decode(q, k, v, key_cache, value_cache, pos, n_heads, n_kv_heads, thet
     return (out, q, k, att) if want_att else out
 
 
+def llama_forward(cfg, w, key_cache, value_cache, tokens, pos):
+    """One whole-transformer decode step, token -> logits, for B independent sequences: the
+    order of operations of TransformerCpu::forward (llama2_cpu.cpp:264-386) restated over the
+    pieces above.  ``cfg`` has the reference's Config fields; ``w`` the checkpoint's arrays;
+    caches (n_layers, B, seq_len, kv_dim) float32 are updated in place.  Unlike the compiled
+    reference this also runs n_kv_heads < n_heads (its rope walks n_heads heads of the kv_dim-long
+    k vector, llama2_cpu.cpp:243-246,293, which overruns the buffer)."""
+    dim, L = cfg["dim"], cfg["n_layers"]
+    tokens, pos = np.asarray(tokens).reshape(-1), _c(np.asarray(pos).reshape(-1), np.int32)
+    B = tokens.size
+    x = np.stack([_c(w["token_embedding_table"][int(t)]) for t in tokens]).copy()
+    for l in range(L):
+        q = np.empty((B, dim), np.float32)
+        kv_dim = w["wk"].shape[1]
+        k, v = np.empty((B, kv_dim), np.float32), np.empty((B, kv_dim), np.float32)
+        for b in range(B):
+            xb = rmsnorm(x[b], w["rms_att_weight"][l])
+            q[b], k[b], v[b] = gemv(w["wq"][l], xb), gemv(w["wk"][l], xb), gemv(w["wv"][l], xb)
+        att = llama_decode(q, k, v, key_cache[l], value_cache[l], pos, cfg["n_heads"], cfg["n_kv_heads"])
+        for b in range(B):
+            x[b] = x[b] + gemv(w["wo"][l], att[b])
+            xb = rmsnorm(x[b], w["rms_ffn_weight"][l])
+            hb, hb2 = gemv(w["w1"][l], xb), gemv(w["w3"][l], xb)
+            hb = hb * (np.float32(1.0) / (np.float32(1.0) + np.exp(-hb))) * hb2
+            x[b] = x[b] + gemv(w["w2"][l], hb)
+    wcls = w.get("wcls", w["token_embedding_table"])
+    return np.stack([gemv(wcls, rmsnorm(x[b], w["rms_final_weight"])) for b in range(B)])
+
+
 def write_llama_checkpoint(path, dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len, weights):
     """Write a llama2.c 'ak42' version-1 checkpoint (read_checkpoint, llama2_cpu.cpp:108-159;
     weight order memory_map_weights :79-103).  ``weights`` maps names to float32 arrays."""

@@ -204,3 +204,31 @@ def test_decode_gqa_matches_expanded_heads():
     out = oracle.llama_decode(q, k, v, kc.copy(), vc.copy(), pos, n_heads, n_kv)
     out_full = oracle.llama_decode(q, rep(k), rep(v), rep(kc), rep(vc), pos, n_heads, n_heads)
     np.testing.assert_array_equal(out, out_full)
+
+
+@pytest.mark.skipif(oracle.ref_lib() is None, reason="compiled reference twin not built")
+def test_whole_step_restatement_matches_compiled_reference(tmp_path):
+    """oracle.llama_forward (attention + feed-forward + classifier over several layers) against the
+    logits of the reference's TransformerCpu::forward (llama2_cpu.cpp:264-386), token by token."""
+    dim, hidden, n_layers, n_heads, vocab, seq_len = 64, 88, 3, 4, 32, 12
+    rng = np.random.default_rng(3)
+    g = lambda *s: (0.15 * rng.standard_normal(s)).astype(np.float32)
+    w = {"rms_att_weight": 1 + g(n_layers, dim), "rms_ffn_weight": 1 + g(n_layers, dim), "rms_final_weight": 1 + g(dim),
+         "token_embedding_table": rng.standard_normal((vocab, dim)).astype(np.float32),
+         "wq": g(n_layers, dim, dim), "wk": g(n_layers, dim, dim), "wv": g(n_layers, dim, dim), "wo": g(n_layers, dim, dim),
+         "w1": g(n_layers, hidden, dim), "w2": g(n_layers, dim, hidden), "w3": g(n_layers, hidden, dim)}
+    path = tmp_path / "m.bin"
+    oracle.write_llama_checkpoint(path, dim, hidden, n_layers, n_heads, n_heads, vocab, seq_len, w)
+    ref = oracle.RefLlama(path)
+    cfg = dict(dim=dim, hidden_dim=hidden, n_layers=n_layers, n_heads=n_heads, n_kv_heads=n_heads, vocab_size=vocab,
+               seq_len=seq_len)
+    kc = np.zeros((n_layers, 1, seq_len, dim), np.float32)
+    vc = np.zeros((n_layers, 1, seq_len, dim), np.float32)
+    tokens = rng.integers(0, vocab, seq_len)
+    for pos in range(seq_len):
+        ref.forward(int(tokens[pos]), pos)
+        logits = oracle.llama_forward(cfg, w, kc, vc, [tokens[pos]], [pos])
+        # same operations in the same order; the SwiGLU exp may differ in the last bit between numpy and libm
+        np.testing.assert_allclose(logits[0], ref.state("logits"), rtol=0, atol=2e-6 * np.abs(ref.state("logits")).max())
+    np.testing.assert_allclose(kc.ravel(), ref.state("key_cache"), rtol=0, atol=5e-6)
+    ref.close()
