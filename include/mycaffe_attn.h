@@ -256,7 +256,8 @@ MCA_API int mca_decode_out_proj(const float* attn, const void* wo, int weights_b
  * llama2_gpu.cpp:84-97 (kernels primitives.cu:87-96,281-364); arithmetic as llama2_cpu.cpp:352-376:
  *   xn = rms_weight o x / sqrt(mean(x^2) + eps);  h = silu(W1 xn) o (W3 xn);  x_inout += W2 h.
  * w1, w3: (hidden_dim, dim); w2: (dim, hidden_dim); hidden_scratch: (B, hidden_dim) floats.
- * dim and hidden_dim must be multiples of 8 and at most 51200. */
+ * dim and hidden_dim must be multiples of 8 and at most 45568 (one sequence's activations are staged
+ * in shared memory). */
 MCA_API int mca_decode_ffn(const float* rms_weight, float eps, const void* w1, const void* w2, const void* w3,
                            int weights_bf16, int B, int dim, int hidden_dim, float* hidden_scratch, float* x_inout,
                            void* stream);

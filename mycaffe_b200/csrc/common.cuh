@@ -75,3 +75,27 @@ static inline int mca_launch_status() {
 }
 
 __host__ __device__ static inline int mca_ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch.  A kernel launched with mca_launch_pdl may start while the
+// previous kernel of the stream is still running (once every CTA of that kernel has executed
+// mca_pdl_launch_dependents or exited); what it does before mca_pdl_wait() must depend on nothing
+// the previous kernels write and must write nothing they read.  mca_pdl_wait() returns when all
+// earlier kernels of the stream have completed and their writes are visible; in a kernel that was
+// launched the ordinary way both calls do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void mca_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mca_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int mca_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+  if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+  return mca_launch_status();
+}
+#endif

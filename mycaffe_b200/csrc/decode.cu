@@ -140,6 +140,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
   __shared__ float s_acc[DEC_WARPS][KVM][HS];
   __shared__ float s_ml[DEC_WARPS][KVM][2];
 
+  mca_pdl_launch_dependents();   // a projection kernel that follows may start fetching its weights
   const int b = blockIdx.z;
   const int h0 = blockIdx.y * KVM;          // first query head of this CTA
   const int kvh = h0 / p.kv_mul;
@@ -362,6 +363,7 @@ __global__ void __launch_bounds__(HS) decode_combine_kernel(const float* __restr
                                                             const float* __restrict__ part_ml,
                                                             const int* __restrict__ pos, int n_heads, int nsplit,
                                                             int split_len, float* __restrict__ out) {
+  mca_pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, e = threadIdx.x;
   const int n_valid = min(nsplit, (pos[b] + split_len) / split_len);  // ceil((pos+1)/split_len)
   const int64_t slot0 = ((int64_t)b * n_heads + h) * nsplit;

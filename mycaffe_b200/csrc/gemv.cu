@@ -12,34 +12,44 @@
 // matmul :224-237): o[j] = w[j] * (s * x[j]) with s = 1/sqrt(sum(x²)/n + eps).
 //
 // These are GEMVs: the weights (dim x dim floats, 67 MB at dim 4096) are read exactly once and
-// nothing else matters, so the kernel is bound by HBM bandwidth.  Every CTA first builds the
-// normalised activation in shared memory (it is 16 KB per sequence and comes from L2), then
-// its warps walk their rows of the stacked [Wq; Wk; Wv] matrix with 128-bit loads, 512
-// contiguous bytes per warp instruction, and reduce with shuffles.  Every warp owns the same number
-// of consecutive rows and requests its first weight vectors before the activations are staged, so
-// HBM is busy from the first cycle.  Up to 8 sequences share one pass over the weights (then two
-// rows at a time per warp share the activation reads); larger batches take several passes.
+// nothing else matters, so the kernel is bound by HBM bandwidth and is built around keeping
+// enough weight bytes in flight.  Every warp streams its part of the matrix through a ring in
+// shared memory filled by cp.async: each lane copies the 16-byte vectors it will itself consume,
+// DEPTH-1 steps ahead, so no synchronisation other than its own wait_group is needed and the
+// bytes in flight do not depend on registers or occupancy.  The first steps of the ring leave
+// for HBM before the CTA stages (and RMS-normalises) the activations in shared memory.
+// Rows are dealt to groups of S warps of one CTA in contiguous, balanced ranges; with S > 1 (few,
+// long rows, as Wo and W2 have) the warps of a group split every row along K and their partial
+// sums are added in a fixed order through shared memory, so results do not depend on timing.
+// Up to 8 sequences share one pass over the weights (then two rows at a time per warp share the
+// activation reads); larger batches take several passes.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "kernels.h"
 
 namespace {
 
-constexpr int GV_BMAX = 8;   // sequences per pass over the weights
+constexpr int GV_SPLIT_STEPS = 16;   // row steps a K-split group may own (their sums wait in registers)
+constexpr size_t GV_SMEM_LIMIT = 226 * 1024;
+
+__device__ __forceinline__ void gv_cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gv_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void gv_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename WT> struct WLoad;
 template <> struct WLoad<float> {
   static constexpr int VEC = 4;
-  using Raw = float4;
-  static __device__ __forceinline__ Raw raw(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
-  static __device__ __forceinline__ void unpack(const Raw& t, float (&w)[4]) { w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w; }
+  static __device__ __forceinline__ void unpack(const uint4& t, float (&w)[4]) {
+    w[0] = __uint_as_float(t.x); w[1] = __uint_as_float(t.y); w[2] = __uint_as_float(t.z); w[3] = __uint_as_float(t.w);
+  }
 };
 template <> struct WLoad<__nv_bfloat16> {
   static constexpr int VEC = 8;
-  using Raw = uint4;
-  static __device__ __forceinline__ Raw raw(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
-  static __device__ __forceinline__ void unpack(const Raw& t, float (&w)[8]) {
+  static __device__ __forceinline__ void unpack(const uint4& t, float (&w)[8]) {
     const uint32_t u[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) { w[2 * i] = __uint_as_float(u[i] << 16); w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
@@ -54,29 +64,42 @@ struct GemvParams {
   int rows[3];
   int n_mats, B, n, accumulate;  // accumulate: out += result (residual connection)
   int swiglu;                    // out[0][r] = silu(w[0] row r . x) * (w[1] row r . x); rows[1] == rows[0]
-  int rows_per_warp;             // consecutive rows owned by one warp (a multiple of R)
+  int split;                     // S: warps of a CTA that share a row along K (1, 2, 4 or 8)
   float eps;
 };
 
-// NB sequences per pass, R rows at a time per warp (they share the activation reads from shared
-// memory), THREADS per CTA.  A warp owns rows_per_warp consecutive rows of the stacked matrix, so
-// that all warps of the grid have the same amount of weight bytes to stream.
-// GLU: the two "rows at a time" are row r of w[0] and row r of w[1], combined by SwiGLU (R must be 2).
-template <typename WT, int NB, int R, int THREADS, bool GLU>
-__global__ void __launch_bounds__(THREADS) gemv_fused_kernel(const GemvParams p, int b0) {
+// NB sequences per pass, R weight rows per step per warp (they share the activation reads from
+// shared memory), THREADS per CTA, DEPTH ring steps per warp, each of U warp-wide vectors per row.  GLU: the two rows of a step are
+// row r of w[0] and row r of w[1], combined by SwiGLU (R must be 2); otherwise they are
+// consecutive rows of the stacked matrix.
+template <typename WT, int NB, int R, int THREADS, bool GLU, int DEPTH, int U>
+__global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const GemvParams p, int b0) {
   static_assert(!GLU || R == 2, "the gated form pairs one row of each matrix");
-  constexpr int STEP = GLU ? 1 : R;   // output rows finished per iteration
+  constexpr int STEP = GLU ? 1 : R;   // output rows finished per step
   constexpr int WARPS = THREADS / 32;
   constexpr int VEC = WLoad<WT>::VEC;
-  constexpr int PRE = NB <= 2 ? 8 : 2;         // weight vectors per row requested before the activations are staged
-  extern __shared__ __align__(16) float xs[];  // [NB][n] normalised activations
+  extern __shared__ __align__(16) unsigned char gv_smem[];
   __shared__ float red[WARPS][NB];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = p.n;
+  float* xs = reinterpret_cast<float*>(gv_smem);                                    // [NB][n] activations
+  uint4* ring = reinterpret_cast<uint4*>(gv_smem + sizeof(float) * (size_t)NB * n); // [WARPS][DEPTH][R][U][32]
+  uint4* my_ring = ring + (size_t)warp * DEPTH * R * U * 32;
+  const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+
   const int total_rows = GLU ? p.rows[0] : p.rows[0] + (p.n_mats > 1 ? p.rows[1] : 0) + (p.n_mats > 2 ? p.rows[2] : 0);
-  const int row_lo = (blockIdx.x * WARPS + warp) * p.rows_per_warp;
-  const int row_hi = min(row_lo + p.rows_per_warp, total_rows);
-  // operand q of the iteration that starts at output row r: which matrix, which of its rows
+  const int total_steps = (total_rows + STEP - 1) / STEP;
+  const int S = p.split;
+  const int groups = gridDim.x * (WARPS / S);
+  auto group_begin = [&](int g) { return (int)(((int64_t)g * total_steps) / groups); };
+  const int gid = blockIdx.x * (WARPS / S) + warp / S;
+  const int step_lo = group_begin(gid);
+  const int n_steps = group_begin(gid + 1) - step_lo;
+  const int chunks = (n + 32 * VEC * U - 1) / (32 * VEC * U);    // ring steps per row
+  const int seg = warp % S;
+  const int c_lo = (seg * chunks) / S, c_hi = ((seg + 1) * chunks) / S;   // this warp's part of every row
+
+  // operand q of the step that starts at output row r: which matrix, which of its rows
   auto row_ptr = [&](int r, int q, int& m, int& rr) -> const WT* {
     if (GLU) {
       m = q; rr = min(r, total_rows - 1);
@@ -87,20 +110,37 @@ __global__ void __launch_bounds__(THREADS) gemv_fused_kernel(const GemvParams p,
     const void* base = m == 0 ? p.w[0] : (m == 1 ? p.w[1] : p.w[2]);  // no dynamic indexing of the parameter block
     return reinterpret_cast<const WT*>(base) + (int64_t)rr * n;
   };
-  // ---- the first weight vectors of this warp's first rows leave for HBM before anything else
-  typename WLoad<WT>::Raw pre[R][PRE];
-  {
+  // ---- producer side of the ring
+  const WT* i_ptr[R];
+  int i_step = 0, i_c = c_lo, i_slot = 0;
+  auto set_issue_rows = [&]() {
 #pragma unroll
-    for (int q = 0; q < R; ++q) {
-      int m, rr;
-      const WT* wrow = row_ptr(row_lo, q, m, rr);
+    for (int q = 0; q < R; ++q) { int m, rr; i_ptr[q] = row_ptr((step_lo + i_step) * STEP, q, m, rr); }
+  };
+  set_issue_rows();
+  auto issue = [&]() {
+    if (i_step < n_steps && c_lo < c_hi) {
 #pragma unroll
-      for (int u = 0; u < PRE; ++u) {
-        const int k = (lane + 32 * u) * VEC;
-        pre[q][u] = WLoad<WT>::raw(wrow + (k < n ? k : 0));
+      for (int u = 0; u < U; ++u) {
+        const int k = ((i_c * U + u) * 32 + lane) * VEC;
+        if (k < n) {
+#pragma unroll
+          for (int q = 0; q < R; ++q)
+            gv_cp_async16(my_ring_s + (uint32_t)((((i_slot * R + q) * U + u) * 32 + lane) * sizeof(uint4)), i_ptr[q] + k);
+        }
       }
+      if (++i_c == c_hi) { i_c = c_lo; ++i_step; set_issue_rows(); }
     }
-  }
+    gv_cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
+    i_slot = (i_slot + 1 == DEPTH) ? 0 : i_slot + 1;
+  };
+  // The first weight vectors leave for HBM before anything else -- also before the kernel that
+  // produces the activations has finished (programmatic dependent launch): weights depend on nothing.
+  mca_pdl_launch_dependents();
+#pragma unroll
+  for (int t = 0; t < DEPTH - 1; ++t) issue();
+  mca_pdl_wait();   // from here on the previous kernel's results are complete and visible
+
   // ---- phase 1: activations of this pass's sequences -> shared memory, RMS-normalised
   float ss[NB];
 #pragma unroll
@@ -141,132 +181,190 @@ __global__ void __launch_bounds__(THREADS) gemv_fused_kernel(const GemvParams p,
     }
   }
   __syncthreads();
-  // ---- phase 2: this warp's rows, R at a time
-  for (int r = row_lo; r < row_hi; r += STEP) {
-    const WT* wrow[R];
-    int mat[R], rin[R];
-#pragma unroll
-    for (int q = 0; q < R; ++q) wrow[q] = row_ptr(r, q, mat[q], rin[q]);
-    float acc[R][NB];
-#pragma unroll
-    for (int q = 0; q < R; ++q)
-#pragma unroll
-      for (int b = 0; b < NB; ++b) acc[q][b] = 0.f;
-    auto fma_vec = [&](const typename WLoad<WT>::Raw& raw, int q, int k) {
-      float w[VEC];
-      WLoad<WT>::unpack(raw, w);
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        const float* xv = xs + b * n + k;
-#pragma unroll
-        for (int i = 0; i < VEC; i += 4) {
-          const float4 t = *reinterpret_cast<const float4*>(xv + i);
-          acc[q][b] = fmaf(w[i], t.x, acc[q][b]); acc[q][b] = fmaf(w[i + 1], t.y, acc[q][b]);
-          acc[q][b] = fmaf(w[i + 2], t.z, acc[q][b]); acc[q][b] = fmaf(w[i + 3], t.w, acc[q][b]);
-        }
-      }
-    };
-    int k_start = lane * VEC;
-    if (r == row_lo) {  // the vectors requested before phase 1
-#pragma unroll
-      for (int u = 0; u < PRE; ++u) {
-        const int k = (lane + 32 * u) * VEC;
-        if (k < n) {
-#pragma unroll
-          for (int q = 0; q < R; ++q) fma_vec(pre[q][u], q, k);
-        }
-      }
-      k_start = (lane + 32 * PRE) * VEC;
-    }
-#pragma unroll(NB <= 2 ? 8 : 2)
-    for (int k = k_start; k < n; k += 32 * VEC) {
-      typename WLoad<WT>::Raw raw[R];
-#pragma unroll
-      for (int q = 0; q < R; ++q) raw[q] = WLoad<WT>::raw(wrow[q] + k);
-#pragma unroll
-      for (int q = 0; q < R; ++q) fma_vec(raw[q], q, k);
-    }
-#pragma unroll
-    for (int q = 0; q < R; ++q)
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[q][b] += __shfl_xor_sync(0xffffffffu, acc[q][b], o);
-      }
+
+  // finished sums of output step `step` (values of rows r .. r+R-1, or the gate pair) -> memory
+  auto emit = [&](int step, const float (&v)[R][NB]) {
+    const int r = step * STEP;
     if (GLU) {
-      if (lane == 0) {
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          // val = hb * (1 / (1 + exp(-hb))) * hb2, llama2_cpu.cpp:359-367
-          float val = acc[0][b];
-          val *= (1.0f / (1.0f + expf(-val)));
-          val *= acc[R - 1][b];
-          p.out[0][(int64_t)(b0 + b) * p.rows[0] + r] = val;
-        }
+      for (int b = 0; b < NB; ++b) {
+        // val = hb * (1 / (1 + exp(-hb))) * hb2, llama2_cpu.cpp:359-367
+        float val = v[0][b];
+        val *= (1.0f / (1.0f + expf(-val)));
+        val *= v[R - 1][b];
+        p.out[0][(int64_t)(b0 + b) * p.rows[0] + r] = val;
       }
-    } else if (lane == 0) {
+    } else {
 #pragma unroll
       for (int q = 0; q < R; ++q) {
-        if (r + q >= row_hi) continue;
+        if (r + q >= total_rows) continue;
+        int m, rr;
+        row_ptr(r, q, m, rr);
+        float* ob = m == 0 ? p.out[0] : (m == 1 ? p.out[1] : p.out[2]);
+        const int orows = m == 0 ? p.rows[0] : (m == 1 ? p.rows[1] : p.rows[2]);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          float* ob = mat[q] == 0 ? p.out[0] : (mat[q] == 1 ? p.out[1] : p.out[2]);
-          const int orows = mat[q] == 0 ? p.rows[0] : (mat[q] == 1 ? p.rows[1] : p.rows[2]);
-          float* dst = ob + (int64_t)(b0 + b) * orows + rin[q];
-          *dst = p.accumulate ? (*dst + acc[q][b]) : acc[q][b];
+          float* dst = ob + (int64_t)(b0 + b) * orows + rr;
+          *dst = p.accumulate ? (*dst + v[q][b]) : v[q][b];
         }
       }
     }
+  };
+
+  // ---- phase 2: consume the ring
+  float acc[R][NB], keep[R][NB];
+#pragma unroll
+  for (int q = 0; q < R; ++q)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) { acc[q][b] = 0.f; keep[q][b] = 0.f; }
+  const int T = (c_lo < c_hi) ? n_steps * (c_hi - c_lo) : 0;
+  int c = c_lo, step = 0, slot = 0;
+  for (int t = 0; t < T; ++t) {
+    issue();
+    gv_cp_async_wait<DEPTH - 1>();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+    const int k = ((c * U + u) * 32 + lane) * VEC;
+    if (k < n) {
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        const uint4 raw = my_ring[((slot * R + q) * U + u) * 32 + lane];
+        float w[VEC];
+        WLoad<WT>::unpack(raw, w);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const float* xv = xs + b * n + k;
+#pragma unroll
+          for (int i = 0; i < VEC; i += 4) {
+            const float4 xx = *reinterpret_cast<const float4*>(xv + i);
+            acc[q][b] = fmaf(w[i], xx.x, acc[q][b]); acc[q][b] = fmaf(w[i + 1], xx.y, acc[q][b]);
+            acc[q][b] = fmaf(w[i + 2], xx.z, acc[q][b]); acc[q][b] = fmaf(w[i + 3], xx.w, acc[q][b]);
+          }
+        }
+      }
+    }
+    }
+    slot = (slot + 1 == DEPTH) ? 0 : slot + 1;
+    if (++c == c_hi) {   // this warp's part of the step is complete
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) acc[q][b] += __shfl_xor_sync(0xffffffffu, acc[q][b], o);
+        }
+      if (S == 1) {
+        if (lane == 0) emit(step_lo + step, acc);
+      } else if (lane == step) {   // lane i keeps the sums of the group's step i until the group adds them
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) keep[q][b] = acc[q][b];
+      }
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[q][b] = 0.f;
+      c = c_lo; ++step;
+    }
+  }
+  gv_cp_async_wait<0>();
+  if (S == 1) return;   // uniform over the CTA
+
+  // ---- K-split groups: partial sums -> this warp's (now idle) ring -> added in warp order
+  float* my_part = reinterpret_cast<float*>(my_ring);   // [GV_SPLIT_STEPS][R][NB]
+  if (lane < n_steps && lane < GV_SPLIT_STEPS) {
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) my_part[(lane * R + q) * NB + b] = keep[q][b];
+  }
+  __syncthreads();
+  if (seg == 0 && lane < n_steps && lane < GV_SPLIT_STEPS) {
+    float v[R][NB];
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) v[q][b] = 0.f;
+    for (int s2 = 0; s2 < S; ++s2) {
+      const float* part = reinterpret_cast<const float*>(ring + (size_t)(warp + s2) * DEPTH * R * U * 32);
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) v[q][b] += part[(lane * R + q) * NB + b];
+    }
+    emit(step_lo + lane, v);
   }
 }
 
-template <typename WT, int NB, int R, int THREADS, bool GLU = false>
+template <int R, int THREADS, int DEPTH, int U = 1>
+constexpr size_t ring_bytes() { return (size_t)(THREADS / 32) * DEPTH * R * U * 32 * sizeof(uint4); }
+
+template <typename WT, int NB, int R, int THREADS, bool GLU, int DEPTH, int U = 1>
 int launch_pass(GemvParams p, int b0, cudaStream_t st) {
   constexpr int STEP = GLU ? 1 : R;
   constexpr int WARPS = THREADS / 32;
-  const size_t smem = sizeof(float) * (size_t)NB * p.n;
-  if (smem > 200 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(gemv_fused_kernel<WT, NB, R, THREADS, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  static_assert(ring_bytes<R, THREADS, DEPTH, U>() / WARPS >= sizeof(float) * GV_SPLIT_STEPS * R * NB, "partials fit the ring");
+  const size_t smem = sizeof(float) * (size_t)NB * p.n + ring_bytes<R, THREADS, DEPTH, U>();
+  if (smem > GV_SMEM_LIMIT) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  auto kern = gemv_stream_kernel<WT, NB, R, THREADS, GLU, DEPTH, U>;
   const int total_rows = GLU ? p.rows[0] : p.rows[0] + (p.n_mats > 1 ? p.rows[1] : 0) + (p.n_mats > 2 ? p.rows[2] : 0);
-  // as many warps as fit on the 148 SMs at once, every one of them with the same number of rows
+  const int total_steps = mca_ceil_div(total_rows, STEP);
+  // every CTA resident at once; rows dealt evenly to groups of S warps.  The attribute and the
+  // occupancy of this instantiation are looked up once per (device, shared-memory size).
   int ctas_per_sm = 1, dev = 0, sms = 148;
-  MCA_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_fused_kernel<WT, NB, R, THREADS, GLU>, THREADS, smem));
   MCA_CUDA_TRY(cudaGetDevice(&dev));
-  MCA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int max_warps = sms * std::max(1, ctas_per_sm) * WARPS;
-  int rpw = mca_ceil_div(total_rows, max_warps);
-  rpw = mca_ceil_div(rpw, STEP) * STEP;
-  p.rows_per_warp = rpw;
-  const int grid = mca_ceil_div(total_rows, rpw * WARPS);
-  gemv_fused_kernel<WT, NB, R, THREADS, GLU><<<grid, THREADS, smem, st>>>(p, b0);
-  return mca_launch_status();
+  {
+    static std::mutex lock;
+    static int c_dev = -1, c_ctas = 0, c_sms = 0;
+    static size_t c_smem = 0;
+    std::lock_guard<std::mutex> g(lock);
+    if (c_dev != dev || c_smem != smem) {
+      MCA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      MCA_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&c_ctas, kern, THREADS, smem));
+      MCA_CUDA_TRY(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
+      c_dev = dev; c_smem = smem;
+    }
+    ctas_per_sm = c_ctas; sms = c_sms;
+  }
+  int grid = sms * std::max(1, ctas_per_sm);
+  int S = 1;
+  while (S < WARPS && total_steps / (grid * WARPS / S) < 8) S *= 2;
+  if (S > 1 && mca_ceil_div(total_steps, grid * WARPS / S) > GV_SPLIT_STEPS) S = 1;   // cannot happen by construction
+  if (grid * (WARPS / S) > total_steps) grid = mca_ceil_div(total_steps, WARPS / S);
+  p.split = S;
+  return mca_launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, p, b0);
 }
 
 template <typename WT>
 int run_gemv(const GemvParams& p, cudaStream_t st) {
   int e = 0;
-  if (p.swiglu) {
-    for (int b0 = 0; b0 < p.B && !e;) {
-      const int left = p.B - b0;
-      if (left >= 8 && (size_t)8 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 8, 2, 512, true>(p, b0, st); b0 += 8; }
-      else if (left >= 4 && (size_t)4 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 4, 2, 512, true>(p, b0, st); b0 += 4; }
-      else if (left >= 2) { e = launch_pass<WT, 2, 2, 256, true>(p, b0, st); b0 += 2; }
-      else { e = launch_pass<WT, 1, 2, 256, true>(p, b0, st); b0 += 1; }
-    }
-    return e;
-  }
-  // two rows at a time need the stacked matrices to start on even rows
-  const bool even = (p.rows[0] % 2 == 0) && (p.rows[1] % 2 == 0);
+  const size_t xbytes = sizeof(float) * (size_t)p.n;
+  auto fits = [&](int nb, size_t ring) { return nb * xbytes + ring <= GV_SMEM_LIMIT; };
+  constexpr size_t RING_512 = ring_bytes<2, 512, 6>(), RING_256 = ring_bytes<2, 256, 6>();
+  constexpr size_t RING_1 = ring_bytes<1, 256, 4, 4>();   // = ring_bytes<2, 256, 4, 2>(), the one- and two-sequence kernels
+  if (!fits(1, RING_1)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   for (int b0 = 0; b0 < p.B && !e;) {
     const int left = p.B - b0;
-    if (left >= 8 && even && (size_t)8 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 8, 2, 512>(p, b0, st); b0 += 8; }
-    else if (left >= 4 && even && (size_t)4 * p.n * 4 <= 100 * 1024) { e = launch_pass<WT, 4, 2, 512>(p, b0, st); b0 += 4; }
-    else if (left >= 4 && (size_t)4 * p.n * 4 <= 200 * 1024) { e = launch_pass<WT, 4, 1, 256>(p, b0, st); b0 += 4; }
-    else if (left >= 2) { e = launch_pass<WT, 2, 1, 256>(p, b0, st); b0 += 2; }
-    else { e = launch_pass<WT, 1, 1, 256>(p, b0, st); b0 += 1; }
+    if (p.swiglu) {
+      if (left >= 8 && fits(8, RING_512)) { e = launch_pass<WT, 8, 2, 512, true, 6>(p, b0, st); b0 += 8; }
+      else if (left >= 4 && fits(4, RING_512)) { e = launch_pass<WT, 4, 2, 512, true, 6>(p, b0, st); b0 += 4; }
+      else if (left >= 4 && fits(4, RING_256)) { e = launch_pass<WT, 4, 2, 256, true, 6>(p, b0, st); b0 += 4; }
+      else if (left >= 2 && fits(2, RING_1)) { e = launch_pass<WT, 2, 2, 256, true, 4, 2>(p, b0, st); b0 += 2; }
+      else { e = launch_pass<WT, 1, 2, 256, true, 4, 2>(p, b0, st); b0 += 1; }
+    } else {
+      if (left >= 8 && fits(8, RING_512)) { e = launch_pass<WT, 8, 2, 512, false, 6>(p, b0, st); b0 += 8; }
+      else if (left >= 4 && fits(4, RING_512)) { e = launch_pass<WT, 4, 2, 512, false, 6>(p, b0, st); b0 += 4; }
+      else if (left >= 4 && fits(4, RING_256)) { e = launch_pass<WT, 4, 2, 256, false, 6>(p, b0, st); b0 += 4; }
+      else if (left >= 2 && fits(2, RING_1)) { e = launch_pass<WT, 2, 1, 256, false, 4, 4>(p, b0, st); b0 += 2; }
+      else { e = launch_pass<WT, 1, 1, 256, false, 4, 4>(p, b0, st); b0 += 1; }
+    }
   }
   return e;
 }
+
+// one sequence's activations and the smallest ring fit in shared memory
+bool gemv_supported(int n) { return sizeof(float) * (size_t)n + ring_bytes<1, 256, 4, 4>() <= GV_SMEM_LIMIT; }
 
 bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -307,7 +405,7 @@ int mca_decode_ffn(const float* rms_weight, float eps, const void* w1, const voi
   if (B <= 0 || dim <= 0 || hidden_dim <= 0 || dim % 8 != 0 || hidden_dim % 8 != 0) return ERROR_PARAM_OUT_OF_RANGE;
   if (!al16(x_inout) || !al16(rms_weight) || !al16(w1) || !al16(w2) || !al16(w3) || !al16(hidden_scratch))
     return ERROR_PARAM_OUT_OF_RANGE;
-  if ((size_t)hidden_dim * 4 > 200 * 1024 || (size_t)dim * 4 > 200 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (!gemv_supported(hidden_dim) || !gemv_supported(dim)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   GemvParams p;
   // h = silu(W1 xn) * (W3 xn)
   p.swiglu = 1;

@@ -22,6 +22,7 @@ namespace {
 // of the table instead of memory outside it.
 __global__ void embed_rows_kernel(const float* __restrict__ table, const int* __restrict__ tokens, int vocab, int dim,
                                   float* __restrict__ x) {
+  mca_pdl_launch_dependents();
   const int b = blockIdx.y;
   int t = tokens[b];
   if (t < 0 || t >= vocab) t = 0;
