@@ -59,6 +59,10 @@ typedef char* MCA_LPTSTR;
                                       (device.h:2463-2486) + optional 10th long: MCA_DTYPE_*, 11th: MCA_FLAG_* */
 #define CUDNN_FN_ATTN_FWD 163      /* longs {hCuDnn,hAttn,T,hQ,hK,hV,hMask,hY,bBatchMask}   (device.h:2488-2506) */
 #define CUDNN_FN_ATTN_BWD 164      /* longs {hCuDnn,hAttn,hQ,hdQ,hK,hdK,hV,hdV,hMask,hY,hdY} (device.h:2508-2529) */
+#define CUDA_FN_CREATE_LAYERNORM 970 /* floats {eps}; longs {gpuId,count,outerNum,channels,innerNum} -> hLayerNorm (device.h:4123-4147) */
+#define CUDA_FN_FREE_LAYERNORM 971   /* floats {hLayerNorm}                                  (device.h:4150-4160) */
+#define CUDA_FN_LAYERNORM_FWD 975    /* longs {hLayerNorm,hXdata,hYdata}                     (device.h:4163-4178) */
+#define CUDA_FN_LAYERNORM_BWD 976    /* longs {hLayerNorm,hYdata,hYdiff,hXdiff}              (CudaDnn.cs:6354-6360) */
 #define CUDA_FN_CREATE_ROPE 980    /* floats {theta}; longs {sharedIdx,gpuId,count,B,T,H,D} -> hRope (device.h:4200-4228) */
 #define CUDA_FN_FREE_ROPE 981      /* floats {hRope} */
 #define CUDA_FN_ROPE_FWD 982       /* longs {hRope,n,hX,hY[,freqOffset]}      (device.h:4243-4265) */
@@ -77,6 +81,8 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_DECODE_OUT 2014     /* longs {hAttn,hWo,B,dim,hX}: x += Wo . attn */
 #define MCA_FN_TFT_ATTN_FWD 2020   /* longs {hQ,hK,hV,hMask,B,H,Nq,Nk,d,hOut,hAttn} */
 #define MCA_FN_TFT_ATTN_BWD 2021   /* longs {hQ,hK,hV,hMask,hdOut,hdAttn,B,H,Nq,Nk,d,hdQ,hdK,hdV} (hMask, hdAttn may be 0) */
+#define MCA_FN_RMSNORM_FWD 2040    /* floats {eps}; longs {hX,hW (0: none),hY,hInvRms,rows,inner}: RMSNormLayer forward in one pass */
+#define MCA_FN_RMSNORM_BWD 2041    /* longs {hX,hW,hdY,hInvRms,hdX,hdW (0: frozen),rows,inner}: its backward */
 #define MCA_FN_SET_ASYNC 2030      /* longs {0|1}: 1 = do not synchronise the stream after each call (default 0, as the reference) */
 
 /* 10th long of ATTN_SET */
@@ -337,6 +343,32 @@ MCA_API int mca_tft_attention_forward_f32(const float* q, const float* k, const 
 MCA_API int mca_tft_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
                                            const float* d_out, const float* d_attn, int B, int H, int Nq, int Nk,
                                            int d, float* dq, float* dk, float* dv, void* stream);
+
+/* LayerNorm over rows of `inner` floats, one pass each way.  Replace LayerNormData<T>::Forward /
+ * Backward, CudaDnnDLL/Cuda Files/layernorm.cu:291-333, :340-384 (10 and 9 kernels over seven
+ * count-sized scratch tensors; no affine part, the C# layer applies it):
+ *   y = (x - mean) / stdev,  stdev = sqrt(mean((x - mean)^2) + eps)        (stdev: `rows` floats, kept for backward)
+ *   dx = (dy - (y * mean(y dy) + mean(dy))) / stdev
+ * As the reference does (add_scalar over outer*channels items of its count-sized stdev tensor,
+ * layernorm.cu:377), the divisor of the first `rows` elements of the flat tensor is stdev + eps.
+ * inner <= 16384. */
+MCA_API int mca_layernorm_forward_f32(const float* x, float* y, float* stdev, int64_t rows, int inner, float eps,
+                                      void* stream);
+MCA_API int mca_layernorm_backward_f32(const float* y, const float* dy, const float* stdev, float* dx, int64_t rows,
+                                       int inner, float eps, void* stream);
+/* RMSNorm layer, one pass each way.  Replace the 8 and 14 CudaDnn calls of RMSNormLayer<T>.forward /
+ * backward, MyCaffe.layers.gpt/layers.gpt/RMSNormLayer.cs:156-179, :190-231:
+ *   inv = 1 / sqrt(mean(x^2) + eps);  y = w o (x inv)                     (w may be null; inv_rms: `rows` floats or null)
+ *   g = dy o w;  dx = g inv - x sum(g x) inv^3 / inner;  dw = sum over ALL rows of dy o (x inv)
+ * (the reference's channel_sum writes outerNum*inner sums into the inner-sized weight diff,
+ * RMSNormLayer.cs:199 with math.cu:6945-6961: identical to this for outerNum == 1, out of bounds beyond).
+ * dw null skips the weight gradient; otherwise scratch holds mca_rmsnorm_backward_scratch_floats(inner) floats. */
+MCA_API int mca_rmsnorm_forward_f32(const float* x, const float* w, float* y, float* inv_rms, int64_t rows, int inner,
+                                    float eps, void* stream);
+MCA_API int64_t mca_rmsnorm_backward_scratch_floats(int inner);
+MCA_API int mca_rmsnorm_backward_f32(const float* x, const float* w, const float* dy, const float* inv_rms, float* dx,
+                                     float* dw, float* scratch, int64_t scratch_floats, int64_t rows, int inner,
+                                     void* stream);
 
 /* float <-> bf16 copies used at the handle boundary. */
 MCA_API int mca_convert_f32_to_bf16(const float* x, void* y, int64_t n, void* stream);

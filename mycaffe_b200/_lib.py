@@ -58,6 +58,11 @@ SIGNATURES = {
     "mca_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_tft_attention_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "mca_tft_attention_backward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "mca_layernorm_forward_f32": (_i, [_vp, _vp, _vp, _i64, _i, C.c_float, _vp]),
+    "mca_layernorm_backward_f32": (_i, [_vp, _vp, _vp, _vp, _i64, _i, C.c_float, _vp]),
+    "mca_rmsnorm_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i64, _i, C.c_float, _vp]),
+    "mca_rmsnorm_backward_scratch_floats": (_i64, [_i]),
+    "mca_rmsnorm_backward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "mca_convert_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "mca_convert_bf16_to_f32": (_i, [_vp, _vp, _i64, _vp]),
     "mca_version": (C.c_char_p, []),

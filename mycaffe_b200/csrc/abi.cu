@@ -62,6 +62,14 @@ struct DecodeHandle {
   int64_t scratch_floats = 0;
 };
 
+struct LayerNormHandle {
+  int64_t rows = 0;
+  int inner = 0;
+  float eps = 0.f;
+  float* stdev = nullptr;   // (rows) from the last forward
+  bool have_fwd = false;
+};
+
 struct Kernel {
   int device = 0;
   bool async = false;
@@ -70,6 +78,9 @@ struct Kernel {
   std::unordered_map<long, AttnHandle> attn;
   std::unordered_map<long, RopeHandle> rope;
   std::unordered_map<long, DecodeHandle> decode;
+  std::unordered_map<long, LayerNormHandle> layernorm;
+  float* norm_scratch = nullptr;   // grow-only: dW partials of the RMSNorm backward
+  int64_t norm_scratch_floats = 0;
   std::unordered_map<long, int> cudnn;
   std::vector<void*> host_bufs;
   std::string last_detail;
@@ -108,6 +119,7 @@ const char* error_name(long e) {
     case ERROR_MEMORY_NOT_FOUND: return "memory handle not found";
     case ERROR_MEMORY_TOO_SMALL: return "memory too small";
     case ERROR_ROPE_NOT_INITIALIZED: return "rope not initialized";
+    case ERROR_LAYERNORM_NOT_INITIALIZED: return "layernorm not initialized";
     case ERROR_ATTN_NOT_INITIALIZED: return "attn not initialized";
     case ERROR_ATTN + 3: return "attn missing descriptor";
     case ERROR_ATTN_INCOMPATIBLE_BLOB_SIZE: return "attn incompatible blob size";
@@ -671,6 +683,82 @@ long decode_out(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   return mca_decode_out_proj(attn, wo->ptr, wo->bf16 ? 1 : 0, B, dim, x, 0);
 }
 
+// Device<T>::CreateLayerNorm / FreeLayerNorm / LayerNormForward / LayerNormBackward, device.h:4123-4195
+long layernorm_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput, float** ppOutput) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1)) || (e = verify_in(llInput, pl, 5, 5)) || (e = verify_out(plOutput, ppOutput))) return e;
+  const int64_t count = pl[1], outer = pl[2], channels = pl[3], inner = pl[4];
+  if (count <= 0 || outer <= 0 || channels <= 0 || inner <= 0 || inner > INT32_MAX) return ERROR_PARAM_OUT_OF_RANGE;
+  if (count != outer * channels * inner) return ERROR_PARAM_OUT_OF_RANGE;   // LayerNormMemory<T>::Initialize, layernorm.cu:154-155
+  LayerNormHandle h;
+  h.rows = outer * channels; h.inner = (int)inner; h.eps = pf[0];
+  if (cudaMalloc(&h.stdev, (size_t)h.rows * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return ERROR_MEMORY_OUT; }
+  const long id = k->next_handle++;
+  k->layernorm[id] = h;
+  return set_out((float)id, plOutput, ppOutput);
+}
+
+long layernorm_free(Kernel* k, long lInput, float* pf) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  auto it = k->layernorm.find((long)pf[0]);
+  if (it == k->layernorm.end()) return ERROR_LAYERNORM_NOT_INITIALIZED;
+  cudaFree(it->second.stdev);
+  k->layernorm.erase(it);
+  return 0;
+}
+
+long layernorm_run(Kernel* k, long llInput, MCA_LONGLONG* pl, bool backward) {
+  long e;
+  if ((e = verify_in(llInput, pl, backward ? 4 : 3, backward ? 4 : 3))) return e;
+  auto it = k->layernorm.find((long)pl[0]);
+  if (it == k->layernorm.end()) return ERROR_LAYERNORM_NOT_INITIALIZED;
+  LayerNormHandle& h = it->second;
+  const int64_t n = h.rows * h.inner;
+  if (!backward) {
+    float *x, *y;
+    if ((e = check_f32(k, (long)pl[1], n, &x)) || (e = check_f32(k, (long)pl[2], n, &y))) return e;
+    h.have_fwd = true;
+    return mca_layernorm_forward_f32(x, y, h.stdev, h.rows, h.inner, h.eps, 0);
+  }
+  if (!h.have_fwd) return ERROR_LAYERNORM_NOT_INITIALIZED;   // the divisor is the forward's stdev
+  float *y, *dy, *dx;
+  if ((e = check_f32(k, (long)pl[1], n, &y)) || (e = check_f32(k, (long)pl[2], n, &dy)) || (e = check_f32(k, (long)pl[3], n, &dx))) return e;
+  return mca_layernorm_backward_f32(y, dy, h.stdev, dx, h.rows, h.inner, h.eps, 0);
+}
+
+long rmsnorm_run(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, bool backward) {
+  long e;
+  if ((e = verify_in(llInput, pl, backward ? 8 : 6, backward ? 8 : 6))) return e;
+  const int64_t rows = pl[backward ? 6 : 4], inner = pl[backward ? 7 : 5];
+  if (rows <= 0 || inner <= 0 || inner > INT32_MAX) return ERROR_PARAM_OUT_OF_RANGE;
+  const int64_t n = rows * inner;
+  float *x, *w = nullptr;
+  if ((e = check_f32(k, (long)pl[0], n, &x))) return e;
+  if (pl[1] != 0 && (e = check_f32(k, (long)pl[1], inner, &w))) return e;
+  if (!backward) {
+    if ((e = verify_in(lInput, pf, 1, 1))) return e;
+    float *y, *inv = nullptr;
+    if ((e = check_f32(k, (long)pl[2], n, &y))) return e;
+    if (pl[3] != 0 && (e = check_f32(k, (long)pl[3], rows, &inv))) return e;
+    return mca_rmsnorm_forward_f32(x, w, y, inv, rows, (int)inner, pf[0], 0);
+  }
+  float *dy, *inv, *dx, *dw = nullptr;
+  if ((e = check_f32(k, (long)pl[2], n, &dy)) || (e = check_f32(k, (long)pl[3], rows, &inv)) || (e = check_f32(k, (long)pl[4], n, &dx))) return e;
+  if (pl[5] != 0) {
+    if (!w) return ERROR_PARAM_NULL;
+    if ((e = check_f32(k, (long)pl[5], inner, &dw))) return e;
+    const int64_t need = mca_rmsnorm_backward_scratch_floats((int)inner);
+    if (need > k->norm_scratch_floats) {
+      cudaFree(k->norm_scratch);
+      k->norm_scratch = nullptr; k->norm_scratch_floats = 0;
+      if (cudaMalloc(&k->norm_scratch, (size_t)need * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return ERROR_MEMORY_OUT; }
+      k->norm_scratch_floats = need;
+    }
+  }
+  return mca_rmsnorm_backward_f32(x, w, dy, inv, dx, dw, k->norm_scratch, k->norm_scratch_floats, rows, (int)inner, 0);
+}
+
 long tft_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   long e;
   if ((e = verify_in(llInput, pl, 11, 11))) return e;
@@ -736,6 +824,8 @@ void kernel_cleanup(long idx) {
   for (auto& kv : k->mem) cudaFree(kv.second.ptr);
   for (auto& kv : k->attn) kv.second.release();
   for (auto& kv : k->rope) { cudaFree(kv.second.cos_t); cudaFree(kv.second.sin_t); }
+  for (auto& kv : k->layernorm) cudaFree(kv.second.stdev);
+  cudaFree(k->norm_scratch);
   for (auto& kv : k->decode) { cudaFree(kv.second.fr); cudaFree(kv.second.fi); cudaFree(kv.second.scratch); }
   for (void* p : k->host_bufs) cudaFreeHost(p);
   cudaFree(k->stage);
@@ -796,6 +886,12 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
       MCA_LONGLONG a11[11] = {pl[0], pl[1], pl[2], pl[3], pl[2], pl[3], pl[2], pl[3], pl[4], pl[5], pl[6]};
       return finish(k, attn_bwd(k, 11, a11, MCA_LAYOUT_PACKED));
     }
+    case CUDA_FN_CREATE_LAYERNORM: return layernorm_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
+    case CUDA_FN_FREE_LAYERNORM: return layernorm_free(k, lInput, pf);
+    case CUDA_FN_LAYERNORM_FWD: return finish(k, layernorm_run(k, llInput, pl, false));
+    case CUDA_FN_LAYERNORM_BWD: return finish(k, layernorm_run(k, llInput, pl, true));
+    case MCA_FN_RMSNORM_FWD: return finish(k, rmsnorm_run(k, lInput, pf, llInput, pl, false));
+    case MCA_FN_RMSNORM_BWD: return finish(k, rmsnorm_run(k, lInput, pf, llInput, pl, true));
     case CUDA_FN_CREATE_ROPE: return rope_create(k, lInput, pf, llInput, pl, plOutput, ppOutput);
     case CUDA_FN_FREE_ROPE: return rope_free(k, lInput, pf);
     case CUDA_FN_ROPE_FWD: return finish(k, rope_run(k, llInput, pl, false));

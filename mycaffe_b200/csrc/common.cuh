@@ -22,6 +22,8 @@ constexpr int ERROR_MEMORY_TOO_SMALL = ERROR_PARAM + 16;
 // LAYERNORM = +160, ROPE = +200, RNN8 = +240, ATTN = +280 (util.h:150-211).
 constexpr int ERROR_ROPE = ERROR_PARAM + 200;
 constexpr int ERROR_ROPE_NOT_INITIALIZED = ERROR_ROPE + 1;
+constexpr int ERROR_LAYERNORM = ERROR_ROPE - 40;                  // util.h:195-198
+constexpr int ERROR_LAYERNORM_NOT_INITIALIZED = ERROR_LAYERNORM + 1;
 constexpr int ERROR_ATTN = ERROR_PARAM + 280;
 constexpr int ERROR_ATTN_NOT_INITIALIZED = ERROR_ATTN + 1;
 constexpr int ERROR_ATTN_INCOMPATIBLE_BLOB_SIZE = ERROR_ATTN + 4;

@@ -171,6 +171,29 @@ class CudaDnn:
     def AttnScaledDotProductBackward(self, hCuDnn, hAttn, hQ, hdQ, hK, hdK, hV, hdV, hMask, hY, hdY):
         self._invoke(ids.CUDNN_FN_ATTN_BWD, None, [hCuDnn, hAttn, hQ, hdQ, hK, hdK, hV, hdV, hMask, hY, hdY])
 
+    # ------------------------------------------------------------------ LayerNorm (CudaDnn.cs:6307-6360)
+    def CreateLayerNorm(self, nGpuID, nCount, nOuterNum, nChannels, nInnerNum, fEps=1e-10) -> int:
+        return int(self._invoke(ids.CUDA_FN_CREATE_LAYERNORM, [float(fEps)],
+                                [nGpuID, nCount, nOuterNum, nChannels, nInnerNum])[0])
+
+    def FreeLayerNorm(self, h):
+        self._invoke(ids.CUDA_FN_FREE_LAYERNORM, [float(h)])
+
+    def LayerNormForward(self, hLayerNorm, hXdata, hYdata):
+        self._invoke(ids.CUDA_FN_LAYERNORM_FWD, None, [hLayerNorm, hXdata, hYdata])
+
+    def LayerNormBackward(self, hLayerNorm, hYdata, hYdiff, hXdiff):
+        self._invoke(ids.CUDA_FN_LAYERNORM_BWD, None, [hLayerNorm, hYdata, hYdiff, hXdiff])
+
+    # ------------------------------------------------------------------ RMSNorm layer (RMSNormLayer.cs:156-231)
+    def RmsNormForward(self, hX, hW, hY, hInvRms, nRows, nInner, fEps=1e-5):
+        """y = w * x / sqrt(mean(x^2) + eps) in one pass; hW = 0 for a layer without weights."""
+        self._invoke(ids.MCA_FN_RMSNORM_FWD, [float(fEps)], [hX, hW, hY, hInvRms, nRows, nInner])
+
+    def RmsNormBackward(self, hX, hW, hdY, hInvRms, hdX, hdW, nRows, nInner):
+        """dx (and dw unless hdW = 0) from dy and the 1/rms the forward saved."""
+        self._invoke(ids.MCA_FN_RMSNORM_BWD, None, [hX, hW, hdY, hInvRms, hdX, hdW, nRows, nInner])
+
     # ------------------------------------------------------------------ RoPE (CudaDnn.cs:6375-6431)
     def CreateRope(self, nSharedIndex, nGpuID, nCount, nBatch, nSeqLen, nHeads, nDim, fTheta=10000.0) -> int:
         return int(self._invoke(ids.CUDA_FN_CREATE_ROPE, [float(fTheta)],

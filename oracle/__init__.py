@@ -32,7 +32,9 @@ _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 def build(force: bool = False) -> None:
     """Compile the checkers (make -C oracle).  The reference twin is only rebuilt when
     the reference tree is present; otherwise a prebuilt one is kept."""
-    if force or not (_HERE / "_build" / "liboracle.so").exists() or not (_HERE / "_ref" / "libllama2_ref.so").exists():
+    so, src = _HERE / "_build" / "liboracle.so", _HERE / "attn_oracle.cpp"
+    stale = so.exists() and so.stat().st_mtime < src.stat().st_mtime
+    if force or stale or not so.exists() or not (_HERE / "_ref" / "libllama2_ref.so").exists():
         subprocess.run(["make", "-C", str(_HERE)] + (["-B"] if force else []), check=True,
                        stdout=subprocess.DEVNULL)
 
@@ -41,7 +43,7 @@ def lib() -> C.CDLL:
     global _LIB
     if _LIB is None:
         path = _HERE / "_build" / "liboracle.so"
-        if not path.exists():
+        if not path.exists() or path.stat().st_mtime < (_HERE / "attn_oracle.cpp").stat().st_mtime:
             build()
         _LIB = C.CDLL(str(path))
         _LIB.oracle_num_threads.restype = C.c_int
@@ -185,6 +187,47 @@ def tft_backward(q, k, v, mask, d_out, d_attn=None, f64=False):
 
 
 # --------------------------------------------------------------------------- llama2 decode
+
+def layernorm_forward(x, eps=1e-10):
+    """LayerNormData<T>::Forward (layernorm.cu:291-333) over the last axis: returns (y, stdev)."""
+    x = _c(x)
+    rows, inner = int(np.prod(x.shape[:-1])), x.shape[-1]
+    y, sd = np.empty_like(x), np.empty(rows, np.float32)
+    lib().oracle_layernorm_fwd(x.ctypes, y.ctypes, sd.ctypes, C.c_int64(rows), inner, C.c_float(eps))
+    return y, sd
+
+
+def layernorm_backward(y, dy, stdev, eps=1e-10):
+    """LayerNormData<T>::Backward (layernorm.cu:340-384), including its eps on the first `rows` elements."""
+    y, dy, stdev = _c(y), _c(dy), _c(stdev)
+    rows, inner = stdev.size, y.shape[-1]
+    dx = np.empty_like(y)
+    lib().oracle_layernorm_bwd(y.ctypes, dy.ctypes, stdev.ctypes, dx.ctypes, C.c_int64(rows), inner, C.c_float(eps))
+    return dx
+
+
+def rmsnorm_layer_forward(x, w=None, eps=1e-5):
+    """RMSNormLayer<T>.forward (RMSNormLayer.cs:156-179) over the last axis: returns (y, 1/rms)."""
+    x = _c(x)
+    rows, inner = int(np.prod(x.shape[:-1])), x.shape[-1]
+    y, inv = np.empty_like(x), np.empty(rows, np.float32)
+    wc = _c(w) if w is not None else None
+    lib().oracle_rmsnorm_layer_fwd(x.ctypes, wc.ctypes if wc is not None else None, y.ctypes, inv.ctypes, C.c_int64(rows),
+                                   inner, C.c_float(eps))
+    return y, inv
+
+
+def rmsnorm_layer_backward(x, w, dy, eps=1e-5):
+    """RMSNormLayer<T>.backward (RMSNormLayer.cs:190-231): returns (dx, dw); dw is None without weights."""
+    x, dy = _c(x), _c(dy)
+    rows, inner = int(np.prod(x.shape[:-1])), x.shape[-1]
+    dx = np.empty_like(x)
+    wc = _c(w) if w is not None else None
+    dw = np.empty(inner, np.float32) if w is not None else None
+    lib().oracle_rmsnorm_layer_bwd(x.ctypes, wc.ctypes if wc is not None else None, dy.ctypes, dx.ctypes,
+                                   dw.ctypes if dw is not None else None, C.c_int64(rows), inner, C.c_float(eps))
+    return dx, dw
+
 
 def llama_freqs(head_size, seq_len, theta=10000.0):
     fr = np.empty((seq_len, head_size // 2), np.float32)

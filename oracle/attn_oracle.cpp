@@ -454,4 +454,95 @@ void oracle_llama_decode(float* q, float* k, const float* v, float* kc, float* v
   llama_decode(q, k, v, kc, vc, pos, B, n_heads, n_kv_heads, hs, seq_len, fr, fi, out, att_out);
 }
 
+// ---- LayerNorm, operation by operation as LayerNormData<T>::Forward / Backward issue them
+// (CudaDnnDLL/Cuda Files/layernorm.cu:291-333, :340-384).  channel_mean accumulates a row in
+// double and rounds the mean to float (math.cu:6817-6831); everything else is float arithmetic.
+void oracle_layernorm_fwd(const float* x, float* y, float* stdev, int64_t rows, int inner, float eps) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * inner;
+    double acc = 0;
+    for (int j = 0; j < inner; ++j) acc += (double)xr[j];
+    const float mean = (float)(acc / (double)inner);
+    acc = 0;
+    for (int j = 0; j < inner; ++j) {
+      const float xmu = xr[j] - mean;
+      const float sq = xmu * xmu;          // powx(.., 2)
+      acc += (double)sq;
+    }
+    const float var = (float)(acc / (double)inner);
+    const float sd = sqrtf(var + eps);     // scale, add_scalar, sqrt
+    stdev[r] = sd;
+    for (int j = 0; j < inner; ++j) y[r * inner + j] = (xr[j] - mean) / sd;
+  }
+}
+void oracle_layernorm_bwd(const float* y, const float* dy, const float* stdev, float* dx, int64_t rows, int inner, float eps) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float *yr = y + r * inner, *dyr = dy + r * inner;
+    double a1 = 0, a2 = 0;
+    for (int j = 0; j < inner; ++j) { a1 += (double)(yr[j] * dyr[j]); a2 += (double)dyr[j]; }
+    const float m1 = (float)(a1 / (double)inner), m2 = (float)(a2 / (double)inner);
+    for (int j = 0; j < inner; ++j) {
+      float work = yr[j] * m1;
+      work = work + m2;
+      work = dyr[j] - work;
+      // add_scalar(outer*channels, eps, stdevfull) touches the first `rows` elements of the
+      // count-sized broadcast tensor only (layernorm.cu:377)
+      const int64_t flat = r * inner + j;
+      const float denom = flat < rows ? stdev[r] + eps : stdev[r];
+      dx[flat] = work / denom;
+    }
+  }
+}
+
+// ---- RMSNorm layer, operation by operation as RMSNormLayer<T>.forward / backward issue them
+// (MyCaffe.layers.gpt/layers.gpt/RMSNormLayer.cs:156-179, :190-231).  w may be null
+// (enable_weights false).  dw sums over all rows (for outerNum == 1 this is the reference's channel_sum).
+void oracle_rmsnorm_layer_fwd(const float* x, const float* w, float* y, float* inv_rms, int64_t rows, int inner, float eps) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * inner;
+    double acc = 0;
+    for (int j = 0; j < inner; ++j) acc += (double)(xr[j] * xr[j]);       // powx, channel_mean
+    const float rms = sqrtf((float)(acc / (double)inner) + eps);          // sqrt(x + eps)
+    const float inv = rms == 0.f ? 0.f : 1.0f / rms;                      // invert
+    if (inv_rms) inv_rms[r] = inv;
+    for (int j = 0; j < inner; ++j) {
+      const float out = xr[j] * inv;
+      y[r * inner + j] = w ? w[j] * out : out;
+    }
+  }
+}
+void oracle_rmsnorm_layer_bwd(const float* x, const float* w, const float* dy, float* dx, float* dw, int64_t rows, int inner,
+                              float eps) {
+  std::vector<double> dwacc(inner, 0.0);
+  for (int64_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * inner, *dyr = dy + r * inner;
+    double acc = 0;
+    for (int j = 0; j < inner; ++j) acc += (double)(xr[j] * xr[j]);
+    const float rms = sqrtf((float)(acc / (double)inner) + eps);
+    const float inv = rms == 0.f ? 0.f : 1.0f / rms;
+    double dinv_acc = 0;
+    for (int j = 0; j < inner; ++j) {
+      const float out = xr[j] * inv;
+      if (w) dwacc[j] += (double)(dyr[j] * out);
+      const float g = w ? dyr[j] * w[j] : dyr[j];
+      dinv_acc += (double)(g * xr[j]);                                    // mul, channel_sumEx
+    }
+    const float dinv = (float)dinv_acc;
+    const float rms2 = rms * rms;                                         // powx(rms, 2)
+    const float neg_inv2 = rms2 == 0.f ? 0.f : -1.0f / rms2;              // invert(.., numerator -1)
+    const float drms = dinv * neg_inv2;
+    const float half_inv = rms == 0.f ? 0.f : 1.0f / (rms * 2.0f);        // invert(.., 1, 2)
+    float dmean = half_inv * drms;
+    dmean = dmean * (float)(1.0 / (double)inner);                         // channel_duplicate, scal(1/inner)
+    for (int j = 0; j < inner; ++j) {
+      const float g = w ? dyr[j] * w[j] : dyr[j];
+      const float dxa = g * inv;
+      float dxb = 2.0f * xr[j];                                           // scale(2, x)
+      dxb = dxb * dmean;
+      dx[r * inner + j] = dxb + dxa;                                      // add
+    }
+  }
+  if (dw) for (int j = 0; j < inner; ++j) dw[j] = (float)dwacc[j];
+}
+
 }  // extern "C"

@@ -232,3 +232,55 @@ def test_whole_step_restatement_matches_compiled_reference(tmp_path):
         np.testing.assert_allclose(logits[0], ref.state("logits"), rtol=0, atol=2e-6 * np.abs(ref.state("logits")).max())
     np.testing.assert_allclose(kc.ravel(), ref.state("key_cache"), rtol=0, atol=5e-6)
     ref.close()
+
+
+def test_layernorm_restatement_against_closed_form():
+    """The op-by-op LayerNorm (layernorm.cu:291-384) against the textbook formulas in float64."""
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, 5, 48)).astype(np.float32) * 2 + 0.5
+    dy = rng.standard_normal(x.shape).astype(np.float32)
+    eps = 1e-5
+    y, sd = oracle.layernorm_forward(x, eps)
+    x64 = x.astype(np.float64)
+    mu = x64.mean(-1, keepdims=True)
+    sd64 = np.sqrt(((x64 - mu) ** 2).mean(-1, keepdims=True) + eps)
+    np.testing.assert_allclose(y, (x64 - mu) / sd64, atol=2e-6)
+    np.testing.assert_allclose(sd, sd64.ravel(), rtol=1e-6)
+    dx = oracle.layernorm_backward(y, dy, sd, eps)
+    y64, dy64 = y.astype(np.float64), dy.astype(np.float64)
+    ref = (dy64 - (y64 * (y64 * dy64).mean(-1, keepdims=True) + dy64.mean(-1, keepdims=True))) / sd64
+    # the reference divides the first rows (= 15) elements of the flat tensor by stdev + eps
+    np.testing.assert_allclose(dx, ref, atol=3e-5)
+    flat, rows = dx.ravel(), 15
+    np.testing.assert_allclose(flat[rows:], ref.ravel()[rows:], atol=3e-6)
+
+
+def test_rmsnorm_layer_restatement_against_autograd_formula():
+    """The op-by-op RMSNorm layer (RMSNormLayer.cs:156-231) against d/dx of w * x / sqrt(mean(x^2)+eps)
+    in float64, by central differences on a scalar loss."""
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((1, 6, 40)).astype(np.float32)
+    w = (1 + 0.2 * rng.standard_normal(40)).astype(np.float32)
+    dy = rng.standard_normal(x.shape).astype(np.float32)
+    eps = 1e-5
+    f = lambda xx, ww: ww * xx / np.sqrt((xx ** 2).mean(-1, keepdims=True) + eps)
+    y, inv = oracle.rmsnorm_layer_forward(x, w, eps)
+    np.testing.assert_allclose(y, f(x.astype(np.float64), w.astype(np.float64)), atol=2e-6)
+    np.testing.assert_allclose(inv, 1 / np.sqrt((x.astype(np.float64) ** 2).mean(-1) + eps).ravel(), rtol=1e-6)
+    dx, dw = oracle.rmsnorm_layer_backward(x, w, dy, eps)
+    x64, w64, dy64 = x.astype(np.float64), w.astype(np.float64), dy.astype(np.float64)
+    loss = lambda xx, ww: (f(xx, ww) * dy64).sum()
+    num_dx = np.zeros_like(x64)
+    h = 1e-6
+    for idx in np.ndindex(*x.shape):
+        xp, xm = x64.copy(), x64.copy()
+        xp[idx] += h; xm[idx] -= h
+        num_dx[idx] = (loss(xp, w64) - loss(xm, w64)) / (2 * h)
+    np.testing.assert_allclose(dx, num_dx, atol=5e-6)
+    num_dw = np.array([(loss(x64, w64 + h * np.eye(40)[j]) - loss(x64, w64 - h * np.eye(40)[j])) / (2 * h) for j in range(40)])
+    np.testing.assert_allclose(dw, num_dw, atol=1e-5)
+    # without weights
+    y2, _ = oracle.rmsnorm_layer_forward(x, None, eps)
+    np.testing.assert_allclose(y2, f(x64, 1.0), atol=2e-6)
+    dx2, dw2 = oracle.rmsnorm_layer_backward(x, None, dy, eps)
+    assert dw2 is None
