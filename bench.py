@@ -512,7 +512,10 @@ def run_profile_case(case):
     `prefill-small` = config-5 shape at T = 8192, B = 1; `prefill-full` = the bench workload itself, two
     launches (single-pass metrics only); `bwd-small` = bf16 backward at the prefill-small shape;
     `decode-small` = config-3 shape, 16 sequences of 4096 keys; `gemv-small` = the decode projections at
-    dim 4096 for 1 and 8 sequences (also prints their CUDA-event bandwidth)."""
+    dim 4096 for 1 and 8 sequences plus the feed-forward half and the classifier for one (also prints their
+    CUDA-event bandwidth); `norm-small` = the LayerNorm / RMSNorm layer kernels on a 268 MB tensor;
+    `llama-step` = the whole decode step of an 8-layer llama2-7B-shaped model, eager and from a CUDA graph
+    (a timing case, about 15 GB on the device: not for ncu)."""
     import torch
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
@@ -542,6 +545,122 @@ def run_profile_case(case):
                 torch.cuda.synchronize()
                 ms = e0.elapsed_time(e1) / 20
                 res[f"{name}_B{Bn}"] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+        # feed-forward half (RMSNorm + W1/W3 + SwiGLU, W2 + residual) and the classifier, one sequence
+        hidden, vocab = 11008, 32000
+        del ws
+        w1, w3 = (torch.randn(hidden, dim, device=dev) * 0.02 for _ in range(2))
+        w2 = torch.randn(dim, hidden, device=dev) * 0.02
+        wc = torch.randn(vocab, dim, device=dev) * 0.02
+        x = torch.randn(1, dim, device=dev)
+        hbuf, logits = torch.empty(1, hidden, device=dev), torch.empty(1, vocab, device=dev)
+        def ffn():
+            return lib.mca_decode_ffn(rms.data_ptr(), 1e-5, w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), 0, 1, dim, hidden,
+                                      hbuf.data_ptr(), x.data_ptr(), None)
+        def cls():
+            return lib.mca_decode_logits(x.data_ptr(), rms.data_ptr(), 1e-5, wc.data_ptr(), 0, 1, dim, vocab, logits.data_ptr(), None)
+        for name, fn, nbytes in (("ffn", ffn, 3 * hidden * dim * 4), ("logits", cls, vocab * dim * 4)):
+            for _ in range(3):
+                rc = fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(20):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 20
+            res[f"{name}_B1"] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+        print(json.dumps(res))
+        return
+    if case == "norm-small":
+        # LayerNorm / RMSNorm layer kernels on a (16384, 4096) tensor (268 MB each way, above L2)
+        rows, inner = 16384, 4096
+        x, dy = torch.randn(rows, inner, device=dev), torch.randn(rows, inner, device=dev)
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        w, dw = torch.ones(inner, device=dev), torch.empty(inner, device=dev)
+        stat = torch.empty(rows, device=dev)
+        scratch = torch.empty(lib.mca_rmsnorm_backward_scratch_floats(inner), device=dev)
+        calls = {
+            "layernorm_fwd": (lambda: lib.mca_layernorm_forward_f32(x.data_ptr(), y.data_ptr(), stat.data_ptr(), rows, inner, 1e-5, None), 2),
+            "layernorm_bwd": (lambda: lib.mca_layernorm_backward_f32(y.data_ptr(), dy.data_ptr(), stat.data_ptr(), dx.data_ptr(), rows, inner, 1e-5, None), 3),
+            "rmsnorm_fwd": (lambda: lib.mca_rmsnorm_forward_f32(x.data_ptr(), w.data_ptr(), y.data_ptr(), stat.data_ptr(), rows, inner, 1e-5, None), 2),
+            "rmsnorm_bwd": (lambda: lib.mca_rmsnorm_backward_f32(x.data_ptr(), w.data_ptr(), dy.data_ptr(), stat.data_ptr(), dx.data_ptr(),
+                                                                 dw.data_ptr(), scratch.data_ptr(), scratch.numel(), rows, inner, None), 3),
+        }
+        res = {"case": case, "rows": rows, "inner": inner}
+        for name, (fn, tensors) in calls.items():
+            for _ in range(3):
+                rc = fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 10
+            res[name] = {"rc": rc, "ms": round(ms, 4), "GBps": round(tensors * rows * inner * 4 / ms / 1e6, 1)}
+        print(json.dumps(res))
+        return
+    if case == "llama-step":
+        # whole-transformer decode step, llama2-7B geometry cut to 8 layers, one sequence at position 2047
+        import ctypes as C
+        from mycaffe_b200 import llama2 as M
+        cfg = dict(dim=4096, hidden_dim=11008, n_layers=8, n_heads=32, n_kv_heads=32, vocab_size=32000, seq_len=4096)
+        res = {"case": case, "config": cfg}
+        for bf16 in (False, True):
+            wdt = torch.bfloat16 if bf16 else torch.float32
+            L, dim, hidden, vocab, S = cfg["n_layers"], cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"], cfg["seq_len"]
+            mk = lambda *sh, dt=torch.float32: (torch.randn(*sh, device=dev) * 0.02).to(dt)
+            w = {"token_embedding_table": mk(vocab, dim), "rms_att_weight": torch.ones(L, dim, device=dev),
+                 "rms_ffn_weight": torch.ones(L, dim, device=dev), "rms_final_weight": torch.ones(dim, device=dev),
+                 "wq": mk(L, dim, dim, dt=wdt), "wk": mk(L, dim, dim, dt=wdt), "wv": mk(L, dim, dim, dt=wdt),
+                 "wo": mk(L, dim, dim, dt=wdt), "w1": mk(L, hidden, dim, dt=wdt), "w2": mk(L, dim, hidden, dt=wdt),
+                 "w3": mk(L, hidden, dim, dt=wdt), "wcls": mk(vocab, dim, dt=wdt)}
+            kc, vc = (torch.randn(L, 1, S, dim, device=dev).to(wdt) for _ in range(2))
+            fr, fi = np.empty((S, 64), np.float32), np.empty((S, 64), np.float32)
+            fp = C.POINTER(C.c_float)
+            lib.mca_rope_tables_host(S, 128, 10000.0, fr.ctypes.data_as(fp), fi.ctypes.data_as(fp))
+            frd, fid = torch.from_numpy(fr).to(dev), torch.from_numpy(fi).to(dev)
+            cfg_c = M.McaLlamaConfig(**cfg)
+            need = lib.mca_llama_workspace_floats(C.byref(cfg_c), 1, S)
+            ws_, logits = torch.empty(need, device=dev), torch.empty(1, vocab, device=dev)
+            tok = torch.zeros(1, dtype=torch.int32, device=dev)
+            pos = torch.full((1,), 2047, dtype=torch.int32, device=dev)
+            names = ("token_embedding_table", "rms_att_weight", "rms_ffn_weight", "rms_final_weight", "wq", "wk", "wv", "wo",
+                     "w1", "w2", "w3", "wcls")
+            w_c = M.McaLlamaWeights(*[w[n].data_ptr() for n in names], int(bf16))
+            s_c = M.McaLlamaState(kc.data_ptr(), vc.data_ptr(), int(bf16), frd.data_ptr(), fid.data_ptr(), ws_.data_ptr(), need)
+            def step(stream=None):
+                st = stream if stream is not None else torch.cuda.current_stream()
+                return lib.mca_llama_forward(C.byref(cfg_c), C.byref(w_c), C.byref(s_c), tok.data_ptr(), pos.data_ptr(), 1, 2048,
+                                             logits.data_ptr(), st.cuda_stream)
+            for _ in range(3):
+                rc = step()
+            side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph.capture_begin()
+                step(side)
+                graph.capture_end()
+            torch.cuda.current_stream().wait_stream(side)
+            out = {}
+            for name, fn in (("eager", step), ("graph", graph.replay)):
+                fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(10):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                out[name + "_ms"] = round(e0.elapsed_time(e1) / 10, 4)
+            sz = 2 if bf16 else 4
+            nbytes = (L * (4 * dim * dim + 3 * dim * hidden) + vocab * dim) * sz + L * 2 * 2048 * dim * sz
+            out.update({"rc": rc, "bytes": nbytes, "GBps_graph": round(nbytes / out["graph_ms"] / 1e6, 1)})
+            res["bf16" if bf16 else "f32"] = out
+            del w, kc, vc, graph
+            torch.cuda.empty_cache()
         print(json.dumps(res))
         return
     if case in ("prefill-small", "prefill-full", "bwd-small"):
@@ -601,7 +720,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small"],
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "norm-small", "llama-step"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
     if args.case:

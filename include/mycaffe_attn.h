@@ -79,6 +79,8 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_DECODE_STEP 2012    /* longs {hDecode,hQ,hKnew,hVnew,hKcache,hVcache,hPos,maxLen,hOut}: one token for B sequences */
 #define MCA_FN_DECODE_QKV 2013     /* floats {eps}; longs {hX,hRmsW,hWq,hWk,hWv,B,dim,kvDim,hQ,hK,hV}: RMSNorm + q,k,v projections */
 #define MCA_FN_DECODE_OUT 2014     /* longs {hAttn,hWo,B,dim,hX}: x += Wo . attn */
+#define MCA_FN_DECODE_FFN 2015     /* floats {eps}; longs {hX,hRmsW,hW1,hW2,hW3,B,dim,hiddenDim,hHidden}: x += W2 (silu(W1 xn) o W3 xn) */
+#define MCA_FN_DECODE_LOGITS 2016  /* floats {eps}; longs {hX,hRmsW,hWcls,B,dim,vocab,hLogits}: final RMSNorm + classifier */
 #define MCA_FN_TFT_ATTN_FWD 2020   /* longs {hQ,hK,hV,hMask,B,H,Nq,Nk,d,hOut,hAttn} */
 #define MCA_FN_TFT_ATTN_BWD 2021   /* longs {hQ,hK,hV,hMask,hdOut,hdAttn,B,H,Nq,Nk,d,hdQ,hdK,hdV} (hMask, hdAttn may be 0) */
 #define MCA_FN_RMSNORM_FWD 2040    /* floats {eps}; longs {hX,hW (0: none),hY,hInvRms,rows,inner}: RMSNormLayer forward in one pass */

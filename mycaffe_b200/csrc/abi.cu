@@ -683,6 +683,37 @@ long decode_out(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   return mca_decode_out_proj(attn, wo->ptr, wo->bf16 ? 1 : 0, B, dim, x, 0);
 }
 
+long decode_ffn(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1)) || (e = verify_in(llInput, pl, 9, 9))) return e;
+  const int64_t B = pl[5], dim = pl[6], hidden = pl[7];
+  if (B <= 0 || dim <= 0 || hidden <= 0 || B > INT32_MAX || dim > INT32_MAX || hidden > INT32_MAX) return ERROR_PARAM_OUT_OF_RANGE;
+  float *x, *g, *h;
+  if ((e = check_f32(k, (long)pl[0], B * dim, &x)) || (e = check_f32(k, (long)pl[1], dim, &g)) ||
+      (e = check_f32(k, (long)pl[8], B * hidden, &h)))
+    return e;
+  MemItem *w1 = k->get((long)pl[2]), *w2 = k->get((long)pl[3]), *w3 = k->get((long)pl[4]);
+  if (!w1 || !w2 || !w3) return ERROR_MEMORY_NOT_FOUND;
+  if (w1->count < hidden * dim || w2->count < hidden * dim || w3->count < hidden * dim) return ERROR_MEMORY_TOO_SMALL;
+  if (w1->bf16 != w2->bf16 || w1->bf16 != w3->bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
+  return mca_decode_ffn(g, pf[0], w1->ptr, w2->ptr, w3->ptr, w1->bf16 ? 1 : 0, (int)B, (int)dim, (int)hidden, h, x, 0);
+}
+
+long decode_logits(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1)) || (e = verify_in(llInput, pl, 7, 7))) return e;
+  const int64_t B = pl[3], dim = pl[4], vocab = pl[5];
+  if (B <= 0 || dim <= 0 || vocab <= 0 || B > INT32_MAX || dim > INT32_MAX || vocab > INT32_MAX) return ERROR_PARAM_OUT_OF_RANGE;
+  float *x, *g, *out;
+  if ((e = check_f32(k, (long)pl[0], B * dim, &x)) || (e = check_f32(k, (long)pl[1], dim, &g)) ||
+      (e = check_f32(k, (long)pl[6], B * vocab, &out)))
+    return e;
+  MemItem* wc = k->get((long)pl[2]);
+  if (!wc) return ERROR_MEMORY_NOT_FOUND;
+  if (wc->count < vocab * dim) return ERROR_MEMORY_TOO_SMALL;
+  return mca_decode_logits(x, g, pf[0], wc->ptr, wc->bf16 ? 1 : 0, (int)B, (int)dim, (int)vocab, out, 0);
+}
+
 // Device<T>::CreateLayerNorm / FreeLayerNorm / LayerNormForward / LayerNormBackward, device.h:4123-4195
 long layernorm_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl, MCA_LONG* plOutput, float** ppOutput) {
   long e;
@@ -901,6 +932,8 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
     case MCA_FN_DECODE_STEP: return finish(k, decode_step(k, llInput, pl));
     case MCA_FN_DECODE_QKV: return finish(k, decode_qkv(k, lInput, pf, llInput, pl));
     case MCA_FN_DECODE_OUT: return finish(k, decode_out(k, llInput, pl));
+    case MCA_FN_DECODE_FFN: return finish(k, decode_ffn(k, lInput, pf, llInput, pl));
+    case MCA_FN_DECODE_LOGITS: return finish(k, decode_logits(k, lInput, pf, llInput, pl));
     case MCA_FN_TFT_ATTN_FWD: return finish(k, tft_fwd(k, llInput, pl));
     case MCA_FN_TFT_ATTN_BWD: return finish(k, tft_bwd(k, llInput, pl));
     case MCA_FN_ATTN_FWD_HOST:

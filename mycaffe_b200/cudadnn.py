@@ -227,6 +227,14 @@ class CudaDnn:
         """x += Wo . attn (llama2_gpu.cpp:78-81)."""
         self._invoke(ids.MCA_FN_DECODE_OUT, None, [hAttn, hWo, nBatch, nDim, hX])
 
+    def DecodeFfn(self, hX, hRmsW, hW1, hW2, hW3, nBatch, nDim, nHiddenDim, hHidden, fEps=1e-5):
+        """x += W2 . (silu(W1 xn) * (W3 xn)), xn = rmsnorm(x) (llama2_gpu.cpp:84-97)."""
+        self._invoke(ids.MCA_FN_DECODE_FFN, [float(fEps)], [hX, hRmsW, hW1, hW2, hW3, nBatch, nDim, nHiddenDim, hHidden])
+
+    def DecodeLogits(self, hX, hRmsW, hWcls, nBatch, nDim, nVocab, hLogits, fEps=1e-5):
+        """logits = Wcls . rmsnorm(x) (llama2_gpu.cpp:101-105)."""
+        self._invoke(ids.MCA_FN_DECODE_LOGITS, [float(fEps)], [hX, hRmsW, hWcls, nBatch, nDim, nVocab, hLogits])
+
     def AttnScaledDotProductForwardPacked(self, hCuDnn, hAttn, nBlockSize, hQKV, hMask, hY, bBatchMask=False):
         """ATTN_FWD on the (B,T,3C) c_attn output: q, k, v are read in place, y is written as (B,T,C)."""
         self._invoke(ids.MCA_FN_ATTN_FWD_PACKED, None,

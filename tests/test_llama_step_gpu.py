@@ -242,3 +242,36 @@ def test_step_rejects_bad_arguments():
     assert lib.mca_llama_workspace_floats(C.byref(good), 3, 41) == -1          # longer than the cache
     assert lib.mca_llama_workspace_floats(C.byref(McaLlamaConfig(256, 344, 2, 4, 3, 64, 40)), 1, 8) == -1
     assert lib.mca_llama_forward(C.byref(good), None, None, None, None, 1, 8, None, None) == ids.ERROR_PARAM_NULL
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_feed_forward_and_classifier_function_ids(bf16):
+    """The handle-based route (ids 2015 / 2016) a host that owns its tensors through ALLOCMEM takes."""
+    from mycaffe_b200 import CudaDnn
+    cuda = CudaDnn(0)
+    B, dim, hidden, vocab = 3, 512, 1376, 333
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((B, dim)).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    w1, w3 = (0.05 * rng.standard_normal((hidden, dim))).astype(np.float32), (0.05 * rng.standard_normal((hidden, dim))).astype(np.float32)
+    w2, wc = (0.05 * rng.standard_normal((dim, hidden))).astype(np.float32), (0.05 * rng.standard_normal((vocab, dim))).astype(np.float32)
+    if bf16:
+        w1, w2, w3, wc = (bf16_round(a) for a in (w1, w2, w3, wc))
+    alloc_w = cuda.AllocMemoryBf16 if bf16 else cuda.AllocMemory
+    hX, hG, hH, hL = cuda.AllocMemory(x), cuda.AllocMemory(g), cuda.AllocMemory(B * hidden), cuda.AllocMemory(B * vocab)
+    hW1, hW2, hW3, hWc = alloc_w(w1), alloc_w(w2), alloc_w(w3), alloc_w(wc)
+    cuda.DecodeFfn(hX, hG, hW1, hW2, hW3, B, dim, hidden, hH)
+    got_x = cuda.GetMemory(hX, x.size).reshape(x.shape)
+    cuda.DecodeLogits(hX, hG, hWc, B, dim, vocab, hL)
+    got_l = cuda.GetMemory(hL, B * vocab).reshape(B, vocab)
+    ref_x = np.empty_like(x)
+    for b in range(B):
+        xn = oracle.rmsnorm(x[b], g)
+        a, c = oracle.gemv(w1, xn), oracle.gemv(w3, xn)
+        ref_x[b] = x[b] + oracle.gemv(w2, a * (1.0 / (1.0 + np.exp(-a))) * c)
+    ref_l = np.stack([oracle.gemv(wc, oracle.rmsnorm(ref_x[b], g)) for b in range(B)])
+    assert rel_err(got_x, ref_x) < 1e-4
+    assert rel_err(got_l, ref_l) < 1e-4
+    for h in (hX, hG, hH, hL, hW1, hW2, hW3, hWc):
+        cuda.FreeMemory(h)
+    cuda.Dispose()
