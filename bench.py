@@ -249,6 +249,10 @@ def run_ours(args):
         if args.cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_prefill(T, D, H)
             line["decode"]["cpu_baseline"] = cpu_baseline_decode()
+            try:
+                line["decode"]["whole_model"] = whole_model_decode()
+            except Exception as exc:   # an extra; never the reason the bench line is lost
+                line["decode"]["whole_model"] = {"unavailable": repr(exc)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -426,6 +430,56 @@ def cpu_baseline_prefill(T, D, H, q_step=4, heads=16):
     return {"value": round(flops / dt / 1e12, 5), "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
             "sample": f"{len(rows)} strided query rows x {heads} heads of the T={T} causal problem "
                       f"({flops / 1e9:.1f} GFLOP, {dt:.1f} s); full-problem time extrapolated from this rate"}
+
+
+def whole_model_decode(tokens=24, start=200):
+    """Token -> logits for a llama2.c-110M-shaped model (dim 768, 12 layers, 12 heads of 64, hidden 2048,
+    vocabulary 8000, fp32), one sequence, on the SAME checkpoint file by both sides: TransformerGpu.forward
+    (mca_llama_forward replayed from one CUDA graph + the logits copy to the host, as the reference's
+    TransformerGpu::forward returns them) and the reference's own TransformerCpu::forward compiled from its source.  Both first
+    fill positions 0..start-1, then `tokens` steps are timed; the logits of the last step are compared."""
+    import oracle
+    import tempfile
+    from mycaffe_b200.llama2 import TransformerGpu
+    if oracle.ref_lib() is None:
+        return {"unavailable": "compiled reference twin not built"}
+    dim, hidden, L, H, vocab, S = 768, 2048, 12, 12, 8000, 512
+    rng = np.random.default_rng(0)
+    g = lambda *sh: (0.04 * rng.standard_normal(sh)).astype(np.float32)
+    w = {"rms_att_weight": np.ones((L, dim), np.float32), "rms_ffn_weight": np.ones((L, dim), np.float32),
+         "rms_final_weight": np.ones(dim, np.float32), "token_embedding_table": rng.standard_normal((vocab, dim)).astype(np.float32),
+         "wq": g(L, dim, dim), "wk": g(L, dim, dim), "wv": g(L, dim, dim), "wo": g(L, dim, dim),
+         "w1": g(L, hidden, dim), "w2": g(L, dim, hidden), "w3": g(L, hidden, dim)}
+    toks = rng.integers(0, vocab, start + tokens)
+    with tempfile.TemporaryDirectory() as td:
+        path = os.path.join(td, "m110.bin")
+        oracle.write_llama_checkpoint(path, dim, hidden, L, H, H, vocab, S, w)
+        t = TransformerGpu(0, use_graph=True)
+        t.build(path)
+        for pos in range(start):
+            t.forward(int(toks[pos]), pos)
+        t0 = time.perf_counter()
+        for pos in range(start, start + tokens):
+            got = t.forward(int(toks[pos]), pos)
+        gpu_dt = (time.perf_counter() - t0) / tokens
+        ref = oracle.RefLlama(path)
+        for pos in range(start):
+            ref.forward(int(toks[pos]), pos)
+        t0 = time.perf_counter()
+        for pos in range(start, start + tokens):
+            ref.forward(int(toks[pos]), pos)
+        cpu_dt = (time.perf_counter() - t0) / tokens
+        want = ref.state("logits").copy()
+        ref.close()
+    err = float(np.abs(got - want).max() / np.abs(want).max())
+    params = L * (4 * dim * dim + 3 * dim * hidden) + vocab * dim
+    return {"workload": f"llama2.c 110M geometry (dim {dim}, {L} layers, {H} heads, hidden {hidden}, vocab {vocab}), fp32, "
+                        f"1 sequence, positions {start}..{start + tokens - 1}, host call to host logits",
+            "value": round(1.0 / gpu_dt, 1), "unit": "tok/s", "ms_per_token": round(gpu_dt * 1e3, 4),
+            "weight_GBps": round(params * 4 / gpu_dt / 1e9, 1),
+            "reference_cpu": {"value": round(1.0 / cpu_dt, 2), "unit": "tok/s", "kind": "reference", "cores": oracle.num_threads(),
+                              "sample": f"TransformerCpu::forward on the same checkpoint, {tokens} tokens"},
+            "max_rel_err_vs_reference": err}
 
 
 def cpu_baseline_decode(L=2304, dim=4096, n_heads=32):

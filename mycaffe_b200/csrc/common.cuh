@@ -85,6 +85,13 @@ __host__ __device__ static inline int mca_ceil_div(int a, int b) { return (a + b
 // earlier kernels of the stream have completed and their writes are visible; in a kernel that was
 // launched the ordinary way both calls do nothing.
 #ifdef __CUDACC__
+// 16-byte asynchronous copy global -> shared, bypassing L1; groups complete in order.
+__device__ __forceinline__ void mca_cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void mca_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void mca_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ void mca_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void mca_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

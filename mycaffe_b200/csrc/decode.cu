@@ -99,11 +99,6 @@ template <> struct Row16<__nv_bfloat16> {
 // (two vectors of the K row, two of the V row), so no synchronisation other than its own wait_group is needed.
 constexpr int DEC_RING = 6;   // row steps in flight per warp (96 KB per CTA: two CTAs per SM overlap their ramps)
 constexpr size_t DEC_RING_BYTES = (size_t)DEC_WARPS * DEC_RING * 4 * 32 * sizeof(uint4);   // per CTA
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void unpack_bf16x8(const uint4& t, float* x) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -190,19 +185,19 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
           const uint32_t dst = my_ring_s + (uint32_t)(((t % DEC_RING) * 4 * 32 + lane) * sizeof(uint4));
           const uint4* ks = reinterpret_cast<const uint4*>(kcb + (int64_t)row * kv_dim);
           const uint4* vs = reinterpret_cast<const uint4*>(vcb + (int64_t)row * kv_dim);
-          cp_async16(dst, ks + gl);
-          cp_async16(dst + 32 * sizeof(uint4), ks + G + gl);
-          cp_async16(dst + 64 * sizeof(uint4), vs + gl);
-          cp_async16(dst + 96 * sizeof(uint4), vs + G + gl);
+          mca_cp_async16(dst, ks + gl);
+          mca_cp_async16(dst + 32 * sizeof(uint4), ks + G + gl);
+          mca_cp_async16(dst + 64 * sizeof(uint4), vs + gl);
+          mca_cp_async16(dst + 96 * sizeof(uint4), vs + G + gl);
         }
       }
-      cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
+      mca_cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
     };
 #pragma unroll
     for (int t = 0; t < DEC_RING - 1; ++t) issue(t);
     for (int t = 0; t < n_steps; ++t) {
       issue(t + DEC_RING - 1);     // its slot was read in the previous iteration
-      cp_async_wait<DEC_RING - 1>();
+      mca_cp_async_wait<DEC_RING - 1>();
       const int row = first + t * stride + g;
       const bool valid = row < r_end;
       float kx[EPL], vx[EPL];
@@ -253,7 +248,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
         }
       }
     }
-    cp_async_wait<0>();
+    mca_cp_async_wait<0>();
   } else {
   for (int base = r_begin + warp * RPW; base < r_end; base += DEC_WARPS * RPW * U) {
     float kx[U][EPL], vx[U][EPL];

@@ -34,12 +34,6 @@ namespace {
 constexpr int GV_SPLIT_STEPS = 16;   // row steps a K-split group may own (their sums wait in registers)
 constexpr size_t GV_SMEM_LIMIT = 226 * 1024;
 
-__device__ __forceinline__ void gv_cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-__device__ __forceinline__ void gv_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void gv_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 template <typename WT> struct WLoad;
 template <> struct WLoad<float> {
   static constexpr int VEC = 4;
@@ -126,12 +120,12 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const GemvParams p
         if (k < n) {
 #pragma unroll
           for (int q = 0; q < R; ++q)
-            gv_cp_async16(my_ring_s + (uint32_t)((((i_slot * R + q) * U + u) * 32 + lane) * sizeof(uint4)), i_ptr[q] + k);
+            mca_cp_async16(my_ring_s + (uint32_t)((((i_slot * R + q) * U + u) * 32 + lane) * sizeof(uint4)), i_ptr[q] + k);
         }
       }
       if (++i_c == c_hi) { i_c = c_lo; ++i_step; set_issue_rows(); }
     }
-    gv_cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
+    mca_cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
     i_slot = (i_slot + 1 == DEPTH) ? 0 : i_slot + 1;
   };
   // The first weight vectors leave for HBM before anything else -- also before the kernel that
@@ -221,7 +215,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const GemvParams p
   int c = c_lo, step = 0, slot = 0;
   for (int t = 0; t < T; ++t) {
     issue();
-    gv_cp_async_wait<DEPTH - 1>();
+    mca_cp_async_wait<DEPTH - 1>();
 #pragma unroll
     for (int u = 0; u < U; ++u) {
     const int k = ((c * U + u) * 32 + lane) * VEC;
@@ -268,7 +262,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const GemvParams p
       c = c_lo; ++step;
     }
   }
-  gv_cp_async_wait<0>();
+  mca_cp_async_wait<0>();
   if (S == 1) return;   // uniform over the CTA
 
   // ---- K-split groups: partial sums -> this warp's (now idle) ring -> added in warp order

@@ -79,7 +79,7 @@ def read_checkpoint(path):
 class TransformerGpu:
     """``build(checkpoint)`` then ``forward(token, pos)`` -> logits, as the reference class."""
 
-    def __init__(self, device=0, batch=1, weights_bf16=False, cache_bf16=False, max_seq_len=None):
+    def __init__(self, device=0, batch=1, weights_bf16=False, cache_bf16=False, max_seq_len=None, use_graph=False):
         import torch
         if not torch.cuda.is_available():
             raise RuntimeError("TransformerGpu needs a CUDA device: there is no CPU path")
@@ -89,6 +89,8 @@ class TransformerGpu:
         self.batch = int(batch)
         self.weights_bf16, self.cache_bf16 = bool(weights_bf16), bool(cache_bf16)
         self.max_seq_len = max_seq_len
+        self.use_graph = bool(use_graph)   # replay the step from one CUDA graph (small models are launch-bound)
+        self._graph = None
         self.config = None
 
     # -- build ------------------------------------------------------------------------------
@@ -102,6 +104,7 @@ class TransformerGpu:
         if self.max_seq_len:
             cfg = dict(cfg, seq_len=min(cfg["seq_len"], int(self.max_seq_len)))
         self.config = cfg
+        self._graph = None
         hs = cfg["dim"] // cfg["n_heads"]
         kv_dim = cfg["n_kv_heads"] * hs
         wdt = torch.bfloat16 if self.weights_bf16 else torch.float32
@@ -156,6 +159,21 @@ class TransformerGpu:
         if rc:
             raise RuntimeError(f"mca_llama_forward failed with {rc}")
 
+    def _capture(self):
+        """One graph serves every token: tokens and positions are read from device memory, and the
+        split plan is the one for the longest sequence the cache holds (splits beyond a sequence's
+        length return at once)."""
+        torch = self._torch
+        side = torch.cuda.Stream(self.device)
+        graph = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            self.enqueue(self.config["seq_len"], stream=side)
+            graph.capture_end()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self._graph = graph
+
     def forward_batch(self, tokens, pos):
         """tokens, pos: ``batch`` ints each -> logits (batch, vocab_size) on the host."""
         torch = self._torch
@@ -168,7 +186,14 @@ class TransformerGpu:
         with torch.cuda.device(self.device):
             self._tokens.copy_(torch.from_numpy(tokens))
             self._pos.copy_(torch.from_numpy(pos))
-            self.enqueue(int(pos.max()) + 1)
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self.enqueue(int(pos.max()) + 1)     # also the warm-up that precedes a capture
+                if self.use_graph:
+                    result = self.logits.cpu().numpy()
+                    self._capture()
+                    return result
             return self.logits.cpu().numpy()
 
     def forward(self, token, pos):

@@ -31,8 +31,9 @@ def need_ref():
         pytest.skip("compiled reference twin not available")
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
 @pytest.mark.parametrize("dim,hidden,n_layers,n_heads,n_kv", [(256, 344, 3, 4, 4), (512, 1376, 2, 4, 4), (1024, 96, 1, 8, 8)])
-def test_generation_matches_reference_transformer(tmp_path, dim, hidden, n_layers, n_heads, n_kv):
+def test_generation_matches_reference_transformer(tmp_path, dim, hidden, n_layers, n_heads, n_kv, use_graph):
     """Token by token from an empty cache: logits of every step and the caches at the end equal
     TransformerCpu::forward's on the same checkpoint file."""
     need_ref()
@@ -43,7 +44,7 @@ def test_generation_matches_reference_transformer(tmp_path, dim, hidden, n_layer
     path = tmp_path / "m.bin"
     oracle.write_llama_checkpoint(path, dim, hidden, n_layers, n_heads, n_kv, vocab, seq_len, w)
     ref = oracle.RefLlama(path)
-    t = TransformerGpu(0)
+    t = TransformerGpu(0, use_graph=use_graph)
     t.build(str(path))
     assert t.config == dict(dim=dim, hidden_dim=hidden, n_layers=n_layers, n_heads=n_heads, n_kv_heads=n_kv,
                             vocab_size=vocab, seq_len=seq_len)
