@@ -160,15 +160,17 @@ def run_ours(args):
                 peer_out = None
                 exchange += f" (symmetric memory unavailable: {type(exc).__name__})"
 
+    use_fused = [peer_out is not None]
+
     def launch_prefill():
-        if peer_out is not None:
+        if use_fused[0]:
             return lib.mca_sdpa_forward_tc_scatter(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
                                                    peer_dst, world, ysb, ysh, yst, None, status.data_ptr(), sp)
         return lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, Hl, T, D,
                                        y.data_ptr(), None, status.data_ptr(), sp)
 
     def exchange_outputs():
-        if peer_out is not None:
+        if use_fused[0]:
             peer_out.wait()
         elif world > 1:
             head_shard.gather_heads(y, out=y_all, strided=True)
@@ -193,6 +195,26 @@ def run_ours(args):
         if rc or not torch.equal(ref, peer_out.tensor):
             raise RuntimeError("peer-store exchange disagrees with the NCCL all-gather")
         del ref
+        # Both exchanges are correct; time two steps of each (max over ranks) and keep the faster one for this size.
+        trial = {}
+        for name, flag in (("fused", True), ("nccl", False)):
+            use_fused[0] = flag
+            prefill_step()
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            prefill_step()
+            prefill_step()
+            t1.record(stream)
+            barrier()
+            tt = torch.tensor([t0.elapsed_time(t1) / 2], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            trial[name] = float(tt.item())
+        use_fused[0] = trial["fused"] <= trial["nccl"]
+        if not use_fused[0]:
+            exchange = "nccl all-gather after the kernel"
+        exchange += " (chosen by a two-step trial: epilogue peer stores %.3f ms, kernel + NCCL all-gather %.3f ms per step)" % (
+            trial["fused"], trial["nccl"])
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

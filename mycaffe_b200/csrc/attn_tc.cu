@@ -494,6 +494,51 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
         float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
+        bool scattered = false;
+        if constexpr (!TF32) {
+          if (p.n_more > 0) {   // uniform over the grid
+            // Output that also goes to peers' buffers: stage this warp's 32 rows x OC columns in the shared memory
+            // of its query tile (every product that read it has completed), then store whole 16-byte pieces so
+            // that one store instruction covers full contiguous row segments (128 bytes at head size 128)
+            // instead of 32 pieces from 32 different rows: NVLink carries them as full packets.
+            scattered = true;
+            constexpr int PIECES = OC * 2 / 16;          // 16-byte pieces of a row-half
+            constexpr int RPI = 32 / PIECES;             // rows one store instruction covers
+            uint4* stage = reinterpret_cast<uint4*>(smem_gen + PL::OFF_Q + x * PL::TILE_BYTES) +
+                           (size_t)((warp & 3) * 2 + half) * 32 * PIECES;   // private to this warp
+#pragma unroll
+            for (int c = 0; c < OC / 16; ++c) {
+              uint32_t o[16];
+              tmem_ld16(t_o32 + c * 16, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; i += 8) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+                w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                const int piece = c * 2 + i / 8;
+                stage[lane * PIECES + (piece ^ (lane & (PIECES - 1)))] = w;   // swizzled against bank conflicts
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int kk = 0; kk < PIECES; ++kk) {
+              const int r = kk * RPI + lane / PIECES, pc = lane % PIECES;
+              const uint4 w = stage[r * PIECES + (pc ^ (r & (PIECES - 1)))];
+              const int qr = qrow0 + (warp & 3) * 32 + r;
+              if (qr < T) {
+                const int64_t off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qr * p.ys.t + half * OC + pc * 8;
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + off) = w;
+#pragma unroll
+                for (int d = 0; d < 7; ++d)   // constant indices: the parameter block is not copied to local memory
+                  if (d < p.n_more) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + off) = w;
+              }
+            }
+          }
+        }
+        if (!scattered) {
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t o[16];
@@ -516,12 +561,9 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
               w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
               *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
-              // the same 16 bytes to every further destination: plain stores, over NVLink when it is a peer's buffer
-#pragma unroll
-              for (int d = 0; d < 7; ++d)   // constant indices: the parameter block is not copied to local memory
-                if (d < p.n_more) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + y_off + c * 16 + i) = w;
             }
           }
+        }
         }
         if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum);
       }
