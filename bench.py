@@ -58,15 +58,56 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples during the timed region."""
+    """SM clock and throttle-reason samples during the timed region (read-only queries).  NVML through
+    pynvml when it loads: a sample costs microseconds, so that a timed region of a few milliseconds still gets
+    several; otherwise `nvidia-smi -lms 20`, whose first line arrives after about 100 ms."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index):
         self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.nvml, self.handle, self.samples, self.run = None, None, [], False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # CUDA_VISIBLE_DEVICES may renumber the devices: look the handle up by the CUDA device's PCI bus id
+            import torch
+            bus = torch.cuda.get_device_properties(gpu_index).pci_bus_id if hasattr(torch.cuda.get_device_properties(gpu_index), "pci_bus_id") else None
+            self.handle = None
+            if bus is not None:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    if int(pynvml.nvmlDeviceGetPciInfo(h).bus) == int(bus):
+                        self.handle = h
+                        break
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.nvml = pynvml
+        except Exception:  # noqa: BLE001 - any NVML problem selects nvidia-smi
+            self.nvml = None
+
+    def _nvml_loop(self):
+        n = self.nvml
+        masks = [n.nvmlClocksEventReasonHwSlowdown, n.nvmlClocksEventReasonHwThermalSlowdown,
+                 n.nvmlClocksEventReasonSwThermalSlowdown, n.nvmlClocksEventReasonSwPowerCap]
+        while self.run:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                smax = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+                bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((float(sm), float(smax), [nm for nm, m in zip(self.NAMES, masks) if bits & m]))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        if self.nvml is not None:
+            self.run = True
+            self.t = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.t.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "20", "-i", str(self.gpu_index)],
@@ -81,6 +122,14 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.run = False
+            self.t.join(timeout=1)
+            sm = [s_[0] for s_ in self.samples]
+            reasons = sorted({r for s_ in self.samples for r in s_[2]})
+            return {"sm_mhz": float(np.median(sm)) if sm else None,
+                    "sm_max_mhz": max(s_[1] for s_ in self.samples) if self.samples else None,
+                    "reasons": reasons, "samples": len(sm), "source": "nvml"}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -89,7 +138,6 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
@@ -98,11 +146,11 @@ class ClockSampler:
                 sm.append(float(f[1])); smax.append(float(f[2]))
             except ValueError:
                 continue
-            for name, val in zip(names, f[5:9]):
+            for name, val in zip(self.NAMES, f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------------------------- ours
