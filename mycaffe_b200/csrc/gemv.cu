@@ -338,6 +338,7 @@ int run_gemv(const GemvParams& p, cudaStream_t st) {
   constexpr size_t RING_512 = ring_bytes<2, 512, 6>(), RING_256 = ring_bytes<2, 256, 6>();
   constexpr size_t RING_1 = ring_bytes<1, 256, 4, 4>();   // = ring_bytes<2, 256, 4, 2>(), the one- and two-sequence kernels
   if (!fits(1, RING_1)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  const bool deep = xbytes + ring_bytes<1, 256, 6, 4>() <= 112 * 1024;   // half an SM's shared memory, less the per-CTA reserve
   for (int b0 = 0; b0 < p.B && !e;) {
     const int left = p.B - b0;
     if (p.swiglu) {
@@ -345,13 +346,19 @@ int run_gemv(const GemvParams& p, cudaStream_t st) {
       else if (left >= 4 && fits(4, RING_512)) { e = launch_pass<WT, 4, 2, 512, true, 6>(p, b0, st); b0 += 4; }
       else if (left >= 4 && fits(4, RING_256)) { e = launch_pass<WT, 4, 2, 256, true, 6>(p, b0, st); b0 += 4; }
       else if (left >= 2 && fits(2, RING_1)) { e = launch_pass<WT, 2, 2, 256, true, 4, 2>(p, b0, st); b0 += 2; }
-      else { e = launch_pass<WT, 1, 2, 256, true, 4, 2>(p, b0, st); b0 += 1; }
+      else {   // a deeper ring while two CTAs per SM still fit
+        e = deep ? launch_pass<WT, 1, 2, 256, true, 6, 2>(p, b0, st) : launch_pass<WT, 1, 2, 256, true, 4, 2>(p, b0, st);
+        b0 += 1;
+      }
     } else {
       if (left >= 8 && fits(8, RING_512)) { e = launch_pass<WT, 8, 2, 512, false, 6>(p, b0, st); b0 += 8; }
       else if (left >= 4 && fits(4, RING_512)) { e = launch_pass<WT, 4, 2, 512, false, 6>(p, b0, st); b0 += 4; }
       else if (left >= 4 && fits(4, RING_256)) { e = launch_pass<WT, 4, 2, 256, false, 6>(p, b0, st); b0 += 4; }
       else if (left >= 2 && fits(2, RING_1)) { e = launch_pass<WT, 2, 1, 256, false, 4, 4>(p, b0, st); b0 += 2; }
-      else { e = launch_pass<WT, 1, 1, 256, false, 4, 4>(p, b0, st); b0 += 1; }
+      else {
+        e = deep ? launch_pass<WT, 1, 1, 256, false, 6, 4>(p, b0, st) : launch_pass<WT, 1, 1, 256, false, 4, 4>(p, b0, st);
+        b0 += 1;
+      }
     }
   }
   return e;
