@@ -53,6 +53,11 @@ typedef char* MCA_LPTSTR;
 #define CUDA_FN_SETMEM 23          /* longs {h,count}, floats {h,count,data...} (device.cu:1029) */
 #define CUDNN_FN_CREATE_CUDNN 47   /* -> out[0] = hCuDnn (passed through by ATTN_*) */
 #define CUDNN_FN_FREE_CUDNN 48
+#define CUDA_FN_CREATE_EXTENSION 67 /* DLL_InvokeFloatEx, string = path of the extension library ("" = this library's own
+                                       llama2 extension) -> out[0] = hExtension          (device.h:4498-4524) */
+#define CUDA_FN_FREE_EXTENSION 68   /* floats {hExtension}                               (device.h:4556-4566) */
+#define CUDA_FN_EXTENSION_RUN 69    /* floats {hExtension, extensionFn, args...}; through DLL_InvokeFloatEx the string
+                                       goes to the extension's ...Ex entry             (device.h:4570-4588, CudaDnnDLL.cpp:1053-1064) */
 #define CUDNN_FN_ATTN_CREATE 160   /* -> out[0] = hAttn                      (device.h:2435-2448) */
 #define CUDNN_FN_ATTN_FREE 161     /* floats {hAttn}                          (device.h:2450-2461) */
 #define CUDNN_FN_ATTN_SET 162      /* floats {dropout}; longs {hCuDnn,hAttn,gpuId,bTraining,B,blockSize,H,D,seed}
@@ -67,6 +72,9 @@ typedef char* MCA_LPTSTR;
 #define CUDA_FN_FREE_ROPE 981      /* floats {hRope} */
 #define CUDA_FN_ROPE_FWD 982       /* longs {hRope,n,hX,hY[,freqOffset]}      (device.h:4243-4265) */
 #define CUDA_FN_ROPE_BWD 983       /* longs {hRope,n,hX,hYdiff,hXdiff}        (device.h:4267-4283) */
+/* ids of DLL_QueryString / DLL_QueryStringFloatEx (Cuda Files/main.h:37-40) */
+#define CUDA_FN_GET_DEVICE_NAME 1000      /* longs {deviceId} -> "<name> (<GB> GB - P2P on|off; compute M.m)" (device.cu:528-554) */
+#define CUDA_FN_GET_EXTENSION_STRING 1003 /* DLL_QueryStringFloatEx: longs {hExtension, extensionFn, args...} -> extension's string */
 /* Ids added by this library (no counterpart in the reference; above its highest id). */
 #define MCA_FN_ALLOCMEM_BF16 2001  /* longs {count} -> handle to bf16 storage; SETMEM/GETMEM convert from/to float */
 #define MCA_FN_CONVERT 2002        /* longs {hSrc,hDst,count}: copy with float<->bf16 conversion as the handles require */
@@ -86,6 +94,23 @@ typedef char* MCA_LPTSTR;
 #define MCA_FN_RMSNORM_FWD 2040    /* floats {eps}; longs {hX,hW (0: none),hY,hInvRms,rows,inner}: RMSNormLayer forward in one pass */
 #define MCA_FN_RMSNORM_BWD 2041    /* longs {hX,hW,hdY,hInvRms,hdX,hdW (0: frozen),rows,inner}: its backward */
 #define MCA_FN_SET_ASYNC 2030      /* longs {0|1}: 1 = do not synchronise the stream after each call (default 0, as the reference) */
+#define MCA_FN_SET_TIMING 2031     /* longs {0|1}: 1 = bracket every dispatched call with CUDA events (read with MCA_FN_QUERY_COUNTERS) */
+#define MCA_FN_WAIT_PROBE 2032     /* longs {hAttn, limitMicroseconds}: runs mca_wait_probe on the handle's status words, then reports
+                                      them as a tensor-core launch would (ERROR_ATTN_KERNEL_TIMEOUT); a self-check, no tensor work */
+#define MCA_FN_QUERY_VERSION 2050  /* DLL_QueryString: the text of mca_version() */
+#define MCA_FN_QUERY_COUNTERS 2051 /* DLL_QueryString: one line per function id used on this kernel index:
+                                      "<id> calls=<n> errors=<n> gpu_ms_last=<t> gpu_ms_total=<t>" (times only while timing is on) */
+
+/* Function ids of the llama2 extension (CudaExtension.llm32.llama2/CudaExtension.llm32.cpp:20-26). */
+#define LLM_CUDA_EXTENSION_CREATE 1        /* floats {temperature, top-p, seed} (all optional) -> out[0] = hLlm */
+#define LLM_CUDA_EXTENSION_DESTROY 2       /* floats {hLlm} */
+#define LLM_CUDA_EXTENSION_LOAD 3          /* Ex: floats {hLlm}, string "model.bin;tokenizer.bin" (the tokenizer part is not read) */
+#define LLM_CUDA_EXTENSION_QUERYSTATUS 4   /* floats {hLlm} -> {fraction loaded, status (1 = loaded)} */
+#define LLM_CUDA_EXTENSION_GENERATE 5      /* not provided: tokenizer and sampler are outside this library */
+#define LLM_CUDA_EXTENSION_QUERYRESPONSE 6 /* not provided */
+#define LLM_CUDA_EXTENSION_ABORT 7         /* floats {hLlm}: sets the cancel flag */
+#define MCA_LLM_EXTENSION_FORWARD 100      /* added: floats {hLlm, token, pos} -> logits (vocab_size floats): one
+                                              TransformerGpu::forward(token, pos), llama2_gpu.cpp:32-111 */
 
 /* 10th long of ATTN_SET */
 #define MCA_DTYPE_F32 0   /* exact fp32 arithmetic on CUDA cores (default; what the reference computes) */
@@ -130,11 +155,56 @@ MCA_API MCA_LONG DLL_InvokeDouble(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, do
 MCA_API MCA_LONG DLL_InvokeDoubleEx2(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, double* pInput, MCA_LONG lInput,
                                      MCA_LONGLONG* plInput, MCA_LONG llInput, double** ppOutput,
                                      MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+/* Replaces DLL_InvokeDoubleEx, CudaDnnDLL.cpp:1090-1160 (ordinal 5): ERROR_NOT_IMPLEMENTED as the other double entries. */
+MCA_API MCA_LONG DLL_InvokeDoubleEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, double* pInput, MCA_LONG lInput,
+                                    MCA_LPTSTR pszInput, double** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr,
+                                    MCA_LONG lszErrMax);
+/* Replaces DLL_QueryString, CudaDnnDLL.cpp:855-933 (ordinal 3).  pInput are 32-bit LONGs.  The answer is a
+ * malloc'ed string returned through *ppOutput; the caller hands it back with lFunctionIdx = CUDA_DLL_FREEMEM.
+ * Ids: CUDA_FN_GET_DEVICE_NAME, MCA_FN_QUERY_VERSION, MCA_FN_QUERY_COUNTERS; others ERROR_PARAM_OUT_OF_RANGE
+ * (what Kernel<T>::Query answers for an id it does not know, Cuda Files/main.cu:2457-2478). */
+MCA_API MCA_LONG DLL_QueryString(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, MCA_LONG* pInput, MCA_LONG lInput,
+                                 MCA_LPTSTR* ppOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+/* Replace DLL_QueryStringFloatEx / DLL_QueryStringDoubleEx, CudaDnnDLL.cpp:935-1015: the answer is written into the
+ * caller's buffer.  Id CUDA_FN_GET_EXTENSION_STRING forwards to the extension's ...Ex entry and appends "\n[END]"
+ * when the extension reports the end of its text (extension.cu:153-180).  The double form returns ERROR_NOT_IMPLEMENTED. */
+MCA_API MCA_LONG DLL_QueryStringFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, MCA_LONG* pInput, MCA_LONG lInput,
+                                        MCA_LPTSTR pszOutput, MCA_LONG lOutputMax, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
+MCA_API MCA_LONG DLL_QueryStringDoubleEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, MCA_LONG* pInput, MCA_LONG lInput,
+                                         MCA_LPTSTR pszOutput, MCA_LONG lOutputMax, MCA_LPTSTR szErr, MCA_LONG lszErrMax);
 /* Replaces Internal_GetPointerFloat, CudaDnnDLL.cpp:57-73: raw device pointer behind a memory handle. */
 MCA_API MCA_LONG Internal_GetPointerFloat(MCA_LONG ht, MCA_LONG lKernelIdx, MCA_LONG hHandle, void** ppPtr);
 /* Replaces Internal_AllocHostFloat, CudaDnnDLL.cpp:93-109: pinned host buffer, optionally filled from pSrc. */
 MCA_API MCA_LONG Internal_AllocHostFloat(MCA_LONG lKernelIdx, MCA_LONG lCount, float** ppDst, float* pSrc,
                                          bool bSrcOnDevice);
+/* Replace Internal_GetPointerDouble / Internal_AllocHostDouble, CudaDnnDLL.cpp:75-91,111-127 (ordinals 101, 103).  No
+ * double kernel can exist here (INITIALIZE through DLL_InvokeDouble is refused), so both answer ERROR_PARAM_NULL --
+ * the reference's answer for a slot of its double table that holds no kernel. */
+MCA_API MCA_LONG Internal_GetPointerDouble(MCA_LONG ht, MCA_LONG lKernelIdx, MCA_LONG hHandle, void** ppPtr);
+MCA_API MCA_LONG Internal_AllocHostDouble(MCA_LONG lKernelIdx, MCA_LONG lCount, double** ppDst, double* pSrc,
+                                          bool bSrcOnDevice);
+
+/* ---- 1b. extension ABI of the llama2 route ------------------------------------------------ */
+/* What a parent CudaDnnDLL resolves in an extension library after LoadLibrary (Cuda Files/extension.cu:18-83,
+ * extension.h:20-38).  This library is such an extension: it replaces CudaExtension.llm32.llama2
+ * (CudaExtension.llm32.cpp:67-83 init, :91-205 invoke, :213-268 invoke-ex) for loading a llama2 'ak42' checkpoint and
+ * running TransformerGpu::forward on it; text generation (tokenizer, sampler) is not part of it.
+ * hParent: module handle of the parent (a dlopen handle here; HMODULE on Windows); the extension resolves
+ * DLL_InvokeFloat and Internal_AllocHostFloat in it and returns 87 (ERROR_INVALID_PARAMETER) when either is missing.
+ * Results are returned in buffers from the parent's Internal_AllocHostFloat, as the reference requires. */
+MCA_API MCA_LONG DLL_InitFloatCustomExtension(void* hParent, MCA_LONG lKernelIdx);
+MCA_API MCA_LONG DLL_InvokeFloatCustomExtension(MCA_LONG lfnIdx, float* pInput, MCA_LONG lInput, float** ppOutput,
+                                                MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lErrMax);
+MCA_API MCA_LONG DLL_InvokeFloatCustomExtensionEx(MCA_LONG lfnIdx, float* pInput, MCA_LONG lInput, float** ppOutput,
+                                                  MCA_LONG* plOutput, MCA_LPTSTR szInput, MCA_LPTSTR szOutput,
+                                                  MCA_LONG lOutputMax, MCA_LPTSTR szErr, MCA_LONG lErrMax);
+/* The double forms (CudaExtension.llm32.cpp:275-490): ERROR_NOT_IMPLEMENTED. */
+MCA_API MCA_LONG DLL_InitDoubleCustomExtension(void* hParent, MCA_LONG lKernelIdx);
+MCA_API MCA_LONG DLL_InvokeDoubleCustomExtension(MCA_LONG lfnIdx, double* pInput, MCA_LONG lInput, double** ppOutput,
+                                                 MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lErrMax);
+MCA_API MCA_LONG DLL_InvokeDoubleCustomExtensionEx(MCA_LONG lfnIdx, double* pInput, MCA_LONG lInput, double** ppOutput,
+                                                   MCA_LONG* plOutput, MCA_LPTSTR szInput, MCA_LPTSTR szOutput,
+                                                   MCA_LONG lOutputMax, MCA_LPTSTR szErr, MCA_LONG lErrMax);
 
 /* ---- 2. raw entry points ------------------------------------------------------------------ */
 /* All tensors are contiguous row-major device memory; `stream` is a cudaStream_t (0 = default). */
@@ -178,6 +248,12 @@ MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* 
  * status: device int[4] the kernel writes when a bounded wait gives up (0 = ok). */
 MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                 int T, int D, void* y, float* lse, int* status, void* stream);
+
+/* Self-check of the bounded waits inside the tensor-core kernels: launches one small kernel whose only thread waits
+ * on a barrier nothing arrives on, for at most limit_us microseconds (<= 100000), then gives up the way a stalled
+ * pipeline stage would: status[0] = 1, status[1] = 99, and the kernel returns.  Nothing hangs, traps or faults.
+ * status: device int[4], zeroed by the caller. */
+MCA_API int mca_wait_probe(int* status, int limit_us, void* stream);
 
 /* Tensor-core SDPA backward (bf16).  Same math as attnHandle<T>::Backward, attn.cu:608-661, with a
  * causal or absent mask; P is recomputed from `lse` (written by mca_sdpa_forward_tc on the same
@@ -237,7 +313,11 @@ MCA_API int mca_rope_tables_host(int T, int D, float theta, float* cos_table, fl
  * before RoPE; caches are (B, seq_len, n_kv_heads*hs) fp32 or bf16 with cache_batch_stride
  * elements between sequences; row pos[b] is written, rows 0..pos[b] are attended.  max_len
  * must be >= max_b pos[b]+1.  freq_real/imag: (seq_len, hs/2) or both null (no RoPE, q/k already
- * rotated).  k_new = v_new = null skips the append.  scratch: floats from mca_decode_plan. */
+ * rotated).  k_new = v_new = null skips the append.  scratch: floats from mca_decode_plan.
+ * head_size: 32, 48, 64, 96 or 128 (the reference kernel takes any, primitives.cu:158-202; llama2.c's models use
+ * 48, 64 and 128).  Caches must be 16-byte aligned with cache_batch_stride a multiple of 4 (fp32) or 8 (bf16)
+ * elements.  A sequence whose pos[b] lies outside [0, max_len) is not followed out of the cache: nothing of it is
+ * read or appended, its output row is zero, and mca_decode_status reports it. */
 MCA_API int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_len, int* split_len,
                             int* nsplit, int64_t* scratch_floats);
 MCA_API int mca_decode_attention(const float* q, const float* k_new, const float* v_new, void* k_cache,
@@ -245,6 +325,12 @@ MCA_API int mca_decode_attention(const float* q, const float* k_new, const float
                                  int B, int n_heads, int n_kv_heads, int head_size, int seq_len, int max_len,
                                  const float* freq_real, const float* freq_imag, float* scratch,
                                  int64_t scratch_floats, float* out, void* stream);
+/* 1 if mca_decode_attention has a kernel for this head size. */
+MCA_API int mca_decode_head_size_supported(int head_size);
+/* Reads and clears the decode kernels' status words on the current device (blocking; call after the stream has been
+ * synchronised): status3[0] = number of sequences refused for an out-of-range position since the last call,
+ * status3[1] = the first such sequence, status3[2] = its position. */
+MCA_API int mca_decode_status(int* status3);
 
 /* The projections around the decode attention, each fused with its neighbour and bound by the
  * one pass over the weights.  Replace Primitives::rmsnorm + three Primitives::matmul (cublasSgemv)
@@ -285,7 +371,7 @@ MCA_API int mca_decode_logits(const float* x, const float* rms_weight, float eps
  * freq_real/imag (seq_len, head_size/2) as mca_rope_tables_host builds them.  tokens, pos: device
  * int32 (B); row pos[b] of every layer's cache is written; max_len >= max_b pos[b] + 1.
  * workspace: mca_llama_workspace_floats(cfg, B, max_len) floats, 16-byte aligned (returns -1 for a
- * bad configuration).  head_size must be 64 or 128. */
+ * bad configuration).  head_size as mca_decode_attention. */
 typedef struct McaLlamaConfig {
   int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
 } McaLlamaConfig;

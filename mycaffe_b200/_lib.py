@@ -26,6 +26,22 @@ SIGNATURES = {
                                 C.POINTER(LONG), C.c_char_p, LONG]),
     "DLL_InvokeDoubleEx2": (LONG, [LONG, LONG, C.POINTER(C.c_double), LONG, C.POINTER(LONGLONG), LONG,
                                    C.POINTER(C.POINTER(C.c_double)), C.POINTER(LONG), C.c_char_p, LONG]),
+    "DLL_InvokeDoubleEx": (LONG, [LONG, LONG, C.POINTER(C.c_double), LONG, C.c_char_p, C.POINTER(C.POINTER(C.c_double)),
+                                  C.POINTER(LONG), C.c_char_p, LONG]),
+    "DLL_QueryString": (LONG, [LONG, LONG, C.POINTER(LONG), LONG, C.POINTER(C.c_void_p), C.c_char_p, LONG]),
+    "DLL_QueryStringFloatEx": (LONG, [LONG, LONG, C.POINTER(LONG), LONG, C.c_char_p, LONG, C.c_char_p, LONG]),
+    "DLL_QueryStringDoubleEx": (LONG, [LONG, LONG, C.POINTER(LONG), LONG, C.c_char_p, LONG, C.c_char_p, LONG]),
+    "Internal_GetPointerDouble": (LONG, [LONG, LONG, LONG, C.POINTER(_vp)]),
+    "Internal_AllocHostDouble": (LONG, [LONG, LONG, C.POINTER(C.POINTER(C.c_double)), C.POINTER(C.c_double), C.c_bool]),
+    "DLL_InitFloatCustomExtension": (LONG, [_vp, LONG]),
+    "DLL_InvokeFloatCustomExtension": (LONG, [LONG, _fp, LONG, C.POINTER(_fp), C.POINTER(LONG), C.c_char_p, LONG]),
+    "DLL_InvokeFloatCustomExtensionEx": (LONG, [LONG, _fp, LONG, C.POINTER(_fp), C.POINTER(LONG), C.c_char_p, C.c_char_p, LONG,
+                                                C.c_char_p, LONG]),
+    "DLL_InitDoubleCustomExtension": (LONG, [_vp, LONG]),
+    "DLL_InvokeDoubleCustomExtension": (LONG, [LONG, C.POINTER(C.c_double), LONG, C.POINTER(C.POINTER(C.c_double)),
+                                               C.POINTER(LONG), C.c_char_p, LONG]),
+    "DLL_InvokeDoubleCustomExtensionEx": (LONG, [LONG, C.POINTER(C.c_double), LONG, C.POINTER(C.POINTER(C.c_double)),
+                                                 C.POINTER(LONG), C.c_char_p, C.c_char_p, LONG, C.c_char_p, LONG]),
     "Internal_GetPointerFloat": (LONG, [LONG, LONG, LONG, C.POINTER(_vp)]),
     "Internal_AllocHostFloat": (LONG, [LONG, LONG, C.POINTER(_fp), _fp, C.c_bool]),
     "mca_sdpa_forward_f32": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
@@ -40,6 +56,7 @@ SIGNATURES = {
     "mca_classify_causal_mask": (_i, [_vp, _i, _vp, _vp]),
     "mca_sdpa_forward_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_sdpa_backward_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mca_wait_probe": (_i, [_vp, _i, _vp]),
     "mca_sdpa_forward_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "mca_host_pipeline_chunk": (_i, [_i, _i, _i, _i]),
     "mca_host_pipeline_release": (_i, []),
@@ -48,6 +65,8 @@ SIGNATURES = {
     "mca_decode_plan": (_i, [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "mca_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i64,
                                   _vp, _vp]),
+    "mca_decode_head_size_supported": (_i, [_i]),
+    "mca_decode_status": (_i, [C.POINTER(_i)]),
     "mca_decode_qkv_rmsnorm": (_i, [_vp, _vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_decode_out_proj": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "mca_decode_ffn": (_i, [_vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp]),

@@ -2,10 +2,14 @@
 // function-id switch.  Mirrors CudaDnnDLL/CudaDnnDLL.cpp (exports), Cuda Files/main.cu
 // (Kernel<T>::Run switch) and Cuda Files/device.h / device.cu (argument unpacking) for the
 // ids listed in mycaffe_attn.h, and nothing else of that DLL.
+#include <dlfcn.h>
+
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <algorithm>
+#include <map>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -36,17 +40,15 @@ struct AttnHandle {
   // state of the last forward, consumed by backward
   bool have_fwd = false;
   int fwd_T = 0, fwd_mask_mode = 0, fwd_layout = 0;
-  const float* fwd_mask = nullptr;
-  // mask classification cache
-  const float* cls_mask = nullptr;
-  int cls_T = 0;
-  int cls_host = -1;  // host copy of the flag (-1 unknown)
+  long fwd_mask_handle = 0;   // memory handle of the forward's mask (0: none); resolved again by Backward
+  bool fwd_batch_mask = false;
+  bool status_pending = false;  // a tensor-core launch was made in asynchronous mode and its status words are unread
   void release() {
     cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
     row_max = row_sum = y_copy = delta = lse = nullptr;
     causal_flag = nullptr;
     configured = have_fwd = false;
-    cls_mask = nullptr; cls_T = 0; cls_host = -1;
+    fwd_mask_handle = 0;
   }
 };
 
@@ -70,9 +72,29 @@ struct LayerNormHandle {
   bool have_fwd = false;
 };
 
+// An extension library loaded through CUDA_FN_CREATE_EXTENSION (extensionHandle<T>, Cuda Files/extension.h:57-90).
+typedef MCA_LONG (*ExtInitFn)(void*, MCA_LONG);
+typedef MCA_LONG (*ExtInvokeFn)(MCA_LONG, float*, MCA_LONG, float**, MCA_LONG*, MCA_LPTSTR, MCA_LONG);
+typedef MCA_LONG (*ExtInvokeExFn)(MCA_LONG, float*, MCA_LONG, float**, MCA_LONG*, MCA_LPTSTR, MCA_LPTSTR, MCA_LONG, MCA_LPTSTR,
+                                  MCA_LONG);
+struct ExtensionHandle {
+  void* lib = nullptr;       // dlopen handle (null: the extension entry points of this library itself)
+  ExtInvokeFn run = nullptr;
+  ExtInvokeExFn run_ex = nullptr;
+};
+
+struct CallCounter {
+  long calls = 0, errors = 0;
+  double gpu_ms_last = 0.0, gpu_ms_total = 0.0;
+};
+
 struct Kernel {
   int device = 0;
   bool async = false;
+  bool timing = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::map<long, CallCounter> counters;
+  std::unordered_map<long, ExtensionHandle> extensions;
   long next_handle = 1;
   std::unordered_map<long, MemItem> mem;
   std::unordered_map<long, AttnHandle> attn;
@@ -349,7 +371,9 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
   return 0;
 }
 
-// Decide how the mask of this call is applied; classifies a (T,T) mask once per (pointer, T).
+// Decide how the mask of this call is applied.  A (T,T) mask is classified on every call (one pass over
+// T*T floats, small next to the attention itself): the caller may have rewritten the handle with SETMEM, or
+// freed it and been given the same address again, so nothing about it is remembered between calls.
 long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, const float** mask, int* mode,
                   bool need_host_answer) {
   *mask = nullptr;
@@ -361,26 +385,21 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   *mask = m;
   if (batch_mask) { *mode = MCA_MASK_BATCH; return 0; }
   *mode = MCA_MASK_TT;
-  if (a.cls_mask != m || a.cls_T != T) {
-    if ((e = mca_classify_causal_mask(m, T, a.causal_flag, 0))) return e;
-    a.cls_mask = m; a.cls_T = T; a.cls_host = -1;
-  }
+  if ((e = mca_classify_causal_mask(m, T, a.causal_flag, 0))) return e;
   if (need_host_answer) {
-    if (a.cls_host < 0) {
-      int v = 0;
-      cudaError_t ce = cudaMemcpy(&v, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost);
-      if (ce != cudaSuccess) return ce;
-      a.cls_host = v;
-    }
-    if (a.cls_host == 1) *mode = MCA_MASK_CAUSAL;
+    int v = 0;
+    cudaError_t ce = cudaMemcpy(&v, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return ce;
+    if (v == 1) *mode = MCA_MASK_CAUSAL;
   }
   return 0;
 }
 
-// After a tensor-core launch (unless the caller asked for asynchronous calls): read the status
-// words the kernel writes when one of its bounded waits gives up.
-long tc_status(Kernel* k, AttnHandle& a) {
-  if (k->async) return 0;
+// Read the status words a tensor-core kernel writes when one of its bounded waits gives up.  Blocking: in
+// synchronous mode it follows every tensor-core launch; in asynchronous mode the words are read for every
+// attention handle at the next call that synchronises (CUDA_FN_SYNCHRONIZEDEVICE).
+long read_status(Kernel* k, AttnHandle& a) {
+  if (!a.causal_flag) return 0;
   int st[4] = {0, 0, 0, 0};
   cudaError_t ce = cudaMemcpy(st, a.causal_flag + 1, sizeof(st), cudaMemcpyDeviceToHost);
   if (ce != cudaSuccess) return ce;
@@ -388,10 +407,34 @@ long tc_status(Kernel* k, AttnHandle& a) {
     char buf[96];
     snprintf(buf, sizeof(buf), "status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
     k->last_detail = buf;
-    cudaMemsetAsync(a.causal_flag + 1, 0, 4 * sizeof(int), 0);
+    cudaMemset(a.causal_flag + 1, 0, 4 * sizeof(int));   // the next launch starts clean
+    a.have_fwd = false;                                   // whatever that launch left behind is not a result
     return ERROR_ATTN_KERNEL_TIMEOUT;
   }
   return 0;
+}
+long tc_status(Kernel* k, AttnHandle& a) {
+  if (k->async) { a.status_pending = true; return 0; }
+  return read_status(k, a);
+}
+long sync_and_collect_status(Kernel* k) {
+  cudaError_t ce = cudaStreamSynchronize(0);
+  if (ce != cudaSuccess) return ce;
+  long first = 0;
+  for (auto& kv : k->attn) {
+    if (!kv.second.status_pending) continue;
+    kv.second.status_pending = false;
+    const long e = read_status(k, kv.second);
+    if (e && !first) first = e;
+  }
+  return first;
+}
+
+void remember_forward(AttnHandle& a, int T, int mode, int layout, long hMask, bool batch_mask) {
+  a.have_fwd = true; a.fwd_T = T; a.fwd_mask_mode = mode; a.fwd_layout = layout;
+  const bool reads_mask = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;
+  a.fwd_mask_handle = reads_mask ? hMask : 0;
+  a.fwd_batch_mask = batch_mask;
 }
 
 // layout MCA_LAYOUT_PACKED: pl[3..5] all name the (B,T,3C) projection output and pl[7] a (B,T,C) tensor
@@ -423,7 +466,7 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     const bool save = a.training && T == a.block;
     e = mca_sdpa_forward_f32_layout(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
                                     save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, layout, 0);
-    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; a.fwd_layout = layout; }
+    if (!e && save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
     return e;
   }
   // tensor-core variants: causal or absent mask only
@@ -448,7 +491,7 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     e = mca_sdpa_forward_f32_layout((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
                                     (float*)y, save ? a.row_max : nullptr, save ? a.row_sum : nullptr,
                                     save ? a.y_copy : nullptr, layout, 0);
-    if (!e && save) { a.have_fwd = true; a.fwd_T = T; a.fwd_mask = mask; a.fwd_mask_mode = mode; a.fwd_layout = layout; }
+    if (!e && save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
     return e;
   }
   e = mca_sdpa_forward_tc_layout(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1,
@@ -459,7 +502,7 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     // the layout y was written in.
     cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
     if (ce != cudaSuccess) return ce;
-    a.have_fwd = true; a.fwd_T = T; a.fwd_mask = nullptr; a.fwd_mask_mode = mode; a.fwd_layout = layout;
+    remember_forward(a, T, mode, layout, 0, false);
   }
   return tc_status(k, a);
 }
@@ -503,8 +546,15 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
       (e = check_f32(k, (long)pl[10], n, &dy)))
     return e;
   if (packed) { kk += C; dk += C; v += 2 * C; dv += 2 * C; }
-  return mca_sdpa_backward_f32_layout(q, kk, v, dy, a.y_copy, a.fwd_mask, a.fwd_mask_mode, a.causal_flag, a.row_max,
-                                      a.row_sum, a.delta, a.B, a.H, T, a.D, dq, dk, dv, layout, 0);
+  // The probabilities are recomputed, so the forward's mask is applied again: it is looked up by the handle
+  // the forward was given (a freed handle is an error, not a dangling pointer) and classified afresh.
+  const float* mask = nullptr;
+  int mode = a.fwd_mask_mode;
+  if (a.fwd_mask_handle != 0) {
+    if ((e = resolve_mask(k, a, a.fwd_mask_handle, a.fwd_batch_mask, T, &mask, &mode, false))) return e;
+  }
+  return mca_sdpa_backward_f32_layout(q, kk, v, dy, a.y_copy, mask, mode, a.causal_flag, a.row_max, a.row_sum, a.delta,
+                                      a.B, a.H, T, a.D, dq, dk, dv, layout, 0);
 }
 
 // ---- rope ids ------------------------------------------------------------------------------
@@ -583,7 +633,7 @@ long decode_create(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG
   d.B = (int)pl[0]; d.n_heads = (int)pl[1]; d.n_kv_heads = (int)pl[2]; d.hs = (int)pl[3]; d.seq_len = (int)pl[4];
   d.bf16 = pl[5] != 0;
   if (d.B <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.seq_len <= 0 || d.n_heads % d.n_kv_heads) return ERROR_PARAM_OUT_OF_RANGE;
-  if (d.hs != 64 && d.hs != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (!mca_decode_head_size_supported(d.hs)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   int sl, ns;
   if ((e = mca_decode_plan(d.B, d.n_heads, d.n_kv_heads, d.hs, d.seq_len, &sl, &ns, &d.scratch_floats))) return e;
   // the plan's split length grows with the work, so the longest plan bounds every shorter one
@@ -647,9 +697,23 @@ long decode_step(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   if ((e = check_f32(k, (long)pl[8], (int64_t)d.B * dim, &out))) return e;
   const int max_len = (int)pl[7];
   if (max_len <= 0 || max_len > d.seq_len) return ERROR_PARAM_OUT_OF_RANGE;
-  return mca_decode_attention(q, kn, vn, kc, vc, d.bf16 ? 1 : 0, (int64_t)d.seq_len * kv_dim, (const int*)posf, d.B,
-                              d.n_heads, d.n_kv_heads, d.hs, d.seq_len, max_len, d.fr, d.fi, d.scratch,
-                              d.scratch_floats, out, 0);
+  e = mca_decode_attention(q, kn, vn, kc, vc, d.bf16 ? 1 : 0, (int64_t)d.seq_len * kv_dim, (const int*)posf, d.B,
+                           d.n_heads, d.n_kv_heads, d.hs, d.seq_len, max_len, d.fr, d.fi, d.scratch, d.scratch_floats, out, 0);
+  if (e || k->async) return e;
+  // synchronous mode: a position outside [0, maxLen) was refused on the device (that sequence's output is zero,
+  // its cache untouched); report it instead of returning success
+  cudaError_t ce = cudaStreamSynchronize(0);
+  if (ce != cudaSuccess) return ce;
+  int st[3] = {0, 0, 0};
+  if ((e = mca_decode_status(st))) return e;
+  if (st[0] != 0) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "%d sequence(s) with a position outside [0, %d): first is sequence %d at position %d", st[0],
+             max_len, st[1], st[2]);
+    k->last_detail = buf;
+    return ERROR_PARAM_OUT_OF_RANGE;
+  }
+  return 0;
 }
 
 long decode_qkv(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
@@ -820,6 +884,75 @@ long tft_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   return mca_tft_attention_backward_f32(q, kk, v, mask, go, ga, B, H, Nq, Nk, d, dq, dk, dv, 0);
 }
 
+// ---- extensions (parent side) --------------------------------------------------------------
+
+// This library's own dlopen handle: what an extension is given as hParent (g_hModule in the reference).
+void* self_module() {
+  static void* self = nullptr;
+  if (!self) {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<void*>(&DLL_InvokeFloat), &info) && info.dli_fname)
+      self = dlopen(info.dli_fname, RTLD_NOW | RTLD_NOLOAD);
+  }
+  return self;
+}
+
+// extensionHandle<float>::InitializeFloat, Cuda Files/extension.cu:33-83.  An empty path selects the llama2
+// extension built into this library.
+long extension_create(Kernel* k, MCA_LONG kernel_idx, const char* path, MCA_LONG* plOutput, float** ppOutput) {
+  long e;
+  if ((e = verify_out(plOutput, ppOutput))) return e;
+  ExtensionHandle x;
+  ExtInitFn init = nullptr;
+  if (!path || !path[0]) {
+    init = &DLL_InitFloatCustomExtension;
+    x.run = &DLL_InvokeFloatCustomExtension;
+    x.run_ex = &DLL_InvokeFloatCustomExtensionEx;
+  } else {
+    x.lib = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+    if (!x.lib) { k->last_detail = dlerror(); return 126; }  // ERROR_MOD_NOT_FOUND, what GetLastError gives after LoadLibrary
+    init = (ExtInitFn)dlsym(x.lib, "DLL_InitFloatCustomExtension");
+    x.run = (ExtInvokeFn)dlsym(x.lib, "DLL_InvokeFloatCustomExtension");
+    x.run_ex = (ExtInvokeExFn)dlsym(x.lib, "DLL_InvokeFloatCustomExtensionEx");   // optional
+    if (!init || !x.run) { dlclose(x.lib); return 50; }  // ERROR_NOT_SUPPORTED
+  }
+  void* self = self_module();
+  if (!self) { if (x.lib) dlclose(x.lib); return ERROR_DLL_NOT_INIT; }
+  if ((e = init(self, kernel_idx))) { if (x.lib) dlclose(x.lib); return e; }
+  const long h = k->next_handle++;
+  k->extensions[h] = x;
+  return set_out((float)h, plOutput, ppOutput);
+}
+
+long extension_free(Kernel* k, long lInput, float* pf) {
+  long e;
+  if ((e = verify_in(lInput, pf, 1, 1))) return e;
+  auto it = k->extensions.find((long)pf[0]);
+  if (it == k->extensions.end()) return ERROR_PARAM_OUT_OF_RANGE;
+  if (it->second.lib) dlclose(it->second.lib);
+  k->extensions.erase(it);
+  return 0;
+}
+
+// Device<T>::ExtensionRun, device.h:4570-4588 (floats {hExtension, fn, args...}); with a string the call goes to
+// the extension's ...Ex entry (Kernel<T>::RunExtensionFloat, CudaDnnDLL.cpp:1053-1064).  The extension writes
+// its own message into szErr.
+long extension_run(Kernel* k, long lInput, float* pf, const char* text, float** ppOutput, MCA_LONG* plOutput,
+                   MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  long e;
+  if ((e = verify_in(lInput, pf, 2, 0x7fffffff))) return e;
+  auto it = k->extensions.find((long)pf[0]);
+  if (it == k->extensions.end()) return ERROR_PARAM_OUT_OF_RANGE;
+  const MCA_LONG fn = (MCA_LONG)pf[1];
+  float* args = lInput > 2 ? pf + 2 : nullptr;
+  if (szErr && lszErrMax > 0) szErr[0] = 0;
+  if (text) {
+    if (!it->second.run_ex) return ERROR_NOT_IMPLEMENTED;
+    return it->second.run_ex(fn, args, (MCA_LONG)(lInput - 2), nullptr, nullptr, const_cast<char*>(text), nullptr, 0, szErr, lszErrMax);
+  }
+  return it->second.run(fn, args, (MCA_LONG)(lInput - 2), ppOutput, plOutput, szErr, lszErrMax);
+}
+
 // ---- kernel lifecycle ----------------------------------------------------------------------
 
 long kernel_init(float* pInput, long lInput, long* idx_out) {
@@ -859,6 +992,9 @@ void kernel_cleanup(long idx) {
   cudaFree(k->norm_scratch);
   for (auto& kv : k->decode) { cudaFree(kv.second.fr); cudaFree(kv.second.fi); cudaFree(kv.second.scratch); }
   for (void* p : k->host_bufs) cudaFreeHost(p);
+  for (auto& kv : k->extensions) if (kv.second.lib) dlclose(kv.second.lib);
+  if (k->ev0) cudaEventDestroy(k->ev0);
+  if (k->ev1) cudaEventDestroy(k->ev1);
   cudaFree(k->stage);
   delete k;
   g_kernels[idx] = nullptr;
@@ -872,7 +1008,7 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
   long e;
   switch (fn) {
     case CUDA_FN_SETDEVICE: return 0;
-    case CUDA_FN_SYNCHRONIZEDEVICE: return (long)cudaStreamSynchronize(0);
+    case CUDA_FN_SYNCHRONIZEDEVICE: return sync_and_collect_status(k);
     case CUDA_FN_ALLOCMEM: return alloc_mem(k, lInput, pf, llInput, pl, plOutput, ppOutput, false);
     case MCA_FN_ALLOCMEM_BF16: return alloc_mem(k, lInput, pf, llInput, pl, plOutput, ppOutput, true);
     case CUDA_FN_FREEMEM: return free_mem(k, llInput, pl);
@@ -944,10 +1080,49 @@ long run(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llIn
                                    llInput > 10 ? (int)pl[10] : 0);
     case MCA_FN_SET_ASYNC:
       if ((e = verify_in(llInput, pl, 1, 1))) return e;
+      if (k->async && pl[0] == 0 && (e = sync_and_collect_status(k))) return e;
       k->async = pl[0] != 0;
       return 0;
+    case MCA_FN_SET_TIMING:
+      if ((e = verify_in(llInput, pl, 1, 1))) return e;
+      k->timing = pl[0] != 0;
+      if (k->timing && !k->ev0) {
+        cudaError_t c1 = cudaEventCreate(&k->ev0), c2 = cudaEventCreate(&k->ev1);
+        if (c1 != cudaSuccess || c2 != cudaSuccess) { k->timing = false; return c1 != cudaSuccess ? c1 : c2; }
+      }
+      return 0;
+    case CUDA_FN_FREE_EXTENSION: return extension_free(k, lInput, pf);
+    case MCA_FN_WAIT_PROBE: {
+      if ((e = verify_in(llInput, pl, 2, 2))) return e;
+      auto it = k->attn.find((long)pl[0]);
+      if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
+      if ((e = mca_wait_probe(it->second.causal_flag + 1, (int)pl[1], 0))) return e;
+      return finish(k, tc_status(k, it->second));
+    }
   }
   return ERROR_NOT_IMPLEMENTED;
+}
+
+// Every dispatched call is counted per function id; with MCA_FN_SET_TIMING on it is also bracketed by two events on
+// the stream the work is issued on (the per-call figure the reference only has as a host Stopwatch around a layer,
+// MyCaffe/layers/Layer.cs:695-722).  Read back as text through DLL_QueryString(MCA_FN_QUERY_COUNTERS).
+long run_counted(Kernel* k, long fn, float* pf, long lInput, MCA_LONGLONG* pl, long llInput, float** ppOutput,
+                 MCA_LONG* plOutput) {
+  const bool timed = k->timing && fn != MCA_FN_SET_TIMING && fn != MCA_FN_ATTN_FWD_HOST;
+  if (timed) { cudaSetDevice(k->device); cudaEventRecord(k->ev0, 0); }
+  const long e = run(k, fn, pf, lInput, pl, llInput, ppOutput, plOutput);
+  CallCounter& c = k->counters[fn];
+  c.calls++;
+  if (e) c.errors++;
+  if (timed) {
+    cudaEventRecord(k->ev1, 0);
+    if (cudaEventSynchronize(k->ev1) == cudaSuccess) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, k->ev0, k->ev1) == cudaSuccess) { c.gpu_ms_last = ms; c.gpu_ms_total += ms; }
+    }
+    cudaGetLastError();
+  }
+  return e;
 }
 
 long invoke(MCA_LONG lKernelIdx, MCA_LONG fn, float* pInput, MCA_LONG lInput, MCA_LONGLONG* plInput,
@@ -974,9 +1149,71 @@ long invoke(MCA_LONG lKernelIdx, MCA_LONG fn, float* pInput, MCA_LONG lInput, MC
     get_error(e, szErr, lszErrMax);
     return e;
   }
-  e = run(k, fn, pInput, lInput, plInput, llInput, ppOutput, plOutput);
+  if (fn == CUDA_FN_EXTENSION_RUN) {  // Kernel<T>::Run(lfnIdx, ..., szErr), Cuda Files/main.cu:1262-1275
+    cudaSetDevice(k->device);
+    k->last_detail.clear();
+    e = extension_run(k, lInput, pInput, nullptr, ppOutput, plOutput, szErr, lszErrMax);
+    if (e && szErr && lszErrMax > 0 && szErr[0] == 0) get_error(e, szErr, lszErrMax, k);
+    return e;
+  }
+  e = run_counted(k, fn, pInput, lInput, plInput, llInput, ppOutput, plOutput);
   if (e) get_error(e, szErr, lszErrMax, k);
   return e;
+}
+
+// DLL_InvokeFloatEx: only the two ids that take a string exist there (CudaDnnDLL.cpp:1036-1084); everything else is
+// ERROR_NOT_SUPPORTED in the reference.  Other ids are passed to the ordinary dispatch here so that a binding that
+// routes everything through this entry keeps working.
+long invoke_ex(MCA_LONG lKernelIdx, MCA_LONG fn, float* pInput, MCA_LONG lInput, const char* text, float** ppOutput,
+               MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  if (fn != CUDA_FN_CREATE_EXTENSION && fn != CUDA_FN_EXTENSION_RUN)
+    return invoke(lKernelIdx, fn, pInput, lInput, nullptr, 0, ppOutput, plOutput, szErr, lszErrMax);
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  Kernel* k = g_kernels[lKernelIdx];
+  long e = 0;
+  if (!k) { e = ERROR_PARAM_NULL; get_error(e, szErr, lszErrMax); return e; }
+  cudaSetDevice(k->device);
+  k->last_detail.clear();
+  if (fn == CUDA_FN_CREATE_EXTENSION) {
+    e = extension_create(k, lKernelIdx, text, plOutput, ppOutput);
+    if (e) get_error(e, szErr, lszErrMax, k);
+    return e;
+  }
+  e = extension_run(k, lInput, pInput, text ? text : "", ppOutput, plOutput, szErr, lszErrMax);
+  if (e && szErr && lszErrMax > 0 && szErr[0] == 0) get_error(e, szErr, lszErrMax, k);
+  return e;
+}
+
+// Device<T>::GetDeviceName, Cuda Files/device.cu:528-554.
+long device_name(long lInput, const MCA_LONG* pInput, char** out) {
+  if (!pInput) return ERROR_PARAM_NULL;
+  if (lInput < 1) return ERROR_PARAM_OUT_OF_RANGE;
+  cudaDeviceProp prop;
+  cudaError_t ce = cudaGetDeviceProperties(&prop, (int)pInput[0]);
+  if (ce != cudaSuccess) { cudaGetLastError(); return ce; }
+  char* dst = (char*)malloc(512);
+  if (!dst) return ERROR_MEMORY_OUT;
+  const double gb = (double)prop.totalGlobalMem / 1000000000.00;
+  const bool p2p = sizeof(void*) == 8 && prop.tccDriver == 1 && prop.major >= 2;
+  snprintf(dst, 512, "%s (%d.%02d GB - %s; compute %d.%d)", prop.name, (int)gb, (int)(gb * 100) % 100, p2p ? "P2P on" : "P2P off",
+           prop.major, prop.minor);
+  *out = dst;
+  return 0;
+}
+
+long counters_text(const Kernel* k, char** out) {
+  std::string t;
+  char line[160];
+  for (const auto& kv : k->counters) {
+    snprintf(line, sizeof(line), "%ld calls=%ld errors=%ld gpu_ms_last=%.4f gpu_ms_total=%.4f\n", kv.first, kv.second.calls,
+             kv.second.errors, kv.second.gpu_ms_last, kv.second.gpu_ms_total);
+    t += line;
+  }
+  char* dst = (char*)malloc(t.size() + 1);
+  if (!dst) return ERROR_MEMORY_OUT;
+  memcpy(dst, t.c_str(), t.size() + 1);
+  *out = dst;
+  return 0;
 }
 
 }  // namespace
@@ -994,9 +1231,9 @@ MCA_LONG DLL_InvokeFloatEx2(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* p
   return (MCA_LONG)invoke(lKernelIdx, lFunctionIdx, pInput, lInput, plInput, llInput, ppOutput, plOutput, szErr, lszErrMax);
 }
 
-MCA_LONG DLL_InvokeFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput, MCA_LPTSTR,
+MCA_LONG DLL_InvokeFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, float* pInput, MCA_LONG lInput, MCA_LPTSTR pszInput,
                            float** ppOutput, MCA_LONG* plOutput, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
-  return (MCA_LONG)invoke(lKernelIdx, lFunctionIdx, pInput, lInput, nullptr, 0, ppOutput, plOutput, szErr, lszErrMax);
+  return (MCA_LONG)invoke_ex(lKernelIdx, lFunctionIdx, pInput, lInput, pszInput, ppOutput, plOutput, szErr, lszErrMax);
 }
 
 MCA_LONG DLL_InvokeDouble(MCA_LONG, MCA_LONG, double*, MCA_LONG, double**, MCA_LONG*, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
@@ -1008,6 +1245,87 @@ MCA_LONG DLL_InvokeDoubleEx2(MCA_LONG, MCA_LONG, double*, MCA_LONG, MCA_LONGLONG
                              MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
   get_error(ERROR_NOT_IMPLEMENTED, szErr, lszErrMax);
   return ERROR_NOT_IMPLEMENTED;
+}
+
+MCA_LONG DLL_InvokeDoubleEx(MCA_LONG, MCA_LONG, double*, MCA_LONG, MCA_LPTSTR, double**, MCA_LONG*, MCA_LPTSTR szErr,
+                            MCA_LONG lszErrMax) {
+  get_error(ERROR_NOT_IMPLEMENTED, szErr, lszErrMax);
+  return ERROR_NOT_IMPLEMENTED;
+}
+
+MCA_LONG DLL_QueryString(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, MCA_LONG* pInput, MCA_LONG lInput, MCA_LPTSTR* ppOutput,
+                         MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  Kernel* k = g_kernels[lKernelIdx];
+  long e = 0;
+  if (!k) { e = ERROR_PARAM_OUT_OF_RANGE; get_error(e, szErr, lszErrMax); return (MCA_LONG)e; }  // CudaDnnDLL.cpp:928-931
+  if (lFunctionIdx == CUDA_DLL_FREEMEM) {  // the string came from malloc, CudaDnnDLL.cpp:876-882
+    if (ppOutput && *ppOutput) { free(*ppOutput); *ppOutput = nullptr; }
+    return 0;
+  }
+  if (!ppOutput) return ERROR_PARAM_NULL;
+  *ppOutput = nullptr;
+  if (szErr && lszErrMax > 0) szErr[0] = 0;
+  switch (lFunctionIdx) {
+    case CUDA_FN_GET_DEVICE_NAME: e = device_name(lInput, pInput, ppOutput); break;
+    case MCA_FN_QUERY_VERSION: {
+      const char* v = mca_version();
+      *ppOutput = (char*)malloc(strlen(v) + 1);
+      if (*ppOutput) strcpy(*ppOutput, v); else e = ERROR_MEMORY_OUT;
+      break;
+    }
+    case MCA_FN_QUERY_COUNTERS: e = counters_text(k, ppOutput); break;
+    default: e = ERROR_PARAM_OUT_OF_RANGE;  // Kernel<T>::Query, Cuda Files/main.cu:2475-2476
+  }
+  if (e) get_error(e, szErr, lszErrMax);
+  return (MCA_LONG)e;
+}
+
+MCA_LONG DLL_QueryStringFloatEx(MCA_LONG lKernelIdx, MCA_LONG lFunctionIdx, MCA_LONG* pInput, MCA_LONG lInput,
+                                MCA_LPTSTR pszOutput, MCA_LONG lOutputMax, MCA_LPTSTR szErr, MCA_LONG lszErrMax) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  Kernel* k = g_kernels[lKernelIdx];
+  long e = 0;
+  if (!k) { e = ERROR_PARAM_OUT_OF_RANGE; get_error(e, szErr, lszErrMax); return (MCA_LONG)e; }
+  if (szErr && lszErrMax > 0) szErr[0] = 0;
+  if (lFunctionIdx != CUDA_FN_GET_EXTENSION_STRING) e = ERROR_PARAM_OUT_OF_RANGE;  // Kernel<T>::QueryEx, main.cu:2492-2499
+  else if (lInput < 2) e = ERROR_PARAM_OUT_OF_RANGE;                               // Device<T>::QueryExtensionResult, device.h:4591-4603
+  else if (!pInput) e = ERROR_PARAM_NULL;
+  else {
+    // extensionHandle<float>::Query, Cuda Files/extension.cu:153-180: at most five arguments, passed as floats
+    auto it = k->extensions.find((long)pInput[0]);
+    const long n = lInput - 2;
+    if (it == k->extensions.end() || n > 5) e = ERROR_PARAM_OUT_OF_RANGE;
+    else if (!it->second.run_ex) e = ERROR_NOT_IMPLEMENTED;
+    else {
+      float args[5];
+      for (long i = 0; i < n; ++i) args[i] = (float)pInput[2 + i];
+      float* out = nullptr;
+      MCA_LONG n_out = 0;
+      cudaSetDevice(k->device);
+      e = it->second.run_ex(pInput[1], args, (MCA_LONG)n, &out, &n_out, nullptr, pszOutput, lOutputMax, szErr, lszErrMax);
+      if (!e && out != nullptr && pszOutput && lOutputMax > 0) strncat(pszOutput, "\n[END]", (size_t)lOutputMax - strlen(pszOutput) - 1);
+    }
+  }
+  if (e && szErr && lszErrMax > 0 && szErr[0] == 0) get_error(e, szErr, lszErrMax);
+  return (MCA_LONG)e;
+}
+
+MCA_LONG DLL_QueryStringDoubleEx(MCA_LONG lKernelIdx, MCA_LONG, MCA_LONG*, MCA_LONG, MCA_LPTSTR, MCA_LONG, MCA_LPTSTR szErr,
+                                 MCA_LONG lszErrMax) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  get_error(ERROR_NOT_IMPLEMENTED, szErr, lszErrMax);
+  return ERROR_NOT_IMPLEMENTED;
+}
+
+MCA_LONG Internal_GetPointerDouble(MCA_LONG, MCA_LONG lKernelIdx, MCA_LONG, void**) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  return ERROR_PARAM_NULL;  // no double kernel exists in any slot
+}
+
+MCA_LONG Internal_AllocHostDouble(MCA_LONG lKernelIdx, MCA_LONG, double**, double*, bool) {
+  if (lKernelIdx < 0 || lKernelIdx >= kMaxKernels) return ERROR_PARAM_OUT_OF_RANGE;
+  return ERROR_PARAM_NULL;
 }
 
 MCA_LONG Internal_GetPointerFloat(MCA_LONG ht, MCA_LONG lKernelIdx, MCA_LONG hHandle, void** ppPtr) {
@@ -1048,6 +1366,6 @@ int mca_rope_tables_host(int T, int D, float theta, float* cos_table, float* sin
   return 0;
 }
 
-const char* mca_version(void) { return "mycaffe_attn_b200 0.1 sm_100a"; }
+const char* mca_version(void) { return "mycaffe_attn_b200 0.2 sm_100a"; }
 
 }  // extern "C"

@@ -29,7 +29,18 @@ namespace {
 
 constexpr int DEC_THREADS = 256;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int EPL = 16;  // cache elements per lane per row
+
+// Cache elements one lane holds of a row.  A group of G = HS / EPL lanes (a power of two) covers one contiguous
+// cache row with 128-bit loads, so EPL is a multiple of 4 (fp32) or 8 (bf16) elements: 16 for head sizes that are
+// 16 x a power of two, 12 (fp32) or 24 (bf16) for 48 and 96.
+template <typename CT, int HS> struct Epl {
+  static constexpr int VEC = 16 / (int)sizeof(CT);
+  static constexpr int value = (HS % 48 == 0) ? (VEC == 4 ? 12 : 24) : 16;
+};
+
+// Status words of the decode kernels: [0] number of sequences whose position was outside [0, max_len) since the
+// last read, [1] the first such sequence, [2] its position.  Such a sequence is not attended and its output is zero.
+__device__ int g_decode_status[4];
 
 struct DecodeParams {
   const float* q;        // (B, n_heads*HS): projection of the new token (before RoPE when fr != null)
@@ -45,30 +56,33 @@ struct DecodeParams {
   float* out;            // (B, n_heads*HS)
   int64_t cache_batch_stride;  // elements between sequences in the caches
   int n_heads, n_kv_heads, kv_mul, seq_len, split_len, nsplit;
+  int pos_limit;         // positions must lie in [0, pos_limit): the planned splits and the cache cover no more
 };
 
-template <typename CT> struct Row16;
-template <> struct Row16<float> {
+template <typename CT, int EPL> struct RowSlice;
+template <int EPL> struct RowSlice<float, EPL> {
+  static constexpr int NV = EPL / 4;
   // chunk c of lane gl covers elements (c*G + gl)*4 .. +3
   template <int G> static __device__ __forceinline__ void load(const float* row, int gl, float (&x)[EPL]) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < NV; ++c) {
       const float4 t = __ldcs(reinterpret_cast<const float4*>(row) + c * G + gl);
       x[c * 4 + 0] = t.x; x[c * 4 + 1] = t.y; x[c * 4 + 2] = t.z; x[c * 4 + 3] = t.w;
     }
   }
   template <int G> static __device__ __forceinline__ void store(float* row, int gl, const float (&x)[EPL]) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+    for (int c = 0; c < NV; ++c)
       reinterpret_cast<float4*>(row)[c * G + gl] = make_float4(x[c * 4], x[c * 4 + 1], x[c * 4 + 2], x[c * 4 + 3]);
   }
   template <int G> static __device__ __forceinline__ int elem(int gl, int i) { return ((i >> 2) * G + gl) * 4 + (i & 3); }
 };
-template <> struct Row16<__nv_bfloat16> {
+template <int EPL> struct RowSlice<__nv_bfloat16, EPL> {
+  static constexpr int NV = EPL / 8;
   // chunk c of lane gl covers elements (c*G + gl)*8 .. +7
   template <int G> static __device__ __forceinline__ void load(const __nv_bfloat16* row, int gl, float (&x)[EPL]) {
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    for (int c = 0; c < NV; ++c) {
       const uint4 t = __ldcs(reinterpret_cast<const uint4*>(row) + c * G + gl);
       const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -80,7 +94,7 @@ template <> struct Row16<__nv_bfloat16> {
   }
   template <int G> static __device__ __forceinline__ void store(__nv_bfloat16* row, int gl, const float (&x)[EPL]) {
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    for (int c = 0; c < NV; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -96,9 +110,13 @@ template <> struct Row16<__nv_bfloat16> {
 // bf16 caches stream through a per-warp ring in shared memory filled by cp.async: a bf16 row is half the bytes of
 // an fp32 one, so twice the rows have to be outstanding to cover the HBM latency, and asynchronous copies keep them
 // in flight without holding them in registers.  Every lane copies exactly the 4 x 16 bytes it consumes itself
-// (two vectors of the K row, two of the V row), so no synchronisation other than its own wait_group is needed.
-constexpr int DEC_RING = 6;   // row steps in flight per warp (96 KB per CTA: two CTAs per SM overlap their ramps)
-constexpr size_t DEC_RING_BYTES = (size_t)DEC_WARPS * DEC_RING * 4 * 32 * sizeof(uint4);   // per CTA
+// (NV vectors of the K row, NV of the V row; NV = 2, or 3 for head sizes 48 and 96), so no synchronisation other than
+// its own wait_group is needed.  Row steps in flight per warp: six (96 KB per CTA: two CTAs per SM overlap their
+// ramps), four with three vectors per row.
+template <int NV> struct DecRing {
+  static constexpr int STAGES = NV <= 2 ? 6 : 4;
+  static constexpr size_t BYTES = (size_t)DEC_WARPS * STAGES * 2 * NV * 32 * sizeof(uint4);   // per CTA
+};
 __device__ __forceinline__ void unpack_bf16x8(const uint4& t, float* x) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -110,12 +128,12 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& t, float* x) {
 
 // Load 16 elements of a float vector in the lane's element order, optionally rotating
 // adjacent pairs by the RoPE angle of this position (rope, llama2_cpu.cpp:239-262).
-template <typename CT, int G>
+template <typename CT, int G, int EPL>
 __device__ __forceinline__ void load_vec_rope(const float* __restrict__ src, int gl, const float* __restrict__ cr,
                                               const float* __restrict__ ci, float (&x)[EPL]) {
 #pragma unroll
   for (int i = 0; i < EPL; i += 2) {
-    const int e = Row16<CT>::template elem<G>(gl, i);  // even
+    const int e = RowSlice<CT, EPL>::template elem<G>(gl, i);  // even
     const float x0 = src[e], x1 = src[e + 1];
     if (cr != nullptr) {
       const float c = cr[e >> 1], s = ci[e >> 1];
@@ -129,6 +147,8 @@ __device__ __forceinline__ void load_vec_rope(const float* __restrict__ src, int
 
 template <typename CT, int HS, int KVM>
 __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeParams p) {
+  constexpr int EPL = Epl<CT, HS>::value;
+  using Row = RowSlice<CT, EPL>;
   constexpr int G = HS / EPL;     // lanes per cache row
   constexpr int RPW = 32 / G;     // rows per warp per step
   constexpr int U = 2;            // steps in flight
@@ -141,6 +161,19 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
   const int kvh = h0 / p.kv_mul;
   const int split = blockIdx.x;
   const int pos = p.pos[b];
+  if (pos < 0 || pos >= p.pos_limit) {
+    // A position outside the cache (or beyond the planned splits) is not followed: nothing of this sequence is
+    // read or appended, its output is zero, and the status words say which sequence it was.
+    if (split == 0) {
+      if (blockIdx.y == 0 && threadIdx.x == 0 && atomicAdd(&g_decode_status[0], 1) == 0) {
+        g_decode_status[1] = b;
+        g_decode_status[2] = pos;
+      }
+      if (p.nsplit == 1)
+        for (int i = threadIdx.x; i < KVM * HS; i += DEC_THREADS) p.out[(int64_t)b * p.n_heads * HS + (int64_t)h0 * HS + i] = 0.f;
+    }
+    return;
+  }
   const int L = pos + 1;
   const int r_begin = split * p.split_len;
   if (r_begin >= L) return;
@@ -157,7 +190,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
 
   float q[KVM][EPL];
 #pragma unroll
-  for (int x = 0; x < KVM; ++x) load_vec_rope<CT, G>(p.q + (int64_t)b * dim + (int64_t)(h0 + x) * HS, gl, cr, ci, q[x]);
+  for (int x = 0; x < KVM; ++x) load_vec_rope<CT, G, EPL>(p.q + (int64_t)b * dim + (int64_t)(h0 + x) * HS, gl, cr, ci, q[x]);
 
   float m[KVM], l[KVM], acc[KVM][EPL];
 #pragma unroll
@@ -170,8 +203,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
   const bool has_new = (p.k_new != nullptr);
   if constexpr (sizeof(CT) == 2) {
     // ---- bf16 cache: cp.async ring
+    constexpr int NV = Row::NV;                 // 16-byte vectors of a K (or V) row per lane
+    constexpr int DEC_RING = DecRing<NV>::STAGES;
     extern __shared__ __align__(16) uint4 dec_ring[];
-    uint4* my_ring = dec_ring + (size_t)warp * DEC_RING * 4 * 32;          // [stage][vector][lane]
+    uint4* my_ring = dec_ring + (size_t)warp * DEC_RING * 2 * NV * 32;     // [stage][vector][lane]
     const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
     const __nv_bfloat16* kcb = reinterpret_cast<const __nv_bfloat16*>(kc);
     const __nv_bfloat16* vcb = reinterpret_cast<const __nv_bfloat16*>(vc);
@@ -182,13 +217,14 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
       if (t < n_steps) {
         const int row = first + t * stride + g;
         if (row < r_end && !(has_new && row == pos)) {
-          const uint32_t dst = my_ring_s + (uint32_t)(((t % DEC_RING) * 4 * 32 + lane) * sizeof(uint4));
+          const uint32_t dst = my_ring_s + (uint32_t)(((t % DEC_RING) * 2 * NV * 32 + lane) * sizeof(uint4));
           const uint4* ks = reinterpret_cast<const uint4*>(kcb + (int64_t)row * kv_dim);
           const uint4* vs = reinterpret_cast<const uint4*>(vcb + (int64_t)row * kv_dim);
-          mca_cp_async16(dst, ks + gl);
-          mca_cp_async16(dst + 32 * sizeof(uint4), ks + G + gl);
-          mca_cp_async16(dst + 64 * sizeof(uint4), vs + gl);
-          mca_cp_async16(dst + 96 * sizeof(uint4), vs + G + gl);
+#pragma unroll
+          for (int c = 0; c < NV; ++c) {
+            mca_cp_async16(dst + (uint32_t)(c * 32 * sizeof(uint4)), ks + c * G + gl);
+            mca_cp_async16(dst + (uint32_t)((NV + c) * 32 * sizeof(uint4)), vs + c * G + gl);
+          }
         }
       }
       mca_cp_async_commit();   // one group per step, also when it is empty, so that the group count is the step count
@@ -204,11 +240,11 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
       if (valid && has_new && row == pos) {
         // the new token: take k,v from the projections, rotate k, append both to the cache, and attend to what a
         // later step will read back from the cache
-        load_vec_rope<CT, G>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx);
-        load_vec_rope<CT, G>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx);
+        load_vec_rope<CT, G, EPL>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx);
+        load_vec_rope<CT, G, EPL>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx);
         if (h0 % p.kv_mul == 0) {
-          Row16<CT>::template store<G>(kc + (int64_t)row * kv_dim, gl, kx);
-          Row16<CT>::template store<G>(vc + (int64_t)row * kv_dim, gl, vx);
+          Row::template store<G>(kc + (int64_t)row * kv_dim, gl, kx);
+          Row::template store<G>(vc + (int64_t)row * kv_dim, gl, vx);
         }
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
@@ -216,11 +252,12 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
           vx[i] = __bfloat162float(__float2bfloat16_rn(vx[i]));
         }
       } else if (valid) {
-        const uint4* src = my_ring + (size_t)(t % DEC_RING) * 4 * 32 + lane;
-        unpack_bf16x8(src[0], kx);
-        unpack_bf16x8(src[32], kx + 8);
-        unpack_bf16x8(src[64], vx);
-        unpack_bf16x8(src[96], vx + 8);
+        const uint4* src = my_ring + (size_t)(t % DEC_RING) * 2 * NV * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+          unpack_bf16x8(src[c * 32], kx + 8 * c);
+          unpack_bf16x8(src[(NV + c) * 32], vx + 8 * c);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < EPL; ++i) { kx[i] = 0.f; vx[i] = 0.f; }
@@ -260,11 +297,11 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
       if (valid[u]) {
         if (has_new && row == pos) {
           // the new token: take k,v from the projections, rotate k, and append both to the cache
-          load_vec_rope<CT, G>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx[u]);
-          load_vec_rope<CT, G>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx[u]);
+          load_vec_rope<CT, G, EPL>(p.k_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, cr, ci, kx[u]);
+          load_vec_rope<CT, G, EPL>(p.v_new + (int64_t)b * kv_dim + (int64_t)kvh * HS, gl, nullptr, nullptr, vx[u]);
           if (h0 % p.kv_mul == 0) {
-            Row16<CT>::template store<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
-            Row16<CT>::template store<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
+            Row::template store<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
+            Row::template store<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
           }
           if (sizeof(CT) == 2) {  // attend to what a later step will read back from the cache
 #pragma unroll
@@ -274,8 +311,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
             }
           }
         } else {
-          Row16<CT>::template load<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
-          Row16<CT>::template load<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
+          Row::template load<G>(kc + (int64_t)row * kv_dim, gl, kx[u]);
+          Row::template load<G>(vc + (int64_t)row * kv_dim, gl, vx[u]);
         }
       }
     }
@@ -323,7 +360,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeP
       float a = acc[x][i] * f;
 #pragma unroll
       for (int o = G; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (g == 0) s_acc[warp][x][Row16<CT>::template elem<G>(gl, i)] = a;
+      if (g == 0) s_acc[warp][x][Row::template elem<G>(gl, i)] = a;
     }
     if (lane == 0) { s_ml[warp][x][0] = m_all; s_ml[warp][x][1] = lsum; }
   }
@@ -357,10 +394,13 @@ template <int HS>
 __global__ void __launch_bounds__(HS) decode_combine_kernel(const float* __restrict__ part_acc,
                                                             const float* __restrict__ part_ml,
                                                             const int* __restrict__ pos, int n_heads, int nsplit,
-                                                            int split_len, float* __restrict__ out) {
+                                                            int split_len, int pos_limit, float* __restrict__ out) {
   mca_pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, e = threadIdx.x;
-  const int n_valid = min(nsplit, (pos[b] + split_len) / split_len);  // ceil((pos+1)/split_len)
+  const int pb = pos[b];
+  mca_pdl_wait();   // the partials are the split kernel's output
+  if (pb < 0 || pb >= pos_limit) { out[((int64_t)b * n_heads + h) * HS + e] = 0.f; return; }
+  const int n_valid = min(nsplit, (pb + split_len) / split_len);  // ceil((pos+1)/split_len)
   const int64_t slot0 = ((int64_t)b * n_heads + h) * nsplit;
   float M = -INFINITY;
   for (int s = 0; s < n_valid; ++s) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
@@ -377,7 +417,7 @@ template <typename CT, int HS>
 int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
   const int kvmt = p.kv_mul >= 4 ? 4 : p.kv_mul;
   dim3 grid(p.nsplit, p.n_heads / kvmt, B);
-  const size_t smem = sizeof(CT) == 2 ? DEC_RING_BYTES : 0;   // the bf16 path's cp.async ring
+  const size_t smem = sizeof(CT) == 2 ? DecRing<Epl<CT, HS>::value / 8>::BYTES : 0;   // the bf16 path's cp.async ring
   if (smem) {
     MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -392,9 +432,9 @@ int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
   int e = mca_launch_status();
   if (e) return e;
   if (p.nsplit > 1) {
-    decode_combine_kernel<HS><<<dim3(p.n_heads, B), HS, 0, st>>>(p.part_acc, p.part_ml, p.pos, p.n_heads, p.nsplit,
-                                                                 p.split_len, p.out);
-    e = mca_launch_status();
+    // programmatic dependent launch: the combine pass is resident and waiting when the last split finishes
+    e = mca_launch_pdl(decode_combine_kernel<HS>, dim3(p.n_heads, B), dim3(HS), 0, st, (const float*)p.part_acc,
+                       (const float*)p.part_ml, p.pos, p.n_heads, p.nsplit, p.split_len, p.pos_limit, p.out);
   }
   return e;
 }
@@ -457,8 +497,18 @@ int mca_decode_attention(const float* q, const float* k_new, const float* v_new,
   if (!q || !k_cache || !v_cache || !pos || !out) return ERROR_PARAM_NULL;
   if ((k_new == nullptr) != (v_new == nullptr)) return ERROR_PARAM_NULL;
   if ((freq_real == nullptr) != (freq_imag == nullptr)) return ERROR_PARAM_NULL;
-  if (head_size != 64 && head_size != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (!mca_decode_head_size_supported(head_size)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   if (max_len <= 0 || max_len > seq_len || B > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  {
+    // The kernels read and write cache rows as 16-byte vectors: base addresses must be 16-byte aligned and the
+    // distance between sequences a whole number of vectors (rows are: kv_dim is a multiple of 16 elements).
+    const int vec = cache_is_bf16 ? 8 : 4;
+    if (((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) != 0) return ERROR_PARAM_OUT_OF_RANGE;
+    if (cache_batch_stride % vec != 0 || cache_batch_stride < (int64_t)max_len * n_kv_heads * head_size) return ERROR_PARAM_OUT_OF_RANGE;
+    if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_new) |
+          reinterpret_cast<uintptr_t>(v_new) | reinterpret_cast<uintptr_t>(pos)) & 3) != 0)
+      return ERROR_PARAM_OUT_OF_RANGE;
+  }
   DecodeParams p;
   int64_t need = 0;
   int e = mca_decode_plan(B, n_heads, n_kv_heads, head_size, max_len, &p.split_len, &p.nsplit, &need);
@@ -470,11 +520,31 @@ int mca_decode_attention(const float* q, const float* k_new, const float* v_new,
   p.part_ml = scratch ? scratch + (int64_t)B * n_heads * p.nsplit * head_size : nullptr;
   p.cache_batch_stride = cache_batch_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.kv_mul = n_heads / n_kv_heads; p.seq_len = seq_len;
+  p.pos_limit = max_len;   // <= seq_len, and the planned splits cover [0, max_len)
   if (p.kv_mul > 4 && p.kv_mul % 4 != 0) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   if (p.kv_mul == 3) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (cache_is_bf16) {
-    return head_size == 128 ? launch_decode<__nv_bfloat16, 128>(p, B, st) : launch_decode<__nv_bfloat16, 64>(p, B, st);
+  switch (head_size) {
+#define MCA_DECODE_CASE(HS_) \
+    case HS_: return cache_is_bf16 ? launch_decode<__nv_bfloat16, HS_>(p, B, st) : launch_decode<float, HS_>(p, B, st);
+    MCA_DECODE_CASE(32) MCA_DECODE_CASE(48) MCA_DECODE_CASE(64) MCA_DECODE_CASE(96) MCA_DECODE_CASE(128)
+#undef MCA_DECODE_CASE
   }
-  return head_size == 128 ? launch_decode<float, 128>(p, B, st) : launch_decode<float, 64>(p, B, st);
+  return ERROR_ATTN_UNSUPPORTED_SHAPE;
+}
+
+int mca_decode_head_size_supported(int head_size) {
+  return head_size == 32 || head_size == 48 || head_size == 64 || head_size == 96 || head_size == 128;
+}
+
+int mca_decode_status(int* status3) {
+  if (!status3) return ERROR_PARAM_NULL;
+  int st[4] = {0, 0, 0, 0};
+  MCA_CUDA_TRY(cudaMemcpyFromSymbol(st, g_decode_status, sizeof(st)));
+  if (st[0] != 0) {
+    const int zero[4] = {0, 0, 0, 0};
+    MCA_CUDA_TRY(cudaMemcpyToSymbol(g_decode_status, zero, sizeof(zero)));
+  }
+  status3[0] = st[0]; status3[1] = st[1]; status3[2] = st[2];
+  return 0;
 }

@@ -48,15 +48,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait.  Returns false after WAIT_LIMIT_NS (or as soon as another CTA reported a
+// Bounded wait.  Returns false after limit_ns (or as soon as another CTA reported a
 // failure) and records {code, stage, block, iteration} in status[0..3].
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
+static __device__ __noinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, int* status, int stage, int iter,
+                                                      uint64_t limit_ns) {
   const uint64_t t0 = global_timer_ns();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 63u) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (global_timer_ns() - t0 > limit_ns) {
         if (atomicCAS(status, 0, 1) == 0) {
           status[1] = stage;
           status[2] = (int)(blockIdx.x + gridDim.x * blockIdx.y);
@@ -68,6 +69,9 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
   }
   return true;
+}
+static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int stage, int iter) {
+  return mbar_wait_limited(bar, parity, status, stage, iter, WAIT_LIMIT_NS);
 }
 #ifndef MCA_SPIN_POLLS
 #define MCA_SPIN_POLLS 0

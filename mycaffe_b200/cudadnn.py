@@ -60,6 +60,84 @@ class CudaDnn:
             return res
         return out_buf[:n]
 
+    def _finish(self, rc, err, pp, n_out, out_buf):
+        if rc != 0:
+            raise CudaDnnError(rc, err.value.decode(errors="replace"))
+        n = n_out.value
+        if C.cast(pp, C.c_void_p).value != out_buf.ctypes.data:
+            res = np.ctypeslib.as_array(pp, shape=(n,)).copy()
+            self._lib.DLL_InvokeFloat(self._kernel, ids.CUDA_DLL_FREEMEM, pp, 0, None, None, err, 1024)
+            return res
+        return out_buf[:n]
+
+    def _invoke_float(self, fn, floats=None, text=None):
+        """DLL_InvokeFloat (RunFloat), or DLL_InvokeFloatEx (RunFloatEx) when a string goes with the call."""
+        fa = np.ascontiguousarray(floats, dtype=np.float32) if floats is not None else None
+        out_buf = np.zeros(1, np.float32)
+        pp = C.cast(out_buf.ctypes.data, C.POINTER(C.c_float))
+        n_out = _lib.LONG(out_buf.size)
+        err = C.create_string_buffer(1024)
+        fp = fa.ctypes.data_as(C.POINTER(C.c_float)) if fa is not None else None
+        nf = fa.size if fa is not None else 0
+        if text is None:
+            rc = self._lib.DLL_InvokeFloat(self._kernel, fn, fp, nf, C.byref(pp), C.byref(n_out), err, 1024)
+        else:
+            rc = self._lib.DLL_InvokeFloatEx(self._kernel, fn, fp, nf, text.encode(), C.byref(pp), C.byref(n_out), err, 1024)
+        return self._finish(rc, err, pp, n_out, out_buf)
+
+    def QueryString(self, fn, ints=()):
+        """DLL_QueryString: the answer is a string the library allocates and takes back (FREEMEM)."""
+        ia = np.ascontiguousarray(list(ints), dtype=np.int32)
+        out = C.c_void_p()
+        err = C.create_string_buffer(1024)
+        rc = self._lib.DLL_QueryString(self._kernel, fn, ia.ctypes.data_as(C.POINTER(_lib.LONG)) if ia.size else None, ia.size,
+                                       C.byref(out), err, 1024)
+        if rc != 0:
+            raise CudaDnnError(rc, err.value.decode(errors="replace"))
+        text = C.string_at(out.value).decode() if out.value else ""
+        self._lib.DLL_QueryString(self._kernel, ids.CUDA_DLL_FREEMEM, None, 0, C.byref(out), err, 1024)
+        return text
+
+    def GetDeviceName(self, nDeviceID):
+        return self.QueryString(ids.CUDA_FN_GET_DEVICE_NAME, [int(nDeviceID)])
+
+    # ------------------------------------------------------------------ extensions (CudaDnn.cs:3703-3812)
+    def CreateExtension(self, strExtensionDllPath="") -> int:
+        """An empty path selects the llama2 extension built into the library."""
+        return int(self._invoke_float(ids.CUDA_FN_CREATE_EXTENSION, None, strExtensionDllPath)[0])
+
+    def FreeExtension(self, hExtension):
+        self._invoke_float(ids.CUDA_FN_FREE_EXTENSION, [float(hExtension)])
+
+    def RunExtension(self, hExtension, lfnIdx, rgParam=None):
+        return np.array(self._invoke_float(ids.CUDA_FN_EXTENSION_RUN, [float(hExtension), float(lfnIdx)] + [float(x) for x in (rgParam or [])]))
+
+    def RunExtensionEx(self, hExtension, lfnIdx, rgParam, strInput):
+        return np.array(self._invoke_float(ids.CUDA_FN_EXTENSION_RUN,
+                                           [float(hExtension), float(lfnIdx)] + [float(x) for x in (rgParam or [])], strInput))
+
+    def QueryExtensionStrings(self, hExtension, lfnIdx, rgParam=()):
+        ia = np.ascontiguousarray([int(hExtension), int(lfnIdx)] + [int(x) for x in rgParam], dtype=np.int32)
+        buf = C.create_string_buffer(4096)
+        err = C.create_string_buffer(1024)
+        rc = self._lib.DLL_QueryStringFloatEx(self._kernel, ids.CUDA_FN_GET_EXTENSION_STRING, ia.ctypes.data_as(C.POINTER(_lib.LONG)),
+                                              ia.size, buf, 4096, err, 1024)
+        if rc != 0:
+            raise CudaDnnError(rc, err.value.decode(errors="replace"))
+        return buf.value.decode()
+
+    def SetTiming(self, enabled: bool):
+        """Addition: bracket every dispatched call with CUDA events; read with QueryCounters()."""
+        self._invoke(ids.MCA_FN_SET_TIMING, None, [1 if enabled else 0])
+
+    def QueryCounters(self):
+        """{function id: {calls, errors, gpu_ms_last, gpu_ms_total}} of this kernel index."""
+        res = {}
+        for line in self.QueryString(ids.MCA_FN_QUERY_COUNTERS).splitlines():
+            f = line.split()
+            res[int(f[0])] = {kv.split("=")[0]: float(kv.split("=")[1]) for kv in f[1:]}
+        return res
+
     def Dispose(self):
         if self._kernel:
             self._lib.DLL_InvokeFloat(self._kernel, ids.CUDA_DLL_CLEANUP, None, 0, None, None, None, 0)

@@ -29,6 +29,57 @@ def test_header_declares_the_reference_exports():
         assert required in names
 
 
+# EXPORTS of CudaDnnDLL/CudaDnnDLL.12.3.def (ordinals 1-7, 100-103), the two query-string entries CudaDnnDLL.cpp:935,976
+# adds beside them, and EXPORTS of CudaExtension.llm32.llama2/CudaExtension.llm32.11.8.def (ordinals 1-6).
+REFERENCE_DEF_EXPORTS = ["DLL_InvokeFloat", "DLL_InvokeDouble", "DLL_QueryString", "DLL_InvokeFloatEx", "DLL_InvokeDoubleEx",
+                         "DLL_InvokeFloatEx2", "DLL_InvokeDoubleEx2", "Internal_GetPointerFloat", "Internal_GetPointerDouble",
+                         "Internal_AllocHostFloat", "Internal_AllocHostDouble", "DLL_QueryStringFloatEx", "DLL_QueryStringDoubleEx"]
+EXTENSION_DEF_EXPORTS = ["DLL_InitFloatCustomExtension", "DLL_InvokeFloatCustomExtension", "DLL_InitDoubleCustomExtension",
+                         "DLL_InvokeDoubleCustomExtension", "DLL_InvokeFloatCustomExtensionEx", "DLL_InvokeDoubleCustomExtensionEx"]
+
+
+def test_every_export_of_the_reference_def_files_resolves(lib):
+    """A loader that GetProcAddress'es the reference's whole export table must find every name."""
+    raw = C.CDLL(str(lib._name))
+    names = declared_functions()
+    for n in REFERENCE_DEF_EXPORTS + EXTENSION_DEF_EXPORTS:
+        assert n in names, f"{n} not declared in the header"
+        assert getattr(raw, n) is not None
+
+
+def test_double_and_uninitialised_entries_answer_without_a_gpu(lib):
+    from mycaffe_b200 import function_ids as ids
+    err = C.create_string_buffer(256)
+    out = C.c_void_p()
+    # double twins: not implemented, with a message
+    assert lib.DLL_InvokeDoubleEx(0, ids.CUDNN_FN_ATTN_CREATE, None, 0, None, None, None, err, 256) == ids.ERROR_NOT_IMPLEMENTED
+    assert b"not implemented" in err.value
+    assert lib.DLL_QueryStringDoubleEx(0, 1003, None, 0, None, 0, err, 256) == ids.ERROR_NOT_IMPLEMENTED
+    assert lib.Internal_GetPointerDouble(1, 3, 1, C.byref(out)) == ids.ERROR_PARAM_NULL      # empty double table, CudaDnnDLL.cpp:84-88
+    assert lib.Internal_AllocHostDouble(3, 1, None, None, False) == ids.ERROR_PARAM_NULL
+    assert lib.Internal_GetPointerDouble(1, 5000, 1, C.byref(out)) == ids.ERROR_PARAM_OUT_OF_RANGE
+    assert lib.DLL_InitDoubleCustomExtension(None, 0) == ids.ERROR_NOT_IMPLEMENTED
+    # query string on a slot that holds no kernel: ERROR_PARAM_OUT_OF_RANGE (CudaDnnDLL.cpp:928-931)
+    assert lib.DLL_QueryString(9, ids.CUDA_FN_GET_DEVICE_NAME, None, 0, C.byref(out), err, 256) == ids.ERROR_PARAM_OUT_OF_RANGE
+    assert lib.DLL_QueryStringFloatEx(9, ids.CUDA_FN_GET_EXTENSION_STRING, None, 0, None, 0, err, 256) == ids.ERROR_PARAM_OUT_OF_RANGE
+    # the extension before DLL_InitFloatCustomExtension: PEER_E_NOT_INITIALIZED (CudaExtension.llm32.cpp:95-96)
+    n = C.c_int32(0)
+    pp = C.POINTER(C.c_float)()
+    rc = lib.DLL_InvokeFloatCustomExtension(ids.LLM_CUDA_EXTENSION_CREATE, None, 0, C.byref(pp), C.byref(n), err, 256)
+    assert rc & 0xFFFFFFFF == 0x80630001
+    assert lib.DLL_InitFloatCustomExtension(None, 1) == 87                                   # ERROR_INVALID_PARAMETER
+    # initialised against this library as the parent (it exports DLL_InvokeFloat and Internal_AllocHostFloat)
+    assert lib.DLL_InitFloatCustomExtension(C.c_void_p(lib._handle), 1) == 0
+    rc = lib.DLL_InvokeFloatCustomExtension(999, None, 0, C.byref(pp), C.byref(n), err, 256)
+    assert rc == 50 and b"not supported" in err.value                                        # ERROR_NOT_SUPPORTED + the reference's text
+    rc = lib.DLL_InvokeFloatCustomExtensionEx(ids.LLM_CUDA_EXTENSION_GENERATE, None, 0, None, None, b"x", None, 0, err, 256)
+    assert rc == 50 and b"not provided" in err.value
+
+
+def test_decode_head_sizes(lib):
+    assert [h for h in range(1, 257) if lib.mca_decode_head_size_supported(h)] == [32, 48, 64, 96, 128]
+
+
 def test_library_exports_every_declared_symbol(lib):
     from mycaffe_b200 import _lib
     names = declared_functions()
