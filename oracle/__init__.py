@@ -35,8 +35,21 @@ def build(force: bool = False) -> None:
     so, src = _HERE / "_build" / "liboracle.so", _HERE / "attn_oracle.cpp"
     stale = so.exists() and so.stat().st_mtime < src.stat().st_mtime
     if force or stale or not so.exists() or not (_HERE / "_ref" / "libllama2_ref.so").exists():
-        subprocess.run(["make", "-C", str(_HERE)] + (["-B"] if force else []), check=True,
-                       stdout=subprocess.DEVNULL)
+        cmd = ["make", "-C", str(_HERE)] + (["-B"] if force else [])
+        ref = reference_root()
+        if ref is not None:
+            cmd.append(f"REFERENCE={ref}")
+        subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
+
+
+def reference_root():
+    """Where the reference's source tree is: $MYCAFFE_REFERENCE, else a directory named `reference` beside this
+    repository; None when neither exists (the twin is then not rebuilt)."""
+    cand = os.environ.get("MYCAFFE_REFERENCE")
+    for c in ([Path(cand)] if cand else []) + [_HERE.parent.parent / "reference"]:
+        if (c / "CudaExtension.llm32.llama2" / "Files" / "llama2_cpu.cpp").exists():
+            return c
+    return None
 
 
 def lib() -> C.CDLL:
@@ -71,6 +84,18 @@ def ref_lib() -> C.CDLL | None:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int | None = None) -> int:
+    """Set the OpenMP team size of the checkers (this library and the compiled reference twin share the
+    runtime).  Default: every core this process may run on.  Returns the size now in effect."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
 
 
 def _c(a, dt=np.float32):

@@ -394,6 +394,16 @@ int oracle_num_threads() {
 #endif
 }
 
+// The OpenMP team size of this process (the compiled reference twin shares the same runtime).  A launcher may
+// export OMP_NUM_THREADS=1 for its workers; the CPU legs of the benchmark set the size they report explicitly.
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void oracle_sdpa_forward_f32(const float* Q, const float* K, const float* V, const float* mask, int mask_mode,
                              int B, int H, int T, int D, float* Y, float* P) {
   sdpa_forward<float, float>(Q, K, V, mask, mask_mode, B, H, T, D, Y, P, 0, 1);

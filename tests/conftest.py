@@ -16,3 +16,10 @@ def pytest_configure(config):
 def pico():
     import numpy as np
     return np.load(ROOT / "tests" / "golden" / "pico_csa.npz")
+
+
+@pytest.fixture(scope="session")
+def pico_ln():
+    """The reference's LayerNorm and transformer-block vectors (gpt-pico-ln*, gpt-pico-blk*)."""
+    import numpy as np
+    return np.load(ROOT / "tests" / "golden" / "pico_ln_blk.npz")

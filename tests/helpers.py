@@ -38,3 +38,16 @@ def csa_forward(x, w_attn, b_attn, w_proj, b_proj, H, sdpa):
     q, k, v = csa_qkv(x, w_attn, b_attn, H)
     y = merge_heads(np.asarray(sdpa(q, k, v), np.float32))
     return y @ w_proj.T + b_proj
+
+
+PICO_BLOCK_CASES = {"blk": 1, "blk3": 3, "blk3B": 3}  # case -> heads
+
+
+def csa_backward(x, w_attn, b_attn, w_proj, H, d_out, sdpa_bwd):
+    """Gradient of the layer output w.r.t. the layer input (CausalSelfAttentionLayer.cs:641-744):
+    c_proj backward, head split, ``sdpa_bwd(q,k,v,dy)`` -> (dq,dk,dv), head merge, c_attn backward."""
+    q, k, v = csa_qkv(x, w_attn, b_attn, H)
+    dy = split_heads(d_out @ w_proj, H)
+    dq, dk, dv = (np.asarray(g, np.float32) for g in sdpa_bwd(q, k, v, dy))
+    d_ca = np.concatenate([merge_heads(dq), merge_heads(dk), merge_heads(dv)], axis=-1)
+    return d_ca @ w_attn

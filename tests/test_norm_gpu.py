@@ -116,3 +116,57 @@ def test_raw_entry_points_reject_bad_arguments():
     assert lib.mca_layernorm_forward_f32(None, None, None, 4, 8, 1e-5, None) == ids.ERROR_PARAM_NULL
     assert lib.mca_rmsnorm_forward_f32(None, None, None, None, 4, 8, 1e-5, None) == ids.ERROR_PARAM_NULL
     assert lib.mca_rmsnorm_backward_scratch_floats(768) >= 768
+
+
+@pytest.mark.parametrize("case", ["ln", "ln3", "ln3B", "ln-blk"])
+def test_layernorm_ids_match_the_reference_vectors(cuda, pico_ln, case):
+    """ids 970 / 975 / 976 on the reference's own LayerNorm vectors (gpt-pico-ln*, epsilon 1e-10): y from x, and the
+    gradient at x from the gradient at y."""
+    g = lambda n: pico_ln[f"{case}/{n}"]
+    x = g("x")
+    outer, channels, inner = x.shape
+    h = cuda.CreateLayerNorm(0, x.size, outer, channels, inner, 1e-10)
+    hX, hY, hdY, hdX = cuda.AllocMemory(x), cuda.AllocMemory(x.size), cuda.AllocMemory(g("grad_1a_y")), cuda.AllocMemory(x.size)
+    cuda.LayerNormForward(h, hX, hY)
+    np.testing.assert_allclose(cuda.GetMemory(hY, x.size).reshape(x.shape), g("y"), atol=5e-7)
+    cuda.LayerNormBackward(h, hY, hdY, hdX)
+    assert rel_err(cuda.GetMemory(hdX, x.size).reshape(x.shape), g("grad_9_x")) < 1e-5
+    for m in (hX, hY, hdY, hdX):
+        cuda.FreeMemory(m)
+    cuda.FreeLayerNorm(h)
+
+
+@pytest.mark.parametrize("case", ["blk", "blk3", "blk3B"])
+def test_block_layernorm_then_attention_matches_the_reference_vectors(cuda, pico_ln, case):
+    """The reference's transformer-block vectors through the library: 1_x -> LAYERNORM_FWD -> 2_x_ln11 -> the
+    attention layer with ATTN_FWD at its core -> 3_x_attn; back: grad_8_x_attn -> ATTN_BWD -> grad_9_ln1 ->
+    LAYERNORM_BWD (+ the residual branch) -> grad_10_x.  The InnerProduct glue either side of the attention core is
+    the C# layer's and is restated in numpy."""
+    from gpu_util import Sdpa
+    from helpers import PICO_BLOCK_CASES, csa_backward, csa_forward
+    H = PICO_BLOCK_CASES[case]
+    g = lambda n: pico_ln[f"{case}/{n}"]
+    x = g("1_x")
+    B, T, Cn = x.shape
+    hL = cuda.CreateLayerNorm(0, x.size, B, T, Cn, 1e-10)
+    hX, hY = cuda.AllocMemory(x), cuda.AllocMemory(x.size)
+    cuda.LayerNormForward(hL, hX, hY)
+    ln1 = cuda.GetMemory(hY, x.size).reshape(x.shape)
+    np.testing.assert_allclose(ln1, g("2_x_ln11"), atol=5e-7)
+
+    a = Sdpa(cuda, B, T, H, Cn // H, training=True)
+    mask = oracle.causal_mask(T)
+    attn = csa_forward(ln1, g("attn_weight"), g("attn_bias"), g("attn_proj_weight"), g("attn_proj_bias"), H,
+                       lambda q, k, v: a.forward(q, k, v, mask))
+    np.testing.assert_allclose(attn, g("3_x_attn"), atol=3e-7)
+    d_ln1 = csa_backward(ln1, g("attn_weight"), g("attn_bias"), g("attn_proj_weight"), H, g("grad_8_x_attn"),
+                         lambda q, k, v, dy: a.backward(dy))
+    assert rel_err(d_ln1, g("grad_9_ln1")) < 1e-5
+    hdY, hdX = cuda.AllocMemory(g("grad_9_ln1")), cuda.AllocMemory(x.size)
+    cuda.LayerNormBackward(hL, hY, hdY, hdX)
+    dx = cuda.GetMemory(hdX, x.size).reshape(x.shape) + g("grad_8_x")
+    assert rel_err(dx, g("grad_10_x")) < 1e-5
+    a.close()
+    for m in (hX, hY, hdY, hdX):
+        cuda.FreeMemory(m)
+    cuda.FreeLayerNorm(hL)

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import oracle
-from helpers import PICO_CASES, csa_forward, csa_qkv, rel_err
+from helpers import PICO_BLOCK_CASES, PICO_CASES, csa_backward, csa_forward, csa_qkv, rel_err
 
 
 @pytest.mark.parametrize("case", list(PICO_CASES))
@@ -43,6 +43,40 @@ def test_pico_backward(pico, case):
         np.testing.assert_allclose(dq, g("grad_qt"), atol=2e-8)
         np.testing.assert_allclose(dk, g("grad_kt"), atol=2e-8)
         np.testing.assert_allclose(dv, g("grad_vt"), atol=2e-8)
+
+
+@pytest.mark.parametrize("case", ["ln", "ln3", "ln3B", "ln-blk"])
+def test_pico_layernorm(pico_ln, case):
+    """The LayerNorm restatement (layernorm.cu:291-384) against the reference's gpt-pico-ln* vectors: y, and the
+    gradient at x from the gradient at y.  The vectors were generated with epsilon 1e-10, the layer's default
+    (LayerNormParameter.cs), and no affine part."""
+    g = lambda n: pico_ln[f"{case}/{n}"]
+    y, stdev = oracle.layernorm_forward(g("x"), 1e-10)
+    np.testing.assert_allclose(y, g("y"), atol=3e-7)
+    if case == "ln-blk":
+        np.testing.assert_allclose(stdev.reshape(g("std").shape), g("std"), rtol=1e-6)
+    for y_in in (g("y"), y):
+        dx = oracle.layernorm_backward(y_in, g("grad_1a_y"), stdev, 1e-10)
+        assert rel_err(dx, g("grad_9_x")) < 1e-6      # fp32 round-off of a gradient with heavy cancellation
+
+
+@pytest.mark.parametrize("case", list(PICO_BLOCK_CASES))
+def test_pico_block_layernorm_then_attention(pico_ln, case):
+    """Inside the reference's transformer-block vectors: 1_x -> LayerNorm -> 2_x_ln11 -> attention layer -> 3_x_attn,
+    and back: grad_8_x_attn -> grad_9_ln1 -> (LayerNorm backward + the residual branch grad_8_x) -> grad_10_x."""
+    H = PICO_BLOCK_CASES[case]
+    g = lambda n: pico_ln[f"{case}/{n}"]
+    ln1, stdev = oracle.layernorm_forward(g("1_x"), 1e-10)
+    np.testing.assert_allclose(ln1, g("2_x_ln11"), atol=3e-7)
+    mask = oracle.causal_mask(ln1.shape[1])
+    attn = csa_forward(g("2_x_ln11"), g("attn_weight"), g("attn_bias"), g("attn_proj_weight"), g("attn_proj_bias"), H,
+                       lambda q, k, v: oracle.sdpa_forward(q, k, v, mask, 1))
+    np.testing.assert_allclose(attn, g("3_x_attn"), atol=1e-7)
+    d_ln1 = csa_backward(g("2_x_ln11"), g("attn_weight"), g("attn_bias"), g("attn_proj_weight"), H, g("grad_8_x_attn"),
+                         lambda q, k, v, dy: oracle.sdpa_backward(q, k, v, dy, mask, 1))
+    assert rel_err(d_ln1, g("grad_9_ln1")) < 2e-7
+    dx = oracle.layernorm_backward(ln1, g("grad_9_ln1"), stdev, 1e-10) + g("grad_8_x")
+    assert rel_err(dx, g("grad_10_x")) < 2e-7
 
 
 def test_masked_row_is_uniform():
