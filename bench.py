@@ -678,8 +678,14 @@ def run_train(cx, steps=4):
     res = {"workload": f"config2 attention core: {L} layers x (forward + backward), B={B} H={H} D={D} T={T}, causal",
            "flops_per_step": {"forward": fwd_flops, "backward": bwd_flops}}
     st = torch.zeros(8, dtype=torch.int32, device=dev)
-    for name in ("fp32", "bf16"):
+    ws_bytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
+    ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=dev)
+    ws_ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+    # fp32: what a default handle runs (forward on the tensor cores with split fp16 operands, backward exact fp32 on
+    # CUDA cores); fp32_cuda_cores: forward on CUDA cores as well (MCA_FLAG_EXACT_FP32)
+    for name in ("fp32", "fp32_cuda_cores", "bf16"):
         bf = name == "bf16"
+        split_fwd = name == "fp32"
         dt = torch.bfloat16 if bf else torch.float32
         n_sets = 4
         sets = []
@@ -693,6 +699,10 @@ def run_train(cx, steps=4):
             if bf:
                 return lib.mca_sdpa_forward_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
                                                s["y"].data_ptr(), s["a"].data_ptr(), st.data_ptr(), sp)
+            if split_fwd:
+                return lib.mca_sdpa_forward_f32_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), 1, B, H, T, D, s["y"].data_ptr(),
+                                                   s["a"].data_ptr(), s["b"].data_ptr(), s["yc"].data_ptr(), ws_ptr, ws_bytes,
+                                                   st.data_ptr(), 0, sp)
             return lib.mca_sdpa_forward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), None, 3, None, B, H, T, D,
                                             s["y"].data_ptr(), s["a"].data_ptr(), s["b"].data_ptr(), s["yc"].data_ptr(), sp)
 
@@ -739,7 +749,8 @@ def run_train(cx, steps=4):
                                                 "useful FLOPs of forward + backward over their summed time, per layer")
         else:
             peak = 148 * 128 * 2 * 1.965e9 / 1e12    # fp32 FMA lanes x 2 flop x max SM clock: no measured figure exists for this pipe
-            entry["roofline"] = {"bound": "fp32 FMA issue (CUDA cores)", "kernel": "sdpa_fwd_f32_kernel<64> + sdpa_bwd_*_f32_kernel<64>",
+            entry["roofline"] = {"bound": "fp32 FMA issue (CUDA cores)" + (" for the backward; the forward is three fp16 tensor-core products per contraction" if split_fwd else ""),
+                                 "kernel": ("sdpa_fwd_tc_kernel<64,split> (+ pre-pass)" if split_fwd else "sdpa_fwd_f32_kernel<64>") + " + sdpa_bwd_*_f32_kernel<64>",
                                  "achieved": round(tot, 2), "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(tot / peak, 4),
                                  "peak_source": "nominal (148 SMs x 128 lanes x 2 x 1965 MHz)", "kernel_ms": round((fms + bms) / L, 4),
                                  "traffic": None}

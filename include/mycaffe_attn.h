@@ -113,11 +113,14 @@ typedef char* MCA_LPTSTR;
                                               TransformerGpu::forward(token, pos), llama2_gpu.cpp:32-111 */
 
 /* 10th long of ATTN_SET */
-#define MCA_DTYPE_F32 0   /* exact fp32 arithmetic on CUDA cores (default; what the reference computes) */
+#define MCA_DTYPE_F32 0   /* fp32 tensors at fp32 accuracy (default; what the reference computes): the forward runs on the tensor
+                             cores with every operand carried as two fp16 halves (head sizes 16, 32, 64; causal or no mask),
+                             otherwise, and always for the backward, exact fp32 arithmetic on CUDA cores */
 #define MCA_DTYPE_TF32 1  /* fp32 tensors, tcgen05 kind::tf32 products with fp32 accumulation */
 #define MCA_DTYPE_BF16 2  /* bf16 tensors (handles from MCA_FN_ALLOCMEM_BF16), tcgen05 kind::f16 */
 /* 11th long of ATTN_SET */
 #define MCA_FLAG_CAUSAL_IMPLICIT 1  /* hMask is ignored and the mask is the analytic lower triangle */
+#define MCA_FLAG_EXACT_FP32 2       /* MCA_DTYPE_F32 handles: never use the split-operand tensor-core forward */
 
 /* mask_mode of the raw entry points */
 #define MCA_MASK_MODE_NONE 0
@@ -248,6 +251,19 @@ MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* 
  * status: device int[4] the kernel writes when a bounded wait gives up (0 = ok). */
 MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                 int T, int D, void* y, float* lse, int* status, void* stream);
+
+/* fp32 SDPA forward at fp32 accuracy on the tensor cores.  Same math as attn.cu:518-602 with a causal or absent mask.
+ * q, k, v, y: fp32, (B,H,T,D) or the packed layout; D in {16, 32, 64}.  A pre-pass scales each tensor by a power of two
+ * and writes every element as two fp16 halves hi = fp16(x), lo = fp16(x - hi) into `workspace`
+ * (mca_sdpa_forward_f32_tc_workspace_bytes(B,H,T) bytes, 1024-byte aligned); every contraction is then three
+ * tcgen05 kind::f16 products hi.hi + hi.lo + lo.hi accumulated in fp32, P split the same way.  Within 1e-6 of the output
+ * scale of the fp64 result.  row_max, row_sum (optional, (B,H,T)) and y_copy (optional, (B,H,T,D) contiguous) are what
+ * mca_sdpa_backward_f32 needs.  status as mca_sdpa_forward_tc. */
+MCA_API int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T);
+MCA_API int mca_sdpa_forward_f32_tc_supported(int D);
+MCA_API int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D,
+                                    float* y, float* row_max, float* row_sum, float* y_copy, void* workspace,
+                                    int64_t workspace_bytes, int* status, int layout, void* stream);
 
 /* Self-check of the bounded waits inside the tensor-core kernels: launches one small kernel whose only thread waits
  * on a barrier nothing arrives on, for at most limit_us microseconds (<= 100000), then gives up the way a stalled

@@ -36,6 +36,8 @@ struct AttnHandle {
   float dropout = 0.f;
   // owned device buffers, sized at Set for the configured block size
   float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr, *delta = nullptr, *lse = nullptr;
+  void* split_ws = nullptr;    // fp16 halves of q, k, v for the split-operand tensor-core forward of fp32 handles
+  int64_t split_ws_bytes = 0;
   int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
   // state of the last forward, consumed by backward
   bool have_fwd = false;
@@ -45,6 +47,8 @@ struct AttnHandle {
   bool status_pending = false;  // a tensor-core launch was made in asynchronous mode and its status words are unread
   void release() {
     cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
+    cudaFree(split_ws);
+    split_ws = nullptr; split_ws_bytes = 0;
     row_max = row_sum = y_copy = delta = lse = nullptr;
     causal_flag = nullptr;
     configured = have_fwd = false;
@@ -367,6 +371,13 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
       return ERROR_MEMORY_OUT;
     }
   }
+  if (a.dtype == MCA_DTYPE_F32 && !(a.flags & MCA_FLAG_EXACT_FP32) && mca_sdpa_forward_f32_tc_supported(a.D) &&
+      (int64_t)a.B * a.H <= 65535) {
+    // fp32 callers get the tensor-core forward: room for the fp16 halves of q, k, v.  If it cannot be had the handle
+    // simply keeps to the CUDA-core kernels.
+    a.split_ws_bytes = mca_sdpa_forward_f32_tc_workspace_bytes(a.B, a.H, a.block);
+    if (cudaMalloc(&a.split_ws, (size_t)a.split_ws_bytes) != cudaSuccess) { cudaGetLastError(); a.split_ws = nullptr; a.split_ws_bytes = 0; }
+  }
   a.configured = true;
   return 0;
 }
@@ -462,8 +473,16 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
         (e = check_f32(k, (long)pl[5], n_in, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
       return e;
     if (packed) { kk += C; v += 2 * C; }
-    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, false))) return e;
+    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr))) return e;
     const bool save = a.training && T == a.block;
+    if (a.split_ws != nullptr && (mode == MCA_MASK_CAUSAL || mode == MCA_MASK_NONE)) {
+      e = mca_sdpa_forward_f32_tc(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
+                                  save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, a.split_ws, a.split_ws_bytes,
+                                  a.causal_flag + 1, layout, 0);
+      if (e) return e;
+      if (save) remember_forward(a, T, mode, layout, 0, false);
+      return tc_status(k, a);
+    }
     e = mca_sdpa_forward_f32_layout(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
                                     save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, layout, 0);
     if (!e && save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);

@@ -28,7 +28,18 @@
 //
 // Every wait on an mbarrier is bounded: after about a second without progress the waiting
 // thread records where it gave up in a status word and the CTA drains and exits.
+//
+// Three operand modes share the kernel:
+//   MODE_BF16   bf16 tensors, one kind::f16 product per contraction.
+//   MODE_TF32   fp32 tensors read as tf32 (kind::tf32), 64-wide heads.
+//   MODE_SPLIT  fp32 callers at fp32 accuracy: every operand x is carried as two fp16 values hi = fp16(x),
+//               lo = fp16(x - hi) (22 mantissa bits together; a pre-pass writes rows [hi | lo] after scaling each
+//               tensor by a power of two so that neither half leaves the fp16 range), and every contraction is three
+//               kind::f16 products hi.hi + hi.lo + lo.hi accumulated in the same fp32 TMEM tile.  P is split the
+//               same way by the softmax warps.  Measured against the fp64 oracle this is within 1e-6 of the output
+//               scale, i.e. what the exact fp32 CUDA-core kernel gives, at a third of the bf16 tensor rate.
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 
@@ -46,6 +57,7 @@ constexpr int WARP_TMA = NQT * 8;       // after the softmax warps (eight per qu
 constexpr int WARP_MMA = NQT * 8 + 1;
 constexpr int TC_THREADS = (NQT * 8 + 2) * 32;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr int MODE_BF16 = 0, MODE_TF32 = 1, MODE_SPLIT = 2;
 
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan (all tiles 1024-byte aligned)
@@ -106,17 +118,26 @@ struct TcParams {
   McaStrides ys;     // element strides of the output view
   void* y_more[7];   // further destinations of the same bf16 output tile (peer GPUs' buffers), same strides
   int n_more;
+  // MODE_SPLIT: {1 / (scale_q * scale_k), 1 / scale_v} of the pre-pass (device memory); exact softmax statistics for
+  // the fp32 backward: row_max in natural-log units of the scaled logits and the matching row sum, (B*H, T) each
+  const float* split_fac;
+  float* row_max;
+  float* row_sum;
+  float* y_copy;      // second copy of the fp32 output, (B*H, T, HD) contiguous, or null
 };
 
-// TF32 = false: bf16 tensors, kind::f16.  TF32 = true: fp32 tensors read as tf32 (kind::tf32),
-// P handed to the second product as fp32 in place of S, fp32 output.
-template <int HD, bool TF32>
+// MODE_TF32: P is handed to the second product as fp32 in place of S; MODE_TF32 and MODE_SPLIT write fp32 output.
+template <int HD, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  constexpr bool TF32 = MODE == MODE_TF32;
+  constexpr bool SPLIT = MODE == MODE_SPLIT;
+  constexpr bool F32_OUT = TF32 || SPLIT;
   constexpr int ELT = TF32 ? 4 : 2;            // bytes per element
   constexpr int BOX = 128 / ELT;               // elements per 128-byte sub-tile row
-  using PL = Plan<HD * ELT>;
+  // split rows are [hi (64 fp16, HD used) | lo (64 fp16, HD used)]: two 128-byte sub-tiles whatever the head size
+  using PL = Plan<SPLIT ? 256 : HD * ELT>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -225,10 +246,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     {
       const uint32_t leader = elect_one() ? 1u : 0u;
       const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      constexpr uint32_t IDESC_QK = make_idesc_fmt(BLK, BLK, 0, 0, TF32 ? 2 : 1);
-      constexpr uint32_t IDESC_PV = make_idesc_fmt(BLK, HD, 0, 1, TF32 ? 2 : 1);
-      constexpr int KSTEPS_QK = HD * ELT / 32;   // 32 bytes of the head dimension per MMA
-      constexpr int KSTEPS_PV = BLK * ELT / 32;  // 16 (bf16) or 8 (tf32) keys per MMA
+      constexpr int FMT = TF32 ? 2 : (SPLIT ? 0 : 1);      // operand format of the instruction descriptor: tf32, fp16, bf16
+      constexpr uint32_t IDESC_QK = make_idesc_fmt(BLK, BLK, 0, 0, FMT);
+      constexpr uint32_t IDESC_PV = make_idesc_fmt(BLK, HD, 0, 1, FMT);
+      constexpr int KSTEPS_QK = HD * ELT / 32;   // 32 bytes of the head dimension per MMA (per half in split mode)
+      constexpr int KSTEPS_PV = BLK * ELT / 32;  // 16 (bf16, fp16) or 8 (tf32) keys per MMA
       // A descriptor's start-address field (bits 0-13, in 16-byte units) never carries for offsets
       // inside the CTA's shared memory, so stepping a tile is an add on the low word.
       const uint64_t desc_q0 = make_desc(smem_base + PL::OFF_Q, 16, 1024);
@@ -241,10 +263,23 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint64_t dq = desc_q0 + (uint64_t)((x * PL::TILE_BYTES) >> 4);
         const uint64_t dk = desc_k0 + (uint64_t)((st * PL::TILE_BYTES) >> 4);
         const uint32_t d_tmem = tmem_base_u + x * BLK;
+        if constexpr (SPLIT) {
+          // S = Qhi Khi^T + Qhi Klo^T + Qlo Khi^T: the halves are the two sub-tiles of a row
+          constexpr uint32_t LO = PL::SUB_BYTES >> 4;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS_QK; ++kk) {
-          const uint32_t off = ((uint32_t)(kk >> 2) * PL::SUB_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
-          umma_ss_if<TF32>(leader, d_tmem, dq + off, dk + off, IDESC_QK, kk > 0 ? 1u : 0u);
+          for (int term = 0; term < 3; ++term) {
+            const uint32_t oq = term == 2 ? LO : 0u, ok_ = term == 1 ? LO : 0u;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS_QK; ++kk)
+              umma_ss_if<false>(leader, d_tmem, dq + oq + (uint32_t)(kk * 2), dk + ok_ + (uint32_t)(kk * 2), IDESC_QK,
+                                (term > 0 || kk > 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS_QK; ++kk) {
+            const uint32_t off = ((uint32_t)(kk >> 2) * PL::SUB_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
+            umma_ss_if<TF32>(leader, d_tmem, dq + off, dk + off, IDESC_QK, kk > 0 ? 1u : 0u);
+          }
         }
       };
       auto issue_pv = [&](int x, int st, bool first, int half) {
@@ -255,9 +290,19 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t d_tmem = tmem_base_u + 2 * BLK + x * BLK;
         const uint32_t a_tmem = tmem_base_u + x * BLK;
 #pragma unroll
-        for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk)
-          umma_ts_if<TF32>(leader, d_tmem, a_tmem + (uint32_t)(kk * 8), dv + (uint64_t)((uint32_t)kk * V_STEP), IDESC_PV,
-                           (first && kk == 0) ? 0u : 1u);
+        for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk) {
+          if constexpr (SPLIT) {
+            // O += Phi Vhi + Phi Vlo + Plo Vhi: Phi in columns [0,64) of the S region, Plo in [64,128)
+            const uint64_t dvk = dv + (uint64_t)((uint32_t)kk * V_STEP);
+            const uint32_t a_hi = a_tmem + (uint32_t)(kk * 8);
+            umma_ts_if<false>(leader, d_tmem, a_hi, dvk, IDESC_PV, (first && kk == 0) ? 0u : 1u);
+            umma_ts_if<false>(leader, d_tmem, a_hi, dvk + (uint64_t)(PL::SUB_BYTES >> 4), IDESC_PV, 1u);
+            umma_ts_if<false>(leader, d_tmem, a_hi + 64u, dvk, IDESC_PV, 1u);
+          } else {
+            umma_ts_if<TF32>(leader, d_tmem, a_tmem + (uint32_t)(kk * 8), dv + (uint64_t)((uint32_t)kk * V_STEP), IDESC_PV,
+                             (first && kk == 0) ? 0u : 1u);
+          }
+        }
       };
 #pragma unroll
       for (int x = 0; x < NQT; ++x)
@@ -343,6 +388,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int qrow0 = q0 + x * BLK;
     float m_used[2] = {-INFINITY, -INFINITY};
     float l[2] = {0.f, 0.f};                            // this thread's part of the row sums
+    // split mode: the pre-pass scaled q and k by powers of two; dividing them out of the logit scale is exact
+    const float scale_log2 = SPLIT ? p.scale_log2 * __ldg(p.split_fac) : p.scale_log2;
     for (int j = 0; j < n && ok; ++j) {
       TC_TRACE(x, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
@@ -377,7 +424,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         float m = fmaxf(ma, mb);
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        mx[h] = m * p.scale_log2;
+        mx[h] = m * scale_log2;
       }
       TC_TRACE_W(j, 1);
       float m_new[2];
@@ -399,24 +446,35 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           f[h] = (m_new[h] != m_used[h]) ? fast_exp2(m_used[h] - m_new[h]) : 1.0f;
           l[h] *= f[h];
         }
+        if constexpr (HD >= 32) {
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[16];
-          tmem_ldq256_x4(t_o + c * 32, o);
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[16];
+            tmem_ldq256_x4(t_o + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f[(i >> 1) & 1]);
+            tmem_stq256_x4(t_o + c * 32, o);
+          }
+        } else {   // 16 columns
+          uint32_t o[8];
+          tmem_ldq256_x2(t_o, o);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f[(i >> 1) & 1]);
-          tmem_stq256_x4(t_o + c * 32, o);
+          for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f[(i >> 1) & 1]);
+          tmem_stq256_x2(t_o, o);
         }
       }
       TC_TRACE_W(j, 2);
       // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
       // the row sum is taken in fp32.  The first 64 keys are handed to the MMA warp before the rest.
       const float2 nm2[2] = {make_float2(-m_new[0], -m_new[0]), make_float2(-m_new[1], -m_new[1])};
-      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 scale2 = make_float2(scale_log2, scale_log2);
       float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[16];
-      // exponentials of key groups [g_lo, g_hi) (8 keys each); bf16 results packed into pk[0..], tf32 in place.
+      uint32_t pk_lo[SPLIT ? 16 : 1];
+      // exponentials of key groups [g_lo, g_hi) (8 keys each); bf16 results packed into pk[0..], tf32 in place;
+      // split mode: hi = p with the mantissa cut to fp16 width (so the conversion is exact), lo = p - hi.
       // A thread's two adjacent keys of a row go through the scale-and-subtract and the row sum as one fp32 pair.
       auto exp_groups = [&](const int g_lo, const int g_hi) {
 #pragma unroll
@@ -429,6 +487,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if constexpr (TF32) {
               s[4 * g + 2 * h] = __float_as_uint(p0);
               s[4 * g + 2 * h + 1] = __float_as_uint(p1);
+            } else if constexpr (SPLIT) {
+              const float h0 = __uint_as_float(__float_as_uint(p0) & 0xffffe000u), h1 = __uint_as_float(__float_as_uint(p1) & 0xffffe000u);
+              pk[2 * (g - g_lo) + h] = pack_f16(h0, h1);
+              pk_lo[2 * (g - g_lo) + h] = pack_f16(p0 - h0, p1 - h1);
             } else {
               pk[2 * (g - g_lo) + h] = pack_bf16(p0, p1);
             }
@@ -442,6 +504,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       exp_groups(0, 8);
       if constexpr (TF32) tmem_stq256_x8(t_s, s);
       else tmem_stq128_x8(t_s, pk);
+      if constexpr (SPLIT) tmem_stq128_x8(t_s + 64, pk_lo);
       TC_TRACE(x, j, 3);
       exp_groups(8, 12);
       tmem_wait_st();
@@ -450,9 +513,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (lane == 0) mbar_arrive(bar(BAR_P_HALF + x));
       if constexpr (TF32) tmem_stq256_x4(t_s + 64, s + 32);
       else tmem_stq128_x4(t_s + 32, pk);
+      if constexpr (SPLIT) tmem_stq128_x4(t_s + 96, pk_lo);
       exp_groups(12, 16);
       if constexpr (TF32) tmem_stq256_x4(t_s + 96, s + 48);
       else tmem_stq128_x4(t_s + 48, pk);
+      if constexpr (SPLIT) tmem_stq128_x4(t_s + 112, pk_lo);
       TC_TRACE(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
@@ -489,13 +554,14 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int row = (warp & 3) * 32 + lane;
         const int qi = qrow0 + row;
         const float lsum = red_l[row];
-        const float inv = 1.0f / lsum;
+        // split mode: the pre-pass scaled v by a power of two; dividing it out here is exact
+        const float inv = SPLIT ? __ldg(p.split_fac + 1) / lsum : 1.0f / lsum;
         const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BLK + x * BLK + half * OC);
         const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
         float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
         bool scattered = false;
-        if constexpr (!TF32) {
+        if constexpr (!F32_OUT) {
           if (p.n_more > 0) {   // uniform over the grid
             // Output that also goes to peers' buffers: stage this warp's 32 rows x OC columns in the shared memory
             // of its query tile (every product that read it has completed), then store whole 16-byte pieces so
@@ -538,19 +604,36 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
           }
         }
-        if (!scattered) {
+        if constexpr (OC < 16) {   // 16-wide heads (split mode): eight columns per thread
+          uint32_t o[8];
+          tmem_ld8(t_o32, o);
+          tmem_wait_ld();
+          if (qi < T) {
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) {
+              const float4 w = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                           __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              *reinterpret_cast<float4*>(yrow_f + i) = w;
+              if (p.y_copy) *reinterpret_cast<float4*>(p.y_copy + ((int64_t)bh * T + qi) * HD + half * OC + i) = w;
+            }
+          }
+        } else if (!scattered) {
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t o[16];
           tmem_ld16(t_o32 + c * 16, o);
           tmem_wait_ld();
-          if constexpr (TF32) {
+          if constexpr (F32_OUT) {
             if (qi < T) {
 #pragma unroll
-              for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4*>(yrow_f + c * 16 + i) =
-                    make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, __uint_as_float(o[i + 2]) * inv,
-                                __uint_as_float(o[i + 3]) * inv);
+              for (int i = 0; i < 16; i += 4) {
+                const float4 w = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                             __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                *reinterpret_cast<float4*>(yrow_f + c * 16 + i) = w;
+                if constexpr (SPLIT) {
+                  if (p.y_copy) *reinterpret_cast<float4*>(p.y_copy + ((int64_t)bh * T + qi) * HD + half * OC + c * 16 + i) = w;
+                }
+              }
             }
           } else if (qi < T) {
 #pragma unroll
@@ -566,6 +649,14 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         }
         if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum);
+        if constexpr (SPLIT) {
+          // what the exact fp32 backward needs to recompute P = exp(s - row_max) / row_sum: the exponent's reference
+          // point in natural-log units (it need not be the true maximum) and the sum taken against it
+          if (half == 0 && p.row_max != nullptr && qi < T) {
+            p.row_max[(int64_t)bh * T + qi] = red_m[row] * 0.6931471805599453f;
+            p.row_sum[(int64_t)bh * T + qi] = lsum;
+          }
+        }
       }
     }
   }
@@ -579,16 +670,28 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 
-template <int HD, bool TF32>
+struct SplitExtras {
+  const float* fac = nullptr;   // {1 / (scale_q * scale_k), 1 / scale_v}
+  float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr;
+};
+
+template <int HD, int MODE>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
               int* status, int layout, cudaStream_t st, void* const* y_more = nullptr, int n_more = 0,
-              const McaStrides* y_strides = nullptr) {
+              const McaStrides* y_strides = nullptr, const SplitExtras* split = nullptr) {
   CUtensorMap mq, mk, mv;
   int e;
   const McaStrides sin = mca_in_strides(layout, H, T, HD);
-  if constexpr (TF32) {
+  if constexpr (MODE == MODE_TF32) {
     if ((e = make_map_f32(&mq, q, B, H, T, HD, sin)) || (e = make_map_f32(&mk, k, B, H, T, HD, sin)) ||
         (e = make_map_f32(&mv, v, B, H, T, HD, sin, true)))
+      return e;
+  } else if constexpr (MODE == MODE_SPLIT) {
+    // the pre-pass wrote contiguous (B, H, T, 128) fp16 rows [hi | lo], whatever layout the fp32 tensors have
+    const McaStrides sp{(int64_t)H * T * 128, (int64_t)T * 128, 128};
+    if ((e = make_map_4d(&mq, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
+        (e = make_map_4d(&mk, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
+        (e = make_map_4d(&mv, v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)))
       return e;
   } else {
     if ((e = make_map_bf16(&mq, q, B, H, T, HD, sin)) || (e = make_map_bf16(&mk, k, B, H, T, HD, sin)) ||
@@ -599,7 +702,8 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal; p.H = H;
   // K and V of one (batch, head) are 2 * T * HD elements; keep a group's set under about 64 MB of the 126 MB L2
   {
-    const int64_t kv_bytes = (int64_t)2 * T * HD * (TF32 ? 4 : 2);
+    const int64_t row_bytes = MODE == MODE_SPLIT ? 256 : HD * (MODE == MODE_TF32 ? 4 : 2);
+    const int64_t kv_bytes = (int64_t)2 * T * row_bytes;
     int64_t g = (64ll << 20) / kv_bytes;
     p.group = (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)B * H));
     if (!causal) p.group = 1;   // equal work per CTA: nothing to balance
@@ -608,11 +712,109 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.n_more = n_more;
   for (int i = 0; i < 7; ++i) p.y_more[i] = i < n_more ? y_more[i] : nullptr;
   p.scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
-  const size_t smem = Plan<HD * (TF32 ? 4 : 2)>::BYTES;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  p.split_fac = split ? split->fac : nullptr;
+  p.row_max = split ? split->row_max : nullptr;
+  p.row_sum = split ? split->row_sum : nullptr;
+  p.y_copy = split ? split->y_copy : nullptr;
+  const size_t smem = Plan<MODE == MODE_SPLIT ? 256 : HD * (MODE == MODE_TF32 ? 4 : 2)>::BYTES;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(mca_ceil_div(T, NQT * BLK), B * H);
-  sdpa_fwd_tc_kernel<HD, TF32><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
+  sdpa_fwd_tc_kernel<HD, MODE><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
   return mca_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pre-pass of the split mode: per-tensor maximum, then rows [hi | lo] in fp16.
+// ---------------------------------------------------------------------------------------------
+struct SplitSrc {
+  const float* ptr[3];   // q, k, v (fp32), element strides `st`
+  __half* dst[3];        // (B, H, T, 128) fp16
+};
+
+// amax[i] = max |x| of tensor i (as the bit pattern of a non-negative float: integer order = float order)
+template <int HD>
+__global__ void __launch_bounds__(256) split_amax_kernel(const SplitSrc src, McaStrides st, int H, int T, int64_t rows,
+                                                         unsigned int* __restrict__ amax) {
+  const float* x = src.ptr[blockIdx.y];
+  constexpr int V4 = HD / 4;
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / V4;
+    const int c = (int)(i - row * V4);
+    const int64_t bh = row / T, t = row - bh * T;
+    const int64_t b = bh / H, h = bh - b * H;
+    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax + blockIdx.y, __float_as_uint(m));
+}
+
+// The power of two that brings max |x| to about 2^13: both halves of every element that matters then lie in the
+// normal range of fp16 (largest 65504; the low half of x is about 2^-11 |x|).
+__device__ __forceinline__ float split_scale(unsigned int amax_bits) {
+  const float a = __uint_as_float(amax_bits);
+  if (!(a > 0.f) || !(a < 3.0e38f)) return 1.0f;
+  int e;
+  frexpf(a, &e);                    // a = f * 2^e, f in [0.5, 1)
+  return ldexpf(1.0f, 13 - e);      // a * scale in [2^12, 2^13)
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) split_rows_kernel(const SplitSrc src, McaStrides st, int H, int T, int64_t rows,
+                                                         const unsigned int* __restrict__ amax, float* __restrict__ fac) {
+  const int which = blockIdx.y;
+  const float* x = src.ptr[which];
+  __half* dst = src.dst[which];
+  const float sc = split_scale(amax[which]);
+  if (which == 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+    fac[0] = 1.0f / (split_scale(amax[0]) * split_scale(amax[1]));   // powers of two: exact
+    fac[1] = 1.0f / split_scale(amax[2]);
+  }
+  constexpr int V4 = HD / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / V4;
+    const int c = (int)(i - row * V4);
+    const int64_t bh = row / T, t = row - bh * T;
+    const int64_t b = bh / H, h = bh - b * H;
+    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+    const float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+    __half hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      hi[j] = __float2half_rn(e[j]);
+      lo[j] = __float2half_rn(e[j] - __half2float(hi[j]));
+    }
+    __half* o = dst + row * 128 + c * 4;
+    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(hi);
+    *reinterpret_cast<uint2*>(o + 64) = *reinterpret_cast<const uint2*>(lo);
+  }
+}
+
+template <int HD>
+int launch_split(const float* q, const float* k, const float* v, int causal, int B, int H, int T, float* y, float* row_max,
+                 float* row_sum, float* y_copy, void* workspace, int* status, int layout, cudaStream_t st) {
+  const int64_t rows = (int64_t)B * H * T;
+  // workspace: amax[4] (uint) | fac[4] (float) | 3 x rows x 128 fp16, the tensors 1024-byte aligned
+  unsigned int* amax = static_cast<unsigned int*>(workspace);
+  float* fac = reinterpret_cast<float*>(amax + 4);
+  __half* base = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 1024);
+  SplitSrc src;
+  src.ptr[0] = q; src.ptr[1] = k; src.ptr[2] = v;
+  for (int i = 0; i < 3; ++i) src.dst[i] = base + (size_t)i * rows * 128;
+  const McaStrides sin = mca_in_strides(layout, H, T, HD);
+  MCA_CUDA_TRY(cudaMemsetAsync(amax, 0, 4 * sizeof(unsigned int), st));
+  const int blocks = (int)std::min<int64_t>(148 * 8, (rows * (HD / 4) + 255) / 256);
+  split_amax_kernel<HD><<<dim3(blocks, 3), 256, 0, st>>>(src, sin, H, T, rows, amax);
+  int e = mca_launch_status();
+  if (e) return e;
+  split_rows_kernel<HD><<<dim3(blocks, 3), 256, 0, st>>>(src, sin, H, T, rows, amax, fac);
+  if ((e = mca_launch_status())) return e;
+  SplitExtras ex;
+  ex.fac = fac; ex.row_max = row_max; ex.row_sum = row_sum; ex.y_copy = y_copy;
+  return launch_tc<HD, MODE_SPLIT>(src.dst[0], src.dst[1], src.dst[2], causal, B, H, T, y, nullptr, status, layout, st, nullptr, 0,
+                                   nullptr, &ex);
 }
 
 }  // namespace
@@ -647,8 +849,8 @@ int mca_sdpa_forward_tc_scatter(const void* q, const void* k, const void* v, int
   if (bits & 15) return ERROR_PARAM_OUT_OF_RANGE;
   const McaStrides ys{y_stride_b, y_stride_h, y_stride_t};
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
-  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
+  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
+  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y_dst[0], lse, status, MCA_LAYOUT_BHTD, st, y_dst + 1, n_dst - 1, &ys);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }
 
@@ -665,10 +867,39 @@ int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int 
   if (dtype == MCA_DTYPE_TF32) {
     // fp32 rows are twice as wide: only the 64-wide head fits the shared-memory plan (two query tiles,
     // two K/V stages); wider heads use the exact fp32 kernel
-    if (D == 64) return launch_tc<64, true>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+    if (D == 64) return launch_tc<64, MODE_TF32>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
   }
-  if (D == 128) return launch_tc<128, false>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
-  if (D == 64) return launch_tc<64, false>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+  return ERROR_ATTN_UNSUPPORTED_SHAPE;
+}
+
+int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T) {
+  if (B <= 0 || H <= 0 || T <= 0) return -1;
+  return 1024 + (int64_t)3 * B * H * T * 128 * 2;
+}
+
+int mca_sdpa_forward_f32_tc_supported(int D) { return D == 16 || D == 32 || D == 64; }
+
+int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D, float* y,
+                            float* row_max, float* row_sum, float* y_copy, void* workspace, int64_t workspace_bytes,
+                            int* status, int layout, void* stream) {
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
+  if (!q || !k || !v || !y || !status || !workspace) return ERROR_PARAM_NULL;
+  if ((row_max == nullptr) != (row_sum == nullptr)) return ERROR_PARAM_NULL;
+  if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  if (!mca_sdpa_forward_f32_tc_supported(D)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (workspace_bytes < mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(y_copy)) & 15)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return ERROR_PARAM_OUT_OF_RANGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (D) {
+    case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
+    case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
+    case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
+  }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

@@ -146,7 +146,7 @@ __device__ __forceinline__ void load_vec_rope(const float* __restrict__ src, int
 }
 
 template <typename CT, int HS, int KVM>
-__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(DEC_THREADS, KVM == 1 ? 2 : 1) decode_split_kernel(const DecodeParams p) {   // one query head per kv head: two CTAs per SM (at most 128 registers)
   constexpr int EPL = Epl<CT, HS>::value;
   using Row = RowSlice<CT, EPL>;
   constexpr int G = HS / EPL;     // lanes per cache row

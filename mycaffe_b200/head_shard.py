@@ -71,7 +71,13 @@ class PeerOutput:
     buffers, and the forward kernel stores every finished piece of its heads' output tiles into all of them
     (`mca_sdpa_forward_tc_scatter`), so the all-gather disappears into the kernel's epilogue.  `wait()` is the
     only synchronisation left: a one-element all-reduce on the current stream, after which every rank's
-    stores have landed everywhere."""
+    stores have landed everywhere.
+
+    Every rank writes into every buffer, so the buffer is also a write-after-read hazard: a rank that is still
+    reading step n's result must not have step n+1's kernels of its peers writing into it.  `wait()` only orders
+    "all kernels finished" before the local reads; a consumer therefore calls `release()` (a second collective)
+    once it has finished reading and before anyone launches the next scatter -- or alternates between two
+    `PeerOutput` buffers.  A caller with no consumer between steps (the benchmark) needs neither."""
 
     def __init__(self, B: int, H: int, T: int, D: int, device, group=None):
         import ctypes
@@ -109,4 +115,8 @@ class PeerOutput:
 
     def wait(self) -> None:
         """Every rank's kernel has finished (stream-ordered; the host does not block)."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def release(self) -> None:
+        """Every rank has finished reading the buffer (stream-ordered): the next scatter may overwrite it."""
         dist.all_reduce(self._flag, group=self.group)

@@ -1,0 +1,139 @@
+"""The split-operand tensor-core forward for fp32 callers (every operand carried as two fp16 halves, three products
+per contraction): parity with the fp64 oracle at fp32 accuracy, through the raw entry point and through ATTN_FWD on a
+default (fp32) handle."""
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import Sdpa
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+SPLIT_TOL = 5e-6   # measured about 1e-7 .. 7e-7; the exact CUDA-core kernel is held to 2e-5 elsewhere
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    from mycaffe_b200 import CudaDnn
+    c = CudaDnn(0)
+    yield c
+    c.Dispose()
+
+
+def run_raw(q, k, v, causal, want_stats=False, layout=0):
+    import torch
+    from mycaffe_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    B, H, T, D = q.shape
+    if layout == 1:   # (B,T,3C) projection output, y as (B,T,C)
+        C_ = H * D
+        qkv = np.concatenate([a.transpose(0, 2, 1, 3).reshape(B, T, C_) for a in (q, k, v)], axis=-1)
+        t = torch.from_numpy(np.ascontiguousarray(qkv)).to(dev)
+        qd, kd, vd = t, t, t
+        ptrs = (t.data_ptr(), t.data_ptr() + C_ * 4, t.data_ptr() + 2 * C_ * 4)
+    else:
+        qd, kd, vd = (torch.from_numpy(a).to(dev) for a in (q, k, v))
+        ptrs = (qd.data_ptr(), kd.data_ptr(), vd.data_ptr())
+    y = torch.empty(B * H * T * D, device=dev)
+    rm, rs = torch.empty(B * H * T, device=dev), torch.empty(B * H * T, device=dev)
+    yc = torch.empty(B * H * T * D, device=dev)
+    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
+    ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+    wp = (ws.data_ptr() + 1023) // 1024 * 1024
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
+    rc = lib.mca_sdpa_forward_f32_tc(*ptrs, int(causal), B, H, T, D, y.data_ptr(), rm.data_ptr() if want_stats else None,
+                                     rs.data_ptr() if want_stats else None, yc.data_ptr() if want_stats else None, wp, nbytes,
+                                     st.data_ptr(), layout, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and st[0].item() == 0, (rc, st[:4].tolist())
+    yh = y.cpu().numpy()
+    yh = yh.reshape(B, T, H, D).transpose(0, 2, 1, 3) if layout == 1 else yh.reshape(B, H, T, D)
+    if want_stats:
+        return yh, rm.cpu().numpy().reshape(B, H, T), rs.cpu().numpy().reshape(B, H, T), yc.cpu().numpy().reshape(B, H, T, D)
+    return yh
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D", [16, 32, 64])
+@pytest.mark.parametrize("T", [1, 17, 128, 200, 257, 1024])
+def test_split_forward_matches_fp64(T, D, causal):
+    rng = np.random.default_rng(31 * T + D)
+    B, H = 2, 3
+    q, k, v = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(3))
+    y = run_raw(q, k, v, causal)
+    ref = oracle.sdpa_forward(q, k, v, None, 3 if causal else 0, f64=True)
+    assert rel_err(y, ref) < SPLIT_TOL
+
+
+@pytest.mark.parametrize("scale", [1e-4, 0.02, 300.0, 1e6])
+def test_split_forward_is_scale_free(scale):
+    """Each tensor is scaled by a power of two before it is split, so tiny and huge tensors keep fp32 accuracy
+    (unscaled, their low halves would leave the fp16 range)."""
+    rng = np.random.default_rng(7)
+    B, H, T, D = 1, 2, 300, 64
+    q = (scale * rng.standard_normal((B, H, T, D))).astype(np.float32)
+    k = (rng.standard_normal((B, H, T, D)) / scale).astype(np.float32)     # logits stay O(1)
+    v = (scale * rng.standard_normal((B, H, T, D))).astype(np.float32)
+    y = run_raw(q, k, v, True)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < SPLIT_TOL
+    z = np.zeros_like(q)                                                    # an all-zero tensor has no scale
+    y0 = run_raw(z, k, v, True)
+    cm = np.cumsum(v.astype(np.float64), axis=2) / np.arange(1, T + 1)[None, None, :, None]
+    assert rel_err(y0, cm) < SPLIT_TOL
+
+
+def test_split_forward_statistics_and_packed_layout():
+    rng = np.random.default_rng(11)
+    B, H, T, D = 2, 4, 160, 32
+    q, k, v = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(3))
+    ref, p = oracle.sdpa_forward(q, k, v, None, 3, f64=True, want_probs=True)
+    y, rm, rs, yc = run_raw(q, k, v, True, want_stats=True)
+    assert rel_err(y, ref) < SPLIT_TOL
+    np.testing.assert_array_equal(yc, y)
+    # exp(s - row_max) / row_sum must be the probabilities (row_max need not be the true maximum)
+    s = np.einsum("bhid,bhjd->bhij", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(D)
+    got = np.exp(s - rm[..., None]) / rs[..., None]
+    got = np.where(np.tril(np.ones((T, T), bool)), got, 0.0)
+    assert np.abs(got - p).max() < 5e-6
+    yp = run_raw(q, k, v, True, layout=1)
+    np.testing.assert_array_equal(yp, y)
+
+
+def test_default_fp32_handle_uses_it_and_the_flag_switches_it_off(cuda):
+    """ATTN_FWD / ATTN_BWD on a default handle (what an unmodified C# layer creates): forward on the tensor cores,
+    backward in exact fp32 from the statistics the forward left; with MCA_FLAG_EXACT_FP32 both on CUDA cores."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(12)
+    B, H, T, D = 2, 4, 384, 64
+    q, k, v, dy = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(4))
+    mask = oracle.causal_mask(T)
+    ref = oracle.sdpa_forward(q, k, v, mask, 1, f64=True)
+    gref = oracle.sdpa_backward(q, k, v, dy, mask, 1, f64=True)
+    outs = {}
+    for name, flags in (("default", None), ("exact", ids.MCA_FLAG_EXACT_FP32)):
+        a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_F32 if flags else None, flags=flags)
+        outs[name] = a.forward(q, k, v, mask)
+        assert rel_err(outs[name], ref) < 2e-5
+        for g_, r_ in zip(a.backward(dy), gref):
+            assert rel_err(g_, r_) < 2e-5
+        a.close()
+    assert rel_err(outs["default"], ref) < SPLIT_TOL
+    assert not np.array_equal(outs["default"], outs["exact"])     # two different kernels ran
+    # a general (non-causal) mask keeps to the CUDA-core kernel on the default handle
+    band = np.triu(mask, -5).astype(np.float32)
+    a = Sdpa(cuda, B, T, H, D)
+    assert rel_err(a.forward(q, k, v, band), oracle.sdpa_forward(q, k, v, band, 1, f64=True)) < 2e-5
+    a.close()
+
+
+def test_gpt2_layer_shape_split(cuda):
+    """Config 2's layer shape (12 heads x 64, T = 1024) on the default handle, B = 2, every (batch, head)."""
+    rng = np.random.default_rng(2)
+    B, H, T, D = 2, 12, 1024, 64
+    q, k, v = ((0.5 * rng.standard_normal((B, H, T, D))).astype(np.float32) for _ in range(3))
+    a = Sdpa(cuda, B, T, H, D)
+    y = a.forward(q, k, v, oracle.causal_mask(T))
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < SPLIT_TOL
+    a.close()
