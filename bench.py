@@ -679,10 +679,8 @@ def run_train(cx, steps=4):
            "flops_per_step": {"forward": fwd_flops, "backward": bwd_flops}}
     st = torch.zeros(8, dtype=torch.int32, device=dev)
     ws_bytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
-    ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=dev)
-    ws_ptr = (ws.data_ptr() + 1023) // 1024 * 1024
-    # fp32: what a default handle runs (forward on the tensor cores with split fp16 operands, backward exact fp32 on
-    # CUDA cores); fp32_cuda_cores: forward on CUDA cores as well (MCA_FLAG_EXACT_FP32)
+    # fp32: what a default handle runs (forward and backward on the tensor cores with split fp16 operands);
+    # fp32_cuda_cores: exact fp32 arithmetic on CUDA cores (MCA_FLAG_EXACT_FP32)
     for name in ("fp32", "fp32_cuda_cores", "bf16"):
         bf = name == "bf16"
         split_fwd = name == "fp32"
@@ -694,6 +692,9 @@ def run_train(cx, steps=4):
             sets.append(dict(q=q, k=k, v=v, dy=dy, y=torch.empty_like(q), dq=torch.empty_like(q), dk=torch.empty_like(q),
                              dv=torch.empty_like(q), a=torch.empty(B, H, T, device=dev), b=torch.empty(B, H, T, device=dev),
                              delta=torch.empty(B, H, T, device=dev), yc=torch.empty(B, H, T, D, device=dev) if not bf else None))
+            if split_fwd:   # each layer keeps the fp16 halves of its q, k, v from forward to backward
+                sets[-1]["ws_t"] = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+                sets[-1]["ws"] = sets[-1]["ws_t"].data_ptr()
 
         def fwd(s):
             if bf:
@@ -701,7 +702,7 @@ def run_train(cx, steps=4):
                                                s["y"].data_ptr(), s["a"].data_ptr(), st.data_ptr(), sp)
             if split_fwd:
                 return lib.mca_sdpa_forward_f32_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), 1, B, H, T, D, s["y"].data_ptr(),
-                                                   s["a"].data_ptr(), s["b"].data_ptr(), s["yc"].data_ptr(), ws_ptr, ws_bytes,
+                                                   None, None, s["yc"].data_ptr(), s["a"].data_ptr(), s["ws"], ws_bytes,
                                                    st.data_ptr(), 0, sp)
             return lib.mca_sdpa_forward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), None, 3, None, B, H, T, D,
                                             s["y"].data_ptr(), s["a"].data_ptr(), s["b"].data_ptr(), s["yc"].data_ptr(), sp)
@@ -711,6 +712,10 @@ def run_train(cx, steps=4):
                 return lib.mca_sdpa_backward_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), s["y"].data_ptr(), s["dy"].data_ptr(),
                                                 s["a"].data_ptr(), s["delta"].data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
                                                 s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), st.data_ptr(), sp)
+            if split_fwd:
+                return lib.mca_sdpa_backward_f32_tc(s["dy"].data_ptr(), s["yc"].data_ptr(), s["a"].data_ptr(), s["delta"].data_ptr(), 1, B, H, T, D,
+                                                    s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), s["ws"], ws_bytes,
+                                                    st.data_ptr(), 0, sp)
             return lib.mca_sdpa_backward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), s["dy"].data_ptr(), s["yc"].data_ptr(),
                                              None, 3, None, s["a"].data_ptr(), s["b"].data_ptr(), s["delta"].data_ptr(), B, H, T, D,
                                              s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), sp)
@@ -747,10 +752,13 @@ def run_train(cx, steps=4):
         if bf:
             entry["roofline"] = tensor_roofline(cx, tot, "sdpa_fwd_tc_kernel<64> + backward kernels<64>", (fms + bms) / L,
                                                 "useful FLOPs of forward + backward over their summed time, per layer")
+        elif split_fwd:
+            entry["roofline"] = tensor_roofline(cx, tot, "sdpa_fwd_tc_kernel<64,split> + sdpa_bwd_dkdv/dq_tc_kernel<64,split> (+ pre-passes)",
+                                                (fms + bms) / L, "useful FLOPs over the summed time, per layer; every contraction is three "
+                                                "fp16 products, so a third of the bf16 peak is this path's ceiling")
         else:
             peak = 148 * 128 * 2 * 1.965e9 / 1e12    # fp32 FMA lanes x 2 flop x max SM clock: no measured figure exists for this pipe
-            entry["roofline"] = {"bound": "fp32 FMA issue (CUDA cores)" + (" for the backward; the forward is three fp16 tensor-core products per contraction" if split_fwd else ""),
-                                 "kernel": ("sdpa_fwd_tc_kernel<64,split> (+ pre-pass)" if split_fwd else "sdpa_fwd_f32_kernel<64>") + " + sdpa_bwd_*_f32_kernel<64>",
+            entry["roofline"] = {"bound": "fp32 FMA issue (CUDA cores)", "kernel": "sdpa_fwd_f32_kernel<64> + sdpa_bwd_*_f32_kernel<64>",
                                  "achieved": round(tot, 2), "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(tot / peak, 4),
                                  "peak_source": "nominal (148 SMs x 128 lanes x 2 x 1965 MHz)", "kernel_ms": round((fms + bms) / L, 4),
                                  "traffic": None}

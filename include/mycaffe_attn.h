@@ -255,15 +255,23 @@ MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int
 /* fp32 SDPA forward at fp32 accuracy on the tensor cores.  Same math as attn.cu:518-602 with a causal or absent mask.
  * q, k, v, y: fp32, (B,H,T,D) or the packed layout; D in {16, 32, 64}.  A pre-pass scales each tensor by a power of two
  * and writes every element as two fp16 halves hi = fp16(x), lo = fp16(x - hi) into `workspace`
- * (mca_sdpa_forward_f32_tc_workspace_bytes(B,H,T) bytes, 1024-byte aligned); every contraction is then three
- * tcgen05 kind::f16 products hi.hi + hi.lo + lo.hi accumulated in fp32, P split the same way.  Within 1e-6 of the output
- * scale of the fp64 result.  row_max, row_sum (optional, (B,H,T)) and y_copy (optional, (B,H,T,D) contiguous) are what
- * mca_sdpa_backward_f32 needs.  status as mca_sdpa_forward_tc. */
+ * (mca_sdpa_forward_f32_tc_workspace_bytes(B,H,T) bytes, 16-byte aligned); every contraction is then three
+ * tcgen05 kind::f16 products hi.hi + hi.lo + lo.hi accumulated in fp32, P split the same way.  Within 1e-5 of the output
+ * scale of the fp64 result (measured 1e-7 .. 7e-6).  row_max, row_sum (optional, (B,H,T)) and y_copy (optional, (B,H,T,D) contiguous) are what
+ * mca_sdpa_backward_f32 needs; lse (optional, (B,H,T), log2 domain) and y_copy are what mca_sdpa_backward_f32_tc needs.
+ * status as mca_sdpa_forward_tc. */
 MCA_API int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T);
 MCA_API int mca_sdpa_forward_f32_tc_supported(int D);
 MCA_API int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D,
-                                    float* y, float* row_max, float* row_sum, float* y_copy, void* workspace,
+                                    float* y, float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
                                     int64_t workspace_bytes, int* status, int layout, void* stream);
+/* Its backward (attnHandle<T>::Backward, attn.cu:608-661) on the tensor cores with the same split operands: `workspace`
+ * must still hold what mca_sdpa_forward_f32_tc left in it for the same q, k, v (their fp16 halves and scales); dY is split
+ * here.  dy in the output layout, y_copy and lse from the forward; dq, dk, dv fp32 in the input layout;
+ * delta_scratch: (B,H,T) floats.  Deterministic (no atomics). */
+MCA_API int mca_sdpa_backward_f32_tc(const float* dy, const float* y_copy, const float* lse, float* delta_scratch, int causal,
+                                     int B, int H, int T, int D, float* dq, float* dk, float* dv, void* workspace,
+                                     int64_t workspace_bytes, int* status, int layout, void* stream);
 
 /* Self-check of the bounded waits inside the tensor-core kernels: launches one small kernel whose only thread waits
  * on a barrier nothing arrives on, for at most limit_us microseconds (<= 100000), then gives up the way a stalled

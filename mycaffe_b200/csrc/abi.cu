@@ -44,6 +44,7 @@ struct AttnHandle {
   int fwd_T = 0, fwd_mask_mode = 0, fwd_layout = 0;
   long fwd_mask_handle = 0;   // memory handle of the forward's mask (0: none); resolved again by Backward
   bool fwd_batch_mask = false;
+  bool fwd_split = false;       // the forward was the split-operand tensor-core kernel: its workspace holds q, k, v halves
   bool status_pending = false;  // a tensor-core launch was made in asynchronous mode and its status words are unread
   void release() {
     cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
@@ -443,6 +444,7 @@ long sync_and_collect_status(Kernel* k) {
 
 void remember_forward(AttnHandle& a, int T, int mode, int layout, long hMask, bool batch_mask) {
   a.have_fwd = true; a.fwd_T = T; a.fwd_mask_mode = mode; a.fwd_layout = layout;
+  a.fwd_split = false;
   const bool reads_mask = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;
   a.fwd_mask_handle = reads_mask ? hMask : 0;
   a.fwd_batch_mask = batch_mask;
@@ -476,11 +478,10 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr))) return e;
     const bool save = a.training && T == a.block;
     if (a.split_ws != nullptr && (mode == MCA_MASK_CAUSAL || mode == MCA_MASK_NONE)) {
-      e = mca_sdpa_forward_f32_tc(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
-                                  save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, a.split_ws, a.split_ws_bytes,
-                                  a.causal_flag + 1, layout, 0);
+      e = mca_sdpa_forward_f32_tc(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, nullptr, nullptr, save ? a.y_copy : nullptr,
+                                  save ? a.lse : nullptr, a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, 0);
       if (e) return e;
-      if (save) remember_forward(a, T, mode, layout, 0, false);
+      if (save) { remember_forward(a, T, mode, layout, 0, false); a.fwd_split = true; }
       return tc_status(k, a);
     }
     e = mca_sdpa_forward_f32_layout(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,
@@ -565,6 +566,14 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
       (e = check_f32(k, (long)pl[10], n, &dy)))
     return e;
   if (packed) { kk += C; dk += C; v += 2 * C; dv += 2 * C; }
+  if (a.fwd_split) {
+    // the forward ran on the tensor cores with split operands; so does the backward, from the halves of q, k, v that
+    // forward left in the handle's workspace (the reference's Backward likewise works on what its Forward saved)
+    e = mca_sdpa_backward_f32_tc(dy, a.y_copy, a.lse, a.delta, a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, dq, dk, dv,
+                                 a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, 0);
+    if (e) return e;
+    return tc_status(k, a);
+  }
   // The probabilities are recomputed, so the forward's mask is applied again: it is looked up by the handle
   // the forward was given (a freed handle is an error, not a dangling pointer) and classified afresh.
   const float* mask = nullptr;

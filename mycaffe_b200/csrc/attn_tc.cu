@@ -36,8 +36,9 @@
 //               lo = fp16(x - hi) (22 mantissa bits together; a pre-pass writes rows [hi | lo] after scaling each
 //               tensor by a power of two so that neither half leaves the fp16 range), and every contraction is three
 //               kind::f16 products hi.hi + hi.lo + lo.hi accumulated in the same fp32 TMEM tile.  P is split the
-//               same way by the softmax warps.  Measured against the fp64 oracle this is within 1e-6 of the output
-//               scale, i.e. what the exact fp32 CUDA-core kernel gives, at a third of the bf16 tensor rate.
+//               same way by the softmax warps.  Measured against the fp64 oracle this is within 1e-5 of the output
+//               scale (what limits it is the fp32 accumulation inside the tensor core, not the operands), at a third of
+//               the bf16 tensor rate.
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -47,6 +48,7 @@
 #include "kernels.h"
 
 #include "tc_common.cuh"
+#include "split_prepass.cuh"
 
 namespace {
 
@@ -118,7 +120,7 @@ struct TcParams {
   McaStrides ys;     // element strides of the output view
   void* y_more[7];   // further destinations of the same bf16 output tile (peer GPUs' buffers), same strides
   int n_more;
-  // MODE_SPLIT: {1 / (scale_q * scale_k), 1 / scale_v} of the pre-pass (device memory); exact softmax statistics for
+  // MODE_SPLIT: the pre-pass's scale factors (split::SplitFac, device memory); exact softmax statistics for
   // the fp32 backward: row_max in natural-log units of the scaled logits and the matching row sum, (B*H, T) each
   const float* split_fac;
   float* row_max;
@@ -389,7 +391,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float m_used[2] = {-INFINITY, -INFINITY};
     float l[2] = {0.f, 0.f};                            // this thread's part of the row sums
     // split mode: the pre-pass scaled q and k by powers of two; dividing them out of the logit scale is exact
-    const float scale_log2 = SPLIT ? p.scale_log2 * __ldg(p.split_fac) : p.scale_log2;
+    const float scale_log2 = SPLIT ? p.scale_log2 * __ldg(p.split_fac + split::FAC_INV_QK) : p.scale_log2;
     for (int j = 0; j < n && ok; ++j) {
       TC_TRACE(x, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
@@ -468,7 +470,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       TC_TRACE_W(j, 2);
       // p = 2^(s * scale_log2 - m): one FFMA and one exponential per element, packed to bf16;
       // the row sum is taken in fp32.  The first 64 keys are handed to the MMA warp before the rest.
-      const float2 nm2[2] = {make_float2(-m_new[0], -m_new[0]), make_float2(-m_new[1], -m_new[1])};
+      // split mode: the probabilities are kept 2^6 larger (they stay below 2^14), so that their fp16 halves leave the
+      // normal range only below 2^-20 of the row's largest; the row sum carries the same factor and it cancels
+      constexpr float P_BIAS = SPLIT ? 6.0f : 0.0f;
+      const float2 nm2[2] = {make_float2(P_BIAS - m_new[0], P_BIAS - m_new[0]), make_float2(P_BIAS - m_new[1], P_BIAS - m_new[1])};
       const float2 scale2 = make_float2(scale_log2, scale_log2);
       float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[16];
@@ -555,7 +560,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int qi = qrow0 + row;
         const float lsum = red_l[row];
         // split mode: the pre-pass scaled v by a power of two; dividing it out here is exact
-        const float inv = SPLIT ? __ldg(p.split_fac + 1) / lsum : 1.0f / lsum;
+        const float inv = SPLIT ? __ldg(p.split_fac + split::FAC_INV_V) / lsum : 1.0f / lsum;
         const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BLK + x * BLK + half * OC);
         const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
@@ -648,12 +653,12 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
         }
-        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum);
+        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum) - (SPLIT ? 6.0f : 0.0f);
         if constexpr (SPLIT) {
           // what the exact fp32 backward needs to recompute P = exp(s - row_max) / row_sum: the exponent's reference
           // point in natural-log units (it need not be the true maximum) and the sum taken against it
           if (half == 0 && p.row_max != nullptr && qi < T) {
-            p.row_max[(int64_t)bh * T + qi] = red_m[row] * 0.6931471805599453f;
+            p.row_max[(int64_t)bh * T + qi] = (red_m[row] - 6.0f) * 0.6931471805599453f;   // the 2^6 kept in the probabilities
             p.row_sum[(int64_t)bh * T + qi] = lsum;
           }
         }
@@ -671,7 +676,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 
 struct SplitExtras {
-  const float* fac = nullptr;   // {1 / (scale_q * scale_k), 1 / scale_v}
+  const float* fac = nullptr;   // split::SplitFac
   float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr;
 };
 
@@ -723,97 +728,19 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   return mca_launch_status();
 }
 
-// ---------------------------------------------------------------------------------------------
-// Pre-pass of the split mode: per-tensor maximum, then rows [hi | lo] in fp16.
-// ---------------------------------------------------------------------------------------------
-struct SplitSrc {
-  const float* ptr[3];   // q, k, v (fp32), element strides `st`
-  __half* dst[3];        // (B, H, T, 128) fp16
-};
-
-// amax[i] = max |x| of tensor i (as the bit pattern of a non-negative float: integer order = float order)
-template <int HD>
-__global__ void __launch_bounds__(256) split_amax_kernel(const SplitSrc src, McaStrides st, int H, int T, int64_t rows,
-                                                         unsigned int* __restrict__ amax) {
-  const float* x = src.ptr[blockIdx.y];
-  constexpr int V4 = HD / 4;
-  float m = 0.f;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / V4;
-    const int c = (int)(i - row * V4);
-    const int64_t bh = row / T, t = row - bh * T;
-    const int64_t b = bh / H, h = bh - b * H;
-    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
-    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax + blockIdx.y, __float_as_uint(m));
-}
-
-// The power of two that brings max |x| to about 2^13: both halves of every element that matters then lie in the
-// normal range of fp16 (largest 65504; the low half of x is about 2^-11 |x|).
-__device__ __forceinline__ float split_scale(unsigned int amax_bits) {
-  const float a = __uint_as_float(amax_bits);
-  if (!(a > 0.f) || !(a < 3.0e38f)) return 1.0f;
-  int e;
-  frexpf(a, &e);                    // a = f * 2^e, f in [0.5, 1)
-  return ldexpf(1.0f, 13 - e);      // a * scale in [2^12, 2^13)
-}
-
-template <int HD>
-__global__ void __launch_bounds__(256) split_rows_kernel(const SplitSrc src, McaStrides st, int H, int T, int64_t rows,
-                                                         const unsigned int* __restrict__ amax, float* __restrict__ fac) {
-  const int which = blockIdx.y;
-  const float* x = src.ptr[which];
-  __half* dst = src.dst[which];
-  const float sc = split_scale(amax[which]);
-  if (which == 0 && blockIdx.x == 0 && threadIdx.x == 0) {
-    fac[0] = 1.0f / (split_scale(amax[0]) * split_scale(amax[1]));   // powers of two: exact
-    fac[1] = 1.0f / split_scale(amax[2]);
-  }
-  constexpr int V4 = HD / 4;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / V4;
-    const int c = (int)(i - row * V4);
-    const int64_t bh = row / T, t = row - bh * T;
-    const int64_t b = bh / H, h = bh - b * H;
-    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
-    const float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-    __half hi[4], lo[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      hi[j] = __float2half_rn(e[j]);
-      lo[j] = __float2half_rn(e[j] - __half2float(hi[j]));
-    }
-    __half* o = dst + row * 128 + c * 4;
-    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(hi);
-    *reinterpret_cast<uint2*>(o + 64) = *reinterpret_cast<const uint2*>(lo);
-  }
-}
-
 template <int HD>
 int launch_split(const float* q, const float* k, const float* v, int causal, int B, int H, int T, float* y, float* row_max,
-                 float* row_sum, float* y_copy, void* workspace, int* status, int layout, cudaStream_t st) {
+                 float* row_sum, float* y_copy, float* lse, void* workspace, int* status, int layout, cudaStream_t st) {
   const int64_t rows = (int64_t)B * H * T;
-  // workspace: amax[4] (uint) | fac[4] (float) | 3 x rows x 128 fp16, the tensors 1024-byte aligned
-  unsigned int* amax = static_cast<unsigned int*>(workspace);
-  float* fac = reinterpret_cast<float*>(amax + 4);
-  __half* base = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 1024);
-  SplitSrc src;
-  src.ptr[0] = q; src.ptr[1] = k; src.ptr[2] = v;
-  for (int i = 0; i < 3; ++i) src.dst[i] = base + (size_t)i * rows * 128;
-  const McaStrides sin = mca_in_strides(layout, H, T, HD);
-  MCA_CUDA_TRY(cudaMemsetAsync(amax, 0, 4 * sizeof(unsigned int), st));
-  const int blocks = (int)std::min<int64_t>(148 * 8, (rows * (HD / 4) + 255) / 256);
-  split_amax_kernel<HD><<<dim3(blocks, 3), 256, 0, st>>>(src, sin, H, T, rows, amax);
-  int e = mca_launch_status();
+  const split::Workspace w = split::carve(workspace, rows);
+  split::Job job;
+  job.src[0] = q; job.src[1] = k; job.src[2] = v;
+  for (int i = 0; i < 3; ++i) { job.dst[i] = w.tensor[i]; job.slot[i] = i; }
+  int e = split::run<HD>(job, 3, mca_in_strides(layout, H, T, HD), H, T, rows, w, false, st);
   if (e) return e;
-  split_rows_kernel<HD><<<dim3(blocks, 3), 256, 0, st>>>(src, sin, H, T, rows, amax, fac);
-  if ((e = mca_launch_status())) return e;
   SplitExtras ex;
-  ex.fac = fac; ex.row_max = row_max; ex.row_sum = row_sum; ex.y_copy = y_copy;
-  return launch_tc<HD, MODE_SPLIT>(src.dst[0], src.dst[1], src.dst[2], causal, B, H, T, y, nullptr, status, layout, st, nullptr, 0,
+  ex.fac = w.fac; ex.row_max = row_max; ex.row_sum = row_sum; ex.y_copy = y_copy;
+  return launch_tc<HD, MODE_SPLIT>(w.tensor[0], w.tensor[1], w.tensor[2], causal, B, H, T, y, lse, status, layout, st, nullptr, 0,
                                    nullptr, &ex);
 }
 
@@ -877,14 +804,14 @@ int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int 
 
 int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T) {
   if (B <= 0 || H <= 0 || T <= 0) return -1;
-  return 1024 + (int64_t)3 * B * H * T * 128 * 2;
+  return split::workspace_bytes((int64_t)B * H * T);
 }
 
 int mca_sdpa_forward_f32_tc_supported(int D) { return D == 16 || D == 32 || D == 64; }
 
 int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D, float* y,
-                            float* row_max, float* row_sum, float* y_copy, void* workspace, int64_t workspace_bytes,
-                            int* status, int layout, void* stream) {
+                            float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
+                            int64_t workspace_bytes, int* status, int layout, void* stream) {
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !status || !workspace) return ERROR_PARAM_NULL;
   if ((row_max == nullptr) != (row_sum == nullptr)) return ERROR_PARAM_NULL;
@@ -894,12 +821,12 @@ int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int 
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(y_copy)) & 15)
     return ERROR_PARAM_OUT_OF_RANGE;
-  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return ERROR_PARAM_OUT_OF_RANGE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) return ERROR_PARAM_OUT_OF_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   switch (D) {
-    case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
-    case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
-    case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, workspace, status, layout, st);
+    case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
+    case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
+    case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

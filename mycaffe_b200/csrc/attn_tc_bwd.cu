@@ -18,8 +18,14 @@
 //     A operand of dV += P^T dY and dK += dS^T Q needs.
 // Q/K/V/dY tiles arrive by TMA (no multicast) through two-stage rings; every mbarrier wait is
 // bounded as in the forward kernel.
+//
+// SPLIT = true is the variant for fp32 callers: every operand is carried as two fp16 halves (rows [hi | lo] written by
+// the pre-pass in split_prepass.cuh, each tensor scaled by a power of two), every product is the three kind::f16
+// products hi.hi + hi.lo + lo.hi into one fp32 TMEM tile, P^T / dS / dS^T are split the same way by the element-wise
+// warps, and the gradients are written in fp32.  Head sizes up to 64: a split tile is as large as a 128-wide bf16 one.
 #include "kernels.h"
 #include "tc_common.cuh"
+#include "split_prepass.cuh"
 
 namespace {
 
@@ -57,7 +63,19 @@ template <int HD> struct BwdPlan {
   static constexpr uint32_t BYTES_KV = (NEED_KV + 1024 <= 227u * 1024u) ? NEED_KV + 1024 : 227u * 1024u;
 };
 
+// fp16 halves of a value the tensor core must see at fp32 accuracy: hi = v with the mantissa cut to fp16 width (the
+// conversion is then exact for normal numbers), lo = v - hi.
+__device__ __forceinline__ void split_pack(float v0, float v1, uint32_t& hi, uint32_t& lo) {
+  const float h0 = __uint_as_float(__float_as_uint(v0) & 0xffffe000u), h1 = __uint_as_float(__float_as_uint(v1) & 0xffffe000u);
+  hi = pack_f16(h0, h1);
+  lo = pack_f16(v0 - h0, v1 - h1);
+}
+// Split mode keeps dS 2^-19 smaller than dP' = dY' V'^T (both operands scaled to below 2^13, so |dP'| < 2^32 at 64-wide
+// heads) and P^T 2^10 larger than P <= 1: both then sit in the middle of the fp16 range.
+constexpr float DS_SHIFT = 1.0f / 524288.0f, DS_UNSHIFT = 524288.0f, PT_SHIFT = 1024.0f, PT_UNSHIFT = 1.0f / 1024.0f;
+
 struct BwdParams {
+  const float* fac;    // split mode: the pre-pass's scale factors (split::SplitFac), device memory
   const float* lse;    // (BH, T) log2-domain log-sum-exp of the scaled logits, from the forward kernel
   const float* delta;  // (BH, T) rowsum(dY o Y)
   void* out0;          // dq kernel: dQ;  dkdv kernel: dK
@@ -83,7 +101,8 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_
 }
 
 // ---------------------------------------------------------------------------------------------
-// dQ kernel.  TMEM columns: S [0,128)  dP [128,256)  dS (bf16, packed) [256,320)  dQ [320,320+HD)
+// dQ kernel.  TMEM columns: S [0,128)  dP [128,256)  dS (bf16, packed) [256,320)  dQ [320,320+HD);
+// split mode: dS hi [256,320), dS lo [320,384), dQ [384,384+HD)
 // ---------------------------------------------------------------------------------------------
 enum DqBar : int {
   DQ_QDO_FULL = 0,
@@ -99,12 +118,13 @@ enum DqBar : int {
   DQ_BAR_COUNT = 16
 };
 
-template <int HD>
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const BwdParams p) {
-  using PL = BwdPlan<HD>;
+  using PL = BwdPlan<SPLIT ? 128 : HD>;   // a split row is two 128-byte sub-tiles [hi | lo]
+  constexpr int FMT = SPLIT ? 0 : 1;       // operand format of the instruction descriptor: fp16 or bf16
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -139,7 +159,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t C_S = 0, C_DP = 128, C_DS = 256, C_DQ = 320;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DS = 256, C_DQ = SPLIT ? 384 : 320;
   bool ok = true;
 
   if (warp == WARP_TMA) {
@@ -182,22 +202,33 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     {
       const uint32_t leader = elect_one() ? 1u : 0u;
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);  // both operands K-major
-      constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 0, 1);   // A from TMEM, B = K tile MN-major
+      constexpr uint32_t IDESC_NT = make_idesc_fmt(BLK, BLK, 0, 0, FMT);  // both operands K-major
+      constexpr uint32_t IDESC_DQ = make_idesc_fmt(BLK, HD, 0, 1, FMT);   // A from TMEM, B = K tile MN-major
       const uint32_t q_addr = smem_base + PL::OFF_RES0, do_addr = smem_base + PL::OFF_RES1;
+      // D = A B^T over the head dimension, both operands K-major in shared memory; split mode: hi.hi + hi.lo + lo.hi
+      auto issue_nt = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
+        if constexpr (SPLIT) {
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            const uint32_t oa = term == 2 ? PL::SUB_BYTES : 0u, ob = term == 1 ? PL::SUB_BYTES : 0u;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+              umma_ss_if<false>(leader, tmem_u + d_col, make_desc(a_addr + oa + kk * 32, 16, 1024), make_desc(b_addr + ob + kk * 32, 16, 1024),
+                                IDESC_NT, (term > 0 || kk > 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+            umma_ss_if<false>(leader, tmem_u + d_col, make_desc(a_addr + off, 16, 1024), make_desc(b_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          }
+        }
+      };
       auto issue_sdp = [&](int j) {
         const uint32_t k_addr = smem_base + PL::OFF_KRING + (j % PL::K_STAGES) * PL::TILE_BYTES;
         const uint32_t v_addr = smem_base + PL::OFF_VRING + (j % PL::V_STAGES) * PL::TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss_if<false>(leader, tmem_u + C_S, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), IDESC_NT, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss_if<false>(leader, tmem_u + C_DP, make_desc(do_addr + off, 16, 1024), make_desc(v_addr + off, 16, 1024), IDESC_NT, kk > 0);
-        }
+        issue_nt(C_S, q_addr, k_addr);
+        issue_nt(C_DP, do_addr, v_addr);
       };
       ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_QDO_FULL), 0, p.status, 120, 0));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_K_FULL + 0), 0, p.status, 121, 0));
@@ -226,9 +257,15 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tc_fence_after();
         const uint32_t k_addr = smem_base + PL::OFF_KRING + (j % PL::K_STAGES) * PL::TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)
+        for (int kk = 0; kk < BLK / 16; ++kk) {
           umma_ts_if<false>(leader, tmem_u + C_DQ, tmem_u + C_DS + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ,
                   (j > 0 || kk > 0) ? 1u : 0u);
+          if constexpr (SPLIT) {   // + dS_hi K_lo + dS_lo K_hi
+            umma_ts_if<false>(leader, tmem_u + C_DQ, tmem_u + C_DS + kk * 8, make_desc(k_addr + PL::SUB_BYTES + kk * 2048, PL::SUB_BYTES, 1024),
+                              IDESC_DQ, 1u);
+            umma_ts_if<false>(leader, tmem_u + C_DQ, tmem_u + C_DS + 64 + kk * 8, make_desc(k_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_DQ, 1u);
+          }
+        }
         umma_commit_if(leader, bar(DQ_DQ_DONE));
         umma_commit_if(leader, bar(DQ_K_EMPTY + j % PL::K_STAGES));
       }
@@ -257,11 +294,17 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (lane == 0) mbar_arrive(bar(DQ_SDP_FREE));
       const int k0 = j * BLK + qtr * 32;
       const bool edge = (p.causal && j * BLK + BLK - 1 > q0) || (j * BLK + BLK > T);
-      // dS = P o (dP - delta) scale with P = 2^(S scale_log2 - lse); adjacent keys go through as fp32 pairs
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse, -lse);
-      const float2 ps2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
+      // dS = P o (dP - delta) scale with P = 2^(S scale_log2 - lse); adjacent keys go through as fp32 pairs.
+      // Split mode: S and dP carry the pre-pass's scales; dS is kept in the units of dP' x 2^-19 and the factor
+      // scale x 2^19 / (s_dy s_v s_k) is applied once to dQ.
+      const float sl2 = SPLIT ? p.scale_log2 * __ldg(p.fac + split::FAC_INV_QK) : p.scale_log2;
+      const float dmul = SPLIT ? DS_SHIFT : p.scale;
+      const float dsub = SPLIT ? delta * __ldg(p.fac + split::FAC_DYV) * DS_SHIFT : delta * p.scale;
+      const float2 sc2 = make_float2(sl2, sl2), nl2 = make_float2(-lse, -lse);
+      const float2 ps2 = make_float2(dmul, dmul), nd2 = make_float2(-dsub, -dsub);
       const float2 zero2 = make_float2(0.f, 0.f);
       uint32_t pk[16];
+      uint32_t pk_lo[SPLIT ? 16 : 1];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
@@ -273,7 +316,8 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (!row_ok || kj >= T || (p.causal && kj > qi)) d0 = 0.f;
           if (!row_ok || kj + 1 >= T || (p.causal && kj + 1 > qi)) d1 = 0.f;
         } else if (!row_ok) { d0 = 0.f; d1 = 0.f; }
-        pk[i / 2] = pack_bf16(d0, d1);
+        if constexpr (SPLIT) split_pack(d0, d1, pk[i / 2], pk_lo[i / 2]);
+        else pk[i / 2] = pack_bf16(d0, d1);
       }
       if (j > 0) {  // the previous dQ product must have consumed the previous dS
         ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((j - 1) & 1), p.status, 131, j));
@@ -281,6 +325,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tc_fence_after();
       }
       tmem_st16(t_row + C_DS + qtr * 16, pk);
+      if constexpr (SPLIT) tmem_st16(t_row + C_DS + 64 + qtr * 16, pk_lo);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -290,13 +335,31 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((n - 1) & 1), p.status, 132, n));
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)qi * p.os.t + qtr * OC;
-#pragma unroll
-        for (int c = 0; c < OC / 16; ++c) {
+        const int64_t d_off = (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)qi * p.os.t + qtr * OC;
+        if constexpr (SPLIT) {
+          // fp32 result; a quarter of the warps covers OC = HD / 4 columns of a row (4, 8 or 16)
+          const float mul = p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVK);
+          float* dst = reinterpret_cast<float*>(p.out0) + d_off;
           uint32_t o[16];
-          tmem_ld16(t_row + C_DQ + qtr * OC + c * 16, o);
+          if constexpr (OC == 16) tmem_ld16(t_row + C_DQ + qtr * OC, o);
+          else if constexpr (OC == 8) tmem_ld8(t_row + C_DQ + qtr * OC, o);
+          else tmem_ld4(t_row + C_DQ + qtr * OC, o);
           tmem_wait_ld();
-          if (row_ok) store_row_bf16(dst + c * 16, o, 1.0f);
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < OC; i += 4)
+              *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(o[i]) * mul, __uint_as_float(o[i + 1]) * mul,
+                                                                __uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + d_off;
+#pragma unroll
+          for (int c = 0; c < OC / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(t_row + C_DQ + qtr * OC + c * 16, o);
+            tmem_wait_ld();
+            if (row_ok) store_row_bf16(dst + c * 16, o, 1.0f);
+          }
         }
       }
     }
@@ -308,7 +371,8 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
 // ---------------------------------------------------------------------------------------------
 // dK/dV kernel.  TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+HD)  dK [384,384+HD);
-// P^T and dS^T (bf16, packed) overwrite the first 16 columns of each 32-column quarter of S^T / dP^T.
+// P^T and dS^T (bf16, packed) overwrite the first 16 columns of each 32-column quarter of S^T / dP^T; in split
+// mode their fp16 hi halves do, and the lo halves take the other 16 columns of the quarter.
 // ---------------------------------------------------------------------------------------------
 enum KvBar : int {
   KV_KV_FULL = 0,
@@ -326,12 +390,13 @@ enum KvBar : int {
   KV_BAR_COUNT = 18
 };
 
-template <int HD>
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                         const BwdParams p) {
-  using PL = BwdPlan<HD>;
+  using PL = BwdPlan<SPLIT ? 128 : HD>;
+  constexpr int FMT = SPLIT ? 0 : 1;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -419,9 +484,40 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     {
       const uint32_t leader = elect_one() ? 1u : 0u;
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      constexpr uint32_t IDESC_NT = make_idesc_bf16(BLK, BLK, 0, 0);
-      constexpr uint32_t IDESC_ACC = make_idesc_bf16(BLK, HD, 0, 1);
+      constexpr uint32_t IDESC_NT = make_idesc_fmt(BLK, BLK, 0, 0, FMT);
+      constexpr uint32_t IDESC_ACC = make_idesc_fmt(BLK, HD, 0, 1, FMT);
       const uint32_t k_addr = smem_base + PL::OFF_RES0, v_addr = smem_base + PL::OFF_RES1;
+      auto issue_nt = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
+        if constexpr (SPLIT) {
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            const uint32_t oa = term == 2 ? PL::SUB_BYTES : 0u, ob = term == 1 ? PL::SUB_BYTES : 0u;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+              umma_ss_if<false>(leader, tmem_u + d_col, make_desc(a_addr + oa + kk * 32, 16, 1024), make_desc(b_addr + ob + kk * 32, 16, 1024),
+                                IDESC_NT, (term > 0 || kk > 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
+            umma_ss_if<false>(leader, tmem_u + d_col, make_desc(a_addr + off, 16, 1024), make_desc(b_addr + off, 16, 1024), IDESC_NT, kk > 0);
+          }
+        }
+      };
+      // acc += A^T-from-TMEM x B with B a 128 x HD tile read MN-major; split mode: hi.hi + hi.lo + lo.hi
+      auto issue_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_addr, bool first_step) {
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {
+          const uint32_t a_hi = tmem_u + a_col + (kk / 2) * 32 + (kk % 2) * 8;
+          umma_ts_if<false>(leader, tmem_u + d_col, a_hi, make_desc(b_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC,
+                            (!first_step || kk > 0) ? 1u : 0u);
+          if constexpr (SPLIT) {
+            umma_ts_if<false>(leader, tmem_u + d_col, a_hi, make_desc(b_addr + PL::SUB_BYTES + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, 1u);
+            umma_ts_if<false>(leader, tmem_u + d_col, a_hi + 16, make_desc(b_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, 1u);
+          }
+        }
+      };
       // S^T = K Q^T and dP^T = V dY^T (rows = keys, columns = queries); P^T overwrites S^T and dS^T overwrites
       // dP^T.  The two halves of a step are interleaved with the next step's first products,
       //   dV(it), S^T(it+1), dK(it), dP^T(it+1),
@@ -436,21 +532,11 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         return __all_sync(0xffffffffu, mbar_wait(bar(KV_DO_FULL + it % PL::V_STAGES), (uint32_t)((it / PL::V_STAGES) & 1), p.status, 224, it));
       };
       auto issue_st = [&](int it) {
-        const uint32_t q_addr = q_stage(it);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss_if<false>(leader, tmem_u + C_ST, make_desc(k_addr + off, 16, 1024), make_desc(q_addr + off, 16, 1024), IDESC_NT, kk > 0);
-        }
+        issue_nt(C_ST, k_addr, q_stage(it));
         umma_commit_if(leader, bar(KV_ST_FULL));
       };
       auto issue_dpt = [&](int it) {
-        const uint32_t do_addr = do_stage(it);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * PL::SUB_BYTES + (kk % 4) * 32;
-          umma_ss_if<false>(leader, tmem_u + C_DPT, make_desc(v_addr + off, 16, 1024), make_desc(do_addr + off, 16, 1024), IDESC_NT, kk > 0);
-        }
+        issue_nt(C_DPT, v_addr, do_stage(it));
         umma_commit_if(leader, bar(KV_DPT_FULL));
       };
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_KV_FULL), 0, p.status, 220, 0));
@@ -469,10 +555,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_PT_READY), (uint32_t)(it & 1), p.status, 222, it));
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_if<false>(leader, tmem_u + C_DV, tmem_u + C_ST + (kk / 2) * 32 + (kk % 2) * 8,
-                  make_desc(do_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+        issue_acc(C_DV, C_ST, do_addr, it == 0);
         umma_commit_if(leader, bar(KV_DO_EMPTY + it % PL::V_STAGES));   // dY(it) was last read by this product
         if (it + 1 < n) {
           ok = wait_q(it + 1);
@@ -484,10 +567,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_DST_READY), (uint32_t)(it & 1), p.status, 223, it));
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_if<false>(leader, tmem_u + C_DK, tmem_u + C_DPT + (kk / 2) * 32 + (kk % 2) * 8,
-                  make_desc(q_addr + kk * 2048, PL::SUB_BYTES, 1024), IDESC_ACC, (it > 0 || kk > 0) ? 1u : 0u);
+        issue_acc(C_DK, C_DPT, q_addr, it == 0);
         umma_commit_if(leader, bar(KV_Q_EMPTY + it % PL::K_STAGES));
         umma_commit_if(leader, bar(KV_ACC_DONE));
         if (it + 1 < n) {
@@ -513,10 +593,14 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // lse = +inf, which makes their probabilities exactly zero.
     float (*s_nlse)[BLK] = reinterpret_cast<float (*)[BLK]>(smem_gen + PL::OFF_STAGE_KV);
     float (*s_del)[BLK] = s_nlse + 2;
+    // split mode: S^T and dP^T carry the pre-pass's scales; dS^T is kept in the units of dP' x 2^-19 and P^T 2^10 larger
+    const float sl2 = SPLIT ? p.scale_log2 * __ldg(p.fac + split::FAC_INV_QK) : p.scale_log2;
+    const float dmul = SPLIT ? DS_SHIFT : p.scale;
+    const float del_mul = SPLIT ? __ldg(p.fac + split::FAC_DYV) * DS_SHIFT : p.scale;
     auto fetch = [&](int it) -> float {
       const int qi = (i_begin + it) * BLK + (tid & (BLK - 1));
       if (tid >= 2 * BLK || it >= n || qi >= T) return tid < BLK ? -INFINITY : 0.f;
-      return tid < BLK ? -__ldg(p.lse + (int64_t)bh * T + qi) : -__ldg(p.delta + (int64_t)bh * T + qi) * p.scale;
+      return tid < BLK ? -__ldg(p.lse + (int64_t)bh * T + qi) : -__ldg(p.delta + (int64_t)bh * T + qi) * del_mul;
     };
     auto stage = [&](int it, float v) {
       if (tid < BLK) s_nlse[it & 1][tid] = v;
@@ -538,9 +622,10 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const float* del_s = s_del[it & 1] + q_local;
       const bool diag = p.causal && (i_begin + it) * BLK < k0 + BLK;   // only the diagonal tile needs the causal test
       // pass 1: P^T = 2^(S^T scale - lse), kept in fp32 for pass 2, packed to bf16 over S^T (fp32 pairs)
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ps2 = make_float2(p.scale, p.scale);
+      const float2 sc2 = make_float2(sl2, sl2), ps2 = make_float2(dmul, dmul);
       const float2 zero2 = make_float2(0.f, 0.f);
       uint32_t s[32], pk[16];
+      uint32_t pk_lo[SPLIT ? 16 : 1];
       tmem_ld32(t_row + C_ST + qtr * 32, s);
       tmem_wait_ld();
 #pragma unroll
@@ -557,10 +642,16 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           s[i + e] = __float_as_uint(v0);
           s[i + e + 1] = __float_as_uint(v1);
         }
-        pk[i / 2] = pack_bf16(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-        pk[i / 2 + 1] = pack_bf16(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        if constexpr (SPLIT) {
+          split_pack(__uint_as_float(s[i]) * PT_SHIFT, __uint_as_float(s[i + 1]) * PT_SHIFT, pk[i / 2], pk_lo[i / 2]);
+          split_pack(__uint_as_float(s[i + 2]) * PT_SHIFT, __uint_as_float(s[i + 3]) * PT_SHIFT, pk[i / 2 + 1], pk_lo[i / 2 + 1]);
+        } else {
+          pk[i / 2] = pack_bf16(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+          pk[i / 2 + 1] = pack_bf16(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        }
       }
       tmem_st16(t_row + C_ST + qtr * 32, pk);
+      if constexpr (SPLIT) tmem_st16(t_row + C_ST + qtr * 32 + 16, pk_lo);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -582,11 +673,13 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           const float2 g = ffma2(make_float2(__uint_as_float(dp[i + e]), __uint_as_float(dp[i + e + 1])), ps2,
                                  make_float2(des[e], des[e + 1]));
           const float2 d = ffma2(make_float2(__uint_as_float(s[i + e]), __uint_as_float(s[i + e + 1])), g, zero2);
-          pk[(i + e) / 2] = pack_bf16(d.x, d.y);
+          if constexpr (SPLIT) split_pack(d.x, d.y, pk[(i + e) / 2], pk_lo[(i + e) / 2]);
+          else pk[(i + e) / 2] = pack_bf16(d.x, d.y);
         }
       }
       if (it + 1 < n) stage(it + 1, next);
       tmem_st16(t_row + C_DPT + qtr * 32, pk);
+      if constexpr (SPLIT) tmem_st16(t_row + C_DPT + qtr * 32 + 16, pk_lo);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -596,17 +689,40 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
       if (ok) {
         tc_fence_after();
-        __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
-        __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
+        const int64_t g_off = (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
+        if constexpr (SPLIT) {
+          const float mul_k = p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVQ);
+          const float mul_v = PT_UNSHIFT * __ldg(p.fac + split::FAC_INV_DY);
+          float* dsts[2] = {reinterpret_cast<float*>(p.out0) + g_off, reinterpret_cast<float*>(p.out1) + g_off};
+          const uint32_t cols[2] = {C_DK, C_DV};
+          const float muls[2] = {mul_k, mul_v};
 #pragma unroll
-        for (int c = 0; c < OC / 16; ++c) {
-          uint32_t o[16];
-          tmem_ld16(t_row + C_DK + qtr * OC + c * 16, o);
-          tmem_wait_ld();
-          if (key_ok) store_row_bf16(dk_dst + c * 16, o, 1.0f);
-          tmem_ld16(t_row + C_DV + qtr * OC + c * 16, o);
-          tmem_wait_ld();
-          if (key_ok) store_row_bf16(dv_dst + c * 16, o, 1.0f);
+          for (int w = 0; w < 2; ++w) {
+            uint32_t o[16];
+            if constexpr (OC == 16) tmem_ld16(t_row + cols[w] + qtr * OC, o);
+            else if constexpr (OC == 8) tmem_ld8(t_row + cols[w] + qtr * OC, o);
+            else tmem_ld4(t_row + cols[w] + qtr * OC, o);
+            tmem_wait_ld();
+            if (key_ok) {
+#pragma unroll
+              for (int i = 0; i < OC; i += 4)
+                *reinterpret_cast<float4*>(dsts[w] + i) = make_float4(__uint_as_float(o[i]) * muls[w], __uint_as_float(o[i + 1]) * muls[w],
+                                                                      __uint_as_float(o[i + 2]) * muls[w], __uint_as_float(o[i + 3]) * muls[w]);
+            }
+          }
+        } else {
+          __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + g_off;
+          __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + g_off;
+#pragma unroll
+          for (int c = 0; c < OC / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(t_row + C_DK + qtr * OC + c * 16, o);
+            tmem_wait_ld();
+            if (key_ok) store_row_bf16(dk_dst + c * 16, o, 1.0f);
+            tmem_ld16(t_row + C_DV + qtr * OC + c * 16, o);
+            tmem_wait_ld();
+            if (key_ok) store_row_bf16(dv_dst + c * 16, o, 1.0f);
+          }
         }
       }
     }
@@ -645,6 +761,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
       (e = make_map_bf16(&mv, v, B, H, T, HD, sin)) || (e = make_map_bf16(&mdo, dy, B, H, T, HD, sout)))
     return e;
   BwdParams p;
+  p.fac = nullptr;
   p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal; p.H = H;
   {
     // Q, K, V, dY of one (batch, head): keep a group's set under about 64 MB of the 126 MB L2
@@ -655,14 +772,73 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const size_t smem_kv = BwdPlan<HD>::BYTES_KV, smem_dq = BwdPlan<HD>::BYTES_DQ;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
   dim3 grid(mca_ceil_div(T, BLK), B * H);
   p.out0 = dk; p.out1 = dv;
-  sdpa_bwd_dkdv_tc_kernel<HD><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
+  sdpa_bwd_dkdv_tc_kernel<HD, false><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
   if ((e = mca_launch_status())) return e;
   p.out0 = dq; p.out1 = nullptr;
-  sdpa_bwd_dq_tc_kernel<HD><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
+  sdpa_bwd_dq_tc_kernel<HD, false><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
+  return mca_launch_status();
+}
+
+// delta[row] = sum_c dY[row][c] * Y[row][c] in fp32: dY in the output layout, Y the handle's contiguous copy.
+__global__ void bwd_delta_f32_kernel(const float* __restrict__ dy, const float* __restrict__ y, int64_t rows, int H, int T, int D,
+                                     const McaStrides ys, float* __restrict__ delta) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t bh = row / T, bi = bh / H;
+  const int64_t off = bi * ys.b + (bh - bi * H) * ys.h + (row - bh * T) * ys.t;
+  float acc = 0.f;
+  for (int c = lane; c < D; c += 32) acc = fmaf(dy[off + c], y[row * D + c], acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) delta[row] = acc;
+}
+
+// Split-operand backward for fp32 callers.  The workspace still holds the fp16 halves of q, k, v the forward's pre-pass
+// wrote; dY is split here.
+template <int HD>
+int launch_bwd_split(const float* dy, const float* y_copy, const float* lse, float* delta, int causal, int B, int H, int T,
+                     float* dq, float* dk, float* dv, void* workspace, int* status, int layout, cudaStream_t st) {
+  const int64_t rows = (int64_t)B * H * T;
+  const split::Workspace w = split::carve(workspace, rows);
+  const McaStrides sin = mca_in_strides(layout, H, T, HD), sout = mca_out_strides(layout, H, T, HD);
+  split::Job job;
+  job.src[0] = dy; job.dst[0] = w.tensor[split::TENSOR_DY]; job.slot[0] = split::TENSOR_DY;
+  job.src[1] = job.src[2] = nullptr; job.dst[1] = job.dst[2] = nullptr; job.slot[1] = job.slot[2] = 0;
+  int e = split::run<HD>(job, 1, sout, H, T, rows, w, true, st);
+  if (e) return e;
+  bwd_delta_f32_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dy, y_copy, rows, H, T, HD, sout, delta);
+  if ((e = mca_launch_status())) return e;
+  CUtensorMap mq, mk, mv, mdo;
+  const McaStrides sp{(int64_t)H * T * 128, (int64_t)T * 128, 128};
+  const CUtensorMap* maps[4] = {&mq, &mk, &mv, &mdo};
+  for (int i = 0; i < 4; ++i)
+    if ((e = make_map_4d(const_cast<CUtensorMap*>(maps[i]), w.tensor[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp,
+                         CU_TENSOR_MAP_SWIZZLE_128B)))
+      return e;
+  BwdParams p;
+  p.fac = w.fac;
+  p.lse = lse; p.delta = delta; p.status = status; p.T = T; p.causal = causal; p.H = H;
+  {
+    const int64_t g = (64ll << 20) / ((int64_t)4 * T * 256);
+    p.group = causal ? (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)B * H)) : 1;
+  }
+  p.os = sin;
+  p.scale = 1.0f / sqrtf((float)HD);
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  const size_t smem_kv = BwdPlan<128>::BYTES_KV, smem_dq = BwdPlan<128>::BYTES_DQ;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
+  dim3 grid(mca_ceil_div(T, BLK), B * H);
+  p.out0 = dk; p.out1 = dv;
+  sdpa_bwd_dkdv_tc_kernel<HD, true><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
+  if ((e = mca_launch_status())) return e;
+  p.out0 = dq; p.out1 = nullptr;
+  sdpa_bwd_dq_tc_kernel<HD, true><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
   return mca_launch_status();
 }
 
@@ -695,4 +871,24 @@ int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, con
   if (e) return e;
   if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
   return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
+}
+
+int mca_sdpa_backward_f32_tc(const float* dy, const float* y_copy, const float* lse, float* delta_scratch, int causal, int B,
+                             int H, int T, int D, float* dq, float* dk, float* dv, void* workspace, int64_t workspace_bytes,
+                             int* status, int layout, void* stream) {
+  if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
+  if (!dy || !y_copy || !lse || !delta_scratch || !dq || !dk || !dv || !workspace || !status) return ERROR_PARAM_NULL;
+  if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
+  if (!mca_sdpa_forward_f32_tc_supported(D)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (workspace_bytes < mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+       reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (D) {
+    case 16: return launch_bwd_split<16>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
+    case 32: return launch_bwd_split<32>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
+    case 64: return launch_bwd_split<64>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
+  }
+  return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

@@ -1,0 +1,137 @@
+// Pre-pass of the split-operand tensor-core kernels for fp32 callers: every fp32 tensor is scaled by a power of two
+// (chosen from its largest magnitude) and written as rows [hi (64 fp16, HD used) | lo (64 fp16, HD used)] with
+// hi = fp16(x), lo = fp16(x - hi): 22 mantissa bits per element, both halves inside the normal range of fp16 for
+// every element that matters.
+//
+// Workspace (one per attention handle or caller):
+//   bytes [0,16)     amax[4]   largest |x| of q, k, v, dY as float bit patterns (integer order = float order)
+//   bytes [64,128)   fac[16]   scale factors derived from them (all powers of two), see SplitFac
+//   bytes [1024,...) four tensors of rows x 128 fp16: q, k, v, dY
+#pragma once
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace split {
+
+enum SplitFac : int {
+  FAC_INV_QK = 0,    // 1 / (s_q s_k): logits = (Q' K'^T) x this
+  FAC_INV_V = 1,     // 1 / s_v: output = (P V') x this
+  FAC_DYV = 2,       // s_dy s_v: delta in the units of dP' = dY' V'^T
+  FAC_INV_DYVK = 3,  // 1 / (s_dy s_v s_k): dQ
+  FAC_INV_DYVQ = 4,  // 1 / (s_dy s_v s_q): dK
+  FAC_INV_DY = 5,    // 1 / s_dy: dV
+};
+
+constexpr int TENSOR_Q = 0, TENSOR_K = 1, TENSOR_V = 2, TENSOR_DY = 3;
+
+struct Workspace {
+  unsigned int* amax;
+  float* fac;
+  __half* tensor[4];
+};
+
+inline int64_t workspace_bytes(int64_t rows) { return 1024 + 4 * rows * 128 * 2; }
+
+inline Workspace carve(void* base, int64_t rows) {
+  Workspace w;
+  w.amax = static_cast<unsigned int*>(base);
+  w.fac = reinterpret_cast<float*>(static_cast<char*>(base) + 64);
+  __half* t = reinterpret_cast<__half*>(static_cast<char*>(base) + 1024);
+  for (int i = 0; i < 4; ++i) w.tensor[i] = t + (size_t)i * rows * 128;
+  return w;
+}
+
+struct Job {
+  const float* src[3];   // up to three fp32 tensors with the same element strides
+  __half* dst[3];
+  int slot[3];           // which amax entry each one owns
+};
+
+// amax[slot] = max |x| of each tensor
+template <int HD>
+__global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
+                                                   unsigned int* __restrict__ amax) {
+  const float* x = job.src[blockIdx.y];
+  constexpr int V4 = HD / 4;
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / V4;
+    const int c = (int)(i - row * V4);
+    const int64_t bh = row / T, t = row - bh * T;
+    const int64_t b = bh / H, h = bh - b * H;
+    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax + job.slot[blockIdx.y], __float_as_uint(m));
+}
+
+// The power of two that brings max |x| into [2^12, 2^13): the largest fp16 is 65504 and the low half of an element
+// is about 2^-11 of it, so both halves of everything within 2^-14 of the maximum are normal fp16 numbers.
+__device__ __forceinline__ float pow2_scale(unsigned int amax_bits) {
+  const float a = __uint_as_float(amax_bits);
+  if (!(a > 0.f) || !(a < 3.0e38f)) return 1.0f;
+  int e;
+  frexpf(a, &e);                    // a = f * 2^e, f in [0.5, 1)
+  return ldexpf(1.0f, 13 - e);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
+                                                   const unsigned int* __restrict__ amax, float* __restrict__ fac,
+                                                   int backward) {
+  const int which = blockIdx.y;
+  const float* x = job.src[which];
+  __half* dst = job.dst[which];
+  const float sc = pow2_scale(amax[job.slot[which]]);
+  if (which == 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+    const float sq = pow2_scale(amax[TENSOR_Q]), sk = pow2_scale(amax[TENSOR_K]), sv = pow2_scale(amax[TENSOR_V]);
+    if (!backward) {
+      fac[FAC_INV_QK] = 1.0f / (sq * sk);   // powers of two: every product and quotient here is exact
+      fac[FAC_INV_V] = 1.0f / sv;
+    } else {
+      const float sdy = pow2_scale(amax[TENSOR_DY]);
+      fac[FAC_DYV] = sdy * sv;
+      fac[FAC_INV_DYVK] = 1.0f / (sdy * sv * sk);
+      fac[FAC_INV_DYVQ] = 1.0f / (sdy * sv * sq);
+      fac[FAC_INV_DY] = 1.0f / sdy;
+    }
+  }
+  constexpr int V4 = HD / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / V4;
+    const int c = (int)(i - row * V4);
+    const int64_t bh = row / T, t = row - bh * T;
+    const int64_t b = bh / H, h = bh - b * H;
+    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+    const float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+    __half hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      hi[j] = __float2half_rn(e[j]);
+      lo[j] = __float2half_rn(e[j] - __half2float(hi[j]));
+    }
+    __half* o = dst + row * 128 + c * 4;
+    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(hi);
+    *reinterpret_cast<uint2*>(o + 64) = *reinterpret_cast<const uint2*>(lo);
+  }
+}
+
+// Split `count` tensors (q, k, v for the forward; dY for the backward) into the workspace.
+template <int HD>
+inline int run(const Job& job, int count, const McaStrides& st, int H, int T, int64_t rows, const Workspace& w, bool backward,
+               cudaStream_t stream) {
+  for (int i = 0; i < count; ++i) MCA_CUDA_TRY(cudaMemsetAsync(w.amax + job.slot[i], 0, sizeof(unsigned int), stream));
+  const int blocks = (int)std::min<int64_t>(148 * 8, (rows * (HD / 4) + 255) / 256);
+  amax_kernel<HD><<<dim3(blocks, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax);
+  int e = mca_launch_status();
+  if (e) return e;
+  rows_kernel<HD><<<dim3(blocks, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax, w.fac, backward ? 1 : 0);
+  return mca_launch_status();
+}
+
+}  // namespace split
