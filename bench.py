@@ -1044,11 +1044,17 @@ def run_profile_case(case):
     dim 4096 for 1 and 8 sequences plus the feed-forward half and the classifier for one (also prints their
     CUDA-event bandwidth); `norm-small` = the LayerNorm / RMSNorm layer kernels on a 268 MB tensor;
     `llama-step` = the whole decode step of an 8-layer llama2-7B-shaped model, eager and from a CUDA graph
-    (a timing case, about 15 GB on the device: not for ncu)."""
+    (a timing case, about 15 GB on the device: not for ncu); `tft`, `train`, `sweep`, `backward` = the N = 1 legs of
+    the benchmark on their own."""
     import torch
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
     dev = torch.device("cuda", 0)
+    if case in ("tft", "train", "sweep", "backward"):
+        # the N = 1 legs of the benchmark on their own (same code, same JSON fragment)
+        cx = Ctx(argparse.Namespace())
+        print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward}[case](cx)}))
+        return
     if case == "gemv-small":
         dim = DEC_HEADS * DEC_HS
         ws = [torch.randn(dim, dim, device=dev) * 0.02 for _ in range(4)]   # wq, wk, wv, wo: 67 MB each
@@ -1252,7 +1258,8 @@ def main():
                     help="one GPU: skip the other configurations (train, sweep, backward, decode variants, tft)")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "norm-small", "llama-step"],
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "norm-small", "llama-step",
+                                                     "tft", "train", "sweep", "backward"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
     if args.case:

@@ -112,6 +112,257 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_fwd_kernel(const float* __res
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Forward, tiled form (the shapes the TFT network runs: d in {16, 32, 64}, Nk <= 192).
+//
+// One CTA = one batch item x 24 query rows, all heads.  The K tiles of the heads and then V (Nk x d each) stream through
+// two shared-memory buffers filled by asynchronous copies, two tiles ahead of the arithmetic.  The scores of the 24 rows
+// are computed in 6-row x 3-key register tiles (warps 0-3 take the rows six at a time over keys [0,96), warps 4-7 over
+// [96,192)): per four values of the head dimension a warp issues 6 broadcast reads of Q and 3 conflict-free reads of K
+// for 72 FMAs, which balances the shared-memory pipe against the FMA pipes (one row per warp, as the generic kernel
+// below does it, is bound by shared memory four times over).  The softmax stays in that register layout: a row's two
+// half-maxima and half-sums cross between the two warps that share it through 2 x 24 floats of shared memory, and the
+// sum over the heads of the probabilities is 18 registers per thread.  Because V is shared by the heads the output is
+// (mean_h P_h) V, one product at the end.  Two CTAs fit an SM.
+// smem: Kt[2][Nk][d] (16-byte pieces swizzled by row) | Qs[2][24][d] | ex[2][2][24]
+// ---------------------------------------------------------------------------------------------
+constexpr int TQ = 24;             // query rows per CTA
+constexpr int TQ_R = 6;            // rows of a register tile
+constexpr int TQ_C = 3;            // keys per lane of a register tile (32 lanes: 96 keys per warp)
+constexpr int TQ_KEYS = 2 * 32 * TQ_C;   // keys a CTA covers: 192
+
+// (Nk, D) tile -> shared memory rows of exactly D floats; the 16-byte pieces of row j are stored at piece ^ (j & SW), so
+// that lanes reading the same piece of consecutive rows hit different banks without padding the rows.
+template <int D>
+__device__ __forceinline__ void tile_to_smem_async_swz(float* dst, const float* __restrict__ src, int Nk, int tid) {
+  constexpr int D4 = D / 4, SW = D4 >= 8 ? 7 : D4 - 1;
+  for (int idx = tid; idx < Nk * D4; idx += TFT_THREADS) {
+    const int j = idx / D4, c4 = idx - j * D4;
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + (size_t)j * D + ((c4 ^ (j & SW)) << 2));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + (size_t)idx * 4) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all_but(int n) {
+  if (n == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+  else asm volatile("cp.async.wait_group 1;" ::: "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(TFT_THREADS, 2) tft_fwd_tiled_kernel(const float* __restrict__ Q, const float* __restrict__ K,
+                                                                       const float* __restrict__ V,
+                                                                       const float* __restrict__ mask, int H, int Nq, int Nk,
+                                                                       float scale, float* __restrict__ out,
+                                                                       float* __restrict__ attn) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int SW = D / 4 >= 8 ? 7 : D / 4 - 1;     // swizzle of the 16-byte pieces of a tile row
+  const size_t tile = (size_t)Nk * D;
+  float* Kt = smem;                                  // two tiles
+  float* Qs = Kt + 2 * tile;                         // two (24, D) blocks
+  float* ex = Qs + 2 * TQ * D;                       // [2 (max | sum)][2 key halves][24 rows]
+  const int b = blockIdx.y, q0 = blockIdx.x * TQ;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int rows = min(TQ, Nq - q0);
+
+  // tile t: K of head t (with that head's 24 query rows) or, for t == H, V; one commit group per call.  Query rows
+  // beyond Nq are zero-filled (a copy with source size 0).
+  auto load_tile = [&](int t) {
+    if (t > H) return;
+    if (t < H) {
+      const float* src = Q + (((int64_t)b * H + t) * Nq + q0) * D;
+      float* dst = Qs + (t & 1) * TQ * D;
+      for (int idx = tid; idx < TQ * (D / 4); idx += TFT_THREADS) {
+        const int r = idx / (D / 4);
+        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + idx * 4);
+        const int nbytes = r < rows ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa), "l"(src + (r < rows ? idx * 4 : 0)), "r"(nbytes) : "memory");
+      }
+    }
+    tile_to_smem_async_swz<D>(Kt + (t & 1) * tile, t < H ? K + ((int64_t)b * H + t) * Nk * D : V + (int64_t)b * Nk * D, Nk, tid);
+  };
+  load_tile(0);
+  load_tile(1);
+
+  const float inv_h = 1.f / (float)H;
+  const int rg = w & 3;                 // this warp's six rows: rg*6 .. rg*6+5
+  const int khalf = w >> 2;             // its half of the keys: khalf*96 + lane + 32c
+  // The mask is the same for every head (and batch item): this thread's entries are kept as bits, bit r*3+c = row
+  // rg*6+r, key khalf*96 + lane + 32c is masked (mask_batch(..., search = 1, replace = -1e29),
+  // MultiHeadAttentionInterpLayer.cs:743).  Keys beyond Nk are marked in `dead` and never contribute.
+  unsigned mbits = 0, dead = 0;
+  {
+    float mv[TQ_R][TQ_C];               // all eighteen loads first (clamped addresses), then the tests
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const int i = min(rg * TQ_R + r, rows - 1), j = min(khalf * (32 * TQ_C) + lane + 32 * c, Nk - 1);
+        mv[r][c] = mask != nullptr ? __ldg(mask + (int64_t)(q0 + i) * Nk + j) : 0.f;
+      }
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const int i = rg * TQ_R + r, j = khalf * (32 * TQ_C) + lane + 32 * c;
+        if (j >= Nk) dead |= 1u << (r * TQ_C + c);
+        else if (i < rows && mv[r][c] == 1.0f) mbits |= 1u << (r * TQ_C + c);
+      }
+  }
+  float pmr[TQ_R][TQ_C];                // sum over the heads of this thread's probabilities
+#pragma unroll
+  for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) pmr[r][c] = 0.f;
+
+  for (int h = 0; h < H; ++h) {
+    cp_async_wait_all_but(h + 1 <= H ? 1 : 0);   // tile h has landed (tile h+1 may still be in flight)
+    __syncthreads();                    // K_h and Q_h visible to all; everyone is past the previous head
+    const float* Kh = Kt + (h & 1) * tile;
+    float acc[TQ_R][TQ_C];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) acc[r][c] = 0.f;
+    const float* krow[TQ_C];
+    int ksw[TQ_C];
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) {
+      const int j = min(khalf * (32 * TQ_C) + lane + 32 * c, Nk - 1);
+      krow[c] = Kh + (size_t)j * D;
+      ksw[c] = j & SW;
+    }
+    const float* qrow = Qs + (h & 1) * TQ * D + rg * TQ_R * D;
+#pragma unroll
+    for (int i = 0; i < D / 4; ++i) {
+      float4 kv[TQ_C], qv[TQ_R];
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) kv[c] = *reinterpret_cast<const float4*>(krow[c] + ((i ^ ksw[c]) << 2));
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r) qv[r] = *reinterpret_cast<const float4*>(qrow + r * D + 4 * i);
+      // component-major order: eighteen independent FMAs stand between two that depend on each other
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) acc[r][c] = fmaf(qv[r].x, kv[c].x, acc[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) acc[r][c] = fmaf(qv[r].y, kv[c].y, acc[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) acc[r][c] = fmaf(qv[r].z, kv[c].z, acc[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) acc[r][c] = fmaf(qv[r].w, kv[c].w, acc[r][c]);
+    }
+    // scale, mask, and this warp's half of every row maximum
+    float hm[TQ_R];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const unsigned bit = 1u << (r * TQ_C + c);
+        acc[r][c] = (mbits & bit) ? MCA_MASKED_LOGIT : acc[r][c] * scale;
+        if (!(dead & bit)) m = fmaxf(m, acc[r][c]);
+      }
+      hm[r] = warp_max(m);
+    }
+    if (lane < TQ_R) {
+      float v = hm[0];
+#pragma unroll
+      for (int r = 1; r < TQ_R; ++r) v = lane == r ? hm[r] : v;
+      ex[khalf * TQ + rg * TQ_R + lane] = v;
+    }
+    __syncthreads();                    // half-maxima exchanged; every reader of K_h is done
+    load_tile(h + 2);                   // into the buffers K_h and Q_h occupied
+    if (h + 2 > H) asm volatile("cp.async.commit_group;" ::: "memory");   // keep one group per iteration
+    float hs[TQ_R];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      const float m = fmaxf(ex[rg * TQ_R + r], ex[TQ + rg * TQ_R + r]);
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        acc[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : expf(acc[r][c] - m);
+        sum += acc[r][c];
+      }
+      hs[r] = warp_sum(sum);
+    }
+    if (lane < TQ_R) {
+      float v = hs[0];
+#pragma unroll
+      for (int r = 1; r < TQ_R; ++r) v = lane == r ? hs[r] : v;
+      ex[2 * TQ + khalf * TQ + rg * TQ_R + lane] = v;
+    }
+    __syncthreads();                    // half-sums exchanged
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      const float inv = inv_h / (ex[2 * TQ + rg * TQ_R + r] + ex[3 * TQ + rg * TQ_R + r]);   // the 1/H of the head mean (:263) goes in here
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) pmr[r][c] = fmaf(acc[r][c], inv, pmr[r][c]);   // running head sum (:255-260)
+    }
+  }
+  // mean probabilities: to global memory from the registers, and into the free K buffer for the product with V
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  float* pm = Kt + ((H + 1) & 1) * tile;                  // V is tile H, in buffer H & 1
+#pragma unroll
+  for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) {
+      const int i = rg * TQ_R + r, j = khalf * (32 * TQ_C) + lane + 32 * c;
+      if (j < Nk) {
+        pm[i * Nk + j] = pmr[r][c];
+        if (i < rows) attn[((int64_t)b * Nq + q0 + i) * Nk + j] = pmr[r][c];
+      }
+    }
+  __syncthreads();                      // V in place, pm complete
+  const float* Vt = Kt + (H & 1) * tile;
+  // out = pm V.  A thread owns four columns of six rows (rq, rq + 4, ...) over a slice of the keys: per key one
+  // 16-byte read of V and six (broadcast) reads of pm feed 24 FMAs.  The slices' partial sums meet in shared memory
+  // behind pm (the buffer holds Nk x D floats, pm takes 24 x Nk of them).
+  constexpr int C4 = D / 4;                               // column groups
+  constexpr int SLOTS = TFT_THREADS / (C4 * 4);           // key slices (4 at D = 64)
+  const int c4 = tid % C4, rq = (tid / C4) & 3, ks = tid / (C4 * 4);
+  const int per = (Nk + SLOTS - 1) / SLOTS;
+  const int j0 = ks * per, j1 = min(Nk, j0 + per);
+  float o[TQ / 4][4];
+#pragma unroll
+  for (int r = 0; r < TQ / 4; ++r) { o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.f; }
+  for (int j = j0; j < j1; ++j) {
+    const float4 vv = *reinterpret_cast<const float4*>(Vt + (size_t)j * D + ((c4 ^ (j & SW)) << 2));
+#pragma unroll
+    for (int r = 0; r < TQ / 4; ++r) {
+      const float pj = pm[(rq + 4 * r) * Nk + j];
+      o[r][0] = fmaf(pj, vv.x, o[r][0]); o[r][1] = fmaf(pj, vv.y, o[r][1]);
+      o[r][2] = fmaf(pj, vv.z, o[r][2]); o[r][3] = fmaf(pj, vv.w, o[r][3]);
+    }
+  }
+  float* part = pm + (size_t)TQ * Nk;                     // (SLOTS - 1) x 24 x D floats (the launcher checks the room)
+  if (ks > 0) {
+#pragma unroll
+    for (int r = 0; r < TQ / 4; ++r)
+      *reinterpret_cast<float4*>(part + (size_t)(ks - 1) * TQ * D + (rq + 4 * r) * D + c4 * 4) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+  }
+  __syncthreads();
+  if (ks == 0) {
+#pragma unroll
+    for (int r = 0; r < TQ / 4; ++r) {
+      const int i = rq + 4 * r;
+      float4 acc4 = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+      for (int s2 = 0; s2 < SLOTS - 1; ++s2) {
+        const float4 t = *reinterpret_cast<const float4*>(part + (size_t)s2 * TQ * D + i * D + c4 * 4);
+        acc4.x += t.x; acc4.y += t.y; acc4.z += t.z; acc4.w += t.w;
+      }
+      if (i < rows) *reinterpret_cast<float4*>(out + ((int64_t)b * Nq + q0 + i) * D + c4 * 4) = acc4;
+    }
+  }
+}
+
 // Backward of the block above (MultiHeadAttentionInterpLayer<T>.backward,
 // MultiHeadAttentionInterpLayer.cs:780-859: the two head-mean backward loops, matmul grads,
 // softmax backward, scale, and the sum of the per-head V gradients into the shared V).
@@ -251,6 +502,22 @@ int mca_tft_attention_forward_f32(const float* q, const float* k, const float* v
   if (B <= 0 || H <= 0 || Nq <= 0 || Nk <= 0 || d <= 0 || B > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if (d % 4 != 0 || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  // the tiled kernel where the shape fits it (two K buffers and two CTAs per SM), else the generic one
+  const size_t smem_t = sizeof(float) * (2 * (size_t)Nk * d + 2 * (size_t)TQ * d + 4 * TQ);
+  const int slices = TFT_THREADS / d;   // key slices of the final product: TFT_THREADS / ((d / 4) * 4)
+  // a K buffer must also hold the mean probabilities (24 x Nk) and the partial outputs of the other slices
+  const bool room = (size_t)TQ * Nk + (size_t)(slices - 1) * TQ * d <= (size_t)Nk * d;
+  if ((d == 16 || d == 32 || d == 64) && Nk <= TQ_KEYS && smem_t <= 113 * 1024 && room && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    dim3 grid_t(mca_ceil_div(Nq, TQ), B);
+    const float sc = 1.0f / sqrtf((float)d);
+    cudaStream_t st = (cudaStream_t)stream;
+#define MCA_TFT_TILED(D_)                                                                                                 \
+    MCA_CUDA_TRY(cudaFuncSetAttribute(tft_fwd_tiled_kernel<D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+    tft_fwd_tiled_kernel<D_><<<grid_t, TFT_THREADS, smem_t, st>>>(q, k, v, mask, H, Nq, Nk, sc, out, attn);
+    if (d == 64) { MCA_TFT_TILED(64) } else if (d == 32) { MCA_TFT_TILED(32) } else { MCA_TFT_TILED(16) }
+#undef MCA_TFT_TILED
+    return mca_launch_status();
+  }
   const size_t smem = sizeof(float) * ((size_t)Nk * (d + 4) + (size_t)H * TFT_ROWS * d + 2 * (size_t)TFT_ROWS * Nk);
   if (smem > 227 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   MCA_CUDA_TRY(cudaFuncSetAttribute(tft_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
