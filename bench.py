@@ -502,6 +502,20 @@ def run_decode(cx, batch, bf16, multi, steps):
             dst[:, hl * DEC_HS:(hl + 1) * DEC_HS] = src
     out = torch.empty(batch, dim, device=dev)
     out_all = torch.empty(world, batch, dim, device=dev) if world > 1 else None
+    # Exchange of the head outputs when world > 1: the library's exchange kernel (peer stores + flags, no collective
+    # per layer-step) when symmetric memory can be set up, else a NCCL all-gather; a short trial picks the faster one.
+    peer, exchange = None, "none"
+    if world > 1:
+        exchange = "nccl all-gather per layer-step"
+        if not cx.args.nccl_exchange:
+            try:
+                peer = head_shard.PeerDecodeOutput(batch, world * dim, dev, lib)
+                exchange = "exchange kernel per layer-step (peer stores over NVLink + flags)"
+            except Exception as exc:  # noqa: BLE001 - any failure to map peer memory selects the NCCL exchange
+                peer = None
+                exchange += f" (symmetric memory unavailable: {type(exc).__name__})"
+    use_peer = [peer is not None]
+    last = [None]
     sl, ns, need = C.c_int(), C.c_int(), C.c_int64()
     lib.mca_decode_plan(batch, heads, heads, DEC_HS, max_len, C.byref(sl), C.byref(ns), C.byref(need))
     scratch = torch.empty(max(1, need.value), device=dev)
@@ -520,7 +534,10 @@ def run_decode(cx, batch, bf16, multi, steps):
         if rc:
             raise RuntimeError(f"mca_decode_attention failed with {rc}")
         if world > 1:  # the head outputs of every rank, as the Wo projection of the next step needs them
-            head_shard.gather_decode_outputs(out, out=out_all)
+            if use_peer[0]:
+                last[0] = peer.exchange(out, stream)
+            else:
+                head_shard.gather_decode_outputs(out, out=out_all)
 
     for i in range(3 * n_buf):
         layer(i)
@@ -528,6 +545,26 @@ def run_decode(cx, batch, bf16, multi, steps):
         cx.barrier()
     else:
         torch.cuda.synchronize()
+    if peer is not None:
+        trial = {}
+        for name, flag in (("peer", True), ("nccl", False)):
+            use_peer[0] = flag
+            for i in range(n_buf):
+                layer(i)
+            cx.barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for i in range(DEC_LAYERS):
+                layer(i)
+            t1.record(stream)
+            cx.barrier()
+            trial[name] = cx.max_over_ranks([t0.elapsed_time(t1)])[0]
+        if peer.status()[0] != 0:
+            raise RuntimeError(f"decode exchange gave up: {peer.status()}")
+        use_peer[0] = trial["peer"] <= trial["nccl"]
+        if not use_peer[0]:
+            exchange = "nccl all-gather per layer-step"
+        exchange += " (chosen by a trial of %d layer-steps: exchange kernel %.3f ms, NCCL all-gather %.3f ms)" % (DEC_LAYERS, trial["peer"], trial["nccl"])
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for s in range(steps):
@@ -553,14 +590,18 @@ def run_decode(cx, batch, bf16, multi, steps):
     layer(0)
     torch.cuda.synchronize()
     seqs = sorted({int(np.argmin(lengths)), int(np.argmax(lengths)), batch // 2})
-    if world > 1:
+    if world > 1 and use_peer[0]:
+        if peer.status()[0] != 0:
+            raise RuntimeError(f"decode exchange gave up: {peer.status()}")
+        got = last[0][seqs].cpu().numpy()
+    elif world > 1:
         got = out_all.transpose(0, 1).reshape(batch, world * dim)[seqs].cpu().numpy()
     else:
         got = out[seqs].cpu().numpy()
     check = {"batch": batch, "bf16": bf16, "seqs": seqs, "lengths": lengths, "got": got, "heads_total": DEC_HEADS if multi else heads}
     res = {"metric": "decode_tokens_per_s", "value": round(batch / (ms_step * 1e-3), 1), "unit": "tok/s",
            "ms_per_step": round(ms_step, 4), "steps": steps, "dtype": "bf16" if bf16 else "f32",
-           "config": {"workload": f"config3 decode attention batch={batch} heads={DEC_HEADS} (x{DEC_HS}) over {world} GPU(s), "
+           "config": {"exchange": exchange, "workload": f"config3 decode attention batch={batch} heads={DEC_HEADS} (x{DEC_HS}) over {world} GPU(s), "
                                   f"cache lengths U[{DEC_LMIN},{DEC_LMAX}] (mean {lengths.mean():.0f}), {'bf16' if bf16 else 'fp32'} cache, "
                                   f"{DEC_LAYERS} layer-steps per token rotating {n_buf} distinct layer caches "
                                   f"({n_buf * per_buffer / 1e6:.0f} MB in all, above the 126 MB L2)",

@@ -356,6 +356,19 @@ MCA_API int mca_decode_head_size_supported(int head_size);
  * status3[1] = the first such sequence, status3[2] = its position. */
 MCA_API int mca_decode_status(int* status3);
 
+/* Exchange of the decode head outputs between the GPUs that share the heads (one process per GPU), replacing an
+ * all-gather per layer-step.  No reference counterpart (the reference decodes on one GPU).  Rank `rank` of n stores its
+ * (B, dim_local) slice at column col0 of the (B, dim_total) buffer of every rank (dst[i]: peer memory mapped into this
+ * process, this rank's own buffer included; plain stores over NVLink), raises entry `rank` of every rank's flag array
+ * (flag_dst[i], int[8]) to `generation`, and waits until every entry of its own array (flag_local) has reached
+ * `generation`: when the kernel has finished, this rank's buffer is complete.  Generations grow by one per exchange;
+ * alternate between two buffers (a rank may still read exchange g while its peers already store exchange g + 1).
+ * counter: a device int, zero before the first call.  The wait is bounded by limit_ms (<= 10000): on expiry the kernel
+ * returns with status[0] = 3, status[1] = the rank it waited for, status[2] = that rank's flag. */
+MCA_API int mca_decode_exchange(const float* src, float* const* dst, int* const* flag_dst, const int* flag_local,
+                                int* counter, int* status, int n, int rank, int B, int dim_local, int dim_total, int col0,
+                                int generation, int limit_ms, void* stream);
+
 /* The projections around the decode attention, each fused with its neighbour and bound by the
  * one pass over the weights.  Replace Primitives::rmsnorm + three Primitives::matmul (cublasSgemv)
  * calls, and the Wo matmul + residual add, of TransformerGpu::forward,

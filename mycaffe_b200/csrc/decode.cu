@@ -13,6 +13,7 @@
 // warp shuffles, keeps an online-softmax state per lane group, and writes one partial
 // (max, sum, weighted V) per head.  A second small kernel combines the partials.  The work
 // is bound by HBM traffic: every cache byte is read exactly once.
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -413,6 +414,69 @@ __global__ void __launch_bounds__(HS) decode_combine_kernel(const float* __restr
   out[((int64_t)b * n_heads + h) * HS + e] = a / lsum;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Exchange of the head outputs between the GPUs that share the heads (one process per GPU), in place of an all-gather
+// per layer-step: every rank stores its (B, dim/N) slice into the (B, dim) buffer of every rank (plain 16-byte stores
+// to peer memory mapped into this process; this GPU's own buffer is one of the destinations), then raises its flag
+// in every rank's flag array and waits until all ranks' flags in its own array have reached this exchange's
+// generation.  When the kernel has finished, this rank's buffer holds every rank's slice.
+// The wait is bounded: if a peer never arrives the kernel records it in the status words and returns.
+// ---------------------------------------------------------------------------------------------
+struct ExchangeParams {
+  const float* src;        // (B, dim_local) this rank's head outputs
+  float* dst[8];           // the (B, dim_total) buffer of every rank, this rank's own included
+  int* flag_dst[8];        // the flag array of every rank (int[8]); this rank raises entry `rank` in each
+  const int* flag_local;   // this rank's own flag array
+  int* counter;            // local ticket of the CTAs that have finished storing (returns to 0)
+  int* status;             // [0] != 0: gave up; [1] the rank waited for, [2] its flag, [3] the generation
+  int n, rank, B, dim_local, dim_total, col0, generation;
+  unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(256) decode_exchange_kernel(const ExchangeParams p) {
+  mca_pdl_launch_dependents();
+  mca_pdl_wait();          // src is the output of the kernel before
+  const int v_per_row = p.dim_local / 4;
+  const int total = p.B * v_per_row;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int b = idx / v_per_row, c = idx - b * v_per_row;
+    const float4 v = *reinterpret_cast<const float4*>(p.src + (int64_t)b * p.dim_local + c * 4);
+    const int64_t off = (int64_t)b * p.dim_total + p.col0 + c * 4;
+#pragma unroll
+    for (int d = 0; d < 8; ++d)   // constant indices: the parameter block stays in constant memory
+      if (d < p.n) *reinterpret_cast<float4*>(p.dst[d] + off) = v;
+  }
+  __threadfence_system();          // this thread's peer stores are ordered before what follows
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const int ticket = atomicAdd(p.counter, 1);
+  if (ticket != (int)gridDim.x - 1) return;
+  // last CTA: every store of this rank has been issued and fenced
+  *p.counter = 0;
+  __threadfence_system();
+#pragma unroll
+  for (int d = 0; d < 8; ++d)
+    if (d < p.n) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_dst[d] + p.rank), "r"(p.generation) : "memory");
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (int r = 0; r < p.n; ++r) {
+    int f;
+    unsigned polls = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(f) : "l"(p.flag_local + r) : "memory");
+      if (f - p.generation >= 0) break;           // generations only grow (wrap-safe comparison)
+      if ((++polls & 63u) == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > p.limit_ns) {
+          if (atomicCAS(p.status, 0, 3) == 0) { p.status[1] = r; p.status[2] = f; p.status[3] = p.generation; }
+          return;
+        }
+      }
+    }
+  }
+}
+
 template <typename CT, int HS>
 int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
   const int kvmt = p.kv_mul >= 4 ? 4 : p.kv_mul;
@@ -547,4 +611,30 @@ int mca_decode_status(int* status3) {
   }
   status3[0] = st[0]; status3[1] = st[1]; status3[2] = st[2];
   return 0;
+}
+
+int mca_decode_exchange(const float* src, float* const* dst, int* const* flag_dst, const int* flag_local, int* counter,
+                        int* status, int n, int rank, int B, int dim_local, int dim_total, int col0, int generation,
+                        int limit_ms, void* stream) {
+  if (!src || !dst || !flag_dst || !flag_local || !counter || !status) return ERROR_PARAM_NULL;
+  if (n < 1 || n > 8 || rank < 0 || rank >= n || B <= 0 || dim_local <= 0 || dim_local % 4 || dim_total % 4 || col0 % 4 ||
+      col0 < 0 || col0 + dim_local > dim_total || limit_ms <= 0 || limit_ms > 10000)
+    return ERROR_PARAM_OUT_OF_RANGE;
+  ExchangeParams p;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(src);
+  for (int i = 0; i < 8; ++i) {
+    p.dst[i] = i < n ? dst[i] : nullptr;
+    p.flag_dst[i] = i < n ? flag_dst[i] : nullptr;
+    if (i < n) {
+      if (!dst[i] || !flag_dst[i]) return ERROR_PARAM_NULL;
+      bits |= reinterpret_cast<uintptr_t>(dst[i]);
+    }
+  }
+  if (bits & 15) return ERROR_PARAM_OUT_OF_RANGE;
+  p.src = src; p.flag_local = flag_local; p.counter = counter; p.status = status;
+  p.n = n; p.rank = rank; p.B = B; p.dim_local = dim_local; p.dim_total = dim_total; p.col0 = col0; p.generation = generation;
+  p.limit_ns = (unsigned long long)limit_ms * 1000000ull;
+  const int total = B * (dim_local / 4);
+  const int blocks = std::max(1, std::min(148, (total + 255) / 256));
+  return mca_launch_pdl(decode_exchange_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, p);
 }

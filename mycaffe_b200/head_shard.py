@@ -120,3 +120,60 @@ class PeerOutput:
     def release(self) -> None:
         """Every rank has finished reading the buffer (stream-ordered): the next scatter may overwrite it."""
         dist.all_reduce(self._flag, group=self.group)
+
+
+class PeerDecodeOutput:
+    """The (B, dim) head outputs of a decode layer-step, held by every rank and completed by every rank's exchange
+    kernel (`mca_decode_exchange`): each rank stores its (B, dim/N) slice into all N buffers over NVLink, raises its
+    flag everywhere and waits for the others' flags, so no collective is launched per layer-step.
+
+    Two buffers alternate by exchange (a rank may still be reading exchange g while its peers store g + 1); a buffer is
+    reused by exchange g + 2, which no rank can reach before every rank has started exchange g + 1, i.e. has finished
+    with the result of exchange g.  Buffers, flag arrays and the ticket are symmetric memory, zeroed at set-up."""
+
+    def __init__(self, B: int, dim: int, device, lib, group=None, limit_ms: int = 2000):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if not 1 <= self.world <= 8 or dim % (4 * self.world):
+            raise ValueError("up to 8 ranks, and dim / ranks must be a multiple of 4")
+        self.B, self.dim, self.dim_local = B, dim, dim // self.world
+        self.data = symm_mem.empty((2, B, dim), dtype=torch.float32, device=device)
+        self.flags = symm_mem.empty((16,), dtype=torch.int32, device=device)   # [0..7] flags, [8] ticket, [12..15] status
+        self.data.zero_()
+        self.flags.zero_()
+        hd = symm_mem.rendezvous(self.data, self.group)
+        hf = symm_mem.rendezvous(self.flags, self.group)
+        self._data_ptrs, self._flag_ptrs = [int(x) for x in hd.buffer_ptrs], [int(x) for x in hf.buffer_ptrs]
+        if self._data_ptrs[self.rank] != self.data.data_ptr() or self._flag_ptrs[self.rank] != self.flags.data_ptr():
+            raise RuntimeError("unexpected symmetric-memory mapping")
+        self._handles = (hd, hf)
+        self._lib, self._ctypes, self.limit_ms = lib, ctypes, int(limit_ms)
+        self.generation = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)         # every rank's buffers and flags are zero before anyone stores
+
+    def exchange(self, out_local: torch.Tensor, stream=None) -> torch.Tensor:
+        """Enqueue the exchange of `out_local` (B, dim/N) on the stream; returns the (B, dim) buffer that is complete
+        when the enqueued kernel has finished."""
+        C = self._ctypes
+        self.generation += 1
+        g = self.generation
+        buf = g & 1
+        off = buf * self.B * self.dim * 4
+        dst = (C.c_void_p * self.world)(*[p_ + off for p_ in self._data_ptrs])
+        fl = (C.c_void_p * self.world)(*self._flag_ptrs)
+        st = stream if stream is not None else torch.cuda.current_stream()
+        base = self.flags.data_ptr()
+        rc = self._lib.mca_decode_exchange(out_local.data_ptr(), dst, fl, base, base + 8 * 4, base + 12 * 4, self.world, self.rank,
+                                           self.B, self.dim_local, self.dim, self.rank * self.dim_local, g, self.limit_ms,
+                                           st.cuda_stream)
+        if rc:
+            raise RuntimeError(f"mca_decode_exchange failed with {rc}")
+        return self.data[buf]
+
+    def status(self):
+        """The exchange kernels' status words (blocking): [0] != 0 means a bounded wait gave up."""
+        return self.flags[12:16].tolist()

@@ -329,3 +329,56 @@ def test_preset_status_aborts_the_raw_launch():
     torch.cuda.synchronize()
     ref = oracle.sdpa_forward(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), None, 3, f64=True)
     assert rc == 0 and st[0].item() == 0 and rel_err(y.float().cpu().numpy(), ref) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------ decode exchange
+
+def _exchange(lib, src, bufs, flags, counter, status, rank, n, B, dl, gen, limit_ms=2000):
+    dst = (C.c_void_p * n)(*[b.data_ptr() for b in bufs])
+    fl = (C.c_void_p * n)(*[f.data_ptr() for f in flags])
+    return lib.mca_decode_exchange(src.data_ptr(), dst, fl, flags[rank].data_ptr(), counter.data_ptr(), status.data_ptr(), n, rank, B, dl,
+                                   n * dl, rank * dl, gen, limit_ms, None)
+
+
+def test_decode_exchange_kernel_two_ranks_on_one_gpu():
+    """The exchange that replaces the per-layer all-gather, with both "ranks" played one after the other on one GPU
+    (two kernels that wait on each other must not share a GPU, so rank 1's arrival is written before rank 0 runs): each
+    rank's slice lands at its columns of both buffers, and the flags carry the generation."""
+    import torch
+    from mycaffe_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    B, dl, n = 5, 256, 2
+    for gen in (1, 2, 3):
+        src = [torch.randn(B, dl, device=dev) for _ in range(n)]
+        if gen == 1:
+            bufs = [torch.zeros(B, n * dl, device=dev) for _ in range(n)]
+            flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(n)]
+            counters = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(n)]
+            status = [torch.zeros(4, dtype=torch.int32, device=dev) for _ in range(n)]
+        flags[0][1] = gen                               # rank 1 "has arrived" as far as rank 0 can see
+        assert _exchange(lib, src[0], bufs, flags, counters[0], status[0], 0, n, B, dl, gen) == 0
+        assert _exchange(lib, src[1], bufs, flags, counters[1], status[1], 1, n, B, dl, gen) == 0
+        torch.cuda.synchronize()
+        want = torch.cat(src, dim=1)
+        for r in range(n):
+            assert torch.equal(bufs[r], want)
+            assert flags[r][:2].tolist() == [gen, gen] and status[r].tolist() == [0, 0, 0, 0] and counters[r].item() == 0
+
+
+def test_decode_exchange_wait_is_bounded():
+    """A peer that never arrives: the wait runs out after its limit, the kernel returns and says whom it waited for."""
+    import torch
+    from mycaffe_b200 import _lib, function_ids as ids
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    B, dl, n = 3, 64, 2
+    src = torch.randn(B, dl, device=dev)
+    bufs = [torch.zeros(B, n * dl, device=dev) for _ in range(n)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(n)]
+    counter, status = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(4, dtype=torch.int32, device=dev)
+    assert _exchange(lib, src, bufs, flags, counter, status, 0, n, B, dl, 7, limit_ms=5) == 0
+    torch.cuda.synchronize()
+    assert status.tolist() == [3, 1, 0, 7]              # gave up waiting for rank 1, whose flag was still 0
+    assert torch.equal(bufs[1][:, :dl], src)            # its own stores were made all the same
+    assert _exchange(lib, src, bufs, flags, counter, status, 0, n, B, 6, 8) == ids.ERROR_PARAM_OUT_OF_RANGE   # slice not a multiple of 4
