@@ -177,6 +177,11 @@ class Ctx:
             raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
+        # several ranks stage host tensors at once: keep each rank's (pinned) host memory on its GPU's NUMA node
+        self.affinity = {"skipped": "single process"}
+        if self.world > 1:
+            from mycaffe_b200 import head_shard
+            self.affinity = head_shard.bind_near_gpu(self.local)
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.dev)
         self.lib = _lib.load()
@@ -375,6 +380,8 @@ def run_ours(args):
 
     # ----------------------------------------------------------------- end to end through the dispatch ABI (host buffers)
     e2e = run_e2e(args, torch, dev, local, rank, world, barrier, B, H, Hl, T, D, q, k, v)
+    e2e["host_affinity"] = {k_: v_ for k_, v_ in cx.affinity.items() if k_ != "previous"}
+    e2e["h2d_gbs_per_rank"] = round(e2e["h2d_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9, 1)
 
     # ----------------------------------------------------------------- the other configurations (one GPU)
     extras, extra_checks = {}, {}
@@ -395,6 +402,8 @@ def run_ours(args):
         dist.destroy_process_group()
     if rank != 0:
         return
+    if "previous" in cx.affinity:       # the CPU legs below use every core again
+        os.sched_setaffinity(0, cx.affinity["previous"])
     import oracle
     cores = oracle.set_num_threads()    # a launcher may have exported OMP_NUM_THREADS=1 for its workers
     parity, cpu_base = prefill_parity(torch, dev, B, H, T, D, q_begin, q_step, prefill_sample, cores)

@@ -84,10 +84,13 @@ int mca_host_pipeline_chunk(int B, int H, int T, int heads_per_chunk) {
   const int64_t BH = (int64_t)B * H;
   if (heads_per_chunk > 0) return (int)(heads_per_chunk < BH ? heads_per_chunk : BH);
   // enough CTAs (one per 256 query rows) to fill the 148 SMs about four times, but at least
-  // four chunks so that the copies and the kernel have something to overlap with
+  // four chunks -- eight where a chunk of BH/8 pairs still has a CTA for most SMs -- so that the copies
+  // and the kernel have something to overlap with (the first copy and the last read-back are exposed:
+  // 1/chunks of each direction's time)
   const int64_t tiles = (T + 255) / 256;
   int64_t c = (4 * 148 + tiles - 1) / tiles;
   if (c > BH / 4) c = BH / 4;
+  if (BH >= 8 && c > BH / 8 && (BH / 8) * tiles >= 128) c = BH / 8;
   if (c < 1) c = 1;
   return (int)c;
 }

@@ -9,8 +9,59 @@ counterpart: its only multi-GPU mode is data-parallel training (MyCaffe/common/P
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
+
+
+def _parse_cpulist(text: str) -> set[int]:
+    """"0-15,64-79" -> {0..15, 64..79} (the format of sysfs cpulist files)."""
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_near_pci(bdf: str, sysfs_root: str = "/sys/bus/pci/devices") -> dict:
+    """Restrict the calling thread to the CPUs local to PCI device `bdf` ("0000:1b:00.0"): its
+    `local_cpulist` in sysfs, intersected with the CPUs the thread may already use.
+    Returns {"cpus": n, "numa_node": k, "previous": set} or {"skipped": reason}; a missing sysfs entry
+    (containers may hide it) is a skip, not an error.  Undo with os.sched_setaffinity(0, result["previous"])."""
+    try:
+        with open(os.path.join(sysfs_root, bdf, "local_cpulist")) as f:
+            local = _parse_cpulist(f.read())
+    except (OSError, ValueError) as e:
+        return {"skipped": f"{type(e).__name__}: {e}"}
+    node = -1
+    try:
+        with open(os.path.join(sysfs_root, bdf, "numa_node")) as f:
+            node = int(f.read().strip())
+    except (OSError, ValueError):
+        pass
+    previous = os.sched_getaffinity(0)
+    cpus = local & previous
+    if not cpus:
+        return {"skipped": "no local CPU in the allowed set", "numa_node": node}
+    os.sched_setaffinity(0, cpus)
+    return {"cpus": len(cpus), "numa_node": node, "previous": previous}
+
+
+def bind_near_gpu(device_index: int) -> dict:
+    """`bind_near_pci` for a CUDA device: host buffers the thread allocates and first touches afterwards, pinned
+    ones included, then lie in the memory of the GPU's NUMA node.
+
+    With one process per GPU and host tensors on both sides of every call, a rank whose staging memory sits on
+    the other socket pays the inter-socket link on every copy, and eight ranks doing so at once share it."""
+    try:
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    except (AttributeError, RuntimeError, AssertionError) as e:
+        return {"skipped": f"{type(e).__name__}: {e}"}
+    return bind_near_pci(bdf)
 
 
 def head_range(rank: int, world: int, n_heads: int, n_kv_heads: int | None = None) -> tuple[int, int]:

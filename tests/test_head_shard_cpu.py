@@ -57,3 +57,28 @@ def test_head_range_rejects_uneven_splits():
         head_shard.head_range(0, 8, 12)     # 12 heads (GPT-2 small) do not divide over 8 GPUs
     with pytest.raises(ValueError):
         head_shard.head_range(2, 2, 4)
+
+
+def test_bind_near_pci_uses_the_local_cpulist(tmp_path):
+    """The affinity helper: parses sysfs' cpulist, intersects with the allowed set, reports and can be undone;
+    a missing entry is a skip."""
+    import os
+
+    from mycaffe_b200 import head_shard
+    assert head_shard._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    allowed = os.sched_getaffinity(0)
+    keep = sorted(allowed)[: max(1, len(allowed) // 2)]
+    dev = tmp_path / "0000:1b:00.0"
+    dev.mkdir()
+    (dev / "local_cpulist").write_text(",".join(str(c) for c in keep) + ",4095\n")
+    (dev / "numa_node").write_text("1\n")
+    try:
+        r = head_shard.bind_near_pci("0000:1b:00.0", str(tmp_path))
+        assert r["cpus"] == len(keep) and r["numa_node"] == 1 and r["previous"] == allowed
+        assert os.sched_getaffinity(0) == set(keep)
+    finally:
+        os.sched_setaffinity(0, allowed)
+    assert "skipped" in head_shard.bind_near_pci("0000:ff:00.0", str(tmp_path))
+    (dev / "local_cpulist").write_text("4095\n")
+    assert "skipped" in head_shard.bind_near_pci("0000:1b:00.0", str(tmp_path))
+    assert os.sched_getaffinity(0) == allowed
