@@ -845,13 +845,19 @@ def run_tft(cx):
         fbytes = 4 * (q.numel() + k.numel() + v.numel() + out.numel() + attn.numel())
         bbytes = 4 * (2 * q.numel() + 2 * k.numel() + 2 * v.numel() + out.numel() + attn.numel())
         fflops = 2.0 * B * H * Nq * Nk * d + 2.0 * B * Nq * Nk * d
+        # backward: S, dQ, dK per head; dP = dO V^T and dV = (mean P)^T dO are shared by the heads
+        bflops = 2.0 * B * Nq * Nk * d * (3 * H + 2)
         pk = cx.peaks["hbm_gbs"]
+
+        def roof(kernel, nbytes, ms):
+            return {"bound": "hbm", "kernel": kernel, "achieved": round(nbytes / ms / 1e6, 1), "peak": pk, "unit": "GB/s",
+                    "frac": round(nbytes / ms / 1e6 / pk, 4), "peak_source": cx.peaks["source"], "kernel_ms": round(ms, 5),
+                    "bytes_per_launch": nbytes, "traffic": None}
         res["modes"].append({"Nq": Nq, "forward_us": round(fms * 1e3, 1), "backward_us": round(bms * 1e3, 1),
                              "forward_GBps": round(fbytes / fms / 1e6, 1), "backward_GBps": round(bbytes / bms / 1e6, 1),
-                             "forward_gflops": round(fflops / fms / 1e6, 1),
-                             "roofline": {"bound": "hbm", "kernel": "tft_fwd_kernel", "achieved": round(fbytes / fms / 1e6, 1), "peak": pk,
-                                          "unit": "GB/s", "frac": round(fbytes / fms / 1e6 / pk, 4), "peak_source": cx.peaks["source"],
-                                          "kernel_ms": round(fms, 5), "bytes_per_launch": fbytes, "traffic": None}})
+                             "forward_gflops": round(fflops / fms / 1e6, 1), "backward_gflops": round(bflops / bms / 1e6, 1),
+                             "roofline": roof("tft_fwd_tiled_kernel", fbytes, fms),
+                             "roofline_backward": roof("tft_bwd_tiled_kernel", bbytes, bms)})
     return res
 
 

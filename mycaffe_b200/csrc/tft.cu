@@ -15,6 +15,7 @@ namespace {
 
 constexpr int TFT_ROWS = 8;        // query rows per CTA, one per warp
 constexpr int TFT_THREADS = 256;
+constexpr int TFT_TQ_ROWS = 24;   // query rows of a tile of the tiled kernels
 
 // (Nk, d) tile -> shared memory rows of d + 4 floats with asynchronous 16-byte copies: all of a thread's copies are
 // in flight at once (a load-then-store loop serialises on the round trip of each one).
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_fwd_kernel(const float* __res
 // (mean_h P_h) V, one product at the end.  Two CTAs fit an SM.
 // smem: Kt[2][Nk][d] (16-byte pieces swizzled by row) | Qs[2][24][d] | ex[2][2][24]
 // ---------------------------------------------------------------------------------------------
-constexpr int TQ = 24;             // query rows per CTA
+constexpr int TQ = TFT_TQ_ROWS;    // query rows per CTA
 constexpr int TQ_R = 6;            // rows of a register tile
 constexpr int TQ_C = 3;            // keys per lane of a register tile (32 lanes: 96 keys per warp)
 constexpr int TQ_KEYS = 2 * 32 * TQ_C;   // keys a CTA covers: 192
@@ -135,14 +136,30 @@ constexpr int TQ_KEYS = 2 * 32 * TQ_C;   // keys a CTA covers: 192
 // (Nk, D) tile -> shared memory rows of exactly D floats; the 16-byte pieces of row j are stored at piece ^ (j & SW), so
 // that lanes reading the same piece of consecutive rows hit different banks without padding the rows.
 template <int D>
-__device__ __forceinline__ void tile_to_smem_async_swz(float* dst, const float* __restrict__ src, int Nk, int tid) {
+__device__ __forceinline__ void tile_rows_async_swz(float* dst, const float* __restrict__ src, int Nk, int tid) {
   constexpr int D4 = D / 4, SW = D4 >= 8 ? 7 : D4 - 1;
   for (int idx = tid; idx < Nk * D4; idx += TFT_THREADS) {
     const int j = idx / D4, c4 = idx - j * D4;
     const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + (size_t)j * D + ((c4 ^ (j & SW)) << 2));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src + (size_t)idx * 4) : "memory");
   }
+}
+
+template <int D>
+__device__ __forceinline__ void tile_to_smem_async_swz(float* dst, const float* __restrict__ src, int Nk, int tid) {
+  tile_rows_async_swz<D>(dst, src, Nk, tid);
   asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// (24, D) block of consecutive rows -> shared memory, rows beyond `rows` zero-filled (copies with source size 0)
+template <int D>
+__device__ __forceinline__ void rows24_async(float* dst, const float* __restrict__ src, int rows, int tid) {
+  for (int idx = tid; idx < TFT_TQ_ROWS * (D / 4); idx += TFT_THREADS) {
+    const int r = idx / (D / 4);
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + idx * 4);
+    const int nbytes = r < rows ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa), "l"(src + (r < rows ? idx * 4 : 0)), "r"(nbytes) : "memory");
+  }
 }
 
 __device__ __forceinline__ void cp_async_wait_all_but(int n) {
@@ -478,6 +495,368 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_bwd_kernel(const float* __res
   for (int idx = tid; idx < Nk * d; idx += TFT_THREADS) dVg[idx] = dVs[idx];
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward, tiled form (the shapes of the tiled forward: d in {16, 32, 64}, Nk <= 192).
+//
+// One CTA = one batch item; it walks the heads and, inside a head, the 24-row tiles of the queries.  V and two K
+// buffers (head h + 1 arrives while head h is worked on) stay in shared memory, the 24 rows of Q_h and of the output
+// gradient are double-buffered.  Per (head, tile):
+//   A  S = Q K^T and dP = dO V^T in the forward's 6 x 3 register tiles, one loop over the head dimension feeding both
+//      (dP does not depend on the head: with a single tile it is computed for the first head and kept in registers);
+//   B  mask, softmax and its backward in that layout: the row maximum, then the row sum together with sum_j P dP,
+//      cross the two warps that share a row through shared memory; P and dS = P (dP - sum) scale go to shared memory;
+//   C  dK_h += dS^T Q_h and dV += P^T dO: a thread owns 3 keys x d/4 columns of both in registers (the contraction runs
+//      over the 24 rows), dK_h across the tiles of a head, dV across everything -- no atomics, a fixed order;
+//   D  dQ = dS K_h: a thread owns a few rows x 4 columns over a slice of the keys, four keys per step (one 16-byte read
+//      of dS per row, four of K); the slices' partial sums meet in shared memory (in the buffer of P, free by then).
+// The 1/H of the head mean is applied to dP once and to dV at the end.
+// smem: Vt[nk4][d] | Kt[2][nk4][d] (16-byte pieces swizzled by row; nk4 = Nk rounded up to 4, rows beyond Nk zero) |
+//       Qs[2][24][d] | Gs[2][24][d] | Ps[24][192] | Ss[24][192] | ex[6][24]
+// ---------------------------------------------------------------------------------------------
+template <int D, bool WITH_DP>
+__device__ __forceinline__ void tft_bwd_scores(const float* const (&krow)[TQ_C], const float* const (&vrow)[TQ_C],
+                                               const int (&ksw)[TQ_C], const float* __restrict__ qrow,
+                                               const float* __restrict__ grow, float (&s)[TQ_R][TQ_C],
+                                               float (&dp)[TQ_R][TQ_C]) {
+#pragma unroll
+  for (int i = 0; i < D / 4; ++i) {
+    float4 kv[TQ_C], qv[TQ_R];
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) kv[c] = *reinterpret_cast<const float4*>(krow[c] + ((i ^ ksw[c]) << 2));
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) qv[r] = *reinterpret_cast<const float4*>(qrow + r * D + 4 * i);
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) s[r][c] = fmaf(qv[r].x, kv[c].x, s[r][c]);
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) s[r][c] = fmaf(qv[r].y, kv[c].y, s[r][c]);
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) s[r][c] = fmaf(qv[r].z, kv[c].z, s[r][c]);
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) s[r][c] = fmaf(qv[r].w, kv[c].w, s[r][c]);
+    if (WITH_DP) {
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) kv[c] = *reinterpret_cast<const float4*>(vrow[c] + ((i ^ ksw[c]) << 2));
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r) qv[r] = *reinterpret_cast<const float4*>(grow + r * D + 4 * i);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) dp[r][c] = fmaf(qv[r].x, kv[c].x, dp[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) dp[r][c] = fmaf(qv[r].y, kv[c].y, dp[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) dp[r][c] = fmaf(qv[r].z, kv[c].z, dp[r][c]);
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) dp[r][c] = fmaf(qv[r].w, kv[c].w, dp[r][c]);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const float* __restrict__ Q, const float* __restrict__ K,
+                                                                       const float* __restrict__ V,
+                                                                       const float* __restrict__ mask,
+                                                                       const float* __restrict__ d_out,
+                                                                       const float* __restrict__ d_attn, int H, int Nq, int Nk,
+                                                                       float scale, float* __restrict__ dQ,
+                                                                       float* __restrict__ dK, float* __restrict__ dV) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int D4 = D / 4, SW = D4 >= 8 ? 7 : D4 - 1;
+  constexpr int NV = D / 16;                          // 16-byte column pieces of a thread's dK / dV tile
+  constexpr int RPT = D == 64 ? 6 : 3;                // phase D: rows per thread,
+  constexpr int RQ = TQ / RPT;                        //   row classes (a thread's rows are rq, rq + RQ, ...)
+  constexpr int SLOTS = TFT_THREADS / (D4 * RQ);      //   key slices
+  static_assert((SLOTS - 1) * TQ * D <= TQ * TQ_KEYS, "the partial sums of dQ must fit the buffer of P");
+  const int nk4 = (Nk + 3) & ~3;
+  const size_t tile = (size_t)nk4 * D;
+  float* Vt = smem;
+  float* Kt = Vt + tile;                              // two tiles
+  float* Qs = Kt + 2 * tile;                          // two (24, D) blocks
+  float* Gs = Qs + 2 * TQ * D;                        // two (24, D) blocks of the output gradient
+  float* Ps = Gs + 2 * TQ * D;                        // (24, 192) probabilities; later the partial sums of dQ
+  float* Ss = Ps + TQ * TQ_KEYS;                      // (24, 192) dS
+  float* ex = Ss + TQ * TQ_KEYS;                      // [max | sum | dot][2 key halves][24 rows]
+  const int b = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int tiles = (Nq + TQ - 1) / TQ, iters = H * tiles;
+  const float inv_h = 1.f / (float)H;
+
+  // what iteration `it` = (head, row tile) reads; one commit group per call, empty beyond the last iteration
+  auto load_iter = [&](int it) {
+    if (it < iters) {
+      const int h = it / tiles, q0 = (it - h * tiles) * TQ, rows = min(TQ, Nq - q0);
+      rows24_async<D>(Qs + (it & 1) * TQ * D, Q + (((int64_t)b * H + h) * Nq + q0) * D, rows, tid);
+      rows24_async<D>(Gs + (it & 1) * TQ * D, d_out + ((int64_t)b * Nq + q0) * D, rows, tid);
+      if (q0 == 0) tile_rows_async_swz<D>(Kt + (h & 1) * tile, K + ((int64_t)b * H + h) * Nk * D, Nk, tid);
+      if (it == 0) tile_rows_async_swz<D>(Vt, V + (int64_t)b * Nk * D, Nk, tid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_iter(0);
+  // phase D reads K four rows at a time: the rows between Nk and nk4 are never copied, they must be zero
+  for (int idx = tid; idx < (nk4 - Nk) * D; idx += TFT_THREADS) {
+    Kt[(size_t)Nk * D + idx] = 0.f;
+    Kt[tile + (size_t)Nk * D + idx] = 0.f;
+  }
+
+  const int rg = w & 3, khalf = w >> 2;               // phases A, B: rows rg*6 .. +5, keys khalf*96 + lane + 32c
+  const int kg = tid >> 2, cg = tid & 3;              // phase C: keys kg + 64c, columns cg*(D/4) .. +D/4-1
+  const int c4 = tid % D4, rq = (tid / D4) % RQ, ks = tid / (D4 * RQ);   // phase D
+  const int n4 = nk4 / 4, per4 = (n4 + SLOTS - 1) / SLOTS;
+  const int jq0 = ks * per4, jq1 = min(n4, jq0 + per4);
+
+  float dk[TQ_C][NV * 4], dv[TQ_C][NV * 4];
+#pragma unroll
+  for (int c = 0; c < TQ_C; ++c)
+#pragma unroll
+    for (int x = 0; x < NV * 4; ++x) dk[c][x] = dv[c][x] = 0.f;
+  float dp[TQ_R][TQ_C];
+  unsigned mbits = 0, dead = 0;
+
+  for (int it = 0; it < iters; ++it) {
+    const int h = it / tiles, t = it - h * tiles, q0 = t * TQ, rows = min(TQ, Nq - q0);
+    const bool fresh = tiles > 1 || h == 0;           // new rows: mask bits and dP have to be formed
+    load_iter(it + 1);                                // into the buffers iteration it - 1 read (it ended with a barrier)
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();                                  // this iteration's tiles visible; everyone is past the previous one
+    const float* Kh = Kt + (h & 1) * tile;
+    const float* Qh = Qs + (it & 1) * TQ * D;
+    const float* Gh = Gs + (it & 1) * TQ * D;
+
+    // ---- A: scores and dP
+    float da[TQ_R][TQ_C];
+    if (fresh) {
+      float mv[TQ_R][TQ_C];
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) {
+          const int i = min(rg * TQ_R + r, rows - 1), j = min(khalf * (32 * TQ_C) + lane + 32 * c, Nk - 1);
+          mv[r][c] = mask != nullptr ? __ldg(mask + (int64_t)(q0 + i) * Nk + j) : 0.f;
+          da[r][c] = d_attn != nullptr ? __ldg(d_attn + ((int64_t)b * Nq + q0 + i) * Nk + j) : 0.f;
+        }
+      mbits = dead = 0;
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) {
+          const int i = rg * TQ_R + r, j = khalf * (32 * TQ_C) + lane + 32 * c;
+          if (j >= Nk) dead |= 1u << (r * TQ_C + c);
+          else if (i < rows && mv[r][c] == 1.0f) mbits |= 1u << (r * TQ_C + c);
+          if (i >= rows || j >= Nk) da[r][c] = 0.f;
+          dp[r][c] = 0.f;
+        }
+    }
+    float s[TQ_R][TQ_C];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) s[r][c] = 0.f;
+    {
+      const float* krow[TQ_C];
+      const float* vrow[TQ_C];
+      int ksw[TQ_C];
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const int j = min(khalf * (32 * TQ_C) + lane + 32 * c, Nk - 1);
+        krow[c] = Kh + (size_t)j * D;
+        vrow[c] = Vt + (size_t)j * D;
+        ksw[c] = j & SW;
+      }
+      if (fresh) {
+        tft_bwd_scores<D, true>(krow, vrow, ksw, Qh + rg * TQ_R * D, Gh + rg * TQ_R * D, s, dp);
+#pragma unroll
+        for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+          for (int c = 0; c < TQ_C; ++c) dp[r][c] = (dp[r][c] + da[r][c]) * inv_h;   // both head-mean terms (:797-812)
+      } else {
+        tft_bwd_scores<D, false>(krow, vrow, ksw, Qh + rg * TQ_R * D, Gh + rg * TQ_R * D, s, dp);
+      }
+    }
+
+    // ---- B: softmax and its backward
+    float hm[TQ_R];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const unsigned bit = 1u << (r * TQ_C + c);
+        s[r][c] = (mbits & bit) ? MCA_MASKED_LOGIT : s[r][c] * scale;
+        if (!(dead & bit)) m = fmaxf(m, s[r][c]);
+      }
+      hm[r] = warp_max(m);
+    }
+    if (lane < TQ_R) {
+      float v = hm[0];
+#pragma unroll
+      for (int r = 1; r < TQ_R; ++r) v = lane == r ? hm[r] : v;
+      ex[khalf * TQ + rg * TQ_R + lane] = v;
+    }
+    __syncthreads();
+    float hs[TQ_R], hd[TQ_R];
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      const float m = fmaxf(ex[rg * TQ_R + r], ex[TQ + rg * TQ_R + r]);
+      float sum = 0.f, dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        s[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : expf(s[r][c] - m);
+        sum += s[r][c];
+        dot = fmaf(s[r][c], dp[r][c], dot);
+      }
+      hs[r] = warp_sum(sum);
+      hd[r] = warp_sum(dot);
+    }
+    if (lane < TQ_R) {
+      float v = hs[0], u = hd[0];
+#pragma unroll
+      for (int r = 1; r < TQ_R; ++r) {
+        v = lane == r ? hs[r] : v;
+        u = lane == r ? hd[r] : u;
+      }
+      ex[2 * TQ + khalf * TQ + rg * TQ_R + lane] = v;
+      ex[4 * TQ + khalf * TQ + rg * TQ_R + lane] = u;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r) {
+      const int i = rg * TQ_R + r;
+      const float inv = 1.f / (ex[2 * TQ + i] + ex[3 * TQ + i]);
+      const float dot = (ex[4 * TQ + i] + ex[5 * TQ + i]) * inv;      // sum_j P dP of the row
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const int j = khalf * (32 * TQ_C) + lane + 32 * c;
+        const float pj = s[r][c] * inv;
+        Ps[i * TQ_KEYS + j] = pj;
+        Ss[i * TQ_KEYS + j] = pj * (dp[r][c] - dot) * scale;          // softmax backward, then the 1/sqrt(d) (:822-831)
+      }
+    }
+    __syncthreads();                                  // P and dS complete
+
+    // ---- C: dK_h += dS^T Q_h, dV += P^T dO
+#pragma unroll 2
+    for (int r = 0; r < TQ; ++r) {
+      float pv[TQ_C], sv[TQ_C];
+      float4 qv[NV], gv[NV];
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
+        sv[c] = Ss[r * TQ_KEYS + kg + 64 * c];
+      }
+#pragma unroll
+      for (int x = 0; x < NV; ++x) {
+        qv[x] = *reinterpret_cast<const float4*>(Qh + r * D + cg * (D / 4) + 4 * x);
+        gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + cg * (D / 4) + 4 * x);
+      }
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c)
+#pragma unroll
+        for (int x = 0; x < NV; ++x) {
+          dk[c][4 * x + 0] = fmaf(sv[c], qv[x].x, dk[c][4 * x + 0]);
+          dk[c][4 * x + 1] = fmaf(sv[c], qv[x].y, dk[c][4 * x + 1]);
+          dk[c][4 * x + 2] = fmaf(sv[c], qv[x].z, dk[c][4 * x + 2]);
+          dk[c][4 * x + 3] = fmaf(sv[c], qv[x].w, dk[c][4 * x + 3]);
+          dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
+          dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
+          dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
+          dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
+        }
+    }
+
+    // ---- D: dQ = dS K_h over this thread's slice of the keys
+    float o[RPT][4];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.f;
+    for (int jq = jq0; jq < jq1; ++jq) {
+      const int j = 4 * jq;
+      float4 kv[4], sv[RPT];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) kv[u] = *reinterpret_cast<const float4*>(Kh + (size_t)(j + u) * D + ((c4 ^ ((j + u) & SW)) << 2));
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) sv[r] = *reinterpret_cast<const float4*>(Ss + (rq + RQ * r) * TQ_KEYS + j);
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        o[r][0] = fmaf(sv[r].x, kv[0].x, o[r][0]); o[r][1] = fmaf(sv[r].x, kv[0].y, o[r][1]);
+        o[r][2] = fmaf(sv[r].x, kv[0].z, o[r][2]); o[r][3] = fmaf(sv[r].x, kv[0].w, o[r][3]);
+      }
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        o[r][0] = fmaf(sv[r].y, kv[1].x, o[r][0]); o[r][1] = fmaf(sv[r].y, kv[1].y, o[r][1]);
+        o[r][2] = fmaf(sv[r].y, kv[1].z, o[r][2]); o[r][3] = fmaf(sv[r].y, kv[1].w, o[r][3]);
+      }
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        o[r][0] = fmaf(sv[r].z, kv[2].x, o[r][0]); o[r][1] = fmaf(sv[r].z, kv[2].y, o[r][1]);
+        o[r][2] = fmaf(sv[r].z, kv[2].z, o[r][2]); o[r][3] = fmaf(sv[r].z, kv[2].w, o[r][3]);
+      }
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        o[r][0] = fmaf(sv[r].w, kv[3].x, o[r][0]); o[r][1] = fmaf(sv[r].w, kv[3].y, o[r][1]);
+        o[r][2] = fmaf(sv[r].w, kv[3].z, o[r][2]); o[r][3] = fmaf(sv[r].w, kv[3].w, o[r][3]);
+      }
+    }
+    __syncthreads();                                  // nobody reads P any more: its buffer takes the partial sums
+    if (ks > 0) {
+#pragma unroll
+      for (int r = 0; r < RPT; ++r)
+        *reinterpret_cast<float4*>(Ps + (size_t)(ks - 1) * TQ * D + (rq + RQ * r) * D + c4 * 4) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+    }
+    __syncthreads();
+    if (ks == 0) {
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const int i = rq + RQ * r;
+        float4 a = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+#pragma unroll
+        for (int s2 = 0; s2 < SLOTS - 1; ++s2) {
+          const float4 p4 = *reinterpret_cast<const float4*>(Ps + (size_t)s2 * TQ * D + i * D + c4 * 4);
+          a.x += p4.x; a.y += p4.y; a.z += p4.z; a.w += p4.w;
+        }
+        if (i < rows) *reinterpret_cast<float4*>(dQ + (((int64_t)b * H + h) * Nq + q0 + i) * D + c4 * 4) = a;
+      }
+    }
+    if (t == tiles - 1) {                             // the head is finished: its dK leaves the registers
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) {
+        const int j = kg + 64 * c;
+#pragma unroll
+        for (int x = 0; x < NV; ++x) {
+          if (j < Nk)
+            *reinterpret_cast<float4*>(dK + (((int64_t)b * H + h) * Nk + j) * D + cg * (D / 4) + 4 * x) =
+                make_float4(dk[c][4 * x], dk[c][4 * x + 1], dk[c][4 * x + 2], dk[c][4 * x + 3]);
+          dk[c][4 * x] = dk[c][4 * x + 1] = dk[c][4 * x + 2] = dk[c][4 * x + 3] = 0.f;
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int c = 0; c < TQ_C; ++c) {
+    const int j = kg + 64 * c;
+    if (j < Nk) {
+#pragma unroll
+      for (int x = 0; x < NV; ++x)
+        *reinterpret_cast<float4*>(dV + ((int64_t)b * Nk + j) * D + cg * (D / 4) + 4 * x) =
+            make_float4(dv[c][4 * x] * inv_h, dv[c][4 * x + 1] * inv_h, dv[c][4 * x + 2] * inv_h, dv[c][4 * x + 3] * inv_h);
+    }
+  }
+}
+
 }  // namespace
 
 int mca_tft_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
@@ -487,6 +866,20 @@ int mca_tft_attention_backward_f32(const float* q, const float* k, const float* 
   if (B <= 0 || H <= 0 || Nq <= 0 || Nk <= 0 || d <= 0) return ERROR_PARAM_OUT_OF_RANGE;
   if (d % 4 != 0 || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  // the tiled kernel where the shape fits it, else the generic one
+  const auto aligned = [](const void* p_) { return (reinterpret_cast<uintptr_t>(p_) & 15) == 0; };
+  if ((d == 16 || d == 32 || d == 64) && Nk <= TQ_KEYS && aligned(q) && aligned(d_out) && aligned(dq) && aligned(dk) && aligned(dv)) {
+    const size_t nk4 = ((size_t)Nk + 3) & ~(size_t)3;
+    const size_t smem_t = sizeof(float) * (3 * nk4 * d + 4 * (size_t)TQ * d + 2 * (size_t)TQ * TQ_KEYS + 6 * TQ);
+    const float sc = 1.0f / sqrtf((float)d);
+    cudaStream_t st = (cudaStream_t)stream;
+#define MCA_TFT_BWD_TILED(D_)                                                                                                 \
+    MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+    tft_bwd_tiled_kernel<D_><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv);
+    if (d == 64) { MCA_TFT_BWD_TILED(64) } else if (d == 32) { MCA_TFT_BWD_TILED(32) } else { MCA_TFT_BWD_TILED(16) }
+#undef MCA_TFT_BWD_TILED
+    return mca_launch_status();
+  }
   const size_t smem = sizeof(float) * (2 * (size_t)Nk * (d + 4) + 2 * (size_t)Nk * d + 2 * (size_t)TFT_ROWS * Nk +
                                        2 * (size_t)TFT_ROWS * d);
   if (smem > 227 * 1024) return ERROR_ATTN_UNSUPPORTED_SHAPE;

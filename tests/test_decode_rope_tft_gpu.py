@@ -157,7 +157,8 @@ def test_rope_forward_backward(cuda, B, T, H, D):
 
 
 @pytest.mark.parametrize("B,H,Nh,Nf,d,self_attn", [(4, 4, 8, 4, 16, True), (256, 4, 168, 24, 64, True),
-                                                    (16, 4, 168, 24, 64, False), (3, 2, 90, 30, 32, True)])
+                                                    (16, 4, 168, 24, 64, False), (3, 2, 90, 30, 32, True),
+                                                    (2, 3, 23, 7, 32, False), (2, 2, 200, 20, 16, True)])
 def test_tft_interpretable_attention(cuda, B, H, Nh, Nf, d, self_attn):
     """BASELINE config 4: shared V, per-head Q/K, head-means of P and of P V
     (MultiHeadAttentionInterpLayer.cs:728-759); Nq = num_future (one bottom) or Nq = Nk (four bottoms)."""
@@ -183,7 +184,11 @@ def test_tft_interpretable_attention(cuda, B, H, Nh, Nf, d, self_attn):
 
 @pytest.mark.parametrize("B,H,Nh,Nf,d,self_attn,with_attn_grad", [
     (3, 4, 8, 4, 16, True, True), (64, 4, 168, 24, 64, True, True), (8, 4, 168, 24, 64, False, False),
-    (5, 3, 21, 7, 32, True, False)])
+    (5, 3, 21, 7, 32, True, False),
+    # ragged shapes of the tiled kernel: Nk not a multiple of four, a last row tile of 6 and of 23 rows
+    (2, 3, 23, 7, 32, False, True), (2, 4, 150, 41, 64, False, True), (3, 2, 150, 41, 16, True, False),
+    # beyond the tiled kernel (Nk > 192, head size 24): the generic kernel
+    (2, 2, 200, 20, 16, True, True), (2, 2, 30, 10, 24, False, True)])
 def test_tft_interpretable_attention_backward(cuda, B, H, Nh, Nf, d, self_attn, with_attn_grad):
     """Gradients of the TFT attention block w.r.t. Q, K and the shared V, from the gradients of both
     outputs (MultiHeadAttentionInterpLayer.cs:780-859), against the fp64 oracle."""
