@@ -1098,7 +1098,8 @@ def run_profile_case(case):
     launches (single-pass metrics only); `bwd-small` = bf16 backward at the prefill-small shape;
     `decode-small` = config-3 shape, 16 sequences of 4096 keys; `gemv-small` = the decode projections at
     dim 4096 for 1 and 8 sequences plus the feed-forward half and the classifier for one (also prints their
-    CUDA-event bandwidth); `norm-small` = the LayerNorm / RMSNorm layer kernels on a 268 MB tensor;
+    CUDA-event bandwidth); `proj-batch` = the same projections for 16 and 64 sequences, tensor-core kernel and
+    streaming passes side by side; `norm-small` = the LayerNorm / RMSNorm layer kernels on a 268 MB tensor;
     `llama-step` = the whole decode step of an 8-layer llama2-7B-shaped model, eager and from a CUDA graph
     (a timing case, about 15 GB on the device: not for ncu); `tft`, `train`, `sweep`, `backward` = the N = 1 legs of
     the benchmark on their own."""
@@ -1161,6 +1162,59 @@ def run_profile_case(case):
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / 20
             res[f"{name}_B1"] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+        print(json.dumps(res))
+        return
+    if case == "proj-batch":
+        # decode projections of a 7B-shaped layer for 16 and 64 sequences: the tensor-core kernel against the streaming
+        # passes it replaces; every call takes the next of several weight sets, so no weight byte is found in L2
+        dim, hidden, vocab = DEC_HEADS * DEC_HS, 11008, 32000
+        res = {"case": case, "peak_GBps": measured_peaks()["hbm_gbs"]}
+        rms = torch.ones(dim, device=dev)
+        for wname, wdt, esz in (("fp32", torch.float32, 4), ("bf16", torch.bfloat16, 2)):
+            bf = int(wdt == torch.bfloat16)
+            sets = 3
+            mk = lambda r_, c_: [(torch.randn(r_, c_, device=dev) * 0.02).to(wdt) for _ in range(sets)]
+            wq, wk, wv, wo = mk(dim, dim), mk(dim, dim), mk(dim, dim), mk(dim, dim)
+            w1, w3, w2, wc = mk(hidden, dim), mk(hidden, dim), mk(dim, hidden), mk(vocab, dim)
+            for Bn in (16, 64):
+                x = torch.randn(Bn, dim, device=dev)
+                qo, ko, vo = (torch.empty(Bn, dim, device=dev) for _ in range(3))
+                hbuf, logits = torch.empty(Bn, hidden, device=dev), torch.empty(Bn, vocab, device=dev)
+                calls = {
+                    "qkv": (lambda i: lib.mca_decode_qkv_rmsnorm(x.data_ptr(), rms.data_ptr(), 1e-5, wq[i].data_ptr(), wk[i].data_ptr(),
+                                                                 wv[i].data_ptr(), bf, Bn, dim, dim, qo.data_ptr(), ko.data_ptr(),
+                                                                 vo.data_ptr(), None), 3 * dim * dim * esz),
+                    "out": (lambda i: lib.mca_decode_out_proj(qo.data_ptr(), wo[i].data_ptr(), bf, Bn, dim, x.data_ptr(), None), dim * dim * esz),
+                    "ffn": (lambda i: lib.mca_decode_ffn(rms.data_ptr(), 1e-5, w1[i].data_ptr(), w2[i].data_ptr(), w3[i].data_ptr(), bf, Bn, dim,
+                                                         hidden, hbuf.data_ptr(), x.data_ptr(), None), 3 * hidden * dim * esz),
+                    "logits": (lambda i: lib.mca_decode_logits(x.data_ptr(), rms.data_ptr(), 1e-5, wc[i].data_ptr(), bf, Bn, dim, vocab,
+                                                               logits.data_ptr(), None), vocab * dim * esz),
+                }
+                for name, (fn, nbytes) in calls.items():
+                    entry = {}
+                    for mode, on in (("tensor_core", 1), ("streaming", 0)):
+                        lib.mca_proj_tc_enable(on)
+                        for i in range(3):
+                            x.normal_()
+                            rc = fn(i % sets)
+                        iters = 9
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        torch.cuda.synchronize()
+                        e0.record()
+                        for i in range(iters):
+                            fn(i % sets)
+                        e1.record()
+                        torch.cuda.synchronize()
+                        ms = e0.elapsed_time(e1) / iters
+                        entry[mode] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+                    lib.mca_proj_tc_enable(1)
+                    entry["frac_of_copy_bandwidth"] = round(entry["tensor_core"]["weight_GBps"] / res["peak_GBps"], 3)
+                    res[f"{wname}_{name}_B{Bn}"] = entry
+            del wq, wk, wv, wo, w1, w3, w2, wc
+        import ctypes as C
+        st = (C.c_int * 4)()
+        lib.mca_proj_tc_status(st)
+        res["status"] = list(st)
         print(json.dumps(res))
         return
     if case == "norm-small":
@@ -1314,7 +1368,7 @@ def main():
                     help="one GPU: skip the other configurations (train, sweep, backward, decode variants, tft)")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "norm-small", "llama-step",
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "norm-small", "llama-step",
                                                      "tft", "train", "sweep", "backward"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()

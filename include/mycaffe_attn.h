@@ -431,6 +431,16 @@ typedef struct McaLlamaState {
   float* workspace;
   int64_t workspace_floats;
 } McaLlamaState;
+/* Decode projections for 9 to 64 sequences run one pass over the weights on the tensor cores (fp32 weights as fp16
+ * hi/lo halves, three MMAs; bf16 weights directly) instead of one streaming pass per eight sequences; same results to
+ * fp32 round-off.  No counterpart in the reference (it decodes one sequence with cublasSgemv,
+ * CudaExtension.llm32.llama2/Files/primitives.cu:322-340).  The kernel keeps its activation pieces and partial sums
+ * in arrays that are part of the library image, so two such products must not overlap on one device.
+ * mca_proj_tc_enable(0) switches it off (the streaming kernel then serves every batch); returns the previous setting.
+ * mca_proj_tc_status: the kernel's status words ([0] != 0: a bounded wait gave up; reading clears them). */
+MCA_API int mca_proj_tc_enable(int on);
+MCA_API int mca_proj_tc_status(int* status4);
+
 MCA_API int64_t mca_llama_workspace_floats(const McaLlamaConfig* cfg, int B, int max_len);
 MCA_API int mca_llama_forward(const McaLlamaConfig* cfg, const McaLlamaWeights* weights, const McaLlamaState* state,
                               const int* tokens, const int* pos, int B, int max_len, float* logits, void* stream);

@@ -71,6 +71,8 @@ SIGNATURES = {
                                   _vp, _vp]),
     "mca_decode_head_size_supported": (_i, [_i]),
     "mca_decode_status": (_i, [C.POINTER(_i)]),
+    "mca_proj_tc_enable": (_i, [_i]),
+    "mca_proj_tc_status": (_i, [C.POINTER(_i)]),
     "mca_decode_exchange": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mca_decode_qkv_rmsnorm": (_i, [_vp, _vp, C.c_float, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mca_decode_out_proj": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),

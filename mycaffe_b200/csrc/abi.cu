@@ -38,6 +38,8 @@ struct AttnHandle {
   float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr, *delta = nullptr, *lse = nullptr;
   void* split_ws = nullptr;    // fp16 halves of q, k, v for the split-operand tensor-core forward of fp32 handles
   int64_t split_ws_bytes = 0;
+  float* mask_ws = nullptr;    // fp32 copies for a bf16 handle that is given a (T,T) or batch mask (allocated on first use)
+  size_t mask_ws_floats = 0;
   int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
   // state of the last forward, consumed by backward
   bool have_fwd = false;
@@ -48,8 +50,9 @@ struct AttnHandle {
   bool status_pending = false;  // a tensor-core launch was made in asynchronous mode and its status words are unread
   void release() {
     cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
-    cudaFree(split_ws);
+    cudaFree(split_ws); cudaFree(mask_ws);
     split_ws = nullptr; split_ws_bytes = 0;
+    mask_ws = nullptr; mask_ws_floats = 0;
     row_max = row_sum = y_copy = delta = lse = nullptr;
     causal_flag = nullptr;
     configured = have_fwd = false;
@@ -407,6 +410,19 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   return 0;
 }
 
+// fp32 room for a bf16 handle whose mask the tensor-core kernels do not apply: q, k, v, y (and, for training handles,
+// the three gradients and dY), at the configured block size.
+long ensure_mask_ws(AttnHandle& a) {
+  const size_t n = (size_t)a.B * a.H * a.block * a.D;
+  const size_t need = (a.training ? 8 : 4) * n;
+  if (a.mask_ws != nullptr && a.mask_ws_floats >= need) return 0;
+  cudaFree(a.mask_ws);
+  a.mask_ws = nullptr; a.mask_ws_floats = 0;
+  if (cudaMalloc(&a.mask_ws, need * sizeof(float)) != cudaSuccess) { cudaGetLastError(); a.mask_ws = nullptr; return ERROR_MEMORY_OUT; }
+  a.mask_ws_floats = need;
+  return 0;
+}
+
 // Read the status words a tensor-core kernel writes when one of its bounded waits gives up.  Blocking: in
 // synchronous mode it follows every tensor-core launch; in asynchronous mode the words are read for every
 // attention handle at the next call that synchronises (CUDA_FN_SYNCHRONIZEDEVICE).
@@ -504,8 +520,25 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     kk = static_cast<char*>(kk) + C * esz;
     v = static_cast<char*>(v) + 2 * C * esz;
   }
+  if (bf16 && (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH)) {
+    // The tensor-core kernels apply a causal mask or none.  A bf16 handle that is given any other mask runs the exact
+    // fp32 kernels on fp32 copies of its tensors (same mask semantics: -1e29 logits, a uniform fully-masked row).
+    if ((e = ensure_mask_ws(a))) return e;
+    float* w = a.mask_ws;
+    float *qf = w, *kf = packed ? w + C : w + n, *vf = packed ? w + 2 * C : w + 2 * n, *yf = w + 3 * n;
+    if (packed) e = mca_convert_bf16_to_f32(q, w, 3 * n, 0);   // pl[3..5] name one (B,T,3C) tensor
+    else if (!(e = mca_convert_bf16_to_f32(q, qf, n, 0)) && !(e = mca_convert_bf16_to_f32(kk, kf, n, 0)))
+      e = mca_convert_bf16_to_f32(v, vf, n, 0);
+    if (e) return e;
+    const bool save = a.training && T == a.block;
+    e = mca_sdpa_forward_f32_layout(qf, kf, vf, mask, mode, a.causal_flag, a.B, a.H, T, a.D, yf, save ? a.row_max : nullptr,
+                                    save ? a.row_sum : nullptr, save ? a.y_copy : nullptr, layout, 0);
+    if (e) return e;
+    if ((e = mca_convert_f32_to_bf16(yf, y, n, 0))) return e;
+    if (save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
+    return 0;
+  }
   if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH || tf32_exact) {
-    if (bf16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
     // a general mask (or training) with tf32 requested: the exact fp32 kernel handles it
     const bool save = a.training && T == a.block;
     e = mca_sdpa_forward_f32_layout((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
@@ -552,6 +585,27 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if (packed) {
       kk = static_cast<char*>(kk) + C * 2; dk = static_cast<char*>(dk) + C * 2;
       v = static_cast<char*>(v) + 2 * C * 2; dv = static_cast<char*>(dv) + 2 * C * 2;
+    }
+    if (a.fwd_mask_mode == MCA_MASK_TT || a.fwd_mask_mode == MCA_MASK_BATCH) {
+      // the forward ran the exact fp32 kernels on fp32 copies (a mask the tensor-core kernels do not apply): so does
+      // this; the mask is looked up again by the handle the forward was given
+      const float* mask = nullptr;
+      int mode = a.fwd_mask_mode;
+      if ((e = resolve_mask(k, a, a.fwd_mask_handle, a.fwd_batch_mask, T, &mask, &mode, false))) return e;
+      if ((e = ensure_mask_ws(a))) return e;
+      float* w = a.mask_ws;
+      float *qf = w, *kf = packed ? w + C : w + n, *vf = packed ? w + 2 * C : w + 2 * n;
+      float *gq = w + 4 * n, *gk = packed ? gq + C : gq + n, *gv = packed ? gq + 2 * C : gq + 2 * n, *dyf = w + 7 * n;
+      if (packed) e = mca_convert_bf16_to_f32(q, w, 3 * n, 0);
+      else if (!(e = mca_convert_bf16_to_f32(q, qf, n, 0)) && !(e = mca_convert_bf16_to_f32(kk, kf, n, 0)))
+        e = mca_convert_bf16_to_f32(v, vf, n, 0);
+      if (e || (e = mca_convert_bf16_to_f32(dy, dyf, n, 0))) return e;
+      e = mca_sdpa_backward_f32_layout(qf, kf, vf, dyf, a.y_copy, mask, a.fwd_mask_mode, a.causal_flag, a.row_max, a.row_sum,
+                                       a.delta, a.B, a.H, T, a.D, gq, gk, gv, layout, 0);
+      if (e) return e;
+      if (packed) return mca_convert_f32_to_bf16(gq, dq, 3 * n, 0);
+      if ((e = mca_convert_f32_to_bf16(gq, dq, n, 0)) || (e = mca_convert_f32_to_bf16(gk, dk, n, 0))) return e;
+      return mca_convert_f32_to_bf16(gv, dv, n, 0);
     }
     e = mca_sdpa_backward_tc_layout(q, kk, v, a.y_copy, dy, a.lse, a.delta, MCA_DTYPE_BF16,
                                     a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, dq, dk, dv, a.causal_flag + 1,
@@ -744,6 +798,23 @@ long decode_step(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   return 0;
 }
 
+// Batches above eight sequences run the projections on the tensor cores; in synchronous mode a bounded wait that gave
+// up inside that kernel is reported here instead of returning success.
+long proj_result(Kernel* k, long e, long B) {
+  if (e || k->async || B <= 8) return e;
+  cudaError_t ce = cudaStreamSynchronize(0);
+  if (ce != cudaSuccess) return ce;
+  int st[4] = {0, 0, 0, 0};
+  if ((e = mca_proj_tc_status(st))) return e;
+  if (st[0] != 0) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "projection kernel: status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
+    k->last_detail = buf;
+    return ERROR_ATTN_KERNEL_TIMEOUT;
+  }
+  return 0;
+}
+
 long decode_qkv(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
   long e;
   if ((e = verify_in(lInput, pf, 1, 1))) return e;
@@ -759,7 +830,7 @@ long decode_qkv(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* p
   if (!wq || !wk || !wv) return ERROR_MEMORY_NOT_FOUND;
   if (wq->bf16 != wk->bf16 || wq->bf16 != wv->bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
   if (wq->count < (int64_t)dim * dim || wk->count < (int64_t)kv_dim * dim || wv->count < (int64_t)kv_dim * dim) return ERROR_MEMORY_TOO_SMALL;
-  return mca_decode_qkv_rmsnorm(x, rw, pf[0], wq->ptr, wk->ptr, wv->ptr, wq->bf16 ? 1 : 0, B, dim, kv_dim, q, kk, v, 0);
+  return proj_result(k, mca_decode_qkv_rmsnorm(x, rw, pf[0], wq->ptr, wk->ptr, wv->ptr, wq->bf16 ? 1 : 0, B, dim, kv_dim, q, kk, v, 0), B);
 }
 
 long decode_out(Kernel* k, long llInput, MCA_LONGLONG* pl) {
@@ -772,7 +843,7 @@ long decode_out(Kernel* k, long llInput, MCA_LONGLONG* pl) {
   MemItem* wo = k->get((long)pl[1]);
   if (!wo) return ERROR_MEMORY_NOT_FOUND;
   if (wo->count < (int64_t)dim * dim) return ERROR_MEMORY_TOO_SMALL;
-  return mca_decode_out_proj(attn, wo->ptr, wo->bf16 ? 1 : 0, B, dim, x, 0);
+  return proj_result(k, mca_decode_out_proj(attn, wo->ptr, wo->bf16 ? 1 : 0, B, dim, x, 0), B);
 }
 
 long decode_ffn(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
@@ -788,7 +859,7 @@ long decode_ffn(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* p
   if (!w1 || !w2 || !w3) return ERROR_MEMORY_NOT_FOUND;
   if (w1->count < hidden * dim || w2->count < hidden * dim || w3->count < hidden * dim) return ERROR_MEMORY_TOO_SMALL;
   if (w1->bf16 != w2->bf16 || w1->bf16 != w3->bf16) return ERROR_MEMORY_MIXED_HALF_TYPES;
-  return mca_decode_ffn(g, pf[0], w1->ptr, w2->ptr, w3->ptr, w1->bf16 ? 1 : 0, (int)B, (int)dim, (int)hidden, h, x, 0);
+  return proj_result(k, mca_decode_ffn(g, pf[0], w1->ptr, w2->ptr, w3->ptr, w1->bf16 ? 1 : 0, (int)B, (int)dim, (int)hidden, h, x, 0), (long)B);
 }
 
 long decode_logits(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl) {
@@ -803,7 +874,7 @@ long decode_logits(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG
   MemItem* wc = k->get((long)pl[2]);
   if (!wc) return ERROR_MEMORY_NOT_FOUND;
   if (wc->count < vocab * dim) return ERROR_MEMORY_TOO_SMALL;
-  return mca_decode_logits(x, g, pf[0], wc->ptr, wc->bf16 ? 1 : 0, (int)B, (int)dim, (int)vocab, out, 0);
+  return proj_result(k, mca_decode_logits(x, g, pf[0], wc->ptr, wc->bf16 ? 1 : 0, (int)B, (int)dim, (int)vocab, out, 0), (long)B);
 }
 
 // Device<T>::CreateLayerNorm / FreeLayerNorm / LayerNormForward / LayerNormBackward, device.h:4123-4195

@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "proj_tc.cuh"
 
 namespace {
 
@@ -330,9 +331,65 @@ int launch_pass(GemvParams p, int b0, cudaStream_t st) {
   return mca_launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, p, b0);
 }
 
+// More than eight sequences: one pass over the weights on the tensor cores (proj_tc.cuh).  Returns -1 when the shape
+// is outside that kernel (the caller then takes the streaming passes).
+template <typename WT>
+int run_proj_tc(const GemvParams& p, cudaStream_t st) {
+  using PL = proj::Plan<WT>;
+  constexpr bool BF = !PL::CONVERT;
+  if (!proj::enabled() || p.B <= 8 || p.B > proj::MAX_B || p.n > proj::MAX_N || p.n % 8 != 0) return -1;
+  const int Bp = (p.B + 15) & ~15;
+  proj::Params q = {};
+  int tiles = 0;
+  for (int m = 0; m < 3; ++m) { q.out[m] = p.out[m]; q.rows[m] = p.rows[m]; }
+  if (p.swiglu) {
+    tiles = mca_ceil_div(p.rows[0], proj::ROWS);
+    q.tile0[0] = 0; q.tile0[1] = q.tile0[2] = q.tile0[3] = tiles;
+  } else {
+    for (int m = 0; m < 3; ++m) {
+      q.tile0[m] = tiles;
+      if (m < p.n_mats) tiles += mca_ceil_div(p.rows[m], proj::ROWS);
+    }
+    q.tile0[3] = tiles;
+  }
+  if (tiles > proj::MAX_TILES) return -1;
+  int dev = 0, sms = 148;
+  MCA_CUDA_TRY(cudaGetDevice(&dev));
+  MCA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  uint16_t* pieces = nullptr;
+  float* xscale = nullptr;
+  MCA_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&pieces), proj::g_x_pieces));
+  MCA_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&xscale), proj::g_x_scale));
+  q.n_mats = p.n_mats; q.B = p.B; q.Bp = Bp; q.n = p.n; q.accumulate = p.accumulate; q.swiglu = p.swiglu;
+  q.tiles = tiles; q.kchunks = mca_ceil_div(p.n, proj::KC);
+  q.slices = proj::pick_slices(tiles, q.kchunks, sms);
+  CUtensorMap mw[3], mx;
+  int e;
+  for (int m = 0; m < 3; ++m) {
+    const int mm = m < p.n_mats ? m : 0;
+    if ((e = proj::make_map_2d(&mw[m], p.w[mm], BF ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                               (int)sizeof(WT), p.rows[mm], p.n, proj::KC, proj::ROWS,
+                               BF ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE)))
+      return e;
+  }
+  if ((e = proj::make_map_2d(&mx, pieces, BF ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                             (int64_t)PL::PIECES * Bp, p.n, proj::KC, Bp, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return e;
+  proj::x_pieces_kernel<BF><<<Bp, 256, 0, st>>>(p.x, p.norm_w, p.eps, p.n, p.B, Bp, pieces, xscale);
+  if ((e = mca_launch_status())) return e;
+  const size_t smem = proj::smem_bytes<WT>();
+  auto kern = proj::proj_tc_kernel<WT>;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int items = tiles * q.slices;
+  kern<<<std::min(items, sms), proj::THREADS, smem, st>>>(mw[0], mw[1], mw[2], mx, q);
+  return mca_launch_status();
+}
+
 template <typename WT>
 int run_gemv(const GemvParams& p, cudaStream_t st) {
-  int e = 0;
+  int e = run_proj_tc<WT>(p, st);
+  if (e >= 0) return e;
+  e = 0;
   const size_t xbytes = sizeof(float) * (size_t)p.n;
   auto fits = [&](int nb, size_t ring) { return nb * xbytes + ring <= GV_SMEM_LIMIT; };
   constexpr size_t RING_512 = ring_bytes<2, 512, 6>(), RING_256 = ring_bytes<2, 256, 6>();
@@ -437,4 +494,24 @@ int mca_decode_logits(const float* x, const float* rms_weight, float eps, const 
   p.out[0] = logits; p.out[1] = p.out[2] = nullptr;
   p.rows[0] = vocab_size; p.rows[1] = p.rows[2] = 0;
   return weights_bf16 ? run_gemv<__nv_bfloat16>(p, (cudaStream_t)stream) : run_gemv<float>(p, (cudaStream_t)stream);
+}
+
+int mca_proj_tc_enable(int on) {
+  const int was = proj::enabled() ? 1 : 0;
+  proj::enabled() = on != 0;
+  return was;
+}
+
+int mca_proj_tc_status(int* status4) {
+  if (!status4) return ERROR_PARAM_NULL;
+  void* sp = nullptr;
+  MCA_CUDA_TRY(cudaGetSymbolAddress(&sp, proj::g_status));
+  MCA_CUDA_TRY(cudaMemcpy(status4, sp, 4 * sizeof(int), cudaMemcpyDeviceToHost));
+  if (status4[0] != 0) {   // a bounded wait gave up: the tickets of that launch may be left half-counted
+    void* tp = nullptr;
+    MCA_CUDA_TRY(cudaGetSymbolAddress(&tp, proj::g_tickets));
+    MCA_CUDA_TRY(cudaMemset(tp, 0, sizeof(unsigned int) * proj::MAX_TILES * proj::EPI_WARPS));
+    MCA_CUDA_TRY(cudaMemset(sp, 0, 4 * sizeof(int)));
+  }
+  return 0;
 }

@@ -518,7 +518,7 @@ __device__ __forceinline__ void tft_bwd_scores(const float* const (&krow)[TQ_C],
                                                const int (&ksw)[TQ_C], const float* __restrict__ qrow,
                                                const float* __restrict__ grow, float (&s)[TQ_R][TQ_C],
                                                float (&dp)[TQ_R][TQ_C]) {
-#pragma unroll
+#pragma unroll 4
   for (int i = 0; i < D / 4; ++i) {
     float4 kv[TQ_C], qv[TQ_R];
 #pragma unroll
@@ -566,7 +566,7 @@ __device__ __forceinline__ void tft_bwd_scores(const float* const (&krow)[TQ_C],
   }
 }
 
-template <int D>
+template <int D, bool ONE>
 __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const float* __restrict__ Q, const float* __restrict__ K,
                                                                        const float* __restrict__ V,
                                                                        const float* __restrict__ mask,
@@ -614,7 +614,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
   }
 
   const int rg = w & 3, khalf = w >> 2;               // phases A, B: rows rg*6 .. +5, keys khalf*96 + lane + 32c
-  const int kg = tid >> 2, cg = tid & 3;              // phase C: keys kg + 64c, columns cg*(D/4) .. +D/4-1
+  const int kg = tid >> 2, cg = tid & 3;              // phase C: keys kg + 64c, 16-byte column pieces cg, cg + 4, ...
   const int c4 = tid % D4, rq = (tid / D4) % RQ, ks = tid / (D4 * RQ);   // phase D
   const int n4 = nk4 / 4, per4 = (n4 + SLOTS - 1) / SLOTS;
   const int jq0 = ks * per4, jq1 = min(n4, jq0 + per4);
@@ -625,6 +625,11 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
 #pragma unroll
     for (int x = 0; x < NV * 4; ++x) dk[c][x] = dv[c][x] = 0.f;
   float dp[TQ_R][TQ_C];
+  float pm[TQ_R][TQ_C];                               // ONE: the sum over the heads of this thread's probabilities
+#pragma unroll
+  for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) pm[r][c] = 0.f;
   unsigned mbits = 0, dead = 0;
 
   for (int it = 0; it < iters; ++it) {
@@ -742,7 +747,8 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
       for (int c = 0; c < TQ_C; ++c) {
         const int j = khalf * (32 * TQ_C) + lane + 32 * c;
         const float pj = s[r][c] * inv;
-        Ps[i * TQ_KEYS + j] = pj;
+        if (ONE) pm[r][c] += pj;
+        else Ps[i * TQ_KEYS + j] = pj;
         Ss[i * TQ_KEYS + j] = pj * (dp[r][c] - dot) * scale;          // softmax backward, then the 1/sqrt(d) (:822-831)
       }
     }
@@ -755,13 +761,13 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
       float4 qv[NV], gv[NV];
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c) {
-        pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
+        if (!ONE) pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
         sv[c] = Ss[r * TQ_KEYS + kg + 64 * c];
       }
 #pragma unroll
       for (int x = 0; x < NV; ++x) {
-        qv[x] = *reinterpret_cast<const float4*>(Qh + r * D + cg * (D / 4) + 4 * x);
-        gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + cg * (D / 4) + 4 * x);
+        qv[x] = *reinterpret_cast<const float4*>(Qh + r * D + 4 * (cg + 4 * x));   // the four lanes of a key: distinct banks
+        if (!ONE) gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + 4 * (cg + 4 * x));
       }
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c)
@@ -771,10 +777,12 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
           dk[c][4 * x + 1] = fmaf(sv[c], qv[x].y, dk[c][4 * x + 1]);
           dk[c][4 * x + 2] = fmaf(sv[c], qv[x].z, dk[c][4 * x + 2]);
           dk[c][4 * x + 3] = fmaf(sv[c], qv[x].w, dk[c][4 * x + 3]);
-          dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
-          dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
-          dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
-          dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
+          if (!ONE) {
+            dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
+            dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
+            dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
+            dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
+          }
         }
     }
 
@@ -837,7 +845,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
 #pragma unroll
         for (int x = 0; x < NV; ++x) {
           if (j < Nk)
-            *reinterpret_cast<float4*>(dK + (((int64_t)b * H + h) * Nk + j) * D + cg * (D / 4) + 4 * x) =
+            *reinterpret_cast<float4*>(dK + (((int64_t)b * H + h) * Nk + j) * D + 4 * (cg + 4 * x)) =
                 make_float4(dk[c][4 * x], dk[c][4 * x + 1], dk[c][4 * x + 2], dk[c][4 * x + 3]);
           dk[c][4 * x] = dk[c][4 * x + 1] = dk[c][4 * x + 2] = dk[c][4 * x + 3] = 0.f;
         }
@@ -845,13 +853,42 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (ONE) {
+    // a single row tile: V's gradient is (sum_h P_h)^T dO, one product for all heads (the rows of dO are still in
+    // the buffer of the last iteration)
+    __syncthreads();                                  // the last partial sums of dQ have been read
+#pragma unroll
+    for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) Ps[(rg * TQ_R + r) * TQ_KEYS + khalf * (32 * TQ_C) + lane + 32 * c] = pm[r][c];
+    __syncthreads();
+    const float* Gh = Gs + ((iters - 1) & 1) * TQ * D;
+#pragma unroll 2
+    for (int r = 0; r < TQ; ++r) {
+      float pv[TQ_C];
+      float4 gv[NV];
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c) pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
+#pragma unroll
+      for (int x = 0; x < NV; ++x) gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + 4 * (cg + 4 * x));
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c)
+#pragma unroll
+        for (int x = 0; x < NV; ++x) {
+          dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
+          dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
+          dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
+          dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
+        }
+    }
+  }
 #pragma unroll
   for (int c = 0; c < TQ_C; ++c) {
     const int j = kg + 64 * c;
     if (j < Nk) {
 #pragma unroll
       for (int x = 0; x < NV; ++x)
-        *reinterpret_cast<float4*>(dV + ((int64_t)b * Nk + j) * D + cg * (D / 4) + 4 * x) =
+        *reinterpret_cast<float4*>(dV + ((int64_t)b * Nk + j) * D + 4 * (cg + 4 * x)) =
             make_float4(dv[c][4 * x] * inv_h, dv[c][4 * x + 1] * inv_h, dv[c][4 * x + 2] * inv_h, dv[c][4 * x + 3] * inv_h);
     }
   }
@@ -874,8 +911,13 @@ int mca_tft_attention_backward_f32(const float* q, const float* k, const float* 
     const float sc = 1.0f / sqrtf((float)d);
     cudaStream_t st = (cudaStream_t)stream;
 #define MCA_TFT_BWD_TILED(D_)                                                                                                 \
-    MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
-    tft_bwd_tiled_kernel<D_><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv);
+    if (Nq <= TQ) {                                                                                                           \
+      MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+      tft_bwd_tiled_kernel<D_, true><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv); \
+    } else {                                                                                                                  \
+      MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+      tft_bwd_tiled_kernel<D_, false><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv); \
+    }
     if (d == 64) { MCA_TFT_BWD_TILED(64) } else if (d == 32) { MCA_TFT_BWD_TILED(32) } else { MCA_TFT_BWD_TILED(16) }
 #undef MCA_TFT_BWD_TILED
     return mca_launch_status();

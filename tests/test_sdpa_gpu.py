@@ -236,7 +236,9 @@ def test_bf16_tensor_core_forward(cuda, T, D, causal):
 
 
 def test_bf16_tensor_core_accepts_causal_mask_handle(cuda):
-    """A (T,T) tril mask passed the reference's way is recognised as causal; another mask is refused."""
+    """A (T,T) tril mask passed the reference's way is recognised as causal and runs the tensor-core kernel; any other
+    mask (general (T,T), batch) runs the exact fp32 kernels on fp32 copies, forward and backward, with the reference's
+    mask semantics (a fully masked row is uniform)."""
     from mycaffe_b200 import CudaDnnError, function_ids as ids
     rng = np.random.default_rng(9)
     B, H, T, D = 2, 2, 256, 64
@@ -245,10 +247,22 @@ def test_bf16_tensor_core_accepts_causal_mask_handle(cuda):
     y = a.forward(q, k, v, oracle.causal_mask(T))
     assert rel_err(y, oracle.sdpa_forward(q, k, v, oracle.causal_mask(T), 1, f64=True)) < BF16_TOL
     a.close()
-    b = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16)
-    with pytest.raises(CudaDnnError) as e:
-        b.forward(q, k, v, np.ones((T, T), np.float32) - np.eye(T, dtype=np.float32))
-    assert e.value.code == ids.ERROR_ATTN_UNSUPPORTED_SHAPE
+    dy = bf16_round(rng.standard_normal(q.shape).astype(np.float32))
+    general = np.ones((T, T), np.float32) - np.eye(T, dtype=np.float32)
+    general[5] = 0.0                                          # one fully masked row
+    keys = (rng.random((B, T)) > 0.3).astype(np.float32)      # batch mask: keys kept per batch item
+    for mask, mode, batch in ((general, 1, False), (keys, 2, True)):
+        b = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16)
+        y = b.forward(q, k, v, mask, batch_mask=batch)
+        assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, mode, f64=True)) < BF16_TOL
+        got = b.backward(dy)
+        for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
+            assert rel_err(g_, r_) < BF16_TOL
+        b.close()
+    b = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16)      # inference handle: forward only
+    y = b.forward(q, k, v, general)
+    assert rel_err(y, oracle.sdpa_forward(q, k, v, general, 1, f64=True)) < BF16_TOL
+    np.testing.assert_allclose(y[:, :, 5], v.mean(axis=2), atol=2e-2)     # the fully masked row is uniform
     b.close()
 
 
