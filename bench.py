@@ -1164,6 +1164,35 @@ def run_profile_case(case):
             res[f"{name}_B1"] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
         print(json.dumps(res))
         return
+    if case == "proj-small":
+        # ncu-sized: the q/k/v projection (three 67 MB fp32 matrices, above L2) and the gated feed-forward pair for 64
+        # sequences, three launches each
+        dim, hidden, Bn = DEC_HEADS * DEC_HS, 11008, 64
+        rms = torch.ones(dim, device=dev)
+        wq, wk, wv = (torch.randn(dim, dim, device=dev) * 0.02 for _ in range(3))
+        w1, w3 = (torch.randn(hidden, dim, device=dev) * 0.02 for _ in range(2))
+        w2 = torch.randn(dim, hidden, device=dev) * 0.02
+        x = torch.randn(Bn, dim, device=dev)
+        qo, ko, vo = (torch.empty(Bn, dim, device=dev) for _ in range(3))
+        hbuf = torch.empty(Bn, hidden, device=dev)
+        res = {"case": case}
+        for name, fn, nbytes in (
+                ("qkv", lambda: lib.mca_decode_qkv_rmsnorm(x.data_ptr(), rms.data_ptr(), 1e-5, wq.data_ptr(), wk.data_ptr(), wv.data_ptr(), 0, Bn,
+                                                           dim, dim, qo.data_ptr(), ko.data_ptr(), vo.data_ptr(), None), 3 * dim * dim * 4),
+                ("ffn", lambda: lib.mca_decode_ffn(rms.data_ptr(), 1e-5, w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), 0, Bn, dim, hidden,
+                                                   hbuf.data_ptr(), x.data_ptr(), None), 3 * hidden * dim * 4)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            rc = fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(2):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 2
+            res[name] = {"rc": rc, "ms": round(ms, 4), "weight_GBps": round(nbytes / ms / 1e6, 1)}
+        print(json.dumps(res))
+        return
     if case == "proj-batch":
         # decode projections of a 7B-shaped layer for 16 and 64 sequences: the tensor-core kernel against the streaming
         # passes it replaces; every call takes the next of several weight sets, so no weight byte is found in L2
@@ -1248,10 +1277,11 @@ def run_profile_case(case):
         print(json.dumps(res))
         return
     if case == "llama-step":
-        # whole-transformer decode step, llama2-7B geometry cut to 8 layers, one sequence at position 2047
+        # whole-transformer decode step, llama2-7B geometry cut to 8 layers, every sequence at position 2047;
+        # 1, 16 and 64 sequences (above eight the projections run on the tensor cores)
         import ctypes as C
         from mycaffe_b200 import llama2 as M
-        cfg = dict(dim=4096, hidden_dim=11008, n_layers=8, n_heads=32, n_kv_heads=32, vocab_size=32000, seq_len=4096)
+        cfg = dict(dim=4096, hidden_dim=11008, n_layers=8, n_heads=32, n_kv_heads=32, vocab_size=32000, seq_len=2048)
         res = {"case": case, "config": cfg}
         for bf16 in (False, True):
             wdt = torch.bfloat16 if bf16 else torch.float32
@@ -1262,49 +1292,66 @@ def run_profile_case(case):
                  "wq": mk(L, dim, dim, dt=wdt), "wk": mk(L, dim, dim, dt=wdt), "wv": mk(L, dim, dim, dt=wdt),
                  "wo": mk(L, dim, dim, dt=wdt), "w1": mk(L, hidden, dim, dt=wdt), "w2": mk(L, dim, hidden, dt=wdt),
                  "w3": mk(L, hidden, dim, dt=wdt), "wcls": mk(vocab, dim, dt=wdt)}
-            kc, vc = (torch.randn(L, 1, S, dim, device=dev).to(wdt) for _ in range(2))
             fr, fi = np.empty((S, 64), np.float32), np.empty((S, 64), np.float32)
             fp = C.POINTER(C.c_float)
             lib.mca_rope_tables_host(S, 128, 10000.0, fr.ctypes.data_as(fp), fi.ctypes.data_as(fp))
             frd, fid = torch.from_numpy(fr).to(dev), torch.from_numpy(fi).to(dev)
             cfg_c = M.McaLlamaConfig(**cfg)
-            need = lib.mca_llama_workspace_floats(C.byref(cfg_c), 1, S)
-            ws_, logits = torch.empty(need, device=dev), torch.empty(1, vocab, device=dev)
-            tok = torch.zeros(1, dtype=torch.int32, device=dev)
-            pos = torch.full((1,), 2047, dtype=torch.int32, device=dev)
             names = ("token_embedding_table", "rms_att_weight", "rms_ffn_weight", "rms_final_weight", "wq", "wk", "wv", "wo",
                      "w1", "w2", "w3", "wcls")
             w_c = M.McaLlamaWeights(*[w[n].data_ptr() for n in names], int(bf16))
-            s_c = M.McaLlamaState(kc.data_ptr(), vc.data_ptr(), int(bf16), frd.data_ptr(), fid.data_ptr(), ws_.data_ptr(), need)
-            def step(stream=None):
-                st = stream if stream is not None else torch.cuda.current_stream()
-                return lib.mca_llama_forward(C.byref(cfg_c), C.byref(w_c), C.byref(s_c), tok.data_ptr(), pos.data_ptr(), 1, 2048,
-                                             logits.data_ptr(), st.cuda_stream)
-            for _ in range(3):
-                rc = step()
-            side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                graph.capture_begin()
-                step(side)
-                graph.capture_end()
-            torch.cuda.current_stream().wait_stream(side)
-            out = {}
-            for name, fn in (("eager", step), ("graph", graph.replay)):
-                fn()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                e0.record()
-                for _ in range(10):
-                    fn()
-                e1.record()
-                torch.cuda.synchronize()
-                out[name + "_ms"] = round(e0.elapsed_time(e1) / 10, 4)
             sz = 2 if bf16 else 4
-            nbytes = (L * (4 * dim * dim + 3 * dim * hidden) + vocab * dim) * sz + L * 2 * 2048 * dim * sz
-            out.update({"rc": rc, "bytes": nbytes, "GBps_graph": round(nbytes / out["graph_ms"] / 1e6, 1)})
-            res["bf16" if bf16 else "f32"] = out
-            del w, kc, vc, graph
+            for Bn in (1, 16, 64):
+                kc, vc = (torch.empty(L, Bn, S, dim, device=dev, dtype=wdt).normal_() for _ in range(2))
+                need = lib.mca_llama_workspace_floats(C.byref(cfg_c), Bn, S)
+                ws_, logits = torch.empty(need, device=dev), torch.empty(Bn, vocab, device=dev)
+                tok = torch.zeros(Bn, dtype=torch.int32, device=dev)
+                pos = torch.full((Bn,), 2047, dtype=torch.int32, device=dev)
+                s_c = M.McaLlamaState(kc.data_ptr(), vc.data_ptr(), int(bf16), frd.data_ptr(), fid.data_ptr(), ws_.data_ptr(), need)
+
+                def step(stream=None):
+                    st = stream if stream is not None else torch.cuda.current_stream()
+                    return lib.mca_llama_forward(C.byref(cfg_c), C.byref(w_c), C.byref(s_c), tok.data_ptr(), pos.data_ptr(), Bn, 2048,
+                                                 logits.data_ptr(), st.cuda_stream)
+                for _ in range(3):
+                    rc = step()
+                side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    graph.capture_begin()
+                    step(side)
+                    graph.capture_end()
+                torch.cuda.current_stream().wait_stream(side)
+                out = {}
+                for name, fn in (("eager", step), ("graph", graph.replay)):
+                    fn()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for _ in range(10):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    out[name + "_ms"] = round(e0.elapsed_time(e1) / 10, 4)
+                nbytes = (L * (4 * dim * dim + 3 * dim * hidden) + vocab * dim) * sz + Bn * L * 2 * 2048 * dim * sz
+                out.update({"rc": rc, "bytes": nbytes, "GBps_graph": round(nbytes / out["graph_ms"] / 1e6, 1),
+                            "tokens_per_s_8_layers": round(Bn / out["graph_ms"] * 1e3, 1)})
+                if Bn > 8:   # the same step with the streaming passes instead of the tensor-core projections
+                    lib.mca_proj_tc_enable(0)
+                    step()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for _ in range(5):
+                        step()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    lib.mca_proj_tc_enable(1)
+                    out["eager_ms_streaming_projections"] = round(e0.elapsed_time(e1) / 5, 4)
+                res[("bf16" if bf16 else "f32") + f"_B{Bn}"] = out
+                del kc, vc, graph, ws_
+                torch.cuda.empty_cache()
+            del w
             torch.cuda.empty_cache()
         print(json.dumps(res))
         return
@@ -1368,7 +1415,7 @@ def main():
                     help="one GPU: skip the other configurations (train, sweep, backward, decode variants, tft)")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "norm-small", "llama-step",
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "proj-small", "norm-small", "llama-step",
                                                      "tft", "train", "sweep", "backward"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()

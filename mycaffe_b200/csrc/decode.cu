@@ -16,6 +16,8 @@
 #include <algorithm>
 #include <mutex>
 
+#include <cstdint>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -516,6 +518,22 @@ int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_l
   sl = (sl + 127) / 128 * 128;
   if (sl < 128) sl = 128;
   if (sl > 1024) sl = 1024;
+  const int64_t groups = (int64_t)B * n_kv_heads;       // CTAs per split
+  if (groups * ((max_len + 127) / 128) <= 4 * 296) {
+    // Few CTAs (one sequence, or a handful): a partly filled last wave costs as much as a full one, so the split
+    // count is chosen by whole waves over the 296 resident CTAs -- time ~ waves x (set-up, about 64 keys' worth, + keys
+    // per split) -- instead of by a fixed length.  One sequence of 2339 keys and 32 heads: 9 splits of 260 keys in one
+    // wave, where 128-key splits give 608 CTAs, i.e. two waves and sixteen stragglers.
+    int64_t best_cost = INT64_MAX;
+    int best_n = 1;
+    for (int n = 1; n <= (max_len + 63) / 64; ++n) {
+      const int64_t len = ((max_len + n - 1) / n + 15) / 16 * 16;
+      const int64_t waves = (groups * n + 295) / 296;
+      const int64_t cost = waves * (64 + len);
+      if (cost < best_cost) { best_cost = cost; best_n = n; }
+    }
+    sl = (((int64_t)max_len + best_n - 1) / best_n + 15) / 16 * 16;
+  }
   *split_len = (int)sl;
   *nsplit = (max_len + (int)sl - 1) / (int)sl;
   *scratch_floats = (int64_t)B * n_heads * (*nsplit) * (head_size + 2);

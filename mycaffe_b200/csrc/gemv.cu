@@ -375,14 +375,16 @@ int run_proj_tc(const GemvParams& p, cudaStream_t st) {
   if ((e = proj::make_map_2d(&mx, pieces, BF ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                              (int64_t)PL::PIECES * Bp, p.n, proj::KC, Bp, CU_TENSOR_MAP_SWIZZLE_128B)))
     return e;
-  proj::x_pieces_kernel<BF><<<Bp, 256, 0, st>>>(p.x, p.norm_w, p.eps, p.n, p.B, Bp, pieces, xscale);
+  auto pre = proj::x_pieces_kernel<BF>;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(pre, cudaFuncAttributeMaxDynamicSharedMemorySize, proj::MAX_N * 4));
+  pre<<<Bp, 256, sizeof(float) * (size_t)p.n, st>>>(p.x, p.norm_w, p.eps, p.n, p.B, Bp, pieces, xscale);
   if ((e = mca_launch_status())) return e;
   const size_t smem = proj::smem_bytes<WT>();
   auto kern = proj::proj_tc_kernel<WT>;
   MCA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int items = tiles * q.slices;
-  kern<<<std::min(items, sms), proj::THREADS, smem, st>>>(mw[0], mw[1], mw[2], mx, q);
-  return mca_launch_status();
+  // programmatic dependent launch: set-up and the first weight tiles overlap the pre-pass
+  return mca_launch_pdl(kern, dim3(std::min(items, sms)), dim3(proj::THREADS), smem, st, mw[0], mw[1], mw[2], mx, q);
 }
 
 template <typename WT>

@@ -6,8 +6,9 @@
 // as N, so every weight byte leaves HBM once whatever the batch, and the kernel is bound by that stream.
 // Replaces the per-sequence cublasSgemv calls of the reference's decode step (CudaExtension.llm32.llama2/Files/
 // primitives.cu:322-340) with the arithmetic of its CPU twin (llama2_cpu.cpp:189-202,224-237) kept to fp32 accuracy:
-//   * fp32 weights: a tile of 128 rows x 64 k arrives by TMA as fp32; eight warps rewrite it as two fp16 tiles
-//     hi = fp16(16 w), lo = fp16(16 w - hi) in the 128-byte-swizzled K-major layout the MMA reads; the activations are
+//   * fp32 weights: a tile of 128 rows x 64 k arrives by TMA as fp32; eight warps rewrite it in place as two fp16
+//     tiles hi = 16 w cut to fp16's mantissa, lo = fp16(16 w - hi) in the 128-byte-swizzled K-major layout the MMA reads
+//     (in place, so that all of shared memory is weight slots: what bounds the kernel is bytes in flight per SM); the activations are
 //     split the same way by a small pre-pass (after RMSNorm and a per-sequence power-of-two scale), and the product is
 //     the three MMAs hi.hi + hi.lo + lo.hi into one fp32 accumulator in TMEM (the dropped lo.lo term is 2^-22);
 //   * bf16 weights: the TMA tile is the MMA operand itself, the activations are three bf16 pieces (24 bits).
@@ -15,8 +16,10 @@
 // streams; a slice leaves its fp32 partial sums in a scratch array and the slice that arrives last (a ticket per
 // tile and quarter of its rows) adds all of them in slice order, so the result does not depend on timing.  The gated pair W1/W3 of the
 // feed-forward block is one item with two accumulators and silu(a) * b in the epilogue.
-// Roles of a CTA (448 threads, one CTA per SM, persistent over items): warps 0-7 convert, 8-11 epilogue (TMEM lanes
-// 32 (w - 8) ..), warp 12 TMA producer, warp 13 MMA issuer and TMEM owner.  Every wait is bounded.
+// Roles of a CTA (480 threads, one CTA per SM, persistent over items): warps 0-7 convert, 8-11 epilogue (TMEM lanes
+// 32 (w - 8) ..), warp 12 TMA producer of the weights, warp 13 MMA issuer and TMEM owner, warp 14 TMA producer of the
+// activation pieces.  The weight ring (five 32 KB slots for fp32, eight 16 KB slots for bf16) and the activation ring have
+// their own barriers.  Every wait is bounded.
 // The activation pieces, per-sequence scales, partial sums and tickets live in arrays that are part of the library
 // image (about 26 MB per device): nothing is allocated, but two of these products must not overlap on one device.
 #pragma once
@@ -32,8 +35,8 @@ constexpr int MAX_N = 16384;       // longest contraction
 constexpr int MAX_ITEMS = 296;     // (tile, slice) items when K is cut
 constexpr int MAX_TILES = 2048;
 constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
-constexpr int WARP_EPI0 = CONV_WARPS, WARP_TMA = CONV_WARPS + EPI_WARPS, WARP_MMA = WARP_TMA + 1;
-constexpr int THREADS = (WARP_MMA + 1) * 32;
+constexpr int WARP_EPI0 = CONV_WARPS, WARP_TMA = CONV_WARPS + EPI_WARPS, WARP_MMA = WARP_TMA + 1, WARP_TMA_X = WARP_MMA + 1;
+constexpr int THREADS = (WARP_TMA_X + 1) * 32;
 constexpr float W_SCALE = 16.f;    // fp32 weights are split after this exact scaling (keeps the low halves normal)
 constexpr uint32_t TMEM_ALLOC = 256, ACC_COLS = 128;
 
@@ -46,25 +49,25 @@ __device__ int g_status[4];
 template <typename WT> struct Plan;
 template <> struct Plan<float> {
   static constexpr bool CONVERT = true;
-  static constexpr int STAGES = 3, PIECES = 2, FMT = 0;                 // fp16 operands
-  static constexpr uint32_t W_BYTES = ROWS * KC * 4;                    // fp32 staging tile
+  static constexpr int SW = 5, SX = 3, PIECES = 2, FMT = 0;            // weight / activation ring depths; fp16 operands
+  static constexpr uint32_t W_BYTES = ROWS * KC * 4;                    // a slot: the fp32 tile, then hi | lo in its place
   static constexpr uint32_t X_BYTES = PIECES * MAX_B * 128;
-  static constexpr uint32_t OP_BYTES = ROWS * KC * 2;                   // one fp16 operand tile
-  static constexpr uint32_t OFF_W = 0, OFF_X = OFF_W + STAGES * W_BYTES, OFF_OP = OFF_X + STAGES * X_BYTES;
-  static constexpr uint32_t OFF_BAR = OFF_OP + 2 * 2 * OP_BYTES;
+  static constexpr uint32_t OP_BYTES = ROWS * KC * 2;                   // one fp16 operand tile (half a slot)
+  static constexpr uint32_t OFF_W = 0, OFF_X = OFF_W + SW * W_BYTES, OFF_OP = OFF_X + SX * X_BYTES;
+  static constexpr uint32_t OFF_BAR = OFF_OP;
 };
 template <> struct Plan<__nv_bfloat16> {
   static constexpr bool CONVERT = false;
-  static constexpr int STAGES = 4, PIECES = 3, FMT = 1;                 // bf16 operands
+  static constexpr int SW = 8, SX = 3, PIECES = 3, FMT = 1;            // bf16 operands
   static constexpr uint32_t W_BYTES = ROWS * KC * 2;
   static constexpr uint32_t X_BYTES = PIECES * MAX_B * 128;
   static constexpr uint32_t OP_BYTES = 0;
-  static constexpr uint32_t OFF_W = 0, OFF_X = OFF_W + STAGES * W_BYTES, OFF_OP = OFF_X + STAGES * X_BYTES;
+  static constexpr uint32_t OFF_W = 0, OFF_X = OFF_W + SW * W_BYTES, OFF_OP = OFF_X + SX * X_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_OP;
 };
-// barriers: full[S] empty[S] convdone[2] opfree[2] accfull[2] accfree[2], then the TMEM address
-constexpr uint32_t BAR_BYTES = 256;
-template <typename WT> constexpr size_t smem_bytes() { return Plan<WT>::OFF_BAR + BAR_BYTES + MAX_B * 4 + 1024; }
+// barriers: wfull[SW] wempty[SW] xfull[SX] xempty[SX] convdone[SW] accfull[2] accfree[2], then the TMEM address
+constexpr uint32_t BAR_BYTES = 512;
+template <typename WT> constexpr size_t smem_bytes() { return Plan<WT>::OFF_BAR + BAR_BYTES + EPI_WARPS * MAX_B * 4 + 1024; }
 
 struct Params {
   float* out[3];
@@ -80,6 +83,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Barrier 1 over the converter warps, returning the AND of their predicates.
+__device__ __forceinline__ bool conv_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "n"(CONV_WARPS * 32)
+      : "memory");
+  return r != 0;
+}
 
 __device__ __forceinline__ float block_sum(float v, float* red) {   // 256 threads
 #pragma unroll
@@ -114,7 +128,9 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
                                                        int n, int B, int Bp, uint16_t* __restrict__ pieces,
                                                        float* __restrict__ xscale) {
   __shared__ float red[8];
+  extern __shared__ float xrow[];                       // the row, read from global memory once
   const int b = blockIdx.x, tid = threadIdx.x;
+  mca_pdl_launch_dependents();                          // the contraction kernel may start fetching weights
   const size_t piece_stride = (size_t)Bp * n;
   uint16_t* dst = pieces + (size_t)b * n;
   if (b >= B) {
@@ -125,17 +141,22 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
     return;
   }
   const float* xr = x + (size_t)b * n;
+  float ss = 0.f;
+  for (int k = tid; k < n; k += 256) { const float v = xr[k]; xrow[k] = v; ss = fmaf(v, v, ss); }
   float s = 1.f;
   if (norm_w != nullptr) {
-    float ss = 0.f;
-    for (int k = tid; k < n; k += 256) { const float v = xr[k]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     s = 1.0f / sqrtf(ss / (float)n + eps);
   }
-  auto value = [&](int k) { return norm_w != nullptr ? norm_w[k] * (s * xr[k]) : xr[k]; };
+  float amax = 0.f;
+  for (int k = tid; k < n; k += 256) {                  // a thread revisits only the elements it wrote itself
+    const float v = norm_w != nullptr ? __ldg(norm_w + k) * (s * xrow[k]) : xrow[k];
+    xrow[k] = v;
+    amax = fmaxf(amax, fabsf(v));
+  }
   if (BF16) {
     for (int k = tid; k < n; k += 256) {
-      const float v = value(k);
+      const float v = xrow[k];
       const __nv_bfloat16 h = __float2bfloat16_rn(v);
       const float r1 = v - __bfloat162float(h);
       const __nv_bfloat16 m = __float2bfloat16_rn(r1);
@@ -147,14 +168,12 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
     if (tid == 0) xscale[b] = 1.f;
     return;
   }
-  float amax = 0.f;
-  for (int k = tid; k < n; k += 256) amax = fmaxf(amax, fabsf(value(k)));
   amax = block_max(amax, red);
   int e = 0;
   if (amax > 0.f && amax < INFINITY) { frexpf(amax, &e); e -= 14; }
   const float down = ldexpf(1.f, -e);
   for (int k = tid; k < n; k += 256) {
-    const float v = value(k) * down;
+    const float v = xrow[k] * down;
     const __half h = __float2half_rn(v);
     const __half l = __float2half_rn(v - __half2float(h));
     dst[k] = __half_as_ushort(h);
@@ -169,37 +188,42 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
                                                              const __grid_constant__ CUtensorMap mw2,
                                                              const __grid_constant__ CUtensorMap mx, const Params p) {
   using PL = Plan<WT>;
-  constexpr int STAGES = PL::STAGES;
+  constexpr int SW = PL::SW, SX = PL::SX;
   extern __shared__ unsigned char pj_smem_raw[];
   const uint32_t raw = smem_u32(pj_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* gen = pj_smem_raw + (base - raw);
   const uint32_t bar0 = base + PL::OFF_BAR;
-  auto full = [&](int s) { return bar0 + 8u * s; };
-  auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto convdone = [&](int c) { return bar0 + 8u * (2 * STAGES + c); };
-  auto opfree = [&](int c) { return bar0 + 8u * (2 * STAGES + 2 + c); };
-  auto accfull = [&](int a) { return bar0 + 8u * (2 * STAGES + 4 + a); };
-  auto accfree = [&](int a) { return bar0 + 8u * (2 * STAGES + 6 + a); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + PL::OFF_BAR + 8 * (2 * STAGES + 8));
-  float* cs = reinterpret_cast<float*>(gen + PL::OFF_BAR + BAR_BYTES);   // per-sequence output scale
+  auto wfull = [&](int s) { return bar0 + 8u * s; };
+  auto wempty = [&](int s) { return bar0 + 8u * (SW + s); };
+  auto xfull = [&](int s) { return bar0 + 8u * (2 * SW + s); };
+  auto xempty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };
+  constexpr int NB0 = 2 * SW + 2 * SX;
+  auto convdone = [&](int c) { return bar0 + 8u * (NB0 + c); };        // [SW]: slot c holds the converted tiles
+  auto accfull = [&](int a) { return bar0 + 8u * (NB0 + SW + a); };
+  auto accfree = [&](int a) { return bar0 + 8u * (NB0 + SW + 2 + a); };
+  static_assert(8 * (NB0 + SW + 4) + 8 <= BAR_BYTES, "barriers fit their block");
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + PL::OFF_BAR + 8 * (NB0 + SW + 4));
+  float* cs = reinterpret_cast<float*>(gen + PL::OFF_BAR + BAR_BYTES);   // per-sequence output scales, one copy per epilogue warp
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int* status = g_status;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full(s), 1);
-      mbar_init(empty(s), PL::CONVERT ? CONV_WARPS + 1 : 1);
+    for (int s = 0; s < SW; ++s) {
+      mbar_init(wfull(s), 1);
+      mbar_init(wempty(s), 1);                              // the MMA has read the slot
+      mbar_init(convdone(s), CONV_WARPS);
+    }
+    for (int s = 0; s < SX; ++s) {
+      mbar_init(xfull(s), 1);
+      mbar_init(xempty(s), 1);
     }
     for (int c = 0; c < 2; ++c) {
-      mbar_init(convdone(c), CONV_WARPS);
-      mbar_init(opfree(c), 1);
       mbar_init(accfull(c), 1);
       mbar_init(accfree(c), EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (tid < MAX_B) cs[tid] = tid < p.B ? g_x_scale[tid] : 0.f;
   if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_ALLOC);
     tmem_relinquish();
@@ -215,6 +239,7 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  mca_pdl_launch_dependents();   // a dependent launch may take the SMs as this kernel's CTAs leave them
   const int items = p.tiles * p.slices;
   const int nacc = p.swiglu ? 2 : 1;
   // k chunks of slice j: [j * kchunks / slices, (j + 1) * kchunks / slices)
@@ -223,7 +248,10 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
   bool ok = true;
 
   if (warp == WARP_TMA) {
-    // ------------------------------------------------------------------ producer
+    // ------------------------------------------------------------------ weight producer
+    // The weights depend on nothing this stream computes: their tiles are requested from the first instruction on, also
+    // while the pre-pass that this launch may have overtaken is still running.  A slot is free again as soon as the
+    // converters have read it (fp32) or the MMA has (bf16).
     if (lane == 0) {
       int g = 0;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -239,14 +267,32 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
           }
           const CUtensorMap* mw = m == 0 ? &mw0 : (m == 1 ? &mw1 : &mw2);
           for (int kc = k0; kc < k1; ++kc, ++g) {
-            const int s = g % STAGES;
-            ok = mbar_wait(empty(s), (uint32_t)(((g / STAGES) & 1) ^ 1), status, 1, g);
+            const int s = g % SW;
+            ok = mbar_wait(wempty(s), (uint32_t)(((g / SW) & 1) ^ 1), status, 1, g);
             if (!ok) break;
-            mbar_expect_tx(full(s), PL::W_BYTES + PL::PIECES * x_piece_bytes);
-            tma_load_2d(base + PL::OFF_W + s * PL::W_BYTES, mw, full(s), kc * KC, row0);
+            mbar_expect_tx(wfull(s), PL::W_BYTES);
+            tma_load_2d(base + PL::OFF_W + s * PL::W_BYTES, mw, wfull(s), kc * KC, row0);
+          }
+        }
+      }
+    }
+  } else if (warp == WARP_TMA_X) {
+    // ------------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      mca_pdl_wait();                                     // the pieces are the pre-pass's output
+      int g = 0;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int u = item / p.slices, j = item - u * p.slices;
+        const int k0 = slice_lo(j), k1 = slice_lo(j + 1);
+        for (int mi = 0; mi < nacc && ok; ++mi) {
+          for (int kc = k0; kc < k1; ++kc, ++g) {
+            const int s = g % SX;
+            ok = mbar_wait(xempty(s), (uint32_t)(((g / SX) & 1) ^ 1), status, 8, g);
+            if (!ok) break;
+            mbar_expect_tx(xfull(s), PL::PIECES * x_piece_bytes);
 #pragma unroll
             for (int pc = 0; pc < PL::PIECES; ++pc)
-              tma_load_2d(base + PL::OFF_X + s * PL::X_BYTES + pc * x_piece_bytes, &mx, full(s), kc * KC, pc * p.Bp);
+              tma_load_2d(base + PL::OFF_X + s * PL::X_BYTES + pc * x_piece_bytes, &mx, xfull(s), kc * KC, pc * p.Bp);
           }
         }
       }
@@ -266,20 +312,15 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
         for (int mi = 0; mi < nacc && ok; ++mi) {
           const uint32_t d_tmem = tmem_base + (uint32_t)a * ACC_COLS + (uint32_t)(mi * p.Bp);
           for (int kc = k0; kc < k1; ++kc, ++g) {
-            const int s = g % STAGES, c = g & 1;
-            ok = mbar_wait(full(s), (uint32_t)((g / STAGES) & 1), status, 3, g);
+            const int sw = g % SW, sx = g % SX;
+            // fp32 weights: the slot holds the converted hi | lo tiles once all converter warps have arrived
+            ok = mbar_wait(PL::CONVERT ? convdone(sw) : wfull(sw), (uint32_t)((g / SW) & 1), status, 3, g);
             if (!ok) break;
-            uint32_t a_hi, a_lo = 0;
-            if constexpr (PL::CONVERT) {
-              ok = mbar_wait(convdone(c), (uint32_t)((g >> 1) & 1), status, 4, g);
-              if (!ok) break;
-              a_hi = base + PL::OFF_OP + (uint32_t)c * 2 * PL::OP_BYTES;
-              a_lo = a_hi + PL::OP_BYTES;
-            } else {
-              a_hi = base + PL::OFF_W + s * PL::W_BYTES;
-            }
+            const uint32_t a_hi = base + PL::OFF_W + sw * PL::W_BYTES, a_lo = a_hi + PL::OP_BYTES;
+            ok = mbar_wait(xfull(sx), (uint32_t)((g / SX) & 1), status, 9, g);
+            if (!ok) break;
             tc_fence_after();
-            const uint32_t xs = base + PL::OFF_X + s * PL::X_BYTES;
+            const uint32_t xs = base + PL::OFF_X + sx * PL::X_BYTES;
 #pragma unroll
             for (int kk = 0; kk < KC / 16; ++kk) {
               const uint32_t first = (kc == k0 && kk == 0) ? 0u : 1u;
@@ -298,8 +339,8 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
                 umma_ss(d_tmem, da, dx2, idesc, 1u);
               }
             }
-            if constexpr (PL::CONVERT) umma_commit(opfree(c));
-            umma_commit(empty(s));
+            umma_commit(wempty(sw));
+            umma_commit(xempty(sx));
           }
         }
         if (ok) umma_commit(accfull(a));
@@ -313,37 +354,40 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
         const int u = item / p.slices, j = item - u * p.slices;
         const int steps = nacc * (slice_lo(j + 1) - slice_lo(j));
         for (int t = 0; t < steps; ++t, ++g) {
-          const int s = g % STAGES, c = g & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(full(s), (uint32_t)((g / STAGES) & 1), status, 5, g));
-          if (!ok) break;
-          ok = __all_sync(0xffffffffu, mbar_wait(opfree(c), (uint32_t)(((g >> 1) & 1) ^ 1), status, 6, g));
-          if (!ok) break;
-          tc_fence_after();
+          const int s = g % SW;
+          const bool mine = __all_sync(0xffffffffu, mbar_wait(wfull(s), (uint32_t)((g / SW) & 1), status, 5, g));
+          // The tile is rewritten in place: hi over the first half of the slot, lo over the second.  A lane takes the
+          // sixteen rows of its warp into registers (k = 2 lane, 2 lane + 1: 8-byte reads, no bank conflicts); nobody
+          // writes before all eight warps have read.  The barrier also carries the vote on the wait's outcome, so that
+          // either every converter warp goes on or none does.
+          float2 v[ROWS / CONV_WARPS];
           const float* wst = reinterpret_cast<const float*>(gen + PL::OFF_W + s * PL::W_BYTES);
-          unsigned char* ohi = gen + PL::OFF_OP + (size_t)c * 2 * PL::OP_BYTES;
+          if (mine) {
+#pragma unroll
+            for (int rr = 0; rr < ROWS / CONV_WARPS; ++rr)
+              v[rr] = *reinterpret_cast<const float2*>(wst + (warp * (ROWS / CONV_WARPS) + rr) * KC + 2 * lane);
+          }
+          ok = conv_bar_and(mine);
+          if (!ok) break;
+          unsigned char* ohi = gen + PL::OFF_W + s * PL::W_BYTES;
           unsigned char* olo = ohi + PL::OP_BYTES;
-          // a lane owns k = 2 lane, 2 lane + 1 of a row: 8-byte reads and 4-byte writes, both free of bank conflicts
-#pragma unroll 4
+#pragma unroll
           for (int rr = 0; rr < ROWS / CONV_WARPS; ++rr) {
             const int r = warp * (ROWS / CONV_WARPS) + rr;
-            const float2 w2 = *reinterpret_cast<const float2*>(wst + r * KC + 2 * lane);
-            const float a0 = w2.x * W_SCALE, a1 = w2.y * W_SCALE;
-            __half2 h;
-            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(*reinterpret_cast<uint32_t*>(&h)) : "f"(a1), "f"(a0));
-            const float2 hf = __half22float2(h);
-            __half2 l;
-            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(*reinterpret_cast<uint32_t*>(&l)) : "f"(a1 - hf.y), "f"(a0 - hf.x));
+            // hi = the scaled weight cut to fp16's mantissa (exact in fp16), lo = the rest (exact in fp32, rounded once)
+            const float a0 = v[rr].x * W_SCALE, a1 = v[rr].y * W_SCALE;
+            const float h0 = __uint_as_float(__float_as_uint(a0) & 0xffffe000u), h1 = __uint_as_float(__float_as_uint(a1) & 0xffffe000u);
+            uint32_t h, l;
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(h1), "f"(h0));
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(l) : "f"(a1 - h1), "f"(a0 - h0));
             const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (uint32_t)(((lane >> 2) ^ (r & 7)) << 4) +
                                  (uint32_t)(lane & 3) * 4u;
-            *reinterpret_cast<__half2*>(ohi + off) = h;
-            *reinterpret_cast<__half2*>(olo + off) = l;
+            *reinterpret_cast<uint32_t*>(ohi + off) = h;
+            *reinterpret_cast<uint32_t*>(olo + off) = l;
           }
           fence_proxy_async();          // the MMA reads these tiles through the asynchronous proxy
           __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(convdone(c));
-            mbar_arrive(empty(s));      // the staging tile has been read
-          }
+          if (lane == 0) mbar_arrive(convdone(s));
         }
       }
     }
@@ -351,6 +395,12 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
     // ------------------------------------------------------------------ epilogue warps
     const int e = warp - WARP_EPI0;                       // TMEM lanes 32 e .. 32 e + 31
     const int r = e * 32 + lane;                          // row of the tile
+    // per-sequence output scales, written by the pre-pass this launch may have overtaken: every warp keeps a copy
+    mca_pdl_wait();
+    cs += e * MAX_B;
+    cs[lane] = lane < p.B ? __ldcg(g_x_scale + lane) : 0.f;
+    cs[lane + 32] = lane + 32 < p.B ? __ldcg(g_x_scale + lane + 32) : 0.f;
+    __syncwarp();
     const int ncols = nacc * p.Bp;
     int it = 0;
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
@@ -372,10 +422,11 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
       // one output element: the product scaled back, gated if asked, added to the residual if asked
       auto finish = [&](int b, float va, float vb) {
         if (b < p.B && row < rows_m) {
-          float y = va * cs[b];
+          const float sc = cs[b];
+          float y = va * sc;
           if (p.swiglu) {
             y *= (1.0f / (1.0f + expf(-y)));            // silu, llama2_cpu.cpp:360-365
-            y *= vb * cs[b];
+            y *= vb * sc;
           }
           float* dst = outm + (size_t)b * rows_m + row;
           if (p.accumulate) y += *dst;
@@ -419,13 +470,30 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
         if (last) {
           __threadfence();
           const float* p0 = g_partials + ((size_t)(u * p.slices) * ncols) * ROWS + r;
-          for (int b = 0; b < p.B; ++b) {
-            float va = 0.f, vb = 0.f;
-            for (int s2 = 0; s2 < p.slices; ++s2) {      // slice order, whoever arrived last
-              va += __ldcg(p0 + ((size_t)s2 * ncols + b) * ROWS);
-              if (p.swiglu) vb += __ldcg(p0 + ((size_t)s2 * ncols + p.Bp + b) * ROWS);
+          // Sixteen columns at a time, two slices per round: 32 loads are in flight together, and the sums are taken in
+          // slice order whoever arrived last.
+          auto gather = [&](int col0, float (&acc)[16]) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+            for (int s0 = 0; s0 < p.slices; s0 += 2) {
+              float t[2][16];
+#pragma unroll
+              for (int q = 0; q < 2; ++q)
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  t[q][i] = s0 + q < p.slices ? __ldcg(p0 + ((size_t)(s0 + q) * ncols + col0 + i) * ROWS) : 0.f;
+#pragma unroll
+              for (int q = 0; q < 2; ++q)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] += t[q][i];
             }
-            finish(b, va, vb);
+          };
+          for (int c0 = 0; c0 < p.Bp; c0 += 16) {
+            float va[16], vb[16];
+            gather(c0, va);
+            if (p.swiglu) gather(p.Bp + c0, vb);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) finish(c0 + i, va[i], p.swiglu ? vb[i] : 0.f);
           }
         }
       }

@@ -132,10 +132,13 @@ def test_decode_plan_is_consistent(lib):
     sl, ns, sc = C.c_int(), C.c_int(), C.c_int64()
     for B, nh, nkv, L in [(1, 32, 32, 4096), (64, 32, 32, 4096), (16, 32, 8, 513), (1, 8, 8, 1)]:
         assert lib.mca_decode_plan(B, nh, nkv, 128, L, C.byref(sl), C.byref(ns), C.byref(sc)) == 0
-        assert sl.value % 128 == 0 and 128 <= sl.value <= 1024
+        assert sl.value % 16 == 0 and 16 <= sl.value <= 1024
         assert ns.value == -(-L // sl.value)
         assert sc.value == B * nh * ns.value * 130
     assert lib.mca_decode_plan(1, 32, 5, 128, 10, C.byref(sl), C.byref(ns), C.byref(sc)) == 90001
+    # one sequence: the splits fill one wave of the 296 resident CTAs instead of spilling into a third
+    assert lib.mca_decode_plan(1, 32, 32, 128, 2339, C.byref(sl), C.byref(ns), C.byref(sc)) == 0
+    assert 32 * ns.value <= 296 and ns.value == 9
 
 
 def test_no_gpu_fails_loudly(lib):
