@@ -419,28 +419,37 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(e * 32) << 16) + (uint32_t)a * ACC_COLS;
-      // one output element: the product scaled back, gated if asked, added to the residual if asked
-      auto finish = [&](int b, float va, float vb) {
-        if (b < p.B && row < rows_m) {
-          const float sc = cs[b];
-          float y = va * sc;
-          if (p.swiglu) {
-            y *= (1.0f / (1.0f + expf(-y)));            // silu, llama2_cpu.cpp:360-365
-            y *= vb * sc;
+      // sixteen output elements of this thread's row: the products scaled back, gated if asked, added to the residual
+      // if asked (all sixteen residuals are requested before any is used)
+      auto finish16 = [&](int c0, const float (&va)[16], const float (&vb)[16]) {
+        if (row >= rows_m) return;
+        float res[16];
+        float* dst = outm + (size_t)c0 * rows_m + row;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) res[i] = (p.accumulate && c0 + i < p.B) ? __ldcg(dst + (size_t)i * rows_m) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (c0 + i < p.B) {
+            const float sc = cs[c0 + i];
+            float y = va[i] * sc;
+            if (p.swiglu) {
+              y *= (1.0f / (1.0f + expf(-y)));          // silu, llama2_cpu.cpp:360-365
+              y *= vb[i] * sc;
+            }
+            dst[(size_t)i * rows_m] = y + res[i];
           }
-          float* dst = outm + (size_t)b * rows_m + row;
-          if (p.accumulate) y += *dst;
-          *dst = y;
         }
       };
       if (p.slices == 1) {
         for (int c0 = 0; c0 < p.Bp; c0 += 16) {
           uint32_t va[16], vb[16];
+          float fa[16], fb[16];
           tmem_ld16(t_acc + c0, va);
           if (p.swiglu) tmem_ld16(t_acc + p.Bp + c0, vb);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) finish(c0 + i, __uint_as_float(va[i]), p.swiglu ? __uint_as_float(vb[i]) : 0.f);
+          for (int i = 0; i < 16; ++i) { fa[i] = __uint_as_float(va[i]); fb[i] = p.swiglu ? __uint_as_float(vb[i]) : 0.f; }
+          finish16(c0, fa, fb);
         }
         tc_fence_before();
         __syncwarp();
@@ -492,8 +501,11 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
             float va[16], vb[16];
             gather(c0, va);
             if (p.swiglu) gather(p.Bp + c0, vb);
+            if (!p.swiglu) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) finish(c0 + i, va[i], p.swiglu ? vb[i] : 0.f);
+              for (int i = 0; i < 16; ++i) vb[i] = 0.f;
+            }
+            finish16(c0, va, vb);
           }
         }
       }
