@@ -181,7 +181,10 @@ class Ctx:
         self.affinity = {"skipped": "single process"}
         if self.world > 1:
             from mycaffe_b200 import head_shard
-            self.affinity = head_shard.bind_near_gpu(self.local)
+            try:
+                self.affinity = head_shard.bind_near_gpu(self.local)
+            except Exception as e:       # never let the placement hint stop a run
+                self.affinity = {"skipped": f"{type(e).__name__}: {e}"}
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.dev)
         self.lib = _lib.load()
@@ -403,7 +406,10 @@ def run_ours(args):
     if rank != 0:
         return
     if "previous" in cx.affinity:       # the CPU legs below use every core again
-        os.sched_setaffinity(0, cx.affinity["previous"])
+        try:
+            os.sched_setaffinity(0, cx.affinity["previous"])
+        except OSError:
+            pass
     import oracle
     cores = oracle.set_num_threads()    # a launcher may have exported OMP_NUM_THREADS=1 for its workers
     parity, cpu_base = prefill_parity(torch, dev, B, H, T, D, q_begin, q_step, prefill_sample, cores)

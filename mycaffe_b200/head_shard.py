@@ -46,7 +46,10 @@ def bind_near_pci(bdf: str, sysfs_root: str = "/sys/bus/pci/devices") -> dict:
     cpus = local & previous
     if not cpus:
         return {"skipped": "no local CPU in the allowed set", "numa_node": node}
-    os.sched_setaffinity(0, cpus)
+    try:
+        os.sched_setaffinity(0, cpus)
+    except OSError as e:                 # a sandbox may forbid it: run unbound rather than fail
+        return {"skipped": f"{type(e).__name__}: {e}", "numa_node": node}
     return {"cpus": len(cpus), "numa_node": node, "previous": previous}
 
 
@@ -59,7 +62,7 @@ def bind_near_gpu(device_index: int) -> dict:
     try:
         pr = torch.cuda.get_device_properties(device_index)
         bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
-    except (AttributeError, RuntimeError, AssertionError) as e:
+    except (AttributeError, RuntimeError, AssertionError, ValueError, TypeError) as e:
         return {"skipped": f"{type(e).__name__}: {e}"}
     return bind_near_pci(bdf)
 
