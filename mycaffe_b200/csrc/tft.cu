@@ -498,18 +498,21 @@ __global__ void __launch_bounds__(TFT_THREADS) tft_bwd_kernel(const float* __res
 // ---------------------------------------------------------------------------------------------
 // Backward, tiled form (the shapes of the tiled forward: d in {16, 32, 64}, Nk <= 192).
 //
-// One CTA = one batch item; it walks the heads and, inside a head, the 24-row tiles of the queries.  V and two K
-// buffers (head h + 1 arrives while head h is worked on) stay in shared memory, the 24 rows of Q_h and of the output
-// gradient are double-buffered.  Per (head, tile):
-//   A  S = Q K^T and dP = dO V^T in the forward's 6 x 3 register tiles, one loop over the head dimension feeding both
-//      (dP does not depend on the head: with a single tile it is computed for the first head and kept in registers);
+// One CTA = one batch item; it walks the 24-row tiles of the queries and, inside a tile, the heads.  V stays in shared
+// memory; K_h, the 24 rows of Q_h and of the output gradient are double-buffered (the next iteration's arrive while
+// this one is worked on).  Per (tile, head):
+//   A  S = Q K^T in the forward's 6 x 3 register tiles; for the tile's first head the same loop also forms
+//      dP = dO V^T, which does not depend on the head and stays in registers for the others;
 //   B  mask, softmax and its backward in that layout: the row maximum, then the row sum together with sum_j P dP,
-//      cross the two warps that share a row through shared memory; P and dS = P (dP - sum) scale go to shared memory;
-//   C  dK_h += dS^T Q_h and dV += P^T dO: a thread owns 3 keys x d/4 columns of both in registers (the contraction runs
-//      over the 24 rows), dK_h across the tiles of a head, dV across everything -- no atomics, a fixed order;
+//      cross the two warps that share a row through shared memory; dS = P (dP - sum) scale goes to shared memory and P
+//      is added to the running sum over the heads (18 registers);
+//   C  this tile's part of dK_h = dS^T Q_h: a thread owns 3 keys x d/4 columns in registers (the contraction runs over
+//      the 24 rows); it is written for the first tile and added in global memory for the later ones -- one CTA, a
+//      fixed order, no atomics;
 //   D  dQ = dS K_h: a thread owns a few rows x 4 columns over a slice of the keys, four keys per step (one 16-byte read
-//      of dS per row, four of K); the slices' partial sums meet in shared memory (in the buffer of P, free by then).
-// The 1/H of the head mean is applied to dP once and to dV at the end.
+//      of dS per row, four of K); the slices' partial sums meet in shared memory;
+//   after the tile's last head, dV (+)= (sum_h P_h)^T dO / H, one product for all heads.
+// The 1/H of the head mean is applied to dP once and to dV.
 // smem: Vt[nk4][d] | Kt[2][nk4][d] (16-byte pieces swizzled by row; nk4 = Nk rounded up to 4, rows beyond Nk zero) |
 //       Qs[2][24][d] | Gs[2][24][d] | Ps[24][192] | Ss[24][192] | ex[6][24]
 // ---------------------------------------------------------------------------------------------
@@ -566,7 +569,7 @@ __device__ __forceinline__ void tft_bwd_scores(const float* const (&krow)[TQ_C],
   }
 }
 
-template <int D, bool ONE>
+template <int D>
 __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const float* __restrict__ Q, const float* __restrict__ K,
                                                                        const float* __restrict__ V,
                                                                        const float* __restrict__ mask,
@@ -595,13 +598,13 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
   const int tiles = (Nq + TQ - 1) / TQ, iters = H * tiles;
   const float inv_h = 1.f / (float)H;
 
-  // what iteration `it` = (head, row tile) reads; one commit group per call, empty beyond the last iteration
+  // what iteration `it` = (row tile, head) reads; one commit group per call, empty beyond the last iteration
   auto load_iter = [&](int it) {
     if (it < iters) {
-      const int h = it / tiles, q0 = (it - h * tiles) * TQ, rows = min(TQ, Nq - q0);
+      const int t = it / H, h = it - t * H, q0 = t * TQ, rows = min(TQ, Nq - q0);
       rows24_async<D>(Qs + (it & 1) * TQ * D, Q + (((int64_t)b * H + h) * Nq + q0) * D, rows, tid);
       rows24_async<D>(Gs + (it & 1) * TQ * D, d_out + ((int64_t)b * Nq + q0) * D, rows, tid);
-      if (q0 == 0) tile_rows_async_swz<D>(Kt + (h & 1) * tile, K + ((int64_t)b * H + h) * Nk * D, Nk, tid);
+      tile_rows_async_swz<D>(Kt + (it & 1) * tile, K + ((int64_t)b * H + h) * Nk * D, Nk, tid);
       if (it == 0) tile_rows_async_swz<D>(Vt, V + (int64_t)b * Nk * D, Nk, tid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -619,26 +622,22 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
   const int n4 = nk4 / 4, per4 = (n4 + SLOTS - 1) / SLOTS;
   const int jq0 = ks * per4, jq1 = min(n4, jq0 + per4);
 
-  float dk[TQ_C][NV * 4], dv[TQ_C][NV * 4];
+  float dk[TQ_C][NV * 4];
 #pragma unroll
   for (int c = 0; c < TQ_C; ++c)
 #pragma unroll
-    for (int x = 0; x < NV * 4; ++x) dk[c][x] = dv[c][x] = 0.f;
+    for (int x = 0; x < NV * 4; ++x) dk[c][x] = 0.f;
   float dp[TQ_R][TQ_C];
-  float pm[TQ_R][TQ_C];                               // ONE: the sum over the heads of this thread's probabilities
-#pragma unroll
-  for (int r = 0; r < TQ_R; ++r)
-#pragma unroll
-    for (int c = 0; c < TQ_C; ++c) pm[r][c] = 0.f;
+  float pm[TQ_R][TQ_C];                               // the sum over the heads of this thread's probabilities (one row tile)
   unsigned mbits = 0, dead = 0;
 
   for (int it = 0; it < iters; ++it) {
-    const int h = it / tiles, t = it - h * tiles, q0 = t * TQ, rows = min(TQ, Nq - q0);
-    const bool fresh = tiles > 1 || h == 0;           // new rows: mask bits and dP have to be formed
+    const int t = it / H, h = it - t * H, q0 = t * TQ, rows = min(TQ, Nq - q0);
+    const bool fresh = h == 0;                        // new rows: mask bits and dP have to be formed, the head sum starts
     load_iter(it + 1);                                // into the buffers iteration it - 1 read (it ended with a barrier)
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();                                  // this iteration's tiles visible; everyone is past the previous one
-    const float* Kh = Kt + (h & 1) * tile;
+    const float* Kh = Kt + (it & 1) * tile;
     const float* Qh = Qs + (it & 1) * TQ * D;
     const float* Gh = Gs + (it & 1) * TQ * D;
 
@@ -664,6 +663,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
           else if (i < rows && mv[r][c] == 1.0f) mbits |= 1u << (r * TQ_C + c);
           if (i >= rows || j >= Nk) da[r][c] = 0.f;
           dp[r][c] = 0.f;
+          pm[r][c] = 0.f;
         }
     }
     float s[TQ_R][TQ_C];
@@ -747,28 +747,22 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
       for (int c = 0; c < TQ_C; ++c) {
         const int j = khalf * (32 * TQ_C) + lane + 32 * c;
         const float pj = s[r][c] * inv;
-        if (ONE) pm[r][c] += pj;
-        else Ps[i * TQ_KEYS + j] = pj;
+        pm[r][c] += pj;
         Ss[i * TQ_KEYS + j] = pj * (dp[r][c] - dot) * scale;          // softmax backward, then the 1/sqrt(d) (:822-831)
       }
     }
     __syncthreads();                                  // P and dS complete
 
-    // ---- C: dK_h += dS^T Q_h, dV += P^T dO
+    // ---- C: dK_h (this tile's part) = dS^T Q_h
 #pragma unroll 2
     for (int r = 0; r < TQ; ++r) {
-      float pv[TQ_C], sv[TQ_C];
-      float4 qv[NV], gv[NV];
+      float sv[TQ_C];
+      float4 qv[NV];
 #pragma unroll
-      for (int c = 0; c < TQ_C; ++c) {
-        if (!ONE) pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
-        sv[c] = Ss[r * TQ_KEYS + kg + 64 * c];
-      }
+      for (int c = 0; c < TQ_C; ++c) sv[c] = Ss[r * TQ_KEYS + kg + 64 * c];
 #pragma unroll
-      for (int x = 0; x < NV; ++x) {
+      for (int x = 0; x < NV; ++x)
         qv[x] = *reinterpret_cast<const float4*>(Qh + r * D + 4 * (cg + 4 * x));   // the four lanes of a key: distinct banks
-        if (!ONE) gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + 4 * (cg + 4 * x));
-      }
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c)
 #pragma unroll
@@ -777,12 +771,6 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
           dk[c][4 * x + 1] = fmaf(sv[c], qv[x].y, dk[c][4 * x + 1]);
           dk[c][4 * x + 2] = fmaf(sv[c], qv[x].z, dk[c][4 * x + 2]);
           dk[c][4 * x + 3] = fmaf(sv[c], qv[x].w, dk[c][4 * x + 3]);
-          if (!ONE) {
-            dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
-            dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
-            dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
-            dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
-          }
         }
     }
 
@@ -818,7 +806,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
         o[r][2] = fmaf(sv[r].w, kv[3].z, o[r][2]); o[r][3] = fmaf(sv[r].w, kv[3].w, o[r][3]);
       }
     }
-    __syncthreads();                                  // nobody reads P any more: its buffer takes the partial sums
+    __syncthreads();                                  // the buffer of the head sum now takes the partial sums of dQ
     if (ks > 0) {
 #pragma unroll
       for (int r = 0; r < RPT; ++r)
@@ -838,60 +826,69 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
         if (i < rows) *reinterpret_cast<float4*>(dQ + (((int64_t)b * H + h) * Nq + q0 + i) * D + c4 * 4) = a;
       }
     }
-    if (t == tiles - 1) {                             // the head is finished: its dK leaves the registers
+    // this tile's part of dK_h leaves the registers: the first tile writes, later ones add (one CTA, fixed order)
+#pragma unroll
+    for (int c = 0; c < TQ_C; ++c) {
+      const int j = kg + 64 * c;
+#pragma unroll
+      for (int x = 0; x < NV; ++x) {
+        if (j < Nk) {
+          float4* g = reinterpret_cast<float4*>(dK + (((int64_t)b * H + h) * Nk + j) * D + 4 * (cg + 4 * x));
+          float4 acc4 = make_float4(dk[c][4 * x], dk[c][4 * x + 1], dk[c][4 * x + 2], dk[c][4 * x + 3]);
+          if (t > 0) { const float4 old = *g; acc4.x += old.x; acc4.y += old.y; acc4.z += old.z; acc4.w += old.w; }
+          *g = acc4;
+        }
+        dk[c][4 * x] = dk[c][4 * x + 1] = dk[c][4 * x + 2] = dk[c][4 * x + 3] = 0.f;
+      }
+    }
+    if (h == H - 1) {
+      // the tile's last head: V's gradient is (sum_h P_h)^T dO / H, one product for all heads (the rows of dO are
+      // those of this iteration's buffer)
+      __syncthreads();                                // the partial sums of dQ have been read
+#pragma unroll
+      for (int r = 0; r < TQ_R; ++r)
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) Ps[(rg * TQ_R + r) * TQ_KEYS + khalf * (32 * TQ_C) + lane + 32 * c] = pm[r][c];
+      __syncthreads();
+      float dv[TQ_C][NV * 4];
+#pragma unroll
+      for (int c = 0; c < TQ_C; ++c)
+#pragma unroll
+        for (int x = 0; x < NV * 4; ++x) dv[c][x] = 0.f;
+#pragma unroll 2
+      for (int r = 0; r < TQ; ++r) {
+        float pv[TQ_C];
+        float4 gv[NV];
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c) pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
+#pragma unroll
+        for (int x = 0; x < NV; ++x) gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + 4 * (cg + 4 * x));
+#pragma unroll
+        for (int c = 0; c < TQ_C; ++c)
+#pragma unroll
+          for (int x = 0; x < NV; ++x) {
+            dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
+            dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
+            dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
+            dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
+          }
+      }
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c) {
         const int j = kg + 64 * c;
+        if (j < Nk) {
 #pragma unroll
-        for (int x = 0; x < NV; ++x) {
-          if (j < Nk)
-            *reinterpret_cast<float4*>(dK + (((int64_t)b * H + h) * Nk + j) * D + 4 * (cg + 4 * x)) =
-                make_float4(dk[c][4 * x], dk[c][4 * x + 1], dk[c][4 * x + 2], dk[c][4 * x + 3]);
-          dk[c][4 * x] = dk[c][4 * x + 1] = dk[c][4 * x + 2] = dk[c][4 * x + 3] = 0.f;
+          for (int x = 0; x < NV; ++x) {
+            float4* g = reinterpret_cast<float4*>(dV + ((int64_t)b * Nk + j) * D + 4 * (cg + 4 * x));
+            float4 acc4 = make_float4(dv[c][4 * x] * inv_h, dv[c][4 * x + 1] * inv_h, dv[c][4 * x + 2] * inv_h, dv[c][4 * x + 3] * inv_h);
+            if (t > 0) { const float4 old = *g; acc4.x += old.x; acc4.y += old.y; acc4.z += old.z; acc4.w += old.w; }
+            *g = acc4;
+          }
         }
       }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (ONE) {
-    // a single row tile: V's gradient is (sum_h P_h)^T dO, one product for all heads (the rows of dO are still in
-    // the buffer of the last iteration)
-    __syncthreads();                                  // the last partial sums of dQ have been read
-#pragma unroll
-    for (int r = 0; r < TQ_R; ++r)
-#pragma unroll
-      for (int c = 0; c < TQ_C; ++c) Ps[(rg * TQ_R + r) * TQ_KEYS + khalf * (32 * TQ_C) + lane + 32 * c] = pm[r][c];
-    __syncthreads();
-    const float* Gh = Gs + ((iters - 1) & 1) * TQ * D;
-#pragma unroll 2
-    for (int r = 0; r < TQ; ++r) {
-      float pv[TQ_C];
-      float4 gv[NV];
-#pragma unroll
-      for (int c = 0; c < TQ_C; ++c) pv[c] = Ps[r * TQ_KEYS + kg + 64 * c];
-#pragma unroll
-      for (int x = 0; x < NV; ++x) gv[x] = *reinterpret_cast<const float4*>(Gh + r * D + 4 * (cg + 4 * x));
-#pragma unroll
-      for (int c = 0; c < TQ_C; ++c)
-#pragma unroll
-        for (int x = 0; x < NV; ++x) {
-          dv[c][4 * x + 0] = fmaf(pv[c], gv[x].x, dv[c][4 * x + 0]);
-          dv[c][4 * x + 1] = fmaf(pv[c], gv[x].y, dv[c][4 * x + 1]);
-          dv[c][4 * x + 2] = fmaf(pv[c], gv[x].z, dv[c][4 * x + 2]);
-          dv[c][4 * x + 3] = fmaf(pv[c], gv[x].w, dv[c][4 * x + 3]);
-        }
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < TQ_C; ++c) {
-    const int j = kg + 64 * c;
-    if (j < Nk) {
-#pragma unroll
-      for (int x = 0; x < NV; ++x)
-        *reinterpret_cast<float4*>(dV + ((int64_t)b * Nk + j) * D + 4 * (cg + 4 * x)) =
-            make_float4(dv[c][4 * x] * inv_h, dv[c][4 * x + 1] * inv_h, dv[c][4 * x + 2] * inv_h, dv[c][4 * x + 3] * inv_h);
-    }
-  }
 }
 
 }  // namespace
@@ -911,13 +908,8 @@ int mca_tft_attention_backward_f32(const float* q, const float* k, const float* 
     const float sc = 1.0f / sqrtf((float)d);
     cudaStream_t st = (cudaStream_t)stream;
 #define MCA_TFT_BWD_TILED(D_)                                                                                                 \
-    if (Nq <= TQ) {                                                                                                           \
-      MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
-      tft_bwd_tiled_kernel<D_, true><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv); \
-    } else {                                                                                                                  \
-      MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
-      tft_bwd_tiled_kernel<D_, false><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv); \
-    }
+    MCA_CUDA_TRY(cudaFuncSetAttribute(tft_bwd_tiled_kernel<D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+    tft_bwd_tiled_kernel<D_><<<B, TFT_THREADS, smem_t, st>>>(q, k, v, mask, d_out, d_attn, H, Nq, Nk, sc, dq, dk, dv);
     if (d == 64) { MCA_TFT_BWD_TILED(64) } else if (d == 32) { MCA_TFT_BWD_TILED(32) } else { MCA_TFT_BWD_TILED(16) }
 #undef MCA_TFT_BWD_TILED
     return mca_launch_status();
