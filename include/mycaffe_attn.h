@@ -245,6 +245,17 @@ MCA_API int mca_sdpa_backward_f32_layout(const float* q, const float* k, const f
  * MyCaffe.layers.gpt/layers.gpt/CausalSelfAttentionLayer.cs:276-291; else 0. */
 MCA_API int mca_classify_causal_mask(const float* mask, int T, int* flag, void* stream);
 
+/* The reference's other mask forms on the tensor-core kernels.  A (T,T) mask (apply_mask, attn.cu:302-311 with
+ * bBatchMask false: masked where 0) or a (B,T) key mask (bBatchMask true, what MultiheadAttentionLayer.cs:698-702
+ * passes) is first packed into keep-bits by mca_mask_pack: `bits` holds rows x mca_mask_bits_row_words(T) words (rows = T
+ * or B), `bits_t` (a (T,T) mask only; the backward reads it) the same for the transposed mask; both 16-byte aligned.
+ * The *_masked entry points then take (bits, [bits_t,] mask_mode) with mask_mode MCA_MASK_MODE_TT or
+ * MCA_MASK_MODE_BATCH and causal = 0; with MCA_MASK_MODE_NONE and null pointers they are the unmasked calls.
+ * Semantics as the reference: a masked logit is a finite value far below every real one, so a row whose every key is
+ * masked comes out uniform (its lse is written as +inf, which is how the backward recognises it). */
+MCA_API int mca_mask_bits_row_words(int T);
+MCA_API int mca_mask_pack(const float* mask, int mask_mode, int B, int T, uint32_t* bits, uint32_t* bits_t, void* stream);
+
 /* Tensor-core SDPA forward (tcgen05 + TMEM + TMA).  Same math as attn.cu:518-602 with a causal
  * or absent mask.  dtype: MCA_DTYPE_BF16 (q,k,v,y bf16) or MCA_DTYPE_TF32 (q,k,v,y fp32).
  * D in {64,128}; lse: optional (B,H,T) floats, log2-domain log-sum-exp kept for the backward.
@@ -265,6 +276,10 @@ MCA_API int mca_sdpa_forward_f32_tc_supported(int D);
 MCA_API int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D,
                                     float* y, float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
                                     int64_t workspace_bytes, int* status, int layout, void* stream);
+MCA_API int mca_sdpa_forward_f32_tc_masked(const float* q, const float* k, const float* v, int causal, int B, int H, int T,
+                                           int D, float* y, float* row_max, float* row_sum, float* y_copy, float* lse,
+                                           void* workspace, int64_t workspace_bytes, int* status, int layout,
+                                           const uint32_t* mask_bits, int mask_mode, void* stream);
 /* Its backward (attnHandle<T>::Backward, attn.cu:608-661) on the tensor cores with the same split operands: `workspace`
  * must still hold what mca_sdpa_forward_f32_tc left in it for the same q, k, v (their fp16 halves and scales); dY is split
  * here.  dy in the output layout, y_copy and lse from the forward; dq, dk, dv fp32 in the input layout;
@@ -272,6 +287,11 @@ MCA_API int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float*
 MCA_API int mca_sdpa_backward_f32_tc(const float* dy, const float* y_copy, const float* lse, float* delta_scratch, int causal,
                                      int B, int H, int T, int D, float* dq, float* dk, float* dv, void* workspace,
                                      int64_t workspace_bytes, int* status, int layout, void* stream);
+MCA_API int mca_sdpa_backward_f32_tc_masked(const float* dy, const float* y_copy, const float* lse, float* delta_scratch,
+                                            int causal, int B, int H, int T, int D, float* dq, float* dk, float* dv,
+                                            void* workspace, int64_t workspace_bytes, int* status, int layout,
+                                            const uint32_t* mask_bits, const uint32_t* mask_bits_t, int mask_mode,
+                                            void* stream);
 
 /* Self-check of the bounded waits inside the tensor-core kernels: launches one small kernel whose only thread waits
  * on a barrier nothing arrives on, for at most limit_us microseconds (<= 100000), then gives up the way a stalled
@@ -308,9 +328,17 @@ MCA_API int mca_host_pipeline_release(void);
  * the thirds of a (B,T,3C) gradient.  `y` of the backward has the layout the forward wrote it in. */
 MCA_API int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                        int T, int D, void* y, float* lse, int* status, int layout, void* stream);
+MCA_API int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
+                                       int T, int D, void* y, float* lse, int* status, int layout,
+                                       const uint32_t* mask_bits, int mask_mode, void* stream);
 MCA_API int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, const void* y, const void* dy,
                                         const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
                                         int T, int D, void* dq, void* dk, void* dv, int* status, int layout,
+                                        void* stream);
+MCA_API int mca_sdpa_backward_tc_masked(const void* q, const void* k, const void* v, const void* y, const void* dy,
+                                        const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
+                                        int T, int D, void* dq, void* dk, void* dv, int* status, int layout,
+                                        const uint32_t* mask_bits, const uint32_t* mask_bits_t, int mask_mode,
                                         void* stream);
 
 /* Head-parallel forward whose epilogue is also the exchange: every finished 16-byte piece of the output

@@ -59,7 +59,13 @@ SIGNATURES = {
     "mca_sdpa_forward_f32_tc_workspace_bytes": (_i64, [_i, _i, _i]),
     "mca_sdpa_forward_f32_tc_supported": (_i, [_i]),
     "mca_sdpa_forward_f32_tc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _vp]),
+    "mca_sdpa_forward_f32_tc_masked": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _vp, _i, _vp]),
+    "mca_sdpa_forward_tc_masked": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "mca_mask_bits_row_words": (_i, [_i]),
+    "mca_mask_pack": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "mca_sdpa_backward_f32_tc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _vp, _i, _vp]),
+    "mca_sdpa_backward_f32_tc_masked": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _vp, _i, _vp, _vp, _i, _vp]),
+    "mca_sdpa_backward_tc_masked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp]),
     "mca_wait_probe": (_i, [_vp, _i, _vp]),
     "mca_sdpa_forward_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "mca_host_pipeline_chunk": (_i, [_i, _i, _i, _i]),

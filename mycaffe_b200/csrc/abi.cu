@@ -40,6 +40,8 @@ struct AttnHandle {
   int64_t split_ws_bytes = 0;
   float* mask_ws = nullptr;    // fp32 copies for a bf16 handle that is given a (T,T) or batch mask (allocated on first use)
   size_t mask_ws_floats = 0;
+  uint32_t *mask_bits = nullptr, *mask_bits_t = nullptr;   // keep-bits of a (T,T) or batch mask for the tensor-core kernels
+  size_t mask_bits_words = 0;
   int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
   // state of the last forward, consumed by backward
   bool have_fwd = false;
@@ -50,9 +52,10 @@ struct AttnHandle {
   bool status_pending = false;  // a tensor-core launch was made in asynchronous mode and its status words are unread
   void release() {
     cudaFree(row_max); cudaFree(row_sum); cudaFree(y_copy); cudaFree(delta); cudaFree(lse); cudaFree(causal_flag);
-    cudaFree(split_ws); cudaFree(mask_ws);
+    cudaFree(split_ws); cudaFree(mask_ws); cudaFree(mask_bits); cudaFree(mask_bits_t);
     split_ws = nullptr; split_ws_bytes = 0;
     mask_ws = nullptr; mask_ws_floats = 0;
+    mask_bits = mask_bits_t = nullptr; mask_bits_words = 0;
     row_max = row_sum = y_copy = delta = lse = nullptr;
     causal_flag = nullptr;
     configured = have_fwd = false;
@@ -410,6 +413,23 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   return 0;
 }
 
+// Keep-bits of this call's (T,T) or batch mask, packed into buffers the handle owns (room for the configured block
+// size, allocated on first use).  The backward of the same handle reads what the forward packed.
+long pack_mask_bits(AttnHandle& a, const float* mask, int mode, int T) {
+  const size_t rows = (size_t)std::max(a.block, a.B);
+  const size_t need = rows * (size_t)mca_mask_bits_row_words(a.block);
+  if (a.mask_bits == nullptr || a.mask_bits_words < need) {
+    cudaFree(a.mask_bits); cudaFree(a.mask_bits_t);
+    a.mask_bits = a.mask_bits_t = nullptr; a.mask_bits_words = 0;
+    if (cudaMalloc(&a.mask_bits, need * 4) != cudaSuccess || cudaMalloc(&a.mask_bits_t, need * 4) != cudaSuccess) {
+      cudaGetLastError(); cudaFree(a.mask_bits); a.mask_bits = nullptr;
+      return ERROR_MEMORY_OUT;
+    }
+    a.mask_bits_words = need;
+  }
+  return mca_mask_pack(mask, mode, a.B, T, a.mask_bits, a.mask_bits_t, 0);
+}
+
 // fp32 room for a bf16 handle whose mask the tensor-core kernels do not apply: q, k, v, y (and, for training handles,
 // the three gradients and dY), at the configured block size.
 long ensure_mask_ws(AttnHandle& a) {
@@ -493,9 +513,12 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if (packed) { kk += C; v += 2 * C; }
     if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr))) return e;
     const bool save = a.training && T == a.block;
-    if (a.split_ws != nullptr && (mode == MCA_MASK_CAUSAL || mode == MCA_MASK_NONE)) {
-      e = mca_sdpa_forward_f32_tc(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, nullptr, nullptr, save ? a.y_copy : nullptr,
-                                  save ? a.lse : nullptr, a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, 0);
+    if (a.split_ws != nullptr) {
+      const bool bits = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;   // packed for the kernel; causal / none need nothing
+      if (bits && (e = pack_mask_bits(a, mask, mode, T))) return e;
+      e = mca_sdpa_forward_f32_tc_masked(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, nullptr, nullptr,
+                                         save ? a.y_copy : nullptr, save ? a.lse : nullptr, a.split_ws, a.split_ws_bytes,
+                                         a.causal_flag + 1, layout, bits ? a.mask_bits : nullptr, bits ? mode : MCA_MASK_NONE, 0);
       if (e) return e;
       if (save) { remember_forward(a, T, mode, layout, 0, false); a.fwd_split = true; }
       return tc_status(k, a);
@@ -520,9 +543,22 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     kk = static_cast<char*>(kk) + C * esz;
     v = static_cast<char*>(v) + 2 * C * esz;
   }
+  if (bf16 && (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH) && !(a.flags & MCA_FLAG_EXACT_FP32)) {
+    // a general or batch mask: packed into keep-bits, applied by the same tensor-core kernel
+    if ((e = pack_mask_bits(a, mask, mode, T))) return e;
+    e = mca_sdpa_forward_tc_masked(q, kk, v, MCA_DTYPE_BF16, 0, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, layout, a.mask_bits,
+                                   mode, 0);
+    if (e) return e;
+    if (a.training && T == a.block) {
+      cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
+      if (ce != cudaSuccess) return ce;
+      remember_forward(a, T, mode, layout, 0, false);
+    }
+    return tc_status(k, a);
+  }
   if (bf16 && (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH)) {
-    // The tensor-core kernels apply a causal mask or none.  A bf16 handle that is given any other mask runs the exact
-    // fp32 kernels on fp32 copies of its tensors (same mask semantics: -1e29 logits, a uniform fully-masked row).
+    // MCA_FLAG_EXACT_FP32 on a bf16 handle with such a mask: the exact fp32 kernels on fp32 copies of its tensors
+    // (same mask semantics: -1e29 logits, a uniform fully-masked row).
     if ((e = ensure_mask_ws(a))) return e;
     float* w = a.mask_ws;
     float *qf = w, *kf = packed ? w + C : w + n, *vf = packed ? w + 2 * C : w + 2 * n, *yf = w + 3 * n;
@@ -586,9 +622,17 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
       kk = static_cast<char*>(kk) + C * 2; dk = static_cast<char*>(dk) + C * 2;
       v = static_cast<char*>(v) + 2 * C * 2; dv = static_cast<char*>(dv) + 2 * C * 2;
     }
-    if (a.fwd_mask_mode == MCA_MASK_TT || a.fwd_mask_mode == MCA_MASK_BATCH) {
-      // the forward ran the exact fp32 kernels on fp32 copies (a mask the tensor-core kernels do not apply): so does
-      // this; the mask is looked up again by the handle the forward was given
+    const bool fwd_masked = a.fwd_mask_mode == MCA_MASK_TT || a.fwd_mask_mode == MCA_MASK_BATCH;
+    if (fwd_masked && a.fwd_mask_handle == 0) {
+      // the forward applied the mask on the tensor cores from the keep-bits it packed into the handle: so does this
+      e = mca_sdpa_backward_tc_masked(q, kk, v, a.y_copy, dy, a.lse, a.delta, MCA_DTYPE_BF16, 0, a.B, a.H, T, a.D, dq, dk, dv,
+                                      a.causal_flag + 1, layout, a.mask_bits, a.mask_bits_t, a.fwd_mask_mode, 0);
+      if (e) return e;
+      return tc_status(k, a);
+    }
+    if (fwd_masked) {
+      // the forward ran the exact fp32 kernels on fp32 copies (MCA_FLAG_EXACT_FP32): so does this; the mask is looked
+      // up again by the handle the forward was given
       const float* mask = nullptr;
       int mode = a.fwd_mask_mode;
       if ((e = resolve_mask(k, a, a.fwd_mask_handle, a.fwd_batch_mask, T, &mask, &mode, false))) return e;
@@ -623,8 +667,10 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   if (a.fwd_split) {
     // the forward ran on the tensor cores with split operands; so does the backward, from the halves of q, k, v that
     // forward left in the handle's workspace (the reference's Backward likewise works on what its Forward saved)
-    e = mca_sdpa_backward_f32_tc(dy, a.y_copy, a.lse, a.delta, a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, dq, dk, dv,
-                                 a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, 0);
+    const bool bits = a.fwd_mask_mode == MCA_MASK_TT || a.fwd_mask_mode == MCA_MASK_BATCH;   // packed by the forward
+    e = mca_sdpa_backward_f32_tc_masked(dy, a.y_copy, a.lse, a.delta, a.fwd_mask_mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, dq, dk,
+                                        dv, a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, bits ? a.mask_bits : nullptr,
+                                        bits ? a.mask_bits_t : nullptr, bits ? a.fwd_mask_mode : MCA_MASK_NONE, 0);
     if (e) return e;
     return tc_status(k, a);
   }

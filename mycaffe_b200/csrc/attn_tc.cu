@@ -126,10 +126,21 @@ struct TcParams {
   float* row_max;
   float* row_sum;
   float* y_copy;      // second copy of the fp32 output, (B*H, T, HD) contiguous, or null
+  // MASKED: keep-bits of the caller's mask, one bit per (row, key), rows padded to whole 128-key tiles; the words of
+  // query row r, batch item b and key tile j start at mask_bits + b * mask_batch_stride + r * mask_row_stride + 4 j
+  // (a (B,T) key mask has row stride 0, a (T,T) mask batch stride 0)
+  const uint32_t* mask_bits;
+  int64_t mask_batch_stride, mask_row_stride;
 };
 
+// The logit a masked entry is given, in the log2 domain of the softmax.  The reference writes -1e29 over the scaled
+// logit (attn.cu:302-311, math.cu mask kernels): any finite value far below every real logit gives the same result --
+// probability exactly 0 next to an unmasked key, a uniform row when every key is masked.  2^17 keeps the product
+// masked_logit x scale exact to 2^-7, so that the exponent of a fully masked row is 0 +- 0.01.
+constexpr float MASKED_LOG2 = -131072.0f;
+
 // MODE_TF32: P is handed to the second product as fp32 in place of S; MODE_TF32 and MODE_SPLIT write fp32 output.
-template <int HD, int MODE>
+template <int HD, int MODE, bool MASKED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
@@ -414,6 +425,22 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (kj >= T || (p.causal && kj > qi)) s[i] = 0xff800000u;  // -inf
         }
       }
+      if constexpr (MASKED) {
+        // the caller's mask: this thread's two rows x 128 keys of keep-bits (key 8g + 2 quad + e is bit
+        // 8 (g & 3) + 2 quad + e of word g >> 2); a masked logit becomes the same finite value everywhere
+        const uint32_t masked_s = __float_as_uint(MASKED_LOG2 / scale_log2);
+        const uint32_t* mrow = p.mask_bits + (int64_t)bi * p.mask_batch_stride + 4 * j;
+        const uint4 mb0 = __ldg(reinterpret_cast<const uint4*>(mrow + (int64_t)min(qrow0 + r0, T - 1) * p.mask_row_stride));
+        const uint4 mb1 = __ldg(reinterpret_cast<const uint4*>(mrow + (int64_t)min(qrow0 + r0 + 8, T - 1) * p.mask_row_stride));
+        const uint32_t w0[4] = {mb0.x >> (2 * quad), mb0.y >> (2 * quad), mb0.z >> (2 * quad), mb0.w >> (2 * quad)};
+        const uint32_t w1[4] = {mb1.x >> (2 * quad), mb1.y >> (2 * quad), mb1.z >> (2 * quad), mb1.w >> (2 * quad)};
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int g = i >> 2, e = i & 1;
+          const uint32_t w = ((i >> 1) & 1) ? w1[g >> 2] : w0[g >> 2];
+          if (((w >> (8 * (g & 3) + e)) & 1u) == 0u && s[i] != 0xff800000u) s[i] = masked_s;
+        }
+      }
       float mx[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -653,7 +680,13 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
         }
-        if (half == 0 && p.lse != nullptr && qi < T) p.lse[(int64_t)bh * T + qi] = red_m[row] + log2f(lsum) - (SPLIT ? 6.0f : 0.0f);
+        if (half == 0 && p.lse != nullptr && qi < T) {
+          float lse_row = red_m[row] + log2f(lsum) - (SPLIT ? 6.0f : 0.0f);
+          // a row whose every key is masked has uniform probabilities 1 / T; its log-sum-exp cannot carry that next
+          // to the masked logit's magnitude, so the backward is told by +inf instead
+          if (MASKED && red_m[row] < 0.5f * MASKED_LOG2) lse_row = INFINITY;
+          p.lse[(int64_t)bh * T + qi] = lse_row;
+        }
         if constexpr (SPLIT) {
           // what the exact fp32 backward needs to recompute P = exp(s - row_max) / row_sum: the exponent's reference
           // point in natural-log units (it need not be the true maximum) and the sum taken against it
@@ -683,7 +716,8 @@ struct SplitExtras {
 template <int HD, int MODE>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
               int* status, int layout, cudaStream_t st, void* const* y_more = nullptr, int n_more = 0,
-              const McaStrides* y_strides = nullptr, const SplitExtras* split = nullptr) {
+              const McaStrides* y_strides = nullptr, const SplitExtras* split = nullptr, const McaMaskBits* mask = nullptr) {
+  if (mask != nullptr && (MODE == MODE_TF32 || causal)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   CUtensorMap mq, mk, mv;
   int e;
   const McaStrides sin = mca_in_strides(layout, H, T, HD);
@@ -722,15 +756,26 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.row_sum = split ? split->row_sum : nullptr;
   p.y_copy = split ? split->y_copy : nullptr;
   const size_t smem = Plan<MODE == MODE_SPLIT ? 256 : HD * (MODE == MODE_TF32 ? 4 : 2)>::BYTES;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  p.mask_bits = mask ? mask->bits : nullptr;
+  p.mask_batch_stride = mask ? mask->batch_stride : 0;
+  p.mask_row_stride = mask ? mask->row_stride : 0;
   dim3 grid(mca_ceil_div(T, NQT * BLK), B * H);
-  sdpa_fwd_tc_kernel<HD, MODE><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
+  if constexpr (MODE != MODE_TF32) {
+    if (mask != nullptr) {
+      MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sdpa_fwd_tc_kernel<HD, MODE, true><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
+      return mca_launch_status();
+    }
+  }
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  sdpa_fwd_tc_kernel<HD, MODE, false><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
   return mca_launch_status();
 }
 
 template <int HD>
 int launch_split(const float* q, const float* k, const float* v, int causal, int B, int H, int T, float* y, float* row_max,
-                 float* row_sum, float* y_copy, float* lse, void* workspace, int* status, int layout, cudaStream_t st) {
+                 float* row_sum, float* y_copy, float* lse, void* workspace, int* status, int layout, cudaStream_t st,
+                 const McaMaskBits* mask = nullptr) {
   const int64_t rows = (int64_t)B * H * T;
   const split::Workspace w = split::carve(workspace, rows);
   split::Job job;
@@ -741,7 +786,7 @@ int launch_split(const float* q, const float* k, const float* v, int causal, int
   SplitExtras ex;
   ex.fac = w.fac; ex.row_max = row_max; ex.row_sum = row_sum; ex.y_copy = y_copy;
   return launch_tc<HD, MODE_SPLIT>(w.tensor[0], w.tensor[1], w.tensor[2], causal, B, H, T, y, lse, status, layout, st, nullptr, 0,
-                                   nullptr, &ex);
+                                   nullptr, &ex, mask);
 }
 
 }  // namespace
@@ -783,6 +828,17 @@ int mca_sdpa_forward_tc_scatter(const void* q, const void* k, const void* v, int
 
 int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T,
                                int D, void* y, float* lse, int* status, int layout, void* stream) {
+  return mca_sdpa_forward_tc_masked(q, k, v, dtype, causal, B, H, T, D, y, lse, status, layout, nullptr, MCA_MASK_NONE, stream);
+}
+
+int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
+                               void* y, float* lse, int* status, int layout, const uint32_t* mask_bits, int mask_mode,
+                               void* stream) {
+  McaMaskBits mb;
+  const McaMaskBits* mask = nullptr;
+  int me = mca_mask_bits_view(mask_bits, nullptr, mask_mode, T, false, &mb, &mask);
+  if (me) return me;
+  if (mask != nullptr && dtype != MCA_DTYPE_BF16) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
@@ -797,8 +853,8 @@ int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int 
     if (D == 64) return launch_tc<64, MODE_TF32>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
   }
-  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
-  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
+  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
+  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }
 
@@ -812,6 +868,18 @@ int mca_sdpa_forward_f32_tc_supported(int D) { return D == 16 || D == 32 || D ==
 int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D, float* y,
                             float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
                             int64_t workspace_bytes, int* status, int layout, void* stream) {
+  return mca_sdpa_forward_f32_tc_masked(q, k, v, causal, B, H, T, D, y, row_max, row_sum, y_copy, lse, workspace, workspace_bytes,
+                                        status, layout, nullptr, MCA_MASK_NONE, stream);
+}
+
+int mca_sdpa_forward_f32_tc_masked(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D,
+                                   float* y, float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
+                                   int64_t workspace_bytes, int* status, int layout, const uint32_t* mask_bits, int mask_mode,
+                                   void* stream) {
+  McaMaskBits mb;
+  const McaMaskBits* mask = nullptr;
+  int me = mca_mask_bits_view(mask_bits, nullptr, mask_mode, T, false, &mb, &mask);
+  if (me) return me;
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !status || !workspace) return ERROR_PARAM_NULL;
   if ((row_max == nullptr) != (row_sum == nullptr)) return ERROR_PARAM_NULL;
@@ -824,9 +892,61 @@ int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int 
   if (reinterpret_cast<uintptr_t>(workspace) & 15) return ERROR_PARAM_OUT_OF_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   switch (D) {
-    case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
-    case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
-    case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st);
+    case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
+    case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
+    case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Keep-bits of a float mask for the tensor-core kernels.  One warp per output word: bit i of word w of row r is
+// mask[r][32 w + i] != 0 (keys beyond T: 0); the transposed form has bit i of word w of key k = mask[32 w + i][k] != 0.
+// Rows are padded to whole 128-key tiles (mca_mask_bits_row_words(T) words).
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) mask_pack_kernel(const float* __restrict__ mask, int rows, int T, int wpr,
+                                                        uint32_t* __restrict__ bits, uint32_t* __restrict__ bits_t) {
+  const int64_t word = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (word >= (int64_t)rows * wpr) return;
+  const int r = (int)(word / wpr), w = (int)(word - (int64_t)r * wpr);
+  const int c = 32 * w + lane;
+  const uint32_t keep = __ballot_sync(0xffffffffu, c < T && mask[(int64_t)r * T + c] != 0.f);
+  if (lane == 0) bits[word] = keep;
+  if (bits_t != nullptr) {   // square mask: the same word position of the transpose
+    const uint32_t keep_t = __ballot_sync(0xffffffffu, c < T && mask[(int64_t)c * T + r] != 0.f);
+    if (lane == 0) bits_t[word] = keep_t;
+  }
+}
+}  // namespace
+
+int mca_mask_bits_row_words(int T) { return T > 0 ? mca_ceil_div(T, 128) * 4 : 0; }
+
+int mca_mask_bits_view(const uint32_t* bits, const uint32_t* bits_t, int mask_mode, int T, int need_transpose, McaMaskBits* out,
+                       const McaMaskBits** view) {
+  *view = nullptr;
+  if (mask_mode == MCA_MASK_NONE || mask_mode == MCA_MASK_CAUSAL) return bits == nullptr ? 0 : ERROR_PARAM_OUT_OF_RANGE;
+  if (mask_mode != MCA_MASK_TT && mask_mode != MCA_MASK_BATCH) return ERROR_PARAM_OUT_OF_RANGE;
+  if (bits == nullptr || (mask_mode == MCA_MASK_TT && need_transpose && bits_t == nullptr)) return ERROR_PARAM_NULL;
+  if ((reinterpret_cast<uintptr_t>(bits) | reinterpret_cast<uintptr_t>(bits_t)) & 15) return ERROR_PARAM_OUT_OF_RANGE;
+  const int wpr = mca_mask_bits_row_words(T);
+  out->bits = bits;
+  out->bits_t = mask_mode == MCA_MASK_TT ? bits_t : nullptr;
+  out->row_stride = mask_mode == MCA_MASK_TT ? wpr : 0;
+  out->batch_stride = mask_mode == MCA_MASK_BATCH ? wpr : 0;
+  *view = out;
+  return 0;
+}
+
+int mca_mask_pack(const float* mask, int mask_mode, int B, int T, uint32_t* bits, uint32_t* bits_t, void* stream) {
+  if (!mask || !bits) return ERROR_PARAM_NULL;
+  if (T <= 0 || B <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  if (mask_mode != MCA_MASK_TT && mask_mode != MCA_MASK_BATCH) return ERROR_PARAM_OUT_OF_RANGE;
+  const int rows = mask_mode == MCA_MASK_TT ? T : B, wpr = mca_mask_bits_row_words(T);
+  const int64_t words = (int64_t)rows * wpr;
+  mask_pack_kernel<<<(unsigned)((words + 7) / 8), 256, 0, (cudaStream_t)stream>>>(mask, rows, T, wpr, bits,
+                                                                               mask_mode == MCA_MASK_TT ? bits_t : nullptr);
+  return mca_launch_status();
 }

@@ -86,6 +86,15 @@ struct BwdParams {
   float scale_log2;    // (1/sqrt(HD)) * log2(e)
   float scale;         // 1/sqrt(HD)
   McaStrides os;       // element strides of the gradient views dQ, dK, dV
+  // MASKED: keep-bits of the caller's mask as the forward kernel reads them (word of query row r, key tile j, quarter
+  // c: mask_bits[b * batch_stride + r * row_stride + 4 j + c]) and, for a (T,T) mask, their transpose (word of key k,
+  // query tile i, quarter c: mask_bits_t[k * row_stride + 4 i + c]); a (B,T) key mask has row stride 0 and no transpose.
+  // A masked entry has probability 0, or 1 / T in a row whose every key is masked (the forward marks those rows
+  // with lse = +inf).
+  const uint32_t* mask_bits;
+  const uint32_t* mask_bits_t;
+  int64_t mask_batch_stride, mask_row_stride;
+  float inv_T;
 };
 
 __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
@@ -118,7 +127,7 @@ enum DqBar : int {
   DQ_BAR_COUNT = 16
 };
 
-template <int HD, bool SPLIT>
+template <int HD, bool SPLIT, bool MASKED>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -294,6 +303,12 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (lane == 0) mbar_arrive(bar(DQ_SDP_FREE));
       const int k0 = j * BLK + qtr * 32;
       const bool edge = (p.causal && j * BLK + BLK - 1 > q0) || (j * BLK + BLK > T);
+      uint32_t mw = 0xffffffffu;          // keep-bits of this thread's 32 keys
+      float p_masked = 0.f;
+      if constexpr (MASKED) {
+        mw = __ldg(p.mask_bits + (int64_t)bi * p.mask_batch_stride + (int64_t)min(qi, T - 1) * p.mask_row_stride + 4 * j + qtr);
+        p_masked = (row_ok && lse == INFINITY) ? p.inv_T : 0.f;
+      }
       // dS = P o (dP - delta) scale with P = 2^(S scale_log2 - lse); adjacent keys go through as fp32 pairs.
       // Split mode: S and dP carry the pre-pass's scales; dS is kept in the units of dP' x 2^-19 and the factor
       // scale x 2^19 / (s_dy s_v s_k) is applied once to dQ.
@@ -309,7 +324,12 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int i = 0; i < 32; i += 2) {
         const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
         const float2 g = ffma2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ps2, nd2);
-        const float2 d = ffma2(make_float2(fast_exp2(x.x), fast_exp2(x.y)), g, zero2);
+        float e0 = fast_exp2(x.x), e1 = fast_exp2(x.y);
+        if constexpr (MASKED) {
+          if (((mw >> i) & 1u) == 0u) e0 = p_masked;
+          if (((mw >> (i + 1)) & 1u) == 0u) e1 = p_masked;
+        }
+        const float2 d = ffma2(make_float2(e0, e1), g, zero2);
         float d0 = d.x, d1 = d.y;
         if (edge) {
           const int kj = k0 + i;
@@ -390,7 +410,7 @@ enum KvBar : int {
   KV_BAR_COUNT = 18
 };
 
-template <int HD, bool SPLIT>
+template <int HD, bool SPLIT, bool MASKED>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -621,6 +641,13 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const float* nlse_s = s_nlse[it & 1] + q_local;
       const float* del_s = s_del[it & 1] + q_local;
       const bool diag = p.causal && (i_begin + it) * BLK < k0 + BLK;   // only the diagonal tile needs the causal test
+      uint32_t mw = 0xffffffffu;          // keep-bits of this thread's key against its 32 queries of the step
+      if constexpr (MASKED) {
+        if (p.mask_bits_t != nullptr)
+          mw = __ldg(p.mask_bits_t + (int64_t)min(kj, T - 1) * p.mask_row_stride + 4 * (i_begin + it) + qtr);
+        else
+          mw = ((__ldg(p.mask_bits + (int64_t)bi * p.mask_batch_stride + (min(kj, T - 1) >> 5)) >> (kj & 31)) & 1u) ? 0xffffffffu : 0u;
+      }
       // pass 1: P^T = 2^(S^T scale - lse), kept in fp32 for pass 2, packed to bf16 over S^T (fp32 pairs)
       const float2 sc2 = make_float2(sl2, sl2), ps2 = make_float2(dmul, dmul);
       const float2 zero2 = make_float2(0.f, 0.f);
@@ -637,6 +664,12 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           const float2 x = ffma2(make_float2(__uint_as_float(s[i + e]), __uint_as_float(s[i + e + 1])), sc2,
                                  make_float2(nls[e], nls[e + 1]));
           float v0 = fast_exp2(x.x), v1 = fast_exp2(x.y);
+          if constexpr (MASKED) {
+            // a masked entry: 0, or 1 / T in a fully masked row (staged -lse = -inf; rows beyond T are staged the same
+            // way and stay 0)
+            if (((mw >> (i + e)) & 1u) == 0u) v0 = (nls[e] == -INFINITY && q_base + i + e < T) ? p.inv_T : 0.f;
+            if (((mw >> (i + e + 1)) & 1u) == 0u) v1 = (nls[e + 1] == -INFINITY && q_base + i + e + 1 < T) ? p.inv_T : 0.f;
+          }
           if (!key_ok || (diag && kj > q_base + i + e)) v0 = 0.f;
           if (!key_ok || (diag && kj > q_base + i + e + 1)) v1 = 0.f;
           s[i + e] = __float_as_uint(v0);
@@ -751,9 +784,37 @@ __global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, cons
   if (lane == 0) delta[row] = acc;
 }
 
+// Both kernels of one backward, with or without the caller's mask.
+template <int HD, bool SPLIT, bool MASKED>
+int launch_bwd_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo, BwdParams p,
+                    void* dq, void* dk, void* dv, int B, int H, int T, cudaStream_t st) {
+  using PL = BwdPlan<SPLIT ? 128 : HD>;
+  const size_t smem_kv = PL::BYTES_KV, smem_dq = PL::BYTES_DQ;
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD, SPLIT, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, SPLIT, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
+  dim3 grid(mca_ceil_div(T, BLK), B * H);
+  p.out0 = dk; p.out1 = dv;
+  sdpa_bwd_dkdv_tc_kernel<HD, SPLIT, MASKED><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
+  int e = mca_launch_status();
+  if (e) return e;
+  p.out0 = dq; p.out1 = nullptr;
+  sdpa_bwd_dq_tc_kernel<HD, SPLIT, MASKED><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
+  return mca_launch_status();
+}
+
+void set_mask(BwdParams& p, const McaMaskBits* mask, int T) {
+  p.mask_bits = mask ? mask->bits : nullptr;
+  p.mask_bits_t = mask ? mask->bits_t : nullptr;
+  p.mask_batch_stride = mask ? mask->batch_stride : 0;
+  p.mask_row_stride = mask ? mask->row_stride : 0;
+  p.inv_T = 1.0f / (float)T;
+}
+
 template <int HD>
 int launch_bwd(const void* q, const void* k, const void* v, const void* dy, const float* lse, const float* delta,
-               int causal, int B, int H, int T, void* dq, void* dk, void* dv, int* status, int layout, cudaStream_t st) {
+               int causal, int B, int H, int T, void* dq, void* dk, void* dv, int* status, int layout, cudaStream_t st,
+               const McaMaskBits* mask = nullptr) {
+  if (mask != nullptr && causal) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   CUtensorMap mq, mk, mv, mdo;
   int e;
   const McaStrides sin = mca_in_strides(layout, H, T, HD), sout = mca_out_strides(layout, H, T, HD);
@@ -771,16 +832,9 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
   p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
-  const size_t smem_kv = BwdPlan<HD>::BYTES_KV, smem_dq = BwdPlan<HD>::BYTES_DQ;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
-  dim3 grid(mca_ceil_div(T, BLK), B * H);
-  p.out0 = dk; p.out1 = dv;
-  sdpa_bwd_dkdv_tc_kernel<HD, false><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
-  if ((e = mca_launch_status())) return e;
-  p.out0 = dq; p.out1 = nullptr;
-  sdpa_bwd_dq_tc_kernel<HD, false><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
-  return mca_launch_status();
+  set_mask(p, mask, T);
+  if (mask != nullptr) return launch_bwd_pair<HD, false, true>(mq, mk, mv, mdo, p, dq, dk, dv, B, H, T, st);
+  return launch_bwd_pair<HD, false, false>(mq, mk, mv, mdo, p, dq, dk, dv, B, H, T, st);
 }
 
 // delta[row] = sum_c dY[row][c] * Y[row][c] in fp32: dY in the output layout, Y the handle's contiguous copy.
@@ -802,7 +856,9 @@ __global__ void bwd_delta_f32_kernel(const float* __restrict__ dy, const float* 
 // wrote; dY is split here.
 template <int HD>
 int launch_bwd_split(const float* dy, const float* y_copy, const float* lse, float* delta, int causal, int B, int H, int T,
-                     float* dq, float* dk, float* dv, void* workspace, int* status, int layout, cudaStream_t st) {
+                     float* dq, float* dk, float* dv, void* workspace, int* status, int layout, cudaStream_t st,
+                     const McaMaskBits* mask = nullptr) {
+  if (mask != nullptr && causal) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   const int64_t rows = (int64_t)B * H * T;
   const split::Workspace w = split::carve(workspace, rows);
   const McaStrides sin = mca_in_strides(layout, H, T, HD), sout = mca_out_strides(layout, H, T, HD);
@@ -830,16 +886,9 @@ int launch_bwd_split(const float* dy, const float* y_copy, const float* lse, flo
   p.os = sin;
   p.scale = 1.0f / sqrtf((float)HD);
   p.scale_log2 = p.scale * 1.4426950408889634f;
-  const size_t smem_kv = BwdPlan<128>::BYTES_KV, smem_dq = BwdPlan<128>::BYTES_DQ;
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dkdv_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
-  dim3 grid(mca_ceil_div(T, BLK), B * H);
-  p.out0 = dk; p.out1 = dv;
-  sdpa_bwd_dkdv_tc_kernel<HD, true><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
-  if ((e = mca_launch_status())) return e;
-  p.out0 = dq; p.out1 = nullptr;
-  sdpa_bwd_dq_tc_kernel<HD, true><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
-  return mca_launch_status();
+  set_mask(p, mask, T);
+  if (mask != nullptr) return launch_bwd_pair<HD, true, true>(mq, mk, mv, mdo, p, dq, dk, dv, B, H, T, st);
+  return launch_bwd_pair<HD, true, false>(mq, mk, mv, mdo, p, dq, dk, dv, B, H, T, st);
 }
 
 }  // namespace
@@ -854,6 +903,18 @@ int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void
 int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, const void* y, const void* dy,
                                 const float* lse, float* delta_scratch, int dtype, int causal, int B, int H, int T, int D,
                                 void* dq, void* dk, void* dv, int* status, int layout, void* stream) {
+  return mca_sdpa_backward_tc_masked(q, k, v, y, dy, lse, delta_scratch, dtype, causal, B, H, T, D, dq, dk, dv, status, layout,
+                                     nullptr, nullptr, MCA_MASK_NONE, stream);
+}
+
+int mca_sdpa_backward_tc_masked(const void* q, const void* k, const void* v, const void* y, const void* dy, const float* lse,
+                                float* delta_scratch, int dtype, int causal, int B, int H, int T, int D, void* dq, void* dk,
+                                void* dv, int* status, int layout, const uint32_t* mask_bits, const uint32_t* mask_bits_t,
+                                int mask_mode, void* stream) {
+  McaMaskBits mb;
+  const McaMaskBits* mask = nullptr;
+  int me = mca_mask_bits_view(mask_bits, mask_bits_t, mask_mode, T, true, &mb, &mask);
+  if (me) return me;
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!q || !k || !v || !y || !dy || !lse || !delta_scratch || !dq || !dk || !dv || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
@@ -869,13 +930,25 @@ int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, con
                                                                    mca_out_strides(layout, H, T, D), delta_scratch);
   int e = mca_launch_status();
   if (e) return e;
-  if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
-  return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st);
+  if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st, mask);
+  return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st, mask);
 }
 
 int mca_sdpa_backward_f32_tc(const float* dy, const float* y_copy, const float* lse, float* delta_scratch, int causal, int B,
                              int H, int T, int D, float* dq, float* dk, float* dv, void* workspace, int64_t workspace_bytes,
                              int* status, int layout, void* stream) {
+  return mca_sdpa_backward_f32_tc_masked(dy, y_copy, lse, delta_scratch, causal, B, H, T, D, dq, dk, dv, workspace, workspace_bytes,
+                                         status, layout, nullptr, nullptr, MCA_MASK_NONE, stream);
+}
+
+int mca_sdpa_backward_f32_tc_masked(const float* dy, const float* y_copy, const float* lse, float* delta_scratch, int causal,
+                                    int B, int H, int T, int D, float* dq, float* dk, float* dv, void* workspace,
+                                    int64_t workspace_bytes, int* status, int layout, const uint32_t* mask_bits,
+                                    const uint32_t* mask_bits_t, int mask_mode, void* stream) {
+  McaMaskBits mb;
+  const McaMaskBits* mask = nullptr;
+  int me = mca_mask_bits_view(mask_bits, mask_bits_t, mask_mode, T, true, &mb, &mask);
+  if (me) return me;
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!dy || !y_copy || !lse || !delta_scratch || !dq || !dk || !dv || !workspace || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
@@ -886,9 +959,9 @@ int mca_sdpa_backward_f32_tc(const float* dy, const float* y_copy, const float* 
     return ERROR_PARAM_OUT_OF_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   switch (D) {
-    case 16: return launch_bwd_split<16>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
-    case 32: return launch_bwd_split<32>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
-    case 64: return launch_bwd_split<64>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st);
+    case 16: return launch_bwd_split<16>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st, mask);
+    case 32: return launch_bwd_split<32>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st, mask);
+    case 64: return launch_bwd_split<64>(dy, y_copy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, workspace, status, layout, st, mask);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

@@ -48,6 +48,14 @@ enum McaMaskMode : int {
   MCA_MASK_CAUSAL = 3,  // analytic lower triangle: same result as a tril(ones) MCA_MASK_TT mask
 };
 
+// Keep-bits of a caller's mask as the tensor-core kernels read them (mca_mask_pack): the words of query row r of batch
+// item b for key tile j start at bits + b * batch_stride + r * row_stride + 4 j; bits_t is the transpose of a (T,T) mask.
+struct McaMaskBits {
+  const uint32_t* bits;
+  const uint32_t* bits_t;
+  int64_t batch_stride, row_stride;
+};
+
 // Element strides of a (B, H, T, D) view whose head dimension is contiguous.
 struct McaStrides {
   int64_t b, h, t;

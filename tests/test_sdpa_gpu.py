@@ -251,14 +251,16 @@ def test_bf16_tensor_core_accepts_causal_mask_handle(cuda):
     general = np.ones((T, T), np.float32) - np.eye(T, dtype=np.float32)
     general[5] = 0.0                                          # one fully masked row
     keys = (rng.random((B, T)) > 0.3).astype(np.float32)      # batch mask: keys kept per batch item
-    for mask, mode, batch in ((general, 1, False), (keys, 2, True)):
-        b = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16)
-        y = b.forward(q, k, v, mask, batch_mask=batch)
-        assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, mode, f64=True)) < BF16_TOL
-        got = b.backward(dy)
-        for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
-            assert rel_err(g_, r_) < BF16_TOL
-        b.close()
+    # on the tensor cores (keep-bits), and with MCA_FLAG_EXACT_FP32 through the exact fp32 kernels on fp32 copies
+    for flags in (None, ids.MCA_FLAG_EXACT_FP32):
+        for mask, mode, batch in ((general, 1, False), (keys, 2, True)):
+            b = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16, flags=flags)
+            y = b.forward(q, k, v, mask, batch_mask=batch)
+            assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, mode, f64=True)) < BF16_TOL
+            got = b.backward(dy)
+            for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
+                assert rel_err(g_, r_) < BF16_TOL
+            b.close()
     b = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16)      # inference handle: forward only
     y = b.forward(q, k, v, general)
     assert rel_err(y, oracle.sdpa_forward(q, k, v, general, 1, f64=True)) < BF16_TOL
@@ -501,3 +503,25 @@ def test_scatter_epilogue_writes_every_destination(cuda):
     assert np.all(cuda.GetMemory(hst, 8).view(np.int32)[:4] == 0)
     for h in [hq, hk, hv, hst] + dst:
         cuda.FreeMemory(h)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [200, 640])
+def test_bf16_tensor_core_general_and_batch_masks(cuda, T, D):
+    """bf16 handles with the reference's other mask forms over several key tiles: random (T,T) mask with a fully masked
+    row, (B,T) key mask with a batch item that masks everything; forward and backward on the tensor cores."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(T + D)
+    B, H = 2, 2
+    q, k, v, dy = (bf16_round(a) for a in (*rand_qkv(rng, B, H, T, D), rng.standard_normal((B, H, T, D)).astype(np.float32)))
+    general = (rng.random((T, T)) > 0.5).astype(np.float32)
+    general[T // 4] = 0.0
+    keys = (rng.random((B, T)) > 0.3).astype(np.float32)
+    keys[B - 1] = 0.0
+    for mask, mode, batch in ((general, 1, False), (keys, 2, True)):
+        a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_BF16)
+        y = a.forward(q, k, v, mask, batch_mask=batch)
+        assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, mode, f64=True)) < BF16_TOL
+        for g_, r_ in zip(a.backward(dy), oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
+            assert rel_err(g_, r_) < BF16_TOL
+        a.close()

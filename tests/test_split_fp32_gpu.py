@@ -142,7 +142,7 @@ def test_default_fp32_handle_uses_it_and_the_flag_switches_it_off(cuda):
         a.close()
     assert rel_err(outs["default"], ref) < SPLIT_TOL
     assert not np.array_equal(outs["default"], outs["exact"])     # two different kernels ran
-    # a general (non-causal) mask keeps to the CUDA-core kernel on the default handle
+    # a general (non-causal) mask is packed into keep-bits and applied by the same tensor-core kernel
     band = np.triu(mask, -5).astype(np.float32)
     a = Sdpa(cuda, B, T, H, D)
     assert rel_err(a.forward(q, k, v, band), oracle.sdpa_forward(q, k, v, band, 1, f64=True)) < 2e-5
@@ -191,3 +191,38 @@ def test_split_backward_gradient_scales_and_packed_layout(dy_scale):
     got_p = run_raw(q, k, v, True, dy=dy, layout=1)[1:]
     for a_, b_ in zip(got, got_p):
         np.testing.assert_array_equal(a_, b_)
+
+
+def _masks(rng, B, T):
+    """A general (T,T) mask with ragged rows, one fully masked row and one fully kept row; a (B,T) key mask whose last
+    batch item masks every key."""
+    general = (rng.random((T, T)) > 0.4).astype(np.float32)
+    general[T // 3] = 0.0
+    general[T // 2] = 1.0
+    keys = (rng.random((B, T)) > 0.3).astype(np.float32)
+    keys[B - 1] = 0.0
+    return ((general, 1, False), (keys, 2, True))
+
+
+@pytest.mark.parametrize("D", [16, 32, 64])
+@pytest.mark.parametrize("T", [8, 200, 384, 1000])
+def test_default_fp32_handle_with_general_and_batch_masks(cuda, T, D):
+    """The reference's other mask forms (apply_mask / apply_mask_batch, attn.cu:302-311) on the split-operand
+    tensor-core kernels: forward and backward against the fp64 oracle, including rows whose every key is masked (the
+    reference's -1e29 makes them uniform) and, with the batch mask, a batch item without a single visible key."""
+    rng = np.random.default_rng(5 * T + D)
+    B, H = 3, 2
+    q, k, v, dy = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(4))
+    for mask, mode, batch in _masks(rng, B, T):
+        a = Sdpa(cuda, B, T, H, D, training=True)
+        y = a.forward(q, k, v, mask, batch_mask=batch)
+        assert rel_err(y, oracle.sdpa_forward(q, k, v, mask, mode, f64=True)) < SPLIT_TOL
+        for name, g_, r_ in zip("qkv", a.backward(dy), oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
+            assert rel_err(g_, r_) < SPLIT_TOL, (name, mode)
+        a.close()
+    # the fully masked row is the mean of V
+    general = _masks(np.random.default_rng(5 * T + D), B, T)[0][0]
+    a = Sdpa(cuda, B, T, H, D)
+    y = a.forward(q, k, v, general)
+    np.testing.assert_allclose(y[:, :, T // 3], v.mean(axis=2), atol=2e-5)
+    a.close()
