@@ -226,3 +226,49 @@ def test_default_fp32_handle_with_general_and_batch_masks(cuda, T, D):
     y = a.forward(q, k, v, general)
     np.testing.assert_allclose(y[:, :, T // 3], v.mean(axis=2), atol=2e-5)
     a.close()
+
+
+def test_masked_entry_points_are_what_the_handle_runs(cuda):
+    """mca_mask_pack + mca_sdpa_forward_f32_tc_masked called directly give bit for bit what ATTN_FWD on a default handle
+    returns for the same mask: the handle runs the tensor-core kernel, not the CUDA-core one."""
+    import torch
+    from mycaffe_b200 import _lib, function_ids as ids
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(77)
+    B, H, T, D = 2, 3, 300, 64
+    q, k, v = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(3))
+    keys = (rng.random((B, T)) > 0.3).astype(np.float32)
+    qd, kd, vd, md = (torch.from_numpy(a).to(dev) for a in (q, k, v, keys))
+    wpr = lib.mca_mask_bits_row_words(T)
+    assert wpr == 4 * ((T + 127) // 128)
+    bits = torch.zeros(B * wpr, dtype=torch.int32, device=dev)
+    assert lib.mca_mask_pack(md.data_ptr(), 2, B, T, bits.data_ptr(), None, None) == 0
+    torch.cuda.synchronize()
+    packed = bits.cpu().numpy().view(np.uint32).reshape(B, wpr)
+    for b in range(B):
+        for j in (0, 31, 32, T - 1):
+            assert (packed[b, j // 32] >> (j % 32)) & 1 == int(keys[b, j] != 0)
+    assert packed[:, (T + 31) // 32:].sum() == 0                      # nothing beyond T
+    y = torch.empty(B * H * T * D, device=dev)
+    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
+    ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+    wp = (ws.data_ptr() + 1023) // 1024 * 1024
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
+    rc = lib.mca_sdpa_forward_f32_tc_masked(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, B, H, T, D, y.data_ptr(), None, None, None,
+                                            None, wp, nbytes, st.data_ptr(), 0, bits.data_ptr(), 2, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and st[0].item() == 0
+    a = Sdpa(cuda, B, T, H, D)
+    via_handle = a.forward(q, k, v, keys, batch_mask=True)
+    a.close()
+    np.testing.assert_array_equal(y.cpu().numpy().reshape(B, H, T, D), via_handle)
+    e = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_F32, flags=ids.MCA_FLAG_EXACT_FP32)
+    exact = e.forward(q, k, v, keys, batch_mask=True)
+    e.close()
+    assert not np.array_equal(exact, via_handle) and rel_err(exact, via_handle) < 2e-5
+    # a mask mode without its bits, or bits with a causal call, are refused
+    assert lib.mca_sdpa_forward_f32_tc_masked(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, B, H, T, D, y.data_ptr(), None, None, None,
+                                              None, wp, nbytes, st.data_ptr(), 0, None, 2, None) == ids.ERROR_PARAM_NULL
+    assert lib.mca_sdpa_forward_f32_tc_masked(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 1, B, H, T, D, y.data_ptr(), None, None, None,
+                                              None, wp, nbytes, st.data_ptr(), 0, bits.data_ptr(), 2, None) == ids.ERROR_ATTN_UNSUPPORTED_SHAPE
