@@ -135,24 +135,33 @@ def test_mask_rewritten_in_place_is_seen(cuda, dtype):
 
 
 def test_backward_after_the_mask_was_freed_or_rewritten(cuda):
+    """The reference's Backward reads neither hMask nor anything but what its Forward left in the handle
+    (attn.cu:622-634).  The default handle does the same: its Forward packed the mask into keep-bits it owns, so the
+    mask handle may be freed before Backward.  The exact-fp32 handle recomputes the probabilities from the mask itself
+    and looks it up by handle: a freed one is an error, never a dangling pointer."""
     from mycaffe_b200 import CudaDnnError, function_ids as ids
     rng = np.random.default_rng(6)
     B, H, T, D = 1, 2, 40, 32
     q, k, v, dy = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(4))
     mask = (rng.random((T, T)) < 0.7).astype(np.float32)
     mask[np.arange(T), np.arange(T)] = 1
-    a = Sdpa(cuda, B, T, H, D, training=True)
-    a.forward(q, k, v, mask)
-    got = a.backward(dy)
-    for g_, r_ in zip(got, oracle.sdpa_backward(q, k, v, dy, mask, 1, f64=True)):
-        assert rel_err(g_, r_) < 1e-4
-    # the same address can come back from the allocator with other contents: free the mask, allocate a new one
-    cuda.FreeMemory(a.hMask)
-    a._mem.remove(a.hMask)
-    with pytest.raises(CudaDnnError) as e:
-        a.backward(dy)
-    assert e.value.code == ids.ERROR_MEMORY_NOT_FOUND
-    a.close()
+    ref = oracle.sdpa_backward(q, k, v, dy, mask, 1, f64=True)
+    for flags, freed_is_error in ((None, False), (ids.MCA_FLAG_EXACT_FP32, True)):
+        a = Sdpa(cuda, B, T, H, D, training=True, dtype=ids.MCA_DTYPE_F32 if flags else None, flags=flags)
+        a.forward(q, k, v, mask)
+        for g_, r_ in zip(a.backward(dy), ref):
+            assert rel_err(g_, r_) < 1e-4
+        # the same address can come back from the allocator with other contents: free the mask
+        cuda.FreeMemory(a.hMask)
+        a._mem.remove(a.hMask)
+        if freed_is_error:
+            with pytest.raises(CudaDnnError) as e:
+                a.backward(dy)
+            assert e.value.code == ids.ERROR_MEMORY_NOT_FOUND
+        else:
+            for g_, r_ in zip(a.backward(dy), ref):
+                assert rel_err(g_, r_) < 1e-4
+        a.close()
 
 
 # ------------------------------------------------------------------------------------------ decode positions
