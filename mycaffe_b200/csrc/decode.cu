@@ -526,7 +526,7 @@ int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_l
     // wave, where 128-key splits give 608 CTAs, i.e. two waves and sixteen stragglers.
     int64_t best_cost = INT64_MAX;
     int best_n = 1;
-    for (int n = 1; n <= (max_len + 63) / 64; ++n) {
+    for (int n = 1; n <= std::max(1, max_len / 128); ++n) {   // splits of at least 128 keys; up to 255 keys: one split, no scratch
       const int64_t len = ((max_len + n - 1) / n + 15) / 16 * 16;
       const int64_t waves = (groups * n + 295) / 296;
       const int64_t cost = waves * (64 + len);
