@@ -50,19 +50,44 @@ struct Job {
   int slot[3];           // which amax entry each one owns
 };
 
+// Where the i-th 16-byte piece of a (B, H, T, HD) view starts.  A contiguous tensor needs no index arithmetic; otherwise
+// the row index (below 2^31) is taken apart with 32-bit divisions.
+template <int HD>
+__device__ __forceinline__ const float* piece_ptr(const float* x, const McaStrides& st, bool contiguous, int H, int T, int64_t i) {
+  if (contiguous) return x + i * 4;
+  constexpr int V4 = HD / 4;
+  const unsigned row = (unsigned)(i / V4);
+  const int c = (int)(i - (int64_t)row * V4);
+  const unsigned bh = row / (unsigned)T, t = row - bh * (unsigned)T;
+  const unsigned b = bh / (unsigned)H, h = bh - b * (unsigned)H;
+  return x + (int64_t)b * st.b + (int64_t)h * st.h + (int64_t)t * st.t + c * 4;
+}
+__host__ __device__ inline bool is_contiguous(const McaStrides& st, int H, int T, int HD) {
+  return st.t == HD && st.h == (int64_t)T * HD && st.b == (int64_t)H * T * HD;
+}
+
 // amax[slot] = max |x| of each tensor
 template <int HD>
 __global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
                                                    unsigned int* __restrict__ amax) {
   const float* x = job.src[blockIdx.y];
   constexpr int V4 = HD / 4;
+  const bool contiguous = is_contiguous(st, H, T, HD);
+  const int64_t n = rows * V4, stride = (int64_t)gridDim.x * blockDim.x;
   float m = 0.f;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / V4;
-    const int c = (int)(i - row * V4);
-    const int64_t bh = row / T, t = row - bh * T;
-    const int64_t b = bh / H, h = bh - b * H;
-    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n; i += 4 * stride) {   // four independent loads in flight
+    const float4 v0 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
+    const float4 v1 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + stride));
+    const float4 v2 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + 2 * stride));
+    const float4 v3 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + 3 * stride));
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))));
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v2.x), fabsf(v2.y)), fmaxf(fabsf(v2.z), fabsf(v2.w))));
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v3.x), fabsf(v3.y)), fmaxf(fabsf(v3.z), fabsf(v3.w))));
+  }
+  for (; i < n; i += stride) {
+    const float4 v = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
   }
 #pragma unroll
@@ -102,12 +127,11 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
     }
   }
   constexpr int V4 = HD / 4;
+  const bool contiguous = is_contiguous(st, H, T, HD);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / V4;
+    const int64_t row = i / V4;          // V4 is a power of two
     const int c = (int)(i - row * V4);
-    const int64_t bh = row / T, t = row - bh * T;
-    const int64_t b = bh / H, h = bh - b * H;
-    const float4 v = *reinterpret_cast<const float4*>(x + b * st.b + h * st.h + t * st.t + c * 4);
+    const float4 v = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
     const float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
     __half hi[4], lo[4];
 #pragma unroll
@@ -125,7 +149,10 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
 template <int HD>
 inline int run(const Job& job, int count, const McaStrides& st, int H, int T, int64_t rows, const Workspace& w, bool backward,
                cudaStream_t stream) {
-  for (int i = 0; i < count; ++i) MCA_CUDA_TRY(cudaMemsetAsync(w.amax + job.slot[i], 0, sizeof(unsigned int), stream));
+  // the slots of this call's tensors are consecutive (q, k, v or dY alone): one clear
+  int lo = job.slot[0], hi = job.slot[0];
+  for (int i = 1; i < count; ++i) { lo = std::min(lo, job.slot[i]); hi = std::max(hi, job.slot[i]); }
+  MCA_CUDA_TRY(cudaMemsetAsync(w.amax + lo, 0, sizeof(unsigned int) * (size_t)(hi - lo + 1), stream));
   const int blocks = (int)std::min<int64_t>(148 * 8, (rows * (HD / 4) + 255) / 256);
   amax_kernel<HD><<<dim3(blocks, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax);
   int e = mca_launch_status();
