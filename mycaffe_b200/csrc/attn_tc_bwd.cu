@@ -765,23 +765,28 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (warp == WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
-// delta[row] = sum_c dY[row][c] * Y[row][c]  (bf16 inputs, fp32 result); one warp per row.
+// delta[row] = sum_c dY[row][c] * Y[row][c]  (bf16 inputs, fp32 result).  D / 8 lanes share a row (16-byte loads), so a
+// warp covers 256 / D rows.
 __global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
                                       int64_t rows, int H, int T, int D, const McaStrides ys, float* __restrict__ delta) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const int64_t bh = row / T, bi = bh / H;
-  const int64_t off = bi * ys.b + (bh - bi * H) * ys.h + (row - bh * T) * ys.t;   // y and dy share the output layout
+  const int lane = threadIdx.x & 31, g = D / 8, rpw = 32 / g;        // g in {8, 16}
+  const int64_t row = ((int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5)) * rpw + lane / g;
   float acc = 0.f;
-  for (int c = lane * 2; c < D; c += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + off + c));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + off + c));
-    acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
-  }
+  if (row < rows) {
+    const unsigned bh = (unsigned)(row / T), bi = bh / (unsigned)H;
+    const int64_t off = (int64_t)bi * ys.b + (int64_t)(bh - bi * H) * ys.h + (row - (int64_t)bh * T) * ys.t + (lane % g) * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(dy + off);       // y and dy share the output layout
+    const uint4 b = *reinterpret_cast<const uint4*>(y + off);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) delta[row] = acc;
+    for (int i = 0; i < 4; ++i) {
+      const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+      const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      acc = fmaf(fa.x, fb.x, fmaf(fa.y, fb.y, acc));
+    }
+  }
+  for (int o = g / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (row < rows && lane % g == 0) delta[row] = acc;
 }
 
 // Both kernels of one backward, with or without the caller's mask.
@@ -933,8 +938,11 @@ int mca_sdpa_backward_tc_masked(const void* q, const void* k, const void* v, con
   if (D != 64 && D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)B * H * T;
-  bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, H, T, D,
-                                                                   mca_out_strides(layout, H, T, D), delta_scratch);
+  {
+    const int64_t rows_per_block = 8 * (256 / D);   // eight warps, 256 / D rows each
+    bwd_delta_bf16_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, H, T, D, mca_out_strides(layout, H, T, D), delta_scratch);
+  }
   int e = mca_launch_status();
   if (e) return e;
   if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st, mask);
