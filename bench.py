@@ -398,6 +398,7 @@ def run_ours(args):
         for key, (bt, bf) in {"decode_bf16": (DEC_B, True), "decode_b16": (16, False), "decode_b1": (1, False)}.items():
             extras[key], extra_checks[key] = run_decode(cx, bt, bf, multi=False, steps=3)
         extras["tft"] = run_tft(cx)
+        extras["decode_projections"] = run_projections(cx)
 
     # ----------------------------------------------------------------- CPU legs: rank 0, after the process group is gone
     barrier()
@@ -826,6 +827,67 @@ def run_train(cx, steps=4):
     return res
 
 
+def run_projections(cx):
+    """The weight-streaming projections of one llama2-7B decode layer (RMSNorm + q/k/v, Wo + residual, RMSNorm + W1/W3 +
+    SwiGLU + W2 + residual) for 1, 16 and 64 sequences, fp32 weights: one sequence and up to eight share a streaming
+    pass (`gemv_stream_kernel`); above that the tensor-core kernel (`proj_tc_kernel`) reads the weights once.  Every call
+    takes the next of two weight sets (1.6 GB in all), so no weight byte is found in L2."""
+    torch, lib, dev = cx.torch, cx.lib, cx.dev
+    dim, hidden = DEC_HEADS * DEC_HS, 11008
+    sets = 2
+    mk = lambda r_, c_: [torch.randn(r_, c_, device=dev) * 0.02 for _ in range(sets)]
+    wq, wk, wv, wo = mk(dim, dim), mk(dim, dim), mk(dim, dim), mk(dim, dim)
+    w1, w3, w2 = mk(hidden, dim), mk(hidden, dim), mk(dim, hidden)
+    rms = torch.ones(dim, device=dev)
+    nbytes = (4 * dim * dim + 3 * hidden * dim) * 4
+    pk = cx.peaks["hbm_gbs"]
+    res = {"workload": f"decode projections of one layer, dim {dim}, hidden {hidden}, fp32 weights ({nbytes >> 20} MB per layer)", "batches": []}
+    for Bn in (1, 16, 64):
+        x = torch.randn(Bn, dim, device=dev)
+        xb = torch.randn(Bn, dim, device=dev)
+        qo, ko, vo = (torch.empty(Bn, dim, device=dev) for _ in range(3))
+        hbuf = torch.empty(Bn, hidden, device=dev)
+
+        def layer(i):
+            rc = lib.mca_decode_qkv_rmsnorm(x.data_ptr(), rms.data_ptr(), 1e-5, wq[i].data_ptr(), wk[i].data_ptr(), wv[i].data_ptr(), 0, Bn, dim,
+                                            dim, qo.data_ptr(), ko.data_ptr(), vo.data_ptr(), cx.sp)
+            rc |= lib.mca_decode_out_proj(xb.data_ptr(), wo[i].data_ptr(), 0, Bn, dim, x.data_ptr(), cx.sp)
+            rc |= lib.mca_decode_ffn(rms.data_ptr(), 1e-5, w1[i].data_ptr(), w2[i].data_ptr(), w3[i].data_ptr(), 0, Bn, dim, hidden,
+                                     hbuf.data_ptr(), x.data_ptr(), cx.sp)
+            return rc
+        entry = {"sequences": Bn}
+        for mode, on in (("tensor_core", 1), ("streaming", 0)) if Bn > 8 else (("streaming", 1),):
+            lib.mca_proj_tc_enable(on)
+            for i in range(3):
+                x.normal_()
+                if layer(i % sets):
+                    raise RuntimeError("projection launch failed")
+            iters = 8
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record(cx.stream)
+            for i in range(iters):
+                layer(i % sets)
+            e1.record(cx.stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            entry[mode + "_ms"] = round(ms, 4)
+            entry[mode + "_GBps"] = round(nbytes / ms / 1e6, 1)
+        lib.mca_proj_tc_enable(1)
+        best = "tensor_core" if Bn > 8 else "streaming"
+        entry["roofline"] = {"bound": "hbm", "kernel": "proj_tc_kernel<float> + x_pieces_kernel" if Bn > 8 else "gemv_stream_kernel",
+                             "achieved": entry[best + "_GBps"], "peak": pk, "unit": "GB/s", "frac": round(entry[best + "_GBps"] / pk, 4),
+                             "peak_source": cx.peaks["source"], "kernel_ms": entry[best + "_ms"], "bytes_per_launch": nbytes,
+                             "traffic": None, "note": "weight bytes of the layer over the time of its five launches"}
+        res["batches"].append(entry)
+    st = (C.c_int * 4)()
+    lib.mca_proj_tc_status(st)
+    res["status"] = list(st)
+    if st[0] != 0:
+        raise RuntimeError(f"projection kernel reported {list(st)}")
+    return res
+
+
 def run_tft(cx):
     """Config 4: TFT interpretable attention, batch 256, 4 heads, d 64, 192 keys; Nq = 24 (how the TFT net runs it)
     and Nq = 192 (explicit q, k, v mode); forward and backward, L2 flushed before every timed launch (75 MB problem)."""
@@ -1113,10 +1175,10 @@ def run_profile_case(case):
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
     dev = torch.device("cuda", 0)
-    if case in ("tft", "train", "sweep", "backward"):
+    if case in ("tft", "train", "sweep", "backward", "projections"):
         # the N = 1 legs of the benchmark on their own (same code, same JSON fragment)
         cx = Ctx(argparse.Namespace())
-        print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward}[case](cx)}))
+        print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward, "projections": run_projections}[case](cx)}))
         return
     if case == "gemv-small":
         dim = DEC_HEADS * DEC_HS
@@ -1421,7 +1483,7 @@ def main():
                     help="one GPU: skip the other configurations (train, sweep, backward, decode variants, tft)")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
-    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "proj-small", "norm-small", "llama-step",
+    ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "proj-small", "norm-small", "llama-step", "projections",
                                                      "tft", "train", "sweep", "backward"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
