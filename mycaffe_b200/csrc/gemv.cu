@@ -377,8 +377,10 @@ int run_proj_tc(const GemvParams& p, cudaStream_t st) {
     return e;
   auto pre = proj::x_pieces_kernel<BF>;
   MCA_CUDA_TRY(cudaFuncSetAttribute(pre, cudaFuncAttributeMaxDynamicSharedMemorySize, proj::MAX_N * 4));
-  pre<<<Bp, 256, sizeof(float) * (size_t)p.n, st>>>(p.x, p.norm_w, p.eps, p.n, p.B, Bp, pieces, xscale);
-  if ((e = mca_launch_status())) return e;
+  // both kernels are launched programmatically dependent: the pre-pass's launch overlaps the tail of whatever runs
+  // before it (it waits for that before it reads or writes anything), the contraction's set-up overlaps the pre-pass
+  if ((e = mca_launch_pdl(pre, dim3(Bp), dim3(256), sizeof(float) * (size_t)p.n, st, p.x, p.norm_w, p.eps, p.n, p.B, Bp, pieces, xscale)))
+    return e;
   const size_t smem = proj::smem_bytes<WT>();
   auto kern = proj::proj_tc_kernel<WT>;
   MCA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -131,6 +131,8 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
   extern __shared__ float xrow[];                       // the row, read from global memory once
   const int b = blockIdx.x, tid = threadIdx.x;
   mca_pdl_launch_dependents();                          // the contraction kernel may start fetching weights
+  mca_pdl_wait();                                       // launched ahead of the kernels before it: their results (x, and the
+                                                        // previous contraction's last reads of the pieces) come first
   const size_t piece_stride = (size_t)Bp * n;
   uint16_t* dst = pieces + (size_t)b * n;
   if (b >= B) {
