@@ -49,7 +49,13 @@ __device__ int g_status[4];
 template <typename WT> struct Plan;
 template <> struct Plan<float> {
   static constexpr bool CONVERT = true;
-  static constexpr int SW = 5, SX = 3, PIECES = 2, FMT = 0;            // weight / activation ring depths; fp16 operands
+#ifndef MCA_PROJ_SW
+#define MCA_PROJ_SW 5
+#endif
+#ifndef MCA_PROJ_SX
+#define MCA_PROJ_SX 3
+#endif
+  static constexpr int SW = MCA_PROJ_SW, SX = MCA_PROJ_SX, PIECES = 2, FMT = 0;   // weight / activation ring depths; fp16 operands
   static constexpr uint32_t W_BYTES = ROWS * KC * 4;                    // a slot: the fp32 tile, then hi | lo in its place
   static constexpr uint32_t X_BYTES = PIECES * MAX_B * 128;
   static constexpr uint32_t OP_BYTES = ROWS * KC * 2;                   // one fp16 operand tile (half a slot)
