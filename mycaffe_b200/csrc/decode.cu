@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -533,6 +534,16 @@ int mca_decode_plan(int B, int n_heads, int n_kv_heads, int head_size, int max_l
       if (cost < best_cost) { best_cost = cost; best_n = n; }
     }
     sl = (((int64_t)max_len + best_n - 1) / best_n + 15) / 16 * 16;
+  }
+  {
+    // tuning aid: MCA_DECODE_SPLIT_LEN=<keys> (a multiple of 16) overrides the planned split length for every call of
+    // the process; read once
+    static const int forced = [] {
+      const char* e = getenv("MCA_DECODE_SPLIT_LEN");
+      const int v = e ? atoi(e) : 0;
+      return (v >= 16 && v % 16 == 0) ? v : 0;
+    }();
+    if (forced) sl = forced;
   }
   *split_len = (int)sl;
   *nsplit = (max_len + (int)sl - 1) / (int)sl;
