@@ -11,7 +11,8 @@
 //     (in place, so that all of shared memory is weight slots: what bounds the kernel is bytes in flight per SM); the activations are
 //     split the same way by a small pre-pass (after RMSNorm and a per-sequence power-of-two scale), and the product is
 //     the three MMAs hi.hi + hi.lo + lo.hi into one fp32 accumulator in TMEM (the dropped lo.lo term is 2^-22);
-//   * bf16 weights: the TMA tile is the MMA operand itself, the activations are three bf16 pieces (24 bits).
+//   * bf16 weights: the TMA tile is the MMA operand itself, the activations are two bf16 pieces (16 mantissa bits; the
+//     weights themselves carry 8), two MMAs per k16.
 // Work items are (tile of 128 rows, slice of K): matrices with few rows (Wo, W2) are cut along K so that every SM
 // streams; a slice leaves its fp32 partial sums in a scratch array and the slice that arrives last (a ticket per
 // tile and quarter of its rows) adds all of them in slice order, so the result does not depend on timing.  The gated pair W1/W3 of the
@@ -40,7 +41,7 @@ constexpr int THREADS = (WARP_TMA_X + 1) * 32;
 constexpr float W_SCALE = 16.f;    // fp32 weights are split after this exact scaling (keeps the low halves normal)
 constexpr uint32_t TMEM_ALLOC = 256, ACC_COLS = 128;
 
-__device__ __align__(1024) uint16_t g_x_pieces[3 * MAX_B * MAX_N];
+__device__ __align__(1024) uint16_t g_x_pieces[2 * MAX_B * MAX_N];
 __device__ float g_x_scale[MAX_B];
 __device__ float g_partials[(size_t)MAX_ITEMS * ROWS * 2 * MAX_B];
 __device__ unsigned int g_tickets[MAX_TILES * EPI_WARPS];
@@ -64,7 +65,7 @@ template <> struct Plan<float> {
 };
 template <> struct Plan<__nv_bfloat16> {
   static constexpr bool CONVERT = false;
-  static constexpr int SW = 8, SX = 3, PIECES = 3, FMT = 1;            // bf16 operands
+  static constexpr int SW = 8, SX = 3, PIECES = 2, FMT = 1;            // bf16 operands
   static constexpr uint32_t W_BYTES = ROWS * KC * 2;
   static constexpr uint32_t X_BYTES = PIECES * MAX_B * 128;
   static constexpr uint32_t OP_BYTES = 0;
@@ -127,7 +128,8 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // Activations of sequence b -> 16-bit pieces (row p * Bp + b of a (pieces * Bp, n) array): RMSNorm as the CPU twin
 // orders it, o[j] = w[j] * (s * x[j]) with s = 1 / sqrt(sum(x^2) / n + eps) (llama2_cpu.cpp:189-202), then
 //   BF16 = false: v / 2^e with 2^e chosen so that the row's largest magnitude lands in [2^13, 2^14), as fp16 hi + lo;
-//   BF16 = true:  v as three bf16 pieces.
+//   BF16 = true:  v as two bf16 pieces, hi = bf16(v), lo = bf16(v - hi): 16 mantissa bits, two hundred times finer than
+//                 the bf16 weights they multiply.
 // Rows from B up to Bp are written as zeros.  One CTA of 256 threads per row.
 template <bool BF16>
 __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
@@ -144,7 +146,6 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
   if (b >= B) {
     for (int k = tid; k < n; k += 256) {
       dst[k] = 0; dst[piece_stride + k] = 0;
-      if (BF16) dst[2 * piece_stride + k] = 0;
     }
     return;
   }
@@ -166,12 +167,9 @@ __global__ void __launch_bounds__(256) x_pieces_kernel(const float* __restrict__
     for (int k = tid; k < n; k += 256) {
       const float v = xrow[k];
       const __nv_bfloat16 h = __float2bfloat16_rn(v);
-      const float r1 = v - __bfloat162float(h);
-      const __nv_bfloat16 m = __float2bfloat16_rn(r1);
-      const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+      const __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
       dst[k] = __bfloat16_as_ushort(h);
-      dst[piece_stride + k] = __bfloat16_as_ushort(m);
-      dst[2 * piece_stride + k] = __bfloat16_as_ushort(l);
+      dst[piece_stride + k] = __bfloat16_as_ushort(l);
     }
     if (tid == 0) xscale[b] = 1.f;
     return;
@@ -341,10 +339,8 @@ __global__ void __launch_bounds__(THREADS, 1) proj_tc_kernel(const __grid_consta
                 umma_ss(d_tmem, da, dx1, idesc, 1u);        // hi . lo
                 umma_ss(d_tmem, dl, dx0, idesc, 1u);        // lo . hi
               } else {
-                const uint64_t dx2 = make_desc(xs + 2 * x_piece_bytes + kk * 32, 16, 1024);
-                umma_ss(d_tmem, da, dx0, idesc, first);
-                umma_ss(d_tmem, da, dx1, idesc, 1u);
-                umma_ss(d_tmem, da, dx2, idesc, 1u);
+                umma_ss(d_tmem, da, dx0, idesc, first);     // W . x_hi
+                umma_ss(d_tmem, da, dx1, idesc, 1u);        // W . x_lo
               }
             }
             umma_commit(wempty(sw));

@@ -12,7 +12,7 @@ from gpu_util import bf16_round
 pytestmark = pytest.mark.gpu
 
 TOL_F32 = 2e-5      # fp16 hi/lo halves of both operands, fp32 accumulation on the tensor core
-TOL_BF16 = 2e-5     # bf16 weights are exact operands; the activations carry three bf16 pieces
+TOL_BF16 = 5e-5     # bf16 weights are exact operands; the activations carry two bf16 pieces (16 mantissa bits)
 
 
 def _rms(x, g, eps=1e-5):
@@ -73,7 +73,7 @@ def test_qkv_and_out_projection(B, dim, kv_dim, bf16):
     ref_res = x.astype(np.float64) + outs[1][0].astype(np.float64) @ wo.astype(np.float64).T
     assert rel_err(outs[1][3], ref_res) < tol
     for a, b in zip(outs[1], outs[0]):                     # and the streaming kernel agrees
-        assert rel_err(a, b) < 2e-5
+        assert rel_err(a, b) < 5e-5
 
 
 @pytest.mark.parametrize("bf16", [False, True])
