@@ -194,7 +194,14 @@ class TransformerGpu:
                     result = self.logits.cpu().numpy()
                     self._capture()
                     return result
-            return self.logits.cpu().numpy()
+            result = self.logits.cpu().numpy()     # synchronises
+            if self.batch > 8:
+                # above eight sequences the projections run on the tensor cores: a bounded wait that gave up there
+                # leaves stale logits and a status word
+                st = (C.c_int * 4)()
+                if self._lib.mca_proj_tc_status(st) == 0 and st[0] != 0:
+                    raise RuntimeError(f"projection kernel gave up: status {list(st)}")
+            return result
 
     def forward(self, token, pos):
         """The reference's signature: one sequence, logits (vocab_size) on the host."""
