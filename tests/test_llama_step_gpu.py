@@ -86,6 +86,34 @@ def test_grouped_query_generation_matches_restated_step(dim, hidden, n_layers, n
     assert rel_err(t.key_cache.cpu().numpy(), kc) < 1e-5
 
 
+@pytest.mark.parametrize("B,use_graph", [(16, False), (40, True)])
+def test_many_sequences_step_on_the_tensor_core_projections(B, use_graph):
+    """Above eight sequences every projection of the step (q/k/v, Wo, W1/W3, W2, classifier) is the tensor-core kernel;
+    the whole step against the restated reference step, ragged positions included, eager and from a CUDA graph."""
+    from mycaffe_b200.llama2 import TransformerGpu
+    dim, hidden, n_layers, n_heads, n_kv, vocab, seq_len = 256, 344, 2, 4, 4, 200, 24
+    rng = np.random.default_rng(B)
+    w = synthetic_weights(rng, dim, hidden, n_layers, n_heads, n_kv, vocab)
+    w["wcls"] = w["token_embedding_table"]
+    cfg = dict(dim=dim, hidden_dim=hidden, n_layers=n_layers, n_heads=n_heads, n_kv_heads=n_kv, vocab_size=vocab,
+               seq_len=seq_len)
+    t = TransformerGpu(0, batch=B, use_graph=use_graph)
+    t.load_weights(cfg, w)
+    kv_dim = n_kv * (dim // n_heads)
+    kc = np.zeros((n_layers, B, seq_len, kv_dim), np.float32)
+    vc = np.zeros((n_layers, B, seq_len, kv_dim), np.float32)
+    tokens = rng.integers(0, vocab, (seq_len, B))
+    for pos in range(10):
+        ref = oracle.llama_forward(cfg, w, kc, vc, tokens[pos], [pos] * B)
+        got = t.forward_batch(tokens[pos], [pos] * B)
+        assert rel_err(got, ref) < 1e-4, pos
+    ragged = rng.integers(0, 11, B)                    # every sequence goes on from (or back to) its own position
+    ref = oracle.llama_forward(cfg, w, kc, vc, tokens[10], ragged)
+    got = t.forward_batch(tokens[10], ragged)
+    assert rel_err(got, ref) < 1e-4
+    assert rel_err(t.key_cache.cpu().numpy(), kc) < 1e-5
+
+
 def test_batched_ragged_positions_match_independent_references(tmp_path):
     """B sequences with their own tokens step together; then each steps at its own position.  The
     reference runs one TransformerCpu per sequence."""
