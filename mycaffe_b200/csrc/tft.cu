@@ -17,6 +17,14 @@ constexpr int TFT_ROWS = 8;        // query rows per CTA, one per warp
 constexpr int TFT_THREADS = 256;
 constexpr int TFT_TQ_ROWS = 24;   // query rows of a tile of the tiled kernels
 
+// e^x for x <= 0 as one multiply and one ex2.approx (2 ulp): the softmax of the tiled kernels.  Arguments far below
+// the fp32 range (a masked logit against a real maximum) give exactly 0.
+__device__ __forceinline__ float tft_exp(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
 // (Nk, d) tile -> shared memory rows of d + 4 floats with asynchronous 16-byte copies: all of a thread's copies are
 // in flight at once (a load-then-store loop serialises on the round trip of each one).
 __device__ __forceinline__ void tile_to_smem_async(float* dst, const float* __restrict__ src, int Nk, int d, int tid) {
@@ -305,7 +313,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 2) tft_fwd_tiled_kernel(const flo
       float sum = 0.f;
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c) {
-        acc[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : expf(acc[r][c] - m);
+        acc[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : tft_exp(acc[r][c] - m);
         sum += acc[r][c];
       }
       hs[r] = warp_sum(sum);
@@ -720,7 +728,7 @@ __global__ void __launch_bounds__(TFT_THREADS, 1) tft_bwd_tiled_kernel(const flo
       float sum = 0.f, dot = 0.f;
 #pragma unroll
       for (int c = 0; c < TQ_C; ++c) {
-        s[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : expf(s[r][c] - m);
+        s[r][c] = (dead & (1u << (r * TQ_C + c))) ? 0.f : tft_exp(s[r][c] - m);
         sum += s[r][c];
         dot = fmaf(s[r][c], dp[r][c], dot);
       }
