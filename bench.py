@@ -738,9 +738,18 @@ def run_train(cx, steps=4):
     ws_bytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
     # fp32: what a default handle runs (forward and backward on the tensor cores with split fp16 operands);
     # fp32_cuda_cores: exact fp32 arithmetic on CUDA cores (MCA_FLAG_EXACT_FP32)
-    for name in ("fp32", "fp32_cuda_cores", "bf16"):
+    # fp32_key_mask / fp32_key_mask_cuda_cores: the same shape without the causal mask but with a (B,T) key mask (what
+    # MultiheadAttentionLayer passes, MultiheadAttentionLayer.cs:698-702; 30 % of the keys masked), on the tensor cores
+    # (packed keep-bits) and on the exact CUDA-core kernels; twice the causal FLOPs
+    keymask = (torch.rand(B, T, device=dev) > 0.3).float().contiguous()
+    wpr = lib.mca_mask_bits_row_words(T)
+    keybits = torch.zeros(B * wpr, dtype=torch.int32, device=dev)
+    if lib.mca_mask_pack(keymask.data_ptr(), 2, B, T, keybits.data_ptr(), None, sp):
+        raise RuntimeError("mask pack failed")
+    for name in ("fp32", "fp32_cuda_cores", "bf16", "fp32_key_mask", "fp32_key_mask_cuda_cores"):
         bf = name == "bf16"
-        split_fwd = name == "fp32"
+        split_fwd = name in ("fp32", "fp32_key_mask")
+        masked = "key_mask" in name
         dt = torch.bfloat16 if bf else torch.float32
         n_sets = 4
         sets = []
@@ -758,10 +767,11 @@ def run_train(cx, steps=4):
                 return lib.mca_sdpa_forward_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
                                                s["y"].data_ptr(), s["a"].data_ptr(), st.data_ptr(), sp)
             if split_fwd:
-                return lib.mca_sdpa_forward_f32_tc(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), 1, B, H, T, D, s["y"].data_ptr(),
-                                                   None, None, s["yc"].data_ptr(), s["a"].data_ptr(), s["ws"], ws_bytes,
-                                                   st.data_ptr(), 0, sp)
-            return lib.mca_sdpa_forward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), None, 3, None, B, H, T, D,
+                return lib.mca_sdpa_forward_f32_tc_masked(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), 0 if masked else 1, B, H, T, D,
+                                                          s["y"].data_ptr(), None, None, s["yc"].data_ptr(), s["a"].data_ptr(), s["ws"], ws_bytes,
+                                                          st.data_ptr(), 0, keybits.data_ptr() if masked else None, 2 if masked else 0, sp)
+            return lib.mca_sdpa_forward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), keymask.data_ptr() if masked else None,
+                                            2 if masked else 3, None, B, H, T, D,
                                             s["y"].data_ptr(), s["a"].data_ptr(), s["b"].data_ptr(), s["yc"].data_ptr(), sp)
 
         def bwd(s):
@@ -770,11 +780,13 @@ def run_train(cx, steps=4):
                                                 s["a"].data_ptr(), s["delta"].data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H, T, D,
                                                 s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), st.data_ptr(), sp)
             if split_fwd:
-                return lib.mca_sdpa_backward_f32_tc(s["dy"].data_ptr(), s["yc"].data_ptr(), s["a"].data_ptr(), s["delta"].data_ptr(), 1, B, H, T, D,
-                                                    s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), s["ws"], ws_bytes,
-                                                    st.data_ptr(), 0, sp)
+                return lib.mca_sdpa_backward_f32_tc_masked(s["dy"].data_ptr(), s["yc"].data_ptr(), s["a"].data_ptr(), s["delta"].data_ptr(),
+                                                           0 if masked else 1, B, H, T, D, s["dq"].data_ptr(), s["dk"].data_ptr(),
+                                                           s["dv"].data_ptr(), s["ws"], ws_bytes, st.data_ptr(), 0,
+                                                           keybits.data_ptr() if masked else None, None, 2 if masked else 0, sp)
             return lib.mca_sdpa_backward_f32(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), s["dy"].data_ptr(), s["yc"].data_ptr(),
-                                             None, 3, None, s["a"].data_ptr(), s["b"].data_ptr(), s["delta"].data_ptr(), B, H, T, D,
+                                             keymask.data_ptr() if masked else None, 2 if masked else 3, None, s["a"].data_ptr(),
+                                             s["b"].data_ptr(), s["delta"].data_ptr(), B, H, T, D,
                                              s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(), sp)
 
         def step(evs=None):
@@ -802,9 +814,10 @@ def run_train(cx, steps=4):
             torch.cuda.synchronize()
             fms += evs[0].elapsed_time(evs[1]); bms += evs[1].elapsed_time(evs[2])
         fms, bms = fms / steps, bms / steps
-        tot = (fwd_flops + bwd_flops) / ((fms + bms) * 1e-3) / 1e12
+        ff, bfl = (2 * fwd_flops, 2 * bwd_flops) if masked else (fwd_flops, bwd_flops)   # no causal half without the causal mask
+        tot = (ff + bfl) / ((fms + bms) * 1e-3) / 1e12
         entry = {"ms_per_step": round(fms + bms, 3), "forward_ms": round(fms, 3), "backward_ms": round(bms, 3), "tflops": round(tot, 1),
-                 "forward_tflops": round(fwd_flops / (fms * 1e-3) / 1e12, 1), "backward_tflops": round(bwd_flops / (bms * 1e-3) / 1e12, 1),
+                 "forward_tflops": round(ff / (fms * 1e-3) / 1e12, 1), "backward_tflops": round(bfl / (bms * 1e-3) / 1e12, 1),
                  "gpu_launches": steps * L * (2 if bf else 2) }
         if bf:
             entry["roofline"] = tensor_roofline(cx, tot, "sdpa_fwd_tc_kernel<64> + backward kernels<64>", (fms + bms) / L,
