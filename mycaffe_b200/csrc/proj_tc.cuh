@@ -8,21 +8,22 @@
 // primitives.cu:322-340) with the arithmetic of its CPU twin (llama2_cpu.cpp:189-202,224-237) kept to fp32 accuracy:
 //   * fp32 weights: a tile of 128 rows x 64 k arrives by TMA as fp32; eight warps rewrite it in place as two fp16
 //     tiles hi = 16 w cut to fp16's mantissa, lo = fp16(16 w - hi) in the 128-byte-swizzled K-major layout the MMA reads
-//     (in place, so that all of shared memory is weight slots: what bounds the kernel is bytes in flight per SM); the activations are
+//     (in place: a tile costs 32 KB of shared memory, not 64, and what a tile costs in shared-memory traffic -- the TMA
+//     write, the converters' read and write, the MMAs' operand reads -- is what bounds the kernel); the activations are
 //     split the same way by a small pre-pass (after RMSNorm and a per-sequence power-of-two scale), and the product is
 //     the three MMAs hi.hi + hi.lo + lo.hi into one fp32 accumulator in TMEM (the dropped lo.lo term is 2^-22);
 //   * bf16 weights: the TMA tile is the MMA operand itself, the activations are two bf16 pieces (16 mantissa bits; the
 //     weights themselves carry 8), two MMAs per k16.
 // Work items are (tile of 128 rows, slice of K): matrices with few rows (Wo, W2) are cut along K so that every SM
 // streams; a slice leaves its fp32 partial sums in a scratch array and the slice that arrives last (a ticket per
-// tile and quarter of its rows) adds all of them in slice order, so the result does not depend on timing.  The gated pair W1/W3 of the
-// feed-forward block is one item with two accumulators and silu(a) * b in the epilogue.
+// tile and quarter of its rows) adds all of them in slice order, so the result does not depend on timing.  The gated
+// pair W1/W3 of the feed-forward block is one item with two accumulators and silu(a) * b in the epilogue.
 // Roles of a CTA (480 threads, one CTA per SM, persistent over items): warps 0-7 convert, 8-11 epilogue (TMEM lanes
 // 32 (w - 8) ..), warp 12 TMA producer of the weights, warp 13 MMA issuer and TMEM owner, warp 14 TMA producer of the
-// activation pieces.  The weight ring (five 32 KB slots for fp32, eight 16 KB slots for bf16) and the activation ring have
-// their own barriers.  Every wait is bounded.
+// activation pieces.  The weight ring (five 32 KB slots for fp32, eight 16 KB slots for bf16) and the activation ring
+// have their own barriers.  Every wait is bounded.
 // The activation pieces, per-sequence scales, partial sums and tickets live in arrays that are part of the library
-// image (about 26 MB per device): nothing is allocated, but two of these products must not overlap on one device.
+// image (about 24 MB per device): nothing is allocated, but two of these products must not overlap on one device.
 #pragma once
 #include "tc_common.cuh"
 
