@@ -362,7 +362,7 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
   if (a.B <= 0 || a.block <= 0 || a.H <= 0 || a.D <= 0) return ERROR_PARAM_OUT_OF_RANGE;
   if (a.dtype < MCA_DTYPE_F32 || a.dtype > MCA_DTYPE_BF16) return ERROR_PARAM_OUT_OF_RANGE;
   if (a.D > 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
-  if (a.dtype != MCA_DTYPE_F32 && a.D != 64 && a.D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (a.dtype == MCA_DTYPE_BF16 && a.D != 64 && a.D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;   // no bf16 kernel for other head sizes
   const size_t rows = (size_t)a.B * a.H * a.block;
   cudaError_t ce;
   if ((ce = cudaMalloc(&a.causal_flag, 8 * sizeof(int))) != cudaSuccess) { a.release(); return ERROR_MEMORY_OUT; }
@@ -378,7 +378,7 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
       return ERROR_MEMORY_OUT;
     }
   }
-  if (a.dtype == MCA_DTYPE_F32 && !(a.flags & MCA_FLAG_EXACT_FP32) && mca_sdpa_forward_f32_tc_supported(a.D) &&
+  if ((a.dtype == MCA_DTYPE_F32 || a.dtype == MCA_DTYPE_TF32) && !(a.flags & MCA_FLAG_EXACT_FP32) && mca_sdpa_forward_f32_tc_supported(a.D) &&
       (int64_t)a.B * a.H <= 65535) {
     // fp32 callers get the tensor-core forward: room for the fp16 halves of q, k, v.  If it cannot be had the handle
     // simply keeps to the CUDA-core kernels.
@@ -505,7 +505,16 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   const float* mask = nullptr;
   int mode = 0;
   a.have_fwd = false;
-  if (a.dtype == MCA_DTYPE_F32) {
+  // A tf32 handle asks for single-pass tf32 products, which exist for inference at head size 64 with a causal mask or
+  // none.  Everything else it is given -- training, other head sizes, other masks -- goes the way of an fp32 handle:
+  // the split-operand tensor-core kernels where they apply (more accurate than tf32, forward and backward), else the
+  // exact fp32 kernels.
+  bool fp32_path = a.dtype == MCA_DTYPE_F32 || (a.dtype == MCA_DTYPE_TF32 && (a.training || a.D != 64));
+  if (a.dtype == MCA_DTYPE_TF32 && !fp32_path) {
+    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true))) return e;
+    fp32_path = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;
+  }
+  if (fp32_path) {
     float *q, *kk, *v, *y;
     if ((e = check_f32(k, (long)pl[3], n_in, &q)) || (e = check_f32(k, (long)pl[4], n_in, &kk)) ||
         (e = check_f32(k, (long)pl[5], n_in, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
@@ -528,11 +537,8 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if (!e && save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
     return e;
   }
-  // tensor-core variants: causal or absent mask only
+  // bf16, or single-pass tf32 (inference, head size 64, causal mask or none)
   if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true))) return e;
-  // tf32 products are an inference-time option for 64-wide heads; training (Backward needs the exact
-  // row statistics) and other head sizes run the exact fp32 kernel on the same fp32 handles
-  const bool tf32_exact = a.dtype == MCA_DTYPE_TF32 && (a.training || a.D != 64);
   const bool bf16 = a.dtype == MCA_DTYPE_BF16;
   void *q, *kk, *v, *y;
   if ((e = check_any(k, (long)pl[3], n_in, bf16, &q)) || (e = check_any(k, (long)pl[4], n_in, bf16, &kk)) ||
@@ -573,15 +579,6 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if ((e = mca_convert_f32_to_bf16(yf, y, n, 0))) return e;
     if (save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
     return 0;
-  }
-  if (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH || tf32_exact) {
-    // a general mask (or training) with tf32 requested: the exact fp32 kernel handles it
-    const bool save = a.training && T == a.block;
-    e = mca_sdpa_forward_f32_layout((float*)q, (float*)kk, (float*)v, mask, mode, a.causal_flag, a.B, a.H, T, a.D,
-                                    (float*)y, save ? a.row_max : nullptr, save ? a.row_sum : nullptr,
-                                    save ? a.y_copy : nullptr, layout, 0);
-    if (!e && save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
-    return e;
   }
   e = mca_sdpa_forward_tc_layout(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1,
                                  layout, 0);

@@ -330,7 +330,9 @@ def test_tf32_tensor_core_forward(cuda, T, causal):
 
 
 def test_tf32_falls_back_to_exact_fp32_when_training_or_wide(cuda):
-    """Training (Backward needs exact row statistics) and head sizes other than 64 run the exact kernel."""
+    """What single-pass tf32 does not cover goes the way of an fp32 handle: training at head size 64 runs the
+    split-operand tensor-core kernels (fp32 accuracy, forward and backward), 128-wide heads the exact kernel, other head
+    sizes and other masks whichever of the two applies."""
     from mycaffe_b200 import function_ids as ids
     rng = np.random.default_rng(1)
     B, H, T, D = 1, 2, 256, 64
@@ -346,6 +348,16 @@ def test_tf32_falls_back_to_exact_fp32_when_training_or_wide(cuda):
     b = Sdpa(cuda, 1, 256, 2, 128, dtype=ids.MCA_DTYPE_TF32)
     assert rel_err(b.forward(q, k, v, oracle.causal_mask(256)), oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < FP32_TIGHT
     b.close()
+    # head size 32, and head size 64 with a key mask (inference): fp32 accuracy as well
+    q, k, v = rand_qkv(rng, 2, 2, 200, 32)
+    c = Sdpa(cuda, 2, 200, 2, 32, dtype=ids.MCA_DTYPE_TF32, flags=ids.MCA_FLAG_CAUSAL_IMPLICIT)
+    assert rel_err(c.forward(q, k, v, None), oracle.sdpa_forward(q, k, v, None, 3, f64=True)) < FP32_TIGHT
+    c.close()
+    q, k, v = rand_qkv(rng, 2, 2, 200, 64)
+    keys = (rng.random((2, 200)) > 0.3).astype(np.float32)
+    d = Sdpa(cuda, 2, 200, 2, 64, dtype=ids.MCA_DTYPE_TF32)
+    assert rel_err(d.forward(q, k, v, keys, batch_mask=True), oracle.sdpa_forward(q, k, v, keys, 2, f64=True)) < FP32_TIGHT
+    d.close()
 
 
 def test_gpt2_small_shape_layer_bf16(cuda):
