@@ -362,6 +362,18 @@ def run_ours(args):
                 "traffic": int(PREFILL_TRAFFIC_PER_ALGORITHMIC_BYTE * 4 * q.numel() * 2),
                 "traffic_source": "ncu capture of one launch of `--case prefill-full` (sdpa_fwd_tc_kernel, B=4 T=32768)",
                 "flops_per_launch": flops_launch, "flop_count": "causal 4*B*H*D*T*(T+1)/2"}
+    if world > 1:
+        # compute + exchange as one step: the target is the slower of this GPU's FLOPs at the measured GEMM peak and the
+        # bytes it must send over NVLink (its (B, H/N, T, D) bf16 outputs to each of the N - 1 peers) at the measured
+        # peer-copy rate of 770 GB/s per direction
+        nvlink_bytes = (world - 1) * B * Hl * T * D * 2
+        t_flops = flops_launch / (peaks["bf16_tflops"] * 1e12) * 1e3
+        t_link = nvlink_bytes / 770e9 * 1e3
+        roofline["with_exchange"] = {"nvlink_bytes_per_gpu": nvlink_bytes, "nvlink_GBps_reference": 770.0,
+                                     "compute_ms_at_peak": round(t_flops, 4), "nvlink_ms_at_reference": round(t_link, 4),
+                                     "target_ms": round(max(t_flops, t_link), 4), "achieved_ms": round(ms_per_step, 4),
+                                     "frac": round(max(t_flops, t_link) / ms_per_step, 4),
+                                     "fused": bool(use_fused[0])}
 
     # A strided sample of the timed output, every (batch, head), for the oracle comparison after the GPU legs.
     q_step = max(1, T // 512)
