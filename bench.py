@@ -406,6 +406,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         extras["sweep"] = run_sweep(cx)
         extras["backward"] = run_backward(cx)
+        extras["fp32_prefill"] = run_fp32_prefill(cx)
         extras["train"] = run_train(cx)
         for key, (bt, bf) in {"decode_bf16": (DEC_B, True), "decode_b16": (16, False), "decode_b1": (1, False)}.items():
             extras[key], extra_checks[key] = run_decode(cx, bt, bf, multi=False, steps=3)
@@ -710,6 +711,40 @@ def run_sweep(cx):
     if int(st[0].item()):
         raise RuntimeError(f"sweep: kernel status {st[:4].tolist()}")
     return {"workload": f"config5 causal prefill forward, H={H} D={D} bf16", "cases": out}
+
+
+def run_fp32_prefill(cx, B=1, T=PF_T):
+    """The headline shape with fp32 tensors (what a default MyCaffe handle holds): the split-operand tensor-core
+    forward for 128-wide heads next to the exact fp32 CUDA-core kernel, same inputs."""
+    torch, lib, dev, sp = cx.torch, cx.lib, cx.dev, cx.sp
+    H, D = PF_H, PF_D
+    q, k, v = (torch.randn(B, H, T, D, device=dev).div_(D ** 0.5) for _ in range(3))
+    y, y2 = torch.empty_like(q), torch.empty_like(q)
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
+    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes_d(B, H, T, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    rcs = []
+    f_tc = lambda: rcs.append(lib.mca_sdpa_forward_f32_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), 1, B, H, T, D, y.data_ptr(), None, None,
+                                                          None, None, ws.data_ptr(), nbytes, st.data_ptr(), 0, sp))
+    f_cc = lambda: rcs.append(lib.mca_sdpa_forward_f32_layout(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, 3, None, B, H, T, D,
+                                                              y2.data_ptr(), None, None, None, 0, sp))
+    ms_tc = cx.time_kernel(f_tc, 4, warm=3)
+    ms_cc = cx.time_kernel(f_cc, 2, warm=1)
+    if any(rcs) or int(st[0].item()):
+        raise RuntimeError(f"fp32 prefill: rc {sorted(set(rcs))}, status {st[:4].tolist()}")
+    diff = float((y - y2).abs().max().item())
+    scale = float(y2.abs().max().item())
+    if not diff <= 2e-5 * scale:
+        raise RuntimeError(f"fp32 prefill: tensor-core and CUDA-core outputs differ by {diff} (scale {scale})")
+    fl = causal_flops(B, H, T, D)
+    tf = fl / (ms_tc * 1e-3) / 1e12
+    return {"workload": f"config5 shape causal forward B={B} H={H} D={D} T={T}, fp32 tensors",
+            "tensor_cores_ms": round(ms_tc, 3), "tflops": round(tf, 1), "cuda_cores_ms": round(ms_cc, 3),
+            "cuda_cores_tflops": round(fl / (ms_cc * 1e-3) / 1e12, 1), "speedup": round(ms_cc / ms_tc, 2),
+            "max_abs_diff_over_scale": diff / scale,
+            "roofline": tensor_roofline(cx, tf, "split::amax_kernel + split::rows_kernel + sdpa_fwd_tc_kernel<128,split>", ms_tc,
+                                        "useful flops of the fp32 problem over the whole call; the kernel executes three fp16 "
+                                        "products per contraction, so 1/3 of the bf16 peak is its ceiling")}
 
 
 def run_backward(cx, B=1, T=PF_T):
@@ -1200,10 +1235,11 @@ def run_profile_case(case):
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
     dev = torch.device("cuda", 0)
-    if case in ("tft", "train", "sweep", "backward", "projections"):
+    if case in ("tft", "train", "sweep", "backward", "projections", "fp32-prefill"):
         # the N = 1 legs of the benchmark on their own (same code, same JSON fragment)
         cx = Ctx(argparse.Namespace())
-        print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward, "projections": run_projections}[case](cx)}))
+        print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward, "projections": run_projections,
+                                                "fp32-prefill": run_fp32_prefill}[case](cx)}))
         return
     if case == "gemv-small":
         dim = DEC_HEADS * DEC_HS
@@ -1509,7 +1545,7 @@ def main():
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
     ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "proj-small", "norm-small", "llama-step", "projections",
-                                                     "tft", "train", "sweep", "backward"],
+                                                     "tft", "train", "sweep", "backward", "fp32-prefill"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
     if args.case:

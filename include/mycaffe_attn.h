@@ -264,15 +264,19 @@ MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int
                                 int T, int D, void* y, float* lse, int* status, void* stream);
 
 /* fp32 SDPA forward at fp32 accuracy on the tensor cores.  Same math as attn.cu:518-602 with a causal or absent mask.
- * q, k, v, y: fp32, (B,H,T,D) or the packed layout; D in {16, 32, 64}.  A pre-pass scales each tensor by a power of two
+ * q, k, v, y: fp32, (B,H,T,D) or the packed layout; D in {16, 32, 64, 128} (128: one query tile per CTA and
+ * single-stage K and V, since a row's two halves are 512 bytes; forward only, the exact fp32 backward follows it from
+ * row_max / row_sum).  A pre-pass scales each tensor by a power of two
  * and writes every element as two fp16 halves hi = fp16(x), lo = fp16(x - hi) into `workspace`
- * (mca_sdpa_forward_f32_tc_workspace_bytes(B,H,T) bytes, 16-byte aligned); every contraction is then three
+ * (mca_sdpa_forward_f32_tc_workspace_bytes_d(B,H,T,D) bytes, 16-byte aligned); every contraction is then three
  * tcgen05 kind::f16 products hi.hi + hi.lo + lo.hi accumulated in fp32, P split the same way.  Within 1e-5 of the output
  * scale of the fp64 result (measured 1e-7 .. 7e-6).  row_max, row_sum (optional, (B,H,T)) and y_copy (optional, (B,H,T,D) contiguous) are what
  * mca_sdpa_backward_f32 needs; lse (optional, (B,H,T), log2 domain) and y_copy are what mca_sdpa_backward_f32_tc needs.
  * status as mca_sdpa_forward_tc. */
-MCA_API int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T);
-MCA_API int mca_sdpa_forward_f32_tc_supported(int D);
+MCA_API int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T);           /* head sizes up to 64 */
+MCA_API int64_t mca_sdpa_forward_f32_tc_workspace_bytes_d(int B, int H, int T, int D);  /* any supported head size */
+MCA_API int mca_sdpa_forward_f32_tc_supported(int D);    /* 16, 32, 64, 128 */
+MCA_API int mca_sdpa_backward_f32_tc_supported(int D);   /* 16, 32, 64 */
 MCA_API int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D,
                                     float* y, float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
                                     int64_t workspace_bytes, int* status, int layout, void* stream);

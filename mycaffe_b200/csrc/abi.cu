@@ -382,7 +382,7 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
       (int64_t)a.B * a.H <= 65535) {
     // fp32 callers get the tensor-core forward: room for the fp16 halves of q, k, v.  If it cannot be had the handle
     // simply keeps to the CUDA-core kernels.
-    a.split_ws_bytes = mca_sdpa_forward_f32_tc_workspace_bytes(a.B, a.H, a.block);
+    a.split_ws_bytes = mca_sdpa_forward_f32_tc_workspace_bytes_d(a.B, a.H, a.block, a.D);
     if (cudaMalloc(&a.split_ws, (size_t)a.split_ws_bytes) != cudaSuccess) { cudaGetLastError(); a.split_ws = nullptr; a.split_ws_bytes = 0; }
   }
   a.configured = true;
@@ -522,14 +522,20 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if (packed) { kk += C; v += 2 * C; }
     if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr))) return e;
     const bool save = a.training && T == a.block;
-    if (a.split_ws != nullptr) {
-      const bool bits = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;   // packed for the kernel; causal / none need nothing
+    const bool bits = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;   // packed for the kernel; causal / none need nothing
+    // Head sizes with a tensor-core forward but no tensor-core backward (128): the forward leaves the row statistics
+    // the exact fp32 backward recomputes the probabilities from; a saved forward under a general or batch mask keeps
+    // to the exact kernels, whose masked-row convention that backward shares.
+    const bool tc_bwd = mca_sdpa_backward_f32_tc_supported(a.D) != 0;
+    if (a.split_ws != nullptr && (tc_bwd || !save || !bits)) {
       if (bits && (e = pack_mask_bits(a, mask, mode, T))) return e;
-      e = mca_sdpa_forward_f32_tc_masked(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, nullptr, nullptr,
-                                         save ? a.y_copy : nullptr, save ? a.lse : nullptr, a.split_ws, a.split_ws_bytes,
-                                         a.causal_flag + 1, layout, bits ? a.mask_bits : nullptr, bits ? mode : MCA_MASK_NONE, 0);
+      const bool stats = save && !tc_bwd;
+      e = mca_sdpa_forward_f32_tc_masked(q, kk, v, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, stats ? a.row_max : nullptr,
+                                         stats ? a.row_sum : nullptr, save ? a.y_copy : nullptr, save && tc_bwd ? a.lse : nullptr,
+                                         a.split_ws, a.split_ws_bytes, a.causal_flag + 1, layout, bits ? a.mask_bits : nullptr,
+                                         bits ? mode : MCA_MASK_NONE, 0);
       if (e) return e;
-      if (save) { remember_forward(a, T, mode, layout, 0, false); a.fwd_split = true; }
+      if (save) { remember_forward(a, T, mode, layout, 0, false); a.fwd_split = tc_bwd; }
       return tc_status(k, a);
     }
     e = mca_sdpa_forward_f32_layout(q, kk, v, mask, mode, a.causal_flag, a.B, a.H, T, a.D, y, save ? a.row_max : nullptr,

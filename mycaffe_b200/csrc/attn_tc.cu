@@ -64,13 +64,17 @@ constexpr int MODE_BF16 = 0, MODE_TF32 = 1, MODE_SPLIT = 2;
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan (all tiles 1024-byte aligned)
 // ---------------------------------------------------------------------------------------------
-template <int ROW_BYTES> struct Plan {                     // ROW_BYTES = head size x element size
+// QT query tiles of a CTA are in use (the second group of softmax warps idles when QT is 1) and K and V each have STG
+// stages.  Rows of 512 bytes (128-wide heads with split operands) leave room for one query tile and one stage: K(j+1)
+// then arrives while P V(j) runs and V(j+1) while S(j+1) does, which is the order the products need them in anyway.
+template <int ROW_BYTES, int QT = 2, int STG = 2> struct Plan {   // ROW_BYTES = head size x element size
   static constexpr int SUB = ROW_BYTES / 128;              // 128-byte sub-tiles per row
   static constexpr uint32_t SUB_BYTES = BLK * 128;         // one sub-tile: 128 rows x 128 bytes
   static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 rows of one tensor
-  static constexpr int STAGES = 2;
+  static constexpr int STAGES = STG;
+  static constexpr int QTILES = QT;
   static constexpr uint32_t OFF_Q = 0;
-  static constexpr uint32_t OFF_K = OFF_Q + NQT * TILE_BYTES;
+  static constexpr uint32_t OFF_K = OFF_Q + QT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_V + STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_RED = OFF_BAR + 256;       // row sums and maxima for the epilogue: [NQT][2][128] floats
@@ -149,8 +153,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   constexpr bool F32_OUT = TF32 || SPLIT;
   constexpr int ELT = TF32 ? 4 : 2;            // bytes per element
   constexpr int BOX = 128 / ELT;               // elements per 128-byte sub-tile row
-  // split rows are [hi (64 fp16, HD used) | lo (64 fp16, HD used)]: two 128-byte sub-tiles whatever the head size
-  using PL = Plan<SPLIT ? 256 : HD * ELT>;
+  // split rows are [hi (64 fp16, HD used) | lo (64 fp16, HD used)]: two 128-byte sub-tiles for head sizes up to 64;
+  // 128-wide heads have [hi (128) | lo (128)], four sub-tiles, one query tile per CTA and single-stage K and V
+  constexpr bool WIDE = SPLIT && HD > 64;
+  using PL = Plan<SPLIT ? (WIDE ? 512 : 256) : HD * ELT, WIDE ? 1 : 2, WIDE ? 1 : 2>;
+  constexpr int QT = PL::QTILES, STG = PL::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -171,12 +178,12 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int bi = bh / p.H, hi = bh - bi * p.H;   // batch item and head
   const int T = p.T;
   const int pair = (int)gridDim.x - 1 - rank;
-  const int q0 = pair * (NQT * BLK);
+  const int q0 = pair * (QT * BLK);
   int n_tiles[NQT];
 #pragma unroll
   for (int x = 0; x < NQT; ++x) {
     const int qx = q0 + x * BLK;
-    if (qx >= T) n_tiles[x] = 0;
+    if (qx >= T || x >= QT) n_tiles[x] = 0;
     else n_tiles[x] = p.causal ? (min(qx + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
@@ -224,8 +231,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        const int st = j % STG;
+        const uint32_t ph = (uint32_t)((j / STG) & 1);
         ok = mbar_wait(bar(BAR_K_EMPTY + st), ph ^ 1u, p.status, 10, j);
         if (!ok) break;
         mbar_expect_tx(bar(BAR_K_FULL + st), PL::TILE_BYTES);
@@ -247,8 +254,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // give copies already in flight a bounded time to land before the CTA's memory is released
         for (int x = 0; x < NQT; ++x)
           if (n_tiles[x]) mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 12, x);
-        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(bar(BAR_K_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 13, j);
-        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(bar(BAR_V_FULL + (j & 1)), (uint32_t)((j >> 1) & 1), p.status, 14, j);
+        for (int j = max(0, issued_k - STG); j < issued_k; ++j) mbar_wait(bar(BAR_K_FULL + (j % STG)), (uint32_t)((j / STG) & 1), p.status, 13, j);
+        for (int j = max(0, issued_v - STG); j < issued_v; ++j) mbar_wait(bar(BAR_V_FULL + (j % STG)), (uint32_t)((j / STG) & 1), p.status, 14, j);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -277,15 +284,16 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint64_t dk = desc_k0 + (uint64_t)((st * PL::TILE_BYTES) >> 4);
         const uint32_t d_tmem = tmem_base_u + x * BLK;
         if constexpr (SPLIT) {
-          // S = Qhi Khi^T + Qhi Klo^T + Qlo Khi^T: the halves are the two sub-tiles of a row
-          constexpr uint32_t LO = PL::SUB_BYTES >> 4;
+          // S = Qhi Khi^T + Qhi Klo^T + Qlo Khi^T: the halves are the sub-tiles [0, SUB/2) and [SUB/2, SUB) of a row
+          constexpr uint32_t LO = ((PL::SUB / 2) * PL::SUB_BYTES) >> 4;
 #pragma unroll
           for (int term = 0; term < 3; ++term) {
             const uint32_t oq = term == 2 ? LO : 0u, ok_ = term == 1 ? LO : 0u;
 #pragma unroll
-            for (int kk = 0; kk < KSTEPS_QK; ++kk)
-              umma_ss_if<false>(leader, d_tmem, dq + oq + (uint32_t)(kk * 2), dk + ok_ + (uint32_t)(kk * 2), IDESC_QK,
-                                (term > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < KSTEPS_QK; ++kk) {
+              const uint32_t off = ((uint32_t)(kk >> 2) * PL::SUB_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
+              umma_ss_if<false>(leader, d_tmem, dq + oq + off, dk + ok_ + off, IDESC_QK, (term > 0 || kk > 0) ? 1u : 0u);
+            }
           }
         } else {
 #pragma unroll
@@ -309,7 +317,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint64_t dvk = dv + (uint64_t)((uint32_t)kk * V_STEP);
             const uint32_t a_hi = a_tmem + (uint32_t)(kk * 8);
             umma_ts_if<false>(leader, d_tmem, a_hi, dvk, IDESC_PV, (first && kk == 0) ? 0u : 1u);
-            umma_ts_if<false>(leader, d_tmem, a_hi, dvk + (uint64_t)(PL::SUB_BYTES >> 4), IDESC_PV, 1u);
+            umma_ts_if<false>(leader, d_tmem, a_hi, dvk + (uint64_t)(((PL::SUB / 2) * PL::SUB_BYTES) >> 4), IDESC_PV, 1u);
             umma_ts_if<false>(leader, d_tmem, a_hi + 64u, dvk, IDESC_PV, 1u);
           } else {
             umma_ts_if<TF32>(leader, d_tmem, a_tmem + (uint32_t)(kk * 8), dv + (uint64_t)((uint32_t)kk * V_STEP), IDESC_PV,
@@ -332,8 +340,8 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j & 1, st_n = (j + 1) & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1), ph_n = (uint32_t)(((j + 1) >> 1) & 1);
+        const int st = j % STG, st_n = (j + 1) % STG;
+        const uint32_t ph = (uint32_t)((j / STG) & 1), ph_n = (uint32_t)(((j + 1) / STG) & 1);
         TC_TRACE(3, j, 0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_V_FULL + st), ph, p.status, 22, j));
         if (!ok) break;
@@ -726,11 +734,12 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
         (e = make_map_f32(&mv, v, B, H, T, HD, sin, true)))
       return e;
   } else if constexpr (MODE == MODE_SPLIT) {
-    // the pre-pass wrote contiguous (B, H, T, 128) fp16 rows [hi | lo], whatever layout the fp32 tensors have
-    const McaStrides sp{(int64_t)H * T * 128, (int64_t)T * 128, 128};
-    if ((e = make_map_4d(&mq, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
-        (e = make_map_4d(&mk, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
-        (e = make_map_4d(&mv, v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, 128, sp, CU_TENSOR_MAP_SWIZZLE_128B)))
+    // the pre-pass wrote contiguous (B, H, T, RH) fp16 rows [hi | lo], whatever layout the fp32 tensors have
+    constexpr int RH = split::row_halves(HD);
+    const McaStrides sp{(int64_t)H * T * RH, (int64_t)T * RH, RH};
+    if ((e = make_map_4d(&mq, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, RH, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
+        (e = make_map_4d(&mk, k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, RH, sp, CU_TENSOR_MAP_SWIZZLE_128B)) ||
+        (e = make_map_4d(&mv, v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, H, T, RH, sp, CU_TENSOR_MAP_SWIZZLE_128B)))
       return e;
   } else {
     if ((e = make_map_bf16(&mq, q, B, H, T, HD, sin)) || (e = make_map_bf16(&mk, k, B, H, T, HD, sin)) ||
@@ -741,7 +750,7 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.y = y; p.lse = lse; p.status = status; p.T = T; p.causal = causal; p.H = H;
   // K and V of one (batch, head) are 2 * T * HD elements; keep a group's set under about 64 MB of the 126 MB L2
   {
-    const int64_t row_bytes = MODE == MODE_SPLIT ? 256 : HD * (MODE == MODE_TF32 ? 4 : 2);
+    const int64_t row_bytes = MODE == MODE_SPLIT ? 2 * split::row_halves(HD) : HD * (MODE == MODE_TF32 ? 4 : 2);
     const int64_t kv_bytes = (int64_t)2 * T * row_bytes;
     int64_t g = (64ll << 20) / kv_bytes;
     p.group = (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)B * H));
@@ -755,11 +764,13 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.row_max = split ? split->row_max : nullptr;
   p.row_sum = split ? split->row_sum : nullptr;
   p.y_copy = split ? split->y_copy : nullptr;
-  const size_t smem = Plan<MODE == MODE_SPLIT ? 256 : HD * (MODE == MODE_TF32 ? 4 : 2)>::BYTES;
+  constexpr bool WIDE = MODE == MODE_SPLIT && HD > 64;   // as in the kernel: one query tile, single-stage K and V
+  using PL = Plan<MODE == MODE_SPLIT ? (WIDE ? 512 : 256) : HD * (MODE == MODE_TF32 ? 4 : 2), WIDE ? 1 : 2, WIDE ? 1 : 2>;
+  const size_t smem = PL::BYTES;
   p.mask_bits = mask ? mask->bits : nullptr;
   p.mask_batch_stride = mask ? mask->batch_stride : 0;
   p.mask_row_stride = mask ? mask->row_stride : 0;
-  dim3 grid(mca_ceil_div(T, NQT * BLK), B * H);
+  dim3 grid(mca_ceil_div(T, PL::QTILES * BLK), B * H);
   if constexpr (MODE != MODE_TF32) {
     if (mask != nullptr) {
       MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -777,7 +788,7 @@ int launch_split(const float* q, const float* k, const float* v, int causal, int
                  float* row_sum, float* y_copy, float* lse, void* workspace, int* status, int layout, cudaStream_t st,
                  const McaMaskBits* mask = nullptr) {
   const int64_t rows = (int64_t)B * H * T;
-  const split::Workspace w = split::carve(workspace, rows);
+  const split::Workspace w = split::carve(workspace, rows, HD);
   split::Job job;
   job.src[0] = q; job.src[1] = k; job.src[2] = v;
   for (int i = 0; i < 3; ++i) { job.dst[i] = w.tensor[i]; job.slot[i] = i; }
@@ -863,7 +874,14 @@ int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T) {
   return split::workspace_bytes((int64_t)B * H * T);
 }
 
-int mca_sdpa_forward_f32_tc_supported(int D) { return D == 16 || D == 32 || D == 64; }
+int64_t mca_sdpa_forward_f32_tc_workspace_bytes_d(int B, int H, int T, int D) {
+  if (B <= 0 || H <= 0 || T <= 0 || !mca_sdpa_forward_f32_tc_supported(D)) return -1;
+  return split::workspace_bytes((int64_t)B * H * T, D);
+}
+
+int mca_sdpa_forward_f32_tc_supported(int D) { return D == 16 || D == 32 || D == 64 || D == 128; }
+
+int mca_sdpa_backward_f32_tc_supported(int D) { return D == 16 || D == 32 || D == 64; }
 
 int mca_sdpa_forward_f32_tc(const float* q, const float* k, const float* v, int causal, int B, int H, int T, int D, float* y,
                             float* row_max, float* row_sum, float* y_copy, float* lse, void* workspace,
@@ -885,7 +903,7 @@ int mca_sdpa_forward_f32_tc_masked(const float* q, const float* k, const float* 
   if ((row_max == nullptr) != (row_sum == nullptr)) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
   if (!mca_sdpa_forward_f32_tc_supported(D)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
-  if (workspace_bytes < mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
+  if (workspace_bytes < mca_sdpa_forward_f32_tc_workspace_bytes_d(B, H, T, D)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(y_copy)) & 15)
     return ERROR_PARAM_OUT_OF_RANGE;
@@ -895,6 +913,7 @@ int mca_sdpa_forward_f32_tc_masked(const float* q, const float* k, const float* 
     case 16: return launch_split<16>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
     case 32: return launch_split<32>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
     case 64: return launch_split<64>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
+    case 128: return launch_split<128>(q, k, v, causal, B, H, T, y, row_max, row_sum, y_copy, lse, workspace, status, layout, st, mask);
   }
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }

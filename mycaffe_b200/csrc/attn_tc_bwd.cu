@@ -967,7 +967,7 @@ int mca_sdpa_backward_f32_tc_masked(const float* dy, const float* y_copy, const 
   if (layout != MCA_LAYOUT_BHTD && layout != MCA_LAYOUT_PACKED) return ERROR_PARAM_OUT_OF_RANGE;
   if (!dy || !y_copy || !lse || !delta_scratch || !dq || !dk || !dv || !workspace || !status) return ERROR_PARAM_NULL;
   if (B <= 0 || H <= 0 || T <= 0 || (int64_t)B * H > 65535) return ERROR_PARAM_OUT_OF_RANGE;
-  if (!mca_sdpa_forward_f32_tc_supported(D)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  if (!mca_sdpa_backward_f32_tc_supported(D)) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   if (workspace_bytes < mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)) return ERROR_ATTN_SCRATCH_TOO_SMALL;
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
        reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(workspace)) & 15)

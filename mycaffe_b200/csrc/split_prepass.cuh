@@ -1,12 +1,13 @@
 // Pre-pass of the split-operand tensor-core kernels for fp32 callers: every fp32 tensor is scaled by a power of two
-// (chosen from its largest magnitude) and written as rows [hi (64 fp16, HD used) | lo (64 fp16, HD used)] with
+// (chosen from its largest magnitude) and written as rows [hi (64 fp16, HD used) | lo (64 fp16, HD used)] -- for
+// 128-wide heads (forward only) [hi (128) | lo (128)] -- with
 // hi = fp16(x), lo = fp16(x - hi): 22 mantissa bits per element, both halves inside the normal range of fp16 for
 // every element that matters.
 //
 // Workspace (one per attention handle or caller):
 //   bytes [0,16)     amax[4]   largest |x| of q, k, v, dY as float bit patterns (integer order = float order)
 //   bytes [64,128)   fac[16]   scale factors derived from them (all powers of two), see SplitFac
-//   bytes [1024,...) four tensors of rows x 128 fp16: q, k, v, dY
+//   bytes [1024,...) four tensors of rows x 128 fp16 (256 for 128-wide heads): q, k, v, dY
 #pragma once
 #include <cuda_fp16.h>
 
@@ -33,14 +34,17 @@ struct Workspace {
   __half* tensor[4];
 };
 
-inline int64_t workspace_bytes(int64_t rows) { return 1024 + 4 * rows * 128 * 2; }
+// fp16 values per row of a split tensor: two halves of 64 (head sizes up to 64) or of 128
+__host__ __device__ constexpr int row_halves(int HD) { return HD > 64 ? 256 : 128; }
 
-inline Workspace carve(void* base, int64_t rows) {
+inline int64_t workspace_bytes(int64_t rows, int HD = 64) { return 1024 + 4 * rows * row_halves(HD) * 2; }
+
+inline Workspace carve(void* base, int64_t rows, int HD = 64) {
   Workspace w;
   w.amax = static_cast<unsigned int*>(base);
   w.fac = reinterpret_cast<float*>(static_cast<char*>(base) + 64);
   __half* t = reinterpret_cast<__half*>(static_cast<char*>(base) + 1024);
-  for (int i = 0; i < 4; ++i) w.tensor[i] = t + (size_t)i * rows * 128;
+  for (int i = 0; i < 4; ++i) w.tensor[i] = t + (size_t)i * rows * row_halves(HD);
   return w;
 }
 
@@ -139,9 +143,10 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
       hi[j] = __float2half_rn(e[j]);
       lo[j] = __float2half_rn(e[j] - __half2float(hi[j]));
     }
-    __half* o = dst + row * 128 + c * 4;
+    constexpr int RH = row_halves(HD);
+    __half* o = dst + row * RH + c * 4;
     *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(hi);
-    *reinterpret_cast<uint2*>(o + 64) = *reinterpret_cast<const uint2*>(lo);
+    *reinterpret_cast<uint2*>(o + RH / 2) = *reinterpret_cast<const uint2*>(lo);
   }
 }
 

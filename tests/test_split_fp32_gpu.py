@@ -39,7 +39,9 @@ def run_raw(q, k, v, causal, want_stats=False, layout=0, dy=None):
     y = torch.empty(B * H * T * D, device=dev)
     rm, rs = torch.empty(B * H * T, device=dev), torch.empty(B * H * T, device=dev)
     yc = torch.empty(B * H * T * D, device=dev)
-    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
+    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes_d(B, H, T, D)
+    if D <= 64:
+        assert nbytes == lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
     ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
     wp = (ws.data_ptr() + 1023) // 1024 * 1024
     st = torch.zeros(8, dtype=torch.int32, device=dev)
@@ -77,7 +79,7 @@ def run_raw(q, k, v, causal, want_stats=False, layout=0, dy=None):
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("D", [16, 32, 64])
+@pytest.mark.parametrize("D", [16, 32, 64, 128])
 @pytest.mark.parametrize("T", [1, 17, 128, 200, 257, 1024])
 def test_split_forward_matches_fp64(T, D, causal):
     rng = np.random.default_rng(31 * T + D)
@@ -193,6 +195,30 @@ def test_split_backward_gradient_scales_and_packed_layout(dy_scale):
         np.testing.assert_array_equal(a_, b_)
 
 
+@pytest.mark.parametrize("T", [130, 640])
+def test_head_size_128_handle(cuda, T):
+    """128-wide heads: the forward is the split-operand tensor-core kernel (one query tile per CTA), with every mask
+    form for inference; training keeps the exact fp32 backward, fed by the row statistics that forward leaves (causal /
+    no mask) or by the exact forward (general and batch masks)."""
+    rng = np.random.default_rng(128 + T)
+    B, H, D = 2, 3, 128
+    q, k, v, dy = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(4))
+    from mycaffe_b200 import _lib
+    lib = _lib.load()
+    assert lib.mca_sdpa_forward_f32_tc_supported(D) == 1 and lib.mca_sdpa_backward_f32_tc_supported(D) == 0
+    masks = [(oracle.causal_mask(T), 1, False), (None, 0, False)] + list(_masks(rng, B, T))
+    for mask, mode, batch in masks:
+        ref = oracle.sdpa_forward(q, k, v, mask, mode, f64=True)
+        a = Sdpa(cuda, B, T, H, D)
+        assert rel_err(a.forward(q, k, v, mask, batch_mask=batch), ref) < SPLIT_TOL, mode
+        a.close()
+        a = Sdpa(cuda, B, T, H, D, training=True)
+        assert rel_err(a.forward(q, k, v, mask, batch_mask=batch), ref) < SPLIT_TOL, mode
+        for name, g_, r_ in zip("qkv", a.backward(dy), oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
+            assert rel_err(g_, r_) < SPLIT_TOL, (name, mode)
+        a.close()
+
+
 def _masks(rng, B, T):
     """A general (T,T) mask with ragged rows, one fully masked row and one fully kept row; a (B,T) key mask whose last
     batch item masks every key."""
@@ -251,7 +277,9 @@ def test_masked_entry_points_are_what_the_handle_runs(cuda):
             assert (packed[b, j // 32] >> (j % 32)) & 1 == int(keys[b, j] != 0)
     assert packed[:, (T + 31) // 32:].sum() == 0                      # nothing beyond T
     y = torch.empty(B * H * T * D, device=dev)
-    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
+    nbytes = lib.mca_sdpa_forward_f32_tc_workspace_bytes_d(B, H, T, D)
+    if D <= 64:
+        assert nbytes == lib.mca_sdpa_forward_f32_tc_workspace_bytes(B, H, T)
     ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
     wp = (ws.data_ptr() + 1023) // 1024 * 1024
     st = torch.zeros(8, dtype=torch.int32, device=dev)
