@@ -43,6 +43,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -54,10 +55,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int NQT = 2;                 // query tiles per CTA
-constexpr int WARP_TMA = NQT * 8;       // after the softmax warps (eight per query tile)
-constexpr int WARP_MMA = NQT * 8 + 1;
-constexpr int TC_THREADS = (NQT * 8 + 2) * 32;
+constexpr int NQT = 2;                 // query tiles per CTA, at most
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr int MODE_BF16 = 0, MODE_TF32 = 1, MODE_SPLIT = 2;
 
@@ -81,6 +79,28 @@ template <int ROW_BYTES, int QT = 2, int STG = 2> struct Plan {   // ROW_BYTES =
   static constexpr uint32_t BYTES = OFF_RED + 2 * 4 * 128 * 4 + 1024;  // + alignment slack
 };
 
+// What a CTA of the kernel looks like for a head size, an operand mode and the NARROW choice of the launcher.
+//   two query tiles (the default): 16 softmax warps + TMA + MMA warps, one CTA per SM, all 512 TMEM columns;
+//   WIDE (512-byte split rows): one query tile, single-stage K and V, one CTA per SM;
+//   NARROW: one query tile and a shared-memory plan of under 110 KB, so that two CTAs share an SM: each one's set-up,
+//           first loads and epilogue overlap the other's key loop.  For short sequences, where a CTA walks only a few
+//           key tiles and that fixed part is a third of its life; K and V are then read from L2 once per query tile
+//           instead of once per pair, which long sequences would pay for.
+template <int HD, int MODE, bool NARROW> struct Shape {
+  static constexpr int ROW_BYTES = MODE == MODE_SPLIT ? 2 * split::row_halves(HD) : HD * (MODE == MODE_TF32 ? 4 : 2);
+  static constexpr bool WIDE = ROW_BYTES > 256;
+  static_assert(!(WIDE && NARROW), "a wide CTA is already a single query tile");
+  static constexpr int QT = (WIDE || NARROW) ? 1 : 2;
+  static constexpr int STG = WIDE ? 1 : (NARROW ? (ROW_BYTES <= 128 ? 2 : 1) : 2);
+  using PL = Plan<ROW_BYTES, QT, STG>;
+  static constexpr int WARP_TMA = QT * 8;          // after the softmax warps (eight per query tile)
+  static constexpr int WARP_MMA = QT * 8 + 1;
+  static constexpr int THREADS = (QT * 8 + 2) * 32;
+  static constexpr int CTAS_PER_SM = NARROW ? 2 : 1;
+  static constexpr uint32_t TMEM_COLS = QT == 1 ? 256 : 512;   // S tiles in [0, QT x 128), O tiles behind them
+  static_assert(CTAS_PER_SM * (PL::BYTES + 1024) <= 227 * 1024, "shared memory of the CTAs of one SM");
+};
+
 enum Bar : int {  // mbarrier indices
   BAR_Q_FULL = 0,    // [NQT]
   BAR_K_FULL = 2,    // [STAGES]
@@ -101,6 +121,11 @@ enum Bar : int {  // mbarrier indices
 #ifdef MCA_TC_TRACE
 __device__ long long g_tc_trace[4 * 64 * 8];
 __device__ long long g_tc_trace_w[16 * 64 * 4];  // per softmax warp, query tile 0: got S, local max done, exchange done, arrived
+__device__ long long g_tc_phase[16];   // whole-CTA phases of block (0,0): entry, set-up, first loads, loop, epilogue, exit
+#define TC_PHASE(i, who)                                                                                 \
+  do {                                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (who)) g_tc_phase[i] = clock64();                          \
+  } while (0)
 #define TC_TRACE_W(it, slot)                                                                              \
   do {                                                                                                   \
     if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && x == 0 && (it) < 64) g_tc_trace_w[(warp * 64 + (it)) * 4 + (slot)] = clock64(); \
@@ -112,6 +137,7 @@ __device__ long long g_tc_trace_w[16 * 64 * 4];  // per softmax warp, query tile
 #else
 #define TC_TRACE(role, it, slot) do { } while (0)
 #define TC_TRACE_W(it, slot) do { } while (0)
+#define TC_PHASE(i, who) do { } while (0)
 #endif
 
 struct TcParams {
@@ -144,8 +170,8 @@ struct TcParams {
 constexpr float MASKED_LOG2 = -131072.0f;
 
 // MODE_TF32: P is handed to the second product as fp32 in place of S; MODE_TF32 and MODE_SPLIT write fp32 output.
-template <int HD, int MODE, bool MASKED>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int HD, int MODE, bool MASKED, bool NARROW>
+__global__ void __launch_bounds__((Shape<HD, MODE, NARROW>::THREADS), (Shape<HD, MODE, NARROW>::CTAS_PER_SM))
 sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
   constexpr bool TF32 = MODE == MODE_TF32;
@@ -155,9 +181,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   constexpr int BOX = 128 / ELT;               // elements per 128-byte sub-tile row
   // split rows are [hi (64 fp16, HD used) | lo (64 fp16, HD used)]: two 128-byte sub-tiles for head sizes up to 64;
   // 128-wide heads have [hi (128) | lo (128)], four sub-tiles, one query tile per CTA and single-stage K and V
-  constexpr bool WIDE = SPLIT && HD > 64;
-  using PL = Plan<SPLIT ? (WIDE ? 512 : 256) : HD * ELT, WIDE ? 1 : 2, WIDE ? 1 : 2>;
-  constexpr int QT = PL::QTILES, STG = PL::STAGES;
+  using SH = Shape<HD, MODE, NARROW>;
+  using PL = typename SH::PL;
+  constexpr int QT = SH::QT, STG = SH::STG;
+  constexpr int WARP_TMA = SH::WARP_TMA, WARP_MMA = SH::WARP_MMA;
+  constexpr uint32_t TMEM_COLS = SH::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -193,9 +221,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
   __shared__ int s_abort;
+  TC_PHASE(0, tid == 0);
   if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
   __syncthreads();
   if (s_abort != 0) return;
+  TC_PHASE(1, tid == 0);
 
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
@@ -216,6 +246,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  TC_PHASE(2, tid == 0);
 
   if (warp == WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
@@ -241,6 +272,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tma_load_4d(smem_base + PL::OFF_K + st * PL::TILE_BYTES + s * PL::SUB_BYTES, &map_k, bar(BAR_K_FULL + st), s * BOX,
                       j * BLK, hi, bi);
         issued_k = j + 1;
+        if (j == 0) TC_PHASE(3, true);
         ok = mbar_wait(bar(BAR_V_EMPTY + st), ph ^ 1u, p.status, 11, j);
         if (!ok) break;
         mbar_expect_tx(bar(BAR_V_FULL + st), PL::TILE_BYTES);
@@ -308,7 +340,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // into the first 64 columns of the S tile; tf32 P overwrites S column for column.
         // B: V, one step = 16 or 8 key rows of 128 bytes per sub-tile.
         const uint64_t dv = desc_v0 + (uint64_t)((st * PL::TILE_BYTES) >> 4);
-        const uint32_t d_tmem = tmem_base_u + 2 * BLK + x * BLK;
+        const uint32_t d_tmem = tmem_base_u + QT * BLK + x * BLK;
         const uint32_t a_tmem = tmem_base_u + x * BLK;
 #pragma unroll
         for (int kk = half * (KSTEPS_PV / 2); kk < (half + 1) * (KSTEPS_PV / 2); ++kk) {
@@ -328,8 +360,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
       for (int x = 0; x < NQT; ++x)
         if (n_tiles[x] && ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_Q_FULL + x), 0, p.status, 20, x));
+      TC_PHASE(4, lane == 0);
       if (ok && n_max > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_K_FULL + 0), 0, p.status, 21, 0));
+        TC_PHASE(5, lane == 0);
         if (ok) {
           tc_fence_after();
 #pragma unroll
@@ -404,7 +438,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int r0 = lane_base + (lane >> 2);             // tile rows r0 and r0 + 8
     const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
     const uint32_t t_s = t_row + (uint32_t)(x * BLK);
-    const uint32_t t_o = t_row + (uint32_t)(2 * BLK + x * BLK);
+    const uint32_t t_o = t_row + (uint32_t)(QT * BLK + x * BLK);
     const int n = n_tiles[x];
     const int qrow0 = q0 + x * BLK;
     float m_used[2] = {-INFINITY, -INFINITY};
@@ -415,6 +449,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       TC_TRACE(x, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait_hot(bar(BAR_S_FULL + x), (uint32_t)(j & 1), p.status, 30 + x, j));
       if (!ok) break;
+      if (j == 0) TC_PHASE(6, warp == 0 && lane == 0);
       TC_TRACE(x, j, 1);
       TC_TRACE_W(j, 0);
       tc_fence_after();
@@ -572,6 +607,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     // epilogue: finish the row sums, hand them to the thread that owns the row in the one-lane-per-
     // thread layout, then O / l -> global
+    TC_PHASE(7, warp == 0 && lane == 0);
     if (ok && n > 0) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -588,6 +624,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (lane == 0) mbar_arrive(bar(BAR_RED + x));
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_RED + x), 0, p.status, 36 + x, n));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + x), (uint32_t)((n - 1) & 1), p.status, 34 + x, n));
+      TC_PHASE(8, warp == 0 && lane == 0);
       if (ok) {
         tc_fence_after();
         constexpr int OC = HD / 2;                       // O columns per thread: row = lane, half of the head
@@ -596,7 +633,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float lsum = red_l[row];
         // split mode: the pre-pass scaled v by a power of two; dividing it out here is exact
         const float inv = SPLIT ? __ldg(p.split_fac + split::FAC_INV_V) / lsum : 1.0f / lsum;
-        const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * BLK + x * BLK + half * OC);
+        const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(QT * BLK + x * BLK + half * OC);
         const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
         float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
@@ -707,8 +744,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   }
   // ------------------------------------------------------------------ teardown
+  TC_PHASE(9, warp == 0 && lane == 0);
   tc_fence_before();
   __syncthreads();
+  TC_PHASE(10, tid == 0);
   if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -720,6 +759,35 @@ struct SplitExtras {
   const float* fac = nullptr;   // split::SplitFac
   float *row_max = nullptr, *row_sum = nullptr, *y_copy = nullptr;
 };
+
+// Sequences up to this many keys run as NARROW CTAs (one query tile each, two CTAs per SM).  MCA_TC_NARROW_LEN in the
+// environment, or mca_tc_narrow_len(), replaces the threshold (0: never).
+int& narrow_limit() {
+  static int limit = [] {
+    const char* e = getenv("MCA_TC_NARROW_LEN");
+    return e != nullptr ? atoi(e) : 2048;
+  }();
+  return limit;
+}
+inline bool narrow_ctas(int T) { return T <= narrow_limit(); }
+
+template <int HD, int MODE, bool NARROW>
+int launch_shape(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p, int B, int H, int T,
+                 bool masked, cudaStream_t st) {
+  using SH = Shape<HD, MODE, NARROW>;
+  const size_t smem = SH::PL::BYTES;
+  dim3 grid(mca_ceil_div(T, SH::QT * BLK), B * H);
+  if constexpr (MODE != MODE_TF32) {
+    if (masked) {
+      MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, true, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sdpa_fwd_tc_kernel<HD, MODE, true, NARROW><<<grid, SH::THREADS, smem, st>>>(mq, mk, mv, p);
+      return mca_launch_status();
+    }
+  }
+  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, false, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  sdpa_fwd_tc_kernel<HD, MODE, false, NARROW><<<grid, SH::THREADS, smem, st>>>(mq, mk, mv, p);
+  return mca_launch_status();
+}
 
 template <int HD, int MODE>
 int launch_tc(const void* q, const void* k, const void* v, int causal, int B, int H, int T, void* y, float* lse,
@@ -764,23 +832,13 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.row_max = split ? split->row_max : nullptr;
   p.row_sum = split ? split->row_sum : nullptr;
   p.y_copy = split ? split->y_copy : nullptr;
-  constexpr bool WIDE = MODE == MODE_SPLIT && HD > 64;   // as in the kernel: one query tile, single-stage K and V
-  using PL = Plan<MODE == MODE_SPLIT ? (WIDE ? 512 : 256) : HD * (MODE == MODE_TF32 ? 4 : 2), WIDE ? 1 : 2, WIDE ? 1 : 2>;
-  const size_t smem = PL::BYTES;
   p.mask_bits = mask ? mask->bits : nullptr;
   p.mask_batch_stride = mask ? mask->batch_stride : 0;
   p.mask_row_stride = mask ? mask->row_stride : 0;
-  dim3 grid(mca_ceil_div(T, PL::QTILES * BLK), B * H);
-  if constexpr (MODE != MODE_TF32) {
-    if (mask != nullptr) {
-      MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sdpa_fwd_tc_kernel<HD, MODE, true><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
-      return mca_launch_status();
-    }
+  if constexpr (!Shape<HD, MODE, false>::WIDE && MODE != MODE_TF32) {
+    if (narrow_ctas(T)) return launch_shape<HD, MODE, true>(mq, mk, mv, p, B, H, T, mask != nullptr, st);
   }
-  MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  sdpa_fwd_tc_kernel<HD, MODE, false><<<grid, TC_THREADS, smem, st>>>(mq, mk, mv, p);
-  return mca_launch_status();
+  return launch_shape<HD, MODE, false>(mq, mk, mv, p, B, H, T, mask != nullptr, st);
 }
 
 template <int HD>
@@ -805,6 +863,9 @@ int launch_split(const float* q, const float* k, const float* v, int causal, int
 #ifdef MCA_TC_TRACE
 extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch(long long* host, int count) {
   return (int)cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * count);
+}
+extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch_phase(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_tc_phase, sizeof(long long) * count);
 }
 extern "C" __attribute__((visibility("default"))) int mca_tc_trace_fetch_w(long long* host, int count) {
   return (int)cudaMemcpyFromSymbol(host, g_tc_trace_w, sizeof(long long) * count);
@@ -867,6 +928,12 @@ int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int 
   if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
   if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
+}
+
+int mca_tc_narrow_len(int len) {
+  const int before = narrow_limit();
+  if (len >= 0) narrow_limit() = len;
+  return before;
 }
 
 int64_t mca_sdpa_forward_f32_tc_workspace_bytes(int B, int H, int T) {

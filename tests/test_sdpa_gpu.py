@@ -537,3 +537,37 @@ def test_bf16_tensor_core_general_and_batch_masks(cuda, T, D):
         for g_, r_ in zip(a.backward(dy), oracle.sdpa_backward(q, k, v, dy, mask, mode, f64=True)):
             assert rel_err(g_, r_) < BF16_TOL
         a.close()
+
+
+@pytest.mark.parametrize("dtype_name,D", [("bf16", 64), ("bf16", 128), ("fp32", 16), ("fp32", 32), ("fp32", 64)])
+@pytest.mark.parametrize("T", [130, 640, 1300])
+def test_one_tile_and_two_tile_ctas_agree(cuda, dtype_name, D, T):
+    """Short sequences run the forward as CTAs of one query tile, two to an SM; long ones as CTAs of two tiles.  The
+    arithmetic per query tile is the same, so the two shapes agree bit for bit: causal, no mask, general and batch
+    masks; each is also held to the oracle."""
+    from mycaffe_b200 import _lib, function_ids as ids
+    lib = _lib.load()
+    rng = np.random.default_rng(T + D)
+    B, H = 2, 3
+    bf16 = dtype_name == "bf16"
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    if bf16:
+        q, k, v = (bf16_round(a) for a in (q, k, v))
+    general = (rng.random((T, T)) > 0.4).astype(np.float32)
+    general[T // 3] = 0.0
+    keys = (rng.random((B, T)) > 0.3).astype(np.float32)
+    before = lib.mca_tc_narrow_len(-1)
+    try:
+        for mask, mode, batch in ((oracle.causal_mask(T), 1, False), (None, 0, False), (general, 1, False), (keys, 2, True)):
+            out = []
+            for limit in (0, 1 << 30):
+                lib.mca_tc_narrow_len(limit)
+                a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16 if bf16 else None)
+                out.append(a.forward(q, k, v, mask, batch_mask=batch))
+                a.close()
+            np.testing.assert_array_equal(out[0], out[1])
+            ref = oracle.sdpa_forward(q, k, v, mask, mode, f64=True)
+            assert rel_err(out[0], ref) < (BF16_TOL if bf16 else FP32_TIGHT)
+    finally:
+        lib.mca_tc_narrow_len(before)
+    assert lib.mca_tc_narrow_len(-1) == before
