@@ -219,23 +219,22 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0) && (lane == 0) && (warp == 0 || warp == 8 || warp == WARP_MMA);
 #endif
 
-  // An earlier CTA already failed: leave before touching barriers or TMEM (uniform decision).
+  // Set-up, each part by another warp so that their latencies overlap: the status word of the launch (has an
+  // earlier CTA failed?), the barriers, the tensor maps' descriptors, the TMEM allocation.
   __shared__ int s_abort;
   TC_PHASE(0, tid == 0);
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
-  __syncthreads();
-  if (s_abort != 0) return;
-  TC_PHASE(1, tid == 0);
-
+  if (tid == 32) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  if (warp == WARP_TMA && lane == 0) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
   if (tid == 0) {
     for (int i = 0; i < BAR_COUNT; ++i) {
       const bool softmax_bar = (i >= BAR_P_READY && i < BAR_P_READY + NQT) || (i >= BAR_P_HALF && i < BAR_P_HALF + NQT);
       mbar_init(bar(i), (softmax_bar || i >= BAR_RED) ? 8u : 1u);  // the eight warps of a group arrive once per warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tensormap(&map_q);
-    prefetch_tensormap(&map_k);
-    prefetch_tensormap(&map_v);
   }
   if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -245,6 +244,10 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
+    if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
+    return;
+  }
   bool ok = true;
   TC_PHASE(2, tid == 0);
 

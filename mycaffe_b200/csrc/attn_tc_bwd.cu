@@ -153,21 +153,26 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int q0 = qt * BLK;
   const int n = p.causal ? (min(q0 + BLK, T) + BLK - 1) / BLK : (T + BLK - 1) / BLK;
 
+  // set-up, each part by another warp so that their latencies overlap (status word, barriers, descriptors, TMEM)
   __shared__ int s_abort;
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(p.status);
-  __syncthreads();
-  if (s_abort != 0) return;
+  if (tid == 32) s_abort = *reinterpret_cast<volatile int*>(p.status);
+  if (warp == WARP_TMA && lane == 0) {
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
   if (tid == 0) {
     for (int i = 0; i < DQ_BAR_COUNT; ++i)
       mbar_init(bar(i), (i == DQ_SDP_FREE || i == DQ_DS_READY) ? (uint32_t)EW_WARPS : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
   }
   if (warp == WARP_MMA) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
+    if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
+    return;
+  }
   constexpr uint32_t C_S = 0, C_DP = 128, C_DS = 256, C_DQ = SPLIT ? 384 : 320;
   bool ok = true;
 
@@ -446,19 +451,23 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     return;
   }
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + PL::OFF_FLAG_KV);
-  if (tid == 0) *s_abort = *reinterpret_cast<volatile int*>(p.status);
-  __syncthreads();
-  if (*s_abort != 0) return;
+  if (tid == 32) *s_abort = *reinterpret_cast<volatile int*>(p.status);
+  if (warp == WARP_TMA && lane == 0) {
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
   if (tid == 0) {
     for (int i = 0; i < KV_BAR_COUNT; ++i) mbar_init(bar(i), (i == KV_PT_READY || i == KV_LD_READY || i == KV_DST_READY) ? (uint32_t)EW_WARPS : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
   }
   if (warp == WARP_MMA) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (*s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
+    if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
+    return;
+  }
   constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
   bool ok = true;
 
