@@ -642,11 +642,11 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
         bool scattered = false;
         if constexpr (!F32_OUT) {
-          if (p.n_more > 0) {   // uniform over the grid
-            // Output that also goes to peers' buffers: stage this warp's 32 rows x OC columns in the shared memory
-            // of its query tile (every product that read it has completed), then store whole 16-byte pieces so
-            // that one store instruction covers full contiguous row segments (128 bytes at head size 128)
-            // instead of 32 pieces from 32 different rows: NVLink carries them as full packets.
+          {
+            // Stage this warp's 32 rows x OC columns in the shared memory of its query tile (every product that read
+            // it has completed), then store whole 16-byte pieces so that one store instruction covers full contiguous
+            // row segments (128 bytes at head size 128) instead of 32 pieces from 32 different rows: a quarter of the
+            // memory transactions for the local copy, and NVLink carries the copies for the peers as full packets.
             scattered = true;
             constexpr int PIECES = OC * 2 / 16;          // 16-byte pieces of a row-half
             constexpr int RPI = 32 / PIECES;             // rows one store instruction covers
