@@ -94,9 +94,18 @@ __global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st,
     const float4 v = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
   }
+  // one atomic per block: thousands of warps updating the same three words serialise in L2
+  __shared__ float s_m[8];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax + job.slot[blockIdx.y], __float_as_uint(m));
+  if ((threadIdx.x & 31) == 0) s_m[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < 8 ? s_m[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (threadIdx.x == 0 && m > 0.f) atomicMax(amax + job.slot[blockIdx.y], __float_as_uint(m));
+  }
 }
 
 // The power of two that brings max |x| into [2^12, 2^13): the largest fp16 is 65504 and the low half of an element
@@ -130,23 +139,26 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
       fac[FAC_INV_DY] = 1.0f / sdy;
     }
   }
-  constexpr int V4 = HD / 4;
+  // eight elements per thread and step: two 16-byte loads (adjacent pieces of one row), one 16-byte store per half
+  constexpr int V8 = HD / 8;
   const bool contiguous = is_contiguous(st, H, T, HD);
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V4; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / V4;          // V4 is a power of two
-    const int c = (int)(i - row * V4);
-    const float4 v = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
-    const float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-    __half hi[4], lo[4];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V8; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / V8;          // V8 is a power of two
+    const int c = (int)(i - row * V8);
+    const float* src = piece_ptr<HD>(x, st, contiguous, H, T, 2 * i);
+    const float4 v0 = *reinterpret_cast<const float4*>(src), v1 = *reinterpret_cast<const float4*>(src + 4);
+    const float e[8] = {v0.x * sc, v0.y * sc, v0.z * sc, v0.w * sc, v1.x * sc, v1.y * sc, v1.z * sc, v1.w * sc};
+    __align__(16) __half hi[8];
+    __align__(16) __half lo[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       hi[j] = __float2half_rn(e[j]);
       lo[j] = __float2half_rn(e[j] - __half2float(hi[j]));
     }
     constexpr int RH = row_halves(HD);
-    __half* o = dst + row * RH + c * 4;
-    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(hi);
-    *reinterpret_cast<uint2*>(o + RH / 2) = *reinterpret_cast<const uint2*>(lo);
+    __half* o = dst + row * RH + c * 8;
+    *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(hi);
+    *reinterpret_cast<uint4*>(o + RH / 2) = *reinterpret_cast<const uint4*>(lo);
   }
 }
 
@@ -158,11 +170,13 @@ inline int run(const Job& job, int count, const McaStrides& st, int H, int T, in
   int lo = job.slot[0], hi = job.slot[0];
   for (int i = 1; i < count; ++i) { lo = std::min(lo, job.slot[i]); hi = std::max(hi, job.slot[i]); }
   MCA_CUDA_TRY(cudaMemsetAsync(w.amax + lo, 0, sizeof(unsigned int) * (size_t)(hi - lo + 1), stream));
-  const int blocks = (int)std::min<int64_t>(148 * 8, (rows * (HD / 4) + 255) / 256);
-  amax_kernel<HD><<<dim3(blocks, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax);
+  // the reduction as one wave of resident blocks over all its tensors (eight blocks of 256 threads per SM)
+  const int blocks_amax = (int)std::min<int64_t>((148 * 8) / count, (rows * (HD / 4) + 4 * 256 - 1) / (4 * 256));
+  amax_kernel<HD><<<dim3(std::max(1, blocks_amax), count), 256, 0, stream>>>(job, st, H, T, rows, w.amax);
   int e = mca_launch_status();
   if (e) return e;
-  rows_kernel<HD><<<dim3(blocks, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax, w.fac, backward ? 1 : 0);
+  const int blocks_rows = (int)std::min<int64_t>(148 * 8, (rows * (HD / 8) + 255) / 256);
+  rows_kernel<HD><<<dim3(blocks_rows, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax, w.fac, backward ? 1 : 0);
   return mca_launch_status();
 }
 
