@@ -223,6 +223,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   // earlier CTA failed?), the barriers, the tensor maps' descriptors, the TMEM allocation.
   __shared__ int s_abort;
   TC_PHASE(0, tid == 0);
+  mca_pdl_launch_dependents();   // a kernel launched behind this one may set itself up as this one's CTAs leave
   if (tid == 32) s_abort = *reinterpret_cast<volatile int*>(p.status);
   if (warp == WARP_TMA && lane == 0) {
     prefetch_tensormap(&map_q);
@@ -244,6 +245,7 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  mca_pdl_wait();   // launched ahead of the kernels before it: from here on their results are complete and visible
   if (s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
     return;
@@ -783,13 +785,11 @@ int launch_shape(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap
   if constexpr (MODE != MODE_TF32) {
     if (masked) {
       MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, true, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sdpa_fwd_tc_kernel<HD, MODE, true, NARROW><<<grid, SH::THREADS, smem, st>>>(mq, mk, mv, p);
-      return mca_launch_status();
+      return mca_launch_pdl(sdpa_fwd_tc_kernel<HD, MODE, true, NARROW>, grid, dim3(SH::THREADS), smem, st, mq, mk, mv, p);
     }
   }
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_fwd_tc_kernel<HD, MODE, false, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  sdpa_fwd_tc_kernel<HD, MODE, false, NARROW><<<grid, SH::THREADS, smem, st>>>(mq, mk, mv, p);
-  return mca_launch_status();
+  return mca_launch_pdl(sdpa_fwd_tc_kernel<HD, MODE, false, NARROW>, grid, dim3(SH::THREADS), smem, st, mq, mk, mv, p);
 }
 
 template <int HD, int MODE>

@@ -155,6 +155,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   // set-up, each part by another warp so that their latencies overlap (status word, barriers, descriptors, TMEM)
   __shared__ int s_abort;
+  mca_pdl_launch_dependents();
   if (tid == 32) s_abort = *reinterpret_cast<volatile int*>(p.status);
   if (warp == WARP_TMA && lane == 0) {
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
@@ -169,6 +170,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  mca_pdl_wait();   // launched ahead of the kernels before it: from here on their results are complete and visible
   if (s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
     return;
@@ -451,6 +453,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     return;
   }
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + PL::OFF_FLAG_KV);
+  mca_pdl_launch_dependents();
   if (tid == 32) *s_abort = *reinterpret_cast<volatile int*>(p.status);
   if (warp == WARP_TMA && lane == 0) {
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
@@ -464,6 +467,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  mca_pdl_wait();   // launched ahead of the kernels before it: from here on their results are complete and visible
   if (*s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
     return;
@@ -778,6 +782,8 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // warp covers 256 / D rows.
 __global__ void bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
                                       int64_t rows, int H, int T, int D, const McaStrides ys, float* __restrict__ delta) {
+  mca_pdl_launch_dependents();
+  mca_pdl_wait();   // dy and y are earlier kernels' output
   const int lane = threadIdx.x & 31, g = D / 8, rpw = 32 / g;        // g in {8, 16}
   const int64_t row = ((int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5)) * rpw + lane / g;
   float acc = 0.f;
@@ -808,12 +814,10 @@ int launch_bwd_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
   MCA_CUDA_TRY(cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<HD, SPLIT, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
   dim3 grid(mca_ceil_div(T, BLK), B * H);
   p.out0 = dk; p.out1 = dv;
-  sdpa_bwd_dkdv_tc_kernel<HD, SPLIT, MASKED><<<grid, BW_THREADS, smem_kv, st>>>(mq, mk, mv, mdo, p);
-  int e = mca_launch_status();
+  int e = mca_launch_pdl(sdpa_bwd_dkdv_tc_kernel<HD, SPLIT, MASKED>, grid, dim3(BW_THREADS), smem_kv, st, mq, mk, mv, mdo, p);
   if (e) return e;
   p.out0 = dq; p.out1 = nullptr;
-  sdpa_bwd_dq_tc_kernel<HD, SPLIT, MASKED><<<grid, BW_THREADS, smem_dq, st>>>(mq, mk, mv, mdo, p);
-  return mca_launch_status();
+  return mca_launch_pdl(sdpa_bwd_dq_tc_kernel<HD, SPLIT, MASKED>, grid, dim3(BW_THREADS), smem_dq, st, mq, mk, mv, mdo, p);
 }
 
 void set_mask(BwdParams& p, const McaMaskBits* mask, int T) {
@@ -855,6 +859,8 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
 // D / 4 lanes share a row (16-byte loads), so a warp covers 128 / D rows.
 __global__ void bwd_delta_f32_kernel(const float* __restrict__ dy, const float* __restrict__ y, int64_t rows, int H, int T, int D,
                                      const McaStrides ys, float* __restrict__ delta) {
+  mca_pdl_launch_dependents();
+  mca_pdl_wait();   // dy and y are earlier kernels' output
   const int lane = threadIdx.x & 31, g = D / 4, rpw = 32 / g;        // g in {4, 8, 16}
   const int64_t row = ((int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5)) * rpw + lane / g;
   const int c = (lane % g) * 4;
@@ -887,9 +893,10 @@ int launch_bwd_split(const float* dy, const float* y_copy, const float* lse, flo
   if (e) return e;
   {
     const int64_t rows_per_block = 8 * (128 / HD);   // eight warps, 128 / HD rows each
-    bwd_delta_f32_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(dy, y_copy, rows, H, T, HD, sout, delta);
+    e = mca_launch_pdl(bwd_delta_f32_kernel, dim3((unsigned)((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st, dy,
+                       y_copy, rows, H, T, HD, sout, delta);
   }
-  if ((e = mca_launch_status())) return e;
+  if (e) return e;
   CUtensorMap mq, mk, mv, mdo;
   const McaStrides sp{(int64_t)H * T * 128, (int64_t)T * 128, 128};
   const CUtensorMap* maps[4] = {&mq, &mk, &mv, &mdo};
@@ -947,12 +954,12 @@ int mca_sdpa_backward_tc_masked(const void* q, const void* k, const void* v, con
   if (D != 64 && D != 128) return ERROR_ATTN_UNSUPPORTED_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)B * H * T;
+  int e;
   {
     const int64_t rows_per_block = 8 * (256 / D);   // eight warps, 256 / D rows each
-    bwd_delta_bf16_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, H, T, D, mca_out_strides(layout, H, T, D), delta_scratch);
+    e = mca_launch_pdl(bwd_delta_bf16_kernel, dim3((unsigned)((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st,
+                       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, rows, H, T, D, mca_out_strides(layout, H, T, D), delta_scratch);
   }
-  int e = mca_launch_status();
   if (e) return e;
   if (D == 128) return launch_bwd<128>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st, mask);
   return launch_bwd<64>(q, k, v, dy, lse, delta_scratch, causal, B, H, T, dq, dk, dv, status, layout, st, mask);

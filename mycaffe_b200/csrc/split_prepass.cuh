@@ -74,6 +74,8 @@ __host__ __device__ inline bool is_contiguous(const McaStrides& st, int H, int T
 template <int HD>
 __global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
                                                    unsigned int* __restrict__ amax) {
+  mca_pdl_launch_dependents();
+  mca_pdl_wait();   // the tensors are earlier kernels' output
   const float* x = job.src[blockIdx.y];
   constexpr int V4 = HD / 4;
   const bool contiguous = is_contiguous(st, H, T, HD);
@@ -122,6 +124,8 @@ template <int HD>
 __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
                                                    const unsigned int* __restrict__ amax, float* __restrict__ fac,
                                                    int backward) {
+  mca_pdl_launch_dependents();
+  mca_pdl_wait();   // the magnitudes are the reduction's output
   const int which = blockIdx.y;
   const float* x = job.src[which];
   __half* dst = job.dst[which];
@@ -172,12 +176,11 @@ inline int run(const Job& job, int count, const McaStrides& st, int H, int T, in
   MCA_CUDA_TRY(cudaMemsetAsync(w.amax + lo, 0, sizeof(unsigned int) * (size_t)(hi - lo + 1), stream));
   // the reduction as one wave of resident blocks over all its tensors (eight blocks of 256 threads per SM)
   const int blocks_amax = (int)std::min<int64_t>((148 * 8) / count, (rows * (HD / 4) + 4 * 256 - 1) / (4 * 256));
-  amax_kernel<HD><<<dim3(std::max(1, blocks_amax), count), 256, 0, stream>>>(job, st, H, T, rows, w.amax);
-  int e = mca_launch_status();
+  int e = mca_launch_pdl(amax_kernel<HD>, dim3(std::max(1, blocks_amax), count), dim3(256), 0, stream, job, st, H, T, rows, w.amax);
   if (e) return e;
   const int blocks_rows = (int)std::min<int64_t>(148 * 8, (rows * (HD / 8) + 255) / 256);
-  rows_kernel<HD><<<dim3(blocks_rows, count), 256, 0, stream>>>(job, st, H, T, rows, w.amax, w.fac, backward ? 1 : 0);
-  return mca_launch_status();
+  return mca_launch_pdl(rows_kernel<HD>, dim3(blocks_rows, count), dim3(256), 0, stream, job, st, H, T, rows, w.amax, w.fac,
+                        backward ? 1 : 0);
 }
 
 }  // namespace split
