@@ -1,6 +1,7 @@
 // Shared declarations for the attention library (sm_100a only).
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -110,7 +111,8 @@ static inline int mca_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  static const bool plain = getenv("MCA_NO_PDL") != nullptr;   // every launch the ordinary way (for comparisons)
+  cfg.attrs = attr; cfg.numAttrs = plain ? 0 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
   if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
   return mca_launch_status();
