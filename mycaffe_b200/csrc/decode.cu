@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(DEC_THREADS, KVM == 1 ? 2 : 1) decode_split_ke
   __shared__ float s_ml[DEC_WARPS][KVM][2];
 
   mca_pdl_launch_dependents();   // a projection kernel that follows may start fetching its weights
+  mca_pdl_wait();                // launched ahead of the kernels before it: q is their output, and the scratch theirs to read
   const int b = blockIdx.z;
   const int h0 = blockIdx.y * KVM;          // first query head of this CTA
   const int kvh = h0 / p.kv_mul;
@@ -490,13 +491,27 @@ int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
     MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MCA_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<CT, HS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  switch (kvmt) {
-    case 1: decode_split_kernel<CT, HS, 1><<<grid, DEC_THREADS, smem, st>>>(p); break;
-    case 2: decode_split_kernel<CT, HS, 2><<<grid, DEC_THREADS, smem, st>>>(p); break;
-    case 4: decode_split_kernel<CT, HS, 4><<<grid, DEC_THREADS, smem, st>>>(p); break;
-    default: return ERROR_ATTN_UNSUPPORTED_SHAPE;
+  // Up to eight sequences the kernel is launched ahead of the one before it (resident and waiting when that one
+  // finishes: the step is short and the launch latency shows, + 6 % at one sequence).  With more sequences the
+  // kernels either side of it in a decode step are the tensor-core projections, and the whole step measured 15-25 %
+  // slower with the attention launched ahead of them: an ordinary launch.
+  int e;
+  if (B <= 8) {
+    switch (kvmt) {
+      case 1: e = mca_launch_pdl(decode_split_kernel<CT, HS, 1>, grid, dim3(DEC_THREADS), smem, st, p); break;
+      case 2: e = mca_launch_pdl(decode_split_kernel<CT, HS, 2>, grid, dim3(DEC_THREADS), smem, st, p); break;
+      case 4: e = mca_launch_pdl(decode_split_kernel<CT, HS, 4>, grid, dim3(DEC_THREADS), smem, st, p); break;
+      default: return ERROR_ATTN_UNSUPPORTED_SHAPE;
+    }
+  } else {
+    switch (kvmt) {
+      case 1: decode_split_kernel<CT, HS, 1><<<grid, DEC_THREADS, smem, st>>>(p); break;
+      case 2: decode_split_kernel<CT, HS, 2><<<grid, DEC_THREADS, smem, st>>>(p); break;
+      case 4: decode_split_kernel<CT, HS, 4><<<grid, DEC_THREADS, smem, st>>>(p); break;
+      default: return ERROR_ATTN_UNSUPPORTED_SHAPE;
+    }
+    e = mca_launch_status();
   }
-  int e = mca_launch_status();
   if (e) return e;
   if (p.nsplit > 1) {
     // programmatic dependent launch: the combine pass is resident and waiting when the last split finishes
