@@ -311,7 +311,8 @@ MCA_API int mca_wait_probe(int* status, int limit_us, void* stream);
 /* Tensor-core SDPA backward (bf16).  Same math as attnHandle<T>::Backward, attn.cu:608-661, with a
  * causal or absent mask; P is recomputed from `lse` (written by mca_sdpa_forward_tc on the same
  * inputs) instead of read from a saved (B,H,T,T) tensor.  q,k,v,y,dy,dq,dk,dv: (B,H,T,D) bf16,
- * D in {64,128}; delta_scratch: (B,H,T) floats of scratch; status as in the forward. */
+ * D in {64,128}; delta_scratch: (B,H,T) floats of scratch; status as in the forward.  The gradients must not
+ * overlap the inputs (the reference's diff blobs never do): the dQ kernel runs under the tail of the dK/dV kernel. */
 MCA_API int mca_sdpa_backward_tc(const void* q, const void* k, const void* v, const void* y, const void* dy,
                                  const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
                                  int T, int D, void* dq, void* dk, void* dv, int* status, void* stream);

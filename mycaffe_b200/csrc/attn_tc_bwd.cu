@@ -170,9 +170,14 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  mca_pdl_wait();   // launched ahead of the kernels before it: from here on their results are complete and visible
+  // No wait here.  The kernel before this one in a backward is the dK/dV kernel, which lets its dependents go only
+  // after its own wait: when a CTA of this kernel runs, everything before that kernel (delta, the forward, the operand
+  // split) is complete and visible, and that is all this kernel reads.  It writes dQ only, which the dK/dV kernel does
+  // not touch, so its CTAs work in the SMs that kernel's last wave leaves free.  The wait at the end keeps the order
+  // for what follows: this kernel is not complete before the dK/dV kernel is.
   if (s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
+    mca_pdl_wait();
     return;
   }
   constexpr uint32_t C_S = 0, C_DP = 128, C_DS = 256, C_DQ = SPLIT ? 384 : 320;
@@ -394,6 +399,7 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   tc_fence_before();
   __syncthreads();
   if (warp == WARP_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  mca_pdl_wait();   // see the set-up: complete only after the kernels before it
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -453,7 +459,6 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     return;
   }
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + PL::OFF_FLAG_KV);
-  mca_pdl_launch_dependents();
   if (tid == 32) *s_abort = *reinterpret_cast<volatile int*>(p.status);
   if (warp == WARP_TMA && lane == 0) {
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
@@ -468,6 +473,7 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   mca_pdl_wait();   // launched ahead of the kernels before it: from here on their results are complete and visible
+  mca_pdl_launch_dependents();   // only now: the dQ kernel behind this one starts without a wait of its own
   if (*s_abort != 0) {   // an earlier CTA already failed: leave (uniform decision) before any copy or product is issued
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
     return;
