@@ -433,6 +433,7 @@ def _merge_heads(y):
 
 @pytest.mark.parametrize("dtype,B,H,T,D,mask_kind", [
     ("f32", 2, 3, 70, 16, "causal_handle"), ("f32", 1, 4, 128, 16, "none"), ("f32", 2, 2, 200, 64, "batch"),
+    ("f32", 2, 2, 200, 128, "causal_handle"), ("f32", 1, 2, 300, 128, "batch"),
     ("bf16", 2, 3, 200, 64, "causal"), ("bf16", 1, 2, 384, 128, "causal"), ("bf16", 2, 2, 256, 128, "none")])
 def test_packed_qkv_layout_forward_backward(cuda, dtype, B, H, T, D, mask_kind):
     """Ids 2004/2005: q, k, v read in place from the (B,T,3C) projection output, y written as (B,T,C), and the
