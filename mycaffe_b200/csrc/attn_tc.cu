@@ -70,7 +70,6 @@ template <int ROW_BYTES, int QT = 2, int STG = 2> struct Plan {   // ROW_BYTES =
   static constexpr uint32_t SUB_BYTES = BLK * 128;         // one sub-tile: 128 rows x 128 bytes
   static constexpr uint32_t TILE_BYTES = SUB * SUB_BYTES;  // 128 rows of one tensor
   static constexpr int STAGES = STG;
-  static constexpr int QTILES = QT;
   static constexpr uint32_t OFF_Q = 0;
   static constexpr uint32_t OFF_K = OFF_Q + QT * TILE_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + STAGES * TILE_BYTES;
