@@ -638,93 +638,82 @@ sdpa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // split mode: the pre-pass scaled v by a power of two; dividing it out here is exact
         const float inv = SPLIT ? __ldg(p.split_fac + split::FAC_INV_V) / lsum : 1.0f / lsum;
         const uint32_t t_o32 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(QT * BLK + x * BLK + half * OC);
-        const int64_t y_off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + y_off;
-        float* yrow_f = reinterpret_cast<float*>(p.y) + y_off;
-        bool scattered = false;
-        if constexpr (!F32_OUT) {
-          {
-            // Stage this warp's 32 rows x OC columns in the shared memory of its query tile (every product that read
-            // it has completed), then store whole 16-byte pieces so that one store instruction covers full contiguous
-            // row segments (128 bytes at head size 128) instead of 32 pieces from 32 different rows: a quarter of the
-            // memory transactions for the local copy, and NVLink carries the copies for the peers as full packets.
-            scattered = true;
-            constexpr int PIECES = OC * 2 / 16;          // 16-byte pieces of a row-half
-            constexpr int RPI = 32 / PIECES;             // rows one store instruction covers
-            uint4* stage = reinterpret_cast<uint4*>(smem_gen + PL::OFF_Q + x * PL::TILE_BYTES) +
-                           (size_t)((warp & 3) * 2 + half) * 32 * PIECES;   // private to this warp
+        if constexpr (F32_OUT && QT == 2) {
+          // fp32 output of the two-tile shape: each thread stores its own row's pieces.  (Staged like the other
+          // shapes, this instantiation's key loop spilled twice as much and ran 17 % slower at T = 8192.)
+          float* yrow_f = reinterpret_cast<float*>(p.y) + (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qi * p.ys.t + half * OC;
+          constexpr int CHD = OC < 16 ? OC : 16;
 #pragma unroll
-            for (int c = 0; c < OC / 16; ++c) {
-              uint32_t o[16];
-              tmem_ld16(t_o32 + c * 16, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; i += 8) {
-                uint4 w;
-                w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
-                w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                const int piece = c * 2 + i / 8;
-                stage[lane * PIECES + (piece ^ (lane & (PIECES - 1)))] = w;   // swizzled against bank conflicts
-              }
-            }
-            __syncwarp();
-#pragma unroll
-            for (int kk = 0; kk < PIECES; ++kk) {
-              const int r = kk * RPI + lane / PIECES, pc = lane % PIECES;
-              const uint4 w = stage[r * PIECES + (pc ^ (r & (PIECES - 1)))];
-              const int qr = qrow0 + (warp & 3) * 32 + r;
-              if (qr < T) {
-                const int64_t off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qr * p.ys.t + half * OC + pc * 8;
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + off) = w;
-#pragma unroll
-                for (int d = 0; d < 7; ++d)   // constant indices: the parameter block is not copied to local memory
-                  if (d < p.n_more) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + off) = w;
-              }
-            }
-          }
-        }
-        if constexpr (OC < 16) {   // 16-wide heads (split mode): eight columns per thread
-          uint32_t o[8];
-          tmem_ld8(t_o32, o);
-          tmem_wait_ld();
-          if (qi < T) {
-#pragma unroll
-            for (int i = 0; i < 8; i += 4) {
-              const float4 w = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                                           __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              *reinterpret_cast<float4*>(yrow_f + i) = w;
-              if (p.y_copy) *reinterpret_cast<float4*>(p.y_copy + ((int64_t)bh * T + qi) * HD + half * OC + i) = w;
-            }
-          }
-        } else if (!scattered) {
-#pragma unroll
-        for (int c = 0; c < OC / 16; ++c) {
-          uint32_t o[16];
-          tmem_ld16(t_o32 + c * 16, o);
-          tmem_wait_ld();
-          if constexpr (F32_OUT) {
+          for (int c = 0; c < OC / CHD; ++c) {
+            uint32_t o[CHD];
+            if constexpr (CHD == 16) tmem_ld16(t_o32 + c * 16, o);
+            else tmem_ld8(t_o32, o);
+            tmem_wait_ld();
             if (qi < T) {
 #pragma unroll
-              for (int i = 0; i < 16; i += 4) {
+              for (int i = 0; i < CHD; i += 4) {
                 const float4 w = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
                                              __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                *reinterpret_cast<float4*>(yrow_f + c * 16 + i) = w;
+                *reinterpret_cast<float4*>(yrow_f + c * CHD + i) = w;
                 if constexpr (SPLIT) {
-                  if (p.y_copy) *reinterpret_cast<float4*>(p.y_copy + ((int64_t)bh * T + qi) * HD + half * OC + c * 16 + i) = w;
+                  if (p.y_copy) *reinterpret_cast<float4*>(p.y_copy + ((int64_t)bh * T + qi) * HD + half * OC + c * CHD + i) = w;
                 }
               }
             }
-          } else if (qi < T) {
+          }
+        } else {
+        // Stage this warp's 32 rows x OC columns in the shared memory of its query tile (every product that read it
+        // has completed), then store whole 16-byte pieces so that one store instruction covers full contiguous row
+        // segments (128 bytes at head size 128 in bf16) instead of 32 pieces from 32 different rows: a fraction of
+        // the memory transactions for the local copy, and NVLink carries the copies for the peers as full packets.
+        constexpr int ESZ = F32_OUT ? 4 : 2;               // bytes per output element
+        constexpr int EPP = 16 / ESZ;                      // elements per 16-byte piece
+        constexpr int PIECES = OC / EPP;                   // pieces of a row-half
+        constexpr int RPI = 32 / PIECES;                   // rows one store instruction covers
+        constexpr int CH = OC < 16 ? OC : 16;              // columns per TMEM load
+        static_assert(8 * 32 * PIECES * 16 <= (int)PL::TILE_BYTES, "the output tile is staged in its query tile");
+        uint4* stage = reinterpret_cast<uint4*>(smem_gen + PL::OFF_Q + x * PL::TILE_BYTES) +
+                       (size_t)((warp & 3) * 2 + half) * 32 * PIECES;   // private to this warp
 #pragma unroll
-            for (int i = 0; i < 16; i += 8) {
-              uint4 w;
+        for (int c = 0; c < OC / CH; ++c) {
+          uint32_t o[CH];
+          if constexpr (CH == 16) tmem_ld16(t_o32 + c * 16, o);
+          else tmem_ld8(t_o32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < CH; i += EPP) {
+            uint4 w;
+            if constexpr (F32_OUT) {
+              w.x = __float_as_uint(__uint_as_float(o[i + 0]) * inv);
+              w.y = __float_as_uint(__uint_as_float(o[i + 1]) * inv);
+              w.z = __float_as_uint(__uint_as_float(o[i + 2]) * inv);
+              w.w = __float_as_uint(__uint_as_float(o[i + 3]) * inv);
+            } else {
               w.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
               w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
               w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
               w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(yrow + c * 16 + i) = w;
+            }
+            const int piece = (c * CH + i) / EPP;
+            stage[lane * PIECES + (piece ^ (lane & (PIECES - 1)))] = w;   // swizzled against bank conflicts
+          }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int kk = 0; kk < PIECES; ++kk) {
+          const int r = kk * RPI + lane / PIECES, pc = lane % PIECES;
+          const uint4 w = stage[r * PIECES + (pc ^ (r & (PIECES - 1)))];
+          const int qr = qrow0 + (warp & 3) * 32 + r;
+          if (qr < T) {
+            const int64_t off = (int64_t)bi * p.ys.b + (int64_t)hi * p.ys.h + (int64_t)qr * p.ys.t + half * OC + pc * EPP;
+            *reinterpret_cast<uint4*>(static_cast<char*>(p.y) + off * ESZ) = w;
+            if constexpr (!F32_OUT) {
+#pragma unroll
+              for (int d = 0; d < 7; ++d)   // constant indices: the parameter block is not copied to local memory
+                if (d < p.n_more) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_more[d]) + off) = w;
+            }
+            if constexpr (SPLIT) {
+              if (p.y_copy) *reinterpret_cast<uint4*>(p.y_copy + ((int64_t)bh * T + qr) * HD + half * OC + pc * EPP) = w;
             }
           }
         }
