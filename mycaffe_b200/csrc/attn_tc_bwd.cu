@@ -97,15 +97,56 @@ struct BwdParams {
   float inv_T;
 };
 
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
+
+// The gradient tiles leave through shared memory.  In the TMEM layout a thread owns a quarter of one row, so direct
+// stores are 32 sixteen-byte pieces from 32 rows per instruction (9-12 % of the backward at T = 1024 was these
+// stores).  Instead the sixteen element-wise warps write their pieces into a resident operand tile that every product
+// has finished with (Q or K for the first result, dY or V for the second), meet at a named barrier, and each warp
+// stores eight whole rows.  Every element-wise warp reaches the barrier, also after a failed wait.
+__device__ __forceinline__ void ew_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EW_WARPS * 32) : "memory"); }
+// 16-byte piece `piece` of row `row` of a staged 128-row tile with PR pieces per row (XOR-swizzled by row)
+template <int PR> __device__ __forceinline__ uint4* staged_piece(uint8_t* tile, int row, int piece) {
+  return reinterpret_cast<uint4*>(tile) + row * PR + (piece ^ (row & (PR - 1)));
+}
+// this thread's OC columns of its row, scaled, as 16-byte pieces of bf16 or fp32
+template <int PR, int OC, bool F32>
+__device__ __forceinline__ void stage_columns(uint8_t* tile, int row, int qtr, uint32_t t_addr, float mul) {
+  constexpr int CH = OC < 16 ? OC : 16;
 #pragma unroll
-  for (int i = 0; i < 16; i += 8) {
-    uint4 w;
-    w.x = pack_bf16(__uint_as_float(o[i + 0]) * mul, __uint_as_float(o[i + 1]) * mul);
-    w.y = pack_bf16(__uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
-    w.z = pack_bf16(__uint_as_float(o[i + 4]) * mul, __uint_as_float(o[i + 5]) * mul);
-    w.w = pack_bf16(__uint_as_float(o[i + 6]) * mul, __uint_as_float(o[i + 7]) * mul);
-    *reinterpret_cast<uint4*>(dst + i) = w;
+  for (int c = 0; c < OC / CH; ++c) {
+    uint32_t o[CH];
+    if constexpr (CH == 16) tmem_ld16(t_addr + c * 16, o);
+    else if constexpr (CH == 8) tmem_ld8(t_addr, o);
+    else tmem_ld4(t_addr, o);
+    tmem_wait_ld();
+    if constexpr (F32) {
+#pragma unroll
+      for (int i = 0; i < CH; i += 4)
+        *staged_piece<PR>(tile, row, (qtr * OC + c * CH + i) / 4) =
+            make_uint4(__float_as_uint(__uint_as_float(o[i]) * mul), __float_as_uint(__uint_as_float(o[i + 1]) * mul),
+                       __float_as_uint(__uint_as_float(o[i + 2]) * mul), __float_as_uint(__uint_as_float(o[i + 3]) * mul));
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH; i += 8)
+        *staged_piece<PR>(tile, row, (qtr * OC + c * CH + i) / 8) =
+            make_uint4(pack_bf16(__uint_as_float(o[i + 0]) * mul, __uint_as_float(o[i + 1]) * mul),
+                       pack_bf16(__uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul),
+                       pack_bf16(__uint_as_float(o[i + 4]) * mul, __uint_as_float(o[i + 5]) * mul),
+                       pack_bf16(__uint_as_float(o[i + 6]) * mul, __uint_as_float(o[i + 7]) * mul));
+    }
+  }
+}
+// warp w of the sixteen stores rows 8 w .. 8 w + 7 of a staged tile; off0: element offset of the tile's row 0
+template <int PR, int ESZ>
+__device__ __forceinline__ void store_staged_rows(uint8_t* tile, int w, int lane, void* out, int64_t off0, int64_t row_stride,
+                                                  int rows_valid) {
+  constexpr int RPI = 32 / PR;   // rows per store instruction
+#pragma unroll
+  for (int kk = 0; kk < 8 / RPI; ++kk) {
+    const int row = 8 * w + kk * RPI + lane / PR, piece = lane % PR;
+    if (row < rows_valid)
+      *reinterpret_cast<uint4*>(static_cast<char*>(out) + (off0 + (int64_t)row * row_stride) * ESZ + piece * 16) =
+          *staged_piece<PR>(tile, row, piece);
   }
 }
 
@@ -363,38 +404,19 @@ sdpa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_DS_READY));
     }
-    if (ok && n > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((n - 1) & 1), p.status, 132, n));
-      if (ok) {
-        tc_fence_after();
-        const int64_t d_off = (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)qi * p.os.t + qtr * OC;
-        if constexpr (SPLIT) {
-          // fp32 result; a quarter of the warps covers OC = HD / 4 columns of a row (4, 8 or 16)
-          const float mul = p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVK);
-          float* dst = reinterpret_cast<float*>(p.out0) + d_off;
-          uint32_t o[16];
-          if constexpr (OC == 16) tmem_ld16(t_row + C_DQ + qtr * OC, o);
-          else if constexpr (OC == 8) tmem_ld8(t_row + C_DQ + qtr * OC, o);
-          else tmem_ld4(t_row + C_DQ + qtr * OC, o);
-          tmem_wait_ld();
-          if (row_ok) {
-#pragma unroll
-            for (int i = 0; i < OC; i += 4)
-              *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(o[i]) * mul, __uint_as_float(o[i + 1]) * mul,
-                                                                __uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + d_off;
-#pragma unroll
-          for (int c = 0; c < OC / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld16(t_row + C_DQ + qtr * OC + c * 16, o);
-            tmem_wait_ld();
-            if (row_ok) store_row_bf16(dst + c * 16, o, 1.0f);
-          }
-        }
-      }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DQ_DONE), (uint32_t)((n - 1) & 1), p.status, 132, n));
+    constexpr int ESZ = SPLIT ? 4 : 2, PR = HD * ESZ / 16;
+    uint8_t* tile = smem_gen + PL::OFF_RES0;           // the Q tile: every product has finished with it
+    const bool fin = ok && n > 0;
+    if (fin) {
+      tc_fence_after();
+      const float mul = SPLIT ? p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVK) : 1.0f;
+      stage_columns<PR, OC, SPLIT>(tile, row, qtr, t_row + C_DQ + qtr * OC, mul);
     }
+    ew_bar_sync();
+    if (fin)
+      store_staged_rows<PR, ESZ>(tile, warp, lane, p.out0, (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)q0 * p.os.t, p.os.t,
+                                 min(BLK, T - q0));
   }
   tc_fence_before();
   __syncthreads();
@@ -737,46 +759,23 @@ sdpa_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(KV_DST_READY));
     }
-    if (ok && n > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
-      if (ok) {
-        tc_fence_after();
-        const int64_t g_off = (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)kj * p.os.t + qtr * OC;
-        if constexpr (SPLIT) {
-          const float mul_k = p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVQ);
-          const float mul_v = PT_UNSHIFT * __ldg(p.fac + split::FAC_INV_DY);
-          float* dsts[2] = {reinterpret_cast<float*>(p.out0) + g_off, reinterpret_cast<float*>(p.out1) + g_off};
-          const uint32_t cols[2] = {C_DK, C_DV};
-          const float muls[2] = {mul_k, mul_v};
-#pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            uint32_t o[16];
-            if constexpr (OC == 16) tmem_ld16(t_row + cols[w] + qtr * OC, o);
-            else if constexpr (OC == 8) tmem_ld8(t_row + cols[w] + qtr * OC, o);
-            else tmem_ld4(t_row + cols[w] + qtr * OC, o);
-            tmem_wait_ld();
-            if (key_ok) {
-#pragma unroll
-              for (int i = 0; i < OC; i += 4)
-                *reinterpret_cast<float4*>(dsts[w] + i) = make_float4(__uint_as_float(o[i]) * muls[w], __uint_as_float(o[i + 1]) * muls[w],
-                                                                      __uint_as_float(o[i + 2]) * muls[w], __uint_as_float(o[i + 3]) * muls[w]);
-            }
-          }
-        } else {
-          __nv_bfloat16* dk_dst = reinterpret_cast<__nv_bfloat16*>(p.out0) + g_off;
-          __nv_bfloat16* dv_dst = reinterpret_cast<__nv_bfloat16*>(p.out1) + g_off;
-#pragma unroll
-          for (int c = 0; c < OC / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld16(t_row + C_DK + qtr * OC + c * 16, o);
-            tmem_wait_ld();
-            if (key_ok) store_row_bf16(dk_dst + c * 16, o, 1.0f);
-            tmem_ld16(t_row + C_DV + qtr * OC + c * 16, o);
-            tmem_wait_ld();
-            if (key_ok) store_row_bf16(dv_dst + c * 16, o, 1.0f);
-          }
-        }
-      }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(KV_ACC_DONE), (uint32_t)((n - 1) & 1), p.status, 232, n));
+    constexpr int ESZ = SPLIT ? 4 : 2, PR = HD * ESZ / 16;
+    uint8_t* tile_k = smem_gen + PL::OFF_RES0;         // the K and V tiles: every product has finished with them
+    uint8_t* tile_v = smem_gen + PL::OFF_RES1;
+    const bool fin = ok && n > 0;
+    if (fin) {
+      tc_fence_after();
+      const float mul_k = SPLIT ? p.scale * DS_UNSHIFT * __ldg(p.fac + split::FAC_INV_DYVQ) : 1.0f;
+      const float mul_v = SPLIT ? PT_UNSHIFT * __ldg(p.fac + split::FAC_INV_DY) : 1.0f;
+      stage_columns<PR, OC, SPLIT>(tile_k, row, qtr, t_row + C_DK + qtr * OC, mul_k);
+      stage_columns<PR, OC, SPLIT>(tile_v, row, qtr, t_row + C_DV + qtr * OC, mul_v);
+    }
+    ew_bar_sync();
+    if (fin) {
+      const int64_t off0 = (int64_t)bi * p.os.b + (int64_t)hi * p.os.h + (int64_t)k0 * p.os.t;
+      store_staged_rows<PR, ESZ>(tile_k, warp, lane, p.out0, off0, p.os.t, min(BLK, T - k0));
+      store_staged_rows<PR, ESZ>(tile_v, warp, lane, p.out1, off0, p.os.t, min(BLK, T - k0));
     }
   }
   tc_fence_before();
