@@ -860,27 +860,6 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dy, cons
   return launch_bwd_pair<HD, false, false>(mq, mk, mv, mdo, p, dq, dk, dv, B, H, T, st);
 }
 
-// delta[row] = sum_c dY[row][c] * Y[row][c] in fp32: dY in the output layout, Y the handle's contiguous copy.
-// D / 4 lanes share a row (16-byte loads), so a warp covers 128 / D rows.
-__global__ void bwd_delta_f32_kernel(const float* __restrict__ dy, const float* __restrict__ y, int64_t rows, int H, int T, int D,
-                                     const McaStrides ys, float* __restrict__ delta) {
-  mca_pdl_launch_dependents();
-  mca_pdl_wait();   // dy and y are earlier kernels' output
-  const int lane = threadIdx.x & 31, g = D / 4, rpw = 32 / g;        // g in {4, 8, 16}
-  const int64_t row = ((int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5)) * rpw + lane / g;
-  const int c = (lane % g) * 4;
-  float acc = 0.f;
-  if (row < rows) {
-    const unsigned bh = (unsigned)(row / T), bi = bh / (unsigned)H;
-    const int64_t off = (int64_t)bi * ys.b + (int64_t)(bh - bi * H) * ys.h + (row - (int64_t)bh * T) * ys.t;
-    const float4 a = *reinterpret_cast<const float4*>(dy + off + c);
-    const float4 b = *reinterpret_cast<const float4*>(y + row * D + c);
-    acc = fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
-  }
-  for (int o = g / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (row < rows && lane % g == 0) delta[row] = acc;
-}
-
 // Split-operand backward for fp32 callers.  The workspace still holds the fp16 halves of q, k, v the forward's pre-pass
 // wrote; dY is split here.
 template <int HD>
@@ -894,13 +873,8 @@ int launch_bwd_split(const float* dy, const float* y_copy, const float* lse, flo
   split::Job job;
   job.src[0] = dy; job.dst[0] = w.tensor[split::TENSOR_DY]; job.slot[0] = split::TENSOR_DY;
   job.src[1] = job.src[2] = nullptr; job.dst[1] = job.dst[2] = nullptr; job.slot[1] = job.slot[2] = 0;
-  int e = split::run<HD>(job, 1, sout, H, T, rows, w, true, st);
-  if (e) return e;
-  {
-    const int64_t rows_per_block = 8 * (128 / HD);   // eight warps, 128 / HD rows each
-    e = mca_launch_pdl(bwd_delta_f32_kernel, dim3((unsigned)((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st, dy,
-                       y_copy, rows, H, T, HD, sout, delta);
-  }
+  // the kernel that splits dY also forms delta = rowsum(dY o Y) from the elements it holds
+  int e = split::run<HD>(job, 1, sout, H, T, rows, w, true, st, y_copy, delta);
   if (e) return e;
   CUtensorMap mq, mk, mv, mdo;
   const McaStrides sp{(int64_t)H * T * 128, (int64_t)T * 128, 128};

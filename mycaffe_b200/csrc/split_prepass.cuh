@@ -120,10 +120,12 @@ __device__ __forceinline__ float pow2_scale(unsigned int amax_bits) {
   return ldexpf(1.0f, 13 - e);
 }
 
+// backward with ydot / delta given: also delta[row] = sum_c x[row][c] * ydot[row][c] (ydot contiguous rows), the
+// softmax backward's row term, from the elements this kernel holds anyway.
 template <int HD>
 __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
                                                    const unsigned int* __restrict__ amax, float* __restrict__ fac,
-                                                   int backward) {
+                                                   int backward, const float* __restrict__ ydot, float* __restrict__ delta) {
   mca_pdl_launch_dependents();
   mca_pdl_wait();   // the magnitudes are the reduction's output
   const int which = blockIdx.y;
@@ -151,6 +153,15 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
     const int c = (int)(i - row * V8);
     const float* src = piece_ptr<HD>(x, st, contiguous, H, T, 2 * i);
     const float4 v0 = *reinterpret_cast<const float4*>(src), v1 = *reinterpret_cast<const float4*>(src + 4);
+    if (delta != nullptr) {   // uniform: the HD / 8 consecutive lanes of a row are all in this iteration
+      const float4 y0 = *reinterpret_cast<const float4*>(ydot + i * 8), y1 = *reinterpret_cast<const float4*>(ydot + i * 8 + 4);
+      float acc = fmaf(v0.x, y0.x, fmaf(v0.y, y0.y, fmaf(v0.z, y0.z, v0.w * y0.w)));
+      acc += fmaf(v1.x, y1.x, fmaf(v1.y, y1.y, fmaf(v1.z, y1.z, v1.w * y1.w)));
+      const unsigned active = __activemask();
+#pragma unroll
+      for (int o = V8 / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(active, acc, o);
+      if (c == 0) delta[row] = acc;
+    }
     const float e[8] = {v0.x * sc, v0.y * sc, v0.z * sc, v0.w * sc, v1.x * sc, v1.y * sc, v1.z * sc, v1.w * sc};
     __align__(16) __half hi[8];
     __align__(16) __half lo[8];
@@ -169,7 +180,7 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
 // Split `count` tensors (q, k, v for the forward; dY for the backward) into the workspace.
 template <int HD>
 inline int run(const Job& job, int count, const McaStrides& st, int H, int T, int64_t rows, const Workspace& w, bool backward,
-               cudaStream_t stream) {
+               cudaStream_t stream, const float* ydot = nullptr, float* delta = nullptr) {
   // the slots of this call's tensors are consecutive (q, k, v or dY alone): one clear
   int lo = job.slot[0], hi = job.slot[0];
   for (int i = 1; i < count; ++i) { lo = std::min(lo, job.slot[i]); hi = std::max(hi, job.slot[i]); }
@@ -180,7 +191,7 @@ inline int run(const Job& job, int count, const McaStrides& st, int H, int T, in
   if (e) return e;
   const int blocks_rows = (int)std::min<int64_t>(148 * 8, (rows * (HD / 8) + 255) / 256);
   return mca_launch_pdl(rows_kernel<HD>, dim3(blocks_rows, count), dim3(256), 0, stream, job, st, H, T, rows, w.amax, w.fac,
-                        backward ? 1 : 0);
+                        backward ? 1 : 0, ydot, delta);
 }
 
 }  // namespace split
