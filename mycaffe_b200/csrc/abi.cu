@@ -609,6 +609,11 @@ long attn_bwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   // The reference's Backward always works at the configured block size on the tensors its
   // Forward left in the handle (attn.cu:622-634); it reads neither hMask nor the data of hY.
   if (!a.have_fwd || a.fwd_T != a.block || a.fwd_layout != layout) return ERROR_ATTN_BACKWARD_WITHOUT_FORWARD;
+  // The kernels that write dQ and those that write dK, dV run side by side, each reading q, k, v and dY: a gradient
+  // handle that names an input's memory (a blob's diff and data never do) is refused instead of corrupting them.
+  for (int g : {3, 5, 7})
+    for (int i : {2, 4, 6, 10})
+      if (pl[g] != 0 && pl[g] == pl[i]) return ERROR_PARAM_OUT_OF_RANGE;
   const int T = a.block;
   const int64_t n = (int64_t)a.B * a.H * T * a.D;
   const bool packed = layout == MCA_LAYOUT_PACKED;

@@ -572,3 +572,21 @@ def test_one_tile_and_two_tile_ctas_agree(cuda, dtype_name, D, T):
     finally:
         lib.mca_tc_narrow_len(before)
     assert lib.mca_tc_narrow_len(-1) == before
+
+
+def test_backward_refuses_gradients_that_alias_inputs(cuda):
+    """The dQ kernel and the dK/dV kernel run side by side, both reading q, k, v and dY: a gradient handle naming an
+    input's memory is refused (a blob's diff and data never share memory)."""
+    from mycaffe_b200 import CudaDnnError, function_ids as ids
+    rng = np.random.default_rng(4)
+    q, k, v = rand_qkv(rng, 1, 2, 64, 32)
+    a = Sdpa(cuda, 1, 64, 2, 32, training=True)
+    a.forward(q, k, v, oracle.causal_mask(64))
+    hdY, hd = a._alloc(q), a._alloc(q.size)
+    for args in ((a.hQ, a.hQ, a.hK, hd, a.hV, hd), (a.hQ, hd, a.hK, hdY, a.hV, hd), (a.hQ, hd, a.hK, hd, a.hV, a.hK)):
+        with pytest.raises(CudaDnnError) as e:
+            cuda.AttnScaledDotProductBackward(a.hCudnn, a.hAttn, *args, 0, a.hY, hdY)
+        assert e.value.code == ids.ERROR_PARAM_OUT_OF_RANGE
+    g = a.backward(q)          # distinct handles: fine
+    assert all(np.isfinite(x).all() for x in g)
+    a.close()
