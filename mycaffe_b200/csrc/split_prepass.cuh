@@ -70,6 +70,26 @@ __host__ __device__ inline bool is_contiguous(const McaStrides& st, int H, int T
   return st.t == HD && st.h == (int64_t)T * HD && st.b == (int64_t)H * T * HD;
 }
 
+// 16-byte load that asks L2 to keep (or to give up first) the line: the reduction reads each tensor once and the row
+// kernel reads it again right behind it; three tensors of a layer fit in L2, so the second pass need not go to HBM.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t pol;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_drop() {
+  uint64_t pol;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ float4 ld_f4_hint(const float* ptr, uint64_t pol) {
+  float4 v;
+  asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(ptr), "l"(pol));
+  return v;
+}
+
 // amax[slot] = max |x| of each tensor
 template <int HD>
 __global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st, int H, int T, int64_t rows,
@@ -81,19 +101,20 @@ __global__ void __launch_bounds__(256) amax_kernel(const Job job, McaStrides st,
   const bool contiguous = is_contiguous(st, H, T, HD);
   const int64_t n = rows * V4, stride = (int64_t)gridDim.x * blockDim.x;
   float m = 0.f;
+  const uint64_t keep = l2_policy_keep();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < n; i += 4 * stride) {   // four independent loads in flight
-    const float4 v0 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
-    const float4 v1 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + stride));
-    const float4 v2 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + 2 * stride));
-    const float4 v3 = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i + 3 * stride));
+    const float4 v0 = ld_f4_hint(piece_ptr<HD>(x, st, contiguous, H, T, i), keep);
+    const float4 v1 = ld_f4_hint(piece_ptr<HD>(x, st, contiguous, H, T, i + stride), keep);
+    const float4 v2 = ld_f4_hint(piece_ptr<HD>(x, st, contiguous, H, T, i + 2 * stride), keep);
+    const float4 v3 = ld_f4_hint(piece_ptr<HD>(x, st, contiguous, H, T, i + 3 * stride), keep);
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))));
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v2.x), fabsf(v2.y)), fmaxf(fabsf(v2.z), fabsf(v2.w))));
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v3.x), fabsf(v3.y)), fmaxf(fabsf(v3.z), fabsf(v3.w))));
   }
   for (; i < n; i += stride) {
-    const float4 v = *reinterpret_cast<const float4*>(piece_ptr<HD>(x, st, contiguous, H, T, i));
+    const float4 v = ld_f4_hint(piece_ptr<HD>(x, st, contiguous, H, T, i), keep);
     m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
   }
   // one atomic per block: thousands of warps updating the same three words serialise in L2
@@ -148,11 +169,12 @@ __global__ void __launch_bounds__(256) rows_kernel(const Job job, McaStrides st,
   // eight elements per thread and step: two 16-byte loads (adjacent pieces of one row), one 16-byte store per half
   constexpr int V8 = HD / 8;
   const bool contiguous = is_contiguous(st, H, T, HD);
+  const uint64_t drop = l2_policy_drop();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * V8; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / V8;          // V8 is a power of two
     const int c = (int)(i - row * V8);
     const float* src = piece_ptr<HD>(x, st, contiguous, H, T, 2 * i);
-    const float4 v0 = *reinterpret_cast<const float4*>(src), v1 = *reinterpret_cast<const float4*>(src + 4);
+    const float4 v0 = ld_f4_hint(src, drop), v1 = ld_f4_hint(src + 4, drop);
     if (delta != nullptr) {   // uniform: the HD / 8 consecutive lanes of a row are all in this iteration
       const float4 y0 = *reinterpret_cast<const float4*>(ydot + i * 8), y1 = *reinterpret_cast<const float4*>(ydot + i * 8 + 4);
       float acc = fmaf(v0.x, y0.x, fmaf(v0.y, y0.y, fmaf(v0.z, y0.z, v0.w * y0.w)));
