@@ -262,10 +262,10 @@ MCA_API int mca_mask_pack(const float* mask, int mask_mode, int B, int T, uint32
  * status: device int[4] the kernel writes when a bounded wait gives up (0 = ok). */
 MCA_API int mca_sdpa_forward_tc(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                 int T, int D, void* y, float* lse, int* status, void* stream);
-/* Sequences of up to this many keys run the forward (bf16 at head size 128, split fp32) as CTAs of one 128-row query
- * tile, two to an SM, instead of one CTA of two tiles: the fixed part of a CTA's life then overlaps its neighbour's key
- * loop.  64-wide bf16 heads take that shape at every length unless the value is 0.  len < 0
- * only reads; returns the value before the call (default 4096, or MCA_TC_NARROW_LEN from the environment; 0 = never).
+/* Sequences of up to this many keys (half as many with split fp32 operands) run the forward as CTAs of one 128-row
+ * query tile, two to an SM, instead of one CTA of two tiles: the fixed part of a CTA's life then overlaps its neighbour's
+ * key loop.  64-wide bf16 heads take that shape at every length unless the value is 0.  len < 0
+ * only reads; returns the value before the call (default 8192, or MCA_TC_NARROW_LEN from the environment; 0 = never).
  * A tuning knob of this library with no counterpart in the reference; set it before the first call from other threads. */
 MCA_API int mca_tc_narrow_len(int len);
 

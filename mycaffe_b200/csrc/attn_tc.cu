@@ -756,19 +756,21 @@ struct SplitExtras {
 // Which sequences run as NARROW CTAs (one query tile each, two CTAs per SM).  Rows of 128 bytes (64-wide bf16 heads):
 // all of them -- a key tile costs the softmax as much as at 128 and the tensor pipe half, and two independent CTAs per
 // SM keep both busier than one CTA's two tiles in anti-phase (T = 8192: 585 -> 711 TFLOP/s, T = 32768: 653 -> 780).
-// Rows of 256 bytes: sequences up to a threshold, 4096 keys unless MCA_TC_NARROW_LEN in the environment or
-// mca_tc_narrow_len() says otherwise (0: never, for either row size); beyond it the two shapes run alike and the
-// two-tile one reads K and V from L2 once per pair of tiles.
+// Rows of 256 bytes: sequences up to a threshold, 8192 keys for 128-wide bf16 heads (+ 5 % at T = 8192, B = 1) and
+// half of it for split fp32 operands (single-stage K and V; alike beyond), unless MCA_TC_NARROW_LEN in the environment
+// or mca_tc_narrow_len() says otherwise (0: never, for either row size); beyond it the two shapes run alike (the
+// headline shape within 1 %, the one-tile shape at lower clocks under the power cap) and the two-tile one reads K and V
+// from L2 once per pair of tiles.
 int& narrow_limit() {
   static int limit = [] {
     const char* e = getenv("MCA_TC_NARROW_LEN");
-    return e != nullptr ? atoi(e) : 4096;
+    return e != nullptr ? atoi(e) : 8192;
   }();
   return limit;
 }
-inline bool narrow_ctas(int T, int row_bytes) {
+inline bool narrow_ctas(int T, int row_bytes, bool split_operands) {
   const int limit = narrow_limit();
-  return limit > 0 && (row_bytes <= 128 || T <= limit);
+  return limit > 0 && (row_bytes <= 128 || T <= (split_operands ? limit / 2 : limit));
 }
 
 template <int HD, int MODE, bool NARROW>
@@ -834,7 +836,7 @@ int launch_tc(const void* q, const void* k, const void* v, int causal, int B, in
   p.mask_batch_stride = mask ? mask->batch_stride : 0;
   p.mask_row_stride = mask ? mask->row_stride : 0;
   if constexpr (!Shape<HD, MODE, false>::WIDE && MODE != MODE_TF32) {
-    if (narrow_ctas(T, Shape<HD, MODE, false>::ROW_BYTES)) return launch_shape<HD, MODE, true>(mq, mk, mv, p, B, H, T, mask != nullptr, st);
+    if (narrow_ctas(T, Shape<HD, MODE, false>::ROW_BYTES, MODE == MODE_SPLIT)) return launch_shape<HD, MODE, true>(mq, mk, mv, p, B, H, T, mask != nullptr, st);
   }
   return launch_shape<HD, MODE, false>(mq, mk, mv, p, B, H, T, mask != nullptr, st);
 }
