@@ -708,9 +708,25 @@ def run_sweep(cx):
                         "roofline": tensor_roofline(cx, tf, "sdpa_fwd_tc_kernel<128>", ms),
                         "l2": "L2 flushed before every timed launch" if small else "inputs exceed L2"})
             del q, k, v, y
+    # 64-wide heads (config 2's head size) at longer sequences: every length runs as CTAs of one query tile, two per SM
+    out64 = []
+    for B, H64, T in ((8, 12, 2048), (2, 12, 8192), (1, 12, 32768)):
+        q, k, v = (torch.randn(B, H64, T, 64, device=dev).div_(8.0).bfloat16() for _ in range(3))
+        y = torch.empty_like(q)
+        fn = lambda: lib.mca_sdpa_forward_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), ids.MCA_DTYPE_BF16, 1, B, H64, T, 64,
+                                             y.data_ptr(), None, st.data_ptr(), sp)
+        ms = cx.time_kernel(fn, 10, warm=3, flush=True)
+        tf = causal_flops(B, H64, T, 64) / (ms * 1e-3) / 1e12
+        out64.append({"B": B, "H": H64, "T": T, "ms": round(ms, 4), "tflops": round(tf, 1),
+                      "roofline": tensor_roofline(cx, tf, "sdpa_fwd_tc_kernel<64, one-tile shape>", ms,
+                                                  "at this head size a key tile costs the softmax as much as at 128 and the tensor "
+                                                  "pipe half: the exponential unit, not the tensor pipe, is the busiest resource"),
+                      "l2": "L2 flushed before every timed launch"})
+        del q, k, v, y
     if int(st[0].item()):
         raise RuntimeError(f"sweep: kernel status {st[:4].tolist()}")
-    return {"workload": f"config5 causal prefill forward, H={H} D={D} bf16", "cases": out}
+    return {"workload": f"config5 causal prefill forward, H={H} D={D} bf16", "cases": out,
+            "head_size_64": {"workload": "causal forward, 12 heads x 64, bf16", "cases": out64}}
 
 
 def run_fp32_prefill(cx, B=1, T=PF_T):
