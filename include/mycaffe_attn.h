@@ -342,6 +342,12 @@ MCA_API int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void*
 MCA_API int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H,
                                        int T, int D, void* y, float* lse, int* status, int layout,
                                        const uint32_t* mask_bits, int mask_mode, void* stream);
+/* As mca_sdpa_forward_tc_masked, and a second copy of the output, same layout, to y_keep (null: none): what a training
+ * handle keeps for its Backward (the reference keeps the probabilities, attn.cu:436-452), written by the kernel's own
+ * epilogue instead of a device-to-device copy afterwards.  bf16 only. */
+MCA_API int mca_sdpa_forward_tc_keep(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T,
+                                     int D, void* y, void* y_keep, float* lse, int* status, int layout,
+                                     const uint32_t* mask_bits, int mask_mode, void* stream);
 MCA_API int mca_sdpa_backward_tc_layout(const void* q, const void* k, const void* v, const void* y, const void* dy,
                                         const float* lse, float* delta_scratch, int dtype, int causal, int B, int H,
                                         int T, int D, void* dq, void* dk, void* dv, int* status, int layout,

@@ -63,6 +63,7 @@ SIGNATURES = {
     "mca_sdpa_forward_tc_masked": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "mca_mask_bits_row_words": (_i, [_i]),
     "mca_tc_narrow_len": (_i, [_i]),
+    "mca_sdpa_forward_tc_keep": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "mca_sdpa_forward_f32_tc_workspace_bytes_d": (_i64, [_i, _i, _i, _i]),
     "mca_sdpa_backward_f32_tc_supported": (_i, [_i]),
     "mca_mask_pack": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),

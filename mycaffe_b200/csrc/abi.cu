@@ -558,14 +558,11 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   if (bf16 && (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH) && !(a.flags & MCA_FLAG_EXACT_FP32)) {
     // a general or batch mask: packed into keep-bits, applied by the same tensor-core kernel
     if ((e = pack_mask_bits(a, mask, mode, T))) return e;
-    e = mca_sdpa_forward_tc_masked(q, kk, v, MCA_DTYPE_BF16, 0, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1, layout, a.mask_bits,
-                                   mode, 0);
+    const bool keep = a.training && T == a.block;   // Backward needs O: the kernel writes the handle's copy itself
+    e = mca_sdpa_forward_tc_keep(q, kk, v, MCA_DTYPE_BF16, 0, a.B, a.H, T, a.D, y, keep ? a.y_copy : nullptr, a.lse,
+                                 a.causal_flag + 1, layout, a.mask_bits, mode, 0);
     if (e) return e;
-    if (a.training && T == a.block) {
-      cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
-      if (ce != cudaSuccess) return ce;
-      remember_forward(a, T, mode, layout, 0, false);
-    }
+    if (keep) remember_forward(a, T, mode, layout, 0, false);
     return tc_status(k, a);
   }
   if (bf16 && (mode == MCA_MASK_TT || mode == MCA_MASK_BATCH)) {
@@ -586,16 +583,13 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     if (save) remember_forward(a, T, mode, layout, (long)pl[6], batch_mask);
     return 0;
   }
-  e = mca_sdpa_forward_tc_layout(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, a.lse, a.causal_flag + 1,
-                                 layout, 0);
+  // Backward needs O and the log-sum-exp of this Forward; it cannot trust the data of hY.  The handle's copy keeps the
+  // layout y was written in and is one more destination of the kernel's epilogue.
+  const bool keep = a.training && T == a.block && bf16;
+  e = mca_sdpa_forward_tc_keep(q, kk, v, a.dtype, mode == MCA_MASK_CAUSAL, a.B, a.H, T, a.D, y, keep ? a.y_copy : nullptr, a.lse,
+                               a.causal_flag + 1, layout, nullptr, MCA_MASK_NONE, 0);
   if (e) return e;
-  if (a.training && T == a.block && bf16) {
-    // Backward needs O and the log-sum-exp of this Forward; it cannot trust the data of hY.  The copy keeps
-    // the layout y was written in.
-    cudaError_t ce = cudaMemcpyAsync(a.y_copy, y, (size_t)n * 2, cudaMemcpyDeviceToDevice, 0);
-    if (ce != cudaSuccess) return ce;
-    remember_forward(a, T, mode, layout, 0, false);
-  }
+  if (keep) remember_forward(a, T, mode, layout, 0, false);
   return tc_status(k, a);
 }
 

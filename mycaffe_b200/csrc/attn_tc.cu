@@ -906,6 +906,12 @@ int mca_sdpa_forward_tc_layout(const void* q, const void* k, const void* v, int 
 int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
                                void* y, float* lse, int* status, int layout, const uint32_t* mask_bits, int mask_mode,
                                void* stream) {
+  return mca_sdpa_forward_tc_keep(q, k, v, dtype, causal, B, H, T, D, y, nullptr, lse, status, layout, mask_bits, mask_mode, stream);
+}
+
+int mca_sdpa_forward_tc_keep(const void* q, const void* k, const void* v, int dtype, int causal, int B, int H, int T, int D,
+                             void* y, void* y_keep, float* lse, int* status, int layout, const uint32_t* mask_bits,
+                             int mask_mode, void* stream) {
   McaMaskBits mb;
   const McaMaskBits* mask = nullptr;
   int me = mca_mask_bits_view(mask_bits, nullptr, mask_mode, T, false, &mb, &mask);
@@ -922,11 +928,17 @@ int mca_sdpa_forward_tc_masked(const void* q, const void* k, const void* v, int 
   if (dtype == MCA_DTYPE_TF32) {
     // fp32 rows are twice as wide: only the 64-wide head fits the shared-memory plan (two query tiles,
     // two K/V stages); wider heads use the exact fp32 kernel
+    if (y_keep != nullptr) return ERROR_ATTN_UNSUPPORTED_SHAPE;
     if (D == 64) return launch_tc<64, MODE_TF32>(q, k, v, causal, B, H, T, y, lse, status, layout, st);
     return ERROR_ATTN_UNSUPPORTED_SHAPE;
   }
-  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
-  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, nullptr, 0, nullptr, nullptr, mask);
+  // a second copy of the output in the same layout (what a training handle keeps for its backward) is one more
+  // destination of the epilogue's stores
+  if (y_keep != nullptr && (reinterpret_cast<uintptr_t>(y_keep) & 15)) return ERROR_PARAM_OUT_OF_RANGE;
+  void* const more[1] = {y_keep};
+  const int n_more = y_keep != nullptr ? 1 : 0;
+  if (D == 128) return launch_tc<128, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, more, n_more, nullptr, nullptr, mask);
+  if (D == 64) return launch_tc<64, MODE_BF16>(q, k, v, causal, B, H, T, y, lse, status, layout, st, more, n_more, nullptr, nullptr, mask);
   return ERROR_ATTN_UNSUPPORTED_SHAPE;
 }
 
