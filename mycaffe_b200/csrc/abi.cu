@@ -119,6 +119,7 @@ struct Kernel {
   std::string last_detail;
   float* stage = nullptr;  // grow-only fp32 staging buffer for float <-> bf16 transfers
   size_t stage_count = 0;
+  int* h_answer = nullptr; // one pinned word for small device answers the host has to wait for (a mask's class)
 
   float* staging(size_t count) {
     if (count > stage_count) {
@@ -405,10 +406,17 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   *mode = MCA_MASK_TT;
   if ((e = mca_classify_causal_mask(m, T, a.causal_flag, 0))) return e;
   if (need_host_answer) {
-    int v = 0;
-    cudaError_t ce = cudaMemcpy(&v, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost);
+    // into pinned memory on the stream, then one stream synchronisation: a third of the latency of a blocking copy
+    // into pageable memory
+    if (k->h_answer == nullptr && cudaMallocHost((void**)&k->h_answer, sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      k->h_answer = nullptr;
+      return ERROR_MEMORY_OUT;
+    }
+    cudaError_t ce = cudaMemcpyAsync(k->h_answer, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost, 0);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
     if (ce != cudaSuccess) return ce;
-    if (v == 1) *mode = MCA_MASK_CAUSAL;
+    if (*k->h_answer == 1) *mode = MCA_MASK_CAUSAL;
   }
   return 0;
 }
@@ -1139,6 +1147,7 @@ void kernel_cleanup(long idx) {
   cudaFree(k->norm_scratch);
   for (auto& kv : k->decode) { cudaFree(kv.second.fr); cudaFree(kv.second.fi); cudaFree(kv.second.scratch); }
   for (void* p : k->host_bufs) cudaFreeHost(p);
+  if (k->h_answer) cudaFreeHost(k->h_answer);
   for (auto& kv : k->extensions) if (kv.second.lib) dlclose(kv.second.lib);
   if (k->ev0) cudaEventDestroy(k->ev0);
   if (k->ev1) cudaEventDestroy(k->ev1);
