@@ -42,7 +42,7 @@ struct AttnHandle {
   size_t mask_ws_floats = 0;
   uint32_t *mask_bits = nullptr, *mask_bits_t = nullptr;   // keep-bits of a (T,T) or batch mask for the tensor-core kernels
   size_t mask_bits_words = 0;
-  int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words
+  int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words, [6..7] the classification's scratch
   // state of the last forward, consumed by backward
   bool have_fwd = false;
   int fwd_T = 0, fwd_mask_mode = 0, fwd_layout = 0;
@@ -404,7 +404,7 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   *mask = m;
   if (batch_mask) { *mode = MCA_MASK_BATCH; return 0; }
   *mode = MCA_MASK_TT;
-  if ((e = mca_classify_causal_mask(m, T, a.causal_flag, 0))) return e;
+  if ((e = mca_classify_causal_mask_ws(m, T, a.causal_flag, a.causal_flag + 6, 0))) return e;
   if (need_host_answer) {
     // into pinned memory on the stream, then one stream synchronisation: a third of the latency of a blocking copy
     // into pageable memory

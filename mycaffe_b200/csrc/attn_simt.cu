@@ -11,6 +11,8 @@
 // 64x64 score tile, so a row's softmax statistics live in one half-warp (shuffle reductions).
 // Shared tiles are row-major with a stride of DP+4 floats, which keeps every 128-bit shared
 // load of the inner products conflict-free.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -420,6 +422,36 @@ __global__ void classify_causal_kernel(const float* __restrict__ mask, int T, in
 }
 __global__ void set_int_kernel(int* p, int v) { *p = v; }
 
+// The same answer from one launch: a warp per row (16-byte loads when T allows), the blocks' mismatch counts and a
+// ticket in two scratch words that are zero before and after; the last block to finish writes the flag.
+__global__ void __launch_bounds__(256) classify_causal_rows_kernel(const float* __restrict__ mask, int T, int* __restrict__ flag,
+                                                                   int* __restrict__ scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  bool bad = false;
+  for (int i = blockIdx.x * 8 + warp; i < T; i += gridDim.x * 8) {
+    const float* row = mask + (int64_t)i * T;
+    if ((T & 3) == 0) {
+      for (int j = lane * 4; j < T; j += 128) {
+        const float4 m = *reinterpret_cast<const float4*>(row + j);
+        bad |= m.x != (j <= i ? 1.f : 0.f) || m.y != (j + 1 <= i ? 1.f : 0.f) || m.z != (j + 2 <= i ? 1.f : 0.f) ||
+               m.w != (j + 3 <= i ? 1.f : 0.f);
+      }
+    } else {
+      for (int j = lane; j < T; j += 32) bad |= row[j] != (j <= i ? 1.f : 0.f);
+    }
+  }
+  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  if (threadIdx.x == 0) {
+    if (any_bad) atomicAdd(scratch, 1);
+    __threadfence();
+    if (atomicAdd(scratch + 1, 1) == (int)gridDim.x - 1) {
+      __threadfence();
+      *flag = atomicExch(scratch, 0) == 0 ? 1 : 0;
+      scratch[1] = 0;
+    }
+  }
+}
+
 int pick_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : D <= 128 ? 128 : 0; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -430,6 +462,14 @@ template <typename F> int set_smem(F kernel, size_t bytes) {
 }
 
 }  // namespace
+
+int mca_classify_causal_mask_ws(const float* mask, int T, int* flag, int* scratch, void* stream) {
+  if (!mask || !flag || !scratch) return ERROR_PARAM_NULL;
+  if (T <= 0) return ERROR_PARAM_OUT_OF_RANGE;
+  const int blocks = std::min(1184, (T + 7) / 8);
+  classify_causal_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(mask, T, flag, scratch);
+  return mca_launch_status();
+}
 
 int mca_classify_causal_mask(const float* mask, int T, int* flag, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
