@@ -43,6 +43,15 @@ struct AttnHandle {
   uint32_t *mask_bits = nullptr, *mask_bits_t = nullptr;   // keep-bits of a (T,T) or batch mask for the tensor-core kernels
   size_t mask_bits_words = 0;
   int* causal_flag = nullptr;  // [0] mask classification, [1..4] kernel status words, [6..7] the classification's scratch
+  // A (T,T) mask is classified on every Forward, and the host has to know the class to choose the kernel.  In
+  // synchronous mode the call ends with a blocking read of the status words anyway: the class is read with them, and
+  // the kernels are chosen beforehand on the class the last verified call found.  A wrong guess that matters (taken
+  // for the lower triangle, is not) is found by that read and the Forward runs again with the class known; nothing
+  // unverified is ever returned.
+  int spec_class = -1;         // what the last verified classification found (1 lower triangle, 0 other), -1 none yet
+  int spec_assumed = 0;
+  bool spec_pending = false;   // this call's kernels were chosen on spec_class; the read at its end checks it
+  bool spec_allowed = true;
   // state of the last forward, consumed by backward
   bool have_fwd = false;
   int fwd_T = 0, fwd_mask_mode = 0, fwd_layout = 0;
@@ -393,8 +402,10 @@ long attn_set(Kernel* k, long lInput, float* pf, long llInput, MCA_LONGLONG* pl)
 // Decide how the mask of this call is applied.  A (T,T) mask is classified on every call (one pass over
 // T*T floats, small next to the attention itself): the caller may have rewritten the handle with SETMEM, or
 // freed it and been given the same address again, so nothing about it is remembered between calls.
+constexpr long kMaskClassMiss = -7001;   // internal: the class assumed for this call's kernels was wrong
+
 long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, const float** mask, int* mode,
-                  bool need_host_answer) {
+                  bool need_host_answer, bool may_speculate = false) {
   *mask = nullptr;
   if (a.flags & MCA_FLAG_CAUSAL_IMPLICIT) { *mode = MCA_MASK_CAUSAL; return 0; }
   if (hMask == 0) { *mode = MCA_MASK_NONE; return 0; }
@@ -405,6 +416,12 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   if (batch_mask) { *mode = MCA_MASK_BATCH; return 0; }
   *mode = MCA_MASK_TT;
   if ((e = mca_classify_causal_mask_ws(m, T, a.causal_flag, a.causal_flag + 6, 0))) return e;
+  if (need_host_answer && may_speculate && !k->async && a.spec_allowed && a.spec_class >= 0) {
+    a.spec_pending = true;
+    a.spec_assumed = a.spec_class;
+    if (a.spec_class == 1) *mode = MCA_MASK_CAUSAL;
+    return 0;
+  }
   if (need_host_answer) {
     // into pinned memory on the stream, then one stream synchronisation: a third of the latency of a blocking copy
     // into pageable memory
@@ -417,6 +434,7 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
     if (ce != cudaSuccess) return ce;
     if (*k->h_answer == 1) *mode = MCA_MASK_CAUSAL;
+    a.spec_class = *k->h_answer == 1 ? 1 : 0;
   }
   return 0;
 }
@@ -456,9 +474,17 @@ long ensure_mask_ws(AttnHandle& a) {
 // attention handle at the next call that synchronises (CUDA_FN_SYNCHRONIZEDEVICE).
 long read_status(Kernel* k, AttnHandle& a) {
   if (!a.causal_flag) return 0;
-  int st[4] = {0, 0, 0, 0};
-  cudaError_t ce = cudaMemcpy(st, a.causal_flag + 1, sizeof(st), cudaMemcpyDeviceToHost);
+  int w[5] = {0, 0, 0, 0, 0};
+  cudaError_t ce = cudaMemcpy(w, a.causal_flag, sizeof(w), cudaMemcpyDeviceToHost);
   if (ce != cudaSuccess) return ce;
+  const int* st = w + 1;
+  if (a.spec_pending) {   // the class this call's kernels were chosen on, against what its classification found
+    a.spec_pending = false;
+    const int actual = w[0] == 1 ? 1 : 0;
+    const bool matters = a.spec_assumed == 1 && actual == 0;   // the other way round the result is right, only slower
+    a.spec_class = actual;
+    if (matters && st[0] == 0) return kMaskClassMiss;
+  }
   if (st[0] != 0) {
     char buf[96];
     snprintf(buf, sizeof(buf), "status %d at stage %d block %d iter %d", st[0], st[1], st[2], st[3]);
@@ -495,12 +521,25 @@ void remember_forward(AttnHandle& a, int T, int mode, int layout, long hMask, bo
 }
 
 // layout MCA_LAYOUT_PACKED: pl[3..5] all name the (B,T,3C) projection output and pl[7] a (B,T,C) tensor
+long attn_fwd_once(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout);
+
 long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
+  long e = attn_fwd_once(k, llInput, pl, layout);
+  if (e != kMaskClassMiss) return e;
+  AttnHandle& a = k->attn.find((long)pl[1])->second;   // the handle exists: the first pass ran its kernels
+  a.spec_allowed = false;                              // this time the class is read before the kernels are chosen
+  e = attn_fwd_once(k, llInput, pl, layout);
+  a.spec_allowed = true;
+  return e;
+}
+
+long attn_fwd_once(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
   long e;  // Device<T>::AttnForward, device.h:2488-2506; attnHandle<T>::Forward, attn.cu:518-602
   if ((e = verify_in(llInput, pl, 9, 9))) return e;
   auto it = k->attn.find((long)pl[1]);
   if (it == k->attn.end() || !it->second.configured) return ERROR_ATTN_NOT_INITIALIZED;
   AttnHandle& a = it->second;
+  a.spec_pending = false;
   const int T = (int)pl[2];
   if (T > a.block) return ERROR_ATTN_INVALID_BLOCK_SIZE;  // attn.cu:530-531
   if (T <= 0) return ERROR_PARAM_OUT_OF_RANGE;
@@ -528,7 +567,8 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
         (e = check_f32(k, (long)pl[5], n_in, &v)) || (e = check_f32(k, (long)pl[7], n, &y)))
       return e;
     if (packed) { kk += C; v += 2 * C; }
-    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr))) return e;
+    const bool split_path = a.split_ws != nullptr && (mca_sdpa_backward_f32_tc_supported(a.D) != 0 || !a.training);
+    if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, a.split_ws != nullptr, split_path))) return e;
     const bool save = a.training && T == a.block;
     const bool bits = mode == MCA_MASK_TT || mode == MCA_MASK_BATCH;   // packed for the kernel; causal / none need nothing
     // Head sizes with a tensor-core forward but no tensor-core backward (128): the forward leaves the row statistics
@@ -552,8 +592,12 @@ long attn_fwd(Kernel* k, long llInput, MCA_LONGLONG* pl, int layout) {
     return e;
   }
   // bf16, or single-pass tf32 (inference, head size 64, causal mask or none)
-  if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true))) return e;
   const bool bf16 = a.dtype == MCA_DTYPE_BF16;
+  if (a.dtype == MCA_DTYPE_TF32) {
+    // classified above, and the class is known on the host
+  } else if ((e = resolve_mask(k, a, (long)pl[6], batch_mask, T, &mask, &mode, true, bf16 && !(a.flags & MCA_FLAG_EXACT_FP32)))) {
+    return e;
+  }
   void *q, *kk, *v, *y;
   if ((e = check_any(k, (long)pl[3], n_in, bf16, &q)) || (e = check_any(k, (long)pl[4], n_in, bf16, &kk)) ||
       (e = check_any(k, (long)pl[5], n_in, bf16, &v)) || (e = check_any(k, (long)pl[7], n, bf16, &y)))

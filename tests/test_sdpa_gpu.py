@@ -590,3 +590,33 @@ def test_backward_refuses_gradients_that_alias_inputs(cuda):
     g = a.backward(q)          # distinct handles: fine
     assert all(np.isfinite(x).all() for x in g)
     a.close()
+
+
+@pytest.mark.parametrize("dtype_name", ["fp32", "bf16"])
+def test_mask_class_is_verified_on_every_forward(cuda, dtype_name):
+    """A (T,T) mask handle is classified on every Forward; in synchronous mode the kernels are chosen on the class the
+    last verified call found and the class is checked with the status read that ends the call.  Rewriting the mask in
+    place between calls -- lower triangle, then a band, then the lower triangle again -- must give the right result
+    every time (the call whose guess was wrong runs again before it returns)."""
+    from mycaffe_b200 import function_ids as ids
+    rng = np.random.default_rng(9)
+    B, H, T, D = 2, 3, 256, 64
+    bf16 = dtype_name == "bf16"
+    q, k, v = rand_qkv(rng, B, H, T, D)
+    if bf16:
+        q, k, v = (bf16_round(a) for a in (q, k, v))
+    tol = BF16_TOL if bf16 else FP32_TIGHT
+    tril = oracle.causal_mask(T)
+    band = np.triu(tril, -7).astype(np.float32)
+    a = Sdpa(cuda, B, T, H, D, dtype=ids.MCA_DTYPE_BF16 if bf16 else None)
+    alloc = cuda.AllocMemoryBf16 if bf16 else cuda.AllocMemory
+    hq, hk, hv, hy = alloc(q), alloc(k), alloc(v), alloc(q.size)
+    hm = cuda.AllocMemory(tril)
+    for m in (tril, tril, band, band, tril, band, tril):
+        cuda.SetMemory(hm, m)
+        cuda.AttnScaledDotProductForward(a.hCudnn, a.hAttn, T, hq, hk, hv, hm, hy, False)
+        y = cuda.GetMemory(hy, q.size).reshape(q.shape)
+        assert rel_err(y, oracle.sdpa_forward(q, k, v, m, 1, f64=True)) < tol
+    for h in (hq, hk, hv, hy, hm):
+        cuda.FreeMemory(h)
+    a.close()
