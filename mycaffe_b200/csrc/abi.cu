@@ -128,7 +128,15 @@ struct Kernel {
   std::string last_detail;
   float* stage = nullptr;  // grow-only fp32 staging buffer for float <-> bf16 transfers
   size_t stage_count = 0;
-  int* h_answer = nullptr; // one pinned word for small device answers the host has to wait for (a mask's class)
+  int* h_answer = nullptr; // eight pinned words for small device answers the host has to wait for (a mask's class in
+                           // [0], an attention handle's class + status words in [2..6])
+  int* answer_words() {
+    if (h_answer == nullptr && cudaMallocHost((void**)&h_answer, 8 * sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      h_answer = nullptr;
+    }
+    return h_answer;
+  }
 
   float* staging(size_t count) {
     if (count > stage_count) {
@@ -425,11 +433,7 @@ long resolve_mask(Kernel* k, AttnHandle& a, long hMask, bool batch_mask, int T, 
   if (need_host_answer) {
     // into pinned memory on the stream, then one stream synchronisation: a third of the latency of a blocking copy
     // into pageable memory
-    if (k->h_answer == nullptr && cudaMallocHost((void**)&k->h_answer, sizeof(int)) != cudaSuccess) {
-      cudaGetLastError();
-      k->h_answer = nullptr;
-      return ERROR_MEMORY_OUT;
-    }
+    if (k->answer_words() == nullptr) return ERROR_MEMORY_OUT;
     cudaError_t ce = cudaMemcpyAsync(k->h_answer, a.causal_flag, sizeof(int), cudaMemcpyDeviceToHost, 0);
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
     if (ce != cudaSuccess) return ce;
@@ -474,8 +478,12 @@ long ensure_mask_ws(AttnHandle& a) {
 // attention handle at the next call that synchronises (CUDA_FN_SYNCHRONIZEDEVICE).
 long read_status(Kernel* k, AttnHandle& a) {
   if (!a.causal_flag) return 0;
-  int w[5] = {0, 0, 0, 0, 0};
-  cudaError_t ce = cudaMemcpy(w, a.causal_flag, sizeof(w), cudaMemcpyDeviceToHost);
+  // into pinned words on the stream, then one stream synchronisation (a blocking copy into pageable memory takes
+  // several microseconds longer, on every call of the synchronous mode)
+  if (k->answer_words() == nullptr) return ERROR_MEMORY_OUT;
+  int* w = k->h_answer + 2;
+  cudaError_t ce = cudaMemcpyAsync(w, a.causal_flag, 5 * sizeof(int), cudaMemcpyDeviceToHost, 0);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
   if (ce != cudaSuccess) return ce;
   const int* st = w + 1;
   if (a.spec_pending) {   // the class this call's kernels were chosen on, against what its classification found
