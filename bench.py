@@ -408,6 +408,7 @@ def run_ours(args):
         extras["backward"] = run_backward(cx)
         extras["fp32_prefill"] = run_fp32_prefill(cx)
         extras["train"] = run_train(cx)
+        extras["train_function_ids"] = run_train_function_ids(cx)
         for key, (bt, bf) in {"decode_bf16": (DEC_B, True), "decode_b16": (16, False), "decode_b1": (1, False)}.items():
             extras[key], extra_checks[key] = run_decode(cx, bt, bf, multi=False, steps=3)
         extras["tft"] = run_tft(cx)
@@ -964,6 +965,58 @@ def run_projections(cx):
     return res
 
 
+def run_train_function_ids(cx, steps=4):
+    """Config 2's attention core the way the C# layers reach it: ATTN_FWD x 12 then ATTN_BWD x 12 through
+    DLL_InvokeFloatEx2 with memory handles (CudaDnn.cs:5673-5701), host wall clock per step.  `as_the_reference_calls`:
+    a (T,T) lower-triangular mask handle on every Forward and every call synchronised (attn.cu:601);
+    `flag_and_async`: the analytic-mask flag on ATTN_SET and MCA_FN_SET_ASYNC."""
+    import numpy as np
+    from mycaffe_b200 import CudaDnn, function_ids as ids
+    B, T, H, D, L = 8, 1024, 12, 64, 12
+    cuda = CudaDnn(cx.local)
+    rng = np.random.default_rng(0)
+    mask = np.tril(np.ones((T, T), np.float32))
+    out = {"workload": f"config2 attention core through function ids 163/164: {L} layers x (forward + backward), B={B} H={H} D={D} T={T}, "
+                       "host wall clock", "legs": {}}
+    try:
+        for dname, dtype in (("fp32", None), ("bf16", ids.MCA_DTYPE_BF16)):
+            alloc = cuda.AllocMemoryBf16 if dtype else cuda.AllocMemory
+            for leg, flags, use_async in (("as_the_reference_calls", None, False), ("flag_and_async", ids.MCA_FLAG_CAUSAL_IMPLICIT, True)):
+                layers, mem = [], []
+                for _ in range(L):
+                    hC, hA = cuda.CreateCuDNN(), cuda.CreateAttn()
+                    cuda.SetAttn(hC, hA, 0, True, B, T, H, D, 0.0, 0, dtype, flags)
+                    t = [alloc((0.5 * rng.standard_normal((B, H, T, D))).astype(np.float32)) for _ in range(4)]   # q, k, v, dy
+                    o = [alloc(B * H * T * D) for _ in range(4)]                                                # y, dq, dk, dv
+                    layers.append((hC, hA, t, o))
+                    mem += t + o
+                hM = cuda.AllocMemory(mask)
+                cuda.SetAsync(use_async)
+
+                def step():
+                    for hC, hA, t, o in layers:
+                        cuda.AttnScaledDotProductForward(hC, hA, T, t[0], t[1], t[2], hM, o[0], False)
+                    for hC, hA, t, o in reversed(layers):
+                        cuda.AttnScaledDotProductBackward(hC, hA, t[0], o[1], t[1], o[2], t[2], o[3], 0, o[0], t[3])
+                    cuda.SynchronizeDevice()
+                for _ in range(2):
+                    step()
+                t0 = time.perf_counter()
+                for _ in range(steps):
+                    step()
+                ms = (time.perf_counter() - t0) / steps * 1e3
+                cuda.SetAsync(False)
+                out["legs"][f"{dname}_{leg}"] = {"ms_per_step": round(ms, 3)}
+                for h in mem + [hM]:
+                    cuda.FreeMemory(h)
+                for hC, hA, _, _ in layers:
+                    cuda.FreeAttn(hA)
+                    cuda.FreeCuDNN(hC)
+    finally:
+        cuda.Dispose()
+    return out
+
+
 def run_tft(cx):
     """Config 4: TFT interpretable attention, batch 256, 4 heads, d 64, 192 keys; Nq = 24 (how the TFT net runs it)
     and Nq = 192 (explicit q, k, v mode); forward and backward, L2 flushed before every timed launch (75 MB problem)."""
@@ -1251,11 +1304,11 @@ def run_profile_case(case):
     from mycaffe_b200 import _lib, function_ids as ids
     lib = _lib.load()
     dev = torch.device("cuda", 0)
-    if case in ("tft", "train", "sweep", "backward", "projections", "fp32-prefill"):
+    if case in ("tft", "train", "sweep", "backward", "projections", "fp32-prefill", "train-ids"):
         # the N = 1 legs of the benchmark on their own (same code, same JSON fragment)
         cx = Ctx(argparse.Namespace())
         print(json.dumps({"case": case, case: {"tft": run_tft, "train": run_train, "sweep": run_sweep, "backward": run_backward, "projections": run_projections,
-                                                "fp32-prefill": run_fp32_prefill}[case](cx)}))
+                                                "fp32-prefill": run_fp32_prefill, "train-ids": run_train_function_ids}[case](cx)}))
         return
     if case == "gemv-small":
         dim = DEC_HEADS * DEC_HS
@@ -1565,7 +1618,7 @@ def main():
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="multi-GPU: exchange the head outputs with a NCCL all-gather instead of the kernel's peer stores")
     ap.add_argument("--case", default=None, choices=["prefill-small", "prefill-full", "bwd-small", "decode-small", "gemv-small", "proj-batch", "proj-small", "norm-small", "llama-step", "projections",
-                                                     "tft", "train", "sweep", "backward", "fp32-prefill"],
+                                                     "tft", "train", "sweep", "backward", "fp32-prefill", "train-ids"],
                     help="run one small case a few times and exit (for ncu captures)")
     args = ap.parse_args()
     if args.case:
